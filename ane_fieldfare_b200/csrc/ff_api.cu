@@ -1,0 +1,242 @@
+// Operator entry points of the C ABI: argument checks, path selection by row count, launches.
+#include <string>
+
+#include "ff_internal.cuh"
+
+using namespace ff;
+
+namespace {
+
+struct Call {
+    FFContext *ctx;
+    LayerStore *L;
+    cudaStream_t stream;
+};
+
+bool begin(FFContext *ctx, uint32_t layer, void *stream, const char **error, Call *out) {
+    if (error) *error = nullptr;
+    if (!ctx) return fail(error, "null context");
+    if (layer >= ctx->cfg.layers) return fail(error, "layer " + std::to_string(layer) + " out of range");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    out->ctx = ctx;
+    out->L = &ctx->layers[layer];
+    out->stream = static_cast<cudaStream_t>(stream);
+    return true;
+}
+
+bool check_rows(const FFContext *ctx, const void *x, uint32_t xStride, uint32_t tokens,
+                const char **error) {
+    if (!x) return fail(error, "input pointer is null");
+    if (tokens > ctx->cfg.maxTokens)
+        return fail(error, std::to_string(tokens) + " rows exceed the context's maxTokens " +
+                               std::to_string(ctx->cfg.maxTokens));
+    if (xStride < ctx->cfg.d) return fail(error, "hidden stride is too small");
+    if (xStride % 8 || (reinterpret_cast<uintptr_t>(x) & 15u))
+        return fail(error, "input rows must be 16-byte aligned (stride a multiple of 8 elements)");
+    return true;
+}
+
+bool select_matrix(const Call &c, int32_t expert, uint32_t role, const uint8_t **w,
+                   const uint16_t **s, const uint16_t **b, uint32_t *rows, uint32_t *cols,
+                   const char **error) {
+    if (role > 2) return fail(error, "role must be 0 (gate), 1 (up) or 2 (down)");
+    const FFConfig &cfg = c.ctx->cfg;
+    const uint8_t *blob;
+    const FFExpertOffsets *off;
+    uint32_t f;
+    if (expert < 0) {
+        if (!c.L->shared) return fail(error, "layer has no resident shared FFN");
+        blob = c.L->shared;
+        off = &c.L->sharedOff;
+        f = cfg.sharedF;
+    } else {
+        if (!c.L->experts || (uint32_t)expert >= c.L->expertCount)
+            return fail(error, "expert " + std::to_string(expert) + " is not resident");
+        blob = c.L->experts + (uint64_t)expert * c.L->stride;
+        off = &c.L->off;
+        f = cfg.f;
+    }
+    const uint32_t *o = &off->gateWOff;
+    *w = blob + o[3 * role];
+    *s = reinterpret_cast<const uint16_t *>(blob + o[3 * role + 1]);
+    *b = reinterpret_cast<const uint16_t *>(blob + o[3 * role + 2]);
+    *rows = role == 2 ? cfg.d : f;
+    *cols = role == 2 ? f : cfg.d;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+bool ff_dequant_probe(FFContext *ctx, uint32_t layer, int32_t expert, uint32_t role, float *out,
+                      void *stream, const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    const uint8_t *w;
+    const uint16_t *s, *b;
+    uint32_t rows, cols;
+    if (!select_matrix(c, expert, role, &w, &s, &b, &rows, &cols, error)) return false;
+    return launch_dequant_probe(ctx, w, s, b, rows, cols, out, nullptr, c.stream, error);
+}
+
+bool ff_dequant_probe_bf16(FFContext *ctx, uint32_t layer, int32_t expert, uint32_t role,
+                           uint16_t *out, void *stream, const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    const uint8_t *w;
+    const uint16_t *s, *b;
+    uint32_t rows, cols;
+    if (!select_matrix(c, expert, role, &w, &s, &b, &rows, &cols, error)) return false;
+    return launch_dequant_probe(ctx, w, s, b, rows, cols, nullptr, out, c.stream, error);
+}
+
+bool ff_router_topk(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                    uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
+                    void *stream, const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    if (!check_rows(ctx, x, xStride, tokens, error)) return false;
+    if (!ids || !weights) return fail(error, "output pointer is null");
+    return launch_router_topk(ctx, *c.L, x, xStride, tokens, ids, weights, logits, c.stream, error);
+}
+
+bool ff_moe_decode(FFContext *ctx, uint32_t layer, const uint16_t *x, const uint32_t *ids,
+                   const uint16_t *weights, const uint16_t *residual, uint16_t *y, void *stream,
+                   const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    if (!check_rows(ctx, x, ctx->cfg.d, 1, error)) return false;
+    if (!ids || !weights || !y) return fail(error, "null argument");
+    ctx->lastTokens = 1;
+    return launch_block_small(ctx, *c.L, x, ctx->cfg.d, 1, ids, weights, false, true, residual,
+                              nullptr, nullptr, y, c.stream, error);
+}
+
+bool ff_moe_verify(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                   uint32_t tokens, const uint32_t *ids, uint16_t *partials, void *stream,
+                   const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    if (!check_rows(ctx, x, xStride, tokens, error)) return false;
+    if (!ids || !partials) return fail(error, "null argument");
+    if (tokens > (uint32_t)kMaxGemvRows)
+        return fail(error, std::to_string(tokens) + " pairs for one expert");
+    ctx->lastTokens = tokens;
+    return launch_block_small(ctx, *c.L, x, xStride, tokens, ids, nullptr, false, false, nullptr,
+                              partials, nullptr, nullptr, c.stream, error);
+}
+
+bool ff_moe_prefill(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                    uint32_t tokens, const uint32_t *ids, uint16_t *partials, void *stream,
+                    const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    if (!check_rows(ctx, x, xStride, tokens, error)) return false;
+    if (!ids || !partials) return fail(error, "null argument");
+    ctx->lastTokens = tokens > (uint32_t)kMaxGemvRows ? tokens : kMaxGemvRows + 1;
+    return launch_prefill_routed(ctx, *c.L, x, xStride, tokens, ids, partials, c.stream, error);
+}
+
+bool ff_moe_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *weights,
+                   const uint16_t *residual, uint16_t *y, uint32_t tokens, void *stream,
+                   const char **error) {
+    Call c;
+    if (!begin(ctx, 0, stream, error, &c)) return false;
+    if (!partials || !weights || !y) return fail(error, "null argument");
+    return launch_reduce(ctx, partials, weights, residual, y, tokens, c.stream, error);
+}
+
+bool ff_shared_ffn(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                   uint32_t tokens, uint16_t *y, void *stream, const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    if (!check_rows(ctx, x, xStride, tokens, error)) return false;
+    if (!y) return fail(error, "output pointer is null");
+    if (tokens <= (uint32_t)kMaxGemvRows)
+        return launch_shared_small(ctx, *c.L, x, xStride, tokens, y, c.stream, error);
+    return launch_prefill_shared(ctx, *c.L, x, xStride, tokens, y, c.stream, error);
+}
+
+bool ff_int4_gemv_rows(FFContext *ctx, const FFProjection *projection, const uint16_t *x,
+                       uint32_t xStride, uint32_t rows, uint16_t *y, uint32_t yStride,
+                       void *stream, const char **error) {
+    Call c;
+    if (!begin(ctx, 0, stream, error, &c)) return false;
+    if (!projection || !x || !y) return fail(error, "null argument");
+    if (xStride < projection->cols || yStride < projection->rows)
+        return fail(error, "row stride is too small");
+    if (xStride % 2) return fail(error, "input stride must be even");
+    return launch_gemv_rows(ctx, *projection, x, xStride, rows, y, yStride, c.stream, error);
+}
+
+bool ff_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float eps, uint32_t tokens,
+                uint16_t *y, void *stream, const char **error) {
+    Call c;
+    if (!begin(ctx, 0, stream, error, &c)) return false;
+    if (!x || !y) return fail(error, "null argument");
+    return launch_rmsnorm(ctx, x, w, eps, tokens, y, c.stream, error);
+}
+
+bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t tokens,
+                  uint16_t *y, uint32_t *ids, uint16_t *weights, void *stream,
+                  const char **error) {
+    Call c;
+    if (!begin(ctx, layer, stream, error, &c)) return false;
+    const FFConfig &cfg = ctx->cfg;
+    if (!check_rows(ctx, x, cfg.d, tokens, error)) return false;
+    if (!y) return fail(error, "output pointer is null");
+    if (tokens == 0) return true;
+    LayerStore &L = *c.L;
+    const bool withShared = cfg.sharedF != 0 && L.shared != nullptr;
+    ctx->lastTokens = tokens;
+    const size_t routeCount = (size_t)tokens * cfg.topK;
+    bool ok;
+    if (tokens <= (uint32_t)kMaxGemvRows) {
+        const bool decode = tokens == 1;
+        ok = launch_block_small(ctx, L, x, cfg.d, tokens, nullptr, nullptr, withShared, decode,
+                                nullptr, ctx->partials, ctx->h1, y, c.stream, error);
+        if (ok && !decode)
+            ok = launch_reduce(ctx, ctx->partials, ctx->weights, withShared ? ctx->h1 : nullptr, y,
+                               tokens, c.stream, error);
+    } else {
+        ok = launch_router_topk(ctx, L, x, cfg.d, tokens, ctx->ids, ctx->weights, nullptr, c.stream,
+                                error);
+        if (ok && withShared)
+            ok = launch_prefill_shared(ctx, L, x, cfg.d, tokens, ctx->h1, c.stream, error);
+        ok = ok && launch_prefill_routed(ctx, L, x, cfg.d, tokens, ctx->ids, ctx->partials, c.stream,
+                                         error);
+        ok = ok && launch_reduce(ctx, ctx->partials, ctx->weights, withShared ? ctx->h1 : nullptr, y,
+                                 tokens, c.stream, error);
+    }
+    if (!ok) return false;
+    if (ids)
+        FF_CUDA_OK(cudaMemcpyAsync(ids, ctx->ids, routeCount * sizeof(uint32_t),
+                                   cudaMemcpyDeviceToDevice, c.stream),
+                   error);
+    if (weights)
+        FF_CUDA_OK(cudaMemcpyAsync(weights, ctx->weights, routeCount * sizeof(uint16_t),
+                                   cudaMemcpyDeviceToDevice, c.stream),
+                   error);
+    return true;
+}
+
+bool ff_moe_layer_host(FFContext *ctx, uint32_t layer, const uint16_t *hostX, uint32_t tokens,
+                       uint16_t *hostY, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !hostX || !hostY) return fail(error, "null argument");
+    if (tokens > ctx->cfg.maxTokens) return fail(error, "rows exceed the context's maxTokens");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    const size_t bytes = (size_t)tokens * ctx->cfg.d * sizeof(uint16_t);
+    FF_CUDA_OK(cudaMemcpyAsync(ctx->xDev, hostX, bytes, cudaMemcpyHostToDevice, ctx->hostStream), error);
+    if (!ff_moe_layer(ctx, layer, ctx->xDev, tokens, ctx->yDev, nullptr, nullptr, ctx->hostStream, error))
+        return false;
+    FF_CUDA_OK(cudaMemcpyAsync(hostY, ctx->yDev, bytes, cudaMemcpyDeviceToHost, ctx->hostStream), error);
+    FF_CUDA_OK(cudaStreamSynchronize(ctx->hostStream), error);
+    uint32_t flag = 0;
+    FF_CUDA_OK(cudaMemcpy(&flag, ctx->errorFlag, sizeof(flag), cudaMemcpyDeviceToHost), error);
+    if (flag) return fail(error, "a kernel gave up waiting (error flag " + std::to_string(flag) + ")");
+    return true;
+}
+
+}  // extern "C"

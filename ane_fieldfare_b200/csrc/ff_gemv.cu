@@ -1,0 +1,986 @@
+// Bandwidth kernels of the INT4 MoE block for 1..16 token rows: router, top-K + route plan,
+// grouped INT4 GEMV (gate/up/GeGLU and down), decode combine, token-major reduce, RMSNorm and
+// the dequantization probe.
+//
+// GEMV scheme (every matrix, every row count): a weight row of `cols` 4-bit codes is cut into
+// 16-byte chunks of 32 codes.  Eight lanes share a row; lane j takes chunks j, j+8, j+16, ...
+// with one 128-bit load each, unpacks the codes in registers, and for every input row
+// accumulates  acc = fma(scale, sum(q*x), acc); acc = fma(bias, sum(x), acc)  per chunk; the
+// eight lane sums are added by an xor butterfly (4, 2, 1).  A warp therefore covers four weight
+// rows, and the per-(weight row, input row) arithmetic does not depend on how many input rows a
+// job carries.  Input rows are staged once per job in shared memory as fp32, in an order that
+// makes the eight lanes' 128-bit reads contiguous.
+//
+// Reference kernels this file stands in for (paths inside the reference project):
+//   Sources/ANEFieldfareHotpath/Metal/MoE/moe.metal:65-103,186-319,382-517,548-638
+//   Sources/ANEFieldfareHotpath/Metal/Prefill/prefill.metal:544-565,1246-1529
+//   Sources/ANEFieldfareHotpath/Metal/Quant/dequant_int4.metal:78-347
+#include <algorithm>
+
+#include "ff_internal.cuh"
+
+namespace ff {
+
+constexpr int kGemvThreads = 256;
+constexpr int kRowsPerItem = (kGemvThreads / 32) * 4;
+constexpr int kDecodeDownRows = 8;  // output rows per CTA of the decode combine kernel
+
+__device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+
+// Round-half-even on the dropped 16 bits: Quantization.bf16Bits
+// (Sources/ANEFieldfareHotpath/Infrastructure/ModelIO/Quantization.swift:9-16).
+__device__ __forceinline__ uint16_t f2bf(float f) {
+    uint32_t u = __float_as_uint(f);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+__device__ __forceinline__ float bf16_round(float f) { return bf2f(f2bf(f)); }
+
+// gelu_pytorch_tanh with the kernels' clamp (Metal/MoE/moe.metal:40-47).
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float x3 = x * x * x;
+    float inner = 0.7978845608028654f * (x + 0.044715f * x3);
+    inner = fminf(fmaxf(inner, -20.0f), 20.0f);
+    return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+// Position of input element e inside a staged row: chunks are interleaved in blocks of eight so
+// that lanes j = 0..7 (chunks c = 8i + j) read one contiguous 128 bytes per 128-bit load.
+__device__ __forceinline__ int staged_index(int e) {
+    const int c = e >> 5;
+    return ((c >> 3) << 8) + (((e >> 2) & 7) << 5) + ((c & 7) << 2) + (e & 3);
+}
+__host__ __device__ inline int staged_stride(int cols) { return (cols + 255) & ~255; }
+
+// Eight codes of one 32-bit word as the floats 16+q: the code goes into the top mantissa bits of
+// a float whose exponent is 2^4.  The surplus 16*sum(x) is taken out once per chunk through the
+// bias term, so no per-code subtraction is needed.
+__device__ __forceinline__ void unpack8_plus16(uint32_t w, float (&q)[8]) {
+    constexpr uint32_t kMask = 0x00780000u, kBase = 0x41800000u;
+    q[0] = __uint_as_float(((w << 19) & kMask) | kBase);
+    q[1] = __uint_as_float(((w << 15) & kMask) | kBase);
+    q[2] = __uint_as_float(((w << 11) & kMask) | kBase);
+    q[3] = __uint_as_float(((w << 7) & kMask) | kBase);
+    q[4] = __uint_as_float(((w << 3) & kMask) | kBase);
+    q[5] = __uint_as_float(((w >> 1) & kMask) | kBase);
+    q[6] = __uint_as_float(((w >> 5) & kMask) | kBase);
+    q[7] = __uint_as_float(((w >> 9) & kMask) | kBase);
+}
+
+__device__ __forceinline__ uint4 load_stream(const uint4 *p) { return __ldcs(p); }
+
+// Stages n bf16 input rows (indices rowIdx[0..n)) as fp32 in chunk-interleaved order, then the
+// per-chunk sums of each row.  All threads of the CTA take part.
+__device__ void stage_rows(const uint16_t *in, uint32_t inStride, const uint32_t *rowIdx, int n,
+                           int cols, float *xs, float *xsum) {
+    const int stride = staged_stride(cols);
+    const int chunks = cols >> 5;
+    const int pairsPerRow = cols >> 1;
+    for (int i = threadIdx.x; i < n * pairsPerRow; i += blockDim.x) {
+        const int r = i / pairsPerRow, p = i - r * pairsPerRow;
+        const uint32_t two =
+            *reinterpret_cast<const uint32_t *>(in + (size_t)rowIdx[r] * inStride + 2 * p);
+        float *dst = xs + r * stride + staged_index(2 * p);
+        dst[0] = __uint_as_float(two << 16);
+        dst[1] = __uint_as_float(two & 0xFFFF0000u);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * chunks; i += blockDim.x) {
+        const int r = i / chunks, c = i - r * chunks;
+        const float *src = xs + r * stride + ((c >> 3) << 8) + ((c & 7) << 2);
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float4 v = *reinterpret_cast<const float4 *>(src + (k << 5));
+            s += v.x;
+            s += v.y;
+            s += v.z;
+            s += v.w;
+        }
+        xsum[r * chunks + c] = s;
+    }
+    __syncthreads();
+}
+
+// One weight row (or a gate/up row pair) against NT staged input rows; returns the full sums in
+// every lane of the row's eight-lane group.  `live` false skips the loads but keeps the
+// shuffles convergent.
+template <int NT, bool DUAL>
+__device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, const uint16_t *b0,
+                                        const uint8_t *w1, const uint16_t *s1, const uint16_t *b1,
+                                        int row, int cols, bool live, const float *xs,
+                                        const float *xsum, int n, float (&a0)[NT],
+                                        float (&a1)[NT]) {
+    const int lane = threadIdx.x & 31;
+    const int j = lane & 7;
+    const int chunks = cols >> 5;
+    const int groups = cols >> 6;
+    const int stride = staged_stride(cols);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        a0[t] = 0.0f;
+        a1[t] = 0.0f;
+    }
+    if (live) {
+        const uint4 *p0 = reinterpret_cast<const uint4 *>(w0 + (size_t)row * (cols >> 1));
+        const uint4 *p1 = DUAL ? reinterpret_cast<const uint4 *>(w1 + (size_t)row * (cols >> 1)) : p0;
+        const uint16_t *sr0 = s0 + (size_t)row * groups, *br0 = b0 + (size_t)row * groups;
+        const uint16_t *sr1 = DUAL ? s1 + (size_t)row * groups : sr0;
+        const uint16_t *br1 = DUAL ? b1 + (size_t)row * groups : br0;
+        for (int c = j; c < chunks; c += 8) {
+            const uint4 v0 = load_stream(p0 + c);
+            uint4 v1 = v0;
+            if (DUAL) v1 = load_stream(p1 + c);
+            const float sc0 = bf2f(sr0[c >> 1]);
+            const float bi0 = fmaf(-16.0f, sc0, bf2f(br0[c >> 1]));
+            float sc1 = 0.0f, bi1 = 0.0f;
+            if (DUAL) {
+                sc1 = bf2f(sr1[c >> 1]);
+                bi1 = fmaf(-16.0f, sc1, bf2f(br1[c >> 1]));
+            }
+            float d0[NT], d1[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                d0[t] = 0.0f;
+                d1[t] = 0.0f;
+            }
+            const float *xc = xs + ((c >> 3) << 8) + ((c & 7) << 2);
+            const uint32_t words0[4] = {v0.x, v0.y, v0.z, v0.w};
+            const uint32_t words1[4] = {v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float q0[8], q1[8];
+                unpack8_plus16(words0[k], q0);
+                if (DUAL) unpack8_plus16(words1[k], q1);
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const float *xt = xc + (t < n ? t : 0) * stride + (k << 6);
+                    const float4 xa = *reinterpret_cast<const float4 *>(xt);
+                    const float4 xb = *reinterpret_cast<const float4 *>(xt + 32);
+                    float acc = d0[t];
+                    acc = fmaf(q0[0], xa.x, acc);
+                    acc = fmaf(q0[1], xa.y, acc);
+                    acc = fmaf(q0[2], xa.z, acc);
+                    acc = fmaf(q0[3], xa.w, acc);
+                    acc = fmaf(q0[4], xb.x, acc);
+                    acc = fmaf(q0[5], xb.y, acc);
+                    acc = fmaf(q0[6], xb.z, acc);
+                    acc = fmaf(q0[7], xb.w, acc);
+                    d0[t] = acc;
+                    if (DUAL) {
+                        float acu = d1[t];
+                        acu = fmaf(q1[0], xa.x, acu);
+                        acu = fmaf(q1[1], xa.y, acu);
+                        acu = fmaf(q1[2], xa.z, acu);
+                        acu = fmaf(q1[3], xa.w, acu);
+                        acu = fmaf(q1[4], xb.x, acu);
+                        acu = fmaf(q1[5], xb.y, acu);
+                        acu = fmaf(q1[6], xb.z, acu);
+                        acu = fmaf(q1[7], xb.w, acu);
+                        d1[t] = acu;
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const float sx = xsum[(t < n ? t : 0) * chunks + c];
+                a0[t] = fmaf(sc0, d0[t], a0[t]);
+                a0[t] = fmaf(bi0, sx, a0[t]);
+                if (DUAL) {
+                    a1[t] = fmaf(sc1, d1[t], a1[t]);
+                    a1[t] = fmaf(bi1, sx, a1[t]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+#pragma unroll
+        for (int offset = 4; offset >= 1; offset >>= 1) {
+            a0[t] += __shfl_xor_sync(0xFFFFFFFFu, a0[t], offset);
+            if (DUAL) a1[t] += __shfl_xor_sync(0xFFFFFFFFu, a1[t], offset);
+        }
+    }
+}
+
+template <int NT, bool DUAL>
+__device__ __forceinline__ void run_item(const GemvJob &job, int row0, const float *xs,
+                                         const float *xsum) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = row0 + warp * 4 + (lane >> 3);
+    const bool live = row < (int)job.rows;
+    float a0[NT], a1[NT];
+    row_dot<NT, DUAL>(job.w0, job.s0, job.b0, job.w1, job.s1, job.b1, row, (int)job.cols, live, xs,
+                      xsum, (int)job.n, a0, a1);
+    if (live && (lane & 7) == 0) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            if (t < (int)job.n) {
+                float v = a0[t];
+                if (DUAL) {
+                    float g = a0[t], u = a1[t];
+                    if (job.flags & kJobRoundGateUp) {
+                        g = bf16_round(g);
+                        u = bf16_round(u);
+                    }
+                    v = gelu_tanh(g) * u;
+                }
+                job.out[(size_t)job.outRow[t] * job.outStride + row] = f2bf(v);
+            }
+        }
+    }
+}
+
+// Persistent grouped GEMV: each CTA takes a contiguous range of (job, row block) items, restaging
+// the input rows only when the job changes.  With `jobs` null the single `inlineJob` is used.
+template <int MAXNT, bool DUAL>
+__global__ void __launch_bounds__(kGemvThreads)
+k_int4_gemv(const GemvJob *jobs, const uint32_t *items, const uint32_t *itemCountPtr,
+            GemvJob inlineJob, uint32_t inlineItems, uint32_t maxCols) {
+    extern __shared__ float smem[];
+    __shared__ GemvJob sjob;
+    float *xs = smem;
+    float *xsum = smem + MAXNT * staged_stride((int)maxCols);
+    const uint32_t nItems = jobs ? *itemCountPtr : inlineItems;
+    const uint32_t per = (nItems + gridDim.x - 1) / gridDim.x;
+    const uint32_t begin = blockIdx.x * per;
+    const uint32_t end = min(nItems, begin + per);
+    int current = -1;
+    for (uint32_t it = begin; it < end; ++it) {
+        uint32_t jobIdx = 0, block = it;
+        if (jobs) {
+            const uint32_t packed = items[it];
+            jobIdx = packed >> 16;
+            block = packed & 0xFFFFu;
+        }
+        if ((int)jobIdx != current) {
+            __syncthreads();
+            const uint32_t *src =
+                reinterpret_cast<const uint32_t *>(jobs ? jobs + jobIdx : &inlineJob);
+            uint32_t *dst = reinterpret_cast<uint32_t *>(&sjob);
+            for (int i = threadIdx.x; i < (int)(sizeof(GemvJob) / 4); i += blockDim.x) dst[i] = src[i];
+            __syncthreads();
+            stage_rows(sjob.in, sjob.inStride, sjob.inRow, min((int)sjob.n, MAXNT), (int)sjob.cols,
+                       xs, xsum);
+            current = (int)jobIdx;
+        }
+        const int row0 = (int)block * kRowsPerItem;
+        const int n = (int)sjob.n;
+        if (n <= 1) {
+            run_item<1, DUAL>(sjob, row0, xs, xsum);
+        } else if (MAXNT >= 2 && n <= 2) {
+            run_item<(MAXNT >= 2 ? 2 : 1), DUAL>(sjob, row0, xs, xsum);
+        } else if (MAXNT >= 4 && n <= 4) {
+            run_item<(MAXNT >= 4 ? 4 : 1), DUAL>(sjob, row0, xs, xsum);
+        } else if (MAXNT >= 8 && n <= 8) {
+            run_item<(MAXNT >= 8 ? 8 : 1), DUAL>(sjob, row0, xs, xsum);
+        } else if (MAXNT >= 16) {
+            run_item<(MAXNT >= 16 ? 16 : 1), DUAL>(sjob, row0, xs, xsum);
+        }
+    }
+}
+
+// Decode combine (Metal/MoE/moe.metal:597-638): for kDecodeDownRows output rows, warp w computes
+// slot (w & 7)'s down row dots; then y = bf16(residual + sum over slots in order of w_k * v_k).
+__global__ void __launch_bounds__(512)
+k_decode_down(const uint8_t *experts, uint64_t stride, FFExpertOffsets off, const uint32_t *ids,
+              const uint16_t *weights, const uint16_t *acts, const uint16_t *residual, uint16_t *y,
+              int D, int F, int K) {
+    extern __shared__ float smem[];
+    __shared__ float partial[8][kDecodeDownRows];
+    __shared__ uint32_t rowIdx[8];
+    const int strideF = staged_stride(F);
+    float *xs = smem;
+    float *xsum = smem + 8 * strideF;
+    if (threadIdx.x < 8) rowIdx[threadIdx.x] = threadIdx.x;
+    __syncthreads();
+    stage_rows(acts, (uint32_t)F, rowIdx, K, F, xs, xsum);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = warp & 7;
+    const int local = (warp >> 3) * 4 + (lane >> 3);
+    const int row = blockIdx.x * kDecodeDownRows + local;
+    const bool live = slot < K && row < D;
+    const uint8_t *blob = experts + (size_t)(slot < K ? ids[slot] : 0) * stride;
+    float a0[1], a1[1];
+    row_dot<1, false>(blob + off.downWOff, reinterpret_cast<const uint16_t *>(blob + off.downSOff),
+                      reinterpret_cast<const uint16_t *>(blob + off.downBOff), nullptr, nullptr,
+                      nullptr, row, F, live, xs + slot * strideF, xsum + slot * (F >> 5), 1, a0, a1);
+    if ((lane & 7) == 0) partial[slot][local] = live ? bf2f(weights[slot]) * a0[0] : 0.0f;
+    __syncthreads();
+    if (threadIdx.x < kDecodeDownRows) {
+        const int d = blockIdx.x * kDecodeDownRows + threadIdx.x;
+        if (d < D) {
+            float acc = residual ? bf2f(residual[d]) : 0.0f;
+            for (int k = 0; k < K; ++k) acc += partial[k][threadIdx.x];
+            y[d] = f2bf(acc);
+        }
+    }
+}
+
+// ---- router --------------------------------------------------------------------------------
+
+// One warp per (expert, token).  The reduction order is part of the contract (top-K indices are
+// compared for equality with the CPU oracle): lane l chains fmaf over elements
+// [256 i + 8 l, +8) for i = 0, 1, ... in increasing index, the lane sums are added by an xor
+// butterfly (16, 8, 4, 2, 1), then the per-expert logit bias is added.
+__global__ void __launch_bounds__(256)
+k_router_logits(const uint16_t *W, const uint16_t *scale, const float *bias, const uint16_t *x,
+                uint32_t xStride, int E, int D, float *logits) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    const int t = blockIdx.y;
+    if (e >= E) return;
+    const uint16_t *wr = W + (size_t)e * D;
+    const uint16_t *xr = x + (size_t)t * xStride;
+    float acc = 0.0f;
+    for (int base = 8 * lane; base < D; base += 256) {
+        const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
+        const uint4 xv = *reinterpret_cast<const uint4 *>(xr + base);
+        uint4 sv = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+        if (scale) sv = *reinterpret_cast<const uint4 *>(scale + base);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
+        const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float x0 = __uint_as_float(xx[k] << 16), x1 = __uint_as_float(xx[k] & 0xFFFF0000u);
+            if (scale) {
+                x0 = x0 * __uint_as_float(ss[k] << 16);
+                x1 = x1 * __uint_as_float(ss[k] & 0xFFFF0000u);
+            }
+            acc = fmaf(__uint_as_float(ww[k] << 16), x0, acc);
+            acc = fmaf(__uint_as_float(ww[k] & 0xFFFF0000u), x1, acc);
+        }
+    }
+#pragma unroll
+    for (int offset = 16; offset >= 1; offset >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
+    if (lane == 0) logits[(size_t)t * E + e] = bias ? acc + bias[e] : acc;
+}
+
+// Warp-wide top-K over E <= 256 logits held four-plus per lane: K rounds of argmax (higher score,
+// then lower expert id), softmax over the selected scores, times the per-expert gain.  Selection
+// rule and softmax: Metal/MoE/moe.metal:186-237,269-319.
+__device__ void warp_topk(const float *logits, int E, int K, const uint16_t *gain, uint32_t *ids,
+                          uint16_t *weights) {
+    const int lane = threadIdx.x & 31;
+    float v[8];
+    bool live[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int e = j * 32 + lane;
+        v[j] = e < E ? logits[e] : -INFINITY;
+        live[j] = e < E && v[j] > -INFINITY;
+    }
+    float topScore[8];
+    uint32_t topIdx[8];
+    for (int r = 0; r < 8; ++r) {
+        float best = -INFINITY;
+        uint32_t bestE = 0xFFFFFFFFu;
+        if (r < K) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t e = (uint32_t)(j * 32 + lane);
+                if (live[j] && (v[j] > best || (v[j] == best && e < bestE))) {
+                    best = v[j];
+                    bestE = e;
+                }
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset >= 1; offset >>= 1) {
+            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, offset);
+            const uint32_t oe = __shfl_xor_sync(0xFFFFFFFFu, bestE, offset);
+            if (oe != 0xFFFFFFFFu && (bestE == 0xFFFFFFFFu || ob > best || (ob == best && oe < bestE))) {
+                best = ob;
+                bestE = oe;
+            }
+        }
+        if (bestE != 0xFFFFFFFFu && (bestE & 31u) == (uint32_t)lane) live[bestE >> 5] = false;
+        topIdx[r] = bestE == 0xFFFFFFFFu ? 0u : bestE;
+        topScore[r] = bestE == 0xFFFFFFFFu ? -INFINITY : best;
+    }
+    if (lane == 0) {
+        float ex[8], sum = 0.0f;
+        for (int r = 0; r < K; ++r) {
+            ex[r] = expf(topScore[r] - topScore[0]);
+            sum += ex[r];
+        }
+        for (int r = 0; r < K; ++r) {
+            float w = ex[r] / sum;
+            if (gain) w = w * bf2f(gain[topIdx[r]]);
+            ids[r] = topIdx[r];
+            weights[r] = f2bf(w);
+        }
+    }
+}
+
+struct PlanArgs {
+    const float *logits;      // [T][E] or null (ids given)
+    const uint16_t *gain;
+    const uint32_t *idsIn;    // used when logits is null
+    uint32_t *idsOut;         // written when logits is given
+    uint16_t *weightsOut;
+    int T, E, K, D, F, Fs;
+    const uint8_t *experts;
+    uint64_t stride;
+    FFExpertOffsets off;
+    const uint8_t *shared;    // null: no shared job
+    FFExpertOffsets sharedOff;
+    const uint16_t *x;
+    uint32_t xStride;
+    uint16_t *acts;
+    uint16_t *sharedActs;
+    uint16_t *partials;       // null in decode mode: no routed down jobs
+    uint16_t *sharedOut;
+    GemvJob *jobs0, *jobs1;
+    uint32_t *items0, *items1;
+    RoutePlan *plan;
+    int buildPlan;            // 0: top-K only
+};
+
+// One CTA: top-K per token (when logits are given), then the route plan — the role of the
+// reference's verify_bound_plan (Metal/Prefill/prefill.metal:1458-1493): per active expert the
+// routes that chose it, in (token, rank) order, as one gate/up job and one down job, experts
+// ascending; the shared FFN is job 0 of each phase.
+__global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
+    __shared__ uint32_t sIds[kMaxGemvRows * 8];
+    __shared__ uint32_t sPos[kMaxExperts];
+    __shared__ uint32_t sActive;
+    const int warp = threadIdx.x >> 5;
+    const int routes = a.T * a.K;
+    if (a.logits) {
+        if (warp < a.T) {
+            warp_topk(a.logits + (size_t)warp * a.E, a.E, a.K, a.gain, a.idsOut + warp * a.K,
+                      a.weightsOut + warp * a.K);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < routes; i += blockDim.x) sIds[i] = a.idsOut[i];
+    } else {
+        for (int i = threadIdx.x; i < routes; i += blockDim.x) sIds[i] = a.idsIn[i];
+    }
+    if (!a.buildPlan) return;
+    __syncthreads();
+    const int e = threadIdx.x;
+    uint32_t list[kMaxGemvRows];
+    int n = 0;
+    if (e < a.E) {
+        for (int r = 0; r < routes; ++r)
+            if (sIds[r] == (uint32_t)e && n < kMaxGemvRows) list[n++] = (uint32_t)r;
+        sPos[e] = n > 0 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (int i = 0; i < a.E; ++i) {
+            const uint32_t flag = sPos[i];
+            sPos[i] = run;
+            run += flag;
+        }
+        sActive = run;
+    }
+    __syncthreads();
+    const uint32_t sharedJobs = a.shared ? 1u : 0u;
+    const uint32_t active = sActive;
+    if (e < a.E && n > 0) {
+        const uint8_t *blob = a.experts + (size_t)e * a.stride;
+        GemvJob j0{};
+        j0.w0 = blob + a.off.gateWOff;
+        j0.s0 = reinterpret_cast<const uint16_t *>(blob + a.off.gateSOff);
+        j0.b0 = reinterpret_cast<const uint16_t *>(blob + a.off.gateBOff);
+        j0.w1 = blob + a.off.upWOff;
+        j0.s1 = reinterpret_cast<const uint16_t *>(blob + a.off.upSOff);
+        j0.b1 = reinterpret_cast<const uint16_t *>(blob + a.off.upBOff);
+        j0.in = a.x;
+        j0.out = a.acts;
+        j0.rows = (uint32_t)a.F;
+        j0.cols = (uint32_t)a.D;
+        j0.inStride = a.xStride;
+        j0.outStride = (uint32_t)a.F;
+        j0.n = (uint32_t)n;
+        j0.flags = 0;
+        for (int i = 0; i < kMaxGemvRows; ++i) {
+            j0.inRow[i] = i < n ? list[i] / (uint32_t)a.K : 0u;
+            j0.outRow[i] = i < n ? list[i] : 0u;
+        }
+        a.jobs0[sharedJobs + sPos[e]] = j0;
+        if (a.partials) {
+            GemvJob j1{};
+            j1.w0 = blob + a.off.downWOff;
+            j1.s0 = reinterpret_cast<const uint16_t *>(blob + a.off.downSOff);
+            j1.b0 = reinterpret_cast<const uint16_t *>(blob + a.off.downBOff);
+            j1.in = a.acts;
+            j1.out = a.partials;
+            j1.rows = (uint32_t)a.D;
+            j1.cols = (uint32_t)a.F;
+            j1.inStride = (uint32_t)a.F;
+            j1.outStride = (uint32_t)a.D;
+            j1.n = (uint32_t)n;
+            for (int i = 0; i < kMaxGemvRows; ++i) {
+                j1.inRow[i] = i < n ? list[i] : 0u;
+                j1.outRow[i] = i < n ? list[i] : 0u;
+            }
+            a.jobs1[sharedJobs + sPos[e]] = j1;
+        }
+    }
+    if (threadIdx.x == 0 && a.shared) {
+        GemvJob j0{};
+        j0.w0 = a.shared + a.sharedOff.gateWOff;
+        j0.s0 = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.gateSOff);
+        j0.b0 = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.gateBOff);
+        j0.w1 = a.shared + a.sharedOff.upWOff;
+        j0.s1 = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.upSOff);
+        j0.b1 = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.upBOff);
+        j0.in = a.x;
+        j0.out = a.sharedActs;
+        j0.rows = (uint32_t)a.Fs;
+        j0.cols = (uint32_t)a.D;
+        j0.inStride = a.xStride;
+        j0.outStride = (uint32_t)a.Fs;
+        j0.n = (uint32_t)a.T;
+        j0.flags = kJobRoundGateUp;
+        GemvJob j1{};
+        j1.w0 = a.shared + a.sharedOff.downWOff;
+        j1.s0 = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.downSOff);
+        j1.b0 = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.downBOff);
+        j1.in = a.sharedActs;
+        j1.out = a.sharedOut;
+        j1.rows = (uint32_t)a.D;
+        j1.cols = (uint32_t)a.Fs;
+        j1.inStride = (uint32_t)a.Fs;
+        j1.outStride = (uint32_t)a.D;
+        j1.n = (uint32_t)a.T;
+        for (int i = 0; i < kMaxGemvRows; ++i) {
+            j0.inRow[i] = j0.outRow[i] = j1.inRow[i] = j1.outRow[i] = i < a.T ? (uint32_t)i : 0u;
+        }
+        a.jobs0[0] = j0;
+        a.jobs1[0] = j1;
+    }
+    // work items: shared job first, then every routed job, each cut into row blocks
+    const uint32_t sharedBlocks0 = a.shared ? (uint32_t)((a.Fs + kRowsPerItem - 1) / kRowsPerItem) : 0u;
+    const uint32_t routedBlocks0 = (uint32_t)((a.F + kRowsPerItem - 1) / kRowsPerItem);
+    const uint32_t total0 = sharedBlocks0 + active * routedBlocks0;
+    for (uint32_t i = threadIdx.x; i < total0; i += blockDim.x) {
+        uint32_t job, block;
+        if (i < sharedBlocks0) {
+            job = 0;
+            block = i;
+        } else {
+            job = sharedJobs + (i - sharedBlocks0) / routedBlocks0;
+            block = (i - sharedBlocks0) % routedBlocks0;
+        }
+        a.items0[i] = (job << 16) | block;
+    }
+    const uint32_t downBlocks = (uint32_t)((a.D + kRowsPerItem - 1) / kRowsPerItem);
+    const uint32_t sharedBlocks1 = a.shared ? downBlocks : 0u;
+    const uint32_t routedJobs1 = a.partials ? active : 0u;
+    const uint32_t total1 = sharedBlocks1 + routedJobs1 * downBlocks;
+    for (uint32_t i = threadIdx.x; i < total1; i += blockDim.x) {
+        uint32_t job, block;
+        if (i < sharedBlocks1) {
+            job = 0;
+            block = i;
+        } else {
+            job = sharedJobs + (i - sharedBlocks1) / downBlocks;
+            block = (i - sharedBlocks1) % downBlocks;
+        }
+        a.items1[i] = (job << 16) | block;
+    }
+    if (threadIdx.x == 0) {
+        a.plan->jobCount[0] = sharedJobs + active;
+        a.plan->jobCount[1] = sharedJobs + routedJobs1;
+        a.plan->itemCount[0] = total0;
+        a.plan->itemCount[1] = total1;
+        a.plan->activeExperts = active;
+    }
+}
+
+// Metal/Prefill/prefill.metal:544-565 plus an optional residual row added after the ranks.
+__global__ void __launch_bounds__(256)
+k_reduce_token_major(const uint16_t *partials, const uint16_t *weights, const uint16_t *residual,
+                     uint16_t *y, int T, int K, int D) {
+    const int t = blockIdx.y;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (t >= T || d >= D) return;
+    float acc0 = 0.0f, acc1 = 0.0f;
+    for (int r = 0; r < K; ++r) {
+        const float w = bf2f(weights[(size_t)t * K + r]);
+        const uint32_t two =
+            *reinterpret_cast<const uint32_t *>(partials + ((size_t)t * K + r) * D + d);
+        acc0 = fmaf(w, __uint_as_float(two << 16), acc0);
+        acc1 = fmaf(w, __uint_as_float(two & 0xFFFF0000u), acc1);
+    }
+    if (residual) {
+        const uint32_t two = *reinterpret_cast<const uint32_t *>(residual + (size_t)t * D + d);
+        acc0 += __uint_as_float(two << 16);
+        acc1 += __uint_as_float(two & 0xFFFF0000u);
+    }
+    *reinterpret_cast<uint32_t *>(y + (size_t)t * D + d) =
+        (uint32_t)f2bf(acc0) | ((uint32_t)f2bf(acc1) << 16);
+}
+
+// y = x * w * rsqrt(mean(x^2) + eps) per row; one CTA per row, fp32 throughout.
+__global__ void __launch_bounds__(256)
+k_rmsnorm(const uint16_t *x, const uint16_t *w, float eps, int D, uint16_t *y) {
+    __shared__ float warpSums[8];
+    __shared__ float inv;
+    const uint16_t *xr = x + (size_t)blockIdx.x * D;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = bf2f(xr[i]);
+        sum = fmaf(v, v, sum);
+    }
+#pragma unroll
+    for (int offset = 16; offset >= 1; offset >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, offset);
+    if ((threadIdx.x & 31) == 0) warpSums[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int i = 0; i < 8; ++i) total += warpSums[i];
+        inv = 1.0f / sqrtf(total / (float)D + eps);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float wv = w ? bf2f(w[i]) : 1.0f;
+        y[(size_t)blockIdx.x * D + i] = f2bf(bf2f(xr[i]) * wv * inv);
+    }
+}
+
+// w = q*scale + bias for a whole matrix, fp32 and/or bf16 (one rounding of the exact value:
+// a bf16 fused multiply-add).  One thread per 8 codes.
+__global__ void __launch_bounds__(256)
+k_dequant_probe(const uint8_t *w, const uint16_t *s, const uint16_t *b, int rows, int cols,
+                float *out32, uint16_t *out16) {
+    const size_t word = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t wordsPerRow = (size_t)cols / 8;
+    if (word >= (size_t)rows * wordsPerRow) return;
+    const size_t row = word / wordsPerRow;
+    const int col = (int)(word - row * wordsPerRow) * 8;
+    const uint32_t packed = reinterpret_cast<const uint32_t *>(w)[word];
+    const size_t g = row * (size_t)(cols / kGroup) + (size_t)(col / kGroup);
+    const float scale = bf2f(s[g]), bias = bf2f(b[g]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float q = (float)((packed >> (4 * k)) & 0xFu);
+        if (out32) out32[row * cols + col + k] = fmaf(q, scale, bias);
+        if (out16) {
+            // exact in double, then one rounding to bf16 via round-to-odd fp32
+            const double exact = (double)q * (double)scale + (double)bias;
+            float f = __double2float_rz(exact);
+            if ((double)f != exact) f = __uint_as_float(__float_as_uint(f) | 1u);
+            out16[row * cols + col + k] = f2bf(f);
+        }
+    }
+}
+
+// ---- host launchers ------------------------------------------------------------------------
+
+static size_t gemv_smem_bytes(int maxNt, uint32_t maxCols) {
+    return (size_t)maxNt * (staged_stride((int)maxCols) + (maxCols >> 5)) * sizeof(float);
+}
+
+template <int MAXNT, bool DUAL>
+static bool launch_gemv_kernel(FFContext *ctx, const GemvJob *jobs, const uint32_t *items,
+                               const uint32_t *itemCountPtr, const GemvJob &inlineJob,
+                               uint32_t inlineItems, uint32_t maxCols, uint32_t itemBound,
+                               cudaStream_t stream, const char **error) {
+    auto kernel = k_int4_gemv<MAXNT, DUAL>;
+    const size_t smem = gemv_smem_bytes(MAXNT, maxCols);
+    if (smem > 200 * 1024)
+        return fail(error, "input rows do not fit in shared memory: " + std::to_string(MAXNT) +
+                               " rows x " + std::to_string(maxCols) + " columns");
+    // attribute + occupancy are looked up once per (kernel, shared-memory size): nothing but the
+    // launch itself happens on later calls, which keeps the call legal under stream capture
+    static size_t cachedSmem[8] = {0};
+    static int cachedPerSm[8] = {0};
+    static int cachedDevice[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+    int perSm = 0;
+    const int slot = ctx->device & 7;
+    if (cachedDevice[slot] == ctx->device && cachedSmem[slot] == smem) {
+        perSm = cachedPerSm[slot];
+    } else {
+        FF_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem),
+                   error);
+        FF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, kGemvThreads, smem),
+                   error);
+        cachedDevice[slot] = ctx->device;
+        cachedSmem[slot] = smem;
+        cachedPerSm[slot] = perSm;
+    }
+    if (perSm < 1) return fail(error, "GEMV kernel does not fit on an SM");
+    uint32_t grid = (uint32_t)(ctx->smCount * perSm);
+    if (itemBound < grid) grid = itemBound;
+    if (grid == 0) return true;
+    {
+        LaunchScope scope(ctx, stream, DUAL ? "int4_gemv_gate_up_act" : "int4_gemv_down");
+        kernel<<<grid, kGemvThreads, smem, stream>>>(jobs, items, itemCountPtr, inlineJob,
+                                                     inlineItems, maxCols);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+template <bool DUAL>
+static bool launch_gemv_class(FFContext *ctx, uint32_t rowsClass, const GemvJob *jobs,
+                              const uint32_t *items, const uint32_t *itemCountPtr,
+                              const GemvJob &inlineJob, uint32_t inlineItems, uint32_t maxCols,
+                              uint32_t itemBound, cudaStream_t stream, const char **error) {
+    if (rowsClass <= 1)
+        return launch_gemv_kernel<1, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
+                                           maxCols, itemBound, stream, error);
+    if (rowsClass <= 2)
+        return launch_gemv_kernel<2, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
+                                           maxCols, itemBound, stream, error);
+    if (rowsClass <= 4)
+        return launch_gemv_kernel<4, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
+                                           maxCols, itemBound, stream, error);
+    if (rowsClass <= 8)
+        return launch_gemv_kernel<8, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
+                                           maxCols, itemBound, stream, error);
+    return launch_gemv_kernel<16, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
+                                        maxCols, itemBound, stream, error);
+}
+
+static uint32_t blocks_of(uint32_t rows) { return (rows + kRowsPerItem - 1) / kRowsPerItem; }
+
+bool launch_router_topk(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                        uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
+                        cudaStream_t stream, const char **error) {
+    if (tokens == 0) return true;
+    if (!L.routerW) return fail(error, "layer has no resident router");
+    if (tokens > kMaxGemvRows)
+        return launch_router_prefill(ctx, L, x, xStride, tokens, ids, weights, logits, stream, error);
+    const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
+    float *lg = logits ? logits : ctx->logits;
+    dim3 grid((E + 7) / 8, tokens);
+    {
+        LaunchScope scope(ctx, stream, "router_logits");
+        k_router_logits<<<grid, 256, 0, stream>>>(L.routerW, L.routerScale, L.logitBias, x, xStride,
+                                                  E, D, lg);
+    }
+    PlanArgs a{};
+    a.logits = lg;
+    a.gain = L.gain;
+    a.idsOut = ids;
+    a.weightsOut = weights;
+    a.T = (int)tokens;
+    a.E = E;
+    a.K = (int)ctx->cfg.topK;
+    a.buildPlan = 0;
+    {
+        LaunchScope scope(ctx, stream, "topk_plan");
+        k_topk_plan<<<1, 512, 0, stream>>>(a);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+// Router top-K (when ids is null) + routed experts (+ shared FFN) for up to 16 rows.
+//   decodeCombine: one row; y = bf16(residual' + sum_k w_k v_k), residual' = shared output when
+//                  withShared else `residual`.
+//   otherwise:     partial rows are written; sharedOut receives the shared FFN rows.
+bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                        uint32_t tokens, const uint32_t *ids, const uint16_t *weights,
+                        bool withShared, bool decodeCombine, const uint16_t *residual,
+                        uint16_t *partials, uint16_t *sharedOut, uint16_t *y,
+                        cudaStream_t stream, const char **error) {
+    const FFConfig &c = ctx->cfg;
+    if (tokens == 0) return true;
+    if (tokens > kMaxGemvRows) return fail(error, "more than 16 rows in a decode/verify block");
+    if (decodeCombine && tokens != 1) return fail(error, "decode combine takes exactly one row");
+    if (!L.experts) return fail(error, "layer has no resident experts");
+    if (withShared && !L.shared) return fail(error, "layer has no resident shared FFN");
+    const int E = (int)L.expertCount;
+    PlanArgs a{};
+    uint32_t *idsDev = ctx->ids;
+    uint16_t *weightsDev = ctx->weights;
+    if (!ids) {
+        if (!L.routerW) return fail(error, "layer has no resident router");
+        dim3 grid((L.routerExperts + 7) / 8, tokens);
+        {
+            LaunchScope scope(ctx, stream, "router_logits");
+            k_router_logits<<<grid, 256, 0, stream>>>(L.routerW, L.routerScale, L.logitBias, x,
+                                                      xStride, (int)L.routerExperts, (int)c.d,
+                                                      ctx->logits);
+        }
+        a.logits = ctx->logits;
+        a.gain = L.gain;
+        a.idsOut = idsDev;
+        a.weightsOut = weightsDev;
+    } else {
+        a.idsIn = ids;
+        idsDev = const_cast<uint32_t *>(ids);
+        weightsDev = const_cast<uint16_t *>(weights);
+    }
+    a.T = (int)tokens;
+    a.E = E;
+    a.K = (int)c.topK;
+    a.D = (int)c.d;
+    a.F = (int)c.f;
+    a.Fs = (int)c.sharedF;
+    a.experts = L.experts;
+    a.stride = L.stride;
+    a.off = L.off;
+    a.shared = withShared ? L.shared : nullptr;
+    a.sharedOff = L.sharedOff;
+    a.x = x;
+    a.xStride = xStride;
+    a.acts = ctx->acts;
+    a.sharedActs = ctx->sharedActs;
+    a.partials = decodeCombine ? nullptr : partials;
+    a.sharedOut = sharedOut;
+    a.jobs0 = ctx->jobs[0];
+    a.jobs1 = ctx->jobs[1];
+    a.items0 = ctx->items[0];
+    a.items1 = ctx->items[1];
+    a.plan = ctx->plan;
+    a.buildPlan = 1;
+    {
+        LaunchScope scope(ctx, stream, "topk_plan");
+        k_topk_plan<<<1, 512, 0, stream>>>(a);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+
+    const uint32_t maxActive = (uint32_t)std::min<uint64_t>((uint64_t)tokens * c.topK, (uint64_t)E);
+    const uint32_t bound0 = (withShared ? blocks_of(c.sharedF) : 0u) + maxActive * blocks_of(c.f);
+    GemvJob none{};
+    if (!launch_gemv_class<true>(ctx, tokens, ctx->jobs[0], ctx->items[0], &ctx->plan->itemCount[0],
+                                 none, 0, c.d, bound0, stream, error))
+        return false;
+    const uint32_t bound1 =
+        (withShared ? blocks_of(c.d) : 0u) + (decodeCombine ? 0u : maxActive * blocks_of(c.d));
+    if (bound1 > 0) {
+        const uint32_t maxCols = withShared ? std::max(c.f, c.sharedF) : c.f;
+        if (!launch_gemv_class<false>(ctx, tokens, ctx->jobs[1], ctx->items[1],
+                                      &ctx->plan->itemCount[1], none, 0, maxCols, bound1, stream,
+                                      error))
+            return false;
+    }
+    if (decodeCombine) {
+        if (c.topK > 8) return fail(error, "decode combine supports at most 8 routes");
+        const size_t smem = (size_t)8 * (staged_stride((int)c.f) + (c.f >> 5)) * sizeof(float);
+        static size_t configured[8] = {0};
+        if (configured[ctx->device & 7] != smem) {
+            FF_CUDA_OK(cudaFuncSetAttribute(k_decode_down,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                       error);
+            configured[ctx->device & 7] = smem;
+        }
+        const uint32_t grid = (c.d + kDecodeDownRows - 1) / kDecodeDownRows;
+        {
+            LaunchScope scope(ctx, stream, "decode_down_combine");
+            k_decode_down<<<grid, 512, smem, stream>>>(L.experts, L.stride, L.off, idsDev,
+                                                       weightsDev, ctx->acts,
+                                                       withShared ? sharedOut : residual, y,
+                                                       (int)c.d, (int)c.f, (int)c.topK);
+        }
+        FF_CUDA_OK(cudaGetLastError(), error);
+    }
+    return true;
+}
+
+bool launch_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *weights,
+                   const uint16_t *residual, uint16_t *y, uint32_t tokens, cudaStream_t stream,
+                   const char **error) {
+    if (tokens == 0) return true;
+    const int D = (int)ctx->cfg.d;
+    dim3 grid((D / 2 + 255) / 256, tokens);
+    {
+        LaunchScope scope(ctx, stream, "reduce_token_major");
+        k_reduce_token_major<<<grid, 256, 0, stream>>>(partials, weights, residual, y, (int)tokens,
+                                                       (int)ctx->cfg.topK, D);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+bool launch_gemv_rows(FFContext *ctx, const FFProjection &p, const uint16_t *x, uint32_t xStride,
+                      uint32_t rows, uint16_t *y, uint32_t yStride, cudaStream_t stream,
+                      const char **error) {
+    if (rows == 0) return true;
+    if (rows > kMaxGemvRows) return fail(error, "ff_int4_gemv_rows takes at most 16 input rows");
+    if (p.cols % kGroup != 0) return fail(error, "columns must be a multiple of 64");
+    if ((reinterpret_cast<uintptr_t>(p.weights) & 15u) || (p.cols / 2) % 16 != 0)
+        return fail(error, "packed weights must be 16-byte aligned with 16-byte-multiple rows");
+    GemvJob job{};
+    job.w0 = static_cast<const uint8_t *>(p.weights);
+    job.s0 = static_cast<const uint16_t *>(p.scales);
+    job.b0 = static_cast<const uint16_t *>(p.biases);
+    job.in = x;
+    job.out = y;
+    job.rows = p.rows;
+    job.cols = p.cols;
+    job.inStride = xStride;
+    job.outStride = yStride;
+    job.n = rows;
+    for (uint32_t i = 0; i < kMaxGemvRows; ++i) job.inRow[i] = job.outRow[i] = i < rows ? i : 0u;
+    return launch_gemv_class<false>(ctx, rows, nullptr, nullptr, nullptr, job, blocks_of(p.rows),
+                                    p.cols, blocks_of(p.rows), stream, error);
+}
+
+// Shared FFN for up to 16 rows without a route plan: gate/up/GeGLU job, then the down job.
+bool launch_shared_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                         uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error) {
+    const FFConfig &c = ctx->cfg;
+    if (tokens == 0) return true;
+    if (!L.shared) return fail(error, "layer has no resident shared FFN");
+    GemvJob j0{};
+    j0.w0 = L.shared + L.sharedOff.gateWOff;
+    j0.s0 = reinterpret_cast<const uint16_t *>(L.shared + L.sharedOff.gateSOff);
+    j0.b0 = reinterpret_cast<const uint16_t *>(L.shared + L.sharedOff.gateBOff);
+    j0.w1 = L.shared + L.sharedOff.upWOff;
+    j0.s1 = reinterpret_cast<const uint16_t *>(L.shared + L.sharedOff.upSOff);
+    j0.b1 = reinterpret_cast<const uint16_t *>(L.shared + L.sharedOff.upBOff);
+    j0.in = x;
+    j0.out = ctx->sharedActs;
+    j0.rows = c.sharedF;
+    j0.cols = c.d;
+    j0.inStride = xStride;
+    j0.outStride = c.sharedF;
+    j0.n = tokens;
+    j0.flags = kJobRoundGateUp;
+    GemvJob j1{};
+    j1.w0 = L.shared + L.sharedOff.downWOff;
+    j1.s0 = reinterpret_cast<const uint16_t *>(L.shared + L.sharedOff.downSOff);
+    j1.b0 = reinterpret_cast<const uint16_t *>(L.shared + L.sharedOff.downBOff);
+    j1.in = ctx->sharedActs;
+    j1.out = y;
+    j1.rows = c.d;
+    j1.cols = c.sharedF;
+    j1.inStride = c.sharedF;
+    j1.outStride = c.d;
+    j1.n = tokens;
+    for (uint32_t i = 0; i < kMaxGemvRows; ++i)
+        j0.inRow[i] = j0.outRow[i] = j1.inRow[i] = j1.outRow[i] = i < tokens ? i : 0u;
+    if (!launch_gemv_class<true>(ctx, tokens, nullptr, nullptr, nullptr, j0, blocks_of(j0.rows),
+                                 j0.cols, blocks_of(j0.rows), stream, error))
+        return false;
+    return launch_gemv_class<false>(ctx, tokens, nullptr, nullptr, nullptr, j1, blocks_of(j1.rows),
+                                    j1.cols, blocks_of(j1.rows), stream, error);
+}
+
+bool launch_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float eps,
+                    uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error) {
+    if (tokens == 0) return true;
+    {
+        LaunchScope scope(ctx, stream, "rmsnorm");
+        k_rmsnorm<<<tokens, 256, 0, stream>>>(x, w, eps, (int)ctx->cfg.d, y);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, const uint16_t *b,
+                          uint32_t rows, uint32_t cols, float *out32, uint16_t *out16,
+                          cudaStream_t stream, const char **error) {
+    const size_t words = (size_t)rows * cols / 8;
+    {
+        LaunchScope scope(ctx, stream, "dequant_probe");
+        k_dequant_probe<<<(unsigned)((words + 255) / 256), 256, 0, stream>>>(w, s, b, (int)rows,
+                                                                             (int)cols, out32, out16);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+}  // namespace ff

@@ -1,0 +1,191 @@
+// Internal declarations shared by the translation units of libfieldfare_cuda.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "fieldfare_cuda.h"
+
+namespace ff {
+
+constexpr int kGroup = 64;        // codes per scale/bias pair
+constexpr int kMaxGemvRows = 16;  // input rows one GEMV job can carry (a verify block)
+constexpr int kMaxExperts = 256;  // router width limit, as in the reference's prefill router
+
+// ---- error plumbing ------------------------------------------------------------------------
+
+// Stores a strdup'd message in *error (when the caller asked for one) and returns false.
+bool fail(const char **error, const std::string &message);
+
+#define FF_CUDA_OK(call, error)                                                              \
+    do {                                                                                     \
+        cudaError_t ff_status_ = (call);                                                     \
+        if (ff_status_ != cudaSuccess)                                                       \
+            return ff::fail(error, std::string(#call) + ": " + cudaGetErrorString(ff_status_)); \
+    } while (0)
+
+// ---- work descriptions the kernels read ----------------------------------------------------
+
+// One affine INT4 matrix (or a gate/up pair sharing inputs) applied to up to 16 input rows.
+struct GemvJob {
+    const uint8_t *w0;   // gate (or the only) matrix: packed codes
+    const uint16_t *s0;  // scales
+    const uint16_t *b0;  // biases
+    const uint8_t *w1;   // up matrix (dual jobs only)
+    const uint16_t *s1;
+    const uint16_t *b1;
+    const uint16_t *in;  // bf16 input rows
+    uint16_t *out;       // bf16 output rows
+    uint32_t rows;       // weight rows = outputs per input row
+    uint32_t cols;       // weight columns = input width
+    uint32_t inStride;   // elements between input rows
+    uint32_t outStride;  // elements between output rows
+    uint32_t n;          // input rows used, 1..16
+    uint32_t flags;      // kJobRoundGateUp
+    uint32_t inRow[kMaxGemvRows];
+    uint32_t outRow[kMaxGemvRows];
+};
+constexpr uint32_t kJobRoundGateUp = 1u;  // round gate and up to bf16 before the activation
+
+// Output of the device-side route plan for a decode/verify block.
+struct RoutePlan {
+    uint32_t jobCount[2];    // [0] gate/up jobs, [1] down jobs
+    uint32_t itemCount[2];   // (job, row block) work items per phase
+    uint32_t activeExperts;  // distinct routed experts in the block
+    uint32_t pad[3];
+};
+
+struct LayerStore {
+    uint8_t *experts = nullptr;  // expertCount blobs, stride apart (a layer file, verbatim)
+    uint64_t stride = 0;
+    uint32_t expertCount = 0;
+    FFExpertOffsets off{};
+    uint8_t *shared = nullptr;  // gate, up, down of the shared FFN in the same nine-part order
+    FFExpertOffsets sharedOff{};
+    uint16_t *routerW = nullptr;
+    uint16_t *routerScale = nullptr;
+    uint16_t *gain = nullptr;
+    float *logitBias = nullptr;
+    uint32_t routerExperts = 0;
+    // prefill: tensor maps over the packed weights (gate, up, down) of routed and shared blobs
+    bool mapsReady = false;
+    CUtensorMap routedMap[3];
+    CUtensorMap sharedMap[3];
+};
+
+}  // namespace ff
+
+struct FFContext {
+    int device = 0;
+    int smCount = 0;
+    FFConfig cfg{};
+    std::vector<ff::LayerStore> layers;
+    cudaStream_t hostStream = nullptr;  // used by the *_host entry points
+
+    // decode / verify scratch
+    float *logits = nullptr;        // [min(maxTokens,16)][experts]
+    uint32_t *ids = nullptr;        // [maxTokens][topK]
+    uint16_t *weights = nullptr;    // [maxTokens][topK]
+    ff::RoutePlan *plan = nullptr;
+    ff::GemvJob *jobs[2] = {nullptr, nullptr};
+    uint32_t *items[2] = {nullptr, nullptr};
+    uint32_t maxItems = 0;
+    uint16_t *acts = nullptr;       // [maxTokens*topK][f]
+    uint16_t *sharedActs = nullptr; // [maxTokens][sharedF]
+    uint16_t *h1 = nullptr;         // [maxTokens][d]
+    uint16_t *partials = nullptr;   // [maxTokens*topK][d]
+    uint16_t *xDev = nullptr;       // [maxTokens][d] staging for *_host
+    uint16_t *yDev = nullptr;
+
+    // prefill scratch (allocated when maxTokens > 16)
+    uint16_t *xSorted = nullptr;            // [maxTokens*topK][d] rows in expert order
+    FFTokenExpertPair *sortedPairs = nullptr;
+    uint32_t *expertOffsets = nullptr;      // [experts+1]
+    uint32_t *blockCounts = nullptr;        // permute: [blocks][experts]
+    uint32_t *units = nullptr;              // GEMM work units
+    uint32_t *unitCount = nullptr;          // [4]
+    uint32_t maxUnits = 0;
+    uint32_t *errorFlag = nullptr;          // device: set by a kernel that gave up waiting
+    CUtensorMap *mapScratch = nullptr;
+
+    // tracing: CUDA events around every kernel launch, aggregated per kernel name
+    bool tracing = false;
+    struct TraceRecord {
+        const char *name;
+        cudaEvent_t begin, end;
+    };
+    std::vector<TraceRecord> trace;
+
+    // counters
+    uint64_t kernelLaunches = 0;
+    uint64_t weightBytes = 0;
+    uint64_t scratchBytes = 0;
+    uint32_t lastTokens = 0;
+};
+
+namespace ff {
+
+// Counts a kernel launch and, when tracing is on, brackets it with CUDA events on its stream.
+struct LaunchScope {
+    FFContext *ctx;
+    cudaStream_t stream;
+    cudaEvent_t begin = nullptr, end = nullptr;
+    const char *name;
+    LaunchScope(FFContext *c, cudaStream_t s, const char *n) : ctx(c), stream(s), name(n) {
+        ctx->kernelLaunches++;
+        if (ctx->tracing) {
+            cudaEventCreate(&begin);
+            cudaEventCreate(&end);
+            cudaEventRecord(begin, stream);
+        }
+    }
+    ~LaunchScope() {
+        if (begin) {
+            cudaEventRecord(end, stream);
+            ctx->trace.push_back({name, begin, end});
+        }
+    }
+};
+
+// ff_gemv.cu
+bool launch_router_topk(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                        uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
+                        cudaStream_t stream, const char **error);
+bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                        uint32_t tokens, const uint32_t *ids, const uint16_t *weights,
+                        bool withShared, bool decodeCombine, const uint16_t *residual,
+                        uint16_t *partials, uint16_t *sharedOut, uint16_t *y,
+                        cudaStream_t stream, const char **error);
+bool launch_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *weights,
+                   const uint16_t *residual, uint16_t *y, uint32_t tokens, cudaStream_t stream,
+                   const char **error);
+bool launch_gemv_rows(FFContext *ctx, const FFProjection &p, const uint16_t *x, uint32_t xStride,
+                      uint32_t rows, uint16_t *y, uint32_t yStride, cudaStream_t stream,
+                      const char **error);
+bool launch_shared_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                         uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error);
+bool launch_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float eps,
+                    uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error);
+bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, const uint16_t *b,
+                          uint32_t rows, uint32_t cols, float *out32, uint16_t *out16,
+                          cudaStream_t stream, const char **error);
+
+// ff_prefill.cu
+bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error);
+bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uint32_t xStride,
+                           uint32_t tokens, const uint32_t *ids, uint16_t *partials,
+                           cudaStream_t stream, const char **error);
+bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uint32_t xStride,
+                           uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error);
+bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *x,
+                           uint32_t xStride, uint32_t tokens, uint32_t *ids, uint16_t *weights,
+                           float *logits, cudaStream_t stream, const char **error);
+
+// nine offsets for a blob holding gate/up [f][d] and down [d][f]
+FFExpertOffsets packed_offsets(uint32_t d, uint32_t f, uint64_t *payload);
+
+}  // namespace ff

@@ -1,0 +1,304 @@
+#!/usr/bin/env python
+"""Throughput of the INT4 MoE layer on B200, with its roofline fraction and a CPU baseline.
+
+Headline workload (config.workload): one Gemma-4-26B-A4B-shaped MoE layer at decode — one token
+[1 x 2816] through router top-8, eight INT4 GeGLU experts out of 128 and the shared INT4 FFN.
+A "step" is one token through one layer.  Steps rotate over several resident layers and input
+rows so that a step's 37.5 MB of weights cannot be served from L2 by the previous step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+For N > 1 (launched under torch.distributed.run) every rank runs an independent replica of the
+workload on its own GPU — decode does not shard — and the value is the sum over ranks divided by
+the slowest rank's device time.  `--impl reference` times the reference's CPU path (this
+repository's C restatement of it, since the Swift/Metal code cannot run on Linux) on the host
+cores, rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D, F, FS, E, K = 2816, 704, 2112, 128, 8
+EXPERT_BYTES = 3 * (F * D // 2 + 2 * (F * D // 64) * 2)          # 3 345 408
+SHARED_BYTES = 3 * (FS * D // 2 + 2 * (FS * D // 64) * 2)        # 10 036 224
+ROUTER_BYTES = E * D * 2                                         # 720 896
+ACT_IO_BYTES = 2 * D * 2                                         # x in, y out
+DECODE_BYTES = K * EXPERT_BYTES + SHARED_BYTES + ROUTER_BYTES + ACT_IO_BYTES  # 37 531 648
+DECODE_FLOPS = 2 * (K * 3 * F * D + 3 * FS * D + E * D)
+KERNELS_PER_DECODE_STEP = 5
+ROOT_SEED = 0xF1E1DFA2E
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+            int(os.environ.get("WORLD_SIZE", "1")))
+
+
+def cpu_decode_baseline(layer_host, tokens_bits, seconds_budget=12.0, max_steps=None):
+    """Times the CPU oracle's decode layer (all host threads) on a bounded sample of steps."""
+    from oracle import oracle as O
+    ld = O.LayerData(experts=layer_host.blobs, stride=layer_host.layout.stride,
+                     off=layer_host.layout.offsets.as_tuple(), E=E, D=D, F=F, K=K,
+                     shared=layer_host.sharedBlob, shared_off=layer_host.sharedLayout.offsets.as_tuple(),
+                     Fs=FS, router_w=layer_host.routerW, logit_bias=layer_host.logitBias)
+    O.moe_layer(ld, tokens_bits[:1], O.MODE_DECODE)  # warm
+    steps, t0 = 0, time.perf_counter()
+    while True:
+        row = tokens_bits[steps % len(tokens_bits)][None, :]
+        O.moe_layer(ld, row, O.MODE_DECODE)
+        steps += 1
+        elapsed = time.perf_counter() - t0
+        if (max_steps and steps >= max_steps) or (not max_steps and elapsed > seconds_budget):
+            break
+    return steps / elapsed, steps, O.num_threads()
+
+
+def run_reference(args):
+    """The reference arm: the CPU restatement of the reference's decode path on the host cores."""
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from ane_fieldfare_b200 import workload
+    layer = workload.make_layer(ROOT_SEED, 0)
+    tokens = workload.make_tokens(ROOT_SEED, "decode.x", 64, D)
+    for _ in range(max(args.warmup, 1)):
+        cpu_decode_baseline(layer, tokens, max_steps=1)
+    rate, steps, threads = cpu_decode_baseline(layer, tokens, max_steps=args.steps)
+    line = {
+        "impl": "reference", "metric": "int4_moe_layer_tokens_per_s", "value": rate,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 / rate, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights, bf16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "config1_decode_1token_moe_layer", "hidden": D, "experts": E,
+                   "top_k": K, "expert_intermediate": F, "shared_intermediate": FS},
+        "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{steps} decode steps of the C oracle (OpenMP), one layer"},
+        "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from ane_fieldfare_b200 import hotpath, workload
+
+    rank, local_rank, world = dist_env()
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    n_layers = args.layers
+    ctx = hotpath.HotpathContext(layers=n_layers, experts=E, d=D, f=F, sharedF=FS, topK=K,
+                                 maxTokens=16, device=local_rank)
+    host_layer0 = None
+    for slot in range(n_layers):
+        L = workload.make_layer(ROOT_SEED + 977 * rank, slot)
+        workload.load_layer(ctx, slot, L)
+        if slot == 0:
+            host_layer0 = L
+    n_rows = 64
+    tokens_bits = workload.make_tokens(ROOT_SEED, "decode.x", n_rows, D)
+    x_rows = hotpath.bf16_tensor(tokens_bits, device)
+    xs = [x_rows[i:i + 1].contiguous() for i in range(n_rows)]
+    y = torch.zeros((1, D), dtype=torch.bfloat16, device=device)
+
+    def step(i):
+        ctx.moeLayer(i % n_layers, xs[i % n_rows], y)
+
+    # ---- warm-up (also configures kernel attributes before any capture) ----
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+
+    # ---- one CUDA graph holding `group` consecutive steps -------------------
+    group = n_layers * 8
+    stream = torch.cuda.Stream(device=device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        for i in range(3):
+            step(i)
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(group):
+                step(i)
+    replays = max(1, (args.steps + group - 1) // group)
+    steps = replays * group
+    with torch.cuda.stream(stream):
+        for _ in range(max(1, (args.warmup + group - 1) // group)):
+            graph.replay()
+        stream.synchronize()
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        begin.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        end.record(stream)
+        stream.synchronize()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = float(t.item())
+    value = world * steps / (ms * 1e-3)
+
+    # ---- per-kernel device time of the same steps, by CUDA events (not graphed) ----
+    ctx.setTracing(True)
+    for i in range(group):
+        step(i)
+    trace = ctx.trace()
+    ctx.setTracing(False)
+    kernels = {name: {"launches": n, "avg_us": 1e3 * t / n} for name, (n, t) in trace.items()}
+
+    # ---- end to end through the host-buffer entry point ---------------------
+    hx = [torch.from_numpy(tokens_bits[i:i + 1].view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+          for i in range(n_rows)]
+    hy = torch.zeros((1, D), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = min(steps, 2000)
+    for i in range(5):
+        ctx.moeLayerHost(i % n_layers, hx[i % n_rows], hy)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        ctx.moeLayerHost(i % n_layers, hx[i % n_rows], hy)
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * e2e_steps / e2e_s
+
+    if rank == 0:
+        peaks = measured_peaks()
+        step_s = ms * 1e-3 / steps
+        achieved = DECODE_BYTES / step_s / 1e9
+        cpu_rate, cpu_steps, cpu_threads = cpu_decode_baseline(host_layer0, tokens_bits)
+        line = {
+            "metric": "int4_moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int4 weights, bf16 activations, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "config1_decode_1token_moe_layer", "hidden": D, "experts": E,
+                       "top_k": K, "expert_intermediate": F, "shared_intermediate": FS,
+                       "layers_rotated": n_layers, "input_rows_rotated": n_rows,
+                       "l2_policy": f"weights of {n_layers} layers rotate: "
+                                    f"{n_layers * DECODE_BYTES / 1e6:.0f} MB touched > 126 MB L2",
+                       "multi_gpu": "replicas only (decode does not shard)",
+                       "launch": f"CUDA graph of {group} steps"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": D * 2,
+                    "d2h_bytes_per_step": D * 2, "steps": e2e_steps},
+            "gpu_launches": steps * KERNELS_PER_DECODE_STEP,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": peaks["source"], "frac_of_nominal_8TBs": achieved / 8000.0,
+                         "kernel": "the whole decode step (router, top-k/plan, gate/up GEMV, "
+                                   "shared down GEMV, routed down + combine)",
+                         "algorithmic_bytes_per_step": DECODE_BYTES},
+            "kernels": kernels,
+            "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": cpu_threads,
+                             "kind": "port",
+                             "sample": f"{cpu_steps} decode steps of the C oracle (OpenMP), one layer"},
+        }
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4096)
+    ap.add_argument("--warmup", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=8, help="resident layers the steps rotate over")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,250 @@
+/*
+ * libfieldfare_cuda.so — C ABI of the B200 (sm_100a) INT4 mixture-of-experts hot path.
+ *
+ * The library stands in for the reference's Metal kernels and their Swift wrappers on one path:
+ * router top-8 -> routed INT4 GeGLU experts (+ the shared INT4 FFN) -> weighted combine.  Each
+ * entry point names the reference interface it replaces by that file's path inside the reference
+ * project.  Conventions follow the reference's own native boundary
+ * (Sources/ANEFieldfareANECarrier/include/ANEExpertCarrier.h:14-38): an opaque handle, `bool`
+ * results, errors returned as strdup'd C strings the caller frees (ff_string_free or free()),
+ * an explicit destroy, a plain info struct.  Calls on one context must be serialized by the
+ * caller.
+ *
+ * Operators take DEVICE pointers and a CUDA stream (passed as void*, a cudaStream_t; NULL is the
+ * legacy default stream).  They enqueue work and return without waiting, the way the
+ * reference's `encode...(commandBuffer:)` methods do; only the *_host entry points copy and
+ * wait.  All 16-bit activations, scales, biases and route weights are bf16 bit patterns.
+ *
+ * There is no CPU fallback: every operator launches CUDA kernels on the context's device and
+ * fails with a message when that is impossible.
+ */
+#ifndef FIELDFARE_CUDA_H
+#define FIELDFARE_CUDA_H
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct FFContext FFContext;
+
+/* Byte offsets of the nine sub-tensors of one expert blob.  Layout-identical to the reference's
+ * `MoEExpertOffsets` (Sources/ANEFieldfareHotpath/Kernels/MoE/MoE.swift:4-15) and the Metal
+ * `ExpertOffsets` (Metal/MoE/moe.metal:49-59). */
+typedef struct {
+    uint32_t gateWOff, gateSOff, gateBOff;
+    uint32_t upWOff, upSOff, upBOff;
+    uint32_t downWOff, downSOff, downBOff;
+} FFExpertOffsets;
+
+/* Layout-identical to `PrefillTokenExpertPair` (Kernels/Prefill/MoE/PrefillRouter.swift:4-21);
+ * the low 16 bits of weightBitsAndReserved hold the route weight (bf16 here, fp16 there). */
+typedef struct {
+    uint32_t token, expert, rank, weightBitsAndReserved;
+} FFTokenExpertPair;
+
+/* `PrefillMoEGroup` / `PrefillMoETile` (Kernels/Prefill/MoE/PrefillMoEGrouping.swift:4-29). */
+typedef struct {
+    uint32_t expert, pairStart, pairCount;
+} FFMoEGroup;
+typedef struct {
+    uint32_t groupStart, groupCount, pairStart, pairCount;
+} FFMoETile;
+
+/* One affine INT4 matrix [rows][cols]: packed codes (cols/2 bytes per row), bf16 scales and
+ * biases (cols/64 per row).  Mirrors `SharedExpertProjection`
+ * (Kernels/MoE/SharedExpertInt8.swift:7-29) with raw pointers in place of (buffer, offset). */
+typedef struct {
+    const void *weights;
+    const void *scales;
+    const void *biases;
+    uint32_t rows, cols;
+} FFProjection;
+
+/* Shape of the model slice a context serves; fixed at creation so scratch is allocated once. */
+typedef struct {
+    uint32_t layers;        /* layer slots                                   */
+    uint32_t experts;       /* routed experts per layer held by this context */
+    uint32_t d;             /* model width (2816)                            */
+    uint32_t f;             /* routed intermediate width (704)               */
+    uint32_t sharedF;       /* shared FFN intermediate width (2112), 0=none  */
+    uint32_t topK;          /* routes per token (8)                          */
+    uint32_t maxTokens;     /* largest T any operator call will pass         */
+} FFConfig;
+
+/* Counters, in the spirit of `ANEExpertCarrierInfo` (ANEExpertCarrier.h:16-23). */
+typedef struct {
+    uint64_t kernelLaunches;     /* kernels this context has enqueued          */
+    uint64_t weightBytesResident;/* expert + shared + router bytes held in HBM */
+    uint64_t scratchBytes;       /* device scratch owned by the context        */
+    uint32_t lastActiveExperts;  /* distinct experts of the last verify/prefill (after a sync) */
+    uint32_t lastPrefillUnits;   /* GEMM work units of the last prefill call   */
+    uint32_t deviceOrdinal;
+    uint32_t smCount;
+} FFInfo;
+
+/* Device time of one kernel name, summed over the launches made while tracing was on. */
+typedef struct {
+    char name[40];
+    uint64_t launches;
+    double milliseconds;
+} FFTraceEntry;
+
+/* ---- lifetime ---------------------------------------------------------------------------- */
+
+/* Replaces the construction of the reference's kernel wrapper objects from a `MetalContext`
+ * (Kernels/MoE/MoE.swift:62-125, Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:210-250).
+ * Returns NULL and sets *error on failure (no CUDA device, unsupported shape, out of memory). */
+FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char **error);
+void ff_destroy(FFContext *ctx);
+void ff_string_free(const char *message);
+FFInfo ff_get_info(const FFContext *ctx);
+
+/* Per-kernel device timing: while on, every kernel launch is bracketed by CUDA events on its
+ * stream.  ff_get_trace waits for the device, fills up to `capacity` entries (one per kernel
+ * name), clears the record and returns the number of names.  The counterpart of the reference's
+ * per-encoder GPU timestamps (Infrastructure/Metal/GPUTrace.swift:67-90).  Do not trace while a
+ * stream is being captured into a CUDA graph. */
+void ff_set_tracing(FFContext *ctx, bool enabled);
+uint32_t ff_get_trace(FFContext *ctx, FFTraceEntry *entries, uint32_t capacity);
+
+/* ---- HBM-resident weights ---------------------------------------------------------------- */
+
+/* Copies one layer file's bytes (`packed_experts/layer_%02d.bin`: expertCount blobs,
+ * expertStride apart, the nine offsets shared by every expert) verbatim into device memory.
+ * Replaces the mmap expert store: `MappedExpertLayer`
+ * (Infrastructure/Streaming/MappedExpertLayer.swift:44-209) and `Model.routedExpertOffsets`
+ * (Runtime/Inference/ModelExpertIO.swift:11-30).  Checks the schema rules of
+ * Runtime/Inference/Model.swift:478-527 (sizes, 4-byte weight / 2-byte scale alignment) plus
+ * the 16-byte alignment the 128-bit loads need. */
+bool ff_load_layer(FFContext *ctx, uint32_t layer, const void *hostBytes, uint64_t byteCount,
+                   uint32_t expertCount, uint64_t expertStride, const FFExpertOffsets *offsets,
+                   const char **error);
+
+/* The shared FFN's three projections from HOST pointers (the reference keeps them as resident
+ * tensors: Kernels/MoE/SharedExpertInt4.swift:32-38). */
+bool ff_load_shared(FFContext *ctx, uint32_t layer, const FFProjection *gate,
+                    const FFProjection *up, const FFProjection *down, const char **error);
+
+/* Router weights bf16 [experts][d] from HOST memory, with the optional per-input scale
+ * (`effectiveScale`, bf16 [d]), per-expert gain (`perExpertScale`, bf16 [experts]) — the
+ * arguments of `MoE.encodeRouterGemma4` (Kernels/MoE/MoE.swift:168-180) — and an optional fp32
+ * per-expert additive logit bias (used by the synthetic benchmark configurations). */
+bool ff_load_router(FFContext *ctx, uint32_t layer, const uint16_t *weights,
+                    const uint16_t *effectiveScale, const uint16_t *perExpertScale,
+                    const float *logitBias, uint32_t experts, uint32_t d, const char **error);
+
+/* Device address of one resident expert blob (the entry the reference's address table holds:
+ * Metal/MoE/moe.metal:576-593), 0 when absent. */
+uint64_t ff_expert_address(const FFContext *ctx, uint32_t layer, uint32_t expert);
+
+/* ---- operators (device pointers, asynchronous on `stream`) -------------------------------- */
+
+/* Parity hook: expands one resident matrix to fp32 [rows][cols] as w = q*scale + bias.
+ * expert = -1 selects the shared FFN; role 0/1/2 = gate/up/down.  Counterpart of the
+ * reference's expansion check (Tests/ANEFieldfareHotpathTests/ANEQuantizedCarrierTests.swift:67,
+ * Metal/ANE/ane_prefill.metal:17-43). */
+bool ff_dequant_probe(FFContext *ctx, uint32_t layer, int32_t expert, uint32_t role, float *out,
+                      void *stream, const char **error);
+/* Same matrix as the bf16 operand the prefill tensor-core path multiplies. */
+bool ff_dequant_probe_bf16(FFContext *ctx, uint32_t layer, int32_t expert, uint32_t role,
+                           uint16_t *out, void *stream, const char **error);
+
+/* Router logits, top-K selection (higher score, then lower expert id), softmax over the
+ * selected K, times the per-expert gain.  x is bf16 [tokens][xStride]; ids uint32 [tokens][K],
+ * weights bf16 [tokens][K]; logits (optional) fp32 [tokens][experts].  Replaces
+ * `MoE.encodeRouterGemma4` / `encodeRouterRowsGemma4` (Kernels/MoE/MoE.swift:168-300) and
+ * `PrefillRouter.encodeGemma4Block` (Kernels/Prefill/MoE/PrefillRouter.swift:30-73). */
+bool ff_router_topk(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                    uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
+                    void *stream, const char **error);
+
+/* Decode, one token: y[d] = bf16(residual[d] + sum_k w_k * down_k(gelu(gate_k x) * up_k x)).
+ * residual may be NULL (zero).  Replaces `MoE.encodeRoutedPersistentGPUSlots` =
+ * gather slots + phase 1 + phase 2 (Kernels/MoE/MoE.swift:312-341,384-417,429-496). */
+bool ff_moe_decode(FFContext *ctx, uint32_t layer, const uint16_t *x, const uint32_t *ids,
+                   const uint16_t *weights, const uint16_t *residual, uint16_t *y, void *stream,
+                   const char **error);
+
+/* Verify block, 1..16 tokens: every (token, rank) route writes its bf16 partial row at
+ * partials[(token*K + rank)*d]; each active expert's weights are read once for all of its
+ * tokens.  Replaces `PrefillGroupedRoutedMoE.encodeVerifyBound` / `encodeVerifyRows`
+ * (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:331-448). */
+bool ff_moe_verify(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                   uint32_t tokens, const uint32_t *ids, uint16_t *partials, void *stream,
+                   const char **error);
+
+/* Prefill, any token count: device-side permute (the host sort of
+ * Kernels/Prefill/MoE/PrefillMoEGrouping.swift:49-110), then the grouped INT4->bf16 tensor-core
+ * GEMMs, writing the same partial rows.  Replaces `PrefillGroupedRoutedMoE.encodeStreamedBatched`
+ * (PrefillGroupedRoutedMoE.swift:275-326) and the `RoutedPrefillGuest.runLayer` plug-in
+ * (Runtime/Supervisor/DeviceSupervisor.swift:18-22). */
+bool ff_moe_prefill(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                    uint32_t tokens, const uint32_t *ids, uint16_t *partials, void *stream,
+                    const char **error);
+
+/* y[t][c] = bf16(sum_r fma(w[t][r], partials[(t*K+r)*d + c]) (+ residual[t][c])).  Replaces
+ * `PrefillMoE.encodeReduceTokenMajor` (Kernels/Prefill/MoE/PrefillMoE.swift:11-32); the optional
+ * residual is an addition for the shared-FFN sum. */
+bool ff_moe_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *weights,
+                   const uint16_t *residual, uint16_t *y, uint32_t tokens, void *stream,
+                   const char **error);
+
+/* Shared INT4 FFN for `tokens` rows: y = down(gelu(bf16(gate x)) * bf16(up x)).  GEMV kernels
+ * up to 16 rows, tensor-core GEMMs above.  Replaces `SharedExpertInt4.encode`
+ * (Kernels/MoE/SharedExpertInt4.swift:32-88) and `PrefillSharedExpert.encodeBlock`
+ * (Kernels/Prefill/MoE/PrefillSharedExpert.swift:51-137). */
+bool ff_shared_ffn(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
+                   uint32_t tokens, uint16_t *y, void *stream, const char **error);
+
+/* Y[r][o] = sum_k W[o][k] X[r][k] for rows <= 16 input rows, all pointers on the device.
+ * Replaces `DequantInt4GEMV.encodeRows` (Kernels/Quant/DequantInt4GEMV.swift:72-117). */
+bool ff_int4_gemv_rows(FFContext *ctx, const FFProjection *projection, const uint16_t *x,
+                       uint32_t xStride, uint32_t rows, uint16_t *y, uint32_t yStride,
+                       void *stream, const char **error);
+
+/* y = x * rsqrt(mean(x^2) + eps) * w per row (w may be NULL).  The inter-layer glue of the
+ * layer stack (Metal/Primitives/rmsnorm.metal:65, Metal/Prefill/prefill.metal:88). */
+bool ff_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float eps, uint32_t tokens,
+                uint16_t *y, void *stream, const char **error);
+
+/* The whole block for `tokens` rows: router -> routed experts + shared FFN -> y, choosing the
+ * decode (1), verify (2..16) or prefill path by token count.  This is the unit the throughput
+ * metric times.  ids/weights (optional) receive the routes. */
+bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t tokens,
+                  uint16_t *y, uint32_t *ids, uint16_t *weights, void *stream,
+                  const char **error);
+
+/* ff_moe_layer with HOST buffers: copies x in, runs, copies y out, waits.  Host pointers should
+ * be page-locked for full copy bandwidth. */
+bool ff_moe_layer_host(FFContext *ctx, uint32_t layer, const uint16_t *hostX, uint32_t tokens,
+                       uint16_t *hostY, const char **error);
+
+/* ---- host-side permute (exact integer work) ----------------------------------------------- */
+
+/* `PrefillRouter.makeTokenExpertPairs` (Kernels/Prefill/MoE/PrefillRouter.swift:75-95). */
+uint64_t ff_make_token_expert_pairs(const uint32_t *ids, const uint16_t *weights,
+                                    uint32_t tokens, uint32_t topK, FFTokenExpertPair *pairs);
+
+/* `PrefillMoEGrouping.groupTokenExpertPairs` (PrefillMoEGrouping.swift:49-110): sorted pairs,
+ * per-expert groups, tiles of up to tileExpertCount (1..16) groups.  Output arrays must hold
+ * pairCount pairs, min(experts, pairCount) groups and as many tiles.  Fails with
+ * "route expert N is out of range" like the reference. */
+bool ff_group_token_expert_pairs(const FFTokenExpertPair *pairs, uint64_t pairCount,
+                                 uint32_t tokens, uint32_t topK, uint32_t experts,
+                                 uint32_t tileExpertCount, const uint64_t *expertSortKeys,
+                                 FFTokenExpertPair *sortedPairs, FFMoEGroup *groups,
+                                 uint32_t *groupCount, FFMoETile *tiles, uint32_t *tileCount,
+                                 const char **error);
+
+/* Device-side result of the last ff_moe_prefill permute, copied to the host after a sync:
+ * the expert-sorted pairs and per-expert row offsets [experts+1].  For parity tests. */
+bool ff_last_prefill_routes(FFContext *ctx, FFTokenExpertPair *sortedPairs, uint32_t *offsets,
+                            const char **error);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
