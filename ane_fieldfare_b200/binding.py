@@ -46,7 +46,8 @@ class FFConfig(ctypes.Structure):
 class FFInfo(ctypes.Structure):
     _fields_ = [("kernelLaunches", c_uint64), ("weightBytesResident", c_uint64),
                 ("scratchBytes", c_uint64), ("lastActiveExperts", c_uint32),
-                ("lastPrefillUnits", c_uint32), ("deviceOrdinal", c_uint32), ("smCount", c_uint32)]
+                ("lastPrefillUnits", c_uint32), ("deviceOrdinal", c_uint32), ("smCount", c_uint32),
+                ("deviceErrorFlag", c_uint32), ("reserved", c_uint32)]
 
 
 class FFTraceEntry(ctypes.Structure):

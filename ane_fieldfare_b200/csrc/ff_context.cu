@@ -133,8 +133,8 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     ok = ok && dev_alloc(ctx, &ctx->jobs[1], 1 + planExperts, error);
     ok = ok && dev_alloc(ctx, &ctx->items[0], ctx->maxItems, error);
     ok = ok && dev_alloc(ctx, &ctx->items[1], ctx->maxItems, error);
-    ok = ok && dev_alloc(ctx, &ctx->acts, T * K * c.f, error);
-    ok = ok && dev_alloc(ctx, &ctx->sharedActs, T * c.sharedF, error);
+    ok = ok && dev_alloc(ctx, &ctx->acts, (T * K + 128) * c.f, error);  // +128: a GEMM row tile may overhang
+    ok = ok && dev_alloc(ctx, &ctx->sharedActs, (T + 128) * c.sharedF, error);
     ok = ok && dev_alloc(ctx, &ctx->h1, T * c.d, error);
     ok = ok && dev_alloc(ctx, &ctx->partials, T * K * c.d, error);
     ok = ok && dev_alloc(ctx, &ctx->xDev, T * c.d, error);
@@ -145,13 +145,15 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
         const size_t pairs = T * K;
         const size_t permuteBlocks = (T + 255) / 256;
         // one work unit per (expert, 128-row tile, column tile); tiles <= pairs/128 + experts
-        ctx->maxUnits = (uint32_t)((pairs / 128 + c.experts + 1) * 64);
+        ctx->maxUnits = (uint32_t)(2 * (pairs / 128 + c.experts + 2));  // row tiles: routed half, dense half
         ok = ok && dev_alloc(ctx, &ctx->xSorted, (pairs + 128) * c.d, error);
+        if (ok) ok = cudaMemset(ctx->xSorted, 0, (pairs + 128) * c.d * 2) == cudaSuccess;
         ok = ok && dev_alloc(ctx, &ctx->sortedPairs, pairs, error);
         ok = ok && dev_alloc(ctx, &ctx->expertOffsets, c.experts + 1, error);
         ok = ok && dev_alloc(ctx, &ctx->blockCounts, (permuteBlocks + 1) * c.experts, error);
         ok = ok && dev_alloc(ctx, &ctx->units, (size_t)ctx->maxUnits * 4, error);
-        ok = ok && dev_alloc(ctx, &ctx->unitCount, 4, error);
+        ok = ok && dev_alloc(ctx, &ctx->unitCount, 8, error);
+        if (ok) ok = cudaMemset(ctx->unitCount, 0, 32) == cudaSuccess;
     }
     if (!ok) {
         if (error && !*error) fail(error, "context allocation failed");
@@ -173,6 +175,8 @@ FFInfo ff_get_info(const FFContext *ctx) {
     RoutePlan plan{};
     if (ctx->plan && cudaMemcpy(&plan, ctx->plan, sizeof(plan), cudaMemcpyDeviceToHost) == cudaSuccess)
         info.lastActiveExperts = plan.activeExperts;
+    if (ctx->errorFlag)
+        cudaMemcpy(&info.deviceErrorFlag, ctx->errorFlag, sizeof(uint32_t), cudaMemcpyDeviceToHost);
     uint32_t counts[4] = {0, 0, 0, 0};
     if (ctx->unitCount &&
         cudaMemcpy(counts, ctx->unitCount, sizeof(counts), cudaMemcpyDeviceToHost) == cudaSuccess) {

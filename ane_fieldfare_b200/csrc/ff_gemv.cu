@@ -464,8 +464,10 @@ __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
     uint32_t list[kMaxGemvRows];
     int n = 0;
     if (e < a.E) {
+        // a token's routes are distinct experts, so an expert is chosen by at most T routes;
+        // repeats beyond that are dropped rather than overrunning the row class
         for (int r = 0; r < routes; ++r)
-            if (sIds[r] == (uint32_t)e && n < kMaxGemvRows) list[n++] = (uint32_t)r;
+            if (sIds[r] == (uint32_t)e && n < a.T) list[n++] = (uint32_t)r;
         sPos[e] = n > 0 ? 1u : 0u;
     }
     __syncthreads();

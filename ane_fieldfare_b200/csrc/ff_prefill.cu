@@ -1,27 +1,1040 @@
-// Prefill path: router for many rows, device-side permute, grouped INT4->bf16 tensor-core GEMMs.
+// Prefill path of the INT4 MoE block: router for many rows, device-side permute (counting sort by
+// expert), and the grouped INT4 -> bf16 GEMMs on the 5th-generation tensor cores.
+//
+// GEMM scheme.  A work unit is (row tile of up to 128 expert-sorted rows, column tile of 128
+// outputs).  Per 64-wide step along the contraction (= one quantization group):
+//   * one thread issues TMA loads: the activations' [128 x 64] bf16 tile (128-byte swizzle) and
+//     two [64 rows x 32 bytes] tiles of packed 4-bit codes, completing on an mbarrier;
+//   * four warps turn the packed tile into the bf16 operand tile in shared memory, one weight
+//     row per thread: codes -> bf16 pairs by a mask trick, then one bf16x2 fused multiply-add
+//     with the group's scale and bias (a single rounding of q*scale+bias), stored in the
+//     128-byte-swizzled K-major layout the MMA descriptor expects;
+//   * one thread issues four tcgen05.mma (M=128, N=128, K=16) accumulating in TMEM, then
+//     tcgen05.commit to free the stage;
+//   * four warps drain the finished accumulator from TMEM (tcgen05.ld), apply the epilogue
+//     (GeGLU to bf16 activations, or bf16 partial rows scattered to (token, rank)), while the
+//     next unit's MMAs fill the other accumulator buffer.
+// Within every aligned run of eight contraction elements the order is 0,4,1,5,2,6,3,7 in BOTH
+// operands (the mask trick yields codes j and j+4 side by side), which leaves every dot product
+// unchanged; the activation buffers this file writes use that order.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets the context's error flag and
+// the whole CTA leaves its loops, frees its TMEM and returns.
+//
+// Reference kernels this file stands in for (paths inside the reference project):
+//   Sources/ANEFieldfareHotpath/Metal/Prefill/prefill.metal:447-542 (router block),
+//   :609-779 (routed experts as tiled matrix multiplies),
+//   Sources/ANEFieldfareHotpath/Metal/TensorCore/tensorops.metal:14-298 (dense INT4 GEMM),
+//   Sources/ANEFieldfareHotpath/Kernels/Prefill/MoE/PrefillMoEGrouping.swift:49-110 (the sort).
+#include <algorithm>
+#include <cstring>
+
 #include "ff_internal.cuh"
 
 namespace ff {
 
-bool prefill_prepare_layer(FFContext *, LayerStore &, const char **error) {
-    return fail(error, "prefill path is not built");
+// ---- small device helpers --------------------------------------------------------------------
+
+__device__ __forceinline__ float pf_bf2f(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
+__device__ __forceinline__ uint16_t pf_f2bf(float f) {
+    uint32_t u = __float_as_uint(f);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
 }
-bool launch_prefill_routed(FFContext *, LayerStore &, const uint16_t *, uint32_t, uint32_t,
-                           const uint32_t *, uint16_t *, cudaStream_t, const char **error) {
-    return fail(error, "prefill path is not built");
+__device__ __forceinline__ float pf_gelu_tanh(float x) {
+    const float x3 = x * x * x;
+    float inner = 0.7978845608028654f * (x + 0.044715f * x3);
+    inner = fminf(fmaxf(inner, -20.0f), 20.0f);
+    return 0.5f * x * (1.0f + tanhf(inner));
 }
-bool launch_prefill_shared(FFContext *, LayerStore &, const uint16_t *, uint32_t, uint32_t,
-                           uint16_t *, cudaStream_t, const char **error) {
-    return fail(error, "prefill path is not built");
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
 }
-bool launch_router_prefill(FFContext *, const LayerStore &, const uint16_t *, uint32_t, uint32_t,
-                           uint32_t *, uint16_t *, float *, cudaStream_t, const char **error) {
-    return fail(error, "prefill path is not built");
+
+// ---- router for many rows ------------------------------------------------------------------
+
+// One warp per token.  The token's (scaled) inputs sit in shared memory as fp32; for every
+// expert the warp forms the logit in the order the decode router uses (lane l chains fmaf over
+// [256 i + 8 l, +8), butterfly 16..1, then the logit bias), so logits and indices are bitwise
+// those of the single-row kernel.  Then the warp-wide top-K.
+constexpr int kRouterWarps = 4;
+
+__device__ void pf_warp_topk(const float *logits, int E, int K, const uint16_t *gain, uint32_t *ids,
+                             uint16_t *weights) {
+    const int lane = threadIdx.x & 31;
+    float v[8];
+    bool live[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int e = j * 32 + lane;
+        v[j] = e < E ? logits[e] : -INFINITY;
+        live[j] = e < E && v[j] > -INFINITY;
+    }
+    float topScore[8];
+    uint32_t topIdx[8];
+    for (int r = 0; r < 8; ++r) {
+        float best = -INFINITY;
+        uint32_t bestE = 0xFFFFFFFFu;
+        if (r < K) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t e = (uint32_t)(j * 32 + lane);
+                if (live[j] && (v[j] > best || (v[j] == best && e < bestE))) {
+                    best = v[j];
+                    bestE = e;
+                }
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset >= 1; offset >>= 1) {
+            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, offset);
+            const uint32_t oe = __shfl_xor_sync(0xFFFFFFFFu, bestE, offset);
+            if (oe != 0xFFFFFFFFu && (bestE == 0xFFFFFFFFu || ob > best || (ob == best && oe < bestE))) {
+                best = ob;
+                bestE = oe;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (bestE != 0xFFFFFFFFu && bestE == (uint32_t)(j * 32 + lane)) live[j] = false;
+        topIdx[r] = bestE == 0xFFFFFFFFu ? 0u : bestE;
+        topScore[r] = bestE == 0xFFFFFFFFu ? -INFINITY : best;
+    }
+    if (lane == 0) {
+        float ex[8], sum = 0.0f;
+        for (int r = 0; r < K; ++r) {
+            ex[r] = expf(topScore[r] - topScore[0]);
+            sum += ex[r];
+        }
+        for (int r = 0; r < K; ++r) {
+            float w = ex[r] / sum;
+            if (gain) w = w * pf_bf2f(gain[topIdx[r]]);
+            ids[r] = topIdx[r];
+            weights[r] = pf_f2bf(w);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kRouterWarps * 32)
+k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const uint16_t *gain,
+              const uint16_t *x, uint32_t xStride, int T, int E, int D, int K, uint32_t *ids,
+              uint16_t *weights, float *logitsOut) {
+    extern __shared__ float rsm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *xs = rsm + (size_t)warp * (D + kMaxExperts);
+    float *lg = xs + D;
+    const int t = blockIdx.x * kRouterWarps + warp;
+    if (t >= T) return;
+    const uint16_t *xr = x + (size_t)t * xStride;
+    for (int i = lane * 2; i < D; i += 64) {
+        const uint32_t two = *reinterpret_cast<const uint32_t *>(xr + i);
+        float x0 = __uint_as_float(two << 16), x1 = __uint_as_float(two & 0xFFFF0000u);
+        if (scale) {
+            const uint32_t ss = *reinterpret_cast<const uint32_t *>(scale + i);
+            x0 = x0 * __uint_as_float(ss << 16);
+            x1 = x1 * __uint_as_float(ss & 0xFFFF0000u);
+        }
+        xs[i] = x0;
+        xs[i + 1] = x1;
+    }
+    __syncwarp();
+    for (int e = 0; e < E; ++e) {
+        const uint16_t *wr = W + (size_t)e * D;
+        float acc = 0.0f;
+        for (int base = 8 * lane; base < D; base += 256) {
+            const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
+            const float4 xa = *reinterpret_cast<const float4 *>(xs + base);
+            const float4 xb = *reinterpret_cast<const float4 *>(xs + base + 4);
+            acc = fmaf(__uint_as_float(wv.x << 16), xa.x, acc);
+            acc = fmaf(__uint_as_float(wv.x & 0xFFFF0000u), xa.y, acc);
+            acc = fmaf(__uint_as_float(wv.y << 16), xa.z, acc);
+            acc = fmaf(__uint_as_float(wv.y & 0xFFFF0000u), xa.w, acc);
+            acc = fmaf(__uint_as_float(wv.z << 16), xb.x, acc);
+            acc = fmaf(__uint_as_float(wv.z & 0xFFFF0000u), xb.y, acc);
+            acc = fmaf(__uint_as_float(wv.w << 16), xb.z, acc);
+            acc = fmaf(__uint_as_float(wv.w & 0xFFFF0000u), xb.w, acc);
+        }
+#pragma unroll
+        for (int offset = 16; offset >= 1; offset >>= 1)
+            acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
+        if (lane == 0) lg[e] = bias ? acc + bias[e] : acc;
+    }
+    __syncwarp();
+    if (logitsOut)
+        for (int e = lane; e < E; e += 32) logitsOut[(size_t)t * E + e] = lg[e];
+    pf_warp_topk(lg, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
+}
+
+bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                           uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
+                           cudaStream_t stream, const char **error) {
+    const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
+    const size_t smem = (size_t)kRouterWarps * (D + kMaxExperts) * sizeof(float);
+    static size_t configured[8] = {0};
+    if (configured[ctx->device & 7] != smem) {
+        FF_CUDA_OK(cudaFuncSetAttribute(k_router_rows, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem),
+                   error);
+        configured[ctx->device & 7] = smem;
+    }
+    {
+        LaunchScope scope(ctx, stream, "router_rows");
+        k_router_rows<<<(tokens + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, smem, stream>>>(
+            L.routerW, L.routerScale, L.logitBias, L.gain, x, xStride, (int)tokens, E, D,
+            (int)ctx->cfg.topK, ids, weights, logits);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+// ---- device-side permute -------------------------------------------------------------------
+
+constexpr int kSortTokens = 256;  // tokens per permute block
+
+struct RowTile {
+    uint32_t rowStart;  // first row in expert-sorted order
+    uint32_t rows;      // 1..128
+    uint32_t expert;
+    uint32_t pad;
+};
+
+// Pass 1: per block of 256 tokens, how many routes name each expert.
+__global__ void __launch_bounds__(256)
+k_route_count(const uint32_t *ids, int T, int K, int E, uint32_t *blockCounts) {
+    extern __shared__ uint32_t sRoutes[];
+    const int t0 = blockIdx.x * kSortTokens;
+    const int n = min(kSortTokens, T - t0) * K;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sRoutes[i] = ids[(size_t)t0 * K + i];
+    __syncthreads();
+    const int e = threadIdx.x;
+    if (e < E) {
+        uint32_t c = 0;
+        for (int i = 0; i < n; ++i) c += sRoutes[i] == (uint32_t)e ? 1u : 0u;
+        blockCounts[(size_t)blockIdx.x * E + e] = c;
+    }
+}
+
+// Pass 2 (one block): exclusive prefix of every expert's counts over the blocks, expert offsets,
+// and the list of row tiles (up to 128 rows of one expert each), experts ascending.
+// counts[0] = row tiles, counts[1] = pairs, counts[2] = experts with at least one pair.
+__global__ void __launch_bounds__(256)
+k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, RowTile *tiles,
+             uint32_t maxTiles, uint32_t *counts) {
+    __shared__ uint32_t total[kMaxExperts];
+    __shared__ uint32_t offset[kMaxExperts + 1];
+    __shared__ uint32_t tileBase[kMaxExperts + 1];
+    const int e = threadIdx.x;
+    if (e < E) {
+        uint32_t run = 0;
+        for (int b = 0; b < blocks; ++b) {
+            const uint32_t c = blockCounts[(size_t)b * E + e];
+            blockCounts[(size_t)b * E + e] = run;
+            run += c;
+        }
+        total[e] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0, tilesRun = 0, active = 0;
+        for (int i = 0; i < E; ++i) {
+            offset[i] = run;
+            tileBase[i] = tilesRun;
+            run += total[i];
+            tilesRun += (total[i] + 127u) / 128u;
+            active += total[i] ? 1u : 0u;
+        }
+        offset[E] = run;
+        tileBase[E] = tilesRun;
+        counts[0] = min(tilesRun, maxTiles);
+        counts[1] = run;
+        counts[2] = active;
+        counts[3] = 0;
+    }
+    __syncthreads();
+    if (e < E) expertOffsets[e] = offset[e];
+    if (e == 0) expertOffsets[E] = offset[E];
+    if (e < E) {
+        const uint32_t n = total[e];
+        for (uint32_t i = 0, tix = tileBase[e]; i < n; i += 128, ++tix)
+            if (tix < maxTiles) tiles[tix] = RowTile{offset[e] + i, min(128u, n - i), (uint32_t)e, 0u};
+    }
+}
+
+// Pass 3: every route's position in (expert, token, rank) order; writes the sorted pair list.
+__global__ void __launch_bounds__(256)
+k_route_scatter(const uint32_t *ids, const uint16_t *weights, int T, int K, int E,
+                const uint32_t *blockCounts, const uint32_t *expertOffsets,
+                FFTokenExpertPair *sorted) {
+    extern __shared__ uint32_t sRoutes[];
+    const int t0 = blockIdx.x * kSortTokens;
+    const int n = min(kSortTokens, T - t0) * K;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sRoutes[i] = ids[(size_t)t0 * K + i];
+    __syncthreads();
+    const int e = threadIdx.x;
+    if (e < E) {
+        uint32_t pos = expertOffsets[e] + blockCounts[(size_t)blockIdx.x * E + e];
+        for (int i = 0; i < n; ++i) {
+            if (sRoutes[i] == (uint32_t)e) {
+                const uint32_t token = (uint32_t)(t0 + i / K), rank = (uint32_t)(i % K);
+                const uint32_t wbits = weights ? (uint32_t)weights[(size_t)token * K + rank] : 0u;
+                sorted[pos++] = FFTokenExpertPair{token, (uint32_t)e, rank, wbits};
+            }
+        }
+    }
+}
+
+// Row tiles of a dense problem: T rows of one "expert" (the shared FFN).
+__global__ void k_dense_tiles(int T, RowTile *tiles, uint32_t *counts) {
+    const int n = (T + 127) / 128;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        tiles[i] = RowTile{(uint32_t)i * 128u, (uint32_t)min(128, T - i * 128), 0u, 0u};
+    if (threadIdx.x == 0) {
+        counts[0] = (uint32_t)n;
+        counts[1] = (uint32_t)T;
+        counts[2] = 1;
+        counts[3] = 0;
+    }
+}
+
+// Copies rows of x into the GEMM's activation buffer, reordering every aligned run of eight
+// elements to 0,4,1,5,2,6,3,7.  pairs == null: row r of the output is row r of x; otherwise row r
+// is the token of sorted pair r.  One thread per 16 bytes.
+__global__ void __launch_bounds__(256)
+k_gather_rows(const uint16_t *x, uint32_t xStride, const FFTokenExpertPair *pairs,
+              const uint32_t *rowCountPtr, uint32_t rowCount, int D, uint16_t *out) {
+    const uint32_t rows = rowCountPtr ? rowCountPtr[1] : rowCount;
+    const int chunksPerRow = D / 8;
+    const size_t total = (size_t)rows * chunksPerRow;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t r = (uint32_t)(i / chunksPerRow);
+        const int c = (int)(i - (size_t)r * chunksPerRow);
+        const uint32_t src = pairs ? pairs[r].token : r;
+        const uint4 v = *reinterpret_cast<const uint4 *>(x + (size_t)src * xStride + c * 8);
+        // halves h0..h7 -> h0,h4,h1,h5,h2,h6,h3,h7
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410);
+        o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410);
+        o.w = __byte_perm(v.y, v.w, 0x7632);
+        *reinterpret_cast<uint4 *>(out + (size_t)r * D + c * 8) = o;
+    }
+}
+
+// ---- tcgen05 / TMA / mbarrier wrappers ------------------------------------------------------
+
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another thread of the CTA gave up; the
+// caller leaves its loop.  `abortFlag` lives in shared memory.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abortFlag) return false;
+    }
+    *abortFlag = 1u;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_generic_to_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmemD, uint64_t descA, uint64_t descB,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmemD),
+        "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tc_load_32cols(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major bf16 tile stored with the 128-byte swizzle:
+// rows are 128 bytes apart, groups of eight rows 1024 bytes apart (stride byte offset), the
+// leading byte offset is unused for swizzled K-major tiles (set to 1), descriptor version 1,
+// layout type 2 (128-byte swizzle).  The tile base must be 1024-byte aligned; `byteOffset`
+// advances along K inside the swizzle atom (32 bytes per K=16 slice).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smemAddr) {
+    uint64_t desc = (uint64_t)((smemAddr & 0x3FFFFu) >> 4);
+    desc |= (uint64_t)1 << 16;
+    desc |= (uint64_t)(1024 >> 4) << 32;
+    desc |= (uint64_t)1 << 46;
+    desc |= (uint64_t)2 << 61;
+    return desc;
+}
+// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 128, N = 128.
+constexpr uint32_t kIdescBf16M128N128 =
+    (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+// ---- grouped INT4 GEMM ---------------------------------------------------------------------
+
+constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
+constexpr int kStagesLoad = 4;   // activations + packed codes (TMA destinations)
+constexpr int kStagesB = 3;      // dequantized bf16 operand tiles
+constexpr int kGemmThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 dequant, warps 6-9 epilogue
+constexpr uint32_t kTileABytes = kTileM * kTileK * 2;     // 16384
+constexpr uint32_t kTilePackedBytes = kTileN * kTileK / 2;  // 4096
+constexpr uint32_t kTileBBytes = kTileN * kTileK * 2;     // 16384
+constexpr uint32_t kTmemCols = 256;                       // two 128-column accumulators
+
+enum GemmMode : int { kModeGateUp = 0, kModeDown = 1 };
+
+struct GemmArgs {
+    const uint8_t *blobBase;   // expert 0's blob
+    uint64_t expertStride;
+    uint32_t scaleOff[2];      // byte offsets of the scales of matrix 0 / 1 inside a blob
+    uint32_t biasOff[2];
+    uint32_t K;                // contraction length (multiple of 64)
+    uint32_t N;                // outputs per row: F (gate/up) or D (down)
+    uint32_t nTiles;           // column tiles: ceil(N/64) for gate/up, ceil(N/128) for down
+    const RowTile *tiles;
+    const uint32_t *counts;    // counts[0] = row tiles
+    uint16_t *out;             // gate/up: activations [row][N]; down: output rows [*][N]
+    const FFTokenExpertPair *pairs;  // down: row -> (token, rank); null: row -> row
+    uint32_t topK;
+    uint32_t roundGateUp;      // gate/up: round both to bf16 before the activation
+    uint32_t *errorFlag;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW0,
+                    const __grid_constant__ CUtensorMap mapW1, const GemmArgs args) {
+    extern __shared__ uint8_t gemmSmemRaw[];
+    __shared__ uint64_t barriers[2 * kStagesLoad + 2 * kStagesB + 4];
+    __shared__ uint32_t tmemBaseSlot;
+    __shared__ volatile uint32_t abortFlag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rawBase = smem_u32(gemmSmemRaw);
+    const uint32_t base = (rawBase + 1023u) & ~1023u;
+    const uint32_t groupsK = args.K / kTileK;
+
+    // carve-up: A stages, B stages (1024-aligned), packed stages, scales
+    uint32_t aAddr[kStagesLoad], pAddr[kStagesLoad], bAddr[kStagesB];
+    uint32_t cursor = base;
+    for (int s = 0; s < kStagesLoad; ++s, cursor += kTileABytes) aAddr[s] = cursor;
+    for (int s = 0; s < kStagesB; ++s, cursor += kTileBBytes) bAddr[s] = cursor;
+    for (int s = 0; s < kStagesLoad; ++s, cursor += kTilePackedBytes) pAddr[s] = cursor;
+    uint8_t *scalesPtr = gemmSmemRaw + (cursor - rawBase);  // [128 rows][groupsK][2] bf16
+
+    const uint32_t barBase = smem_u32(barriers);
+    auto barLoadFull = [&](int s) { return barBase + 8u * (uint32_t)s; };
+    auto barLoadEmpty = [&](int s) { return barBase + 8u * (uint32_t)(kStagesLoad + s); };
+    auto barBFull = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + s); };
+    auto barBEmpty = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + kStagesB + s); };
+    auto barAccFull = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + 2 * kStagesB + s); };
+    auto barAccEmpty = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + 2 * kStagesB + 2 + s); };
+
+    if (threadIdx.x == 0) {
+        abortFlag = 0;
+        for (int s = 0; s < kStagesLoad; ++s) {
+            mbar_init(barLoadFull(s), 1);
+            mbar_init(barLoadEmpty(s), 5);  // one tcgen05.commit + four dequant warps
+        }
+        for (int s = 0; s < kStagesB; ++s) {
+            mbar_init(barBFull(s), 4);   // four dequant warps
+            mbar_init(barBEmpty(s), 1);  // one tcgen05.commit
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(barAccFull(s), 1);   // one tcgen05.commit
+            mbar_init(barAccEmpty(s), 4);  // four epilogue warps
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&tmemBaseSlot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmemBase = tmemBaseSlot;
+
+    const uint32_t rowTiles = args.counts[0];
+    const uint32_t units = rowTiles * args.nTiles;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const RowTile tile = args.tiles[u / args.nTiles];
+                const uint32_t nt = u % args.nTiles;
+                const int row0 = (int)tile.rowStart;
+                const int wRow0 = MODE == kModeGateUp ? (int)nt * 64 : (int)nt * 128;
+                const int wRow1 = MODE == kModeGateUp ? (int)nt * 64 : (int)nt * 128 + 64;
+                for (uint32_t g = 0; g < groupsK; ++g) {
+                    if (!mbar_wait(barLoadEmpty(stage), phase ^ 1u, &abortFlag)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(barLoadFull(stage), kTileABytes + kTilePackedBytes);
+                    tma_load_2d(aAddr[stage], &mapA, (int)(g * kTileK), row0, barLoadFull(stage));
+                    tma_load_3d(pAddr[stage], &mapW0, (int)(g * (kTileK / 2)), wRow0, (int)tile.expert,
+                                barLoadFull(stage));
+                    tma_load_3d(pAddr[stage] + kTilePackedBytes / 2, &mapW1, (int)(g * (kTileK / 2)),
+                                wRow1, (int)tile.expert, barLoadFull(stage));
+                    if (++stage == kStagesLoad) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0, acc = 0, accPhase = 0;
+            bool ok = true;
+            for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                if (!mbar_wait(barAccEmpty(acc), accPhase ^ 1u, &abortFlag)) break;
+                tc_fence_after();
+                const uint32_t tmemD = tmemBase + acc * (uint32_t)kTileN;
+                for (uint32_t g = 0; g < groupsK; ++g) {
+                    if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
+                        !mbar_wait(barBFull(bStage), bPhase, &abortFlag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t descA = umma_desc_sw128(aAddr[stage]);
+                    const uint64_t descB = umma_desc_sw128(bAddr[bStage]);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < kTileK / 16; ++kk) {
+                        // 32 bytes (>> 4 = 2) further along K for every 16-element slice
+                        tc_mma_bf16(tmemD, descA + 2u * kk, descB + 2u * kk, kIdescBf16M128N128,
+                                    (g | kk) != 0u ? 1u : 0u);
+                    }
+                    tc_commit(barLoadEmpty(stage));
+                    tc_commit(barBEmpty(bStage));
+                    if (++stage == kStagesLoad) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                    if (++bStage == kStagesB) {
+                        bStage = 0;
+                        bPhase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(barAccFull(acc));
+                if (++acc == 2) {
+                    acc = 0;
+                    accPhase ^= 1u;
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------- dequantizers: one operand row per thread ----------------
+        const int r = (warp - 2) * 32 + lane;  // operand row 0..127
+        const int matrix = MODE == kModeGateUp ? (r >> 6) : 0;
+        uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0;
+        uint16_t *myScales = reinterpret_cast<uint16_t *>(scalesPtr) + (size_t)r * groupsK * 2;
+        bool ok = true;
+        for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+            const RowTile tile = args.tiles[u / args.nTiles];
+            const uint32_t nt = u % args.nTiles;
+            const uint32_t wRow = MODE == kModeGateUp ? nt * 64 + (uint32_t)(r & 63) : nt * 128 + (uint32_t)r;
+            const uint8_t *blob = args.blobBase + (size_t)tile.expert * args.expertStride;
+            if (wRow < args.N) {
+                const uint16_t *sg = reinterpret_cast<const uint16_t *>(blob + args.scaleOff[matrix]) +
+                                     (size_t)wRow * groupsK;
+                const uint16_t *bg = reinterpret_cast<const uint16_t *>(blob + args.biasOff[matrix]) +
+                                     (size_t)wRow * groupsK;
+                for (uint32_t g = 0; g < groupsK; ++g) {
+                    myScales[2 * g] = sg[g];
+                    myScales[2 * g + 1] = bg[g];
+                }
+            } else {
+                for (uint32_t g = 0; g < 2 * groupsK; ++g) myScales[g] = 0;
+            }
+            for (uint32_t g = 0; g < groupsK; ++g) {
+                if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
+                    !mbar_wait(barBEmpty(bStage), bPhase ^ 1u, &abortFlag)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t s16 = myScales[2 * g], b16 = myScales[2 * g + 1];
+                const uint32_t s2 = s16 | (s16 << 16), b2 = b16 | (b16 << 16);
+                const uint32_t src = pAddr[stage] + (uint32_t)r * 32u;
+                const uint32_t dstRow = bAddr[bStage] + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t w[4];
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                                 : "r"(src + 16u * half));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            // codes i and i+4 of the word as the bf16 pair (128+q_i, 128+q_{i+4})
+                            uint32_t pair = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+                            uint32_t q2, v2;
+                            asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(q2) : "r"(pair), "r"(0x43004300u));
+                            asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(v2) : "r"(q2), "r"(s2), "r"(b2));
+                            o[i] = v2;
+                        }
+                        const uint32_t chunk = (uint32_t)(half * 4 + j);
+                        const uint32_t dst = dstRow + ((chunk ^ (uint32_t)(r & 7)) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[0]),
+                                     "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                     : "memory");
+                    }
+                }
+                fence_generic_to_async();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(barBFull(bStage));
+                    mbar_arrive(barLoadEmpty(stage));
+                }
+                if (++stage == kStagesLoad) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+                if (++bStage == kStagesB) {
+                    bStage = 0;
+                    bPhase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> global ----------------
+        const int quarter = warp & 3;                // TMEM lanes this warp may read
+        const int m = quarter * 32 + lane;           // row of the tile
+        uint32_t acc = 0, accPhase = 0;
+        for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) {
+            const RowTile tile = args.tiles[u / args.nTiles];
+            const uint32_t nt = u % args.nTiles;
+            if (!mbar_wait(barAccFull(acc), accPhase, &abortFlag)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmemBase + acc * (uint32_t)kTileN + ((uint32_t)(quarter * 32) << 16);
+            const bool rowLive = (uint32_t)m < tile.rows;
+            if (MODE == kModeGateUp) {
+                uint16_t *dstRow = args.out + (size_t)(tile.rowStart + (uint32_t)m) * args.N + (size_t)nt * 64;
+#pragma unroll
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t gr[32], ur[32];
+                    tc_load_32cols(taddr + (uint32_t)c0, gr);
+                    tc_load_32cols(taddr + 64u + (uint32_t)c0, ur);
+                    tc_wait_ld();
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int blk = 0; blk < 4; ++blk) {
+                        // eight activations, stored as 0,4,1,5,2,6,3,7 for the down GEMM
+                        float a[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float g = __uint_as_float(gr[blk * 8 + i]);
+                            float uu = __uint_as_float(ur[blk * 8 + i]);
+                            if (args.roundGateUp) {
+                                g = pf_bf2f(pf_f2bf(g));
+                                uu = pf_bf2f(pf_f2bf(uu));
+                            }
+                            a[i] = pf_gelu_tanh(g) * uu;
+                        }
+                        packed[blk * 4 + 0] = (uint32_t)pf_f2bf(a[0]) | ((uint32_t)pf_f2bf(a[4]) << 16);
+                        packed[blk * 4 + 1] = (uint32_t)pf_f2bf(a[1]) | ((uint32_t)pf_f2bf(a[5]) << 16);
+                        packed[blk * 4 + 2] = (uint32_t)pf_f2bf(a[2]) | ((uint32_t)pf_f2bf(a[6]) << 16);
+                        packed[blk * 4 + 3] = (uint32_t)pf_f2bf(a[3]) | ((uint32_t)pf_f2bf(a[7]) << 16);
+                    }
+                    if (rowLive && nt * 64 + (uint32_t)c0 < args.N) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2],
+                                                packed[4 * q + 3]);
+                    }
+                }
+            } else {
+                size_t outRow = tile.rowStart + (uint32_t)m;
+                if (args.pairs && rowLive) {
+                    const FFTokenExpertPair p = args.pairs[tile.rowStart + (uint32_t)m];
+                    outRow = (size_t)p.token * args.topK + p.rank;
+                }
+                uint16_t *dstRow = args.out + outRow * args.N + (size_t)nt * 128;
+#pragma unroll
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    uint32_t vr[32];
+                    tc_load_32cols(taddr + (uint32_t)c0, vr);
+                    tc_wait_ld();
+                    if (rowLive && nt * 128 + (uint32_t)c0 < args.N) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                o[i] = (uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
+                                       ((uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
+                            dst[q] = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(barAccEmpty(acc));
+            if (++acc == 2) {
+                acc = 0;
+                accPhase ^= 1u;
+            }
+        }
+    }
+
+    // teardown: every thread arrives here, also after a wait that ran out
+    __syncwarp();
+    if (abortFlag) {
+        // give copies still in flight time to land before shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+        if (threadIdx.x == 0) atomicExch(args.errorFlag, 1u + (uint32_t)MODE);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase),
+                     "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled(const char **error) {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t st = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+    if (st != cudaSuccess || q != cudaDriverEntryPointSuccess || !sym) {
+        fail(error, "cuTensorMapEncodeTiled is not available from the driver");
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+    return fn;
+}
+
+// bf16 activations [rows][k] (row pitch `strideElems`), box 64 x 128, 128-byte swizzle.
+static bool make_activation_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k,
+                                uint64_t strideElems, const char **error) {
+    EncodeTiledFn fn = encode_tiled(error);
+    if (!fn) return false;
+    cuuint64_t dims[2] = {k, rows};
+    cuuint64_t strides[1] = {strideElems * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTileM};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
+                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(error, "cuTensorMapEncodeTiled(activations) failed: " + std::to_string((int)rc));
+    return true;
+}
+
+// packed codes of one matrix across all experts: bytes [experts][rows][cols/2], box 32 x 64 x 1.
+static bool make_weight_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
+                            uint64_t experts, uint64_t expertStride, const char **error) {
+    EncodeTiledFn fn = encode_tiled(error);
+    if (!fn) return false;
+    cuuint64_t dims[3] = {cols / 2, rows, experts};
+    cuuint64_t strides[2] = {cols / 2, expertStride};
+    cuuint32_t box[3] = {(cuuint32_t)(kTileK / 2), 64, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides,
+                     box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(error, "cuTensorMapEncodeTiled(weights) failed: " + std::to_string((int)rc));
+    return true;
+}
+
+bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error) {
+    if (L.mapsReady) return true;
+    const FFConfig &c = ctx->cfg;
+    if (L.experts) {
+        const uint32_t *o = &L.off.gateWOff;
+        for (int m = 0; m < 3; ++m) {
+            const uint64_t rows = m == 2 ? c.d : c.f, cols = m == 2 ? c.f : c.d;
+            if (!make_weight_map(&L.routedMap[m], L.experts + o[3 * m], rows, cols, L.expertCount,
+                                 L.stride, error))
+                return false;
+        }
+    }
+    if (L.shared) {
+        const uint32_t *o = &L.sharedOff.gateWOff;
+        uint64_t payload = 0;
+        packed_offsets(c.d, c.sharedF, &payload);
+        for (int m = 0; m < 3; ++m) {
+            const uint64_t rows = m == 2 ? c.d : c.sharedF, cols = m == 2 ? c.sharedF : c.d;
+            if (!make_weight_map(&L.sharedMap[m], L.shared + o[3 * m], rows, cols, 1,
+                                 (payload + 15) & ~15ull, error))
+                return false;
+        }
+    }
+    L.mapsReady = true;
+    return true;
+}
+
+static size_t gemm_smem_bytes(uint32_t K) {
+    return 1024 + (size_t)kStagesLoad * (kTileABytes + kTilePackedBytes) + (size_t)kStagesB * kTileBBytes +
+           (size_t)kTileN * (K / kTileK) * 2 * sizeof(uint16_t);
+}
+
+template <int MODE>
+static bool launch_gemm(FFContext *ctx, const CUtensorMap &mapA, const CUtensorMap &mapW0,
+                        const CUtensorMap &mapW1, const GemmArgs &args, uint32_t maxUnits,
+                        cudaStream_t stream, const char **error) {
+    auto kernel = k_grouped_int4_gemm<MODE>;
+    const size_t smem = gemm_smem_bytes(args.K);
+    if (smem > 220 * 1024) return fail(error, "contraction length too large for the GEMM's shared memory");
+    static size_t configured[8] = {0};
+    if (configured[ctx->device & 7] != smem) {
+        FF_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                   error);
+        configured[ctx->device & 7] = smem;
+    }
+    const uint32_t grid = std::max(1u, std::min<uint32_t>((uint32_t)ctx->smCount, maxUnits));
+    {
+        LaunchScope scope(ctx, stream, MODE == kModeGateUp ? "int4_gemm_gate_up_act" : "int4_gemm_down");
+        kernel<<<grid, kGemmThreads, smem, stream>>>(mapA, mapW0, mapW1, args);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+static bool check_gemm_shapes(const FFConfig &c, uint32_t f, const char **error) {
+    if (c.d % 64 || f % 64) return fail(error, "GEMM path needs widths that are multiples of 64");
+    return true;
+}
+
+bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uint32_t xStride,
+                           uint32_t tokens, const uint32_t *ids, uint16_t *partials,
+                           cudaStream_t stream, const char **error) {
+    const FFConfig &c = ctx->cfg;
+    if (tokens == 0) return true;
+    if (!ctx->xSorted) return fail(error, "context was created with maxTokens <= 16: no prefill scratch");
+    if (!L.experts) return fail(error, "layer has no resident experts");
+    if (!check_gemm_shapes(c, c.f, error) || !prefill_prepare_layer(ctx, L, error)) return false;
+    const int T = (int)tokens, K = (int)c.topK, E = (int)L.expertCount;
+    const uint32_t blocks = (tokens + kSortTokens - 1) / kSortTokens;
+    const size_t sortSmem = (size_t)kSortTokens * K * sizeof(uint32_t);
+    RowTile *tiles = reinterpret_cast<RowTile *>(ctx->units);
+    const uint32_t maxTiles = ctx->maxUnits / 2;  // first half of the tile buffer
+    {
+        LaunchScope scope(ctx, stream, "route_count");
+        k_route_count<<<blocks, 256, sortSmem, stream>>>(ids, T, K, E, ctx->blockCounts);
+    }
+    {
+        LaunchScope scope(ctx, stream, "route_scan");
+        k_route_scan<<<1, 256, 0, stream>>>(ctx->blockCounts, (int)blocks, E, ctx->expertOffsets, tiles,
+                                            maxTiles, ctx->unitCount);
+    }
+    {
+        LaunchScope scope(ctx, stream, "route_scatter");
+        k_route_scatter<<<blocks, 256, sortSmem, stream>>>(ids, nullptr, T, K, E, ctx->blockCounts,
+                                                           ctx->expertOffsets, ctx->sortedPairs);
+    }
+    const uint32_t pairs = tokens * c.topK;
+    {
+        LaunchScope scope(ctx, stream, "gather_rows");
+        k_gather_rows<<<ctx->smCount * 8, 256, 0, stream>>>(x, xStride, ctx->sortedPairs, nullptr, pairs,
+                                                            (int)c.d, ctx->xSorted);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+
+    const uint32_t tileBound = pairs / 128 + (uint32_t)E;
+    CUtensorMap mapX, mapActs;
+    if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)pairs + 128, c.d, c.d, error)) return false;
+    if (!make_activation_map(&mapActs, ctx->acts, (uint64_t)pairs + 128, c.f, c.f, error)) return false;
+
+    GemmArgs a{};
+    a.blobBase = L.experts;
+    a.expertStride = L.stride;
+    a.scaleOff[0] = L.off.gateSOff;
+    a.biasOff[0] = L.off.gateBOff;
+    a.scaleOff[1] = L.off.upSOff;
+    a.biasOff[1] = L.off.upBOff;
+    a.K = c.d;
+    a.N = c.f;
+    a.nTiles = (c.f + 63) / 64;
+    a.tiles = tiles;
+    a.counts = ctx->unitCount;
+    a.out = ctx->acts;
+    a.pairs = nullptr;
+    a.topK = c.topK;
+    a.roundGateUp = 0;
+    a.errorFlag = ctx->errorFlag;
+    if (!launch_gemm<kModeGateUp>(ctx, mapX, L.routedMap[0], L.routedMap[1], a, tileBound * a.nTiles,
+                                  stream, error))
+        return false;
+
+    GemmArgs b = a;
+    b.scaleOff[0] = b.scaleOff[1] = L.off.downSOff;
+    b.biasOff[0] = b.biasOff[1] = L.off.downBOff;
+    b.K = c.f;
+    b.N = c.d;
+    b.nTiles = (c.d + 127) / 128;
+    b.out = partials;
+    b.pairs = ctx->sortedPairs;
+    return launch_gemm<kModeDown>(ctx, mapActs, L.routedMap[2], L.routedMap[2], b, tileBound * b.nTiles,
+                                  stream, error);
+}
+
+bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uint32_t xStride,
+                           uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error) {
+    const FFConfig &c = ctx->cfg;
+    if (tokens == 0) return true;
+    if (!ctx->xSorted) return fail(error, "context was created with maxTokens <= 16: no prefill scratch");
+    if (!L.shared) return fail(error, "layer has no resident shared FFN");
+    if (!check_gemm_shapes(c, c.sharedF, error) || !prefill_prepare_layer(ctx, L, error)) return false;
+    // dense problem: its row tiles live behind the routed ones in the units buffer
+    RowTile *tiles = reinterpret_cast<RowTile *>(ctx->units) + ctx->maxUnits / 2;
+    uint32_t *counts = ctx->unitCount + 4;
+    {
+        LaunchScope scope(ctx, stream, "dense_tiles");
+        k_dense_tiles<<<1, 256, 0, stream>>>((int)tokens, tiles, counts);
+    }
+    {
+        LaunchScope scope(ctx, stream, "gather_rows");
+        k_gather_rows<<<ctx->smCount * 8, 256, 0, stream>>>(x, xStride, nullptr, nullptr, tokens,
+                                                            (int)c.d, ctx->xSorted);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    const uint32_t rowTiles = (tokens + 127) / 128;
+    CUtensorMap mapX, mapActs;
+    if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)tokens + 128, c.d, c.d, error)) return false;
+    if (!make_activation_map(&mapActs, ctx->sharedActs, (uint64_t)tokens + 128, c.sharedF, c.sharedF, error))
+        return false;
+    uint64_t payload = 0;
+    packed_offsets(c.d, c.sharedF, &payload);
+    GemmArgs a{};
+    a.blobBase = L.shared;
+    a.expertStride = (payload + 15) & ~15ull;
+    a.scaleOff[0] = L.sharedOff.gateSOff;
+    a.biasOff[0] = L.sharedOff.gateBOff;
+    a.scaleOff[1] = L.sharedOff.upSOff;
+    a.biasOff[1] = L.sharedOff.upBOff;
+    a.K = c.d;
+    a.N = c.sharedF;
+    a.nTiles = (c.sharedF + 63) / 64;
+    a.tiles = tiles;
+    a.counts = counts;
+    a.out = ctx->sharedActs;
+    a.topK = c.topK;
+    a.roundGateUp = 1;
+    a.errorFlag = ctx->errorFlag;
+    if (!launch_gemm<kModeGateUp>(ctx, mapX, L.sharedMap[0], L.sharedMap[1], a, rowTiles * a.nTiles, stream,
+                                  error))
+        return false;
+    GemmArgs b = a;
+    b.scaleOff[0] = b.scaleOff[1] = L.sharedOff.downSOff;
+    b.biasOff[0] = b.biasOff[1] = L.sharedOff.downBOff;
+    b.K = c.sharedF;
+    b.N = c.d;
+    b.nTiles = (c.d + 127) / 128;
+    b.out = y;
+    b.pairs = nullptr;
+    return launch_gemm<kModeDown>(ctx, mapActs, L.sharedMap[2], L.sharedMap[2], b, rowTiles * b.nTiles,
+                                  stream, error);
 }
 
 }  // namespace ff
 
-extern "C" bool ff_last_prefill_routes(FFContext *, FFTokenExpertPair *, uint32_t *,
-                                       const char **error) {
-    return ff::fail(error, "prefill path is not built");
+extern "C" bool ff_last_prefill_routes(FFContext *ctx, FFTokenExpertPair *sortedPairs,
+                                       uint32_t *offsets, const char **error) {
+    using namespace ff;
+    if (error) *error = nullptr;
+    if (!ctx || !sortedPairs || !offsets) return fail(error, "null argument");
+    if (!ctx->sortedPairs) return fail(error, "context has no prefill scratch");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    FF_CUDA_OK(cudaDeviceSynchronize(), error);
+    uint32_t counts[4] = {0, 0, 0, 0};
+    FF_CUDA_OK(cudaMemcpy(counts, ctx->unitCount, sizeof(counts), cudaMemcpyDeviceToHost), error);
+    FF_CUDA_OK(cudaMemcpy(sortedPairs, ctx->sortedPairs, (size_t)counts[1] * sizeof(FFTokenExpertPair),
+                          cudaMemcpyDeviceToHost),
+               error);
+    FF_CUDA_OK(cudaMemcpy(offsets, ctx->expertOffsets, (size_t)(ctx->cfg.experts + 1) * sizeof(uint32_t),
+                          cudaMemcpyDeviceToHost),
+               error);
+    return true;
 }

@@ -66,6 +66,9 @@ class ClockSampler:
                  "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            deadline = time.time() + 3.0
+            while not self.lines and time.time() < deadline:
+                time.sleep(0.02)
         except OSError:
             self.proc = None
 

@@ -83,6 +83,8 @@ typedef struct {
     uint32_t lastPrefillUnits;   /* GEMM work units of the last prefill call   */
     uint32_t deviceOrdinal;
     uint32_t smCount;
+    uint32_t deviceErrorFlag;    /* non-zero: a kernel gave up a bounded wait (after a sync) */
+    uint32_t reserved;
 } FFInfo;
 
 /* Device time of one kernel name, summed over the launches made while tracing was on. */

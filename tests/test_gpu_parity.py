@@ -193,7 +193,9 @@ def test_single_expert_decode_config0(full, oracle):
     L, ctx = full
     x = workload.make_tokens(50, "cfg0", 1, L.d)
     for expert in (0, 77):
-        ids = torch.tensor([[expert] + [0] * 7], dtype=torch.int32, device=ctx.device)
+        # the other seven slots name distinct experts with weight 0 (a token's routes are distinct)
+        others = [e for e in range(8) if e != expert][:7]
+        ids = torch.tensor([[expert] + others], dtype=torch.int32, device=ctx.device)
         w = dev(synth.bf16_bits(np.array([[1.0] + [0.0] * 7], dtype=np.float32)), ctx)
         y = torch.zeros((1, L.d), dtype=torch.bfloat16, device=ctx.device)
         hp.MoE(ctx).encodeRoutedPersistentGPUSlots(None, 0, ids, dev(x, ctx), w, None, y)
