@@ -986,3 +986,109 @@ bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, c
 }
 
 }  // namespace ff
+
+namespace ff {
+struct GemmJobPair {
+    GemvJob first{}, second{};
+};
+}  // namespace ff
+
+// ---- shared FFN without any allocation -----------------------------------------------------
+
+// Scratch for ff_shared_ffn_noalloc: the GeGLU activations between the gate/up kernel and the
+// down kernel, [kNoAllocMaxRows][kNoAllocMaxIntermediate] bf16 = 128 KiB.  It is part of the
+// library image, so every GPU that loads the library holds it until the process exits.
+constexpr uint32_t kNoAllocMaxRows = 16;
+constexpr uint32_t kNoAllocMaxIntermediate = 4096;
+static __device__ __align__(256) uint16_t g_noAllocActs[kNoAllocMaxRows * kNoAllocMaxIntermediate];
+
+extern "C" bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjection *up,
+                                      const FFProjection *down, const uint16_t *x,
+                                      uint32_t xStride, uint32_t rows, uint16_t *y,
+                                      uint32_t yStride, void *stream, const char **error) {
+    using namespace ff;
+    if (error) *error = nullptr;
+    if (!gate || !up || !down || !x || !y) return fail(error, "null argument");
+    if (rows == 0) return true;
+    if (rows > kNoAllocMaxRows)
+        return fail(error, "ff_shared_ffn_noalloc takes at most " + std::to_string(kNoAllocMaxRows) +
+                               " rows, got " + std::to_string(rows));
+    const uint32_t d = gate->cols, f = gate->rows;
+    if (f > kNoAllocMaxIntermediate)
+        return fail(error, "intermediate width " + std::to_string(f) +
+                               " exceeds the static scratch's maximum of " +
+                               std::to_string(kNoAllocMaxIntermediate));
+    if (up->rows != f || up->cols != d || down->rows != d || down->cols != f)
+        return fail(error, "SharedExpert dimension mismatch: gate=(" + std::to_string(gate->rows) + "," +
+                               std::to_string(gate->cols) + ") up=(" + std::to_string(up->rows) + "," +
+                               std::to_string(up->cols) + ") down=(" + std::to_string(down->rows) + "," +
+                               std::to_string(down->cols) + ")");
+    if (d % kGroup || f % kGroup || d == 0 || f == 0)
+        return fail(error, "widths must be non-zero multiples of the group size 64");
+    if (xStride < d || yStride < d || xStride % 2) return fail(error, "row stride is too small or odd");
+    const FFProjection *ps[3] = {gate, up, down};
+    for (const FFProjection *p : ps)
+        if (!p->weights || !p->scales || !p->biases || (reinterpret_cast<uintptr_t>(p->weights) & 15u))
+            return fail(error, "projection pointers must be non-null and the weights 16-byte aligned");
+
+    // Per-device set-up, done by the first call on each device with that device current: the
+    // array's name is only a host-side handle, so its device address is looked up here.
+    struct DeviceSetup {
+        uint16_t *scratch = nullptr;
+        int smCount = 0;
+    };
+    static DeviceSetup setups[64];
+    int device = 0;
+    FF_CUDA_OK(cudaGetDevice(&device), error);
+    if (device < 0 || device >= 64) return fail(error, "device ordinal out of range");
+    DeviceSetup &setup = setups[device];
+    if (!setup.scratch) {
+        void *ptr = nullptr;
+        FF_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noAllocActs), error);
+        int sms = 0;
+        FF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), error);
+        if (!ptr || sms <= 0) return fail(error, "could not set up the static scratch on this device");
+        setup.smCount = sms;
+        setup.scratch = static_cast<uint16_t *>(ptr);
+    }
+
+    FFContext local;  // launch bookkeeping only: owns nothing on the device
+    local.device = device;
+    local.smCount = setup.smCount;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    GemmJobPair jobs;
+    GemvJob &j0 = jobs.first, &j1 = jobs.second;
+    j0.w0 = static_cast<const uint8_t *>(gate->weights);
+    j0.s0 = static_cast<const uint16_t *>(gate->scales);
+    j0.b0 = static_cast<const uint16_t *>(gate->biases);
+    j0.w1 = static_cast<const uint8_t *>(up->weights);
+    j0.s1 = static_cast<const uint16_t *>(up->scales);
+    j0.b1 = static_cast<const uint16_t *>(up->biases);
+    j0.in = x;
+    j0.out = setup.scratch;
+    j0.rows = f;
+    j0.cols = d;
+    j0.inStride = xStride;
+    j0.outStride = f;
+    j0.n = rows;
+    j0.flags = kJobRoundGateUp;
+    j1.w0 = static_cast<const uint8_t *>(down->weights);
+    j1.s0 = static_cast<const uint16_t *>(down->scales);
+    j1.b0 = static_cast<const uint16_t *>(down->biases);
+    j1.in = setup.scratch;
+    j1.out = y;
+    j1.rows = d;
+    j1.cols = f;
+    j1.inStride = f;
+    j1.outStride = yStride;
+    j1.n = rows;
+    for (uint32_t i = 0; i < (uint32_t)kMaxGemvRows; ++i)
+        j0.inRow[i] = j0.outRow[i] = j1.inRow[i] = j1.outRow[i] = i < rows ? i : 0u;
+    if (!launch_gemv_class<true>(&local, rows, nullptr, nullptr, nullptr, j0, blocks_of(j0.rows),
+                                 j0.cols, blocks_of(j0.rows), s, error))
+        return false;
+    return launch_gemv_class<false>(&local, rows, nullptr, nullptr, nullptr, j1, blocks_of(j1.rows),
+                                    j1.cols, blocks_of(j1.rows), s, error);
+}
+

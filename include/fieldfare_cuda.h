@@ -201,6 +201,27 @@ bool ff_moe_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *wei
 bool ff_shared_ffn(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
                    uint32_t tokens, uint16_t *y, void *stream, const char **error);
 
+/* The shared INT4 FFN for up to 16 rows for callers that must not allocate device memory: a
+ * decode loop on a latency budget, where cudaMalloc/cudaFree would synchronize the whole device,
+ * or a process whose HBM is already reserved by another runtime (a serving engine that
+ * pre-allocates its pool), where cudaMalloc fails or is forbidden by policy.  It has no
+ * counterpart in the reference.  It needs no FFContext: the three projections, x and y are
+ * DEVICE pointers supplied by the caller, and the only scratch (the GeGLU activations between the
+ * two kernels) is a fixed 128 KiB array inside the library image, which every GPU that loads the
+ * library holds until the process exits.  Sizes are therefore limited to rows <= 16 and
+ * intermediate width (gate->rows) <= 4096; larger requests fail with a message.  The call
+ * performs no cudaMalloc, cudaFree or other allocating routine.  The first call on each device
+ * looks up that array's device address (with the device current); make that first call before
+ * any stream capture begins.  All calls on a device share the one array and it keeps the last
+ * call's contents: nothing in it needs clearing (every element read was written earlier in the
+ * same call), but two calls whose kernels overlap on the GPU (issued on different streams without
+ * an ordering between them) race on it and must be ordered by the caller.  Results are bitwise
+ * those of ff_shared_ffn on the same weights and rows. */
+bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjection *up,
+                           const FFProjection *down, const uint16_t *x, uint32_t xStride,
+                           uint32_t rows, uint16_t *y, uint32_t yStride, void *stream,
+                           const char **error);
+
 /* Y[r][o] = sum_k W[o][k] X[r][k] for rows <= 16 input rows, all pointers on the device.
  * Replaces `DequantInt4GEMV.encodeRows` (Kernels/Quant/DequantInt4GEMV.swift:72-117). */
 bool ff_int4_gemv_rows(FFContext *ctx, const FFProjection *projection, const uint16_t *x,

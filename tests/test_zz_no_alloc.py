@@ -1,0 +1,57 @@
+"""ff_shared_ffn_noalloc: the shared INT4 FFN for callers that cannot allocate device memory
+(a decode loop where cudaMalloc would stall the GPU, or a process whose HBM another runtime has
+already reserved).
+Its activations scratch is a fixed array inside the library; this test drives it through the
+C ABI and checks it against the context-based ff_shared_ffn on the same weights, twice in a row
+(the second call reuses the array with the first call's contents still in it)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from ane_fieldfare_b200 import binding, gturbo, workload
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def test_noalloc_shared_ffn_matches_context_path_twice():
+    from ane_fieldfare_b200 import hotpath as hp
+    L = workload.make_layer(0x40A110C, 0, experts=8, d=256, f=64, sharedF=320, topK=4)
+    ctx = hp.HotpathContext(layers=1, experts=8, d=256, f=64, sharedF=320, topK=4, maxTokens=16)
+    try:
+        workload.load_layer(ctx, 0, L)
+        device = ctx.device
+        keep, projs = [], []
+        for role in gturbo.ROLES:
+            w, s, b = gturbo.sub_tensor(L.sharedBlob, L.sharedLayout, role)
+            rows, cols = L.sharedLayout.matrix_shape(role)
+            wd = torch.from_numpy(np.ascontiguousarray(w)).to(device)
+            sd = hp.bf16_tensor(np.ascontiguousarray(s), device)
+            bd = hp.bf16_tensor(np.ascontiguousarray(b), device)
+            keep += [wd, sd, bd]
+            projs.append(binding.FFProjection(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), rows, cols))
+        stream = torch.cuda.current_stream().cuda_stream or None
+        for call_index, rows in enumerate((16, 5)):
+            x = hp.bf16_tensor(workload.make_tokens(7 + call_index, "noalloc", rows, 256), device)
+            want = torch.zeros((rows, 256), dtype=torch.bfloat16, device=device)
+            hp.SharedExpertInt4(ctx).encode(None, 0, x, want, rows=rows)
+            got = torch.full((rows, 256), 7.0, dtype=torch.bfloat16, device=device)
+            binding.call("ff_shared_ffn_noalloc", ctypes.byref(projs[0]), ctypes.byref(projs[1]),
+                         ctypes.byref(projs[2]), x.data_ptr(), 256, rows, got.data_ptr(), 256, stream)
+            torch.cuda.synchronize()
+            assert torch.isfinite(got.float()).all()
+            diff = (got.float() - want.float()).abs().max().item()
+            peak = max(1.0, want.float().abs().max().item())
+            assert diff <= 2e-2 * peak, (call_index, diff)
+            assert torch.equal(got, want), f"call {call_index}: not bitwise the context path"
+        # sizes beyond the static scratch are refused with a message
+        with pytest.raises(binding.FieldfareError, match="at most 16 rows"):
+            binding.call("ff_shared_ffn_noalloc", ctypes.byref(projs[0]), ctypes.byref(projs[1]),
+                         ctypes.byref(projs[2]), x.data_ptr(), 256, 17, got.data_ptr(), 256, stream)
+        wide = binding.FFProjection(projs[0].weights, projs[0].scales, projs[0].biases, 8192, 256)
+        with pytest.raises(binding.FieldfareError, match="exceeds the static scratch"):
+            binding.call("ff_shared_ffn_noalloc", ctypes.byref(wide), ctypes.byref(projs[1]),
+                         ctypes.byref(projs[2]), x.data_ptr(), 256, 4, got.data_ptr(), 256, stream)
+    finally:
+        ctx.close()
