@@ -67,7 +67,7 @@ void ff_destroy(FFContext *ctx) {
                     ctx->items[0], ctx->items[1], ctx->acts, ctx->sharedActs, ctx->h1,
                     ctx->partials, ctx->xDev, ctx->yDev, ctx->xSorted, ctx->sortedPairs,
                     ctx->expertOffsets, ctx->blockCounts, ctx->units, ctx->unitCount,
-                    ctx->errorFlag, ctx->mapScratch};
+                    ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch};
     for (void *p : ptrs) cudaFree(p);
     if (ctx->hostStream) cudaStreamDestroy(ctx->hostStream);
     delete ctx;
@@ -133,21 +133,25 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     ok = ok && dev_alloc(ctx, &ctx->jobs[1], 1 + planExperts, error);
     ok = ok && dev_alloc(ctx, &ctx->items[0], ctx->maxItems, error);
     ok = ok && dev_alloc(ctx, &ctx->items[1], ctx->maxItems, error);
-    ok = ok && dev_alloc(ctx, &ctx->acts, (T * K + 128) * c.f, error);  // +128: a GEMM row tile may overhang
-    ok = ok && dev_alloc(ctx, &ctx->sharedActs, (T + 128) * c.sharedF, error);
+    ok = ok && dev_alloc(ctx, &ctx->acts, (T * K + 256) * c.f, error);  // +256: a GEMM row tile may overhang
+    ok = ok && dev_alloc(ctx, &ctx->sharedActs, (T + 256) * c.sharedF, error);
     ok = ok && dev_alloc(ctx, &ctx->h1, T * c.d, error);
     ok = ok && dev_alloc(ctx, &ctx->partials, T * K * c.d, error);
     ok = ok && dev_alloc(ctx, &ctx->xDev, T * c.d, error);
     ok = ok && dev_alloc(ctx, &ctx->yDev, T * c.d, error);
     ok = ok && dev_alloc(ctx, &ctx->errorFlag, 4, error);
     if (ok) ok = cudaMemset(ctx->errorFlag, 0, 16) == cudaSuccess;
+    ok = ok && dev_alloc(ctx, &ctx->phaseStamps, 8, error);
+    if (ok) ok = cudaMemset(ctx->phaseStamps, 0, 64) == cudaSuccess;
+    ok = ok && dev_alloc(ctx, &ctx->gridBarrier, 4, error);
+    if (ok) ok = cudaMemset(ctx->gridBarrier, 0, 16) == cudaSuccess;
     if (ok && T > (size_t)kMaxGemvRows) {
         const size_t pairs = T * K;
         const size_t permuteBlocks = (T + 255) / 256;
         // one work unit per (expert, 128-row tile, column tile); tiles <= pairs/128 + experts
         ctx->maxUnits = (uint32_t)(2 * (pairs / 128 + c.experts + 2));  // row tiles: routed half, dense half
-        ok = ok && dev_alloc(ctx, &ctx->xSorted, (pairs + 128) * c.d, error);
-        if (ok) ok = cudaMemset(ctx->xSorted, 0, (pairs + 128) * c.d * 2) == cudaSuccess;
+        ok = ok && dev_alloc(ctx, &ctx->xSorted, (pairs + 256) * c.d, error);
+        if (ok) ok = cudaMemset(ctx->xSorted, 0, (pairs + 256) * c.d * 2) == cudaSuccess;
         ok = ok && dev_alloc(ctx, &ctx->sortedPairs, pairs, error);
         ok = ok && dev_alloc(ctx, &ctx->expertOffsets, c.experts + 1, error);
         ok = ok && dev_alloc(ctx, &ctx->blockCounts, (permuteBlocks + 1) * c.experts, error);
@@ -188,6 +192,17 @@ FFInfo ff_get_info(const FFContext *ctx) {
 
 void ff_set_tracing(FFContext *ctx, bool enabled) {
     if (ctx) ctx->tracing = enabled;
+}
+
+bool ff_decode_phase_times(FFContext *ctx, double *microseconds, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !microseconds) return fail(error, "null argument");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    FF_CUDA_OK(cudaDeviceSynchronize(), error);
+    unsigned long long t[8] = {0};
+    FF_CUDA_OK(cudaMemcpy(t, ctx->phaseStamps, sizeof(t), cudaMemcpyDeviceToHost), error);
+    for (int i = 0; i < 6; ++i) microseconds[i] = t[i + 1] >= t[i] ? (double)(t[i + 1] - t[i]) * 1e-3 : 0.0;
+    return true;
 }
 
 uint32_t ff_get_trace(FFContext *ctx, FFTraceEntry *entries, uint32_t capacity) {

@@ -17,191 +17,10 @@
 //   Sources/ANEFieldfareHotpath/Metal/Quant/dequant_int4.metal:78-347
 #include <algorithm>
 
+#include "ff_gemv_device.cuh"
 #include "ff_internal.cuh"
 
 namespace ff {
-
-constexpr int kGemvThreads = 256;
-constexpr int kRowsPerItem = (kGemvThreads / 32) * 4;
-constexpr int kDecodeDownRows = 8;  // output rows per CTA of the decode combine kernel
-
-__device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
-
-// Round-half-even on the dropped 16 bits: Quantization.bf16Bits
-// (Sources/ANEFieldfareHotpath/Infrastructure/ModelIO/Quantization.swift:9-16).
-__device__ __forceinline__ uint16_t f2bf(float f) {
-    uint32_t u = __float_as_uint(f);
-    u += 0x7FFFu + ((u >> 16) & 1u);
-    return (uint16_t)(u >> 16);
-}
-__device__ __forceinline__ float bf16_round(float f) { return bf2f(f2bf(f)); }
-
-// gelu_pytorch_tanh with the kernels' clamp (Metal/MoE/moe.metal:40-47).
-__device__ __forceinline__ float gelu_tanh(float x) {
-    const float x3 = x * x * x;
-    float inner = 0.7978845608028654f * (x + 0.044715f * x3);
-    inner = fminf(fmaxf(inner, -20.0f), 20.0f);
-    return 0.5f * x * (1.0f + tanhf(inner));
-}
-
-// Position of input element e inside a staged row: chunks are interleaved in blocks of eight so
-// that lanes j = 0..7 (chunks c = 8i + j) read one contiguous 128 bytes per 128-bit load.
-__device__ __forceinline__ int staged_index(int e) {
-    const int c = e >> 5;
-    return ((c >> 3) << 8) + (((e >> 2) & 7) << 5) + ((c & 7) << 2) + (e & 3);
-}
-__host__ __device__ inline int staged_stride(int cols) { return (cols + 255) & ~255; }
-
-// Eight codes of one 32-bit word as the floats 16+q: the code goes into the top mantissa bits of
-// a float whose exponent is 2^4.  The surplus 16*sum(x) is taken out once per chunk through the
-// bias term, so no per-code subtraction is needed.
-__device__ __forceinline__ void unpack8_plus16(uint32_t w, float (&q)[8]) {
-    constexpr uint32_t kMask = 0x00780000u, kBase = 0x41800000u;
-    q[0] = __uint_as_float(((w << 19) & kMask) | kBase);
-    q[1] = __uint_as_float(((w << 15) & kMask) | kBase);
-    q[2] = __uint_as_float(((w << 11) & kMask) | kBase);
-    q[3] = __uint_as_float(((w << 7) & kMask) | kBase);
-    q[4] = __uint_as_float(((w << 3) & kMask) | kBase);
-    q[5] = __uint_as_float(((w >> 1) & kMask) | kBase);
-    q[6] = __uint_as_float(((w >> 5) & kMask) | kBase);
-    q[7] = __uint_as_float(((w >> 9) & kMask) | kBase);
-}
-
-__device__ __forceinline__ uint4 load_stream(const uint4 *p) { return __ldcs(p); }
-
-// Stages n bf16 input rows (indices rowIdx[0..n)) as fp32 in chunk-interleaved order, then the
-// per-chunk sums of each row.  All threads of the CTA take part.
-__device__ void stage_rows(const uint16_t *in, uint32_t inStride, const uint32_t *rowIdx, int n,
-                           int cols, float *xs, float *xsum) {
-    const int stride = staged_stride(cols);
-    const int chunks = cols >> 5;
-    const int pairsPerRow = cols >> 1;
-    for (int i = threadIdx.x; i < n * pairsPerRow; i += blockDim.x) {
-        const int r = i / pairsPerRow, p = i - r * pairsPerRow;
-        const uint32_t two =
-            *reinterpret_cast<const uint32_t *>(in + (size_t)rowIdx[r] * inStride + 2 * p);
-        float *dst = xs + r * stride + staged_index(2 * p);
-        dst[0] = __uint_as_float(two << 16);
-        dst[1] = __uint_as_float(two & 0xFFFF0000u);
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < n * chunks; i += blockDim.x) {
-        const int r = i / chunks, c = i - r * chunks;
-        const float *src = xs + r * stride + ((c >> 3) << 8) + ((c & 7) << 2);
-        float s = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float4 v = *reinterpret_cast<const float4 *>(src + (k << 5));
-            s += v.x;
-            s += v.y;
-            s += v.z;
-            s += v.w;
-        }
-        xsum[r * chunks + c] = s;
-    }
-    __syncthreads();
-}
-
-// One weight row (or a gate/up row pair) against NT staged input rows; returns the full sums in
-// every lane of the row's eight-lane group.  `live` false skips the loads but keeps the
-// shuffles convergent.
-template <int NT, bool DUAL>
-__device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, const uint16_t *b0,
-                                        const uint8_t *w1, const uint16_t *s1, const uint16_t *b1,
-                                        int row, int cols, bool live, const float *xs,
-                                        const float *xsum, int n, float (&a0)[NT],
-                                        float (&a1)[NT]) {
-    const int lane = threadIdx.x & 31;
-    const int j = lane & 7;
-    const int chunks = cols >> 5;
-    const int groups = cols >> 6;
-    const int stride = staged_stride(cols);
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-        a0[t] = 0.0f;
-        a1[t] = 0.0f;
-    }
-    if (live) {
-        const uint4 *p0 = reinterpret_cast<const uint4 *>(w0 + (size_t)row * (cols >> 1));
-        const uint4 *p1 = DUAL ? reinterpret_cast<const uint4 *>(w1 + (size_t)row * (cols >> 1)) : p0;
-        const uint16_t *sr0 = s0 + (size_t)row * groups, *br0 = b0 + (size_t)row * groups;
-        const uint16_t *sr1 = DUAL ? s1 + (size_t)row * groups : sr0;
-        const uint16_t *br1 = DUAL ? b1 + (size_t)row * groups : br0;
-        for (int c = j; c < chunks; c += 8) {
-            const uint4 v0 = load_stream(p0 + c);
-            uint4 v1 = v0;
-            if (DUAL) v1 = load_stream(p1 + c);
-            const float sc0 = bf2f(sr0[c >> 1]);
-            const float bi0 = fmaf(-16.0f, sc0, bf2f(br0[c >> 1]));
-            float sc1 = 0.0f, bi1 = 0.0f;
-            if (DUAL) {
-                sc1 = bf2f(sr1[c >> 1]);
-                bi1 = fmaf(-16.0f, sc1, bf2f(br1[c >> 1]));
-            }
-            float d0[NT], d1[NT];
-#pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                d0[t] = 0.0f;
-                d1[t] = 0.0f;
-            }
-            const float *xc = xs + ((c >> 3) << 8) + ((c & 7) << 2);
-            const uint32_t words0[4] = {v0.x, v0.y, v0.z, v0.w};
-            const uint32_t words1[4] = {v1.x, v1.y, v1.z, v1.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float q0[8], q1[8];
-                unpack8_plus16(words0[k], q0);
-                if (DUAL) unpack8_plus16(words1[k], q1);
-#pragma unroll
-                for (int t = 0; t < NT; ++t) {
-                    const float *xt = xc + (t < n ? t : 0) * stride + (k << 6);
-                    const float4 xa = *reinterpret_cast<const float4 *>(xt);
-                    const float4 xb = *reinterpret_cast<const float4 *>(xt + 32);
-                    float acc = d0[t];
-                    acc = fmaf(q0[0], xa.x, acc);
-                    acc = fmaf(q0[1], xa.y, acc);
-                    acc = fmaf(q0[2], xa.z, acc);
-                    acc = fmaf(q0[3], xa.w, acc);
-                    acc = fmaf(q0[4], xb.x, acc);
-                    acc = fmaf(q0[5], xb.y, acc);
-                    acc = fmaf(q0[6], xb.z, acc);
-                    acc = fmaf(q0[7], xb.w, acc);
-                    d0[t] = acc;
-                    if (DUAL) {
-                        float acu = d1[t];
-                        acu = fmaf(q1[0], xa.x, acu);
-                        acu = fmaf(q1[1], xa.y, acu);
-                        acu = fmaf(q1[2], xa.z, acu);
-                        acu = fmaf(q1[3], xa.w, acu);
-                        acu = fmaf(q1[4], xb.x, acu);
-                        acu = fmaf(q1[5], xb.y, acu);
-                        acu = fmaf(q1[6], xb.z, acu);
-                        acu = fmaf(q1[7], xb.w, acu);
-                        d1[t] = acu;
-                    }
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                const float sx = xsum[(t < n ? t : 0) * chunks + c];
-                a0[t] = fmaf(sc0, d0[t], a0[t]);
-                a0[t] = fmaf(bi0, sx, a0[t]);
-                if (DUAL) {
-                    a1[t] = fmaf(sc1, d1[t], a1[t]);
-                    a1[t] = fmaf(bi1, sx, a1[t]);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-#pragma unroll
-        for (int offset = 4; offset >= 1; offset >>= 1) {
-            a0[t] += __shfl_xor_sync(0xFFFFFFFFu, a0[t], offset);
-            if (DUAL) a1[t] += __shfl_xor_sync(0xFFFFFFFFu, a1[t], offset);
-        }
-    }
-}
 
 template <int NT, bool DUAL>
 __device__ __forceinline__ void run_item(const GemvJob &job, int row0, const float *xs,
@@ -242,11 +61,13 @@ k_int4_gemv(const GemvJob *jobs, const uint32_t *items, const uint32_t *itemCoun
     float *xs = smem;
     float *xsum = smem + MAXNT * staged_stride((int)maxCols);
     const uint32_t nItems = jobs ? *itemCountPtr : inlineItems;
-    const uint32_t per = (nItems + gridDim.x - 1) / gridDim.x;
-    const uint32_t begin = blockIdx.x * per;
-    const uint32_t end = min(nItems, begin + per);
+    // items go to CTAs in chunks of kItemChunk, round robin: heavy jobs (many input rows) are
+    // spread over the whole grid while a chunk still shares one staging of its job's inputs
+    constexpr uint32_t kItemChunk = 2;
+    const uint32_t nChunks = (nItems + kItemChunk - 1) / kItemChunk;
     int current = -1;
-    for (uint32_t it = begin; it < end; ++it) {
+    for (uint32_t chunk = blockIdx.x; chunk < nChunks; chunk += gridDim.x)
+    for (uint32_t it = chunk * kItemChunk; it < min(nItems, (chunk + 1) * kItemChunk); ++it) {
         uint32_t jobIdx = 0, block = it;
         if (jobs) {
             const uint32_t packed = items[it];
@@ -276,43 +97,6 @@ k_int4_gemv(const GemvJob *jobs, const uint32_t *items, const uint32_t *itemCoun
             run_item<(MAXNT >= 8 ? 8 : 1), DUAL>(sjob, row0, xs, xsum);
         } else if (MAXNT >= 16) {
             run_item<(MAXNT >= 16 ? 16 : 1), DUAL>(sjob, row0, xs, xsum);
-        }
-    }
-}
-
-// Decode combine (Metal/MoE/moe.metal:597-638): for kDecodeDownRows output rows, warp w computes
-// slot (w & 7)'s down row dots; then y = bf16(residual + sum over slots in order of w_k * v_k).
-__global__ void __launch_bounds__(512)
-k_decode_down(const uint8_t *experts, uint64_t stride, FFExpertOffsets off, const uint32_t *ids,
-              const uint16_t *weights, const uint16_t *acts, const uint16_t *residual, uint16_t *y,
-              int D, int F, int K) {
-    extern __shared__ float smem[];
-    __shared__ float partial[8][kDecodeDownRows];
-    __shared__ uint32_t rowIdx[8];
-    const int strideF = staged_stride(F);
-    float *xs = smem;
-    float *xsum = smem + 8 * strideF;
-    if (threadIdx.x < 8) rowIdx[threadIdx.x] = threadIdx.x;
-    __syncthreads();
-    stage_rows(acts, (uint32_t)F, rowIdx, K, F, xs, xsum);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slot = warp & 7;
-    const int local = (warp >> 3) * 4 + (lane >> 3);
-    const int row = blockIdx.x * kDecodeDownRows + local;
-    const bool live = slot < K && row < D;
-    const uint8_t *blob = experts + (size_t)(slot < K ? ids[slot] : 0) * stride;
-    float a0[1], a1[1];
-    row_dot<1, false>(blob + off.downWOff, reinterpret_cast<const uint16_t *>(blob + off.downSOff),
-                      reinterpret_cast<const uint16_t *>(blob + off.downBOff), nullptr, nullptr,
-                      nullptr, row, F, live, xs + slot * strideF, xsum + slot * (F >> 5), 1, a0, a1);
-    if ((lane & 7) == 0) partial[slot][local] = live ? bf2f(weights[slot]) * a0[0] : 0.0f;
-    __syncthreads();
-    if (threadIdx.x < kDecodeDownRows) {
-        const int d = blockIdx.x * kDecodeDownRows + threadIdx.x;
-        if (d < D) {
-            float acc = residual ? bf2f(residual[d]) : 0.0f;
-            for (int k = 0; k < K; ++k) acc += partial[k][threadIdx.x];
-            y[d] = f2bf(acc);
         }
     }
 }
@@ -792,6 +576,8 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     if (decodeCombine && tokens != 1) return fail(error, "decode combine takes exactly one row");
     if (!L.experts) return fail(error, "layer has no resident experts");
     if (withShared && !L.shared) return fail(error, "layer has no resident shared FFN");
+    if (decodeCombine)
+        return launch_decode_fused(ctx, L, x, ids, weights, withShared, residual, y, stream, error);
     const int E = (int)L.expertCount;
     PlanArgs a{};
     uint32_t *idsDev = ctx->ids;
@@ -857,26 +643,6 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
                                       &ctx->plan->itemCount[1], none, 0, maxCols, bound1, stream,
                                       error))
             return false;
-    }
-    if (decodeCombine) {
-        if (c.topK > 8) return fail(error, "decode combine supports at most 8 routes");
-        const size_t smem = (size_t)8 * (staged_stride((int)c.f) + (c.f >> 5)) * sizeof(float);
-        static size_t configured[8] = {0};
-        if (configured[ctx->device & 7] != smem) {
-            FF_CUDA_OK(cudaFuncSetAttribute(k_decode_down,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                       error);
-            configured[ctx->device & 7] = smem;
-        }
-        const uint32_t grid = (c.d + kDecodeDownRows - 1) / kDecodeDownRows;
-        {
-            LaunchScope scope(ctx, stream, "decode_down_combine");
-            k_decode_down<<<grid, 512, smem, stream>>>(L.experts, L.stride, L.off, idsDev,
-                                                       weightsDev, ctx->acts,
-                                                       withShared ? sharedOut : residual, y,
-                                                       (int)c.d, (int)c.f, (int)c.topK);
-        }
-        FF_CUDA_OK(cudaGetLastError(), error);
     }
     return true;
 }

@@ -110,6 +110,8 @@ struct FFContext {
     uint32_t *unitCount = nullptr;          // [4]
     uint32_t maxUnits = 0;
     uint32_t *errorFlag = nullptr;          // device: set by a kernel that gave up waiting
+    unsigned long long *phaseStamps = nullptr;  // device: 8 timestamps of the fused decode kernel
+    uint32_t *gridBarrier = nullptr;        // device: [arrivals, sense] of the fused decode kernel
     CUtensorMap *mapScratch = nullptr;
 
     // tracing: CUDA events around every kernel launch, aggregated per kernel name
@@ -173,6 +175,11 @@ bool launch_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float 
 bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, const uint16_t *b,
                           uint32_t rows, uint32_t cols, float *out32, uint16_t *out16,
                           cudaStream_t stream, const char **error);
+
+// ff_decode.cu
+bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x, const uint32_t *idsIn,
+                         const uint16_t *weightsIn, bool withShared, const uint16_t *residual,
+                         uint16_t *y, cudaStream_t stream, const char **error);
 
 // ff_prefill.cu
 bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error);

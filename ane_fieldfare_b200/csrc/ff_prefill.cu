@@ -1,15 +1,15 @@
 // Prefill path of the INT4 MoE block: router for many rows, device-side permute (counting sort by
 // expert), and the grouped INT4 -> bf16 GEMMs on the 5th-generation tensor cores.
 //
-// GEMM scheme.  A work unit is (row tile of up to 128 expert-sorted rows, column tile of 128
-// outputs).  Per 64-wide step along the contraction (= one quantization group):
+// GEMM scheme.  A work unit is (row tile of up to 256 expert-sorted rows = one or two 128-row MMA
+// tiles sharing the dequantized weights, column tile of 128 outputs).  Per 64-wide step along the contraction (= one quantization group):
 //   * one thread issues TMA loads: the activations' [128 x 64] bf16 tile (128-byte swizzle) and
 //     two [64 rows x 32 bytes] tiles of packed 4-bit codes, completing on an mbarrier;
-//   * four warps turn the packed tile into the bf16 operand tile in shared memory, one weight
+//   * eight warps turn the packed tile into the bf16 operand tile in shared memory, half a weight
 //     row per thread: codes -> bf16 pairs by a mask trick, then one bf16x2 fused multiply-add
 //     with the group's scale and bias (a single rounding of q*scale+bias), stored in the
 //     128-byte-swizzled K-major layout the MMA descriptor expects;
-//   * one thread issues four tcgen05.mma (M=128, N=128, K=16) accumulating in TMEM, then
+//   * one thread issues four (or eight) tcgen05.mma (M=128, N=128, K=16) accumulating in TMEM, then
 //     tcgen05.commit to free the stage;
 //   * four warps drain the finished accumulator from TMEM (tcgen05.ld), apply the epilogue
 //     (GeGLU to bf16 activations, or bf16 partial rows scattered to (token, rank)), while the
@@ -116,61 +116,100 @@ __device__ void pf_warp_topk(const float *logits, int E, int K, const uint16_t *
     }
 }
 
+// Each warp owns kRouterTokens tokens and walks the experts eight at a time with a register tile
+// of kRouterTokens x 8 running sums, so a router row fetched from L2/L1 feeds 4 tokens and an
+// input chunk read from shared memory feeds 8 experts.  Per (token, expert) the chain is exactly
+// the single-row kernel's: lane l, chunks i ascending, elements ascending, then the butterfly.
+constexpr int kRouterTokens = 4;   // tokens per warp
+constexpr int kRouterExperts = 8;  // experts per register tile
+
 __global__ void __launch_bounds__(kRouterWarps * 32)
 k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const uint16_t *gain,
               const uint16_t *x, uint32_t xStride, int T, int E, int D, int K, uint32_t *ids,
               uint16_t *weights, float *logitsOut) {
-    extern __shared__ float rsm[];
+    extern __shared__ uint8_t rsmRaw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float *xs = rsm + (size_t)warp * (D + kMaxExperts);
-    float *lg = xs + D;
-    const int t = blockIdx.x * kRouterWarps + warp;
-    if (t >= T) return;
-    const uint16_t *xr = x + (size_t)t * xStride;
-    for (int i = lane * 2; i < D; i += 64) {
-        const uint32_t two = *reinterpret_cast<const uint32_t *>(xr + i);
-        float x0 = __uint_as_float(two << 16), x1 = __uint_as_float(two & 0xFFFF0000u);
-        if (scale) {
-            const uint32_t ss = *reinterpret_cast<const uint32_t *>(scale + i);
-            x0 = x0 * __uint_as_float(ss << 16);
-            x1 = x1 * __uint_as_float(ss & 0xFFFF0000u);
-        }
-        xs[i] = x0;
-        xs[i + 1] = x1;
+    // per warp: kRouterTokens input rows as bf16, then kRouterTokens x kMaxExperts logits
+    const size_t perWarp = (size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4;
+    uint16_t *xs = reinterpret_cast<uint16_t *>(rsmRaw + warp * perWarp);
+    float *lg = reinterpret_cast<float *>(rsmRaw + warp * perWarp + (size_t)kRouterTokens * D * 2);
+    const int t0 = (blockIdx.x * kRouterWarps + warp) * kRouterTokens;
+    if (t0 >= T) return;
+    const int nTok = min(kRouterTokens, T - t0);
+    for (int tt = 0; tt < kRouterTokens; ++tt) {
+        const uint16_t *xr = x + (size_t)(t0 + min(tt, nTok - 1)) * xStride;
+        for (int i = lane * 8; i < D; i += 256)
+            *reinterpret_cast<uint4 *>(xs + (size_t)tt * D + i) = *reinterpret_cast<const uint4 *>(xr + i);
     }
     __syncwarp();
-    for (int e = 0; e < E; ++e) {
-        const uint16_t *wr = W + (size_t)e * D;
-        float acc = 0.0f;
+    for (int e0 = 0; e0 < E; e0 += kRouterExperts) {
+        float acc[kRouterTokens][kRouterExperts];
+#pragma unroll
+        for (int tt = 0; tt < kRouterTokens; ++tt)
+#pragma unroll
+            for (int ee = 0; ee < kRouterExperts; ++ee) acc[tt][ee] = 0.0f;
         for (int base = 8 * lane; base < D; base += 256) {
-            const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
-            const float4 xa = *reinterpret_cast<const float4 *>(xs + base);
-            const float4 xb = *reinterpret_cast<const float4 *>(xs + base + 4);
-            acc = fmaf(__uint_as_float(wv.x << 16), xa.x, acc);
-            acc = fmaf(__uint_as_float(wv.x & 0xFFFF0000u), xa.y, acc);
-            acc = fmaf(__uint_as_float(wv.y << 16), xa.z, acc);
-            acc = fmaf(__uint_as_float(wv.y & 0xFFFF0000u), xa.w, acc);
-            acc = fmaf(__uint_as_float(wv.z << 16), xb.x, acc);
-            acc = fmaf(__uint_as_float(wv.z & 0xFFFF0000u), xb.y, acc);
-            acc = fmaf(__uint_as_float(wv.w << 16), xb.z, acc);
-            acc = fmaf(__uint_as_float(wv.w & 0xFFFF0000u), xb.w, acc);
+            float xv[kRouterTokens][8];
+            uint4 sv = make_uint4(0, 0, 0, 0);
+            if (scale) sv = *reinterpret_cast<const uint4 *>(scale + base);
+            const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int tt = 0; tt < kRouterTokens; ++tt) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(xs + (size_t)tt * D + base);
+                const uint32_t xx[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float x0 = __uint_as_float(xx[k] << 16), x1 = __uint_as_float(xx[k] & 0xFFFF0000u);
+                    if (scale) {
+                        x0 = x0 * __uint_as_float(ss[k] << 16);
+                        x1 = x1 * __uint_as_float(ss[k] & 0xFFFF0000u);
+                    }
+                    xv[tt][2 * k] = x0;
+                    xv[tt][2 * k + 1] = x1;
+                }
+            }
+#pragma unroll
+            for (int ee = 0; ee < kRouterExperts; ++ee) {
+                const int e = min(e0 + ee, E - 1);
+                const uint4 wv = *reinterpret_cast<const uint4 *>(W + (size_t)e * D + base);
+                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float w0 = __uint_as_float(ww[k] << 16), w1 = __uint_as_float(ww[k] & 0xFFFF0000u);
+#pragma unroll
+                    for (int tt = 0; tt < kRouterTokens; ++tt) {
+                        acc[tt][ee] = fmaf(w0, xv[tt][2 * k], acc[tt][ee]);
+                        acc[tt][ee] = fmaf(w1, xv[tt][2 * k + 1], acc[tt][ee]);
+                    }
+                }
+            }
         }
 #pragma unroll
-        for (int offset = 16; offset >= 1; offset >>= 1)
-            acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
-        if (lane == 0) lg[e] = bias ? acc + bias[e] : acc;
+        for (int tt = 0; tt < kRouterTokens; ++tt)
+#pragma unroll
+            for (int ee = 0; ee < kRouterExperts; ++ee) {
+                float v = acc[tt][ee];
+#pragma unroll
+                for (int offset = 16; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
+                const int e = e0 + ee;
+                if (lane == 0 && e < E) lg[tt * kMaxExperts + e] = bias ? v + bias[e] : v;
+            }
     }
     __syncwarp();
-    if (logitsOut)
-        for (int e = lane; e < E; e += 32) logitsOut[(size_t)t * E + e] = lg[e];
-    pf_warp_topk(lg, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
+    for (int tt = 0; tt < nTok; ++tt) {
+        const int t = t0 + tt;
+        if (logitsOut)
+            for (int e = lane; e < E; e += 32) logitsOut[(size_t)t * E + e] = lg[tt * kMaxExperts + e];
+        pf_warp_topk(lg + tt * kMaxExperts, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
+    }
 }
 
 bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
                            uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
                            cudaStream_t stream, const char **error) {
     const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
-    const size_t smem = (size_t)kRouterWarps * (D + kMaxExperts) * sizeof(float);
+    const size_t smem = (size_t)kRouterWarps * ((size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4);
+    if (smem > 200 * 1024) return fail(error, "model width too large for the router's shared memory");
     static size_t configured[8] = {0};
     if (configured[ctx->device & 7] != smem) {
         FF_CUDA_OK(cudaFuncSetAttribute(k_router_rows, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -178,9 +217,10 @@ bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *
                    error);
         configured[ctx->device & 7] = smem;
     }
+    const uint32_t perCta = kRouterWarps * kRouterTokens;
     {
         LaunchScope scope(ctx, stream, "router_rows");
-        k_router_rows<<<(tokens + kRouterWarps - 1) / kRouterWarps, kRouterWarps * 32, smem, stream>>>(
+        k_router_rows<<<(tokens + perCta - 1) / perCta, kRouterWarps * 32, smem, stream>>>(
             L.routerW, L.routerScale, L.logitBias, L.gain, x, xStride, (int)tokens, E, D,
             (int)ctx->cfg.topK, ids, weights, logits);
     }
@@ -194,7 +234,7 @@ constexpr int kSortTokens = 256;  // tokens per permute block
 
 struct RowTile {
     uint32_t rowStart;  // first row in expert-sorted order
-    uint32_t rows;      // 1..128
+    uint32_t rows;      // 1..256 (one or two 128-row MMA tiles)
     uint32_t expert;
     uint32_t pad;
 };
@@ -216,7 +256,7 @@ k_route_count(const uint32_t *ids, int T, int K, int E, uint32_t *blockCounts) {
 }
 
 // Pass 2 (one block): exclusive prefix of every expert's counts over the blocks, expert offsets,
-// and the list of row tiles (up to 128 rows of one expert each), experts ascending.
+// and the list of row tiles (up to 256 rows of one expert each), experts ascending.
 // counts[0] = row tiles, counts[1] = pairs, counts[2] = experts with at least one pair.
 __global__ void __launch_bounds__(256)
 k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, RowTile *tiles,
@@ -241,7 +281,7 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
             offset[i] = run;
             tileBase[i] = tilesRun;
             run += total[i];
-            tilesRun += (total[i] + 127u) / 128u;
+            tilesRun += (total[i] + 255u) / 256u;
             active += total[i] ? 1u : 0u;
         }
         offset[E] = run;
@@ -256,8 +296,8 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
     if (e == 0) expertOffsets[E] = offset[E];
     if (e < E) {
         const uint32_t n = total[e];
-        for (uint32_t i = 0, tix = tileBase[e]; i < n; i += 128, ++tix)
-            if (tix < maxTiles) tiles[tix] = RowTile{offset[e] + i, min(128u, n - i), (uint32_t)e, 0u};
+        for (uint32_t i = 0, tix = tileBase[e]; i < n; i += 256, ++tix)
+            if (tix < maxTiles) tiles[tix] = RowTile{offset[e] + i, min(256u, n - i), (uint32_t)e, 0u};
     }
 }
 
@@ -286,9 +326,9 @@ k_route_scatter(const uint32_t *ids, const uint16_t *weights, int T, int K, int 
 
 // Row tiles of a dense problem: T rows of one "expert" (the shared FFN).
 __global__ void k_dense_tiles(int T, RowTile *tiles, uint32_t *counts) {
-    const int n = (T + 127) / 128;
+    const int n = (T + 255) / 256;
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        tiles[i] = RowTile{(uint32_t)i * 128u, (uint32_t)min(128, T - i * 128), 0u, 0u};
+        tiles[i] = RowTile{(uint32_t)i * 256u, (uint32_t)min(256, T - i * 256), 0u, 0u};
     if (threadIdx.x == 0) {
         counts[0] = (uint32_t)n;
         counts[1] = (uint32_t)T;
@@ -439,13 +479,15 @@ constexpr uint32_t kIdescBf16M128N128 =
 // ---- grouped INT4 GEMM ---------------------------------------------------------------------
 
 constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
-constexpr int kStagesLoad = 4;   // activations + packed codes (TMA destinations)
+constexpr int kStagesLoad = 3;   // activations + packed codes (TMA destinations)
 constexpr int kStagesB = 3;      // dequantized bf16 operand tiles
-constexpr int kGemmThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 dequant, warps 6-9 epilogue
-constexpr uint32_t kTileABytes = kTileM * kTileK * 2;     // 16384
+constexpr int kDequantWarps = 8;
+// warp 0 TMA, warp 1 MMA, warps 2-9 dequant, warps 10-13 epilogue (TMEM lane quarter = warp & 3)
+constexpr int kGemmThreads = (2 + kDequantWarps + 4) * 32;
+constexpr uint32_t kTileABytes = kTileM * kTileK * 2;     // 16384 per 128-row tile; a stage holds two
 constexpr uint32_t kTilePackedBytes = kTileN * kTileK / 2;  // 4096
 constexpr uint32_t kTileBBytes = kTileN * kTileK * 2;     // 16384
-constexpr uint32_t kTmemCols = 256;                       // two 128-column accumulators
+constexpr uint32_t kTmemCols = 512;  // two accumulator buffers x two 128-row tiles x 128 columns
 
 enum GemmMode : int { kModeGateUp = 0, kModeDown = 1 };
 
@@ -480,10 +522,10 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const uint32_t base = (rawBase + 1023u) & ~1023u;
     const uint32_t groupsK = args.K / kTileK;
 
-    // carve-up: A stages, B stages (1024-aligned), packed stages, scales
+    // carve-up: A stages (two 128-row tiles each), B stages (all 1024-aligned), packed stages, scales
     uint32_t aAddr[kStagesLoad], pAddr[kStagesLoad], bAddr[kStagesB];
     uint32_t cursor = base;
-    for (int s = 0; s < kStagesLoad; ++s, cursor += kTileABytes) aAddr[s] = cursor;
+    for (int s = 0; s < kStagesLoad; ++s, cursor += 2 * kTileABytes) aAddr[s] = cursor;
     for (int s = 0; s < kStagesB; ++s, cursor += kTileBBytes) bAddr[s] = cursor;
     for (int s = 0; s < kStagesLoad; ++s, cursor += kTilePackedBytes) pAddr[s] = cursor;
     uint8_t *scalesPtr = gemmSmemRaw + (cursor - rawBase);  // [128 rows][groupsK][2] bf16
@@ -500,10 +542,10 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
         abortFlag = 0;
         for (int s = 0; s < kStagesLoad; ++s) {
             mbar_init(barLoadFull(s), 1);
-            mbar_init(barLoadEmpty(s), 5);  // one tcgen05.commit + four dequant warps
+            mbar_init(barLoadEmpty(s), 1 + kDequantWarps);  // one tcgen05.commit + the dequant warps
         }
         for (int s = 0; s < kStagesB; ++s) {
-            mbar_init(barBFull(s), 4);   // four dequant warps
+            mbar_init(barBFull(s), kDequantWarps);
             mbar_init(barBEmpty(s), 1);  // one tcgen05.commit
         }
         for (int s = 0; s < 2; ++s) {
@@ -536,6 +578,7 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 const RowTile tile = args.tiles[u / args.nTiles];
                 const uint32_t nt = u % args.nTiles;
                 const int row0 = (int)tile.rowStart;
+                const uint32_t mTiles = tile.rows > 128u ? 2u : 1u;
                 const int wRow0 = MODE == kModeGateUp ? (int)nt * 64 : (int)nt * 128;
                 const int wRow1 = MODE == kModeGateUp ? (int)nt * 64 : (int)nt * 128 + 64;
                 for (uint32_t g = 0; g < groupsK; ++g) {
@@ -543,8 +586,11 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(barLoadFull(stage), kTileABytes + kTilePackedBytes);
+                    mbar_expect_tx(barLoadFull(stage), mTiles * kTileABytes + kTilePackedBytes);
                     tma_load_2d(aAddr[stage], &mapA, (int)(g * kTileK), row0, barLoadFull(stage));
+                    if (mTiles == 2)
+                        tma_load_2d(aAddr[stage] + kTileABytes, &mapA, (int)(g * kTileK), row0 + 128,
+                                    barLoadFull(stage));
                     tma_load_3d(pAddr[stage], &mapW0, (int)(g * (kTileK / 2)), wRow0, (int)tile.expert,
                                 barLoadFull(stage));
                     tma_load_3d(pAddr[stage] + kTilePackedBytes / 2, &mapW1, (int)(g * (kTileK / 2)),
@@ -562,9 +608,11 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
             uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const RowTile tile = args.tiles[u / args.nTiles];
+                const uint32_t mTiles = tile.rows > 128u ? 2u : 1u;
                 if (!mbar_wait(barAccEmpty(acc), accPhase ^ 1u, &abortFlag)) break;
                 tc_fence_after();
-                const uint32_t tmemD = tmemBase + acc * (uint32_t)kTileN;
+                const uint32_t tmemD = tmemBase + acc * 2u * (uint32_t)kTileN;
                 for (uint32_t g = 0; g < groupsK; ++g) {
                     if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
                         !mbar_wait(barBFull(bStage), bPhase, &abortFlag)) {
@@ -572,13 +620,15 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t descA = umma_desc_sw128(aAddr[stage]);
                     const uint64_t descB = umma_desc_sw128(bAddr[bStage]);
 #pragma unroll
                     for (uint32_t kk = 0; kk < kTileK / 16; ++kk) {
                         // 32 bytes (>> 4 = 2) further along K for every 16-element slice
-                        tc_mma_bf16(tmemD, descA + 2u * kk, descB + 2u * kk, kIdescBf16M128N128,
-                                    (g | kk) != 0u ? 1u : 0u);
+                        for (uint32_t m = 0; m < mTiles; ++m) {
+                            const uint64_t descA = umma_desc_sw128(aAddr[stage] + m * kTileABytes);
+                            tc_mma_bf16(tmemD + m * (uint32_t)kTileN, descA + 2u * kk, descB + 2u * kk,
+                                        kIdescBf16M128N128, (g | kk) != 0u ? 1u : 0u);
+                        }
                     }
                     tc_commit(barLoadEmpty(stage));
                     tc_commit(barBEmpty(bStage));
@@ -599,64 +649,69 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 }
             }
         }
-    } else if (warp < 6) {
-        // ---------------- dequantizers: one operand row per thread ----------------
-        const int r = (warp - 2) * 32 + lane;  // operand row 0..127
+    } else if (warp < 2 + kDequantWarps) {
+        // ---------------- dequantizers: half an operand row (32 codes) per thread ----------------
+        const int idx = (warp - 2) * 32 + lane;
+        const int r = idx >> 1;        // operand row 0..127
+        const int half = idx & 1;      // which 16 bytes of the row's 32 packed bytes
         const int matrix = MODE == kModeGateUp ? (r >> 6) : 0;
         uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0;
-        uint16_t *myScales = reinterpret_cast<uint16_t *>(scalesPtr) + (size_t)r * groupsK * 2;
+        uint16_t *rowScales = reinterpret_cast<uint16_t *>(scalesPtr) + (size_t)r * groupsK * 2;
         bool ok = true;
         for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
             const RowTile tile = args.tiles[u / args.nTiles];
             const uint32_t nt = u % args.nTiles;
             const uint32_t wRow = MODE == kModeGateUp ? nt * 64 + (uint32_t)(r & 63) : nt * 128 + (uint32_t)r;
             const uint8_t *blob = args.blobBase + (size_t)tile.expert * args.expertStride;
+            // the row's two threads each fetch half of its scale/bias pairs
+            __syncwarp();
             if (wRow < args.N) {
                 const uint16_t *sg = reinterpret_cast<const uint16_t *>(blob + args.scaleOff[matrix]) +
                                      (size_t)wRow * groupsK;
                 const uint16_t *bg = reinterpret_cast<const uint16_t *>(blob + args.biasOff[matrix]) +
                                      (size_t)wRow * groupsK;
-                for (uint32_t g = 0; g < groupsK; ++g) {
-                    myScales[2 * g] = sg[g];
-                    myScales[2 * g + 1] = bg[g];
+                for (uint32_t g = (uint32_t)half; g < groupsK; g += 2) {
+                    rowScales[2 * g] = sg[g];
+                    rowScales[2 * g + 1] = bg[g];
                 }
             } else {
-                for (uint32_t g = 0; g < 2 * groupsK; ++g) myScales[g] = 0;
+                for (uint32_t g = (uint32_t)half; g < groupsK; g += 2) {
+                    rowScales[2 * g] = 0;
+                    rowScales[2 * g + 1] = 0;
+                }
             }
+            __syncwarp();
             for (uint32_t g = 0; g < groupsK; ++g) {
                 if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
                     !mbar_wait(barBEmpty(bStage), bPhase ^ 1u, &abortFlag)) {
                     ok = false;
                     break;
                 }
-                const uint32_t s16 = myScales[2 * g], b16 = myScales[2 * g + 1];
+                const uint32_t s16 = rowScales[2 * g], b16 = rowScales[2 * g + 1];
                 const uint32_t s2 = s16 | (s16 << 16), b2 = b16 | (b16 << 16);
-                const uint32_t src = pAddr[stage] + (uint32_t)r * 32u;
+                const uint32_t src = pAddr[stage] + (uint32_t)r * 32u + (uint32_t)half * 16u;
                 const uint32_t dstRow = bAddr[bStage] + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+                uint32_t w[4];
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                             : "r"(src));
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t w[4];
-                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                                 : "r"(src + 16u * half));
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t o[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            // codes i and i+4 of the word as the bf16 pair (128+q_i, 128+q_{i+4})
-                            uint32_t pair = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
-                            uint32_t q2, v2;
-                            asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(q2) : "r"(pair), "r"(0x43004300u));
-                            asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(v2) : "r"(q2), "r"(s2), "r"(b2));
-                            o[i] = v2;
-                        }
-                        const uint32_t chunk = (uint32_t)(half * 4 + j);
-                        const uint32_t dst = dstRow + ((chunk ^ (uint32_t)(r & 7)) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[0]),
-                                     "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                     : "memory");
+                    for (int i = 0; i < 4; ++i) {
+                        // codes i and i+4 of the word as the bf16 pair (128+q_i, 128+q_{i+4})
+                        uint32_t pair = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+                        uint32_t q2, v2;
+                        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(q2) : "r"(pair), "r"(0x43004300u));
+                        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(v2) : "r"(q2), "r"(s2), "r"(b2));
+                        o[i] = v2;
                     }
+                    const uint32_t chunk = (uint32_t)(half * 4 + j);
+                    const uint32_t dst = dstRow + ((chunk ^ (uint32_t)(r & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[0]),
+                                 "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                 : "memory");
                 }
                 fence_generic_to_async();
                 __syncwarp();
@@ -676,74 +731,78 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
-        const int quarter = warp & 3;                // TMEM lanes this warp may read
-        const int m = quarter * 32 + lane;           // row of the tile
+        const int quarter = warp & 3;  // TMEM lanes this warp may read
         uint32_t acc = 0, accPhase = 0;
         for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) {
             const RowTile tile = args.tiles[u / args.nTiles];
             const uint32_t nt = u % args.nTiles;
+            const uint32_t mTiles = tile.rows > 128u ? 2u : 1u;
             if (!mbar_wait(barAccFull(acc), accPhase, &abortFlag)) break;
             tc_fence_after();
-            const uint32_t taddr = tmemBase + acc * (uint32_t)kTileN + ((uint32_t)(quarter * 32) << 16);
-            const bool rowLive = (uint32_t)m < tile.rows;
-            if (MODE == kModeGateUp) {
-                uint16_t *dstRow = args.out + (size_t)(tile.rowStart + (uint32_t)m) * args.N + (size_t)nt * 64;
+            for (uint32_t mt = 0; mt < mTiles; ++mt) {
+                const uint32_t m = mt * 128u + (uint32_t)(quarter * 32 + lane);  // row of the unit
+                const uint32_t taddr =
+                    tmemBase + (acc * 2u + mt) * (uint32_t)kTileN + ((uint32_t)(quarter * 32) << 16);
+                const bool rowLive = m < tile.rows;
+                if (MODE == kModeGateUp) {
+                    uint16_t *dstRow = args.out + (size_t)(tile.rowStart + m) * args.N + (size_t)nt * 64;
 #pragma unroll
-                for (int c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t gr[32], ur[32];
-                    tc_load_32cols(taddr + (uint32_t)c0, gr);
-                    tc_load_32cols(taddr + 64u + (uint32_t)c0, ur);
-                    tc_wait_ld();
-                    uint32_t packed[16];
+                    for (int c0 = 0; c0 < 64; c0 += 32) {
+                        uint32_t gr[32], ur[32];
+                        tc_load_32cols(taddr + (uint32_t)c0, gr);
+                        tc_load_32cols(taddr + 64u + (uint32_t)c0, ur);
+                        tc_wait_ld();
+                        uint32_t packed[16];
 #pragma unroll
-                    for (int blk = 0; blk < 4; ++blk) {
-                        // eight activations, stored as 0,4,1,5,2,6,3,7 for the down GEMM
-                        float a[8];
+                        for (int blk = 0; blk < 4; ++blk) {
+                            // eight activations, stored as 0,4,1,5,2,6,3,7 for the down GEMM
+                            float a[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float g = __uint_as_float(gr[blk * 8 + i]);
-                            float uu = __uint_as_float(ur[blk * 8 + i]);
-                            if (args.roundGateUp) {
-                                g = pf_bf2f(pf_f2bf(g));
-                                uu = pf_bf2f(pf_f2bf(uu));
+                            for (int i = 0; i < 8; ++i) {
+                                float g = __uint_as_float(gr[blk * 8 + i]);
+                                float uu = __uint_as_float(ur[blk * 8 + i]);
+                                if (args.roundGateUp) {
+                                    g = pf_bf2f(pf_f2bf(g));
+                                    uu = pf_bf2f(pf_f2bf(uu));
+                                }
+                                a[i] = pf_gelu_tanh(g) * uu;
                             }
-                            a[i] = pf_gelu_tanh(g) * uu;
+                            packed[blk * 4 + 0] = (uint32_t)pf_f2bf(a[0]) | ((uint32_t)pf_f2bf(a[4]) << 16);
+                            packed[blk * 4 + 1] = (uint32_t)pf_f2bf(a[1]) | ((uint32_t)pf_f2bf(a[5]) << 16);
+                            packed[blk * 4 + 2] = (uint32_t)pf_f2bf(a[2]) | ((uint32_t)pf_f2bf(a[6]) << 16);
+                            packed[blk * 4 + 3] = (uint32_t)pf_f2bf(a[3]) | ((uint32_t)pf_f2bf(a[7]) << 16);
                         }
-                        packed[blk * 4 + 0] = (uint32_t)pf_f2bf(a[0]) | ((uint32_t)pf_f2bf(a[4]) << 16);
-                        packed[blk * 4 + 1] = (uint32_t)pf_f2bf(a[1]) | ((uint32_t)pf_f2bf(a[5]) << 16);
-                        packed[blk * 4 + 2] = (uint32_t)pf_f2bf(a[2]) | ((uint32_t)pf_f2bf(a[6]) << 16);
-                        packed[blk * 4 + 3] = (uint32_t)pf_f2bf(a[3]) | ((uint32_t)pf_f2bf(a[7]) << 16);
+                        if (rowLive && nt * 64 + (uint32_t)c0 < args.N) {
+                            uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2],
+                                                    packed[4 * q + 3]);
+                        }
                     }
-                    if (rowLive && nt * 64 + (uint32_t)c0 < args.N) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2],
-                                                packed[4 * q + 3]);
+                } else {
+                    size_t outRow = tile.rowStart + m;
+                    if (args.pairs && rowLive) {
+                        const FFTokenExpertPair p = args.pairs[tile.rowStart + m];
+                        outRow = (size_t)p.token * args.topK + p.rank;
                     }
-                }
-            } else {
-                size_t outRow = tile.rowStart + (uint32_t)m;
-                if (args.pairs && rowLive) {
-                    const FFTokenExpertPair p = args.pairs[tile.rowStart + (uint32_t)m];
-                    outRow = (size_t)p.token * args.topK + p.rank;
-                }
-                uint16_t *dstRow = args.out + outRow * args.N + (size_t)nt * 128;
+                    uint16_t *dstRow = args.out + outRow * args.N + (size_t)nt * 128;
 #pragma unroll
-                for (int c0 = 0; c0 < 128; c0 += 32) {
-                    uint32_t vr[32];
-                    tc_load_32cols(taddr + (uint32_t)c0, vr);
-                    tc_wait_ld();
-                    if (rowLive && nt * 128 + (uint32_t)c0 < args.N) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
+                    for (int c0 = 0; c0 < 128; c0 += 32) {
+                        uint32_t vr[32];
+                        tc_load_32cols(taddr + (uint32_t)c0, vr);
+                        tc_wait_ld();
+                        if (rowLive && nt * 128 + (uint32_t)c0 < args.N) {
+                            uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t o[4];
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t o[4];
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                o[i] = (uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
-                                       ((uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
-                            dst[q] = make_uint4(o[0], o[1], o[2], o[3]);
+                                for (int i = 0; i < 4; ++i)
+                                    o[i] = (uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
+                                           ((uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
+                                dst[q] = make_uint4(o[0], o[1], o[2], o[3]);
+                            }
                         }
                     }
                 }
@@ -856,7 +915,7 @@ bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error) {
 }
 
 static size_t gemm_smem_bytes(uint32_t K) {
-    return 1024 + (size_t)kStagesLoad * (kTileABytes + kTilePackedBytes) + (size_t)kStagesB * kTileBBytes +
+    return 1024 + (size_t)kStagesLoad * (2 * kTileABytes + kTilePackedBytes) + (size_t)kStagesB * kTileBBytes +
            (size_t)kTileN * (K / kTileK) * 2 * sizeof(uint16_t);
 }
 
@@ -922,10 +981,10 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     }
     FF_CUDA_OK(cudaGetLastError(), error);
 
-    const uint32_t tileBound = pairs / 128 + (uint32_t)E;
+    const uint32_t tileBound = pairs / 256 + (uint32_t)E;
     CUtensorMap mapX, mapActs;
-    if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)pairs + 128, c.d, c.d, error)) return false;
-    if (!make_activation_map(&mapActs, ctx->acts, (uint64_t)pairs + 128, c.f, c.f, error)) return false;
+    if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)pairs + 256, c.d, c.d, error)) return false;
+    if (!make_activation_map(&mapActs, ctx->acts, (uint64_t)pairs + 256, c.f, c.f, error)) return false;
 
     GemmArgs a{};
     a.blobBase = L.experts;
@@ -980,10 +1039,10 @@ bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
                                                             (int)c.d, ctx->xSorted);
     }
     FF_CUDA_OK(cudaGetLastError(), error);
-    const uint32_t rowTiles = (tokens + 127) / 128;
+    const uint32_t rowTiles = (tokens + 255) / 256;
     CUtensorMap mapX, mapActs;
-    if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)tokens + 128, c.d, c.d, error)) return false;
-    if (!make_activation_map(&mapActs, ctx->sharedActs, (uint64_t)tokens + 128, c.sharedF, c.sharedF, error))
+    if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)tokens + 256, c.d, c.d, error)) return false;
+    if (!make_activation_map(&mapActs, ctx->sharedActs, (uint64_t)tokens + 256, c.sharedF, c.sharedF, error))
         return false;
     uint64_t payload = 0;
     packed_offsets(c.d, c.sharedF, &payload);

@@ -108,6 +108,12 @@ class HotpathContext:
         n = binding.load().ff_get_trace(self.handle, entries, 32)
         return {entries[i].name.decode(): (entries[i].launches, entries[i].milliseconds) for i in range(n)}
 
+    def decodePhaseTimes(self):
+        """Microseconds of the six phases of the last traced one-token launch (see the header)."""
+        out = (ctypes.c_double * 6)()
+        call("ff_decode_phase_times", self.handle, out)
+        return list(out)
+
     # -- resident weights (replaces MappedExpertLayer / Model.routedExpertViews) ---------------
 
     def loadLayer(self, layer: int, blobs: np.ndarray, expertStride: int,

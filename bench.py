@@ -36,8 +36,21 @@ ROUTER_BYTES = E * D * 2                                         # 720 896
 ACT_IO_BYTES = 2 * D * 2                                         # x in, y out
 DECODE_BYTES = K * EXPERT_BYTES + SHARED_BYTES + ROUTER_BYTES + ACT_IO_BYTES  # 37 531 648
 DECODE_FLOPS = 2 * (K * 3 * F * D + 3 * FS * D + E * D)
-KERNELS_PER_DECODE_STEP = 5
+KERNELS_PER_DECODE_STEP = 1
 ROOT_SEED = 0xF1E1DFA2E
+
+
+PREFILL_TOKENS = 4096
+
+
+def measured_bf16_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"tflops": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "burst_tflops": float(p["bf16_tflops"]), "source": "measured (sustained)"}
+    return {"tflops": 1400.0, "burst_tflops": 1590.0, "source": "fallback"}
 
 
 def measured_peaks():
@@ -149,6 +162,42 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def time_graph(torch, stream, graph, replays):
+    """Device time of `replays` graph launches, CUDA events on the launching stream."""
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        begin.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        end.record(stream)
+        stream.synchronize()
+    return begin.elapsed_time(end)
+
+
+def capture_steps(torch, ctx, stream, step, group):
+    """One CUDA graph holding `group` consecutive steps (a few uncaptured steps run first so that
+    every kernel is configured before the capture)."""
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        for i in range(3):
+            step(i)
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(group):
+                step(i)
+    return graph
+
+
+def traced_kernels(ctx, step, group):
+    """Per-kernel device time of `group` steps by CUDA events (outside any graph)."""
+    ctx.setTracing(True)
+    for i in range(group):
+        step(i)
+    trace = ctx.trace()
+    ctx.setTracing(False)
+    return {name: {"launches": n, "avg_us": round(1e3 * t / n, 3)} for name, (n, t) in trace.items()}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -161,78 +210,74 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     n_layers = args.layers
+    want = set(args.only.split(",")) if args.only else {"decode", "verify", "prefill"}
+    max_tokens = PREFILL_TOKENS if "prefill" in want else 16
     ctx = hotpath.HotpathContext(layers=n_layers, experts=E, d=D, f=F, sharedF=FS, topK=K,
-                                 maxTokens=16, device=local_rank)
-    host_layer0 = None
+                                 maxTokens=max_tokens, device=local_rank)
+    host_layers = []
     for slot in range(n_layers):
         L = workload.make_layer(ROOT_SEED + 977 * rank, slot)
         workload.load_layer(ctx, slot, L)
-        if slot == 0:
-            host_layer0 = L
+        host_layers.append(L if slot == 0 else (L.routerW,))
+    host_layer0 = host_layers[0]
+    peaks = measured_peaks()
+    stream = torch.cuda.Stream(device=device)
+
+    def set_router_bias(kind):
+        from ane_fieldfare_b200 import synth
+        for slot in range(n_layers):
+            router = host_layers[slot].routerW if slot == 0 else host_layers[slot][0]
+            if kind == "none":
+                bias = None
+            elif kind == "normal":
+                bias = synth.normal(synth.seedtree_key(ROOT_SEED, f"bench.bias.{slot}"), E).astype(np.float32)
+            else:
+                bias = synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"bench.zipf.{slot}")
+            ctx.loadRouter(slot, router, logitBias=bias)
+
+    def sync_max(ms):
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    line = {}
+    # ================= decode: config 1, the headline =================
     n_rows = 64
     tokens_bits = workload.make_tokens(ROOT_SEED, "decode.x", n_rows, D)
     x_rows = hotpath.bf16_tensor(tokens_bits, device)
     xs = [x_rows[i:i + 1].contiguous() for i in range(n_rows)]
-    y = torch.zeros((1, D), dtype=torch.bfloat16, device=device)
+    y1 = torch.zeros((1, D), dtype=torch.bfloat16, device=device)
 
-    def step(i):
-        ctx.moeLayer(i % n_layers, xs[i % n_rows], y)
+    def decode_step(i):
+        ctx.moeLayer(i % n_layers, xs[i % n_rows], y1)
 
-    # ---- warm-up (also configures kernel attributes before any capture) ----
+    set_router_bias("none")
     for i in range(max(args.warmup, 3)):
-        step(i)
+        decode_step(i)
     torch.cuda.synchronize()
-
-    # ---- one CUDA graph holding `group` consecutive steps -------------------
     group = n_layers * 8
-    stream = torch.cuda.Stream(device=device)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        for i in range(3):
-            step(i)
-        stream.synchronize()
-        with torch.cuda.graph(graph, stream=stream):
-            for i in range(group):
-                step(i)
+    graph = capture_steps(torch, ctx, stream, decode_step, group)
     replays = max(1, (args.steps + group - 1) // group)
     steps = replays * group
-    with torch.cuda.stream(stream):
-        for _ in range(max(1, (args.warmup + group - 1) // group)):
-            graph.replay()
-        stream.synchronize()
-
+    time_graph(torch, stream, graph, max(1, (args.warmup + group - 1) // group))
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        begin.record(stream)
-        for _ in range(replays):
-            graph.replay()
-        end.record(stream)
-        stream.synchronize()
+    ms = time_graph(torch, stream, graph, replays)
     torch.cuda.synchronize()
-    ms = begin.elapsed_time(end)
     clocks = sampler.stop() if rank == 0 else None
+    ms = sync_max(ms)
     if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.barrier()
-        ms = float(t.item())
     value = world * steps / (ms * 1e-3)
+    kernels = traced_kernels(ctx, decode_step, group)
 
-    # ---- per-kernel device time of the same steps, by CUDA events (not graphed) ----
-    ctx.setTracing(True)
-    for i in range(group):
-        step(i)
-    trace = ctx.trace()
-    ctx.setTracing(False)
-    kernels = {name: {"launches": n, "avg_us": 1e3 * t / n} for name, (n, t) in trace.items()}
-
-    # ---- end to end through the host-buffer entry point ---------------------
+    # end to end through the host-buffer entry point
     hx = [torch.from_numpy(tokens_bits[i:i + 1].view(np.int16).copy()).view(torch.bfloat16).pin_memory()
           for i in range(n_rows)]
     hy = torch.zeros((1, D), dtype=torch.bfloat16).pin_memory()
@@ -244,48 +289,111 @@ def run_ours(args):
     t0 = time.perf_counter()
     for i in range(e2e_steps):
         ctx.moeLayerHost(i % n_layers, hx[i % n_rows], hy)
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = sync_max(time.perf_counter() - t0)
     e2e_value = world * e2e_steps / e2e_s
 
+    step_s = ms * 1e-3 / steps
+    achieved = DECODE_BYTES / step_s / 1e9
+    line.update({
+        "metric": "int4_moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights, bf16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "config1_decode_1token_moe_layer", "hidden": D, "experts": E,
+                   "top_k": K, "expert_intermediate": F, "shared_intermediate": FS,
+                   "layers_rotated": n_layers, "input_rows_rotated": n_rows,
+                   "l2_policy": f"weights of {n_layers} layers rotate: "
+                                f"{n_layers * DECODE_BYTES / 1e6:.0f} MB touched > 126 MB L2",
+                   "multi_gpu": "replicas only (decode does not shard)",
+                   "launch": f"CUDA graph of {group} steps"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": D * 2,
+                "d2h_bytes_per_step": D * 2, "steps": e2e_steps},
+        "gpu_launches": steps * KERNELS_PER_DECODE_STEP,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"], "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "kernel": "the whole decode step (all kernels of one token through one layer)",
+                     "algorithmic_bytes_per_step": DECODE_BYTES},
+        "kernels": kernels,
+    })
+
+    # ================= verify: config 2, 16-token blocks =================
+    if "verify" in want and rank == 0:
+        set_router_bias("normal")
+        n_blocks = 16
+        vbits = workload.make_tokens(ROOT_SEED, "verify.x", 16 * n_blocks, D)
+        vx = hotpath.bf16_tensor(vbits, device)
+        vblocks = [vx[16 * i:16 * i + 16].contiguous() for i in range(n_blocks)]
+        vy = torch.zeros((16, D), dtype=torch.bfloat16, device=device)
+
+        def verify_step(i):
+            ctx.moeLayer(i % n_layers, vblocks[i % n_blocks], vy)
+
+        active = []
+        for i in range(n_layers * 2):
+            verify_step(i)
+            torch.cuda.synchronize()
+            active.append(ctx.info().lastActiveExperts)
+        vgroup = n_layers * 2
+        vgraph = capture_steps(torch, ctx, stream, verify_step, vgroup)
+        vreplays = max(2, args.steps // (8 * vgroup))
+        time_graph(torch, stream, vgraph, 2)
+        vms = time_graph(torch, stream, vgraph, vreplays)
+        vsteps = vreplays * vgroup
+        mean_active = float(np.mean(active))
+        vbytes = mean_active * EXPERT_BYTES + SHARED_BYTES + ROUTER_BYTES + 16 * ACT_IO_BYTES
+        vach = vbytes / (vms * 1e-3 / vsteps) / 1e9
+        line["verify"] = {
+            "workload": "config2_verify_16token_block", "tokens_per_s": 16 * vsteps / (vms * 1e-3),
+            "ms_per_step": vms / vsteps, "steps": vsteps, "active_experts_mean": mean_active,
+            "roofline": {"bound": "hbm", "achieved": vach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": vach / peaks["hbm_gbs"], "frac_of_nominal_8TBs": vach / 8000.0,
+                         "algorithmic_bytes_per_step": vbytes},
+            "kernels": traced_kernels(ctx, verify_step, vgroup)}
+
+    # ================= prefill: config 3, 4096 tokens, Zipf-skewed routing =================
+    if "prefill" in want and rank == 0:
+        set_router_bias("zipf")
+        pbits = workload.make_tokens(ROOT_SEED, "prefill.x", PREFILL_TOKENS, D)
+        px = hotpath.bf16_tensor(pbits, device)
+        py = torch.zeros((PREFILL_TOKENS, D), dtype=torch.bfloat16, device=device)
+
+        def prefill_step(i):
+            ctx.moeLayer(i % n_layers, px, py)
+
+        for i in range(3):
+            prefill_step(i)
+        torch.cuda.synchronize()
+        err = ctx.info().deviceErrorFlag
+        psteps = max(8, min(64, args.steps // 64))
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for i in range(psteps):
+            prefill_step(i)
+        end.record()
+        torch.cuda.synchronize()
+        pms = begin.elapsed_time(end)
+        flops = PREFILL_TOKENS * (2 * (K * 3 * F * D + 3 * FS * D + E * D))
+        tf = flops / (pms * 1e-3 / psteps) / 1e12
+        bf16_peak = measured_bf16_peak()
+        line["prefill"] = {
+            "workload": "config3_prefill_4096tokens_zipf", "tokens_per_s": PREFILL_TOKENS * psteps / (pms * 1e-3),
+            "ms_per_step": pms / psteps, "steps": psteps, "device_error_flag": err,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16_peak["tflops"], "unit": "TFLOP/s",
+                         "frac": tf / bf16_peak["tflops"], "peak_source": bf16_peak["source"],
+                         "frac_of_nominal_2250TF": tf / 2250.0, "algorithmic_flops_per_step": flops},
+            "kernels": traced_kernels(ctx, prefill_step, 4)}
+
     if rank == 0:
-        peaks = measured_peaks()
-        step_s = ms * 1e-3 / steps
-        achieved = DECODE_BYTES / step_s / 1e9
         cpu_rate, cpu_steps, cpu_threads = cpu_decode_baseline(host_layer0, tokens_bits)
-        line = {
-            "metric": "int4_moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
-            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int4 weights, bf16 activations, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": "config1_decode_1token_moe_layer", "hidden": D, "experts": E,
-                       "top_k": K, "expert_intermediate": F, "shared_intermediate": FS,
-                       "layers_rotated": n_layers, "input_rows_rotated": n_rows,
-                       "l2_policy": f"weights of {n_layers} layers rotate: "
-                                    f"{n_layers * DECODE_BYTES / 1e6:.0f} MB touched > 126 MB L2",
-                       "multi_gpu": "replicas only (decode does not shard)",
-                       "launch": f"CUDA graph of {group} steps"},
-            "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": D * 2,
-                    "d2h_bytes_per_step": D * 2, "steps": e2e_steps},
-            "gpu_launches": steps * KERNELS_PER_DECODE_STEP,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
-                         "peak_source": peaks["source"], "frac_of_nominal_8TBs": achieved / 8000.0,
-                         "kernel": "the whole decode step (router, top-k/plan, gate/up GEMV, "
-                                   "shared down GEMV, routed down + combine)",
-                         "algorithmic_bytes_per_step": DECODE_BYTES},
-            "kernels": kernels,
-            "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": cpu_threads,
-                             "kind": "port",
-                             "sample": f"{cpu_steps} decode steps of the C oracle (OpenMP), one layer"},
-        }
+        line["cpu_baseline"] = {"value": cpu_rate, "unit": "tokens/s", "cores": cpu_threads,
+                                "kind": "port",
+                                "sample": f"{cpu_steps} decode steps of the C oracle (OpenMP), one layer"}
         print(json.dumps(line), flush=True)
     ctx.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -296,6 +404,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=64)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=8, help="resident layers the steps rotate over")
+    ap.add_argument("--only", default="", help="comma list of decode,verify,prefill (default all)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -112,6 +112,14 @@ FFInfo ff_get_info(const FFContext *ctx);
 void ff_set_tracing(FFContext *ctx, bool enabled);
 uint32_t ff_get_trace(FFContext *ctx, FFTraceEntry *entries, uint32_t capacity);
 
+/* Phase times of the last one-token ff_moe_layer / ff_moe_decode launched while tracing was on,
+ * in microseconds, from timestamps the first CTA takes inside the kernel: [0] phase A work
+ * (prefetch, router, shared gate/up), [1] first grid barrier, [2] top-k, [3] phase B work (routed
+ * gate/up, shared down), [4] second grid barrier, [5] phase C (routed down + combine).  A
+ * diagnostic with no counterpart in the reference beyond its per-phase GPU nanoseconds
+ * (Runtime/Inference/RealForwardRunner.swift:2146-2150). */
+bool ff_decode_phase_times(FFContext *ctx, double *microseconds, const char **error);
+
 /* ---- HBM-resident weights ---------------------------------------------------------------- */
 
 /* Copies one layer file's bytes (`packed_experts/layer_%02d.bin`: expertCount blobs,
