@@ -56,6 +56,7 @@ struct DecodeArgs {
     unsigned long long *stamps;  // null, or 8 slots for block 0's phase timestamps (ns)
     int E, D, F, Fs, K;
     int prefetch;  // 0: no L2 prefetch (diagnostic)
+    uint32_t slotsOffset, bigBytes, smallBytes;  // shared-memory staging slots (fused_layout)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
@@ -121,8 +122,58 @@ __device__ __forceinline__ void stamp(const DecodeArgs &a, int slot) {
     }
 }
 
+// ---- per-warp staging of weight rows in shared memory ----------------------------------------
+// A warp task covers four consecutive weight rows.  All of their bytes are requested at once with
+// asynchronous copies (16 bytes per lane and request, contiguous across the warp; 8 bytes for the
+// scale/bias runs whose start is only 8-byte aligned), so a warp has its whole task in flight
+// instead of a few loads; the arithmetic then reads the rows from shared memory.
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t sm_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void warp_copy16(uint8_t *dst, const uint8_t *src, int bytes) {
+    const int lane = threadIdx.x & 31;
+    for (int off = lane * 16; off < bytes; off += 512) cp_async16(sm_addr(dst + off), src + off);
+}
+__device__ __forceinline__ void warp_copy8(uint8_t *dst, const uint8_t *src, int bytes) {
+    const int lane = threadIdx.x & 31;
+    for (int off = lane * 8; off < bytes; off += 256) cp_async8(sm_addr(dst + off), src + off);
+}
+__host__ __device__ inline int pad16(int bytes) { return (bytes + 15) & ~15; }
+
+// Shared-memory image of up to four rows of one matrix: packed codes, then scales, then biases.
+struct RowsImage {
+    int wBytes, sBytes;  // per image: 4 * cols/2 and pad16(4 * groups * 2)
+    __host__ __device__ int bytes() const { return wBytes + 2 * sBytes; }
+};
+__host__ __device__ inline RowsImage rows_image(int cols) {
+    return RowsImage{4 * (cols >> 1), pad16(4 * (cols >> 6) * 2)};
+}
+
+// Requests rows [row0, row0+4) (clipped to `rows`) of the matrix at (w, s, b) into `dst`.
+__device__ __forceinline__ void stage_matrix_rows(uint8_t *dst, const RowsImage &im, const uint8_t *w,
+                                                  const uint8_t *s, const uint8_t *b, int row0, int rows,
+                                                  int cols) {
+    const int n = min(4, rows - row0);
+    if (n <= 0) return;
+    const int groups = cols >> 6;
+    warp_copy16(dst, w + (size_t)row0 * (cols >> 1), n * (cols >> 1));
+    warp_copy8(dst + im.wBytes, s + (size_t)row0 * groups * 2, n * groups * 2);
+    warp_copy8(dst + im.wBytes + im.sBytes, b + (size_t)row0 * groups * 2, n * groups * 2);
+}
+
+constexpr int kBigWarps = 10;  // warps with a large staging slot (gate/up pairs, down x 8 slots)
+
 __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeArgs a) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) uint8_t smemRaw[];
     __shared__ float sLogits[kMaxExperts];
     __shared__ uint32_t sIds[8];
     __shared__ float sWeights[8];
@@ -132,80 +183,108 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     __shared__ uint32_t sSense;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // consecutive tasks go to different SMs: global warp w is warp (w / gridDim) of CTA (w % gridDim)
-    const int gwarp = warp * (int)gridDim.x + (int)blockIdx.x;
-    const int totalWarps = gridDim.x * kFusedWarps;
+    const int G = (int)gridDim.x, cta = (int)blockIdx.x;
     const int D = a.D, F = a.F, Fs = a.Fs, K = a.K, E = a.E;
+    const int j = lane & 7, r4 = lane >> 3;
 
-    // shared-memory regions: x (kept through phase B), then a region reused by phases B and C
-    float *xs = smem;
+    // shared memory: x (fp32, staged order) | region for the shared / routed activations |
+    // kBigWarps big staging slots | small staging slots for the remaining warps
+    float *xs = reinterpret_cast<float *>(smemRaw);
     float *xsum = xs + staged_stride(D);
     float *region = xsum + (D >> 5);
+    uint8_t *slots = smemRaw + a.slotsOffset;
+    uint8_t *mySlot = warp < kBigWarps ? slots + (size_t)warp * a.bigBytes
+                                        : slots + (size_t)kBigWarps * a.bigBytes + (size_t)(warp - kBigWarps) * a.smallBytes;
+    const RowsImage imD = rows_image(D), imF = rows_image(F), imFs = rows_image(Fs);
 
     if (threadIdx.x == 0) sSense = ld_acquire_u32(&a.barrier[1]);
     if (threadIdx.x < 8) sRowIdx[threadIdx.x] = threadIdx.x;
     uint32_t cursor = 0;
     stamp(a, 0);
-    // ---------------- phase A ----------------
+
+    // ---------------- phase A: router logits, shared gate/up/GeGLU ----------------
+    const uint8_t *sh = a.shared;
+    const int tasksSharedGU = a.shared ? (Fs + 3) / 4 : 0;
+    const int tasksSharedDown = a.shared ? (D + 3) / 4 : 0;
+    // requests first: shared gate/up rows (warps 0..3), router rows (warps 4..9), and already the
+    // shared down rows of phase B (warps 10..15): none of them depends on the routing
+    auto issue_shared_gu = [&](int t) {
+        stage_matrix_rows(mySlot, imD, sh + a.sharedOff.gateWOff, sh + a.sharedOff.gateSOff,
+                          sh + a.sharedOff.gateBOff, t * 4, Fs, D);
+        stage_matrix_rows(mySlot + imD.bytes(), imD, sh + a.sharedOff.upWOff, sh + a.sharedOff.upSOff,
+                          sh + a.sharedOff.upBOff, t * 4, Fs, D);
+    };
+    auto issue_shared_down = [&](int t) {
+        stage_matrix_rows(mySlot, imFs, sh + a.sharedOff.downWOff, sh + a.sharedOff.downSOff,
+                          sh + a.sharedOff.downBOff, t * 4, D, Fs);
+    };
+    int tA = warp < 4 ? warp * G + cta : 0x7FFFFFFF;
+    if (tA < tasksSharedGU) issue_shared_gu(tA);
+    int eA = (!a.idsIn && warp >= 4 && warp < kBigWarps) ? (warp - 4) * G + cta : 0x7FFFFFFF;
+    if (eA < E) warp_copy16(mySlot, reinterpret_cast<const uint8_t *>(a.routerW + (size_t)eA * D), D * 2);
+    int tSD = warp >= kBigWarps ? (warp - kBigWarps) * G + cta : 0x7FFFFFFF;
+    if (tSD < tasksSharedDown) issue_shared_down(tSD);
     if (a.prefetch && a.shared) prefetch_region(a.shared, a.sharedBytes, cursor);
-    if (a.prefetch && !a.idsIn) prefetch_region(reinterpret_cast<const uint8_t *>(a.routerW), (uint64_t)E * D * 2, cursor);
     __syncthreads();
     uint32_t sense = sSense;
     {
         const uint32_t zero = 0;
         stage_rows(a.x, (uint32_t)D, &zero, 1, D, xs, xsum);
     }
-    if (!a.idsIn) {
-        for (int e = gwarp; e < E; e += totalWarps) {
-            const uint16_t *wr = a.routerW + (size_t)e * D;
-            float acc = 0.0f;
-            for (int base = 8 * lane; base < D; base += 256) {
-                const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
-                const uint4 xv = *reinterpret_cast<const uint4 *>(a.x + base);
-                uint4 sv = make_uint4(0, 0, 0, 0);
-                if (a.routerScale) sv = *reinterpret_cast<const uint4 *>(a.routerScale + base);
-                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-                const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
-                const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float x0 = __uint_as_float(xx[k] << 16), x1 = __uint_as_float(xx[k] & 0xFFFF0000u);
-                    if (a.routerScale) {
-                        x0 = x0 * __uint_as_float(ss[k] << 16);
-                        x1 = x1 * __uint_as_float(ss[k] & 0xFFFF0000u);
-                    }
-                    acc = fmaf(__uint_as_float(ww[k] << 16), x0, acc);
-                    acc = fmaf(__uint_as_float(ww[k] & 0xFFFF0000u), x1, acc);
-                }
-            }
-#pragma unroll
-            for (int offset = 16; offset >= 1; offset >>= 1)
-                acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
-            if (lane == 0) a.logits[e] = a.logitBias ? acc + a.logitBias[e] : acc;
-        }
+    for (; tA < tasksSharedGU; tA += 4 * G) {
+        cp_async_wait_all();
+        __syncwarp();
+        const int row = tA * 4 + r4;
+        const uint8_t *g0 = mySlot, *u0 = mySlot + imD.bytes();
+        float g[1], u[1];
+        row_dot<1, true, true>(g0, reinterpret_cast<const uint16_t *>(g0 + imD.wBytes),
+                               reinterpret_cast<const uint16_t *>(g0 + imD.wBytes + imD.sBytes), u0,
+                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes),
+                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes + imD.sBytes), r4, D, row < Fs,
+                               xs, xsum, 1, g, u);
+        if (row < Fs && j == 0) a.sharedActs[row] = f2bf(gelu_tanh(bf16_round(g[0])) * bf16_round(u[0]));
+        __syncwarp();
+        if (tA + 4 * G < tasksSharedGU) issue_shared_gu(tA + 4 * G);
     }
-    if (a.shared) {
-        // shared gate/up/GeGLU: four rows per warp task, interleaved after the router's warps
-        const uint8_t *gw = a.shared + a.sharedOff.gateWOff, *uw = a.shared + a.sharedOff.upWOff;
-        const uint16_t *gs = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.gateSOff);
-        const uint16_t *gb = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.gateBOff);
-        const uint16_t *us = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.upSOff);
-        const uint16_t *ub = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.upBOff);
-        const int tasks = (Fs + 3) / 4;
-        const int skew = a.idsIn ? 0 : E % totalWarps;
-        for (int t = (gwarp + totalWarps - skew) % totalWarps; t < tasks; t += totalWarps) {
-            const int row = t * 4 + (lane >> 3);
-            float g[1], u[1];
-            row_dot<1, true>(gw, gs, gb, uw, us, ub, row, D, row < Fs, xs, xsum, 1, g, u);
-            if (row < Fs && (lane & 7) == 0)
-                a.sharedActs[row] = f2bf(gelu_tanh(bf16_round(g[0])) * bf16_round(u[0]));
+    for (; eA < E; eA += (kBigWarps - 4) * G) {
+        cp_async_wait_all();
+        __syncwarp();
+        const uint16_t *wr = reinterpret_cast<const uint16_t *>(mySlot);
+        float acc = 0.0f;
+        for (int base = 8 * lane; base < D; base += 256) {
+            const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
+            const uint4 xv = *reinterpret_cast<const uint4 *>(a.x + base);
+            uint4 sv = make_uint4(0, 0, 0, 0);
+            if (a.routerScale) sv = *reinterpret_cast<const uint4 *>(a.routerScale + base);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
+            const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float x0 = __uint_as_float(xx[k] << 16), x1 = __uint_as_float(xx[k] & 0xFFFF0000u);
+                if (a.routerScale) {
+                    x0 = x0 * __uint_as_float(ss[k] << 16);
+                    x1 = x1 * __uint_as_float(ss[k] & 0xFFFF0000u);
+                }
+                acc = fmaf(__uint_as_float(ww[k] << 16), x0, acc);
+                acc = fmaf(__uint_as_float(ww[k] & 0xFFFF0000u), x1, acc);
+            }
         }
+#pragma unroll
+        for (int offset = 16; offset >= 1; offset >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
+        if (lane == 0) a.logits[eA] = a.logitBias ? acc + a.logitBias[eA] : acc;
+        __syncwarp();
+        const int next = eA + (kBigWarps - 4) * G;
+        if (next < E) warp_copy16(mySlot, reinterpret_cast<const uint8_t *>(a.routerW + (size_t)next * D), D * 2);
     }
     stamp(a, 1);
-    if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) return;
+    if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) {
+        cp_async_wait_all();
+        return;
+    }
     stamp(a, 2);
 
-    // ---------------- phase B ----------------
+    // ---------------- phase B: top-8, routed gate/up/GeGLU, shared down ----------------
     if (!a.idsIn) {
         for (int e = threadIdx.x; e < E; e += blockDim.x) sLogits[e] = a.logits[e];
         if (threadIdx.x < 8) {
@@ -214,8 +293,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
         }
         __syncthreads();
         // rank of every logit under (higher score, then lower expert id); scores of -inf or NaN
-        // are never taken — the order of the serial top-8 (moe.metal:269-303)
-        // four threads per expert, each counting a quarter of the competitors
+        // are never taken — the order of the serial top-8 (moe.metal:269-303).  Four threads per
+        // expert, each counting a quarter of the competitors.
         for (int idx = threadIdx.x; idx < 4 * ((E + 127) & ~127); idx += blockDim.x) {
             const int e = idx >> 2, part = idx & 3;
             const float v = e < E ? sLogits[e] : -INFINITY;
@@ -259,150 +338,125 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     }
     __syncthreads();
     stamp(a, 3);
-    for (int k = 0; k < K && a.prefetch; ++k) {
-        const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
-        prefetch_region(blob, (uint64_t)a.off.downBOff + (uint64_t)D * F / kGroup * 2, cursor);
-    }
-    {
-        // routed gate/up/GeGLU: task = (slot, four rows)
-        const int perSlot = (F + 3) / 4;
-        const int tasks = K * perSlot;
-        for (int t = gwarp; t < tasks; t += totalWarps) {
-            const int slot = t / perSlot;
-            const int row = (t - slot * perSlot) * 4 + (lane >> 3);
-            const uint8_t *blob = a.experts + (size_t)sIds[slot] * a.stride;
-            float g[1], u[1];
-            row_dot<1, true>(blob + a.off.gateWOff, reinterpret_cast<const uint16_t *>(blob + a.off.gateSOff),
-                             reinterpret_cast<const uint16_t *>(blob + a.off.gateBOff), blob + a.off.upWOff,
-                             reinterpret_cast<const uint16_t *>(blob + a.off.upSOff),
-                             reinterpret_cast<const uint16_t *>(blob + a.off.upBOff), row, D, row < F, xs,
-                             xsum, 1, g, u);
-            if (row < F && (lane & 7) == 0) a.acts[slot * F + row] = f2bf(gelu_tanh(g[0]) * u[0]);
+    const int perSlot = (F + 3) / 4;
+    const int tasksRouted = K * perSlot;
+    auto stage_routed = [&](int t) {
+        const int slot = t / perSlot, row0 = (t - slot * perSlot) * 4;
+        const uint8_t *blob = a.experts + (size_t)sIds[slot] * a.stride;
+        stage_matrix_rows(mySlot, imD, blob + a.off.gateWOff, blob + a.off.gateSOff, blob + a.off.gateBOff,
+                          row0, F, D);
+        stage_matrix_rows(mySlot + imD.bytes(), imD, blob + a.off.upWOff, blob + a.off.upSOff,
+                          blob + a.off.upBOff, row0, F, D);
+    };
+    int tB = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
+    if (tB < tasksRouted) stage_routed(tB);
+    if (a.prefetch) {
+        // the down projections of the chosen experts go to L2 now and are read in phase C
+        for (int k = 0; k < K; ++k) {
+            const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
+            prefetch_region(blob + a.off.downWOff,
+                            (uint64_t)a.off.downBOff - a.off.downWOff + (uint64_t)D * F / kGroup * 2, cursor);
         }
     }
+    float *as = region;
     if (a.shared) {
-        // shared down rows from the activations phase A wrote
-        float *as = region;
-        float *asum = as + staged_stride(Fs);
         const uint32_t zero = 0;
-        stage_rows(a.sharedActs, (uint32_t)Fs, &zero, 1, Fs, as, asum);
-        const uint8_t *dw = a.shared + a.sharedOff.downWOff;
-        const uint16_t *ds = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.downSOff);
-        const uint16_t *db = reinterpret_cast<const uint16_t *>(a.shared + a.sharedOff.downBOff);
-        const int tasks = (D + 3) / 4;
-        const int skew = (K * ((F + 3) / 4)) % totalWarps;
-        for (int t = (gwarp + totalWarps - skew) % totalWarps; t < tasks; t += totalWarps) {
-            const int row = t * 4 + (lane >> 3);
-            float v[1], unused[1];
-            row_dot<1, false>(dw, ds, db, nullptr, nullptr, nullptr, row, Fs, row < D, as, asum, 1, v, unused);
-            if (row < D && (lane & 7) == 0) a.h1[row] = f2bf(v[0]);
-        }
+        stage_rows(a.sharedActs, (uint32_t)Fs, &zero, 1, Fs, as, as + staged_stride(Fs));
+    }
+    for (; tB < tasksRouted; tB += kBigWarps * G) {
+        cp_async_wait_all();
+        __syncwarp();
+        const int slot = tB / perSlot;
+        const int row = (tB - slot * perSlot) * 4 + r4;
+        const uint8_t *g0 = mySlot, *u0 = mySlot + imD.bytes();
+        float g[1], u[1];
+        row_dot<1, true, true>(g0, reinterpret_cast<const uint16_t *>(g0 + imD.wBytes),
+                               reinterpret_cast<const uint16_t *>(g0 + imD.wBytes + imD.sBytes), u0,
+                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes),
+                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes + imD.sBytes), r4, D, row < F,
+                               xs, xsum, 1, g, u);
+        if (row < F && j == 0) a.acts[slot * F + row] = f2bf(gelu_tanh(g[0]) * u[0]);
+        __syncwarp();
+        if (tB + kBigWarps * G < tasksRouted) stage_routed(tB + kBigWarps * G);
+    }
+    for (; tSD < tasksSharedDown; tSD += (kFusedWarps - kBigWarps) * G) {
+        cp_async_wait_all();
+        __syncwarp();
+        const int row = tSD * 4 + r4;
+        float v[1], unused[1];
+        row_dot<1, false, true>(mySlot, reinterpret_cast<const uint16_t *>(mySlot + imFs.wBytes),
+                                reinterpret_cast<const uint16_t *>(mySlot + imFs.wBytes + imFs.sBytes), nullptr,
+                                nullptr, nullptr, r4, Fs, row < D, as, as + staged_stride(Fs), 1, v, unused);
+        if (row < D && j == 0) a.h1[row] = f2bf(v[0]);
+        __syncwarp();
+        const int next = tSD + (kFusedWarps - kBigWarps) * G;
+        if (next < tasksSharedDown) issue_shared_down(next);
     }
     stamp(a, 4);
-    if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) return;
+    if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) {
+        cp_async_wait_all();
+        return;
+    }
     stamp(a, 5);
 
-    // ---------------- phase C ----------------
+    // ---------------- phase C: routed down rows and the combine ----------------
     {
-        float *as = region;
+        const int tasksDown = (D + 3) / 4;
+        const int imgBytes = imF.bytes();
+        auto stage_down = [&](int t) {
+            for (int k = 0; k < K; ++k) {
+                const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
+                stage_matrix_rows(mySlot + (size_t)k * imgBytes, imF, blob + a.off.downWOff,
+                                  blob + a.off.downSOff, blob + a.off.downBOff, t * 4, D, F);
+            }
+        };
+        int tC = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
+        if (tC < tasksDown) stage_down(tC);
         const int strideF = staged_stride(F);
         float *asum = as + 8 * strideF;
         stage_rows(a.acts, (uint32_t)F, sRowIdx, K, F, as, asum);
         const uint16_t *res = a.shared ? a.h1 : a.residual;
-        const int chunks = F >> 5, groups = F >> 6, j = lane & 7;
-        const int tasks = (D + 3) / 4;
-        for (int t = gwarp; t < tasks; t += totalWarps) {
-            const int row = t * 4 + (lane >> 3);
+        for (; tC < tasksDown; tC += kBigWarps * G) {
+            cp_async_wait_all();
+            __syncwarp();
+            const int row = tC * 4 + r4;
             const bool live = row < D;
             float acc = (live && res) ? bf2f(res[row]) : 0.0f;
-            if (chunks <= 24) {
-                // every slot's row is at most three 16-byte chunks per lane: the next slot's chunks
-                // are fetched while this slot's are accumulated (rolled loop, generic order)
-                uint4 wv[3], wn[3];
-                uint32_t sbv[3], sbn[3];  // scale | bias << 16
-                auto fetch = [&](int k, uint4 (&w)[3], uint32_t (&sb)[3]) {
-                    const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
-                    const uint4 *p = reinterpret_cast<const uint4 *>(blob + a.off.downWOff + (size_t)row * (F >> 1));
-                    const uint16_t *sr = reinterpret_cast<const uint16_t *>(blob + a.off.downSOff) + (size_t)row * groups;
-                    const uint16_t *br = reinterpret_cast<const uint16_t *>(blob + a.off.downBOff) + (size_t)row * groups;
-#pragma unroll
-                    for (int it = 0; it < 3; ++it) {
-                        const int c = j + 8 * it;
-                        if (c < chunks) {
-                            w[it] = load_stream(p + c);
-                            sb[it] = (uint32_t)sr[c >> 1] | ((uint32_t)br[c >> 1] << 16);
-                        }
-                    }
-                };
-                if (live) fetch(0, wv, sbv);
 #pragma unroll 1
-                for (int k = 0; k < K; ++k) {
-                    if (live && k + 1 < K) fetch(k + 1, wn, sbn);
-                    float part = 0.0f;
-                    if (live) {
-                        const float *xk = as + k * strideF;
-                        const float *sk = asum + k * chunks;
-#pragma unroll
-                        for (int it = 0; it < 3; ++it) {
-                            const int c = j + 8 * it;
-                            if (c < chunks) {
-                                const float sc = __uint_as_float(sbv[it] << 16);
-                                const float bi = fmaf(-16.0f, sc, __uint_as_float(sbv[it] & 0xFFFF0000u));
-                                const float *xc = xk + ((c >> 3) << 8) + ((c & 7) << 2);
-                                const uint32_t words[4] = {wv[it].x, wv[it].y, wv[it].z, wv[it].w};
-                                float d = 0.0f;
-#pragma unroll
-                                for (int w4 = 0; w4 < 4; ++w4) {
-                                    float qf[8];
-                                    unpack8_plus16(words[w4], qf);
-                                    const float4 xa = *reinterpret_cast<const float4 *>(xc + (w4 << 6));
-                                    const float4 xb = *reinterpret_cast<const float4 *>(xc + (w4 << 6) + 32);
-                                    d = fmaf(qf[0], xa.x, d);
-                                    d = fmaf(qf[1], xa.y, d);
-                                    d = fmaf(qf[2], xa.z, d);
-                                    d = fmaf(qf[3], xa.w, d);
-                                    d = fmaf(qf[4], xb.x, d);
-                                    d = fmaf(qf[5], xb.y, d);
-                                    d = fmaf(qf[6], xb.z, d);
-                                    d = fmaf(qf[7], xb.w, d);
-                                }
-                                part = fmaf(sc, d, part);
-                                part = fmaf(bi, sk[c], part);
-                            }
-                        }
-                    }
-                    part += __shfl_xor_sync(0xFFFFFFFFu, part, 4);
-                    part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
-                    part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
-                    acc = __fadd_rn(acc, __fmul_rn(sWeights[k], part));
-#pragma unroll
-                    for (int it = 0; it < 3; ++it) {
-                        wv[it] = wn[it];
-                        sbv[it] = sbn[it];
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int k = 0; k < K; ++k) {
-                    const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
-                    float v[1], unused[1];
-                    row_dot<1, false>(blob + a.off.downWOff, reinterpret_cast<const uint16_t *>(blob + a.off.downSOff),
-                                      reinterpret_cast<const uint16_t *>(blob + a.off.downBOff), nullptr, nullptr,
-                                      nullptr, row, F, live, as + k * strideF, asum + k * chunks, 1, v, unused);
-                    acc = __fadd_rn(acc, __fmul_rn(sWeights[k], v[0]));
-                }
+            for (int k = 0; k < K; ++k) {
+                const uint8_t *img = mySlot + (size_t)k * imgBytes;
+                float v[1], unused[1];
+                row_dot<1, false, true>(img, reinterpret_cast<const uint16_t *>(img + imF.wBytes),
+                                        reinterpret_cast<const uint16_t *>(img + imF.wBytes + imF.sBytes),
+                                        nullptr, nullptr, nullptr, r4, F, live, as + k * strideF,
+                                        asum + k * (F >> 5), 1, v, unused);
+                acc = __fadd_rn(acc, __fmul_rn(sWeights[k], v[0]));
             }
             if (live && j == 0) a.y[row] = f2bf(acc);
+            __syncwarp();
+            if (tC + kBigWarps * G < tasksDown) stage_down(tC + kBigWarps * G);
         }
     }
     stamp(a, 6);
 }
 
-static size_t fused_smem_bytes(const FFConfig &c) {
-    const size_t xPart = (size_t)staged_stride((int)c.d) + (c.d >> 5);
-    const size_t sharedPart = c.sharedF ? (size_t)staged_stride((int)c.sharedF) + (c.sharedF >> 5) : 0;
-    const size_t actsPart = (size_t)8 * (staged_stride((int)c.f) + (c.f >> 5));
-    return (xPart + std::max(sharedPart, actsPart)) * sizeof(float);
+struct FusedLayout {
+    size_t slotsOffset, bigBytes, smallBytes, total;
+};
+
+static FusedLayout fused_layout(const FFConfig &c) {
+    const size_t xPart = ((size_t)staged_stride((int)c.d) + (c.d >> 5)) * sizeof(float);
+    const size_t sharedPart =
+        c.sharedF ? ((size_t)staged_stride((int)c.sharedF) + (c.sharedF >> 5)) * sizeof(float) : 0;
+    const size_t actsPart = (size_t)8 * (staged_stride((int)c.f) + (c.f >> 5)) * sizeof(float);
+    FusedLayout l{};
+    l.slotsOffset = (xPart + std::max(sharedPart, actsPart) + 127) & ~(size_t)127;
+    const size_t gateUp = 2 * (size_t)rows_image((int)c.d).bytes();
+    const size_t down8 = 8 * (size_t)rows_image((int)c.f).bytes();
+    l.bigBytes = (std::max({gateUp, down8, (size_t)c.d * 2}) + 127) & ~(size_t)127;
+    l.smallBytes = c.sharedF ? (((size_t)rows_image((int)c.sharedF).bytes() + 127) & ~(size_t)127) : 128;
+    l.total = l.slotsOffset + kBigWarps * l.bigBytes + (kFusedWarps - kBigWarps) * l.smallBytes;
+    return l;
 }
 
 // One decode row through router (unless ids are given), routed experts and the shared FFN (or
@@ -453,7 +507,18 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.F = (int)c.f;
     a.Fs = (int)c.sharedF;
     a.K = (int)c.topK;
-    const size_t smem = fused_smem_bytes(c);
+    const FusedLayout lay = fused_layout(c);
+    const size_t smem = lay.total;
+    if (smem > 227 * 1024)
+        return fail(error, "model shape too large for the fused decode kernel's shared memory");
+    // the asynchronous 8-byte copies need 8-byte aligned scale/bias runs
+    const uint32_t *ro = &L.off.gateWOff, *so = &L.sharedOff.gateWOff;
+    for (int i = 0; i < 9; ++i)
+        if (ro[i] % 8 || (withShared && so[i] % 8) || L.stride % 8)
+            return fail(error, "sub-tensor offsets must be multiples of 8 bytes for the decode kernel");
+    a.slotsOffset = (uint32_t)lay.slotsOffset;
+    a.bigBytes = (uint32_t)lay.bigBytes;
+    a.smallBytes = (uint32_t)lay.smallBytes;
     static size_t configured[8] = {0};
     static int gridFor[8] = {0};
     const int slot = ctx->device & 7;

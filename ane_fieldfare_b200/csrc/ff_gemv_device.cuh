@@ -38,18 +38,54 @@ __device__ __forceinline__ int staged_index(int e) {
 __host__ __device__ inline int staged_stride(int cols) { return (cols + 255) & ~255; }
 
 // Eight codes of one 32-bit word as the floats 16+q: the code goes into the top mantissa bits of
-// a float whose exponent is 2^4.  The surplus 16*sum(x) is taken out once per chunk through the
-// bias term, so no per-code subtraction is needed.
+// a float whose exponent is 2^4 (bits 0x41800000 | q << 19).  The surplus 16*sum(x) is taken out
+// once per chunk through the bias term, so no per-code subtraction is needed.
+// Twelve integer instructions for eight codes, written as PTX so the count is what runs: the even
+// codes (low nibbles) and the odd codes (high nibbles) are each moved to bits 3..6 of their byte
+// and given bit 7 (two shifts, two lop3), then one byte permute per code drops that byte into
+// byte 2 of the float and 0x41 into byte 3.
 __device__ __forceinline__ void unpack8_plus16(uint32_t w, float (&q)[8]) {
-    constexpr uint32_t kMask = 0x00780000u, kBase = 0x41800000u;
-    q[0] = __uint_as_float(((w << 19) & kMask) | kBase);
-    q[1] = __uint_as_float(((w << 15) & kMask) | kBase);
-    q[2] = __uint_as_float(((w << 11) & kMask) | kBase);
-    q[3] = __uint_as_float(((w << 7) & kMask) | kBase);
-    q[4] = __uint_as_float(((w << 3) & kMask) | kBase);
-    q[5] = __uint_as_float(((w >> 1) & kMask) | kBase);
-    q[6] = __uint_as_float(((w >> 5) & kMask) | kBase);
-    q[7] = __uint_as_float(((w >> 9) & kMask) | kBase);
+    uint32_t even, odd, sl, sr;
+    asm("shl.b32 %0, %1, 3;" : "=r"(sl) : "r"(w));
+    asm("shr.b32 %0, %1, 1;" : "=r"(sr) : "r"(w));
+    // (a & b) | c  ->  lop3 immLut 0xEA
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(even) : "r"(sl), "r"(0x78787878u), "r"(0x80808080u));
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(odd) : "r"(sr), "r"(0x78787878u), "r"(0x80808080u));
+    const uint32_t hi = 0x41000000u;
+    uint32_t r0, r1, r2, r3, r4, r5, r6, r7;
+    asm("prmt.b32 %0, %1, %2, 0x7044;" : "=r"(r0) : "r"(even), "r"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7044;" : "=r"(r1) : "r"(odd), "r"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7144;" : "=r"(r2) : "r"(even), "r"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7144;" : "=r"(r3) : "r"(odd), "r"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7244;" : "=r"(r4) : "r"(even), "r"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7244;" : "=r"(r5) : "r"(odd), "r"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7344;" : "=r"(r6) : "r"(even), "r"(hi));
+    asm("prmt.b32 %0, %1, %2, 0x7344;" : "=r"(r7) : "r"(odd), "r"(hi));
+    q[0] = __uint_as_float(r0);
+    q[1] = __uint_as_float(r1);
+    q[2] = __uint_as_float(r2);
+    q[3] = __uint_as_float(r3);
+    q[4] = __uint_as_float(r4);
+    q[5] = __uint_as_float(r5);
+    q[6] = __uint_as_float(r6);
+    q[7] = __uint_as_float(r7);
+}
+
+// Packed fp32 pairs for fma.rn.f32x2 (low half = first value).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ float pair_sum(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo + hi;
 }
 
 __device__ __forceinline__ uint4 load_stream(const uint4 *p) { return __ldcs(p); }
@@ -87,10 +123,86 @@ __device__ inline void stage_rows(const uint16_t *in, uint32_t inStride, const u
     __syncthreads();
 }
 
-// One weight row (or a gate/up row pair) against NT staged input rows; returns the full sums in
-// every lane of the row's eight-lane group.  `live` false skips the loads but keeps the
-// shuffles convergent.
+// One 16-byte chunk (32 codes) of a weight row (or of a gate/up row pair) against NT staged input
+// rows: acc = fma(scale, sum(q*x), acc); acc = fma(bias - 16*scale, sum(x), acc).  `sb` packs the
+// group's scale (low 16 bits) and bias (high 16 bits) as bf16.  Every kernel that multiplies an
+// INT4 row by 1..16 input rows goes through this function, in chunk-ascending order per lane.
 template <int NT, bool DUAL>
+__device__ __forceinline__ void chunk_accumulate(const uint4 &v0, const uint4 &v1, uint32_t sb0v,
+                                                 uint32_t sb1v, int c, const float *xs, const float *xsum,
+                                                 int stride, int chunks, int n, float (&a0)[NT],
+                                                 float (&a1)[NT]) {
+    const float sc0 = __uint_as_float(sb0v << 16);
+    const float bi0 = fmaf(-16.0f, sc0, __uint_as_float(sb0v & 0xFFFF0000u));
+    float sc1 = 0.0f, bi1 = 0.0f;
+    if (DUAL) {
+        sc1 = __uint_as_float(sb1v << 16);
+        bi1 = fmaf(-16.0f, sc1, __uint_as_float(sb1v & 0xFFFF0000u));
+    }
+    // Two running sums per (matrix, input row), held as one packed fp32 pair and advanced by
+    // packed fused multiply-adds (fma.rn.f32x2: two fp32 FMAs per instruction): the even codes of
+    // the chunk accumulate in the low half, the odd codes in the high half; the halves are added
+    // once per chunk.
+    uint64_t d0[NT], d1[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        d0[t] = 0ull;
+        d1[t] = 0ull;
+    }
+    const float *xc = xs + ((c >> 3) << 8) + ((c & 7) << 2);
+    const uint32_t words0[4] = {v0.x, v0.y, v0.z, v0.w};
+    const uint32_t words1[4] = {v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float q0[8], q1[8];
+        unpack8_plus16(words0[k], q0);
+        if (DUAL) unpack8_plus16(words1[k], q1);
+        uint64_t p0[4], p1[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            p0[i] = pack2(q0[2 * i], q0[2 * i + 1]);
+            if (DUAL) p1[i] = pack2(q1[2 * i], q1[2 * i + 1]);
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const float *xt = xc + (t < n ? t : 0) * stride + (k << 6);
+            const float4 xa = *reinterpret_cast<const float4 *>(xt);
+            const float4 xb = *reinterpret_cast<const float4 *>(xt + 32);
+            const uint64_t x01 = pack2(xa.x, xa.y), x23 = pack2(xa.z, xa.w);
+            const uint64_t x45 = pack2(xb.x, xb.y), x67 = pack2(xb.z, xb.w);
+            uint64_t acc = d0[t];
+            acc = fma2(p0[0], x01, acc);
+            acc = fma2(p0[1], x23, acc);
+            acc = fma2(p0[2], x45, acc);
+            acc = fma2(p0[3], x67, acc);
+            d0[t] = acc;
+            if (DUAL) {
+                uint64_t acu = d1[t];
+                acu = fma2(p1[0], x01, acu);
+                acu = fma2(p1[1], x23, acu);
+                acu = fma2(p1[2], x45, acu);
+                acu = fma2(p1[3], x67, acu);
+                d1[t] = acu;
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const float sx = xsum[(t < n ? t : 0) * chunks + c];
+        a0[t] = fmaf(sc0, pair_sum(d0[t]), a0[t]);
+        a0[t] = fmaf(bi0, sx, a0[t]);
+        if (DUAL) {
+            a1[t] = fmaf(sc1, pair_sum(d1[t]), a1[t]);
+            a1[t] = fmaf(bi1, sx, a1[t]);
+        }
+    }
+}
+
+// One weight row (or a gate/up row pair) against NT staged input rows; returns the full sums in
+// every lane of the row's eight-lane group.  SMEM: the weight pointers address a copy of the rows
+// in shared memory (plain loads) instead of global memory (streaming loads).  `live` false skips the loads but keeps the
+// shuffles convergent.
+template <int NT, bool DUAL, bool SMEM = false>
 __device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, const uint16_t *b0,
                                         const uint8_t *w1, const uint16_t *s1, const uint16_t *b1,
                                         int row, int cols, bool live, const float *xs,
@@ -120,10 +232,10 @@ __device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, c
         uint4 v0b[kDepth], v1b[kDepth];
         uint32_t sb0[kDepth], sb1[kDepth];  // scale | bias << 16
         auto fetch = [&](int c, int slot) {
-            v0b[slot] = load_stream(p0 + c);
+            v0b[slot] = SMEM ? p0[c] : load_stream(p0 + c);
             sb0[slot] = (uint32_t)sr0[c >> 1] | ((uint32_t)br0[c >> 1] << 16);
             if (DUAL) {
-                v1b[slot] = load_stream(p1 + c);
+                v1b[slot] = SMEM ? p1[c] : load_stream(p1 + c);
                 sb1[slot] = (uint32_t)sr1[c >> 1] | ((uint32_t)br1[c >> 1] << 16);
             }
         };
@@ -138,67 +250,9 @@ __device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, c
                 if (c < chunks) {
                     const uint4 v0 = v0b[u];
                     const uint4 v1 = DUAL ? v1b[u] : v0b[u];
-                    const float sc0 = __uint_as_float(sb0[u] << 16);
-                    const float bi0 = fmaf(-16.0f, sc0, __uint_as_float(sb0[u] & 0xFFFF0000u));
-                    float sc1 = 0.0f, bi1 = 0.0f;
-                    if (DUAL) {
-                        sc1 = __uint_as_float(sb1[u] << 16);
-                        bi1 = fmaf(-16.0f, sc1, __uint_as_float(sb1[u] & 0xFFFF0000u));
-                    }
+                    const uint32_t p0sb = sb0[u], p1sb = DUAL ? sb1[u] : 0u;
                     if (c + 8 * kDepth < chunks) fetch(c + 8 * kDepth, u);
-                    float d0[NT], d1[NT];
-#pragma unroll
-                    for (int t = 0; t < NT; ++t) {
-                        d0[t] = 0.0f;
-                        d1[t] = 0.0f;
-                    }
-                    const float *xc = xs + ((c >> 3) << 8) + ((c & 7) << 2);
-                    const uint32_t words0[4] = {v0.x, v0.y, v0.z, v0.w};
-                    const uint32_t words1[4] = {v1.x, v1.y, v1.z, v1.w};
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        float q0[8], q1[8];
-                        unpack8_plus16(words0[k], q0);
-                        if (DUAL) unpack8_plus16(words1[k], q1);
-#pragma unroll
-                        for (int t = 0; t < NT; ++t) {
-                            const float *xt = xc + (t < n ? t : 0) * stride + (k << 6);
-                            const float4 xa = *reinterpret_cast<const float4 *>(xt);
-                            const float4 xb = *reinterpret_cast<const float4 *>(xt + 32);
-                            float acc = d0[t];
-                            acc = fmaf(q0[0], xa.x, acc);
-                            acc = fmaf(q0[1], xa.y, acc);
-                            acc = fmaf(q0[2], xa.z, acc);
-                            acc = fmaf(q0[3], xa.w, acc);
-                            acc = fmaf(q0[4], xb.x, acc);
-                            acc = fmaf(q0[5], xb.y, acc);
-                            acc = fmaf(q0[6], xb.z, acc);
-                            acc = fmaf(q0[7], xb.w, acc);
-                            d0[t] = acc;
-                            if (DUAL) {
-                                float acu = d1[t];
-                                acu = fmaf(q1[0], xa.x, acu);
-                                acu = fmaf(q1[1], xa.y, acu);
-                                acu = fmaf(q1[2], xa.z, acu);
-                                acu = fmaf(q1[3], xa.w, acu);
-                                acu = fmaf(q1[4], xb.x, acu);
-                                acu = fmaf(q1[5], xb.y, acu);
-                                acu = fmaf(q1[6], xb.z, acu);
-                                acu = fmaf(q1[7], xb.w, acu);
-                                d1[t] = acu;
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int t = 0; t < NT; ++t) {
-                        const float sx = xsum[(t < n ? t : 0) * chunks + c];
-                        a0[t] = fmaf(sc0, d0[t], a0[t]);
-                        a0[t] = fmaf(bi0, sx, a0[t]);
-                        if (DUAL) {
-                            a1[t] = fmaf(sc1, d1[t], a1[t]);
-                            a1[t] = fmaf(bi1, sx, a1[t]);
-                        }
-                    }
+                    chunk_accumulate<NT, DUAL>(v0, v1, p0sb, p1sb, c, xs, xsum, stride, chunks, n, a0, a1);
                 }
             }
         }

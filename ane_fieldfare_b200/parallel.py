@@ -1,0 +1,145 @@
+"""Expert parallelism for prefill-sized batches: experts sharded over the GPUs of one box, tokens
+data-parallel, one all-to-all each way per layer.
+
+The reference has no multi-device path (one Metal device, no collective library); this is the
+B200 addition.  Rank r of g holds experts [r*E/g, (r+1)*E/g) of every layer in its own HBM; the
+router and the shared FFN are replicated; every rank owns T/g token rows.  Per layer:
+
+  1. local router -> (token, rank) routes with global expert ids;
+  2. routes are ordered by destination rank (stable, so (token, rank) order is kept inside a
+     destination) and the per-destination counts are exchanged;
+  3. dispatch: all-to-all of the routed token rows (bf16) and their local expert ids;
+  4. the receiving rank runs its experts on the rows it got — the grouped INT4 GEMM path with one
+     route per row — reading only its own memory;
+  5. combine: all-to-all of the bf16 partial rows back to the tokens' home ranks;
+  6. the home rank puts them back in (token, rank) order and does the weighted reduce, adding its
+     shared-FFN rows.
+
+The collective is torch.distributed's all_to_all_single: NCCL over NVLink/NVSwitch on GPUs, gloo
+in the CPU tests.  Decode and verify do not use this: they run as independent replicas.
+The planning functions are plain tensor arithmetic so they run (and are tested) on CPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class DispatchPlan:
+    order: torch.Tensor         # int64 [routes]: route index (token*K + rank) in send order
+    send_counts: torch.Tensor   # int64 [world]: routes going to each rank
+    local_expert: torch.Tensor  # int32 [routes]: expert id on the destination rank, in send order
+    token: torch.Tensor         # int64 [routes]: source token row, in send order
+
+
+def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int) -> DispatchPlan:
+    """Routes ordered by destination rank, (token, rank) order kept inside a destination."""
+    tokens, k = ids.shape
+    flat = ids.reshape(-1).to(torch.int64)
+    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
+    if tokens and (int(dest.max()) >= world or int(flat.min()) < 0):
+        raise ValueError("route expert out of range for this expert-parallel group")
+    order = torch.argsort(dest, stable=True)
+    send_counts = torch.bincount(dest, minlength=world).to(torch.int64)
+    local = (flat[order] - dest[order] * experts_per_rank).to(torch.int32)
+    return DispatchPlan(order, send_counts, local, torch.div(order, k, rounding_mode="floor"))
+
+
+def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    recv = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv, send_counts, group=group)
+    return recv
+
+
+def all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group=None) -> torch.Tensor:
+    """Variable-split all-to-all along dim 0; counts are python lists of row counts."""
+    out = torch.empty((int(sum(recv_counts)),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
+                           input_split_sizes=list(send_counts), group=group)
+    return out
+
+
+class ExpertParallelMoE:
+    """One MoE layer under expert parallelism.
+
+    `router_fn(x) -> (ids int32 [T,K], weights [T,K])`, `shared_fn(x) -> [T,D] or None`,
+    `experts_fn(rows [R,D], local_ids int32 [R]) -> partial rows [R,D]`,
+    `reduce_fn(partials [T*K,D], weights, residual) -> y [T,D]` are supplied by the caller: the CUDA
+    library on GPUs (see `cuda_layer_fns`), plain torch functions in the CPU tests."""
+
+    def __init__(self, experts: int, top_k: int, router_fn: Callable, shared_fn: Callable,
+                 experts_fn: Callable, reduce_fn: Callable, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if experts % self.world:
+            raise ValueError("experts must divide evenly over the ranks")
+        self.experts, self.top_k = experts, top_k
+        self.experts_per_rank = experts // self.world
+        self.router_fn, self.shared_fn = router_fn, shared_fn
+        self.experts_fn, self.reduce_fn = experts_fn, reduce_fn
+        self.last_recv_rows = 0
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        ids, weights = self.router_fn(x)
+        plan = dispatch_plan(ids, self.experts_per_rank, self.world)
+        recv_counts = exchange_counts(plan.send_counts.to(x.device), self.group)
+        send_list = plan.send_counts.tolist()
+        recv_list = recv_counts.tolist()
+        rows = all_to_all_rows(x.index_select(0, plan.token.to(x.device)), send_list, recv_list, self.group)
+        local = all_to_all_rows(plan.local_expert.to(x.device), send_list, recv_list, self.group)
+        self.last_recv_rows = rows.shape[0]
+        residual = self.shared_fn(x)
+        partial_rows = self.experts_fn(rows, local)
+        back = all_to_all_rows(partial_rows, recv_list, send_list, self.group)
+        partials = torch.empty_like(back)
+        partials[plan.order.to(x.device)] = back
+        return self.reduce_fn(partials, weights, residual)
+
+
+def cuda_layer_fns(home_ctx, expert_ctx, layer: int):
+    """The four callables for `ExpertParallelMoE` backed by libfieldfare_cuda.so.
+
+    `home_ctx`: a HotpathContext holding the replicated router and shared FFN of `layer`
+    (topK = K); `expert_ctx`: a HotpathContext created with topK = 1 and experts = E/g holding this
+    rank's experts, so a received row with one local expert id is a one-route token."""
+    from . import hotpath
+
+    router = hotpath.PrefillRouter(home_ctx)
+    shared = hotpath.PrefillSharedExpert(home_ctx)
+    reduce = hotpath.PrefillMoE(home_ctx)
+    routed = hotpath.PrefillGroupedRoutedMoE(expert_ctx)
+    d, k = home_ctx.d, home_ctx.topK
+
+    def router_fn(x):
+        t = x.shape[0]
+        ids = torch.empty((t, k), dtype=torch.int32, device=x.device)
+        w = torch.empty((t, k), dtype=torch.bfloat16, device=x.device)
+        router.encodeGemma4Block(None, layer, x, ids, w, t)
+        return ids, w
+
+    def shared_fn(x):
+        if not home_ctx.sharedF:
+            return None
+        y = torch.empty((x.shape[0], d), dtype=torch.bfloat16, device=x.device)
+        shared.encodeBlock(None, layer, x, y, x.shape[0])
+        return y
+
+    def experts_fn(rows, local_ids):
+        out = torch.empty_like(rows)
+        if rows.shape[0]:
+            routed.encodeStreamedBatched(None, layer, rows, local_ids.reshape(-1, 1).contiguous(), out,
+                                         rows.shape[0])
+        return out
+
+    def reduce_fn(partials, weights, residual):
+        t = weights.shape[0]
+        y = torch.empty((t, d), dtype=torch.bfloat16, device=partials.device)
+        reduce.encodeReduceTokenMajor(None, partials, weights, y, t, residual=residual)
+        return y
+
+    return router_fn, shared_fn, experts_fn, reduce_fn
