@@ -173,6 +173,7 @@ __device__ __forceinline__ void stage_matrix_rows(uint8_t *dst, const RowsImage 
 constexpr int kBigWarps = 10;  // warps with a large staging slot (gate/up pairs, down x 8 slots)
 
 __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeArgs a) {
+    const int kSelZero[1] = {0};
     extern __shared__ __align__(16) uint8_t smemRaw[];
     __shared__ float sLogits[kMaxExperts];
     __shared__ uint32_t sIds[8];
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
                                reinterpret_cast<const uint16_t *>(g0 + imD.wBytes + imD.sBytes), u0,
                                reinterpret_cast<const uint16_t *>(u0 + imD.wBytes),
                                reinterpret_cast<const uint16_t *>(u0 + imD.wBytes + imD.sBytes), r4, D, row < Fs,
-                               xs, xsum, 1, g, u);
+                               xs, xsum, kSelZero, g, u);
         if (row < Fs && j == 0) a.sharedActs[row] = f2bf(gelu_tanh(bf16_round(g[0])) * bf16_round(u[0]));
         __syncwarp();
         if (tA + 4 * G < tasksSharedGU) issue_shared_gu(tA + 4 * G);
@@ -374,7 +375,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
                                reinterpret_cast<const uint16_t *>(g0 + imD.wBytes + imD.sBytes), u0,
                                reinterpret_cast<const uint16_t *>(u0 + imD.wBytes),
                                reinterpret_cast<const uint16_t *>(u0 + imD.wBytes + imD.sBytes), r4, D, row < F,
-                               xs, xsum, 1, g, u);
+                               xs, xsum, kSelZero, g, u);
         if (row < F && j == 0) a.acts[slot * F + row] = f2bf(gelu_tanh(g[0]) * u[0]);
         __syncwarp();
         if (tB + kBigWarps * G < tasksRouted) stage_routed(tB + kBigWarps * G);
@@ -386,7 +387,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
         float v[1], unused[1];
         row_dot<1, false, true>(mySlot, reinterpret_cast<const uint16_t *>(mySlot + imFs.wBytes),
                                 reinterpret_cast<const uint16_t *>(mySlot + imFs.wBytes + imFs.sBytes), nullptr,
-                                nullptr, nullptr, r4, Fs, row < D, as, as + staged_stride(Fs), 1, v, unused);
+                                nullptr, nullptr, r4, Fs, row < D, as, as + staged_stride(Fs), kSelZero, v, unused);
         if (row < D && j == 0) a.h1[row] = f2bf(v[0]);
         __syncwarp();
         const int next = tSD + (kFusedWarps - kBigWarps) * G;
@@ -429,7 +430,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
                 row_dot<1, false, true>(img, reinterpret_cast<const uint16_t *>(img + imF.wBytes),
                                         reinterpret_cast<const uint16_t *>(img + imF.wBytes + imF.sBytes),
                                         nullptr, nullptr, nullptr, r4, F, live, as + k * strideF,
-                                        asum + k * (F >> 5), 1, v, unused);
+                                        asum + k * (F >> 5), kSelZero, v, unused);
                 acc = __fadd_rn(acc, __fmul_rn(sWeights[k], v[0]));
             }
             if (live && j == 0) a.y[row] = f2bf(acc);

@@ -22,15 +22,23 @@
 
 namespace ff {
 
-template <int NT, bool DUAL>
+template <int NT, bool DUAL, bool STAGE_ALL>
 __device__ __forceinline__ void run_item(const GemvJob &job, int row0, const float *xs,
                                          const float *xsum) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = row0 + warp * 4 + (lane >> 3);
     const bool live = row < (int)job.rows;
+    // staged row each input reads: with all rows of the block staged once, the job's own row
+    // numbers; otherwise the job's rows were staged compactly in order
+    int sel[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const int tt = t < (int)job.n ? t : 0;
+        sel[t] = STAGE_ALL ? (int)job.inRow[tt] : tt;
+    }
     float a0[NT], a1[NT];
     row_dot<NT, DUAL>(job.w0, job.s0, job.b0, job.w1, job.s1, job.b1, row, (int)job.cols, live, xs,
-                      xsum, (int)job.n, a0, a1);
+                      xsum, sel, a0, a1);
     if (live && (lane & 7) == 0) {
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
@@ -50,20 +58,28 @@ __device__ __forceinline__ void run_item(const GemvJob &job, int row0, const flo
     }
 }
 
-// Persistent grouped GEMV: each CTA takes a contiguous range of (job, row block) items, restaging
-// the input rows only when the job changes.  With `jobs` null the single `inlineJob` is used.
-template <int MAXNT, bool DUAL>
+// Persistent grouped GEMV over (job, row block) items.  With `jobs` null the single `inlineJob`
+// is used.  STAGE_ALL: every job reads rows of one input block (`allRows` x `allCols`), which is
+// staged once per CTA and items are dealt round robin; otherwise a job's input rows are staged
+// when a CTA meets the job, and items are dealt in chunks of two so that a staging is shared.
+template <int MAXNT, bool DUAL, bool STAGE_ALL>
 __global__ void __launch_bounds__(kGemvThreads)
 k_int4_gemv(const GemvJob *jobs, const uint32_t *items, const uint32_t *itemCountPtr,
-            GemvJob inlineJob, uint32_t inlineItems, uint32_t maxCols) {
+            GemvJob inlineJob, uint32_t inlineItems, uint32_t maxCols, const uint16_t *allIn,
+            uint32_t allStride, uint32_t allRows) {
     extern __shared__ float smem[];
     __shared__ GemvJob sjob;
+    __shared__ uint32_t sAllRows[kMaxGemvRows];
     float *xs = smem;
-    float *xsum = smem + MAXNT * staged_stride((int)maxCols);
+    const int stagedRows = STAGE_ALL ? (int)allRows : MAXNT;
+    float *xsum = smem + stagedRows * staged_stride((int)maxCols);
     const uint32_t nItems = jobs ? *itemCountPtr : inlineItems;
-    // items go to CTAs in chunks of kItemChunk, round robin: heavy jobs (many input rows) are
-    // spread over the whole grid while a chunk still shares one staging of its job's inputs
-    constexpr uint32_t kItemChunk = 2;
+    if (STAGE_ALL) {
+        if (threadIdx.x < kMaxGemvRows) sAllRows[threadIdx.x] = threadIdx.x;
+        __syncthreads();
+        stage_rows(allIn, allStride, sAllRows, (int)allRows, (int)maxCols, xs, xsum);
+    }
+    constexpr uint32_t kItemChunk = STAGE_ALL ? 1 : 2;
     const uint32_t nChunks = (nItems + kItemChunk - 1) / kItemChunk;
     int current = -1;
     for (uint32_t chunk = blockIdx.x; chunk < nChunks; chunk += gridDim.x)
@@ -81,22 +97,23 @@ k_int4_gemv(const GemvJob *jobs, const uint32_t *items, const uint32_t *itemCoun
             uint32_t *dst = reinterpret_cast<uint32_t *>(&sjob);
             for (int i = threadIdx.x; i < (int)(sizeof(GemvJob) / 4); i += blockDim.x) dst[i] = src[i];
             __syncthreads();
-            stage_rows(sjob.in, sjob.inStride, sjob.inRow, min((int)sjob.n, MAXNT), (int)sjob.cols,
-                       xs, xsum);
+            if (!STAGE_ALL)
+                stage_rows(sjob.in, sjob.inStride, sjob.inRow, min((int)sjob.n, MAXNT), (int)sjob.cols,
+                           xs, xsum);
             current = (int)jobIdx;
         }
         const int row0 = (int)block * kRowsPerItem;
         const int n = (int)sjob.n;
         if (n <= 1) {
-            run_item<1, DUAL>(sjob, row0, xs, xsum);
+            run_item<1, DUAL, STAGE_ALL>(sjob, row0, xs, xsum);
         } else if (MAXNT >= 2 && n <= 2) {
-            run_item<(MAXNT >= 2 ? 2 : 1), DUAL>(sjob, row0, xs, xsum);
+            run_item<(MAXNT >= 2 ? 2 : 1), DUAL, STAGE_ALL>(sjob, row0, xs, xsum);
         } else if (MAXNT >= 4 && n <= 4) {
-            run_item<(MAXNT >= 4 ? 4 : 1), DUAL>(sjob, row0, xs, xsum);
+            run_item<(MAXNT >= 4 ? 4 : 1), DUAL, STAGE_ALL>(sjob, row0, xs, xsum);
         } else if (MAXNT >= 8 && n <= 8) {
-            run_item<(MAXNT >= 8 ? 8 : 1), DUAL>(sjob, row0, xs, xsum);
+            run_item<(MAXNT >= 8 ? 8 : 1), DUAL, STAGE_ALL>(sjob, row0, xs, xsum);
         } else if (MAXNT >= 16) {
-            run_item<(MAXNT >= 16 ? 16 : 1), DUAL>(sjob, row0, xs, xsum);
+            run_item<(MAXNT >= 16 ? 16 : 1), DUAL, STAGE_ALL>(sjob, row0, xs, xsum);
         }
     }
 }
@@ -460,17 +477,23 @@ k_dequant_probe(const uint8_t *w, const uint16_t *s, const uint16_t *b, int rows
 
 // ---- host launchers ------------------------------------------------------------------------
 
-static size_t gemv_smem_bytes(int maxNt, uint32_t maxCols) {
-    return (size_t)maxNt * (staged_stride((int)maxCols) + (maxCols >> 5)) * sizeof(float);
+static size_t gemv_smem_bytes(int rows, uint32_t maxCols) {
+    return (size_t)rows * (staged_stride((int)maxCols) + (maxCols >> 5)) * sizeof(float);
 }
 
-template <int MAXNT, bool DUAL>
+// The input block all jobs of a launch read (staged once per CTA), or null.
+struct StageAll {
+    const uint16_t *in = nullptr;
+    uint32_t stride = 0, rows = 0;
+};
+
+template <int MAXNT, bool DUAL, bool STAGE_ALL>
 static bool launch_gemv_kernel(FFContext *ctx, const GemvJob *jobs, const uint32_t *items,
                                const uint32_t *itemCountPtr, const GemvJob &inlineJob,
                                uint32_t inlineItems, uint32_t maxCols, uint32_t itemBound,
-                               cudaStream_t stream, const char **error) {
-    auto kernel = k_int4_gemv<MAXNT, DUAL>;
-    const size_t smem = gemv_smem_bytes(MAXNT, maxCols);
+                               const StageAll &all, cudaStream_t stream, const char **error) {
+    auto kernel = k_int4_gemv<MAXNT, DUAL, STAGE_ALL>;
+    const size_t smem = gemv_smem_bytes(STAGE_ALL ? (int)all.rows : MAXNT, maxCols);
     if (smem > 200 * 1024)
         return fail(error, "input rows do not fit in shared memory: " + std::to_string(MAXNT) +
                                " rows x " + std::to_string(maxCols) + " columns");
@@ -500,7 +523,7 @@ static bool launch_gemv_kernel(FFContext *ctx, const GemvJob *jobs, const uint32
     {
         LaunchScope scope(ctx, stream, DUAL ? "int4_gemv_gate_up_act" : "int4_gemv_down");
         kernel<<<grid, kGemvThreads, smem, stream>>>(jobs, items, itemCountPtr, inlineJob,
-                                                     inlineItems, maxCols);
+                                                     inlineItems, maxCols, all.in, all.stride, all.rows);
     }
     FF_CUDA_OK(cudaGetLastError(), error);
     return true;
@@ -510,21 +533,21 @@ template <bool DUAL>
 static bool launch_gemv_class(FFContext *ctx, uint32_t rowsClass, const GemvJob *jobs,
                               const uint32_t *items, const uint32_t *itemCountPtr,
                               const GemvJob &inlineJob, uint32_t inlineItems, uint32_t maxCols,
-                              uint32_t itemBound, cudaStream_t stream, const char **error) {
-    if (rowsClass <= 1)
-        return launch_gemv_kernel<1, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
-                                           maxCols, itemBound, stream, error);
-    if (rowsClass <= 2)
-        return launch_gemv_kernel<2, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
-                                           maxCols, itemBound, stream, error);
-    if (rowsClass <= 4)
-        return launch_gemv_kernel<4, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
-                                           maxCols, itemBound, stream, error);
-    if (rowsClass <= 8)
-        return launch_gemv_kernel<8, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
-                                           maxCols, itemBound, stream, error);
-    return launch_gemv_kernel<16, DUAL>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems,
-                                        maxCols, itemBound, stream, error);
+                              uint32_t itemBound, cudaStream_t stream, const char **error,
+                              const StageAll &all = StageAll()) {
+#define FF_GEMV_DISPATCH(NTV)                                                                        \
+    return all.in ? launch_gemv_kernel<NTV, DUAL, true>(ctx, jobs, items, itemCountPtr, inlineJob,     \
+                                                        inlineItems, maxCols, itemBound, all, stream, \
+                                                        error)                                        \
+                  : launch_gemv_kernel<NTV, DUAL, false>(ctx, jobs, items, itemCountPtr, inlineJob,    \
+                                                         inlineItems, maxCols, itemBound, all, stream, \
+                                                         error)
+    if (rowsClass <= 1) FF_GEMV_DISPATCH(1);
+    if (rowsClass <= 2) FF_GEMV_DISPATCH(2);
+    if (rowsClass <= 4) FF_GEMV_DISPATCH(4);
+    if (rowsClass <= 8) FF_GEMV_DISPATCH(8);
+    FF_GEMV_DISPATCH(16);
+#undef FF_GEMV_DISPATCH
 }
 
 static uint32_t blocks_of(uint32_t rows) { return (rows + kRowsPerItem - 1) / kRowsPerItem; }
@@ -632,8 +655,12 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     const uint32_t maxActive = (uint32_t)std::min<uint64_t>((uint64_t)tokens * c.topK, (uint64_t)E);
     const uint32_t bound0 = (withShared ? blocks_of(c.sharedF) : 0u) + maxActive * blocks_of(c.f);
     GemvJob none{};
+    StageAll all;
+    all.in = x;
+    all.stride = xStride;
+    all.rows = tokens;
     if (!launch_gemv_class<true>(ctx, tokens, ctx->jobs[0], ctx->items[0], &ctx->plan->itemCount[0],
-                                 none, 0, c.d, bound0, stream, error))
+                                 none, 0, c.d, bound0, stream, error, all))
         return false;
     const uint32_t bound1 =
         (withShared ? blocks_of(c.d) : 0u) + (decodeCombine ? 0u : maxActive * blocks_of(c.d));

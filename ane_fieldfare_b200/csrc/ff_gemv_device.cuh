@@ -127,11 +127,12 @@ __device__ inline void stage_rows(const uint16_t *in, uint32_t inStride, const u
 // rows: acc = fma(scale, sum(q*x), acc); acc = fma(bias - 16*scale, sum(x), acc).  `sb` packs the
 // group's scale (low 16 bits) and bias (high 16 bits) as bf16.  Every kernel that multiplies an
 // INT4 row by 1..16 input rows goes through this function, in chunk-ascending order per lane.
+// sel[t] is the staged row that input t reads.
 template <int NT, bool DUAL>
 __device__ __forceinline__ void chunk_accumulate(const uint4 &v0, const uint4 &v1, uint32_t sb0v,
                                                  uint32_t sb1v, int c, const float *xs, const float *xsum,
-                                                 int stride, int chunks, int n, float (&a0)[NT],
-                                                 float (&a1)[NT]) {
+                                                 int stride, int chunks, const int (&sel)[NT],
+                                                 float (&a0)[NT], float (&a1)[NT]) {
     const float sc0 = __uint_as_float(sb0v << 16);
     const float bi0 = fmaf(-16.0f, sc0, __uint_as_float(sb0v & 0xFFFF0000u));
     float sc1 = 0.0f, bi1 = 0.0f;
@@ -165,7 +166,7 @@ __device__ __forceinline__ void chunk_accumulate(const uint4 &v0, const uint4 &v
         }
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-            const float *xt = xc + (t < n ? t : 0) * stride + (k << 6);
+            const float *xt = xc + sel[t] * stride + (k << 6);
             const float4 xa = *reinterpret_cast<const float4 *>(xt);
             const float4 xb = *reinterpret_cast<const float4 *>(xt + 32);
             const uint64_t x01 = pack2(xa.x, xa.y), x23 = pack2(xa.z, xa.w);
@@ -188,7 +189,7 @@ __device__ __forceinline__ void chunk_accumulate(const uint4 &v0, const uint4 &v
     }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-        const float sx = xsum[(t < n ? t : 0) * chunks + c];
+        const float sx = xsum[sel[t] * chunks + c];
         a0[t] = fmaf(sc0, pair_sum(d0[t]), a0[t]);
         a0[t] = fmaf(bi0, sx, a0[t]);
         if (DUAL) {
@@ -206,7 +207,7 @@ template <int NT, bool DUAL, bool SMEM = false>
 __device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, const uint16_t *b0,
                                         const uint8_t *w1, const uint16_t *s1, const uint16_t *b1,
                                         int row, int cols, bool live, const float *xs,
-                                        const float *xsum, int n, float (&a0)[NT],
+                                        const float *xsum, const int (&sel)[NT], float (&a0)[NT],
                                         float (&a1)[NT]) {
     const int lane = threadIdx.x & 31;
     const int j = lane & 7;
@@ -252,7 +253,7 @@ __device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, c
                     const uint4 v1 = DUAL ? v1b[u] : v0b[u];
                     const uint32_t p0sb = sb0[u], p1sb = DUAL ? sb1[u] : 0u;
                     if (c + 8 * kDepth < chunks) fetch(c + 8 * kDepth, u);
-                    chunk_accumulate<NT, DUAL>(v0, v1, p0sb, p1sb, c, xs, xsum, stride, chunks, n, a0, a1);
+                    chunk_accumulate<NT, DUAL>(v0, v1, p0sb, p1sb, c, xs, xsum, stride, chunks, sel, a0, a1);
                 }
             }
         }

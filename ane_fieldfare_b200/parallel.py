@@ -101,12 +101,13 @@ class ExpertParallelMoE:
         return self.reduce_fn(partials, weights, residual)
 
 
-def cuda_layer_fns(home_ctx, expert_ctx, layer: int):
+def cuda_layer_fns(home_ctx, expert_ctx, layer: int, expert_layer: Optional[int] = None):
     """The four callables for `ExpertParallelMoE` backed by libfieldfare_cuda.so.
 
     `home_ctx`: a HotpathContext holding the replicated router and shared FFN of `layer`
     (topK = K); `expert_ctx`: a HotpathContext created with topK = 1 and experts = E/g holding this
-    rank's experts, so a received row with one local expert id is a one-route token."""
+    rank's experts (in slot `expert_layer`, default `layer`), so a received row with one local
+    expert id is a one-route token."""
     from . import hotpath
 
     router = hotpath.PrefillRouter(home_ctx)
@@ -114,6 +115,7 @@ def cuda_layer_fns(home_ctx, expert_ctx, layer: int):
     reduce = hotpath.PrefillMoE(home_ctx)
     routed = hotpath.PrefillGroupedRoutedMoE(expert_ctx)
     d, k = home_ctx.d, home_ctx.topK
+    slot = layer if expert_layer is None else expert_layer
 
     def router_fn(x):
         t = x.shape[0]
@@ -132,7 +134,7 @@ def cuda_layer_fns(home_ctx, expert_ctx, layer: int):
     def experts_fn(rows, local_ids):
         out = torch.empty_like(rows)
         if rows.shape[0]:
-            routed.encodeStreamedBatched(None, layer, rows, local_ids.reshape(-1, 1).contiguous(), out,
+            routed.encodeStreamedBatched(None, slot, rows, local_ids.reshape(-1, 1).contiguous(), out,
                                          rows.shape[0])
         return out
 

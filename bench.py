@@ -198,6 +198,82 @@ def traced_kernels(ctx, step, group):
     return {name: {"launches": n, "avg_us": round(1e3 * t / n, 3)} for name, (n, t) in trace.items()}
 
 
+STACK_DISTINCT_LAYERS = 3
+STACK_LAYERS = 30
+STACK_TOKENS = 32768
+
+
+def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank, world, device, args):
+    """Benchmark configuration 4: a 30-layer stack of MoE blocks (RMSNorm between layers, no
+    attention), 32768 prefill tokens, experts sharded over the ranks with an NCCL all-to-all
+    dispatch and combine per layer.  All 30 layer slots are resident (13.2 GB over the box); their
+    bytes repeat a few distinct seeded layers, which does not change the work."""
+    from ane_fieldfare_b200 import parallel, synth
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    layers = args.stack_layers
+    tokens_local = STACK_TOKENS // world
+    epr = E // world
+    capacity = min(STACK_TOKENS * K, 3 * tokens_local * K)
+    home = hotpath.HotpathContext(layers=len(host_layers), experts=E, d=D, f=F, sharedF=FS, topK=K,
+                                  maxTokens=tokens_local, device=local_rank)
+    local = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=1,
+                                   maxTokens=capacity, device=local_rank)
+    for i, L in enumerate(host_layers):
+        home.loadShared(i, *L.shared_projections())
+        home.loadRouter(i, L.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}"))
+    for slot in range(layers):
+        L = host_layers[slot % len(host_layers)]
+        local.loadLayer(slot, L.blobs[rank * epr:(rank + 1) * epr], L.layout.stride, L.layout.offsets,
+                        expertCount=epr)
+    blocks = []
+    for slot in range(layers):
+        # the home context is indexed by the distinct layer, the expert context by the stack's slot
+        fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
+        blocks.append(parallel.ExpertParallelMoE(E, K, *fns))
+    x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
+
+    def run_stack():
+        x = x0
+        for block in blocks:
+            x = block.forward(home.rmsnorm(x, None, 1e-6))
+        return x
+
+    for _ in range(2):
+        run_stack()
+    torch.cuda.synchronize()
+    dist.barrier()
+    steps = 3
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        y = run_stack()
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / steps
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    recv = torch.tensor([float(blocks[-1].last_recv_rows)], dtype=torch.float64, device=device)
+    rows = [torch.zeros_like(recv) for _ in range(world)]
+    dist.all_gather(rows, recv)
+    finite = bool(torch.isfinite(y.float()).all().item())
+    err = home.info().deviceErrorFlag | local.info().deviceErrorFlag
+    flops = layers * STACK_TOKENS * (2 * (K * 3 * F * D + 3 * FS * D + E * D))
+    peak = measured_bf16_peak()
+    home.close()
+    local.close()
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens_expert_parallel", "gpus": world,
+            "tokens_per_s": STACK_TOKENS / (ms * 1e-3), "ms_per_stack": ms, "steps": steps,
+            "tflops": tf, "frac_of_measured_bf16_per_gpu": tf / (peak["tflops"] * world),
+            "last_layer_rows_received_per_rank": [int(r.item()) for r in rows],
+            "output_finite": finite, "device_error_flag": int(err),
+            "collective": "NCCL all_to_all_single (dispatch + combine per layer)"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -210,15 +286,15 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     n_layers = args.layers
-    want = set(args.only.split(",")) if args.only else {"decode", "verify", "prefill"}
+    want = set(args.only.split(",")) if args.only else {"decode", "verify", "prefill", "stack"}
     max_tokens = PREFILL_TOKENS if "prefill" in want else 16
     ctx = hotpath.HotpathContext(layers=n_layers, experts=E, d=D, f=F, sharedF=FS, topK=K,
                                  maxTokens=max_tokens, device=local_rank)
     host_layers = []
     for slot in range(n_layers):
-        L = workload.make_layer(ROOT_SEED + 977 * rank, slot)
+        L = workload.make_layer(ROOT_SEED, slot)
         workload.load_layer(ctx, slot, L)
-        host_layers.append(L if slot == 0 else (L.routerW,))
+        host_layers.append(L if slot < STACK_DISTINCT_LAYERS else (L.routerW,))
     host_layer0 = host_layers[0]
     peaks = measured_peaks()
     stream = torch.cuda.Stream(device=device)
@@ -226,7 +302,7 @@ def run_ours(args):
     def set_router_bias(kind):
         from ane_fieldfare_b200 import synth
         for slot in range(n_layers):
-            router = host_layers[slot].routerW if slot == 0 else host_layers[slot][0]
+            router = host_layers[slot].routerW if slot < STACK_DISTINCT_LAYERS else host_layers[slot][0]
             if kind == "none":
                 bias = None
             elif kind == "normal":
@@ -275,13 +351,13 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
     value = world * steps / (ms * 1e-3)
-    kernels = traced_kernels(ctx, decode_step, group)
+    kernels = {} if args.quick else traced_kernels(ctx, decode_step, group)
 
     # end to end through the host-buffer entry point
     hx = [torch.from_numpy(tokens_bits[i:i + 1].view(np.int16).copy()).view(torch.bfloat16).pin_memory()
           for i in range(n_rows)]
     hy = torch.zeros((1, D), dtype=torch.bfloat16).pin_memory()
-    e2e_steps = min(steps, 2000)
+    e2e_steps = 8 if args.quick else min(steps, 2000)
     for i in range(5):
         ctx.moeLayerHost(i % n_layers, hx[i % n_rows], hy)
     if world > 1:
@@ -385,14 +461,25 @@ def run_ours(args):
                          "frac_of_nominal_2250TF": tf / 2250.0, "algorithmic_flops_per_step": flops},
             "kernels": traced_kernels(ctx, prefill_step, 4)}
 
-    if rank == 0:
+    # ================= stack: config 4, 30 layers x 32768 tokens, experts sharded over the ranks ====
+    if "stack" in want:
+        ctx.close()
+        ctx = None
+        stack = measure_stack(torch, dist, hotpath, workload, host_layers[:min(STACK_DISTINCT_LAYERS, n_layers)],
+                              rank, local_rank, world, device, args)
+        if rank == 0:
+            line["stack"] = stack
+
+    if rank == 0 and not args.quick:
         cpu_rate, cpu_steps, cpu_threads = cpu_decode_baseline(host_layer0, tokens_bits)
         line["cpu_baseline"] = {"value": cpu_rate, "unit": "tokens/s", "cores": cpu_threads,
                                 "kind": "port",
                                 "sample": f"{cpu_steps} decode steps of the C oracle (OpenMP), one layer"}
+    if rank == 0:
         print(json.dumps(line), flush=True)
-    ctx.close()
-    if world > 1:
+    if ctx is not None:
+        ctx.close()
+    if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
 
@@ -404,7 +491,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=64)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=8, help="resident layers the steps rotate over")
-    ap.add_argument("--only", default="", help="comma list of decode,verify,prefill (default all)")
+    ap.add_argument("--only", default="", help="comma list of decode,verify,prefill,stack (default all)")
+    ap.add_argument("--stack-layers", type=int, default=STACK_LAYERS, help="layers of the config-4 stack")
+    ap.add_argument("--quick", action="store_true",
+                    help="skip the end-to-end loop, per-kernel tracing and the CPU baseline (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
