@@ -1,15 +1,16 @@
 // Prefill path of the INT4 MoE block: router for many rows, device-side permute (counting sort by
 // expert), and the grouped INT4 -> bf16 GEMMs on the 5th-generation tensor cores.
 //
-// GEMM scheme.  A work unit is (row tile of up to 256 expert-sorted rows = one or two 128-row MMA
-// tiles sharing the dequantized weights, column tile of 128 outputs).  Per 64-wide step along the contraction (= one quantization group):
+// GEMM scheme.  A work unit is (row tile of up to 128 expert-sorted rows, column tile of 256
+// outputs: 128 gate + 128 up rows, or 256 down rows).  The wide column tile halves the re-reads of
+// the activation tile from L2, which bound the narrower tilings.  Per 64-wide step along the contraction (= one quantization group):
 //   * one thread issues TMA loads: the activations' [128 x 64] bf16 tile (128-byte swizzle) and
-//     two [64 rows x 32 bytes] tiles of packed 4-bit codes, completing on an mbarrier;
-//   * eight warps turn the packed tile into the bf16 operand tile in shared memory, half a weight
-//     row per thread: codes -> bf16 pairs by a mask trick, then one bf16x2 fused multiply-add
+//     four [64 rows x 32 bytes] tiles of packed 4-bit codes, completing on an mbarrier;
+//   * sixteen warps turn the packed tile into the bf16 operand tile in shared memory, half a
+//     weight row per thread: codes -> bf16 pairs by a mask trick, then one bf16x2 fused multiply-add
 //     with the group's scale and bias (a single rounding of q*scale+bias), stored in the
 //     128-byte-swizzled K-major layout the MMA descriptor expects;
-//   * one thread issues four (or eight) tcgen05.mma (M=128, N=128, K=16) accumulating in TMEM, then
+//   * one thread issues four tcgen05.mma (M=128, N=256, K=16) accumulating in TMEM, then
 //     tcgen05.commit to free the stage;
 //   * four warps drain the finished accumulator from TMEM (tcgen05.ld), apply the epilogue
 //     (GeGLU to bf16 activations, or bf16 partial rows scattered to (token, rank)), while the
@@ -234,7 +235,7 @@ constexpr int kSortTokens = 256;  // tokens per permute block
 
 struct RowTile {
     uint32_t rowStart;  // first row in expert-sorted order
-    uint32_t rows;      // 1..256 (one or two 128-row MMA tiles)
+    uint32_t rows;      // 1..128
     uint32_t expert;
     uint32_t pad;
 };
@@ -256,7 +257,7 @@ k_route_count(const uint32_t *ids, int T, int K, int E, uint32_t *blockCounts) {
 }
 
 // Pass 2 (one block): exclusive prefix of every expert's counts over the blocks, expert offsets,
-// and the list of row tiles (up to 256 rows of one expert each), experts ascending.
+// and the list of row tiles (up to 128 rows of one expert each), experts ascending.
 // counts[0] = row tiles, counts[1] = pairs, counts[2] = experts with at least one pair.
 __global__ void __launch_bounds__(256)
 k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, RowTile *tiles,
@@ -281,7 +282,7 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
             offset[i] = run;
             tileBase[i] = tilesRun;
             run += total[i];
-            tilesRun += (total[i] + 255u) / 256u;
+            tilesRun += (total[i] + 127u) / 128u;
             active += total[i] ? 1u : 0u;
         }
         offset[E] = run;
@@ -296,8 +297,8 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
     if (e == 0) expertOffsets[E] = offset[E];
     if (e < E) {
         const uint32_t n = total[e];
-        for (uint32_t i = 0, tix = tileBase[e]; i < n; i += 256, ++tix)
-            if (tix < maxTiles) tiles[tix] = RowTile{offset[e] + i, min(256u, n - i), (uint32_t)e, 0u};
+        for (uint32_t i = 0, tix = tileBase[e]; i < n; i += 128, ++tix)
+            if (tix < maxTiles) tiles[tix] = RowTile{offset[e] + i, min(128u, n - i), (uint32_t)e, 0u};
     }
 }
 
@@ -326,9 +327,9 @@ k_route_scatter(const uint32_t *ids, const uint16_t *weights, int T, int K, int 
 
 // Row tiles of a dense problem: T rows of one "expert" (the shared FFN).
 __global__ void k_dense_tiles(int T, RowTile *tiles, uint32_t *counts) {
-    const int n = (T + 255) / 256;
+    const int n = (T + 127) / 128;
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        tiles[i] = RowTile{(uint32_t)i * 256u, (uint32_t)min(256, T - i * 256), 0u, 0u};
+        tiles[i] = RowTile{(uint32_t)i * 128u, (uint32_t)min(128, T - i * 128), 0u, 0u};
     if (threadIdx.x == 0) {
         counts[0] = (uint32_t)n;
         counts[1] = (uint32_t)T;
@@ -390,14 +391,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the limit ran out or another thread of the CTA gave up; the
-// caller leaves its loop.  `abortFlag` lives in shared memory.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+// caller leaves its loop.  `abortFlag` lives in shared memory.  kSleep: pause between polls, for
+// the warps whose polling would otherwise take issue slots from the dequantizing warps.
+template <bool kSleep>
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (kSleep) __nanosleep(40);
         if ((i & 255u) == 255u && *abortFlag) return false;
     }
     *abortFlag = 1u;
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+    return mbar_wait_impl<false>(bar, parity, abortFlag);
+}
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+    return mbar_wait_impl<true>(bar, parity, abortFlag);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
@@ -472,22 +482,22 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smemAddr) {
     desc |= (uint64_t)2 << 61;
     return desc;
 }
-// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 128, N = 128.
-constexpr uint32_t kIdescBf16M128N128 =
-    (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 128, N = 256.
+constexpr uint32_t kIdescBf16M128N256 =
+    (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
 
 // ---- grouped INT4 GEMM ---------------------------------------------------------------------
 
-constexpr int kTileM = 128, kTileN = 128, kTileK = 64;
+constexpr int kTileM = 128, kTileN = 256, kTileK = 64;
 constexpr int kStagesLoad = 3;   // activations + packed codes (TMA destinations)
 constexpr int kStagesB = 3;      // dequantized bf16 operand tiles
-constexpr int kDequantWarps = 8;
-// warp 0 TMA, warp 1 MMA, warps 2-9 dequant, warps 10-13 epilogue (TMEM lane quarter = warp & 3)
+constexpr int kDequantWarps = 16;  // half an operand row (32 codes per step) per thread
+// warp 0 TMA, warp 1 MMA, warps 2-17 dequant, warps 18-21 epilogue (TMEM lane quarter = warp & 3)
 constexpr int kGemmThreads = (2 + kDequantWarps + 4) * 32;
-constexpr uint32_t kTileABytes = kTileM * kTileK * 2;     // 16384 per 128-row tile; a stage holds two
-constexpr uint32_t kTilePackedBytes = kTileN * kTileK / 2;  // 4096
-constexpr uint32_t kTileBBytes = kTileN * kTileK * 2;     // 16384
-constexpr uint32_t kTmemCols = 512;  // two accumulator buffers x two 128-row tiles x 128 columns
+constexpr uint32_t kTileABytes = kTileM * kTileK * 2;       // 16384
+constexpr uint32_t kTilePackedBytes = kTileN * kTileK / 2;  // 8192: four [64 rows x 32 bytes] boxes
+constexpr uint32_t kTileBBytes = kTileN * kTileK * 2;       // 32768
+constexpr uint32_t kTmemCols = 512;  // two accumulator buffers x 256 columns
 
 enum GemmMode : int { kModeGateUp = 0, kModeDown = 1 };
 
@@ -498,7 +508,7 @@ struct GemmArgs {
     uint32_t biasOff[2];
     uint32_t K;                // contraction length (multiple of 64)
     uint32_t N;                // outputs per row: F (gate/up) or D (down)
-    uint32_t nTiles;           // column tiles: ceil(N/64) for gate/up, ceil(N/128) for down
+    uint32_t nTiles;           // column tiles: ceil(N/128) for gate/up, ceil(N/256) for down
     const RowTile *tiles;
     const uint32_t *counts;    // counts[0] = row tiles
     uint16_t *out;             // gate/up: activations [row][N]; down: output rows [*][N]
@@ -522,13 +532,13 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const uint32_t base = (rawBase + 1023u) & ~1023u;
     const uint32_t groupsK = args.K / kTileK;
 
-    // carve-up: A stages (two 128-row tiles each), B stages (all 1024-aligned), packed stages, scales
+    // carve-up: B stages and A stages (1024-aligned), packed stages, then the unit's scales
     uint32_t aAddr[kStagesLoad], pAddr[kStagesLoad], bAddr[kStagesB];
     uint32_t cursor = base;
-    for (int s = 0; s < kStagesLoad; ++s, cursor += 2 * kTileABytes) aAddr[s] = cursor;
     for (int s = 0; s < kStagesB; ++s, cursor += kTileBBytes) bAddr[s] = cursor;
+    for (int s = 0; s < kStagesLoad; ++s, cursor += kTileABytes) aAddr[s] = cursor;
     for (int s = 0; s < kStagesLoad; ++s, cursor += kTilePackedBytes) pAddr[s] = cursor;
-    uint8_t *scalesPtr = gemmSmemRaw + (cursor - rawBase);  // [128 rows][groupsK][2] bf16
+    uint8_t *scalesPtr = gemmSmemRaw + (cursor - rawBase);  // [256 rows][groupsK][2] bf16
 
     const uint32_t barBase = smem_u32(barriers);
     auto barLoadFull = [&](int s) { return barBase + 8u * (uint32_t)s; };
@@ -568,6 +578,8 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
 
     const uint32_t rowTiles = args.counts[0];
     const uint32_t units = rowTiles * args.nTiles;
+    // operand rows 0..127 | 128..255 of a unit: gate | up rows [128 nt, +128) for the gate/up GEMM,
+    // matrix rows [256 nt, +256) for the down GEMM; loaded as four boxes of 64 rows
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -578,23 +590,21 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 const RowTile tile = args.tiles[u / args.nTiles];
                 const uint32_t nt = u % args.nTiles;
                 const int row0 = (int)tile.rowStart;
-                const uint32_t mTiles = tile.rows > 128u ? 2u : 1u;
-                const int wRow0 = MODE == kModeGateUp ? (int)nt * 64 : (int)nt * 128;
-                const int wRow1 = MODE == kModeGateUp ? (int)nt * 64 : (int)nt * 128 + 64;
                 for (uint32_t g = 0; g < groupsK; ++g) {
-                    if (!mbar_wait(barLoadEmpty(stage), phase ^ 1u, &abortFlag)) {
+                    if (!mbar_wait_idle(barLoadEmpty(stage), phase ^ 1u, &abortFlag)) {
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(barLoadFull(stage), mTiles * kTileABytes + kTilePackedBytes);
+                    mbar_expect_tx(barLoadFull(stage), kTileABytes + kTilePackedBytes);
                     tma_load_2d(aAddr[stage], &mapA, (int)(g * kTileK), row0, barLoadFull(stage));
-                    if (mTiles == 2)
-                        tma_load_2d(aAddr[stage] + kTileABytes, &mapA, (int)(g * kTileK), row0 + 128,
-                                    barLoadFull(stage));
-                    tma_load_3d(pAddr[stage], &mapW0, (int)(g * (kTileK / 2)), wRow0, (int)tile.expert,
-                                barLoadFull(stage));
-                    tma_load_3d(pAddr[stage] + kTilePackedBytes / 2, &mapW1, (int)(g * (kTileK / 2)),
-                                wRow1, (int)tile.expert, barLoadFull(stage));
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const CUtensorMap *map = (MODE == kModeGateUp && q >= 2) ? &mapW1 : &mapW0;
+                        const int wRow = MODE == kModeGateUp ? (int)nt * 128 + (q & 1) * 64
+                                                             : (int)nt * 256 + q * 64;
+                        tma_load_3d(pAddr[stage] + (uint32_t)q * (kTilePackedBytes / 4), map,
+                                    (int)(g * (kTileK / 2)), wRow, (int)tile.expert, barLoadFull(stage));
+                    }
                     if (++stage == kStagesLoad) {
                         stage = 0;
                         phase ^= 1u;
@@ -608,11 +618,9 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
             uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                const RowTile tile = args.tiles[u / args.nTiles];
-                const uint32_t mTiles = tile.rows > 128u ? 2u : 1u;
-                if (!mbar_wait(barAccEmpty(acc), accPhase ^ 1u, &abortFlag)) break;
+                if (!mbar_wait_idle(barAccEmpty(acc), accPhase ^ 1u, &abortFlag)) break;
                 tc_fence_after();
-                const uint32_t tmemD = tmemBase + acc * 2u * (uint32_t)kTileN;
+                const uint32_t tmemD = tmemBase + acc * (uint32_t)kTileN;
                 for (uint32_t g = 0; g < groupsK; ++g) {
                     if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
                         !mbar_wait(barBFull(bStage), bPhase, &abortFlag)) {
@@ -620,15 +628,13 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         break;
                     }
                     tc_fence_after();
+                    const uint64_t descA = umma_desc_sw128(aAddr[stage]);
                     const uint64_t descB = umma_desc_sw128(bAddr[bStage]);
 #pragma unroll
                     for (uint32_t kk = 0; kk < kTileK / 16; ++kk) {
                         // 32 bytes (>> 4 = 2) further along K for every 16-element slice
-                        for (uint32_t m = 0; m < mTiles; ++m) {
-                            const uint64_t descA = umma_desc_sw128(aAddr[stage] + m * kTileABytes);
-                            tc_mma_bf16(tmemD + m * (uint32_t)kTileN, descA + 2u * kk, descB + 2u * kk,
-                                        kIdescBf16M128N128, (g | kk) != 0u ? 1u : 0u);
-                        }
+                        tc_mma_bf16(tmemD, descA + 2u * kk, descB + 2u * kk, kIdescBf16M128N256,
+                                    (g | kk) != 0u ? 1u : 0u);
                     }
                     tc_commit(barLoadEmpty(stage));
                     tc_commit(barBEmpty(bStage));
@@ -650,20 +656,24 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
             }
         }
     } else if (warp < 2 + kDequantWarps) {
-        // ---------------- dequantizers: half an operand row (32 codes) per thread ----------------
+        // ---------------- dequantizers: half an operand row (32 codes per step) per thread ----------------
         const int idx = (warp - 2) * 32 + lane;
-        const int r = idx >> 1;        // operand row 0..127
-        const int half = idx & 1;      // which 16 bytes of the row's 32 packed bytes
-        const int matrix = MODE == kModeGateUp ? (r >> 6) : 0;
+        const int r = idx >> 1;    // operand row 0..255
+        const int half = idx & 1;  // which 16 of the row's 32 packed bytes
+        const int matrix = MODE == kModeGateUp ? (r >> 7) : 0;
         uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0;
         uint16_t *rowScales = reinterpret_cast<uint16_t *>(scalesPtr) + (size_t)r * groupsK * 2;
+        const uint32_t dstRowOff = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+        uint32_t dstChunk[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dstChunk[j] = dstRowOff + (((uint32_t)(half * 4 + j) ^ (uint32_t)(r & 7)) << 4);
         bool ok = true;
         for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
             const RowTile tile = args.tiles[u / args.nTiles];
             const uint32_t nt = u % args.nTiles;
-            const uint32_t wRow = MODE == kModeGateUp ? nt * 64 + (uint32_t)(r & 63) : nt * 128 + (uint32_t)r;
+            const uint32_t wRow = MODE == kModeGateUp ? nt * 128 + (uint32_t)(r & 127) : nt * 256 + (uint32_t)r;
             const uint8_t *blob = args.blobBase + (size_t)tile.expert * args.expertStride;
-            // the row's two threads each fetch half of its scale/bias pairs
+            // the row's two threads each fetch half of its scale/bias pairs into shared memory
             __syncwarp();
             if (wRow < args.N) {
                 const uint16_t *sg = reinterpret_cast<const uint16_t *>(blob + args.scaleOff[matrix]) +
@@ -681,20 +691,23 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 }
             }
             __syncwarp();
+            uint32_t sbNext = *reinterpret_cast<const uint32_t *>(rowScales);  // scale | bias << 16
             for (uint32_t g = 0; g < groupsK; ++g) {
+                const uint32_t sb = sbNext;
+                if (g + 1 < groupsK) sbNext = *reinterpret_cast<const uint32_t *>(rowScales + 2 * (g + 1));
                 if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
                     !mbar_wait(barBEmpty(bStage), bPhase ^ 1u, &abortFlag)) {
                     ok = false;
                     break;
                 }
-                const uint32_t s16 = rowScales[2 * g], b16 = rowScales[2 * g + 1];
-                const uint32_t s2 = s16 | (s16 << 16), b2 = b16 | (b16 << 16);
-                const uint32_t src = pAddr[stage] + (uint32_t)r * 32u + (uint32_t)half * 16u;
-                const uint32_t dstRow = bAddr[bStage] + (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+                uint32_t s2, b2;
+                asm("prmt.b32 %0, %1, %1, 0x1010;" : "=r"(s2) : "r"(sb));
+                asm("prmt.b32 %0, %1, %1, 0x3232;" : "=r"(b2) : "r"(sb));
                 uint32_t w[4];
                 asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(src));
+                             : "r"(pAddr[stage] + (uint32_t)r * 32u + (uint32_t)half * 16u));
+                const uint32_t bBase = bAddr[bStage];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t o[4];
@@ -707,9 +720,7 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(v2) : "r"(q2), "r"(s2), "r"(b2));
                         o[i] = v2;
                     }
-                    const uint32_t chunk = (uint32_t)(half * 4 + j);
-                    const uint32_t dst = dstRow + ((chunk ^ (uint32_t)(r & 7)) << 4);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[0]),
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(bBase + dstChunk[j]), "r"(o[0]),
                                  "r"(o[1]), "r"(o[2]), "r"(o[3])
                                  : "memory");
                 }
@@ -736,73 +747,70 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
         for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) {
             const RowTile tile = args.tiles[u / args.nTiles];
             const uint32_t nt = u % args.nTiles;
-            const uint32_t mTiles = tile.rows > 128u ? 2u : 1u;
-            if (!mbar_wait(barAccFull(acc), accPhase, &abortFlag)) break;
+            if (!mbar_wait_idle(barAccFull(acc), accPhase, &abortFlag)) break;
             tc_fence_after();
-            for (uint32_t mt = 0; mt < mTiles; ++mt) {
-                const uint32_t m = mt * 128u + (uint32_t)(quarter * 32 + lane);  // row of the unit
-                const uint32_t taddr =
-                    tmemBase + (acc * 2u + mt) * (uint32_t)kTileN + ((uint32_t)(quarter * 32) << 16);
-                const bool rowLive = m < tile.rows;
-                if (MODE == kModeGateUp) {
-                    uint16_t *dstRow = args.out + (size_t)(tile.rowStart + m) * args.N + (size_t)nt * 64;
+            const uint32_t m = (uint32_t)(quarter * 32 + lane);  // row of the unit
+            const uint32_t taddr = tmemBase + acc * (uint32_t)kTileN + ((uint32_t)(quarter * 32) << 16);
+            const bool rowLive = m < tile.rows;
+            if (MODE == kModeGateUp) {
+                // accumulator columns 0..127 = gate rows, 128..255 = up rows of features [128 nt, +128)
+                uint16_t *dstRow = args.out + (size_t)(tile.rowStart + m) * args.N + (size_t)nt * 128;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 128; c0 += 32) {
+                    uint32_t gr[32], ur[32];
+                    tc_load_32cols(taddr + (uint32_t)c0, gr);
+                    tc_load_32cols(taddr + 128u + (uint32_t)c0, ur);
+                    tc_wait_ld();
+                    uint32_t packed[16];
 #pragma unroll
-                    for (int c0 = 0; c0 < 64; c0 += 32) {
-                        uint32_t gr[32], ur[32];
-                        tc_load_32cols(taddr + (uint32_t)c0, gr);
-                        tc_load_32cols(taddr + 64u + (uint32_t)c0, ur);
-                        tc_wait_ld();
-                        uint32_t packed[16];
+                    for (int blk = 0; blk < 4; ++blk) {
+                        // eight activations, stored as 0,4,1,5,2,6,3,7 for the down GEMM
+                        float a[8];
 #pragma unroll
-                        for (int blk = 0; blk < 4; ++blk) {
-                            // eight activations, stored as 0,4,1,5,2,6,3,7 for the down GEMM
-                            float a[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                float g = __uint_as_float(gr[blk * 8 + i]);
-                                float uu = __uint_as_float(ur[blk * 8 + i]);
-                                if (args.roundGateUp) {
-                                    g = pf_bf2f(pf_f2bf(g));
-                                    uu = pf_bf2f(pf_f2bf(uu));
-                                }
-                                a[i] = pf_gelu_tanh(g) * uu;
+                        for (int i = 0; i < 8; ++i) {
+                            float g = __uint_as_float(gr[blk * 8 + i]);
+                            float uu = __uint_as_float(ur[blk * 8 + i]);
+                            if (args.roundGateUp) {
+                                g = pf_bf2f(pf_f2bf(g));
+                                uu = pf_bf2f(pf_f2bf(uu));
                             }
-                            packed[blk * 4 + 0] = (uint32_t)pf_f2bf(a[0]) | ((uint32_t)pf_f2bf(a[4]) << 16);
-                            packed[blk * 4 + 1] = (uint32_t)pf_f2bf(a[1]) | ((uint32_t)pf_f2bf(a[5]) << 16);
-                            packed[blk * 4 + 2] = (uint32_t)pf_f2bf(a[2]) | ((uint32_t)pf_f2bf(a[6]) << 16);
-                            packed[blk * 4 + 3] = (uint32_t)pf_f2bf(a[3]) | ((uint32_t)pf_f2bf(a[7]) << 16);
+                            a[i] = pf_gelu_tanh(g) * uu;
                         }
-                        if (rowLive && nt * 64 + (uint32_t)c0 < args.N) {
-                            uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
-#pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2],
-                                                    packed[4 * q + 3]);
-                        }
+                        packed[blk * 4 + 0] = (uint32_t)pf_f2bf(a[0]) | ((uint32_t)pf_f2bf(a[4]) << 16);
+                        packed[blk * 4 + 1] = (uint32_t)pf_f2bf(a[1]) | ((uint32_t)pf_f2bf(a[5]) << 16);
+                        packed[blk * 4 + 2] = (uint32_t)pf_f2bf(a[2]) | ((uint32_t)pf_f2bf(a[6]) << 16);
+                        packed[blk * 4 + 3] = (uint32_t)pf_f2bf(a[3]) | ((uint32_t)pf_f2bf(a[7]) << 16);
                     }
-                } else {
-                    size_t outRow = tile.rowStart + m;
-                    if (args.pairs && rowLive) {
-                        const FFTokenExpertPair p = args.pairs[tile.rowStart + m];
-                        outRow = (size_t)p.token * args.topK + p.rank;
+                    if (rowLive && nt * 128 + (uint32_t)c0 < args.N) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2],
+                                                packed[4 * q + 3]);
                     }
-                    uint16_t *dstRow = args.out + outRow * args.N + (size_t)nt * 128;
+                }
+            } else {
+                size_t outRow = tile.rowStart + m;
+                if (args.pairs && rowLive) {
+                    const FFTokenExpertPair p = args.pairs[tile.rowStart + m];
+                    outRow = (size_t)p.token * args.topK + p.rank;
+                }
+                uint16_t *dstRow = args.out + outRow * args.N + (size_t)nt * 256;
+#pragma unroll 1
+                for (int c0 = 0; c0 < 256; c0 += 32) {
+                    uint32_t vr[32];
+                    tc_load_32cols(taddr + (uint32_t)c0, vr);
+                    tc_wait_ld();
+                    if (rowLive && nt * 256 + (uint32_t)c0 < args.N) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
 #pragma unroll
-                    for (int c0 = 0; c0 < 128; c0 += 32) {
-                        uint32_t vr[32];
-                        tc_load_32cols(taddr + (uint32_t)c0, vr);
-                        tc_wait_ld();
-                        if (rowLive && nt * 128 + (uint32_t)c0 < args.N) {
-                            uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t o[4];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                uint32_t o[4];
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-                                    o[i] = (uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
-                                           ((uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
-                                dst[q] = make_uint4(o[0], o[1], o[2], o[3]);
-                            }
+                            for (int i = 0; i < 4; ++i)
+                                o[i] = (uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
+                                       ((uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
+                            dst[q] = make_uint4(o[0], o[1], o[2], o[3]);
                         }
                     }
                 }
@@ -915,7 +923,7 @@ bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error) {
 }
 
 static size_t gemm_smem_bytes(uint32_t K) {
-    return 1024 + (size_t)kStagesLoad * (2 * kTileABytes + kTilePackedBytes) + (size_t)kStagesB * kTileBBytes +
+    return 1024 + (size_t)kStagesLoad * (kTileABytes + kTilePackedBytes) + (size_t)kStagesB * kTileBBytes +
            (size_t)kTileN * (K / kTileK) * 2 * sizeof(uint16_t);
 }
 
@@ -925,7 +933,7 @@ static bool launch_gemm(FFContext *ctx, const CUtensorMap &mapA, const CUtensorM
                         cudaStream_t stream, const char **error) {
     auto kernel = k_grouped_int4_gemm<MODE>;
     const size_t smem = gemm_smem_bytes(args.K);
-    if (smem > 220 * 1024) return fail(error, "contraction length too large for the GEMM's shared memory");
+    if (smem > 226 * 1024) return fail(error, "contraction length too large for the GEMM's shared memory");
     static size_t configured[8] = {0};
     if (configured[ctx->device & 7] != smem) {
         FF_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
@@ -981,7 +989,7 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     }
     FF_CUDA_OK(cudaGetLastError(), error);
 
-    const uint32_t tileBound = pairs / 256 + (uint32_t)E;
+    const uint32_t tileBound = pairs / 128 + (uint32_t)E;
     CUtensorMap mapX, mapActs;
     if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)pairs + 256, c.d, c.d, error)) return false;
     if (!make_activation_map(&mapActs, ctx->acts, (uint64_t)pairs + 256, c.f, c.f, error)) return false;
@@ -995,7 +1003,7 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     a.biasOff[1] = L.off.upBOff;
     a.K = c.d;
     a.N = c.f;
-    a.nTiles = (c.f + 63) / 64;
+    a.nTiles = (c.f + 127) / 128;
     a.tiles = tiles;
     a.counts = ctx->unitCount;
     a.out = ctx->acts;
@@ -1012,7 +1020,7 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     b.biasOff[0] = b.biasOff[1] = L.off.downBOff;
     b.K = c.f;
     b.N = c.d;
-    b.nTiles = (c.d + 127) / 128;
+    b.nTiles = (c.d + 255) / 256;
     b.out = partials;
     b.pairs = ctx->sortedPairs;
     return launch_gemm<kModeDown>(ctx, mapActs, L.routedMap[2], L.routedMap[2], b, tileBound * b.nTiles,
@@ -1039,7 +1047,7 @@ bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
                                                             (int)c.d, ctx->xSorted);
     }
     FF_CUDA_OK(cudaGetLastError(), error);
-    const uint32_t rowTiles = (tokens + 255) / 256;
+    const uint32_t rowTiles = (tokens + 127) / 128;
     CUtensorMap mapX, mapActs;
     if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)tokens + 256, c.d, c.d, error)) return false;
     if (!make_activation_map(&mapActs, ctx->sharedActs, (uint64_t)tokens + 256, c.sharedF, c.sharedF, error))
@@ -1055,7 +1063,7 @@ bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     a.biasOff[1] = L.sharedOff.upBOff;
     a.K = c.d;
     a.N = c.sharedF;
-    a.nTiles = (c.sharedF + 63) / 64;
+    a.nTiles = (c.sharedF + 127) / 128;
     a.tiles = tiles;
     a.counts = counts;
     a.out = ctx->sharedActs;
@@ -1070,7 +1078,7 @@ bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     b.biasOff[0] = b.biasOff[1] = L.sharedOff.downBOff;
     b.K = c.sharedF;
     b.N = c.d;
-    b.nTiles = (c.d + 127) / 128;
+    b.nTiles = (c.d + 255) / 256;
     b.out = y;
     b.pairs = nullptr;
     return launch_gemm<kModeDown>(ctx, mapActs, L.sharedMap[2], L.sharedMap[2], b, rowTiles * b.nTiles,
