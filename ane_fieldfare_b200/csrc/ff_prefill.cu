@@ -49,6 +49,21 @@ __device__ __forceinline__ float pf_gelu_tanh(float x) {
     return 0.5f * x * (1.0f + tanhf(inner));
 }
 
+// Packed fp32 pairs for fma.rn.f32x2 (low half = first value).
+__device__ __forceinline__ uint64_t pf_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pf_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ void pf_unpack2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -144,29 +159,37 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
     }
     __syncwarp();
     for (int e0 = 0; e0 < E; e0 += kRouterExperts) {
-        float acc[kRouterTokens][kRouterExperts];
+        // running sums of two tokens share one packed fp32 pair (fma.rn.f32x2 = two independent fp32
+        // FMAs), so every (token, expert) chain is the scalar chain bit for bit at half the issue
+        uint64_t acc[kRouterTokens / 2][kRouterExperts];
 #pragma unroll
-        for (int tt = 0; tt < kRouterTokens; ++tt)
+        for (int tp = 0; tp < kRouterTokens / 2; ++tp)
 #pragma unroll
-            for (int ee = 0; ee < kRouterExperts; ++ee) acc[tt][ee] = 0.0f;
+            for (int ee = 0; ee < kRouterExperts; ++ee) acc[tp][ee] = 0ull;
         for (int base = 8 * lane; base < D; base += 256) {
-            float xv[kRouterTokens][8];
+            uint64_t xv[kRouterTokens / 2][8];
             uint4 sv = make_uint4(0, 0, 0, 0);
             if (scale) sv = *reinterpret_cast<const uint4 *>(scale + base);
             const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
-            for (int tt = 0; tt < kRouterTokens; ++tt) {
-                const uint4 raw = *reinterpret_cast<const uint4 *>(xs + (size_t)tt * D + base);
-                const uint32_t xx[4] = {raw.x, raw.y, raw.z, raw.w};
+            for (int tp = 0; tp < kRouterTokens / 2; ++tp) {
+                const uint4 rawA = *reinterpret_cast<const uint4 *>(xs + (size_t)(2 * tp) * D + base);
+                const uint4 rawB = *reinterpret_cast<const uint4 *>(xs + (size_t)(2 * tp + 1) * D + base);
+                const uint32_t xa[4] = {rawA.x, rawA.y, rawA.z, rawA.w};
+                const uint32_t xb[4] = {rawB.x, rawB.y, rawB.z, rawB.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    float x0 = __uint_as_float(xx[k] << 16), x1 = __uint_as_float(xx[k] & 0xFFFF0000u);
+                    float a0 = __uint_as_float(xa[k] << 16), a1 = __uint_as_float(xa[k] & 0xFFFF0000u);
+                    float b0 = __uint_as_float(xb[k] << 16), b1 = __uint_as_float(xb[k] & 0xFFFF0000u);
                     if (scale) {
-                        x0 = x0 * __uint_as_float(ss[k] << 16);
-                        x1 = x1 * __uint_as_float(ss[k] & 0xFFFF0000u);
+                        const float s0 = __uint_as_float(ss[k] << 16), s1 = __uint_as_float(ss[k] & 0xFFFF0000u);
+                        a0 = a0 * s0;
+                        a1 = a1 * s1;
+                        b0 = b0 * s0;
+                        b1 = b1 * s1;
                     }
-                    xv[tt][2 * k] = x0;
-                    xv[tt][2 * k + 1] = x1;
+                    xv[tp][2 * k] = pf_pack2(a0, b0);
+                    xv[tp][2 * k + 1] = pf_pack2(a1, b1);
                 }
             }
 #pragma unroll
@@ -177,23 +200,31 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const float w0 = __uint_as_float(ww[k] << 16), w1 = __uint_as_float(ww[k] & 0xFFFF0000u);
+                    const uint64_t w00 = pf_pack2(w0, w0), w11 = pf_pack2(w1, w1);
 #pragma unroll
-                    for (int tt = 0; tt < kRouterTokens; ++tt) {
-                        acc[tt][ee] = fmaf(w0, xv[tt][2 * k], acc[tt][ee]);
-                        acc[tt][ee] = fmaf(w1, xv[tt][2 * k + 1], acc[tt][ee]);
+                    for (int tp = 0; tp < kRouterTokens / 2; ++tp) {
+                        acc[tp][ee] = pf_fma2(w00, xv[tp][2 * k], acc[tp][ee]);
+                        acc[tp][ee] = pf_fma2(w11, xv[tp][2 * k + 1], acc[tp][ee]);
                     }
                 }
             }
         }
 #pragma unroll
-        for (int tt = 0; tt < kRouterTokens; ++tt)
+        for (int tp = 0; tp < kRouterTokens / 2; ++tp)
 #pragma unroll
             for (int ee = 0; ee < kRouterExperts; ++ee) {
-                float v = acc[tt][ee];
+                float v0, v1;
+                pf_unpack2(acc[tp][ee], v0, v1);
 #pragma unroll
-                for (int offset = 16; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
+                for (int offset = 16; offset >= 1; offset >>= 1) {
+                    v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, offset);
+                    v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, offset);
+                }
                 const int e = e0 + ee;
-                if (lane == 0 && e < E) lg[tt * kMaxExperts + e] = bias ? v + bias[e] : v;
+                if (lane == 0 && e < E) {
+                    lg[(2 * tp) * kMaxExperts + e] = bias ? v0 + bias[e] : v0;
+                    lg[(2 * tp + 1) * kMaxExperts + e] = bias ? v1 + bias[e] : v1;
+                }
             }
     }
     __syncwarp();
@@ -240,18 +271,40 @@ struct RowTile {
     uint32_t pad;
 };
 
+// Per-warp segment histogram of a block's routes: warp w owns routes [w*seg, (w+1)*seg) of the
+// block; lanes holding the same expert are grouped with match.any and the group's lowest lane adds
+// the group size.  segCount is [8 warps][E] in shared memory, zeroed by the caller.
+__device__ __forceinline__ void segment_histogram(const uint32_t *routes, int n, int seg, int E,
+                                                  uint32_t *segCount) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int begin = warp * seg, end = min(n, begin + seg);
+    for (int i0 = begin; i0 < end; i0 += 32) {
+        const int i = i0 + lane;
+        const bool valid = i < end;
+        const uint32_t e = valid ? routes[i] : 0xFFFFFFFFu;
+        const uint32_t mask = __match_any_sync(0xFFFFFFFFu, e);
+        if (valid && e < (uint32_t)E && (mask & ((1u << lane) - 1u)) == 0u)
+            segCount[warp * E + e] += (uint32_t)__popc(mask);
+        __syncwarp();
+    }
+}
+
 // Pass 1: per block of 256 tokens, how many routes name each expert.
 __global__ void __launch_bounds__(256)
 k_route_count(const uint32_t *ids, int T, int K, int E, uint32_t *blockCounts) {
     extern __shared__ uint32_t sRoutes[];
+    __shared__ uint32_t segCount[8 * kMaxExperts];
     const int t0 = blockIdx.x * kSortTokens;
     const int n = min(kSortTokens, T - t0) * K;
     for (int i = threadIdx.x; i < n; i += blockDim.x) sRoutes[i] = ids[(size_t)t0 * K + i];
+    for (int i = threadIdx.x; i < 8 * E; i += blockDim.x) segCount[i] = 0;
+    __syncthreads();
+    segment_histogram(sRoutes, n, (n + 7) / 8, E, segCount);
     __syncthreads();
     const int e = threadIdx.x;
     if (e < E) {
         uint32_t c = 0;
-        for (int i = 0; i < n; ++i) c += sRoutes[i] == (uint32_t)e ? 1u : 0u;
+        for (int w = 0; w < 8; ++w) c += segCount[w * E + e];
         blockCounts[(size_t)blockIdx.x * E + e] = c;
     }
 }
@@ -303,24 +356,50 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
 }
 
 // Pass 3: every route's position in (expert, token, rank) order; writes the sorted pair list.
+// Position = expert offset + routes to the expert in earlier blocks + in earlier warp segments of
+// this block + earlier in this warp's segment (earlier 32-route batches, then lower lanes).
 __global__ void __launch_bounds__(256)
 k_route_scatter(const uint32_t *ids, const uint16_t *weights, int T, int K, int E,
                 const uint32_t *blockCounts, const uint32_t *expertOffsets,
                 FFTokenExpertPair *sorted) {
     extern __shared__ uint32_t sRoutes[];
+    __shared__ uint32_t segCount[8 * kMaxExperts];
     const int t0 = blockIdx.x * kSortTokens;
     const int n = min(kSortTokens, T - t0) * K;
     for (int i = threadIdx.x; i < n; i += blockDim.x) sRoutes[i] = ids[(size_t)t0 * K + i];
+    for (int i = threadIdx.x; i < 8 * E; i += blockDim.x) segCount[i] = 0;
+    __syncthreads();
+    const int seg = (n + 7) / 8;
+    segment_histogram(sRoutes, n, seg, E, segCount);
     __syncthreads();
     const int e = threadIdx.x;
     if (e < E) {
-        uint32_t pos = expertOffsets[e] + blockCounts[(size_t)blockIdx.x * E + e];
-        for (int i = 0; i < n; ++i) {
-            if (sRoutes[i] == (uint32_t)e) {
-                const uint32_t token = (uint32_t)(t0 + i / K), rank = (uint32_t)(i % K);
-                const uint32_t wbits = weights ? (uint32_t)weights[(size_t)token * K + rank] : 0u;
-                sorted[pos++] = FFTokenExpertPair{token, (uint32_t)e, rank, wbits};
-            }
+        // turn the segment counts into each segment's first position for this expert
+        uint32_t run = expertOffsets[e] + blockCounts[(size_t)blockIdx.x * E + e];
+        for (int w = 0; w < 8; ++w) {
+            const uint32_t c = segCount[w * E + e];
+            segCount[w * E + e] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int begin = warp * seg, end = min(n, begin + seg);
+    for (int i0 = begin; i0 < end; i0 += 32) {
+        const int i = i0 + lane;
+        const bool valid = i < end;
+        const uint32_t ex = valid ? sRoutes[i] : 0xFFFFFFFFu;
+        const uint32_t mask = __match_any_sync(0xFFFFFFFFu, ex);
+        const bool live = valid && ex < (uint32_t)E;
+        uint32_t pos = 0;
+        if (live) pos = segCount[warp * E + ex] + (uint32_t)__popc(mask & ((1u << lane) - 1u));
+        __syncwarp();
+        if (live && (mask & ((1u << lane) - 1u)) == 0u) segCount[warp * E + ex] += (uint32_t)__popc(mask);
+        __syncwarp();
+        if (live) {
+            const uint32_t token = (uint32_t)(t0 + i / K), rank = (uint32_t)(i % K);
+            const uint32_t wbits = weights ? (uint32_t)weights[(size_t)token * K + rank] : 0u;
+            sorted[pos] = FFTokenExpertPair{token, ex, rank, wbits};
         }
     }
 }

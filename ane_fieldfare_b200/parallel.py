@@ -36,16 +36,60 @@ class DispatchPlan:
     token: torch.Tensor         # int64 [routes]: source token row, in send order
 
 
-def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int) -> DispatchPlan:
+@dataclass
+class Placement:
+    """Which rank holds each expert and under which local id.  The blob layout of a layer file is
+    not touched: a rank simply loads the blobs of its experts in `experts_of(rank)` order."""
+    rank_of: torch.Tensor   # int64 [experts]
+    local_of: torch.Tensor  # int64 [experts]
+    world: int
+
+    def experts_of(self, rank: int):
+        mine = torch.nonzero(self.rank_of == rank).reshape(-1)
+        return mine[torch.argsort(self.local_of[mine])].tolist()
+
+
+def contiguous_placement(experts: int, world: int) -> Placement:
+    """Expert e on rank e // (experts/world): contiguous blocks."""
+    per = experts // world
+    e = torch.arange(experts, dtype=torch.int64)
+    return Placement(torch.div(e, per, rounding_mode="floor"), e % per, world)
+
+
+def balanced_placement(load, world: int) -> Placement:
+    """Equal expert counts per rank, expected load balanced: experts in decreasing load go to the
+    least-loaded rank that still has room (longest-processing-time greedy).  `load` is the expected
+    share of routes per expert (e.g. the router's prior); ties keep expert order."""
+    load = [float(v) for v in load]
+    experts = len(load)
+    per = experts // world
+    order = sorted(range(experts), key=lambda e: (-load[e], e))
+    totals, counts = [0.0] * world, [0] * world
+    rank_of, local_of = [0] * experts, [0] * experts
+    for e in order:
+        r = min((r for r in range(world) if counts[r] < per), key=lambda r: (totals[r], r))
+        rank_of[e], local_of[e] = r, counts[r]
+        counts[r] += 1
+        totals[r] += load[e]
+    return Placement(torch.tensor(rank_of, dtype=torch.int64), torch.tensor(local_of, dtype=torch.int64), world)
+
+
+def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int,
+                  placement: Optional[Placement] = None) -> DispatchPlan:
     """Routes ordered by destination rank, (token, rank) order kept inside a destination."""
     tokens, k = ids.shape
     flat = ids.reshape(-1).to(torch.int64)
-    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
-    if tokens and (int(dest.max()) >= world or int(flat.min()) < 0):
+    if tokens and (int(flat.max()) >= experts_per_rank * world or int(flat.min()) < 0):
         raise ValueError("route expert out of range for this expert-parallel group")
+    if placement is None:
+        dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
+        local_all = flat - dest * experts_per_rank
+    else:
+        dest = placement.rank_of.to(flat.device)[flat]
+        local_all = placement.local_of.to(flat.device)[flat]
     order = torch.argsort(dest, stable=True)
     send_counts = torch.bincount(dest, minlength=world).to(torch.int64)
-    local = (flat[order] - dest[order] * experts_per_rank).to(torch.int32)
+    local = local_all[order].to(torch.int32)
     return DispatchPlan(order, send_counts, local, torch.div(order, k, rounding_mode="floor"))
 
 
@@ -72,8 +116,10 @@ class ExpertParallelMoE:
     library on GPUs (see `cuda_layer_fns`), plain torch functions in the CPU tests."""
 
     def __init__(self, experts: int, top_k: int, router_fn: Callable, shared_fn: Callable,
-                 experts_fn: Callable, reduce_fn: Callable, group=None):
+                 experts_fn: Callable, reduce_fn: Callable, group=None,
+                 placement: Optional[Placement] = None):
         self.group = group
+        self.placement = placement
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         if experts % self.world:
@@ -86,7 +132,7 @@ class ExpertParallelMoE:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         ids, weights = self.router_fn(x)
-        plan = dispatch_plan(ids, self.experts_per_rank, self.world)
+        plan = dispatch_plan(ids, self.experts_per_rank, self.world, self.placement)
         recv_counts = exchange_counts(plan.send_counts.to(x.device), self.group)
         send_list = plan.send_counts.tolist()
         recv_list = recv_counts.tolist()

@@ -121,6 +121,7 @@ def dist_env():
 def cpu_decode_baseline(layer_host, tokens_bits, seconds_budget=12.0, max_steps=None):
     """Times the CPU oracle's decode layer (all host threads) on a bounded sample of steps."""
     from oracle import oracle as O
+    O.set_num_threads(os.cpu_count() or 1)
     ld = O.LayerData(experts=layer_host.blobs, stride=layer_host.layout.stride,
                      off=layer_host.layout.offsets.as_tuple(), E=E, D=D, F=F, K=K,
                      shared=layer_host.sharedBlob, shared_off=layer_host.sharedLayout.offsets.as_tuple(),
@@ -221,18 +222,23 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
                                   maxTokens=tokens_local, device=local_rank)
     local = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=1,
                                    maxTokens=capacity, device=local_rank)
+    placements = []
     for i, L in enumerate(host_layers):
+        prior = synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}")
         home.loadShared(i, *L.shared_projections())
-        home.loadRouter(i, L.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}"))
+        home.loadRouter(i, L.routerW, logitBias=prior)
+        # experts go to ranks so that the router's prior is balanced (the blob layout is untouched)
+        placements.append(parallel.balanced_placement(np.exp(prior.astype(np.float64)), world))
     for slot in range(layers):
         L = host_layers[slot % len(host_layers)]
-        local.loadLayer(slot, L.blobs[rank * epr:(rank + 1) * epr], L.layout.stride, L.layout.offsets,
+        mine = placements[slot % len(host_layers)].experts_of(rank)
+        local.loadLayer(slot, np.ascontiguousarray(L.blobs[mine]), L.layout.stride, L.layout.offsets,
                         expertCount=epr)
     blocks = []
     for slot in range(layers):
         # the home context is indexed by the distinct layer, the expert context by the stack's slot
         fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
-        blocks.append(parallel.ExpertParallelMoE(E, K, *fns))
+        blocks.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot % len(host_layers)]))
     x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
 
     def run_stack():
@@ -271,7 +277,8 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             "tflops": tf, "frac_of_measured_bf16_per_gpu": tf / (peak["tflops"] * world),
             "last_layer_rows_received_per_rank": [int(r.item()) for r in rows],
             "output_finite": finite, "device_error_flag": int(err),
-            "collective": "NCCL all_to_all_single (dispatch + combine per layer)"}
+            "collective": "NCCL all_to_all_single (dispatch + combine per layer)",
+            "placement": "experts assigned to ranks by greedy balancing of the router prior"}
 
 
 def run_ours(args):

@@ -651,6 +651,14 @@ void ffo_moe_layer(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t mod
     free(ids);
 }
 
+void ffo_set_num_threads(int32_t n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int32_t ffo_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

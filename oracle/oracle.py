@@ -231,5 +231,9 @@ def moe_layer(layer: LayerData, x_bits, mode):
     return y, y32, ids, w
 
 
+def set_num_threads(n: int) -> None:
+    lib().ffo_set_num_threads(c_int32(int(n)))
+
+
 def num_threads() -> int:
     return int(lib().ffo_num_threads())

@@ -8,7 +8,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from ane_fieldfare_b200.parallel import ExpertParallelMoE, dispatch_plan
+from ane_fieldfare_b200.parallel import (ExpertParallelMoE, balanced_placement, contiguous_placement,
+                                         dispatch_plan)
 
 E, K, D, T_PER_RANK = 8, 3, 16, 11
 
@@ -25,6 +26,26 @@ def test_dispatch_plan_orders_routes_by_destination_keeping_token_order():
     assert empty.send_counts.tolist() == [0, 0] and empty.order.numel() == 0
     with pytest.raises(ValueError, match="out of range"):
         dispatch_plan(torch.tensor([[9, 1, 2]], dtype=torch.int32), 4, 2)
+
+
+def test_balanced_placement_evens_out_a_skewed_prior():
+    load = [1.0 / (r + 1) ** 1.1 for r in range(16)]  # Zipf over experts 0..15
+    naive = contiguous_placement(16, 4)
+    smart = balanced_placement(load, 4)
+    def rank_loads(p):
+        return [sum(load[e] for e in p.experts_of(r)) for r in range(4)]
+    assert all(len(smart.experts_of(r)) == 4 for r in range(4))
+    assert sorted(e for r in range(4) for e in smart.experts_of(r)) == list(range(16))
+    assert max(rank_loads(smart)) < 0.6 * max(rank_loads(naive))
+    # local ids follow the order in which a rank loads its blobs
+    for r in range(4):
+        assert [int(smart.local_of[e]) for e in smart.experts_of(r)] == [0, 1, 2, 3]
+    ids = torch.tensor([[0, 5, 9]], dtype=torch.int32)
+    plan = dispatch_plan(ids, 4, 4, smart)
+    assert sorted(plan.order.tolist()) == [0, 1, 2]
+    for pos, route in enumerate(plan.order.tolist()):
+        e = int(ids.reshape(-1)[route])
+        assert int(plan.local_expert[pos]) == int(smart.local_of[e])
 
 
 def _tokens(rank):
