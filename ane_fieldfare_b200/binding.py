@@ -66,6 +66,7 @@ SIGNATURES = {
     "ff_set_tracing": (None, [c_void_p, c_bool]),
     "ff_get_trace": (c_uint32, [c_void_p, POINTER(FFTraceEntry), c_uint32]),
     "ff_decode_phase_times": (c_bool, [c_void_p, POINTER(ctypes.c_double), _ERR]),
+    "ff_decode_warp_times": (c_bool, [c_void_p, POINTER(ctypes.c_double), _ERR]),
     "ff_load_layer": (c_bool, [c_void_p, c_uint32, _P, c_uint64, c_uint32, c_uint64,
                                POINTER(MoEExpertOffsets), _ERR]),
     "ff_load_shared": (c_bool, [c_void_p, c_uint32, POINTER(FFProjection), POINTER(FFProjection),

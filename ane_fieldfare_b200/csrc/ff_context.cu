@@ -141,8 +141,8 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     ok = ok && dev_alloc(ctx, &ctx->yDev, T * c.d, error);
     ok = ok && dev_alloc(ctx, &ctx->errorFlag, 4, error);
     if (ok) ok = cudaMemset(ctx->errorFlag, 0, 16) == cudaSuccess;
-    ok = ok && dev_alloc(ctx, &ctx->phaseStamps, 8, error);
-    if (ok) ok = cudaMemset(ctx->phaseStamps, 0, 64) == cudaSuccess;
+    ok = ok && dev_alloc(ctx, &ctx->phaseStamps, kPhaseStampSlots, error);
+    if (ok) ok = cudaMemset(ctx->phaseStamps, 0, kPhaseStampSlots * 8) == cudaSuccess;
     ok = ok && dev_alloc(ctx, &ctx->gridBarrier, 4, error);
     if (ok) ok = cudaMemset(ctx->gridBarrier, 0, 16) == cudaSuccess;
     if (ok && T > (size_t)kMaxGemvRows) {
@@ -202,6 +202,19 @@ bool ff_decode_phase_times(FFContext *ctx, double *microseconds, const char **er
     unsigned long long t[8] = {0};
     FF_CUDA_OK(cudaMemcpy(t, ctx->phaseStamps, sizeof(t), cudaMemcpyDeviceToHost), error);
     for (int i = 0; i < 6; ++i) microseconds[i] = t[i + 1] >= t[i] ? (double)(t[i + 1] - t[i]) * 1e-3 : 0.0;
+    return true;
+}
+
+bool ff_decode_warp_times(FFContext *ctx, double *microseconds, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !microseconds) return fail(error, "null argument");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    FF_CUDA_OK(cudaDeviceSynchronize(), error);
+    std::vector<unsigned long long> t(kPhaseStampSlots, 0);
+    FF_CUDA_OK(cudaMemcpy(t.data(), ctx->phaseStamps, t.size() * sizeof(t[0]), cudaMemcpyDeviceToHost), error);
+    for (int i = 8; i < kPhaseStampSlots; ++i)
+        microseconds[i - 8] = t[i] >= t[0] && t[0] ? (double)(t[i] - t[0]) * 1e-3 : -1.0;
+    FF_CUDA_OK(cudaMemset(ctx->phaseStamps + 8, 0, (kPhaseStampSlots - 8) * sizeof(t[0])), error);
     return true;
 }
 

@@ -122,6 +122,17 @@ __device__ __forceinline__ void stamp(const DecodeArgs &a, int slot) {
     }
 }
 
+// Per-warp timestamps of two CTAs (first and last) when tracing: slot 8 + ((cta01 * 3 + phase) * 16 +
+// warp) * 3 + which, which = 0 requests issued, 1 data arrived, 2 rows done.
+__device__ __forceinline__ void warp_stamp(const DecodeArgs &a, int phase, int which) {
+    if (a.stamps && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && (threadIdx.x & 31) == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        const int c = blockIdx.x == 0 ? 0 : 1;
+        a.stamps[8 + ((c * 3 + phase) * 16 + (threadIdx.x >> 5)) * 3 + which] = t;
+    }
+}
+
 // ---- per-warp staging of weight rows in shared memory ----------------------------------------
 // A warp task covers four consecutive weight rows.  All of their bytes are requested at once with
 // asynchronous copies (16 bytes per lane and request, contiguous across the warp; 8 bytes for the
@@ -226,6 +237,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     int tSD = warp >= kBigWarps ? (warp - kBigWarps) * G + cta : 0x7FFFFFFF;
     if (tSD < tasksSharedDown) issue_shared_down(tSD);
     if (a.prefetch && a.shared) prefetch_region(a.shared, a.sharedBytes, cursor);
+    warp_stamp(a, 0, 0);
     __syncthreads();
     uint32_t sense = sSense;
     {
@@ -235,6 +247,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     for (; tA < tasksSharedGU; tA += 4 * G) {
         cp_async_wait_all();
         __syncwarp();
+        warp_stamp(a, 0, 1);
         const int row = tA * 4 + r4;
         const uint8_t *g0 = mySlot, *u0 = mySlot + imD.bytes();
         float g[1], u[1];
@@ -250,6 +263,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     for (; eA < E; eA += (kBigWarps - 4) * G) {
         cp_async_wait_all();
         __syncwarp();
+        warp_stamp(a, 0, 1);
         const uint16_t *wr = reinterpret_cast<const uint16_t *>(mySlot);
         float acc = 0.0f;
         for (int base = 8 * lane; base < D; base += 256) {
@@ -278,6 +292,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
         const int next = eA + (kBigWarps - 4) * G;
         if (next < E) warp_copy16(mySlot, reinterpret_cast<const uint8_t *>(a.routerW + (size_t)next * D), D * 2);
     }
+    warp_stamp(a, 0, 2);
     stamp(a, 1);
     if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) {
         cp_async_wait_all();
@@ -351,6 +366,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     };
     int tB = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
     if (tB < tasksRouted) stage_routed(tB);
+    warp_stamp(a, 1, 0);
     if (a.prefetch) {
         // the down projections of the chosen experts go to L2 now and are read in phase C
         for (int k = 0; k < K; ++k) {
@@ -367,6 +383,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     for (; tB < tasksRouted; tB += kBigWarps * G) {
         cp_async_wait_all();
         __syncwarp();
+        warp_stamp(a, 1, 1);
         const int slot = tB / perSlot;
         const int row = (tB - slot * perSlot) * 4 + r4;
         const uint8_t *g0 = mySlot, *u0 = mySlot + imD.bytes();
@@ -383,6 +400,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     for (; tSD < tasksSharedDown; tSD += (kFusedWarps - kBigWarps) * G) {
         cp_async_wait_all();
         __syncwarp();
+        warp_stamp(a, 1, 1);
         const int row = tSD * 4 + r4;
         float v[1], unused[1];
         row_dot<1, false, true>(mySlot, reinterpret_cast<const uint16_t *>(mySlot + imFs.wBytes),
@@ -393,6 +411,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
         const int next = tSD + (kFusedWarps - kBigWarps) * G;
         if (next < tasksSharedDown) issue_shared_down(next);
     }
+    warp_stamp(a, 1, 2);
     stamp(a, 4);
     if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) {
         cp_async_wait_all();
@@ -413,6 +432,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
         };
         int tC = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
         if (tC < tasksDown) stage_down(tC);
+        warp_stamp(a, 2, 0);
         const int strideF = staged_stride(F);
         float *asum = as + 8 * strideF;
         stage_rows(a.acts, (uint32_t)F, sRowIdx, K, F, as, asum);
@@ -420,6 +440,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
         for (; tC < tasksDown; tC += kBigWarps * G) {
             cp_async_wait_all();
             __syncwarp();
+            warp_stamp(a, 2, 1);
             const int row = tC * 4 + r4;
             const bool live = row < D;
             float acc = (live && res) ? bf2f(res[row]) : 0.0f;
@@ -438,6 +459,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
             if (tC + kBigWarps * G < tasksDown) stage_down(tC + kBigWarps * G);
         }
     }
+    warp_stamp(a, 2, 2);
     stamp(a, 6);
 }
 

@@ -79,6 +79,8 @@ struct LayerStore {
 
 }  // namespace ff
 
+constexpr int kPhaseStampSlots = 8 + 2 * 3 * 16 * 3;
+
 struct FFContext {
     int device = 0;
     int smCount = 0;
@@ -110,7 +112,7 @@ struct FFContext {
     uint32_t *unitCount = nullptr;          // [4]
     uint32_t maxUnits = 0;
     uint32_t *errorFlag = nullptr;          // device: set by a kernel that gave up waiting
-    unsigned long long *phaseStamps = nullptr;  // device: 8 timestamps of the fused decode kernel
+    unsigned long long *phaseStamps = nullptr;  // device: 8 phase + 288 per-warp timestamps of the fused decode kernel
     uint32_t *gridBarrier = nullptr;        // device: [arrivals, sense] of the fused decode kernel
     CUtensorMap *mapScratch = nullptr;
 

@@ -114,6 +114,13 @@ class HotpathContext:
         call("ff_decode_phase_times", self.handle, out)
         return list(out)
 
+    def decodeWarpTimes(self):
+        """[cta 0/1][phase A/B/C][warp 0..15][issued, arrived, done] microseconds since kernel start of
+        the last traced one-token launch; -1 where a warp had no work."""
+        out = (ctypes.c_double * 288)()
+        call("ff_decode_warp_times", self.handle, out)
+        return np.array(list(out)).reshape(2, 3, 16, 3)
+
     # -- resident weights (replaces MappedExpertLayer / Model.routedExpertViews) ---------------
 
     def loadLayer(self, layer: int, blobs: np.ndarray, expertStride: int,

@@ -37,6 +37,9 @@ ACT_IO_BYTES = 2 * D * 2                                         # x in, y out
 DECODE_BYTES = K * EXPERT_BYTES + SHARED_BYTES + ROUTER_BYTES + ACT_IO_BYTES  # 37 531 648
 DECODE_FLOPS = 2 * (K * 3 * F * D + 3 * FS * D + E * D)
 KERNELS_PER_DECODE_STEP = 1
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch, from an ncu capture of this
+# kernel on these shapes (bytes)
+NCU_DECODE_TRAFFIC_BYTES = 37_712_384
 ROOT_SEED = 0xF1E1DFA2E
 
 
@@ -394,7 +397,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": D * 2, "steps": e2e_steps},
         "gpu_launches": steps * KERNELS_PER_DECODE_STEP,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC_BYTES,
                      "peak_source": peaks["source"], "frac_of_nominal_8TBs": achieved / 8000.0,
                      "kernel": "the whole decode step (all kernels of one token through one layer)",
                      "algorithmic_bytes_per_step": DECODE_BYTES},

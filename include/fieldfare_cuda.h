@@ -120,6 +120,13 @@ uint32_t ff_get_trace(FFContext *ctx, FFTraceEntry *entries, uint32_t capacity);
  * (Runtime/Inference/RealForwardRunner.swift:2146-2150). */
 bool ff_decode_phase_times(FFContext *ctx, double *microseconds, const char **error);
 
+/* Finer view of the same launch: 288 values [cta][phase][warp][event] for the first and the last
+ * CTA (cta 0/1), phases A/B/C, 16 warps, event 0 = the warp's copy requests issued, 1 = its data
+ * arrived, 2 = its rows done; microseconds since the first CTA started, -1 where a warp had no
+ * work.  Diagnostic, no reference counterpart. */
+#define FF_DECODE_WARP_TIME_COUNT 288
+bool ff_decode_warp_times(FFContext *ctx, double *microseconds, const char **error);
+
 /* ---- HBM-resident weights ---------------------------------------------------------------- */
 
 /* Copies one layer file's bytes (`packed_experts/layer_%02d.bin`: expertCount blobs,
