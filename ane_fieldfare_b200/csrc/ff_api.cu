@@ -153,6 +153,10 @@ bool ff_shared_ffn(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t x
     if (!begin(ctx, layer, stream, error, &c)) return false;
     if (!check_rows(ctx, x, xStride, tokens, error)) return false;
     if (!y) return fail(error, "output pointer is null");
+    // one row goes through the decode kernel (shared part only), so that the layer call and the
+    // operators called one by one give the same bits
+    if (tokens == 1 && ((uintptr_t)x & 15) == 0)
+        return launch_decode_fused(ctx, *c.L, x, nullptr, nullptr, true, false, nullptr, y, c.stream, error);
     if (tokens <= (uint32_t)kMaxGemvRows)
         return launch_shared_small(ctx, *c.L, x, xStride, tokens, y, c.stream, error);
     return launch_prefill_shared(ctx, *c.L, x, xStride, tokens, y, c.stream, error);

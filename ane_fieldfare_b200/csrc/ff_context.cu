@@ -286,7 +286,8 @@ bool ff_load_layer(FFContext *ctx, uint32_t layer, const void *hostBytes, uint64
         L.experts = nullptr;
     }
     const uint64_t total = (uint64_t)expertCount * expertStride;
-    FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&L.experts), total), error);
+    // 256 bytes of slack: the decode kernel fetches 16-byte aligned windows around scale rows
+    FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&L.experts), total + 256), error);
     FF_CUDA_OK(cudaMemset(L.experts, 0, total), error);
     FF_CUDA_OK(cudaMemcpy(L.experts, hostBytes, std::min(byteCount, total), cudaMemcpyHostToDevice),
                error);

@@ -4,20 +4,31 @@
 // The step streams 37.5 MB of weights once; at B200's HBM rate that is under 6 us, so separate
 // kernels (launch gaps, cold starts) cannot come near the roofline.  Here one CTA per SM runs
 // three phases separated by two grid-wide barriers:
-//   A  L2 prefetch of everything known up front (router, shared FFN); router logits (one warp per
-//      expert) and the shared gate/up/GeGLU rows;
-//   B  every CTA ranks the 128 logits itself (top-8, softmax, gain), issues L2 prefetches for
-//      the eight chosen experts' blobs, then routed gate/up/GeGLU rows and the shared down rows;
-//   C  routed down rows, warp = slot, fixed-order combine onto the shared output (or the
-//      caller's residual).
-// The prefetches (one bulk L2 prefetch instruction per 8 KiB) keep HBM busy independently of how
-// many loads the compute warps have in flight; the compute loads then hit L2.
-// Row arithmetic is row_dot<1, ...> of the generic GEMV kernels, so the result is bitwise the one
-// the split operators (ff_router_topk, ff_shared_ffn, ff_moe_decode) produce.
+//   A  router logits (one warp per expert) and the shared gate/up/GeGLU rows; the shared down
+//      rows are already requested;
+//   B  every CTA ranks the 128 logits itself (top-8, softmax, gain), then routed gate/up/GeGLU
+//      rows and the shared down rows; the routed down rows are requested before the barrier;
+//   C  routed down rows and the fixed-order combine onto the shared output (or the caller's
+//      residual).
 //
-// The grid barrier is a sense-reversing counter in global memory; cooperative launch guarantees
-// that all CTAs are resident.  Its spin is bounded: on running out it raises the context's error
-// flag and the CTA returns.
+// Weight rows reach the SM as bulk asynchronous copies (cp.async.bulk, one per row piece,
+// completion counted on a per-warp mbarrier) into a per-warp shared-memory slot: a warp has its
+// whole task in flight after one instruction per lane.
+//
+// Row arithmetic runs on the tensor cores without dequantizing: a warp task is a tile of 16 weight
+// rows; per group of 64 codes the packed nibbles are turned into the bf16 values 16+q with two
+// integer instructions per pair (the code goes into the mantissa of 16.0) and multiplied with the
+// bf16 input by mma.sync m16n8k16 (fp32 accumulate; the product of a 5-bit integer and a bf16 is
+// exact).  The group's sum is then scaled:
+//     acc += scale * sum((16+q) x) + (bias - 16 scale) * sum(x).
+// The eight columns of the MMA are one input row for the gate/up and shared rows, and the eight
+// routed experts' activations for the routed down rows (a tile = two output rows of all eight
+// experts).  Long rows are split along K between the warps of a pair (or triple) of one CTA and
+// added in a fixed order, so results do not depend on scheduling.
+//
+// The grid barrier is an arrival counter in global memory; cooperative launch guarantees that all
+// CTAs are resident.  Every spin (grid barrier, copy completion) is bounded: on running
+// out it raises the context's error flag and carries on, so the launch always ends.
 //
 // Reference kernels replaced (paths inside the reference project):
 //   Sources/ANEFieldfareHotpath/Metal/MoE/moe.metal:65-120,242-319,500-517,548-570,597-638
@@ -32,7 +43,10 @@ namespace ff {
 
 constexpr int kFusedThreads = 512;
 constexpr int kFusedWarps = kFusedThreads / 32;
+constexpr int kBigWarps = 10;      // warps 0..9: gate/up pairs and the routed down tiles
+constexpr int kSharedGuWarps = 4;  // warps 0..3 take the shared gate/up tiles in phase A
 constexpr uint32_t kBarrierSpinLimit = 1u << 24;
+constexpr uint32_t kCopySpinLimit = 1u << 22;
 
 struct DecodeArgs {
     const uint16_t *routerW, *routerScale, *gain;
@@ -42,7 +56,6 @@ struct DecodeArgs {
     FFExpertOffsets off;
     const uint8_t *shared;  // null: no shared FFN, `residual` is added instead
     FFExpertOffsets sharedOff;
-    uint64_t sharedBytes;
     const uint16_t *x;
     const uint16_t *residual;
     const uint32_t *idsIn;  // non-null: routes are given, the router is skipped
@@ -51,19 +64,15 @@ struct DecodeArgs {
     uint32_t *ids;
     uint16_t *weights;
     uint16_t *acts, *sharedActs, *h1, *y;
-    uint32_t *barrier;  // [0] arrivals, [1] sense
+    unsigned long long *barrier;  // arrival counter of the grid barrier
     uint32_t *errorFlag;
-    unsigned long long *stamps;  // null, or 8 slots for block 0's phase timestamps (ns)
-    int E, D, F, Fs, K;
-    int prefetch;  // 0: no L2 prefetch (diagnostic)
-    uint32_t slotsOffset, bigBytes, smallBytes;  // shared-memory staging slots (fused_layout)
+    unsigned long long *stamps;  // null, or the phase / per-warp timestamp slots (ns)
+    int E, D, F, Fs, K;          // K = 0: shared FFN only (y receives its output)
+    int prefetch;                // bit 0: L2 prefetch of the chosen experts' down projections
+    // shared-memory carve-up (fused_layout)
+    uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
+    uint32_t strideGU, strideSD, strideRD, actStride, winBytes;
 };
-
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 // Bulk L2 prefetch of [p, p + bytes); bytes a multiple of 16, p 16-byte aligned.
 __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) {
@@ -85,33 +94,39 @@ __device__ __forceinline__ void prefetch_region(const uint8_t *base, uint64_t by
     cursor += pieces;
 }
 
-// Sense-reversing grid barrier with a bounded spin.  Returns false when the wait ran out.
-__device__ bool grid_barrier(uint32_t *bar, uint32_t &sense, uint32_t *errorFlag, volatile uint32_t *sOk) {
+// Grid barrier on one 64-bit arrival counter that only grows: an arrival's old value tells its
+// generation, the target is the next multiple of the grid size, and waiting is polling the counter
+// itself — no reset, no host-side state, one round trip after the last arrival.  Split in two so
+// that work that does not depend on the other CTAs (requests for the next phase) sits between
+// arriving and waiting.  Thread 0 arrives and waits; the spin is bounded.
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long grid_arrive(unsigned long long *count) {
     __syncthreads();
+    unsigned long long target = 0;
     if (threadIdx.x == 0) {
-        sense ^= 1u;
         __threadfence();
-        const uint32_t arrived = atomicAdd(&bar[0], 1u);
-        uint32_t ok = 1u;
-        if (arrived == gridDim.x - 1) {
-            bar[0] = 0u;
-            __threadfence();
-            atomicExch(&bar[1], sense);
-        } else {
-            uint32_t spins = 0;
-            while (ld_acquire_u32(&bar[1]) != sense) {
-                if (++spins > kBarrierSpinLimit) {
-                    atomicExch(errorFlag, 9u);
-                    ok = 0u;
-                    break;
-                }
+        const unsigned long long old = atomicAdd(count, 1ull);
+        target = (old / gridDim.x + 1ull) * gridDim.x;
+    }
+    return target;
+}
+__device__ __forceinline__ void grid_wait(const unsigned long long *count, unsigned long long target,
+                                          uint32_t *errorFlag) {
+    if (threadIdx.x == 0) {
+        uint32_t spins = 0;
+        while (ld_acquire_u64(count) < target) {
+            if (++spins > kBarrierSpinLimit) {
+                atomicExch(errorFlag, 9u);
+                break;
             }
         }
         __threadfence();
-        *sOk = ok;
     }
     __syncthreads();
-    return *sOk != 0u;
 }
 
 __device__ __forceinline__ void stamp(const DecodeArgs &a, int slot) {
@@ -133,136 +148,340 @@ __device__ __forceinline__ void warp_stamp(const DecodeArgs &a, int phase, int w
     }
 }
 
-// ---- per-warp staging of weight rows in shared memory ----------------------------------------
-// A warp task covers four consecutive weight rows.  All of their bytes are requested at once with
-// asynchronous copies (16 bytes per lane and request, contiguous across the warp; 8 bytes for the
-// scale/bias runs whose start is only 8-byte aligned), so a warp has its whole task in flight
-// instead of a few loads; the arithmetic then reads the rows from shared memory.
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async8(uint32_t dst, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-    asm volatile("cp.async.wait_all;" ::: "memory");
-}
 __device__ __forceinline__ uint32_t sm_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void warp_copy16(uint8_t *dst, const uint8_t *src, int bytes) {
-    const int lane = threadIdx.x & 31;
-    for (int off = lane * 16; off < bytes; off += 512) cp_async16(sm_addr(dst + off), src + off);
-}
-__device__ __forceinline__ void warp_copy8(uint8_t *dst, const uint8_t *src, int bytes) {
-    const int lane = threadIdx.x & 31;
-    for (int off = lane * 8; off < bytes; off += 256) cp_async8(sm_addr(dst + off), src + off);
-}
-__host__ __device__ inline int pad16(int bytes) { return (bytes + 15) & ~15; }
+// ---- bulk copies into a warp's slot, completion on the warp's mbarrier -------------------------
 
-// Shared-memory image of up to four rows of one matrix: packed codes, then scales, then biases.
-struct RowsImage {
-    int wBytes, sBytes;  // per image: 4 * cols/2 and pad16(4 * groups * 2)
-    __host__ __device__ int bytes() const { return wBytes + 2 * sBytes; }
-};
-__host__ __device__ inline RowsImage rows_image(int cols) {
-    return RowsImage{4 * (cols >> 1), pad16(4 * (cols >> 6) * 2)};
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// 16-byte aligned source and destination, size a multiple of 16.
+__device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+// Orders this warp's earlier shared-memory reads of its slot before the next bulk copies into it.
+__device__ __forceinline__ void slot_release() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+}
+// Bounded wait for the warp's copies; flips the parity.  On running out the error flag is raised
+// and the warp carries on (its rows are then wrong, the launch still ends).
+__device__ __forceinline__ void slot_wait(uint32_t bar, uint32_t &parity, uint32_t *errorFlag) {
+    bool done = false;
+    for (uint32_t i = 0; i < kCopySpinLimit && !done; ++i) done = bar_try_wait(bar, parity);
+    if (!done && (threadIdx.x & 31) == 0) atomicExch(errorFlag, 10u);
+    parity ^= 1u;
+    __syncwarp();
 }
 
-// Requests rows [row0, row0+4) (clipped to `rows`) of the matrix at (w, s, b) into `dst`.
-__device__ __forceinline__ void stage_matrix_rows(uint8_t *dst, const RowsImage &im, const uint8_t *w,
-                                                  const uint8_t *s, const uint8_t *b, int row0, int rows,
-                                                  int cols) {
-    const int n = min(4, rows - row0);
-    if (n <= 0) return;
-    const int groups = cols >> 6;
-    warp_copy16(dst, w + (size_t)row0 * (cols >> 1), n * (cols >> 1));
-    warp_copy8(dst + im.wBytes, s + (size_t)row0 * groups * 2, n * groups * 2);
-    warp_copy8(dst + im.wBytes + im.sBytes, b + (size_t)row0 * groups * 2, n * groups * 2);
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-constexpr int kBigWarps = 10;  // warps with a large staging slot (gate/up pairs, down x 8 slots)
+// ---- tensor-core row arithmetic on packed codes ------------------------------------------------
+
+// Codes i and i+4 of a word (already shifted so that they sit at bits 3..6 of each half) as the
+// bf16 pair (16+q_i, 16+q_{i+4}): (s & 0x00780078) | 0x41804180.
+__device__ __forceinline__ uint32_t code_pair(uint32_t shifted) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(shifted), "r"(0x00780078u), "r"(0x41804180u));
+    return r;
+}
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// N consecutive groups of 64 codes of a 16-row tile against the (up to eight) input columns.
+//   lo / hi: this thread's eight packed bytes of tile rows g and g+8 (g = lane / 4) for the first
+//            group: bytes [8 t, 8 t + 8) of the group's 32, t = lane % 4; next group 32 bytes on;
+//   xg:      this thread's 32 bytes of input column lane / 4: elements [16 t, 16 t + 16) of the
+//            group, every aligned run of eight stored in the order 0,4,1,5,2,6,3,7; next group 128
+//            bytes on.
+// Word j of the eight bytes feeds MMAs 2j and 2j+1; MMA 2j+h multiplies codes (2h, 2h+4 | 2h+1,
+// 2h+5) of the word with input register pair h of the run — the same elements, whatever position
+// the MMA gives them.  d[u]: group u's sums for rows g (d[u][0], d[u][1]) and g+8 (d[u][2],
+// d[u][3]), columns 2t and 2t+1.  The N accumulator chains are independent, so their MMAs overlap.
+template <int N>
+__device__ __forceinline__ void groups_mma(const uint8_t *lo, const uint8_t *hi, const uint8_t *xg, float (&d)[N][4]) {
+    uint2 wl[N], wh[N];
+    uint4 x0[N], x1[N];
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+        wl[u] = *reinterpret_cast<const uint2 *>(lo + 32 * u);
+        wh[u] = *reinterpret_cast<const uint2 *>(hi + 32 * u);
+        x0[u] = *reinterpret_cast<const uint4 *>(xg + 128 * u);
+        x1[u] = *reinterpret_cast<const uint4 *>(xg + 128 * u + 16);
+        d[u][0] = d[u][1] = d[u][2] = d[u][3] = 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < N; ++u)
+        mma_16816(d[u], code_pair(wl[u].x << 3), code_pair(wh[u].x << 3), code_pair(wl[u].x >> 1),
+                  code_pair(wh[u].x >> 1), x0[u].x, x0[u].y);
+#pragma unroll
+    for (int u = 0; u < N; ++u)
+        mma_16816(d[u], code_pair(wl[u].x >> 5), code_pair(wh[u].x >> 5), code_pair(wl[u].x >> 9),
+                  code_pair(wh[u].x >> 9), x0[u].z, x0[u].w);
+#pragma unroll
+    for (int u = 0; u < N; ++u)
+        mma_16816(d[u], code_pair(wl[u].y << 3), code_pair(wh[u].y << 3), code_pair(wl[u].y >> 1),
+                  code_pair(wh[u].y >> 1), x1[u].x, x1[u].y);
+#pragma unroll
+    for (int u = 0; u < N; ++u)
+        mma_16816(d[u], code_pair(wl[u].y >> 5), code_pair(wh[u].y >> 5), code_pair(wl[u].y >> 9),
+                  code_pair(wh[u].y >> 9), x1[u].z, x1[u].w);
+}
+
+// acc += scale * sum((16+q) x) + (bias - 16 scale) * sum(x)
+__device__ __forceinline__ float group_scale(float acc, uint16_t scale, uint16_t bias, float dsum, float xsum) {
+    const float s = bf2f(scale);
+    acc = fmaf(s, dsum, acc);
+    return fmaf(fmaf(-16.0f, s, bf2f(bias)), xsum, acc);
+}
+
+// `n` consecutive groups of a 16-row tile: acc0 / acc1 = this thread's sums for tile rows g and
+// g+8.  s0/b0 and s1/b1: the two rows' scales and biases, xs: the input's group sums, all starting
+// at the first group.  `odd` picks MMA column 2t+1 instead of 2t.  Groups are taken in ascending
+// order whatever the batching, so the result does not depend on it.  Shared by every phase.
+__device__ __noinline__ void tile_rows(const uint8_t *lo, const uint8_t *hi, const uint8_t *xg, const uint16_t *s0,
+                                       const uint16_t *b0, const uint16_t *s1, const uint16_t *b1, const float *xs,
+                                       int n, bool odd, float &acc0, float &acc1) {
+    float v0 = 0.0f, v1 = 0.0f;
+    int i = 0;
+#pragma unroll 1
+    for (; i + 4 <= n; i += 4) {
+        float d[4][4];
+        groups_mma<4>(lo + 32 * i, hi + 32 * i, xg + 128 * i, d);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            v0 = group_scale(v0, s0[i + u], b0[i + u], odd ? d[u][1] : d[u][0], xs[i + u]);
+            v1 = group_scale(v1, s1[i + u], b1[i + u], odd ? d[u][3] : d[u][2], xs[i + u]);
+        }
+    }
+    if (i + 2 <= n) {
+        float d[2][4];
+        groups_mma<2>(lo + 32 * i, hi + 32 * i, xg + 128 * i, d);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            v0 = group_scale(v0, s0[i + u], b0[i + u], odd ? d[u][1] : d[u][0], xs[i + u]);
+            v1 = group_scale(v1, s1[i + u], b1[i + u], odd ? d[u][3] : d[u][2], xs[i + u]);
+        }
+        i += 2;
+    }
+    if (i < n) {
+        float d[1][4];
+        groups_mma<1>(lo + 32 * i, hi + 32 * i, xg + 128 * i, d);
+        v0 = group_scale(v0, s0[i], b0[i], odd ? d[0][1] : d[0][0], xs[i]);
+        v1 = group_scale(v1, s1[i], b1[i], odd ? d[0][3] : d[0][2], xs[i]);
+    }
+    acc0 = v0;
+    acc1 = v1;
+}
+
+// Copies `rows` bf16 rows of `n` values (n a multiple of 64, rows contiguous at the source,
+// `dstStride` bytes apart in shared memory) with every aligned run of eight stored in the order
+// 0,4,1,5,2,6,3,7, then the fp32 sum of each group of 64 (sums[row * n/64 + group]).  All threads
+// of the CTA take part; ends with a CTA barrier.
+__device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n, uint8_t *dst, uint32_t dstStride,
+                                            float *sums) {
+    const int runsPerRow = n >> 3, runs = rows * runsPerRow;
+    for (int i = threadIdx.x; i < runs; i += blockDim.x) {
+        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(src) + i);
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410);
+        o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410);
+        o.w = __byte_perm(v.y, v.w, 0x7632);
+        const int r = i / runsPerRow;
+        *reinterpret_cast<uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16) = o;
+    }
+    __syncthreads();
+    // eight lanes per group: each sums one run of eight in stored order, then a fixed butterfly;
+    // the loop bound is the same for all lanes of a warp
+    for (int base = (threadIdx.x >> 5) << 5; base < runs; base += blockDim.x) {
+        const int i = base + (threadIdx.x & 31);
+        float s = 0.0f;
+        if (i < runs) {
+            const int r = i / runsPerRow;
+            const uint4 v = *reinterpret_cast<const uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16);
+            s = __uint_as_float(v.x << 16);
+            s += __uint_as_float(v.x & 0xFFFF0000u);
+            s += __uint_as_float(v.y << 16);
+            s += __uint_as_float(v.y & 0xFFFF0000u);
+            s += __uint_as_float(v.z << 16);
+            s += __uint_as_float(v.z & 0xFFFF0000u);
+            s += __uint_as_float(v.w << 16);
+            s += __uint_as_float(v.w & 0xFFFF0000u);
+        }
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+        if (i < runs && (i & 7) == 0) sums[i >> 3] = s;
+    }
+    __syncthreads();
+}
+
+__host__ __device__ inline uint32_t pad16u(uint32_t bytes) { return (bytes + 15u) & ~15u; }
+// Row-piece stride in a slot: at least `bytes`, a multiple of 16, and 32 or 96 modulo 128 so that
+// the four tile rows a half-warp reads with 64-bit loads fall into different bank octets.
+__host__ __device__ inline uint32_t piece_stride(uint32_t bytes) {
+    uint32_t s = pad16u(bytes);
+    while ((s & 127u) != 32u && (s & 127u) != 96u) s += 16u;
+    return s;
+}
+// Groups [begin, end) of part p when `groups` are split into `parts` runs of (almost) equal length.
+__host__ __device__ inline void part_range(int groups, int parts, int p, int &begin, int &end) {
+    const int per = (groups + parts - 1) / parts;
+    begin = min(groups, p * per);
+    end = min(groups, begin + per);
+}
 
 __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeArgs a) {
-    const int kSelZero[1] = {0};
-    extern __shared__ __align__(16) uint8_t smemRaw[];
+    extern __shared__ __align__(128) uint8_t smemRaw[];
     __shared__ float sLogits[kMaxExperts];
     __shared__ uint32_t sIds[8];
     __shared__ float sWeights[8];
     __shared__ float sScore[8];
-    __shared__ uint32_t sRowIdx[8];
-    __shared__ volatile uint32_t sOk;
-    __shared__ uint32_t sSense;
+    __shared__ __align__(8) uint64_t sCopyBar[kFusedWarps];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = (int)gridDim.x, cta = (int)blockIdx.x;
     const int D = a.D, F = a.F, Fs = a.Fs, K = a.K, E = a.E;
-    const int j = lane & 7, r4 = lane >> 3;
+    const int g = lane >> 2, t = lane & 3;
+    const int groupsD = D >> 6, groupsF = F >> 6, groupsFs = Fs >> 6;
 
-    // shared memory: x (fp32, staged order) | region for the shared / routed activations |
-    // kBigWarps big staging slots | small staging slots for the remaining warps
-    float *xs = reinterpret_cast<float *>(smemRaw);
-    float *xsum = xs + staged_stride(D);
-    float *region = xsum + (D >> 5);
+    // shared memory: x (bf16, run-permuted) | its group sums | region for the shared / routed
+    // activations | K-split partial sums | kBigWarps big slots | small slots for the other warps
+    uint8_t *xPerm = smemRaw;
+    float *xSum = reinterpret_cast<float *>(smemRaw + D * 2);
+    uint8_t *region = smemRaw + a.regionOffset;
+    float *partial = reinterpret_cast<float *>(smemRaw + a.partialOffset);  // [warp][16]
     uint8_t *slots = smemRaw + a.slotsOffset;
     uint8_t *mySlot = warp < kBigWarps ? slots + (size_t)warp * a.bigBytes
                                         : slots + (size_t)kBigWarps * a.bigBytes + (size_t)(warp - kBigWarps) * a.smallBytes;
-    const RowsImage imD = rows_image(D), imF = rows_image(F), imFs = rows_image(Fs);
+    const uint32_t slotAddr = sm_addr(mySlot);
+    const uint32_t myBar = sm_addr(&sCopyBar[warp]);
+    uint32_t parity = 0;
 
-    if (threadIdx.x == 0) sSense = ld_acquire_u32(&a.barrier[1]);
-    if (threadIdx.x < 8) sRowIdx[threadIdx.x] = threadIdx.x;
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < kFusedWarps; ++w) bar_init(sm_addr(&sCopyBar[w]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
     uint32_t cursor = 0;
     stamp(a, 0);
 
-    // ---------------- phase A: router logits, shared gate/up/GeGLU ----------------
     const uint8_t *sh = a.shared;
-    const int tasksSharedGU = a.shared ? (Fs + 3) / 4 : 0;
-    const int tasksSharedDown = a.shared ? (D + 3) / 4 : 0;
-    // requests first: shared gate/up rows (warps 0..3), router rows (warps 4..9), and already the
-    // shared down rows of phase B (warps 10..15): none of them depends on the routing
-    auto issue_shared_gu = [&](int t) {
-        stage_matrix_rows(mySlot, imD, sh + a.sharedOff.gateWOff, sh + a.sharedOff.gateSOff,
-                          sh + a.sharedOff.gateBOff, t * 4, Fs, D);
-        stage_matrix_rows(mySlot + imD.bytes(), imD, sh + a.sharedOff.upWOff, sh + a.sharedOff.upSOff,
-                          sh + a.sharedOff.upBOff, t * 4, Fs, D);
+    const int tilesSGU = sh ? Fs >> 3 : 0;  // 8 gate + 8 up rows per tile, two K halves
+    const int tilesSD = sh ? D >> 4 : 0;    // 16 down rows per tile, three K parts
+
+    // Requests of a gate/up tile half: 16 row pieces, then the eight rows' scales and biases of both
+    // matrices over the full K (contiguous runs).  Lane l issues copy l.
+    auto issue_gate_up = [&](const uint8_t *blob, const FFExpertOffsets &off, int tile, int half) {
+        int gb, ge;
+        part_range(groupsD, 2, half, gb, ge);
+        const uint32_t piece = (uint32_t)(ge - gb) * 32u, sb = (uint32_t)groupsD * 16u;
+        if (lane == 0) bar_expect(myBar, 16u * piece + 4u * sb);
+        __syncwarp();
+        if (lane < 16) {
+            const int row = tile * 8 + (lane & 7);
+            const uint8_t *w = blob + (lane < 8 ? off.gateWOff : off.upWOff) + (size_t)row * (D >> 1) + gb * 32;
+            if (piece) bulk_copy(slotAddr + (uint32_t)lane * a.strideGU, w, piece, myBar);
+        } else if (lane < 20) {
+            const uint32_t which = (uint32_t)lane - 16u;
+            const uint32_t src = which == 0 ? off.gateSOff : which == 1 ? off.gateBOff : which == 2 ? off.upSOff : off.upBOff;
+            bulk_copy(slotAddr + 16u * a.strideGU + which * sb, blob + src + (size_t)tile * sb, sb, myBar);
+        }
     };
-    auto issue_shared_down = [&](int t) {
-        stage_matrix_rows(mySlot, imFs, sh + a.sharedOff.downWOff, sh + a.sharedOff.downSOff,
-                          sh + a.sharedOff.downBOff, t * 4, D, Fs);
+    // Gate/up tile half -> this thread's partial sums of gate row tile*8+g and up row tile*8+g.
+    auto compute_gate_up = [&](int half, const uint8_t *xp, const float *xs, float &gate, float &up) {
+        int gb, ge;
+        part_range(groupsD, 2, half, gb, ge);
+        const uint8_t *lo = mySlot + (size_t)g * a.strideGU + 8 * t;
+        const uint8_t *hi = mySlot + (size_t)(g + 8) * a.strideGU + 8 * t;
+        const uint16_t *sc = reinterpret_cast<const uint16_t *>(mySlot + 16u * a.strideGU);
+        const uint16_t *gS = sc + g * groupsD, *gB = gS + 8 * groupsD, *uS = gB + 8 * groupsD, *uB = uS + 8 * groupsD;
+        tile_rows(lo, hi, xp + gb * 128 + t * 32, gS + gb, gB + gb, uS + gb, uB + gb, xs + gb, ge - gb, false, gate, up);
     };
-    int tA = warp < 4 ? warp * G + cta : 0x7FFFFFFF;
-    if (tA < tasksSharedGU) issue_shared_gu(tA);
-    int eA = (!a.idsIn && warp >= 4 && warp < kBigWarps) ? (warp - 4) * G + cta : 0x7FFFFFFF;
-    if (eA < E) warp_copy16(mySlot, reinterpret_cast<const uint8_t *>(a.routerW + (size_t)eA * D), D * 2);
-    int tSD = warp >= kBigWarps ? (warp - kBigWarps) * G + cta : 0x7FFFFFFF;
-    if (tSD < tasksSharedDown) issue_shared_down(tSD);
-    if (a.prefetch && a.shared) prefetch_region(a.shared, a.sharedBytes, cursor);
+    auto issue_shared_down = [&](int tile, int part) {
+        int gb, ge;
+        part_range(groupsFs, 3, part, gb, ge);
+        const uint32_t piece = (uint32_t)(ge - gb) * 32u, sb = (uint32_t)groupsFs * 32u;
+        if (lane == 0) bar_expect(myBar, 16u * piece + 2u * sb);
+        __syncwarp();
+        if (lane < 16) {
+            const uint8_t *w = sh + a.sharedOff.downWOff + (size_t)(tile * 16 + lane) * (Fs >> 1) + gb * 32;
+            if (piece) bulk_copy(slotAddr + (uint32_t)lane * a.strideSD, w, piece, myBar);
+        } else if (lane < 18) {
+            const uint32_t which = (uint32_t)lane - 16u;
+            bulk_copy(slotAddr + 16u * a.strideSD + which * sb,
+                      sh + (which ? a.sharedOff.downBOff : a.sharedOff.downSOff) + (size_t)tile * sb, sb, myBar);
+        }
+    };
+
+    // ---------------- phase A: router logits, shared gate/up/GeGLU ----------------
+    int tA = warp < kSharedGuWarps ? (warp >> 1) * G + cta : 0x7FFFFFFF;
+    if (tA < tilesSGU) issue_gate_up(sh, a.sharedOff, tA, warp & 1);
+    int eA = (!a.idsIn && K > 0 && warp >= kSharedGuWarps && warp < kBigWarps) ? (warp - kSharedGuWarps) * G + cta
+                                                                             : 0x7FFFFFFF;
+    if (eA < E) {
+        if (lane == 0) {
+            bar_expect(myBar, (uint32_t)D * 2u);
+            bulk_copy(slotAddr, a.routerW + (size_t)eA * D, (uint32_t)D * 2u, myBar);
+        }
+        __syncwarp();
+    }
+    const int triple = warp >= kBigWarps ? (warp - kBigWarps) / 3 : 0;
+    const int part3 = warp >= kBigWarps ? (warp - kBigWarps) % 3 : 0;
+    int tSD = warp >= kBigWarps ? triple * G + cta : 0x7FFFFFFF;
+    if (tSD < tilesSD) issue_shared_down(tSD, part3);
     warp_stamp(a, 0, 0);
-    __syncthreads();
-    uint32_t sense = sSense;
-    {
-        const uint32_t zero = 0;
-        stage_rows(a.x, (uint32_t)D, &zero, 1, D, xs, xsum);
-    }
-    for (; tA < tasksSharedGU; tA += 4 * G) {
-        cp_async_wait_all();
-        __syncwarp();
+    stage_input(a.x, 1, D, xPerm, 0, xSum);
+    for (; tA < tilesSGU; tA += (kSharedGuWarps / 2) * G) {
+        slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
-        const int row = tA * 4 + r4;
-        const uint8_t *g0 = mySlot, *u0 = mySlot + imD.bytes();
-        float g[1], u[1];
-        row_dot<1, true, true>(g0, reinterpret_cast<const uint16_t *>(g0 + imD.wBytes),
-                               reinterpret_cast<const uint16_t *>(g0 + imD.wBytes + imD.sBytes), u0,
-                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes),
-                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes + imD.sBytes), r4, D, row < Fs,
-                               xs, xsum, kSelZero, g, u);
-        if (row < Fs && j == 0) a.sharedActs[row] = f2bf(gelu_tanh(bf16_round(g[0])) * bf16_round(u[0]));
-        __syncwarp();
-        if (tA + 4 * G < tasksSharedGU) issue_shared_gu(tA + 4 * G);
+        float gate, up;
+        compute_gate_up(warp & 1, xPerm, xSum, gate, up);
+        slot_release();
+        const int next = tA + (kSharedGuWarps / 2) * G;
+        if (next < tilesSGU) issue_gate_up(sh, a.sharedOff, next, warp & 1);
+        float *mine = partial + warp * 16;
+        if ((warp & 1) && t == 0) {
+            mine[g] = gate;
+            mine[8 + g] = up;
+        }
+        named_barrier(1 + (warp >> 1), 64);
+        if (!(warp & 1) && t == 0) {
+            gate += mine[16 + g];
+            up += mine[16 + 8 + g];
+            a.sharedActs[tA * 8 + g] = f2bf(gelu_tanh(bf16_round(gate)) * bf16_round(up));
+        }
+        named_barrier(1 + (warp >> 1), 64);
     }
-    for (; eA < E; eA += (kBigWarps - 4) * G) {
-        cp_async_wait_all();
-        __syncwarp();
+    for (; eA < E; eA += (kBigWarps - kSharedGuWarps) * G) {
+        slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
         const uint16_t *wr = reinterpret_cast<const uint16_t *>(mySlot);
         float acc = 0.0f;
@@ -288,86 +507,85 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
 #pragma unroll
         for (int offset = 16; offset >= 1; offset >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
         if (lane == 0) a.logits[eA] = a.logitBias ? acc + a.logitBias[eA] : acc;
+        slot_release();
+        const int next = eA + (kBigWarps - kSharedGuWarps) * G;
+        if (next < E && lane == 0) {
+            bar_expect(myBar, (uint32_t)D * 2u);
+            bulk_copy(slotAddr, a.routerW + (size_t)next * D, (uint32_t)D * 2u, myBar);
+        }
         __syncwarp();
-        const int next = eA + (kBigWarps - 4) * G;
-        if (next < E) warp_copy16(mySlot, reinterpret_cast<const uint8_t *>(a.routerW + (size_t)next * D), D * 2);
     }
     warp_stamp(a, 0, 2);
     stamp(a, 1);
-    if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) {
-        cp_async_wait_all();
-        return;
-    }
+    if (sh || (!a.idsIn && K > 0)) grid_wait(a.barrier, grid_arrive(a.barrier), a.errorFlag);
     stamp(a, 2);
 
     // ---------------- phase B: top-8, routed gate/up/GeGLU, shared down ----------------
-    if (!a.idsIn) {
-        for (int e = threadIdx.x; e < E; e += blockDim.x) sLogits[e] = a.logits[e];
-        if (threadIdx.x < 8) {
-            sIds[threadIdx.x] = 0u;
-            sScore[threadIdx.x] = -INFINITY;
-        }
-        __syncthreads();
-        // rank of every logit under (higher score, then lower expert id); scores of -inf or NaN
-        // are never taken — the order of the serial top-8 (moe.metal:269-303).  Four threads per
-        // expert, each counting a quarter of the competitors.
-        for (int idx = threadIdx.x; idx < 4 * ((E + 127) & ~127); idx += blockDim.x) {
-            const int e = idx >> 2, part = idx & 3;
-            const float v = e < E ? sLogits[e] : -INFINITY;
-            const int span = (E + 3) >> 2;
-            int rank = 0;
-            if (v > -INFINITY) {
-                const int end = min(E, (part + 1) * span);
-                for (int o = part * span; o < end; ++o) {
-                    const float w = sLogits[o];
-                    rank += (w > -INFINITY && (w > v || (w == v && o < e))) ? 1 : 0;
+    if (K > 0) {
+        if (!a.idsIn) {
+            for (int e = threadIdx.x; e < E; e += blockDim.x) sLogits[e] = __ldcg(a.logits + e);
+            if (threadIdx.x < 8) {
+                sIds[threadIdx.x] = 0u;
+                sScore[threadIdx.x] = -INFINITY;
+            }
+            __syncthreads();
+            // rank of every logit under (higher score, then lower expert id); scores of -inf or NaN
+            // are never taken — the order of the serial top-8 (moe.metal:269-303).  Four threads per
+            // expert, each counting a quarter of the competitors.
+            for (int idx = threadIdx.x; idx < 4 * ((E + 127) & ~127); idx += blockDim.x) {
+                const int e = idx >> 2, quarter = idx & 3;
+                const float v = e < E ? sLogits[e] : -INFINITY;
+                const int span = (E + 3) >> 2;
+                int rank = 0;
+                if (v > -INFINITY) {
+                    const int end = min(E, (quarter + 1) * span);
+                    for (int o = quarter * span; o < end; ++o) {
+                        const float w = sLogits[o];
+                        rank += (w > -INFINITY && (w > v || (w == v && o < e))) ? 1 : 0;
+                    }
+                }
+                rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
+                rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 2);
+                if (quarter == 0 && v > -INFINITY && rank < K) {
+                    sIds[rank] = (uint32_t)e;
+                    sScore[rank] = v;
                 }
             }
-            rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
-            rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 2);
-            if (part == 0 && v > -INFINITY && rank < K) {
-                sIds[rank] = (uint32_t)e;
-                sScore[rank] = v;
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float ex[8], sum = 0.0f;
-            for (int r = 0; r < K; ++r) {
-                ex[r] = expf(sScore[r] - sScore[0]);
-                sum += ex[r];
-            }
-            for (int r = 0; r < K; ++r) {
-                float w = ex[r] / sum;
-                if (a.gain) w = w * bf2f(a.gain[sIds[r]]);
-                const uint16_t wb = f2bf(w);
-                sWeights[r] = bf2f(wb);
-                if (blockIdx.x == 0) {
-                    a.ids[r] = sIds[r];
-                    a.weights[r] = wb;
+            __syncthreads();
+            if (warp == 0) {
+                // softmax over the chosen scores: exponentials in parallel, the sum in rank order
+                const float score = lane < K ? sScore[lane] : -INFINITY;
+                const float top = __shfl_sync(0xFFFFFFFFu, score, 0);
+                const float ex = lane < K ? expf(score - top) : 0.0f;
+                float sum = 0.0f;
+                for (int r = 0; r < K; ++r) sum += __shfl_sync(0xFFFFFFFFu, ex, r);
+                if (lane < K) {
+                    float w = ex / sum;
+                    if (a.gain) w = w * bf2f(a.gain[sIds[lane]]);
+                    const uint16_t wb = f2bf(w);
+                    sWeights[lane] = bf2f(wb);
+                    if (blockIdx.x == 0) {
+                        a.ids[lane] = sIds[lane];
+                        a.weights[lane] = wb;
+                    }
                 }
             }
+        } else if (threadIdx.x < K) {
+            sIds[threadIdx.x] = a.idsIn[threadIdx.x];
+            sWeights[threadIdx.x] = bf2f(a.weightsIn[threadIdx.x]);
         }
-    } else if (threadIdx.x < K) {
-        sIds[threadIdx.x] = a.idsIn[threadIdx.x];
-        sWeights[threadIdx.x] = bf2f(a.weightsIn[threadIdx.x]);
+        __syncthreads();
     }
-    __syncthreads();
     stamp(a, 3);
-    const int perSlot = (F + 3) / 4;
-    const int tasksRouted = K * perSlot;
-    auto stage_routed = [&](int t) {
-        const int slot = t / perSlot, row0 = (t - slot * perSlot) * 4;
-        const uint8_t *blob = a.experts + (size_t)sIds[slot] * a.stride;
-        stage_matrix_rows(mySlot, imD, blob + a.off.gateWOff, blob + a.off.gateSOff, blob + a.off.gateBOff,
-                          row0, F, D);
-        stage_matrix_rows(mySlot + imD.bytes(), imD, blob + a.off.upWOff, blob + a.off.upSOff,
-                          blob + a.off.upBOff, row0, F, D);
-    };
-    int tB = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
-    if (tB < tasksRouted) stage_routed(tB);
+    const int tilesF = F >> 3;
+    const int tilesRouted = K * tilesF;
+    int tB = warp < kBigWarps ? (warp >> 1) * G + cta : 0x7FFFFFFF;
+    if (tB < tilesRouted) {
+        const int slot = tB / tilesF;
+        issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, tB - slot * tilesF, warp & 1);
+    }
     warp_stamp(a, 1, 0);
-    if (a.prefetch) {
+    if ((a.prefetch & 1) && K > 0) {
         // the down projections of the chosen experts go to L2 now and are read in phase C
         for (int k = 0; k < K; ++k) {
             const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
@@ -375,88 +593,140 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
                             (uint64_t)a.off.downBOff - a.off.downWOff + (uint64_t)D * F / kGroup * 2, cursor);
         }
     }
-    float *as = region;
-    if (a.shared) {
-        const uint32_t zero = 0;
-        stage_rows(a.sharedActs, (uint32_t)Fs, &zero, 1, Fs, as, as + staged_stride(Fs));
-    }
-    for (; tB < tasksRouted; tB += kBigWarps * G) {
-        cp_async_wait_all();
-        __syncwarp();
+    uint8_t *saPerm = region;
+    float *saSum = reinterpret_cast<float *>(region + Fs * 2);
+    if (sh) stage_input(a.sharedActs, 1, Fs, saPerm, 0, saSum);
+    for (; tB < tilesRouted; tB += (kBigWarps / 2) * G) {
+        slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 1, 1);
-        const int slot = tB / perSlot;
-        const int row = (tB - slot * perSlot) * 4 + r4;
-        const uint8_t *g0 = mySlot, *u0 = mySlot + imD.bytes();
-        float g[1], u[1];
-        row_dot<1, true, true>(g0, reinterpret_cast<const uint16_t *>(g0 + imD.wBytes),
-                               reinterpret_cast<const uint16_t *>(g0 + imD.wBytes + imD.sBytes), u0,
-                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes),
-                               reinterpret_cast<const uint16_t *>(u0 + imD.wBytes + imD.sBytes), r4, D, row < F,
-                               xs, xsum, kSelZero, g, u);
-        if (row < F && j == 0) a.acts[slot * F + row] = f2bf(gelu_tanh(g[0]) * u[0]);
-        __syncwarp();
-        if (tB + kBigWarps * G < tasksRouted) stage_routed(tB + kBigWarps * G);
+        float gate, up;
+        compute_gate_up(warp & 1, xPerm, xSum, gate, up);
+        slot_release();
+        const int next = tB + (kBigWarps / 2) * G;
+        if (next < tilesRouted) {
+            const int slot = next / tilesF;
+            issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, next - slot * tilesF, warp & 1);
+        }
+        float *mine = partial + warp * 16;
+        if ((warp & 1) && t == 0) {
+            mine[g] = gate;
+            mine[8 + g] = up;
+        }
+        named_barrier(1 + (warp >> 1), 64);
+        if (!(warp & 1) && t == 0) {
+            gate += mine[16 + g];
+            up += mine[16 + 8 + g];
+            const int slot = tB / tilesF;
+            a.acts[slot * F + (tB - slot * tilesF) * 8 + g] = f2bf(gelu_tanh(gate) * up);
+        }
+        named_barrier(1 + (warp >> 1), 64);
     }
-    for (; tSD < tasksSharedDown; tSD += (kFusedWarps - kBigWarps) * G) {
-        cp_async_wait_all();
-        __syncwarp();
+    for (; tSD < tilesSD; tSD += 2 * G) {
+        slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 1, 1);
-        const int row = tSD * 4 + r4;
-        float v[1], unused[1];
-        row_dot<1, false, true>(mySlot, reinterpret_cast<const uint16_t *>(mySlot + imFs.wBytes),
-                                reinterpret_cast<const uint16_t *>(mySlot + imFs.wBytes + imFs.sBytes), nullptr,
-                                nullptr, nullptr, r4, Fs, row < D, as, as + staged_stride(Fs), kSelZero, v, unused);
-        if (row < D && j == 0) a.h1[row] = f2bf(v[0]);
-        __syncwarp();
-        const int next = tSD + (kFusedWarps - kBigWarps) * G;
-        if (next < tasksSharedDown) issue_shared_down(next);
+        int gb, ge;
+        part_range(groupsFs, 3, part3, gb, ge);
+        const uint8_t *lo = mySlot + (size_t)g * a.strideSD + 8 * t;
+        const uint8_t *hi = mySlot + (size_t)(g + 8) * a.strideSD + 8 * t;
+        const uint16_t *sS = reinterpret_cast<const uint16_t *>(mySlot + 16u * a.strideSD);
+        const uint16_t *sB = sS + 16 * groupsFs;
+        float v0, v1;
+        tile_rows(lo, hi, saPerm + gb * 128 + t * 32, sS + g * groupsFs + gb, sB + g * groupsFs + gb,
+                  sS + (g + 8) * groupsFs + gb, sB + (g + 8) * groupsFs + gb, saSum + gb, ge - gb, false, v0, v1);
+        slot_release();
+        const int next = tSD + 2 * G;
+        if (next < tilesSD) issue_shared_down(next, part3);
+        float *mine = partial + warp * 16;
+        if (part3 && t == 0) {
+            mine[g] = v0;
+            mine[8 + g] = v1;
+        }
+        named_barrier(6 + triple, 96);
+        if (!part3 && t == 0) {
+            v0 = (v0 + mine[16 + g]) + mine[32 + g];
+            v1 = (v1 + mine[16 + 8 + g]) + mine[32 + 8 + g];
+            uint16_t *out = K > 0 ? a.h1 : a.y;
+            out[tSD * 16 + g] = f2bf(v0);
+            out[tSD * 16 + 8 + g] = f2bf(v1);
+        }
+        named_barrier(6 + triple, 96);
     }
     warp_stamp(a, 1, 2);
     stamp(a, 4);
-    if (!grid_barrier(a.barrier, sense, a.errorFlag, &sOk)) {
-        cp_async_wait_all();
+    if (K == 0) {
+        stamp(a, 5);
+        stamp(a, 6);
         return;
     }
+
+    // Routed down tile: output rows 2*tile, 2*tile+1 of all eight experts.  Tile row rho*8 + e is
+    // row 2*tile+rho of expert e; lane l copies row piece l (l < 16), or the 16-byte aligned window
+    // around the two rows' scales (l even) or biases (l odd) of expert (l-16)/2.
+    const int tilesRD = D >> 1;
+    auto issue_routed_down = [&](int tile) {
+        const uint32_t piece = (uint32_t)groupsF * 32u;
+        if (lane == 0) bar_expect(myBar, 16u * piece + 16u * a.winBytes);
+        __syncwarp();
+        const int e = lane < 16 ? (lane & 7) : ((lane - 16) >> 1);
+        const uint8_t *blob = a.experts + (size_t)sIds[e < K ? e : 0] * a.stride;
+        if (lane < 16) {
+            const int row = tile * 2 + (lane >> 3);
+            bulk_copy(slotAddr + (uint32_t)lane * a.strideRD, blob + a.off.downWOff + (size_t)row * (F >> 1), piece, myBar);
+        } else {
+            const uint32_t srcOff = ((lane & 1) ? a.off.downBOff : a.off.downSOff) + (uint32_t)tile * 4u * (uint32_t)groupsF;
+            bulk_copy(slotAddr + 16u * a.strideRD + (uint32_t)(lane - 16) * a.winBytes, blob + (srcOff & ~15u), a.winBytes, myBar);
+        }
+    };
+    // the weights do not depend on the activations: request them between arriving and waiting
+    const unsigned long long target2 = grid_arrive(a.barrier);
+    int tC = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
+    if (tC < tilesRD) issue_routed_down(tC);
+    warp_stamp(a, 2, 0);
+    grid_wait(a.barrier, target2, a.errorFlag);
     stamp(a, 5);
 
     // ---------------- phase C: routed down rows and the combine ----------------
     {
-        const int tasksDown = (D + 3) / 4;
-        const int imgBytes = imF.bytes();
-        auto stage_down = [&](int t) {
-            for (int k = 0; k < K; ++k) {
-                const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
-                stage_matrix_rows(mySlot + (size_t)k * imgBytes, imF, blob + a.off.downWOff,
-                                  blob + a.off.downSOff, blob + a.off.downBOff, t * 4, D, F);
+        // activations of slot e: run-permuted bf16 at region + e * actStride, group sums behind them
+        float *actSum = reinterpret_cast<float *>(region + 8 * a.actStride);
+        if (K < 8) {
+            for (int e = K; e < 8; ++e) {
+                for (int i = threadIdx.x; i < (F >> 3); i += blockDim.x)
+                    reinterpret_cast<uint4 *>(region + (size_t)e * a.actStride)[i] = make_uint4(0, 0, 0, 0);
+                for (int i = threadIdx.x; i < groupsF; i += blockDim.x) actSum[e * groupsF + i] = 0.0f;
             }
-        };
-        int tC = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
-        if (tC < tasksDown) stage_down(tC);
-        warp_stamp(a, 2, 0);
-        const int strideF = staged_stride(F);
-        float *asum = as + 8 * strideF;
-        stage_rows(a.acts, (uint32_t)F, sRowIdx, K, F, as, asum);
+        }
+        stage_input(a.acts, K, F, region, a.actStride, actSum);
         const uint16_t *res = a.shared ? a.h1 : a.residual;
-        for (; tC < tasksDown; tC += kBigWarps * G) {
-            cp_async_wait_all();
-            __syncwarp();
+        for (; tC < tilesRD; tC += kBigWarps * G) {
+            slot_wait(myBar, parity, a.errorFlag);
             warp_stamp(a, 2, 1);
-            const int row = tC * 4 + r4;
-            const bool live = row < D;
-            float acc = (live && res) ? bf2f(res[row]) : 0.0f;
-#pragma unroll 1
+            // this thread: expert g, tile rows g (rho 0) and g+8 (rho 1); column g of the MMA is
+            // held by the lane with t == g/2 as d[g&1] (rho 0) and d[2 + (g&1)] (rho 1)
+            const uint8_t *lo = mySlot + (size_t)g * a.strideRD + 8 * t;
+            const uint8_t *hi = mySlot + (size_t)(g + 8) * a.strideRD + 8 * t;
+            const uint8_t *xe = region + (size_t)g * a.actStride + t * 32;
+            const uint32_t rowOff = (uint32_t)tC * 4u * (uint32_t)groupsF;
+            const uint8_t *win = mySlot + 16u * a.strideRD + (uint32_t)(2 * g) * a.winBytes;
+            const uint16_t *sS = reinterpret_cast<const uint16_t *>(win + ((a.off.downSOff + rowOff) & 15u));
+            const uint16_t *sB = reinterpret_cast<const uint16_t *>(win + a.winBytes + ((a.off.downBOff + rowOff) & 15u));
+            const float *xs = actSum + g * groupsF;
+            const bool odd = g & 1;
+            float v0, v1;
+            tile_rows(lo, hi, xe, sS, sB, sS + groupsF, sB + groupsF, xs, groupsF, odd, v0, v1);
+            slot_release();
+            const int next = tC + kBigWarps * G;
+            if (next < tilesRD) issue_routed_down(next);
+            // lane 0 combines row 2*tile, lane 1 row 2*tile+1, experts in rank order
+            const int row = tC * 2 + (lane & 1);
+            float acc = (lane < 2 && res) ? bf2f(__ldcg(res + row)) : 0.0f;
             for (int k = 0; k < K; ++k) {
-                const uint8_t *img = mySlot + (size_t)k * imgBytes;
-                float v[1], unused[1];
-                row_dot<1, false, true>(img, reinterpret_cast<const uint16_t *>(img + imF.wBytes),
-                                        reinterpret_cast<const uint16_t *>(img + imF.wBytes + imF.sBytes),
-                                        nullptr, nullptr, nullptr, r4, F, live, as + k * strideF,
-                                        asum + k * (F >> 5), kSelZero, v, unused);
-                acc = __fadd_rn(acc, __fmul_rn(sWeights[k], v[0]));
+                const int src = 4 * k + (k >> 1);
+                const float e0 = __shfl_sync(0xFFFFFFFFu, v0, src);
+                const float e1 = __shfl_sync(0xFFFFFFFFu, v1, src);
+                acc = __fadd_rn(acc, __fmul_rn(sWeights[k], (lane & 1) ? e1 : e0));
             }
-            if (live && j == 0) a.y[row] = f2bf(acc);
-            __syncwarp();
-            if (tC + kBigWarps * G < tasksDown) stage_down(tC + kBigWarps * G);
+            if (lane < 2) a.y[row] = f2bf(acc);
         }
     }
     warp_stamp(a, 2, 2);
@@ -464,34 +734,51 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
 }
 
 struct FusedLayout {
-    size_t slotsOffset, bigBytes, smallBytes, total;
+    uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
+    uint32_t strideGU, strideSD, strideRD, actStride, winBytes;
+    size_t total;
 };
 
 static FusedLayout fused_layout(const FFConfig &c) {
-    const size_t xPart = ((size_t)staged_stride((int)c.d) + (c.d >> 5)) * sizeof(float);
-    const size_t sharedPart =
-        c.sharedF ? ((size_t)staged_stride((int)c.sharedF) + (c.sharedF >> 5)) * sizeof(float) : 0;
-    const size_t actsPart = (size_t)8 * (staged_stride((int)c.f) + (c.f >> 5)) * sizeof(float);
+    const uint32_t D = c.d, F = c.f, Fs = c.sharedF;
+    const uint32_t groupsD = D / 64, groupsF = F / 64, groupsFs = Fs / 64;
     FusedLayout l{};
-    l.slotsOffset = (xPart + std::max(sharedPart, actsPart) + 127) & ~(size_t)127;
-    const size_t gateUp = 2 * (size_t)rows_image((int)c.d).bytes();
-    const size_t down8 = 8 * (size_t)rows_image((int)c.f).bytes();
-    l.bigBytes = (std::max({gateUp, down8, (size_t)c.d * 2}) + 127) & ~(size_t)127;
-    l.smallBytes = c.sharedF ? (((size_t)rows_image((int)c.sharedF).bytes() + 127) & ~(size_t)127) : 128;
-    l.total = l.slotsOffset + kBigWarps * l.bigBytes + (kFusedWarps - kBigWarps) * l.smallBytes;
+    l.strideGU = piece_stride(((groupsD + 1) / 2) * 32);
+    l.strideSD = Fs ? piece_stride(((groupsFs + 2) / 3) * 32) : 32;
+    l.strideRD = piece_stride(groupsF * 32);
+    l.winBytes = pad16u(4 * groupsF) + 16;
+    // per-expert activation stride: 64 modulo 128 so that the two experts a quarter-warp reads
+    // with 128-bit loads use different bank halves
+    l.actStride = F * 2;
+    while ((l.actStride & 127u) != 64u) l.actStride += 16u;
+    const uint32_t xPart = (D * 2 + groupsD * 4 + 127u) & ~127u;
+    const uint32_t sharedPart = Fs ? Fs * 2 + groupsFs * 4 : 0;
+    const uint32_t actsPart = 8 * l.actStride + 8 * groupsF * 4;
+    l.regionOffset = xPart;
+    l.partialOffset = (l.regionOffset + std::max(sharedPart, actsPart) + 127u) & ~127u;
+    l.slotsOffset = l.partialOffset + kFusedWarps * 16 * 4;
+    const uint32_t gateUp = 16 * l.strideGU + 4 * groupsD * 16;
+    const uint32_t down8 = 16 * l.strideRD + 16 * l.winBytes;
+    const uint32_t sharedDown = Fs ? 16 * l.strideSD + 2 * groupsFs * 32 : 0;
+    l.bigBytes = (std::max({gateUp, down8, D * 2}) + 127u) & ~127u;
+    l.smallBytes = (std::max(sharedDown, 128u) + 127u) & ~127u;
+    l.total = (size_t)l.slotsOffset + (size_t)kBigWarps * l.bigBytes + (size_t)(kFusedWarps - kBigWarps) * l.smallBytes;
     return l;
 }
 
 // One decode row through router (unless ids are given), routed experts and the shared FFN (or
-// the caller's residual), as one cooperative launch.
+// the caller's residual), as one cooperative launch.  routed = false: the shared FFN alone, y
+// receives its output.
 bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x, const uint32_t *idsIn,
-                         const uint16_t *weightsIn, bool withShared, const uint16_t *residual,
+                         const uint16_t *weightsIn, bool withShared, bool routed, const uint16_t *residual,
                          uint16_t *y, cudaStream_t stream, const char **error) {
     const FFConfig &c = ctx->cfg;
-    if (!L.experts) return fail(error, "layer has no resident experts");
-    if (!idsIn && !L.routerW) return fail(error, "layer has no resident router");
+    if (routed && !L.experts) return fail(error, "layer has no resident experts");
+    if (routed && !idsIn && !L.routerW) return fail(error, "layer has no resident router");
     if (withShared && !L.shared) return fail(error, "layer has no resident shared FFN");
+    if (!routed && !withShared) return fail(error, "nothing to compute");
     if (c.topK > 8) return fail(error, "decode supports at most 8 routes");
+    if (c.d % 64 || c.f % 64 || c.sharedF % 64) return fail(error, "widths must be multiples of 64");
     DecodeArgs a{};
     a.routerW = L.routerW;
     a.routerScale = L.routerScale;
@@ -502,9 +789,6 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.off = L.off;
     a.shared = withShared ? L.shared : nullptr;
     a.sharedOff = L.sharedOff;
-    uint64_t payload = 0;
-    if (c.sharedF) packed_offsets(c.d, c.sharedF, &payload);
-    a.sharedBytes = payload;
     a.x = x;
     a.residual = residual;
     a.idsIn = idsIn;
@@ -516,7 +800,7 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.sharedActs = ctx->sharedActs;
     a.h1 = ctx->h1;
     a.y = y;
-    a.barrier = ctx->gridBarrier;
+    a.barrier = reinterpret_cast<unsigned long long *>(ctx->gridBarrier);
     a.errorFlag = ctx->errorFlag;
     a.stamps = ctx->tracing ? ctx->phaseStamps : nullptr;
     static int prefetchMode = -1;
@@ -528,20 +812,29 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.E = idsIn ? (int)L.expertCount : (int)L.routerExperts;
     a.D = (int)c.d;
     a.F = (int)c.f;
-    a.Fs = (int)c.sharedF;
-    a.K = (int)c.topK;
+    a.Fs = withShared ? (int)c.sharedF : 0;
+    a.K = routed ? (int)c.topK : 0;
+    if (a.E > kMaxExperts) return fail(error, "too many experts for the decode kernel");
     const FusedLayout lay = fused_layout(c);
     const size_t smem = lay.total;
     if (smem > 227 * 1024)
         return fail(error, "model shape too large for the fused decode kernel's shared memory");
-    // the asynchronous 8-byte copies need 8-byte aligned scale/bias runs
+    // bulk copies need 16-byte aligned sources: every sub-tensor offset and the blob stride
     const uint32_t *ro = &L.off.gateWOff, *so = &L.sharedOff.gateWOff;
     for (int i = 0; i < 9; ++i)
-        if (ro[i] % 8 || (withShared && so[i] % 8) || L.stride % 8)
-            return fail(error, "sub-tensor offsets must be multiples of 8 bytes for the decode kernel");
-    a.slotsOffset = (uint32_t)lay.slotsOffset;
-    a.bigBytes = (uint32_t)lay.bigBytes;
-    a.smallBytes = (uint32_t)lay.smallBytes;
+        if ((routed && (ro[i] % 16 || L.stride % 16)) || (withShared && so[i] % 16))
+            return fail(error, "sub-tensor offsets must be multiples of 16 bytes for the decode kernel");
+    if (((uintptr_t)x & 15) != 0) return fail(error, "input row must be 16-byte aligned");
+    a.regionOffset = lay.regionOffset;
+    a.partialOffset = lay.partialOffset;
+    a.slotsOffset = lay.slotsOffset;
+    a.bigBytes = lay.bigBytes;
+    a.smallBytes = lay.smallBytes;
+    a.strideGU = lay.strideGU;
+    a.strideSD = lay.strideSD;
+    a.strideRD = lay.strideRD;
+    a.actStride = lay.actStride;
+    a.winBytes = lay.winBytes;
     static size_t configured[8] = {0};
     static int gridFor[8] = {0};
     const int slot = ctx->device & 7;

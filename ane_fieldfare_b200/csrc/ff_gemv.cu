@@ -600,7 +600,7 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     if (!L.experts) return fail(error, "layer has no resident experts");
     if (withShared && !L.shared) return fail(error, "layer has no resident shared FFN");
     if (decodeCombine)
-        return launch_decode_fused(ctx, L, x, ids, weights, withShared, residual, y, stream, error);
+        return launch_decode_fused(ctx, L, x, ids, weights, withShared, true, residual, y, stream, error);
     const int E = (int)L.expertCount;
     PlanArgs a{};
     uint32_t *idsDev = ctx->ids;

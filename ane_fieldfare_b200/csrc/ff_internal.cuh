@@ -180,7 +180,7 @@ bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, c
 
 // ff_decode.cu
 bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x, const uint32_t *idsIn,
-                         const uint16_t *weightsIn, bool withShared, const uint16_t *residual,
+                         const uint16_t *weightsIn, bool withShared, bool routed, const uint16_t *residual,
                          uint16_t *y, cudaStream_t stream, const char **error);
 
 // ff_prefill.cu
