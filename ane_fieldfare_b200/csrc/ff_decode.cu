@@ -44,7 +44,7 @@ namespace ff {
 constexpr int kFusedThreads = 512;
 constexpr int kFusedWarps = kFusedThreads / 32;
 constexpr int kBigWarps = 10;      // warps 0..9: gate/up pairs and the routed down tiles
-constexpr int kSharedGuWarps = 4;  // warps 0..3 take the shared gate/up tiles in phase A
+constexpr int kSharedGuWarps = 8;  // warps 0..7 take the shared gate/up tiles in phase A (K quarters)
 constexpr uint32_t kBarrierSpinLimit = 1u << 24;
 constexpr uint32_t kCopySpinLimit = 1u << 22;
 
@@ -71,7 +71,7 @@ struct DecodeArgs {
     int prefetch;                // bit 0: L2 prefetch of the chosen experts' down projections
     // shared-memory carve-up (fused_layout)
     uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
-    uint32_t strideGU, strideSD, strideRD, actStride, winBytes;
+    uint32_t strideGU, strideSD, strideRD, actStride, winBytes, winPitch;
 };
 
 // Bulk L2 prefetch of [p, p + bytes); bytes a multiple of 16, p 16-byte aligned.
@@ -79,6 +79,7 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) 
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
+// (barrier memory: [0] the grid barrier's arrival counter, [1] the logits' arrival counter)
 // The grid prefetches [base, base+bytes) in 8 KiB pieces.  Piece i belongs to CTA (i + cursor) mod
 // gridDim and to one thread of it, so every SM issues the same share: a bulk prefetch is executed
 // by the issuing SM's copy engine, whose throughput is a small fraction of HBM's.
@@ -98,25 +99,33 @@ __device__ __forceinline__ void prefetch_region(const uint8_t *base, uint64_t by
 // generation, the target is the next multiple of the grid size, and waiting is polling the counter
 // itself — no reset, no host-side state, one round trip after the last arrival.  Split in two so
 // that work that does not depend on the other CTAs (requests for the next phase) sits between
-// arriving and waiting.  Thread 0 arrives and waits; the spin is bounded.
+// arriving and waiting.  One thread arrives and waits; the spin is bounded.
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ unsigned long long grid_arrive(unsigned long long *count) {
+// The barrier thread is lane 0 of the CTA's last warp (a warp with no requests to issue between
+// arriving and waiting).  knownTarget != 0: the generation is already known from an earlier
+// arrival of this launch, so the arrival is a release reduction without a return value.
+__device__ __forceinline__ bool is_barrier_thread() { return threadIdx.x == blockDim.x - 32; }
+__device__ __forceinline__ unsigned long long grid_arrive(unsigned long long *count, unsigned long long knownTarget = 0) {
     __syncthreads();
-    unsigned long long target = 0;
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const unsigned long long old = atomicAdd(count, 1ull);
-        target = (old / gridDim.x + 1ull) * gridDim.x;
+    unsigned long long target = knownTarget;
+    if (is_barrier_thread()) {
+        if (knownTarget) {
+            asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(count) : "memory");
+        } else {
+            __threadfence();
+            const unsigned long long old = atomicAdd(count, 1ull);
+            target = (old / gridDim.x + 1ull) * gridDim.x;
+        }
     }
     return target;
 }
 __device__ __forceinline__ void grid_wait(const unsigned long long *count, unsigned long long target,
                                           uint32_t *errorFlag) {
-    if (threadIdx.x == 0) {
+    if (is_barrier_thread()) {
         uint32_t spins = 0;
         while (ld_acquire_u64(count) < target) {
             if (++spins > kBarrierSpinLimit) {
@@ -397,11 +406,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     const int tilesSGU = sh ? Fs >> 3 : 0;  // 8 gate + 8 up rows per tile, two K halves
     const int tilesSD = sh ? D >> 4 : 0;    // 16 down rows per tile, three K parts
 
-    // Requests of a gate/up tile half: 16 row pieces, then the eight rows' scales and biases of both
+    // Requests of part `part` of `parts` (along K) of a gate/up tile: 16 row pieces, then the eight rows' scales and biases of both
     // matrices over the full K (contiguous runs).  Lane l issues copy l.
-    auto issue_gate_up = [&](const uint8_t *blob, const FFExpertOffsets &off, int tile, int half) {
+    auto issue_gate_up = [&](const uint8_t *blob, const FFExpertOffsets &off, int tile, int part, int parts) {
         int gb, ge;
-        part_range(groupsD, 2, half, gb, ge);
+        part_range(groupsD, parts, part, gb, ge);
         const uint32_t piece = (uint32_t)(ge - gb) * 32u, sb = (uint32_t)groupsD * 16u;
         if (lane == 0) bar_expect(myBar, 16u * piece + 4u * sb);
         __syncwarp();
@@ -415,10 +424,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
             bulk_copy(slotAddr + 16u * a.strideGU + which * sb, blob + src + (size_t)tile * sb, sb, myBar);
         }
     };
-    // Gate/up tile half -> this thread's partial sums of gate row tile*8+g and up row tile*8+g.
-    auto compute_gate_up = [&](int half, const uint8_t *xp, const float *xs, float &gate, float &up) {
+    // Gate/up tile part -> this thread's partial sums of gate row tile*8+g and up row tile*8+g.
+    auto compute_gate_up = [&](int part, int parts, const uint8_t *xp, const float *xs, float &gate, float &up) {
         int gb, ge;
-        part_range(groupsD, 2, half, gb, ge);
+        part_range(groupsD, parts, part, gb, ge);
         const uint8_t *lo = mySlot + (size_t)g * a.strideGU + 8 * t;
         const uint8_t *hi = mySlot + (size_t)(g + 8) * a.strideGU + 8 * t;
         const uint16_t *sc = reinterpret_cast<const uint16_t *>(mySlot + 16u * a.strideGU);
@@ -442,8 +451,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     };
 
     // ---------------- phase A: router logits, shared gate/up/GeGLU ----------------
-    int tA = warp < kSharedGuWarps ? (warp >> 1) * G + cta : 0x7FFFFFFF;
-    if (tA < tilesSGU) issue_gate_up(sh, a.sharedOff, tA, warp & 1);
+    // shared gate/up tiles: four warps per tile (K quarters), two tiles per CTA and round
+    const int partA = warp & 3;
+    int tA = warp < kSharedGuWarps ? (warp >> 2) * G + cta : 0x7FFFFFFF;
+    if (tA < tilesSGU) issue_gate_up(sh, a.sharedOff, tA, partA, 4);
     int eA = (!a.idsIn && K > 0 && warp >= kSharedGuWarps && warp < kBigWarps) ? (warp - kSharedGuWarps) * G + cta
                                                                              : 0x7FFFFFFF;
     if (eA < E) {
@@ -459,26 +470,26 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     if (tSD < tilesSD) issue_shared_down(tSD, part3);
     warp_stamp(a, 0, 0);
     stage_input(a.x, 1, D, xPerm, 0, xSum);
-    for (; tA < tilesSGU; tA += (kSharedGuWarps / 2) * G) {
+    for (; tA < tilesSGU; tA += (kSharedGuWarps / 4) * G) {
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
         float gate, up;
-        compute_gate_up(warp & 1, xPerm, xSum, gate, up);
+        compute_gate_up(partA, 4, xPerm, xSum, gate, up);
         slot_release();
-        const int next = tA + (kSharedGuWarps / 2) * G;
-        if (next < tilesSGU) issue_gate_up(sh, a.sharedOff, next, warp & 1);
+        const int next = tA + (kSharedGuWarps / 4) * G;
+        if (next < tilesSGU) issue_gate_up(sh, a.sharedOff, next, partA, 4);
         float *mine = partial + warp * 16;
-        if ((warp & 1) && t == 0) {
+        if (partA && t == 0) {
             mine[g] = gate;
             mine[8 + g] = up;
         }
-        named_barrier(1 + (warp >> 1), 64);
-        if (!(warp & 1) && t == 0) {
-            gate += mine[16 + g];
-            up += mine[16 + 8 + g];
+        named_barrier(1 + (warp >> 2), 128);
+        if (!partA && t == 0) {
+            gate = ((gate + mine[16 + g]) + mine[32 + g]) + mine[48 + g];
+            up = ((up + mine[16 + 8 + g]) + mine[32 + 8 + g]) + mine[48 + 8 + g];
             a.sharedActs[tA * 8 + g] = f2bf(gelu_tanh(bf16_round(gate)) * bf16_round(up));
         }
-        named_barrier(1 + (warp >> 1), 64);
+        named_barrier(1 + (warp >> 2), 128);
     }
     for (; eA < E; eA += (kBigWarps - kSharedGuWarps) * G) {
         slot_wait(myBar, parity, a.errorFlag);
@@ -487,21 +498,26 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
         float acc = 0.0f;
         for (int base = 8 * lane; base < D; base += 256) {
             const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
-            const uint4 xv = *reinterpret_cast<const uint4 *>(a.x + base);
-            uint4 sv = make_uint4(0, 0, 0, 0);
-            if (a.routerScale) sv = *reinterpret_cast<const uint4 *>(a.routerScale + base);
+            // the staged run holds elements 0,4,1,5,2,6,3,7: low halves are 0..3, high halves 4..7
+            const uint4 xv = *reinterpret_cast<const uint4 *>(xPerm + base * 2);
+            float xe[8] = {__uint_as_float(xv.x << 16),         __uint_as_float(xv.y << 16),
+                           __uint_as_float(xv.z << 16),         __uint_as_float(xv.w << 16),
+                           __uint_as_float(xv.x & 0xFFFF0000u), __uint_as_float(xv.y & 0xFFFF0000u),
+                           __uint_as_float(xv.z & 0xFFFF0000u), __uint_as_float(xv.w & 0xFFFF0000u)};
+            if (a.routerScale) {
+                const uint4 sv = *reinterpret_cast<const uint4 *>(a.routerScale + base);
+                const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    xe[2 * k] = xe[2 * k] * __uint_as_float(ss[k] << 16);
+                    xe[2 * k + 1] = xe[2 * k + 1] * __uint_as_float(ss[k] & 0xFFFF0000u);
+                }
+            }
             const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-            const uint32_t xx[4] = {xv.x, xv.y, xv.z, xv.w};
-            const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                float x0 = __uint_as_float(xx[k] << 16), x1 = __uint_as_float(xx[k] & 0xFFFF0000u);
-                if (a.routerScale) {
-                    x0 = x0 * __uint_as_float(ss[k] << 16);
-                    x1 = x1 * __uint_as_float(ss[k] & 0xFFFF0000u);
-                }
-                acc = fmaf(__uint_as_float(ww[k] << 16), x0, acc);
-                acc = fmaf(__uint_as_float(ww[k] & 0xFFFF0000u), x1, acc);
+                acc = fmaf(__uint_as_float(ww[k] << 16), xe[2 * k], acc);
+                acc = fmaf(__uint_as_float(ww[k] & 0xFFFF0000u), xe[2 * k + 1], acc);
             }
         }
 #pragma unroll
@@ -517,72 +533,93 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     }
     warp_stamp(a, 0, 2);
     stamp(a, 1);
-    if (sh || (!a.idsIn && K > 0)) grid_wait(a.barrier, grid_arrive(a.barrier), a.errorFlag);
-    stamp(a, 2);
 
-    // ---------------- phase B: top-8, routed gate/up/GeGLU, shared down ----------------
-    if (K > 0) {
-        if (!a.idsIn) {
-            for (int e = threadIdx.x; e < E; e += blockDim.x) sLogits[e] = __ldcg(a.logits + e);
-            if (threadIdx.x < 8) {
-                sIds[threadIdx.x] = 0u;
-                sScore[threadIdx.x] = -INFINITY;
+    // ---------------- top-8 by warps 8..15 while warps 0..7 finish the shared gate/up rows ----------
+    // The logits have their own arrival counter (every CTA arrives once its router rows are
+    // written), so ranking does not wait for the other CTAs' shared rows.
+    if (K > 0 && !a.idsIn && warp >= kSharedGuWarps) {
+        constexpr int kTopkThreads = (kFusedWarps - kSharedGuWarps) * 32;
+        const int tid2 = (int)threadIdx.x - kSharedGuWarps * 32;
+        named_barrier(8, kTopkThreads);  // this CTA's logits are written
+        if (tid2 == 0) {
+            __threadfence();
+            unsigned long long *count = a.barrier + 1;
+            const unsigned long long old = atomicAdd(count, 1ull);
+            const unsigned long long target = (old / gridDim.x + 1ull) * gridDim.x;
+            uint32_t spins = 0;
+            while (ld_acquire_u64(count) < target) {
+                if (++spins > kBarrierSpinLimit) {
+                    atomicExch(a.errorFlag, 9u);
+                    break;
+                }
             }
-            __syncthreads();
-            // rank of every logit under (higher score, then lower expert id); scores of -inf or NaN
-            // are never taken — the order of the serial top-8 (moe.metal:269-303).  Four threads per
-            // expert, each counting a quarter of the competitors.
-            for (int idx = threadIdx.x; idx < 4 * ((E + 127) & ~127); idx += blockDim.x) {
-                const int e = idx >> 2, quarter = idx & 3;
+            __threadfence();
+        }
+        named_barrier(8, kTopkThreads);
+        for (int e = tid2; e < E; e += kTopkThreads) sLogits[e] = __ldcg(a.logits + e);
+        if (tid2 < 8) {
+            sIds[tid2] = 0u;
+            sScore[tid2] = -INFINITY;
+        }
+        named_barrier(8, kTopkThreads);
+        // rank of every logit under (higher score, then lower expert id); scores of -inf or NaN
+        // are never taken — the order of the serial top-8 (moe.metal:269-303).  Two threads per
+        // expert, each counting half of the competitors with the loads unrolled.
+        {
+            const int halfSpan = (E + 1) >> 1;
+            for (int idx = tid2; idx < 2 * ((E + 127) & ~127); idx += kTopkThreads) {
+                const int e = idx >> 1, half = idx & 1;
                 const float v = e < E ? sLogits[e] : -INFINITY;
-                const int span = (E + 3) >> 2;
+                const int begin = half * halfSpan, end = min(E, begin + halfSpan);
                 int rank = 0;
-                if (v > -INFINITY) {
-                    const int end = min(E, (quarter + 1) * span);
-                    for (int o = quarter * span; o < end; ++o) {
-                        const float w = sLogits[o];
-                        rank += (w > -INFINITY && (w > v || (w == v && o < e))) ? 1 : 0;
-                    }
+#pragma unroll 8
+                for (int o = begin; o < end; ++o) {
+                    const float w = sLogits[o];
+                    rank += (w > v || (w == v && o < e)) ? 1 : 0;  // w > -inf follows from v > -inf
                 }
                 rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
-                rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 2);
-                if (quarter == 0 && v > -INFINITY && rank < K) {
+                if (half == 0 && v > -INFINITY && rank < K) {
                     sIds[rank] = (uint32_t)e;
                     sScore[rank] = v;
                 }
             }
-            __syncthreads();
-            if (warp == 0) {
-                // softmax over the chosen scores: exponentials in parallel, the sum in rank order
-                const float score = lane < K ? sScore[lane] : -INFINITY;
-                const float top = __shfl_sync(0xFFFFFFFFu, score, 0);
-                const float ex = lane < K ? expf(score - top) : 0.0f;
-                float sum = 0.0f;
-                for (int r = 0; r < K; ++r) sum += __shfl_sync(0xFFFFFFFFu, ex, r);
-                if (lane < K) {
-                    float w = ex / sum;
-                    if (a.gain) w = w * bf2f(a.gain[sIds[lane]]);
-                    const uint16_t wb = f2bf(w);
-                    sWeights[lane] = bf2f(wb);
-                    if (blockIdx.x == 0) {
-                        a.ids[lane] = sIds[lane];
-                        a.weights[lane] = wb;
-                    }
+        }
+        named_barrier(8, kTopkThreads);
+        if (warp == kSharedGuWarps) {
+            // softmax over the chosen scores: exponentials in parallel, the sum in rank order
+            const float score = lane < K ? sScore[lane] : -INFINITY;
+            const float top = __shfl_sync(0xFFFFFFFFu, score, 0);
+            const float ex = lane < K ? expf(score - top) : 0.0f;
+            float sum = 0.0f;
+            for (int r = 0; r < K; ++r) sum += __shfl_sync(0xFFFFFFFFu, ex, r);
+            if (lane < K) {
+                float w = ex / sum;
+                if (a.gain) w = w * bf2f(a.gain[sIds[lane]]);
+                const uint16_t wb = f2bf(w);
+                sWeights[lane] = bf2f(wb);
+                if (blockIdx.x == 0) {
+                    a.ids[lane] = sIds[lane];
+                    a.weights[lane] = wb;
                 }
             }
-        } else if (threadIdx.x < K) {
-            sIds[threadIdx.x] = a.idsIn[threadIdx.x];
-            sWeights[threadIdx.x] = bf2f(a.weightsIn[threadIdx.x]);
         }
-        __syncthreads();
+    } else if (K > 0 && a.idsIn && threadIdx.x < K) {
+        sIds[threadIdx.x] = a.idsIn[threadIdx.x];
+        sWeights[threadIdx.x] = bf2f(a.weightsIn[threadIdx.x]);
     }
+    // barrier 1 covers the shared activations; the routed rows are requested between arriving
+    // and waiting (grid_arrive's CTA barrier also publishes the routes to all warps)
+    unsigned long long target1 = 0;
+    if (sh) target1 = grid_arrive(a.barrier);
+    else __syncthreads();
+    stamp(a, 2);
     stamp(a, 3);
     const int tilesF = F >> 3;
     const int tilesRouted = K * tilesF;
     int tB = warp < kBigWarps ? (warp >> 1) * G + cta : 0x7FFFFFFF;
     if (tB < tilesRouted) {
         const int slot = tB / tilesF;
-        issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, tB - slot * tilesF, warp & 1);
+        issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, tB - slot * tilesF, warp & 1, 2);
     }
     warp_stamp(a, 1, 0);
     if ((a.prefetch & 1) && K > 0) {
@@ -595,17 +632,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     }
     uint8_t *saPerm = region;
     float *saSum = reinterpret_cast<float *>(region + Fs * 2);
-    if (sh) stage_input(a.sharedActs, 1, Fs, saPerm, 0, saSum);
+    if (sh) {
+        grid_wait(a.barrier, target1, a.errorFlag);
+        stage_input(a.sharedActs, 1, Fs, saPerm, 0, saSum);
+    }
     for (; tB < tilesRouted; tB += (kBigWarps / 2) * G) {
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 1, 1);
         float gate, up;
-        compute_gate_up(warp & 1, xPerm, xSum, gate, up);
+        compute_gate_up(warp & 1, 2, xPerm, xSum, gate, up);
         slot_release();
         const int next = tB + (kBigWarps / 2) * G;
         if (next < tilesRouted) {
             const int slot = next / tilesF;
-            issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, next - slot * tilesF, warp & 1);
+            issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, next - slot * tilesF, warp & 1, 2);
         }
         float *mine = partial + warp * 16;
         if ((warp & 1) && t == 0) {
@@ -674,11 +714,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
             bulk_copy(slotAddr + (uint32_t)lane * a.strideRD, blob + a.off.downWOff + (size_t)row * (F >> 1), piece, myBar);
         } else {
             const uint32_t srcOff = ((lane & 1) ? a.off.downBOff : a.off.downSOff) + (uint32_t)tile * 4u * (uint32_t)groupsF;
-            bulk_copy(slotAddr + 16u * a.strideRD + (uint32_t)(lane - 16) * a.winBytes, blob + (srcOff & ~15u), a.winBytes, myBar);
+            // windows: scales of expert e at e * winPitch, biases at (8 + e) * winPitch
+            bulk_copy(slotAddr + 16u * a.strideRD + (uint32_t)(((lane & 1) << 3) + e) * a.winPitch, blob + (srcOff & ~15u),
+                      a.winBytes, myBar);
         }
     };
     // the weights do not depend on the activations: request them between arriving and waiting
-    const unsigned long long target2 = grid_arrive(a.barrier);
+    // (the barrier thread knows barrier 1's target: barrier 2 is the next generation)
+    const unsigned long long target2 = grid_arrive(a.barrier, target1 ? target1 + gridDim.x : 0ull);
     int tC = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
     if (tC < tilesRD) issue_routed_down(tC);
     warp_stamp(a, 2, 0);
@@ -707,19 +750,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
             const uint8_t *hi = mySlot + (size_t)(g + 8) * a.strideRD + 8 * t;
             const uint8_t *xe = region + (size_t)g * a.actStride + t * 32;
             const uint32_t rowOff = (uint32_t)tC * 4u * (uint32_t)groupsF;
-            const uint8_t *win = mySlot + 16u * a.strideRD + (uint32_t)(2 * g) * a.winBytes;
+            const uint8_t *win = mySlot + 16u * a.strideRD + (uint32_t)g * a.winPitch;
             const uint16_t *sS = reinterpret_cast<const uint16_t *>(win + ((a.off.downSOff + rowOff) & 15u));
-            const uint16_t *sB = reinterpret_cast<const uint16_t *>(win + a.winBytes + ((a.off.downBOff + rowOff) & 15u));
+            const uint16_t *sB = reinterpret_cast<const uint16_t *>(win + 8u * a.winPitch + ((a.off.downBOff + rowOff) & 15u));
             const float *xs = actSum + g * groupsF;
             const bool odd = g & 1;
+            const int row = tC * 2 + (lane & 1);
+            float acc = (lane < 2 && res) ? bf2f(__ldcg(res + row)) : 0.0f;
             float v0, v1;
             tile_rows(lo, hi, xe, sS, sB, sS + groupsF, sB + groupsF, xs, groupsF, odd, v0, v1);
             slot_release();
             const int next = tC + kBigWarps * G;
             if (next < tilesRD) issue_routed_down(next);
             // lane 0 combines row 2*tile, lane 1 row 2*tile+1, experts in rank order
-            const int row = tC * 2 + (lane & 1);
-            float acc = (lane < 2 && res) ? bf2f(__ldcg(res + row)) : 0.0f;
             for (int k = 0; k < K; ++k) {
                 const int src = 4 * k + (k >> 1);
                 const float e0 = __shfl_sync(0xFFFFFFFFu, v0, src);
@@ -735,7 +778,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
 
 struct FusedLayout {
     uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
-    uint32_t strideGU, strideSD, strideRD, actStride, winBytes;
+    uint32_t strideGU, strideSD, strideRD, actStride, winBytes, winPitch;
     size_t total;
 };
 
@@ -747,10 +790,14 @@ static FusedLayout fused_layout(const FFConfig &c) {
     l.strideSD = Fs ? piece_stride(((groupsFs + 2) / 3) * 32) : 32;
     l.strideRD = piece_stride(groupsF * 32);
     l.winBytes = pad16u(4 * groupsF) + 16;
-    // per-expert activation stride: 64 modulo 128 so that the two experts a quarter-warp reads
-    // with 128-bit loads use different bank halves
+    // window pitch: 80 modulo 128 puts the eight experts' windows on different banks
+    l.winPitch = l.winBytes;
+    while ((l.winPitch & 127u) != 80u) l.winPitch += 16u;
+    // per-expert activation stride: 16 modulo 128.  A quarter-warp's 128-bit load covers two
+    // experts, four lanes each reading 16 bytes at 32-byte steps; the second expert's chunks then
+    // fall into the gaps of the first.
     l.actStride = F * 2;
-    while ((l.actStride & 127u) != 64u) l.actStride += 16u;
+    while ((l.actStride & 127u) != 16u) l.actStride += 16u;
     const uint32_t xPart = (D * 2 + groupsD * 4 + 127u) & ~127u;
     const uint32_t sharedPart = Fs ? Fs * 2 + groupsFs * 4 : 0;
     const uint32_t actsPart = 8 * l.actStride + 8 * groupsF * 4;
@@ -758,7 +805,7 @@ static FusedLayout fused_layout(const FFConfig &c) {
     l.partialOffset = (l.regionOffset + std::max(sharedPart, actsPart) + 127u) & ~127u;
     l.slotsOffset = l.partialOffset + kFusedWarps * 16 * 4;
     const uint32_t gateUp = 16 * l.strideGU + 4 * groupsD * 16;
-    const uint32_t down8 = 16 * l.strideRD + 16 * l.winBytes;
+    const uint32_t down8 = 16 * l.strideRD + 16 * l.winPitch;
     const uint32_t sharedDown = Fs ? 16 * l.strideSD + 2 * groupsFs * 32 : 0;
     l.bigBytes = (std::max({gateUp, down8, D * 2}) + 127u) & ~127u;
     l.smallBytes = (std::max(sharedDown, 128u) + 127u) & ~127u;
@@ -835,6 +882,7 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.strideRD = lay.strideRD;
     a.actStride = lay.actStride;
     a.winBytes = lay.winBytes;
+    a.winPitch = lay.winPitch;
     static size_t configured[8] = {0};
     static int gridFor[8] = {0};
     const int slot = ctx->device & 7;
