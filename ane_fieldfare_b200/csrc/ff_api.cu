@@ -225,12 +225,59 @@ bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t to
     return true;
 }
 
+// One token with host buffers, without copies around the kernel: the input row travels in the
+// kernel parameters, the last CTA writes the output straight into the caller's pinned buffer and
+// reports through a mailbox in pinned memory that the host polls.  Returns false (with *handled
+// false) when the fast path does not apply.
+static bool moe_layer_host_one_token(FFContext *ctx, uint32_t layer, const uint16_t *hostX, uint16_t *hostY,
+                                     bool *handled, const char **error) {
+    *handled = false;
+    const FFConfig &cfg = ctx->cfg;
+    if (layer >= cfg.layers || cfg.d > 4096 || !ctx->mailbox) return true;
+    LayerStore &L = ctx->layers[layer];
+    if (!L.experts || !L.routerW) return true;
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, hostY) != cudaSuccess) {
+        cudaGetLastError();
+        return true;
+    }
+    if (attr.type != cudaMemoryTypeHost || !attr.devicePointer || ((uintptr_t)attr.devicePointer & 15)) return true;
+    *handled = true;
+    const bool withShared = cfg.sharedF != 0 && L.shared != nullptr;
+    ctx->lastTokens = 1;
+    DecodeHostHandoff handoff{hostX, static_cast<uint16_t *>(attr.devicePointer), ctx->mailbox, ++ctx->hostEpoch};
+    if (handoff.epoch == 0) handoff.epoch = ++ctx->hostEpoch;  // 0 is the mailbox's initial value
+    if (!launch_decode_fused(ctx, L, ctx->xDev, nullptr, nullptr, withShared, true, nullptr, ctx->yDev,
+                             ctx->hostStream, error, &handoff))
+        return false;
+    // poll the mailbox; look at the stream now and then so that a failed launch cannot spin forever
+    for (uint64_t spins = 1;; ++spins) {
+        if (ctx->mailbox[0] == handoff.epoch) break;
+        if ((spins & 0xFFFF) == 0) {
+            const cudaError_t state = cudaStreamQuery(ctx->hostStream);
+            if (state == cudaSuccess) {
+                if (ctx->mailbox[0] == handoff.epoch) break;
+                return fail(error, "the decode kernel ended without reporting");
+            }
+            if (state != cudaErrorNotReady) return fail(error, std::string("CUDA: ") + cudaGetErrorString(state));
+        }
+    }
+    const uint32_t flag = ctx->mailbox[1];
+    if (flag) return fail(error, "a kernel gave up waiting (error flag " + std::to_string(flag) + ")");
+    return true;
+}
+
 bool ff_moe_layer_host(FFContext *ctx, uint32_t layer, const uint16_t *hostX, uint32_t tokens,
                        uint16_t *hostY, const char **error) {
     if (error) *error = nullptr;
     if (!ctx || !hostX || !hostY) return fail(error, "null argument");
     if (tokens > ctx->cfg.maxTokens) return fail(error, "rows exceed the context's maxTokens");
     FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    if (tokens == 1) {
+        bool handled = false;
+        const bool ok = moe_layer_host_one_token(ctx, layer, hostX, hostY, &handled, error);
+        if (handled || !ok) return ok;
+    }
     const size_t bytes = (size_t)tokens * ctx->cfg.d * sizeof(uint16_t);
     FF_CUDA_OK(cudaMemcpyAsync(ctx->xDev, hostX, bytes, cudaMemcpyHostToDevice, ctx->hostStream), error);
     if (!ff_moe_layer(ctx, layer, ctx->xDev, tokens, ctx->yDev, nullptr, nullptr, ctx->hostStream, error))

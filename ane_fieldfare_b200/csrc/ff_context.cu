@@ -70,6 +70,7 @@ void ff_destroy(FFContext *ctx) {
                     ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch};
     for (void *p : ptrs) cudaFree(p);
     if (ctx->hostStream) cudaStreamDestroy(ctx->hostStream);
+    if (ctx->mailbox) cudaFreeHost(const_cast<uint32_t *>(ctx->mailbox));
     delete ctx;
 }
 
@@ -143,8 +144,18 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     if (ok) ok = cudaMemset(ctx->errorFlag, 0, 16) == cudaSuccess;
     ok = ok && dev_alloc(ctx, &ctx->phaseStamps, kPhaseStampSlots, error);
     if (ok) ok = cudaMemset(ctx->phaseStamps, 0, kPhaseStampSlots * 8) == cudaSuccess;
-    ok = ok && dev_alloc(ctx, &ctx->gridBarrier, 4, error);
-    if (ok) ok = cudaMemset(ctx->gridBarrier, 0, 16) == cudaSuccess;
+    ok = ok && dev_alloc(ctx, &ctx->gridBarrier, 8, error);
+    if (ok) ok = cudaMemset(ctx->gridBarrier, 0, 32) == cudaSuccess;
+    if (ok) {
+        void *box = nullptr;
+        ok = cudaHostAlloc(&box, 64, cudaHostAllocMapped) == cudaSuccess;
+        if (ok) {
+            memset(box, 0, 64);
+            ctx->mailbox = static_cast<volatile uint32_t *>(box);
+        } else if (error) {
+            fail(error, "cudaHostAlloc of the host mailbox failed");
+        }
+    }
     if (ok && T > (size_t)kMaxGemvRows) {
         const size_t pairs = T * K;
         const size_t permuteBlocks = (T + 255) / 256;

@@ -35,6 +35,7 @@
 //   Sources/ANEFieldfareHotpath/Metal/Quant/dequant_int4.metal:78-169
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 
 #include "ff_gemv_device.cuh"
 #include "ff_internal.cuh"
@@ -69,6 +70,11 @@ struct DecodeArgs {
     unsigned long long *stamps;  // null, or the phase / per-warp timestamp slots (ns)
     int E, D, F, Fs, K;          // K = 0: shared FFN only (y receives its output)
     int prefetch;                // bit 0: L2 prefetch of the chosen experts' down projections
+    // host hand-off (null when unused): the last CTA to finish copies y to `hostY` (host memory the
+    // device can write), then the error flag and `epoch` to `mailbox` — the host polls mailbox[0]
+    uint16_t *hostY;
+    volatile uint32_t *mailbox;
+    uint32_t epoch;
     // shared-memory carve-up (fused_layout)
     uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
     uint32_t strideGU, strideSD, strideRD, actStride, winBytes, winPitch;
@@ -79,7 +85,8 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) 
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
-// (barrier memory: [0] the grid barrier's arrival counter, [1] the logits' arrival counter)
+// (barrier memory: [0] the grid barrier's arrival counter, [1] the logits' arrival counter,
+// [2] the count of finished CTAs for the host hand-off)
 // The grid prefetches [base, base+bytes) in 8 KiB pieces.  Piece i belongs to CTA (i + cursor) mod
 // gridDim and to one thread of it, so every SM issues the same share: a bulk prefetch is executed
 // by the issuing SM's copy engine, whose throughput is a small fraction of HBM's.
@@ -314,10 +321,11 @@ __device__ __noinline__ void tile_rows(const uint8_t *lo, const uint8_t *hi, con
 // 0,4,1,5,2,6,3,7, then the fp32 sum of each group of 64 (sums[row * n/64 + group]).  All threads
 // of the CTA take part; ends with a CTA barrier.
 __device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n, uint8_t *dst, uint32_t dstStride,
-                                            float *sums) {
+                                            float *sums, bool plainLoads = false) {
     const int runsPerRow = n >> 3, runs = rows * runsPerRow;
     for (int i = threadIdx.x; i < runs; i += blockDim.x) {
-        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(src) + i);
+        // plain loads for a source outside global memory (kernel parameters)
+        const uint4 v = plainLoads ? reinterpret_cast<const uint4 *>(src)[i] : __ldcg(reinterpret_cast<const uint4 *>(src) + i);
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410);
         o.y = __byte_perm(v.x, v.z, 0x7632);
@@ -367,7 +375,14 @@ __host__ __device__ inline void part_range(int groups, int parts, int p, int &be
     end = min(groups, begin + per);
 }
 
-__global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeArgs a) {
+// The input row travelling inside the kernel's parameters (no host-to-device copy before the
+// launch): up to 4096 bf16 values.
+struct InlineRow {
+    uint4 v[512];
+};
+
+// xInline: null, or the input row in parameter space (read with plain loads).
+__device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t *xInline) {
     extern __shared__ __align__(128) uint8_t smemRaw[];
     __shared__ float sLogits[kMaxExperts];
     __shared__ uint32_t sIds[8];
@@ -469,7 +484,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     int tSD = warp >= kBigWarps ? triple * G + cta : 0x7FFFFFFF;
     if (tSD < tilesSD) issue_shared_down(tSD, part3);
     warp_stamp(a, 0, 0);
-    stage_input(a.x, 1, D, xPerm, 0, xSum);
+    stage_input(xInline ? xInline : a.x, 1, D, xPerm, 0, xSum, xInline != nullptr);
     for (; tA < tilesSGU; tA += (kSharedGuWarps / 4) * G) {
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
@@ -774,6 +789,37 @@ __global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeA
     }
     warp_stamp(a, 2, 2);
     stamp(a, 6);
+
+    // ---------------- host hand-off by the last CTA to finish ----------------
+    if (a.mailbox) {
+        __shared__ uint32_t sLast;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            const unsigned long long old = atomicAdd(a.barrier + 2, 1ull);
+            sLast = (old % gridDim.x == gridDim.x - 1) ? 1u : 0u;
+        }
+        __syncthreads();
+        if (sLast) {
+            __threadfence();
+            for (int i = threadIdx.x; i < (D >> 3); i += blockDim.x)
+                reinterpret_cast<uint4 *>(a.hostY)[i] = __ldcg(reinterpret_cast<const uint4 *>(a.y) + i);
+            __threadfence_system();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                a.mailbox[1] = __ldcg(a.errorFlag);
+                __threadfence_system();
+                a.mailbox[0] = a.epoch;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeArgs a) { decode_body(a, nullptr); }
+
+__global__ void __launch_bounds__(kFusedThreads, 1)
+k_decode_fused_inline_x(const DecodeArgs a, const __grid_constant__ InlineRow row) {
+    decode_body(a, reinterpret_cast<const uint16_t *>(&row));
 }
 
 struct FusedLayout {
@@ -818,7 +864,7 @@ static FusedLayout fused_layout(const FFConfig &c) {
 // receives its output.
 bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x, const uint32_t *idsIn,
                          const uint16_t *weightsIn, bool withShared, bool routed, const uint16_t *residual,
-                         uint16_t *y, cudaStream_t stream, const char **error) {
+                         uint16_t *y, cudaStream_t stream, const char **error, const DecodeHostHandoff *host) {
     const FFConfig &c = ctx->cfg;
     if (routed && !L.experts) return fail(error, "layer has no resident experts");
     if (routed && !idsIn && !L.routerW) return fail(error, "layer has no resident router");
@@ -871,7 +917,7 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     for (int i = 0; i < 9; ++i)
         if ((routed && (ro[i] % 16 || L.stride % 16)) || (withShared && so[i] % 16))
             return fail(error, "sub-tensor offsets must be multiples of 16 bytes for the decode kernel");
-    if (((uintptr_t)x & 15) != 0) return fail(error, "input row must be 16-byte aligned");
+    if (!(host && host->inlineX) && ((uintptr_t)x & 15) != 0) return fail(error, "input row must be 16-byte aligned");
     a.regionOffset = lay.regionOffset;
     a.partialOffset = lay.partialOffset;
     a.slotsOffset = lay.slotsOffset;
@@ -890,17 +936,37 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
         FF_CUDA_OK(cudaFuncSetAttribute(k_decode_fused, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (int)smem),
                    error);
+        FF_CUDA_OK(cudaFuncSetAttribute(k_decode_fused_inline_x, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem),
+                   error);
         int perSm = 0;
         FF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, k_decode_fused, kFusedThreads,
+                                                                 smem),
+                   error);
+        if (perSm < 1) return fail(error, "fused decode kernel does not fit on an SM");
+        FF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, k_decode_fused_inline_x, kFusedThreads,
                                                                  smem),
                    error);
         if (perSm < 1) return fail(error, "fused decode kernel does not fit on an SM");
         gridFor[slot] = ctx->smCount;
         configured[slot] = smem;
     }
-    void *params[] = {&a};
-    {
-        LaunchScope scope(ctx, stream, "decode_fused");
+    if (host) {
+        a.hostY = host->hostY;
+        a.mailbox = host->mailbox;
+        a.epoch = host->epoch;
+    }
+    LaunchScope scope(ctx, stream, "decode_fused");
+    if (host && host->inlineX) {
+        if (c.d > 4096) return fail(error, "input row too long to travel in the kernel parameters");
+        static thread_local InlineRow row;
+        memcpy(&row, host->inlineX, (size_t)c.d * 2);
+        void *params[] = {&a, &row};
+        FF_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(k_decode_fused_inline_x),
+                                               dim3(gridFor[slot]), dim3(kFusedThreads), params, smem, stream),
+                   error);
+    } else {
+        void *params[] = {&a};
         FF_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(k_decode_fused), dim3(gridFor[slot]),
                                                dim3(kFusedThreads), params, smem, stream),
                    error);

@@ -113,7 +113,9 @@ struct FFContext {
     uint32_t maxUnits = 0;
     uint32_t *errorFlag = nullptr;          // device: set by a kernel that gave up waiting
     unsigned long long *phaseStamps = nullptr;  // device: 8 phase + 288 per-warp timestamps of the fused decode kernel
-    uint32_t *gridBarrier = nullptr;        // device: [arrivals, sense] of the fused decode kernel
+    uint32_t *gridBarrier = nullptr;        // device: four 64-bit counters of the fused decode kernel
+    volatile uint32_t *mailbox = nullptr;   // pinned host memory the decode kernel reports to
+    uint32_t hostEpoch = 0;
     CUtensorMap *mapScratch = nullptr;
 
     // tracing: CUDA events around every kernel launch, aggregated per kernel name
@@ -179,9 +181,19 @@ bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, c
                           cudaStream_t stream, const char **error);
 
 // ff_decode.cu
+// Host hand-off of the one-token kernel: `inlineX` (host memory) travels in the kernel parameters
+// instead of `x`; the last CTA copies the output to `hostY` (host memory mapped for the device) and
+// writes the error flag and `epoch` to mailbox[1], mailbox[0].
+struct DecodeHostHandoff {
+    const uint16_t *inlineX;
+    uint16_t *hostY;
+    volatile uint32_t *mailbox;
+    uint32_t epoch;
+};
 bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x, const uint32_t *idsIn,
                          const uint16_t *weightsIn, bool withShared, bool routed, const uint16_t *residual,
-                         uint16_t *y, cudaStream_t stream, const char **error);
+                         uint16_t *y, cudaStream_t stream, const char **error,
+                         const DecodeHostHandoff *host = nullptr);
 
 // ff_prefill.cu
 bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error);

@@ -230,8 +230,15 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
         prior = synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}")
         home.loadShared(i, *L.shared_projections())
         home.loadRouter(i, L.routerW, logitBias=prior)
-        # experts go to ranks so that the router's prior is balanced (the blob layout is untouched)
-        placements.append(parallel.balanced_placement(np.exp(prior.astype(np.float64)), world))
+        # experts go to ranks so that the expected routed load is balanced (the blob layout is
+        # untouched): the load is estimated on the host from the router itself, top-8 over seeded
+        # unit-RMS rows, which is what the inter-layer RMSNorm feeds every block
+        rows = synth.normal(synth.seedtree_key(ROOT_SEED, f"stack.calib.{i}"), 1024 * D).reshape(1024, D)
+        rows /= np.sqrt(np.mean(rows * rows, axis=1, keepdims=True))
+        logits = rows.astype(np.float32) @ synth.bf16_to_float(L.routerW).T + prior[None, :]
+        chosen = np.argpartition(-logits, K - 1, axis=1)[:, :K]
+        load = np.bincount(chosen.reshape(-1), minlength=E).astype(np.float64) + 0.5
+        placements.append(parallel.balanced_placement(load, world))
     for slot in range(layers):
         L = host_layers[slot % len(host_layers)]
         mine = placements[slot % len(host_layers)].experts_of(rank)
@@ -480,7 +487,7 @@ def run_ours(args):
         if rank == 0:
             line["stack"] = stack
 
-    if rank == 0 and not args.quick:
+    if rank == 0 and world == 1 and not args.quick:
         cpu_rate, cpu_steps, cpu_threads = cpu_decode_baseline(host_layer0, tokens_bits)
         line["cpu_baseline"] = {"value": cpu_rate, "unit": "tokens/s", "cores": cpu_threads,
                                 "kind": "port",

@@ -256,7 +256,10 @@ bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t to
                   const char **error);
 
 /* ff_moe_layer with HOST buffers: copies x in, runs, copies y out, waits.  Host pointers should
- * be page-locked for full copy bandwidth. */
+ * be page-locked for full copy bandwidth.  One token with a page-locked, 16-byte aligned hostY
+ * takes a path without copies around the kernel: the row travels in the kernel's parameters, the
+ * kernel writes hostY itself and reports completion through page-locked memory that this call
+ * polls; results are the same bits. */
 bool ff_moe_layer_host(FFContext *ctx, uint32_t layer, const uint16_t *hostX, uint32_t tokens,
                        uint16_t *hostY, const char **error);
 

@@ -319,6 +319,19 @@ def test_host_entry_point_and_errors(tiny, oracle):
     y = ctx.moeLayer(0, dev(x, ctx))
     torch.cuda.synchronize()
     assert torch.equal(hy, y.cpu())
+    # one token: the row travels in the kernel parameters and the kernel writes a pinned output
+    # itself; a pageable output takes the copy path.  Both equal the device-buffer call bit for bit,
+    # also when called again (the mailbox epoch moves on).
+    y1 = ctx.moeLayer(0, dev(x[2:3], ctx))
+    torch.cuda.synchronize()
+    for attempt in range(3):
+        hy1 = torch.full((1, L.d), 3.0, dtype=torch.bfloat16).pin_memory()
+        ctx.moeLayerHost(0, hx[2:3], hy1)
+        assert torch.equal(hy1, y1.cpu()), attempt
+    pageable_x = torch.from_numpy(x[2:3].view(np.int16).copy()).view(torch.bfloat16)
+    pageable_y = torch.full((1, L.d), 3.0, dtype=torch.bfloat16)
+    ctx.moeLayerHost(0, pageable_x, pageable_y)
+    assert torch.equal(pageable_y, y1.cpu())
     with pytest.raises(hp.FieldfareError, match="exceed the context's maxTokens"):
         ctx.moeLayer(0, torch.zeros((17, L.d), dtype=torch.bfloat16, device=ctx.device))
     with pytest.raises(hp.FieldfareError, match="out of range"):
