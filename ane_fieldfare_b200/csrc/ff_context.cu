@@ -67,7 +67,7 @@ void ff_destroy(FFContext *ctx) {
                     ctx->items[0], ctx->items[1], ctx->acts, ctx->sharedActs, ctx->h1,
                     ctx->partials, ctx->xDev, ctx->yDev, ctx->xSorted, ctx->sortedPairs,
                     ctx->expertOffsets, ctx->blockCounts, ctx->units, ctx->unitCount,
-                    ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch};
+                    ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch, ctx->taggedLogits};
     for (void *p : ptrs) cudaFree(p);
     if (ctx->hostStream) cudaStreamDestroy(ctx->hostStream);
     if (ctx->mailbox) cudaFreeHost(const_cast<uint32_t *>(ctx->mailbox));
@@ -144,8 +144,10 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     if (ok) ok = cudaMemset(ctx->errorFlag, 0, 16) == cudaSuccess;
     ok = ok && dev_alloc(ctx, &ctx->phaseStamps, kPhaseStampSlots, error);
     if (ok) ok = cudaMemset(ctx->phaseStamps, 0, kPhaseStampSlots * 8) == cudaSuccess;
-    ok = ok && dev_alloc(ctx, &ctx->gridBarrier, 8, error);
-    if (ok) ok = cudaMemset(ctx->gridBarrier, 0, 32) == cudaSuccess;
+    ok = ok && dev_alloc(ctx, &ctx->taggedLogits, kMaxExperts, error);
+    if (ok) ok = cudaMemset(ctx->taggedLogits, 0, kMaxExperts * 8) == cudaSuccess;
+    ok = ok && dev_alloc(ctx, &ctx->gridBarrier, 16, error);
+    if (ok) ok = cudaMemset(ctx->gridBarrier, 0, 64) == cudaSuccess;
     if (ok) {
         void *box = nullptr;
         ok = cudaHostAlloc(&box, 64, cudaHostAllocMapped) == cudaSuccess;

@@ -26,7 +26,7 @@
 // experts).  Long rows are split along K between the warps of a pair (or triple) of one CTA and
 // added in a fixed order, so results do not depend on scheduling.
 //
-// The grid barrier is an arrival counter in global memory; cooperative launch guarantees that all
+// Grid-wide waits poll arrival counters in global memory; cooperative launch guarantees that all
 // CTAs are resident.  Every spin (grid barrier, copy completion) is bounded: on running
 // out it raises the context's error flag and carries on, so the launch always ends.
 //
@@ -62,6 +62,7 @@ struct DecodeArgs {
     const uint32_t *idsIn;  // non-null: routes are given, the router is skipped
     const uint16_t *weightsIn;
     float *logits;
+    unsigned long long *taggedLogits;  // [E] (1 << 32 | logit bits) while valid, 0 otherwise
     uint32_t *ids;
     uint16_t *weights;
     uint16_t *acts, *sharedActs, *h1, *y;
@@ -85,8 +86,6 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) 
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 
-// (barrier memory: [0] the grid barrier's arrival counter, [1] the logits' arrival counter,
-// [2] the count of finished CTAs for the host hand-off)
 // The grid prefetches [base, base+bytes) in 8 KiB pieces.  Piece i belongs to CTA (i + cursor) mod
 // gridDim and to one thread of it, so every SM issues the same share: a bulk prefetch is executed
 // by the issuing SM's copy engine, whose throughput is a small fraction of HBM's.
@@ -102,48 +101,39 @@ __device__ __forceinline__ void prefetch_region(const uint8_t *base, uint64_t by
     cursor += pieces;
 }
 
-// Grid barrier on one 64-bit arrival counter that only grows: an arrival's old value tells its
-// generation, the target is the next multiple of the grid size, and waiting is polling the counter
-// itself — no reset, no host-side state, one round trip after the last arrival.  Split in two so
-// that work that does not depend on the other CTAs (requests for the next phase) sits between
-// arriving and waiting.  One thread arrives and waits; the spin is bounded.
+// Grid-wide synchronisation on 64-bit counters that only grow.  At its start every CTA draws a
+// ticket from counter [3]; ticket / gridDim is the launch's generation g (launches on a context
+// are serialised, so all CTAs of a launch get the same g).  Every launch adds exactly gridDim to
+// each of the counters [0] (shared activations written) and [4] (routed activations written) — also when a mode does not wait on one of them — so "everyone
+// has arrived" is counter >= (g + 1) * gridDim.  An arrival is a release reduction without a
+// return value; a wait polls the counter with acquire loads, bounded.  No reset, no host-side
+// state.  [2] counts finished CTAs for the host hand-off.
+enum : int { kCountShared = 0, kCountDone = 2, kCountTicket = 3, kCountRouted = 4 };
+
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
     unsigned long long v;
     asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
-// The barrier thread is lane 0 of the CTA's last warp (a warp with no requests to issue between
-// arriving and waiting).  knownTarget != 0: the generation is already known from an earlier
-// arrival of this launch, so the arrival is a release reduction without a return value.
+// Called by ONE thread after a CTA-level barrier that covers the writes to publish.
+__device__ __forceinline__ void counter_arrive(unsigned long long *count) {
+    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(count) : "memory");
+}
+// Called by ONE thread; a CTA-level barrier afterwards releases the other threads.
+__device__ __forceinline__ void counter_wait(const unsigned long long *count, unsigned long long target,
+                                             uint32_t *errorFlag) {
+    uint32_t spins = 0;
+    while (ld_acquire_u64(count) < target) {
+        if (++spins > kBarrierSpinLimit) {
+            atomicExch(errorFlag, 9u);
+            break;
+        }
+    }
+    __threadfence();
+}
+// The thread that arrives at and waits for the CTA-wide barriers: lane 0 of the last warp (a warp
+// with no requests to issue between arriving and waiting).
 __device__ __forceinline__ bool is_barrier_thread() { return threadIdx.x == blockDim.x - 32; }
-__device__ __forceinline__ unsigned long long grid_arrive(unsigned long long *count, unsigned long long knownTarget = 0) {
-    __syncthreads();
-    unsigned long long target = knownTarget;
-    if (is_barrier_thread()) {
-        if (knownTarget) {
-            asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(count) : "memory");
-        } else {
-            __threadfence();
-            const unsigned long long old = atomicAdd(count, 1ull);
-            target = (old / gridDim.x + 1ull) * gridDim.x;
-        }
-    }
-    return target;
-}
-__device__ __forceinline__ void grid_wait(const unsigned long long *count, unsigned long long target,
-                                          uint32_t *errorFlag) {
-    if (is_barrier_thread()) {
-        uint32_t spins = 0;
-        while (ld_acquire_u64(count) < target) {
-            if (++spins > kBarrierSpinLimit) {
-                atomicExch(errorFlag, 9u);
-                break;
-            }
-        }
-        __threadfence();
-    }
-    __syncthreads();
-}
 
 __device__ __forceinline__ void stamp(const DecodeArgs &a, int slot) {
     if (a.stamps && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -320,12 +310,15 @@ __device__ __noinline__ void tile_rows(const uint8_t *lo, const uint8_t *hi, con
 // `dstStride` bytes apart in shared memory) with every aligned run of eight stored in the order
 // 0,4,1,5,2,6,3,7, then the fp32 sum of each group of 64 (sums[row * n/64 + group]).  All threads
 // of the CTA take part; ends with a CTA barrier.
+// `first`: the run with index threadIdx.x, already loaded by the caller (or null).
 __device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n, uint8_t *dst, uint32_t dstStride,
-                                            float *sums, bool plainLoads = false) {
+                                            float *sums, bool plainLoads = false, const uint4 *first = nullptr) {
     const int runsPerRow = n >> 3, runs = rows * runsPerRow;
     for (int i = threadIdx.x; i < runs; i += blockDim.x) {
         // plain loads for a source outside global memory (kernel parameters)
-        const uint4 v = plainLoads ? reinterpret_cast<const uint4 *>(src)[i] : __ldcg(reinterpret_cast<const uint4 *>(src) + i);
+        const uint4 v = (first && i == (int)threadIdx.x) ? *first
+                        : plainLoads              ? reinterpret_cast<const uint4 *>(src)[i]
+                                                  : __ldcg(reinterpret_cast<const uint4 *>(src) + i);
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410);
         o.y = __byte_perm(v.x, v.z, 0x7632);
@@ -389,6 +382,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     __shared__ float sWeights[8];
     __shared__ float sScore[8];
     __shared__ __align__(8) uint64_t sCopyBar[kFusedWarps];
+    __shared__ unsigned long long sTarget;  // (generation + 1) * gridDim
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = (int)gridDim.x, cta = (int)blockIdx.x;
@@ -413,6 +407,17 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
         for (int w = 0; w < kFusedWarps; ++w) bar_init(sm_addr(&sCopyBar[w]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // the ticket: drawn now by a thread with nothing to request (warp 9), published to the CTA
+    // further down so that nobody waits for the atomic's round trip here
+    unsigned long long ticket = 0;
+    if (threadIdx.x == 9 * 32) ticket = atomicAdd(a.barrier + kCountTicket, 1ull);
+    // this thread's share of the input row is requested before anything else
+    const bool xPlain = xInline != nullptr;
+    const uint16_t *xSrc = xPlain ? xInline : a.x;
+    uint4 xMine = make_uint4(0, 0, 0, 0);
+    if ((int)threadIdx.x < (D >> 3))
+        xMine = xPlain ? reinterpret_cast<const uint4 *>(xSrc)[threadIdx.x]
+                       : __ldcg(reinterpret_cast<const uint4 *>(xSrc) + threadIdx.x);
     __syncthreads();
     uint32_t cursor = 0;
     stamp(a, 0);
@@ -466,10 +471,8 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     };
 
     // ---------------- phase A: router logits, shared gate/up/GeGLU ----------------
-    // shared gate/up tiles: four warps per tile (K quarters), two tiles per CTA and round
-    const int partA = warp & 3;
-    int tA = warp < kSharedGuWarps ? (warp >> 2) * G + cta : 0x7FFFFFFF;
-    if (tA < tilesSGU) issue_gate_up(sh, a.sharedOff, tA, partA, 4);
+    // The router rows are requested first, alone: top-8 heads the critical path, and the copy
+    // engine serves an SM's requests in order.
     int eA = (!a.idsIn && K > 0 && warp >= kSharedGuWarps && warp < kBigWarps) ? (warp - kSharedGuWarps) * G + cta
                                                                              : 0x7FFFFFFF;
     if (eA < E) {
@@ -479,12 +482,18 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
         }
         __syncwarp();
     }
+    __syncthreads();
+    // shared gate/up tiles: four warps per tile (K quarters), two tiles per CTA and round
+    const int partA = warp & 3;
+    int tA = warp < kSharedGuWarps ? (warp >> 2) * G + cta : 0x7FFFFFFF;
+    if (tA < tilesSGU) issue_gate_up(sh, a.sharedOff, tA, partA, 4);
     const int triple = warp >= kBigWarps ? (warp - kBigWarps) / 3 : 0;
     const int part3 = warp >= kBigWarps ? (warp - kBigWarps) % 3 : 0;
     int tSD = warp >= kBigWarps ? triple * G + cta : 0x7FFFFFFF;
     if (tSD < tilesSD) issue_shared_down(tSD, part3);
     warp_stamp(a, 0, 0);
-    stage_input(xInline ? xInline : a.x, 1, D, xPerm, 0, xSum, xInline != nullptr);
+    stage_input(xSrc, 1, D, xPerm, 0, xSum, xPlain, &xMine);
+    if (threadIdx.x == 9 * 32) sTarget = (ticket / gridDim.x + 1ull) * gridDim.x;
     for (; tA < tilesSGU; tA += (kSharedGuWarps / 4) * G) {
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
@@ -537,7 +546,14 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
         }
 #pragma unroll
         for (int offset = 16; offset >= 1; offset >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
-        if (lane == 0) a.logits[eA] = a.logitBias ? acc + a.logitBias[eA] : acc;
+        if (lane == 0) {
+            const float logit = a.logitBias ? acc + a.logitBias[eA] : acc;
+            a.logits[eA] = logit;
+            // value and validity in one 64-bit store: the readers poll these words
+            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.taggedLogits + eA),
+                         "l"((1ull << 32) | (unsigned long long)__float_as_uint(logit))
+                         : "memory");
+        }
         slot_release();
         const int next = eA + (kBigWarps - kSharedGuWarps) * G;
         if (next < E && lane == 0) {
@@ -550,28 +566,36 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     stamp(a, 1);
 
     // ---------------- top-8 by warps 8..15 while warps 0..7 finish the shared gate/up rows ----------
-    // The logits have their own arrival counter (every CTA arrives once its router rows are
-    // written), so ranking does not wait for the other CTAs' shared rows.
+    // Each logit travels as one 64-bit word (validity | value) that the readers poll, so ranking
+    // waits neither for a counter round trip nor for the other CTAs' shared rows.  The writer
+    // clears its words again in phase C, when every CTA has read them.
     if (K > 0 && !a.idsIn && warp >= kSharedGuWarps) {
         constexpr int kTopkThreads = (kFusedWarps - kSharedGuWarps) * 32;
         const int tid2 = (int)threadIdx.x - kSharedGuWarps * 32;
-        named_barrier(8, kTopkThreads);  // this CTA's logits are written
-        if (tid2 == 0) {
-            __threadfence();
-            unsigned long long *count = a.barrier + 1;
-            const unsigned long long old = atomicAdd(count, 1ull);
-            const unsigned long long target = (old / gridDim.x + 1ull) * gridDim.x;
-            uint32_t spins = 0;
-            while (ld_acquire_u64(count) < target) {
-                if (++spins > kBarrierSpinLimit) {
-                    atomicExch(a.errorFlag, 9u);
-                    break;
+        // one warp fetches the logits, polling the tagged words (four per lane, coalesced) until
+        // every writer's store has shown up
+        if (warp == kSharedGuWarps) {
+            for (int base = 0; base < E; base += 128) {
+                const int e0 = base + 4 * lane;
+                unsigned long long w[4] = {1ull << 32, 1ull << 32, 1ull << 32, 1ull << 32};
+                bool ready = false;
+                for (uint32_t spins = 0; spins < kBarrierSpinLimit && !ready; ++spins) {
+                    if (e0 + 3 < E) {
+                        asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w[0]), "=l"(w[1]) : "l"(a.taggedLogits + e0) : "memory");
+                        asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w[2]), "=l"(w[3]) : "l"(a.taggedLogits + e0 + 2) : "memory");
+                    } else {
+                        for (int i = 0; i < 4; ++i)
+                            if (e0 + i < E)
+                                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[i]) : "l"(a.taggedLogits + e0 + i) : "memory");
+                    }
+                    const bool mine = (w[0] >> 32) && (w[1] >> 32) && (w[2] >> 32) && (w[3] >> 32);
+                    ready = __all_sync(0xFFFFFFFFu, mine);
                 }
+                if (!ready && lane == 0) atomicExch(a.errorFlag, 9u);
+                for (int i = 0; i < 4; ++i)
+                    if (e0 + i < E) sLogits[e0 + i] = __uint_as_float((uint32_t)w[i]);
             }
-            __threadfence();
         }
-        named_barrier(8, kTopkThreads);
-        for (int e = tid2; e < E; e += kTopkThreads) sLogits[e] = __ldcg(a.logits + e);
         if (tid2 < 8) {
             sIds[tid2] = 0u;
             sScore[tid2] = -INFINITY;
@@ -586,12 +610,13 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
                 const int e = idx >> 1, half = idx & 1;
                 const float v = e < E ? sLogits[e] : -INFINITY;
                 const int begin = half * halfSpan, end = min(E, begin + halfSpan);
+                // competitors before e win ties, those after e do not
+                const int mid = min(max(e, begin), end);
                 int rank = 0;
 #pragma unroll 8
-                for (int o = begin; o < end; ++o) {
-                    const float w = sLogits[o];
-                    rank += (w > v || (w == v && o < e)) ? 1 : 0;  // w > -inf follows from v > -inf
-                }
+                for (int o = begin; o < mid; ++o) rank += sLogits[o] >= v ? 1 : 0;
+#pragma unroll 8
+                for (int o = max(mid, e + 1); o < end; ++o) rank += sLogits[o] > v ? 1 : 0;
                 rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
                 if (half == 0 && v > -INFINITY && rank < K) {
                     sIds[rank] = (uint32_t)e;
@@ -618,15 +643,16 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
                 }
             }
         }
-    } else if (K > 0 && a.idsIn && threadIdx.x < K) {
-        sIds[threadIdx.x] = a.idsIn[threadIdx.x];
-        sWeights[threadIdx.x] = bf2f(a.weightsIn[threadIdx.x]);
+    } else {
+        if (K > 0 && a.idsIn && threadIdx.x < K) {
+            sIds[threadIdx.x] = a.idsIn[threadIdx.x];
+            sWeights[threadIdx.x] = bf2f(a.weightsIn[threadIdx.x]);
+        }
     }
     // barrier 1 covers the shared activations; the routed rows are requested between arriving
-    // and waiting (grid_arrive's CTA barrier also publishes the routes to all warps)
-    unsigned long long target1 = 0;
-    if (sh) target1 = grid_arrive(a.barrier);
-    else __syncthreads();
+    // and waiting (the CTA barrier also publishes the routes to all warps)
+    __syncthreads();
+    if (is_barrier_thread()) counter_arrive(a.barrier + kCountShared);
     stamp(a, 2);
     stamp(a, 3);
     const int tilesF = F >> 3;
@@ -648,7 +674,8 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     uint8_t *saPerm = region;
     float *saSum = reinterpret_cast<float *>(region + Fs * 2);
     if (sh) {
-        grid_wait(a.barrier, target1, a.errorFlag);
+        if (is_barrier_thread()) counter_wait(a.barrier + kCountShared, sTarget, a.errorFlag);
+        __syncthreads();
         stage_input(a.sharedActs, 1, Fs, saPerm, 0, saSum);
     }
     for (; tB < tilesRouted; tB += (kBigWarps / 2) * G) {
@@ -709,6 +736,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     warp_stamp(a, 1, 2);
     stamp(a, 4);
     if (K == 0) {
+        if (is_barrier_thread()) counter_arrive(a.barrier + kCountRouted);  // keeps the counters in step
         stamp(a, 5);
         stamp(a, 6);
         return;
@@ -735,13 +763,16 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
         }
     };
     // the weights do not depend on the activations: request them between arriving and waiting
-    // (the barrier thread knows barrier 1's target: barrier 2 is the next generation)
-    const unsigned long long target2 = grid_arrive(a.barrier, target1 ? target1 + gridDim.x : 0ull);
+    __syncthreads();
+    if (is_barrier_thread()) counter_arrive(a.barrier + kCountRouted);
     int tC = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
     if (tC < tilesRD) issue_routed_down(tC);
     warp_stamp(a, 2, 0);
-    grid_wait(a.barrier, target2, a.errorFlag);
+    if (is_barrier_thread()) counter_wait(a.barrier + kCountRouted, sTarget, a.errorFlag);
+    __syncthreads();
     stamp(a, 5);
+    if (!a.idsIn && lane == 0 && warp >= kSharedGuWarps && warp < kBigWarps)
+        for (int e = (warp - kSharedGuWarps) * G + cta; e < E; e += (kBigWarps - kSharedGuWarps) * G) a.taggedLogits[e] = 0ull;
 
     // ---------------- phase C: routed down rows and the combine ----------------
     {
@@ -796,7 +827,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence();
-            const unsigned long long old = atomicAdd(a.barrier + 2, 1ull);
+            const unsigned long long old = atomicAdd(a.barrier + kCountDone, 1ull);
             sLast = (old % gridDim.x == gridDim.x - 1) ? 1u : 0u;
         }
         __syncthreads();
@@ -887,6 +918,7 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.idsIn = idsIn;
     a.weightsIn = weightsIn;
     a.logits = ctx->logits;
+    a.taggedLogits = ctx->taggedLogits;
     a.ids = ctx->ids;
     a.weights = ctx->weights;
     a.acts = ctx->acts;

@@ -113,7 +113,8 @@ struct FFContext {
     uint32_t maxUnits = 0;
     uint32_t *errorFlag = nullptr;          // device: set by a kernel that gave up waiting
     unsigned long long *phaseStamps = nullptr;  // device: 8 phase + 288 per-warp timestamps of the fused decode kernel
-    uint32_t *gridBarrier = nullptr;        // device: four 64-bit counters of the fused decode kernel
+    unsigned long long *taggedLogits = nullptr;  // device: [kMaxExperts] router logits of the fused decode kernel
+    uint32_t *gridBarrier = nullptr;        // device: eight 64-bit counters of the fused decode kernel
     volatile uint32_t *mailbox = nullptr;   // pinned host memory the decode kernel reports to
     uint32_t hostEpoch = 0;
     CUtensorMap *mapScratch = nullptr;
