@@ -652,26 +652,8 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     }
     FF_CUDA_OK(cudaGetLastError(), error);
 
-    const uint32_t maxActive = (uint32_t)std::min<uint64_t>((uint64_t)tokens * c.topK, (uint64_t)E);
-    const uint32_t bound0 = (withShared ? blocks_of(c.sharedF) : 0u) + maxActive * blocks_of(c.f);
-    GemvJob none{};
-    StageAll all;
-    all.in = x;
-    all.stride = xStride;
-    all.rows = tokens;
-    if (!launch_gemv_class<true>(ctx, tokens, ctx->jobs[0], ctx->items[0], &ctx->plan->itemCount[0],
-                                 none, 0, c.d, bound0, stream, error, all))
-        return false;
-    const uint32_t bound1 =
-        (withShared ? blocks_of(c.d) : 0u) + (decodeCombine ? 0u : maxActive * blocks_of(c.d));
-    if (bound1 > 0) {
-        const uint32_t maxCols = withShared ? std::max(c.f, c.sharedF) : c.f;
-        if (!launch_gemv_class<false>(ctx, tokens, ctx->jobs[1], ctx->items[1],
-                                      &ctx->plan->itemCount[1], none, 0, maxCols, bound1, stream,
-                                      error))
-            return false;
-    }
-    return true;
+    // the planned jobs run on the tensor-core block kernels
+    return launch_block_mma(ctx, x, xStride, tokens, withShared, withShared || !decodeCombine, stream, error);
 }
 
 bool launch_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *weights,

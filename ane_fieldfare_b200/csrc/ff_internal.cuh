@@ -182,6 +182,10 @@ bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, c
                           cudaStream_t stream, const char **error);
 
 // ff_decode.cu
+// Gate/up + GeGLU jobs, then down jobs, of a planned 2..16-row block on the tensor-core block kernels.
+bool launch_block_mma(FFContext *ctx, const uint16_t *x, uint32_t xStride, uint32_t tokens, bool withShared,
+                      bool haveDownJobs, cudaStream_t stream, const char **error);
+
 // Host hand-off of the one-token kernel: `inlineX` (host memory) travels in the kernel parameters
 // instead of `x`; the last CTA copies the output to `hostY` (host memory mapped for the device) and
 // writes the error flag and `epoch` to mailbox[1], mailbox[0].
