@@ -612,12 +612,13 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const uint32_t groupsK = args.K / kTileK;
 
     // carve-up: B stages and A stages (1024-aligned), packed stages, then the unit's scales
-    uint32_t aAddr[kStagesLoad], pAddr[kStagesLoad], bAddr[kStagesB];
-    uint32_t cursor = base;
-    for (int s = 0; s < kStagesB; ++s, cursor += kTileBBytes) bAddr[s] = cursor;
-    for (int s = 0; s < kStagesLoad; ++s, cursor += kTileABytes) aAddr[s] = cursor;
-    for (int s = 0; s < kStagesLoad; ++s, cursor += kTilePackedBytes) pAddr[s] = cursor;
-    uint8_t *scalesPtr = gemmSmemRaw + (cursor - rawBase);  // [256 rows][groupsK][2] bf16
+    // (stage addresses are computed, not tabulated: an array indexed by the running stage would
+    // live in local memory and put a load in front of every MMA and every dequantized tile)
+    const uint32_t bBase = base, aBase = bBase + kStagesB * kTileBBytes, pBase = aBase + kStagesLoad * kTileABytes;
+    auto bAddrOf = [&](uint32_t s) { return bBase + s * kTileBBytes; };
+    auto aAddrOf = [&](uint32_t s) { return aBase + s * kTileABytes; };
+    auto pAddrOf = [&](uint32_t s) { return pBase + s * kTilePackedBytes; };
+    uint8_t *scalesPtr = gemmSmemRaw + (pBase + kStagesLoad * kTilePackedBytes - rawBase);  // [256 rows][groupsK][2] bf16
 
     const uint32_t barBase = smem_u32(barriers);
     auto barLoadFull = [&](int s) { return barBase + 8u * (uint32_t)s; };
@@ -675,13 +676,13 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         break;
                     }
                     mbar_expect_tx(barLoadFull(stage), kTileABytes + kTilePackedBytes);
-                    tma_load_2d(aAddr[stage], &mapA, (int)(g * kTileK), row0, barLoadFull(stage));
+                    tma_load_2d(aAddrOf(stage), &mapA, (int)(g * kTileK), row0, barLoadFull(stage));
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const CUtensorMap *map = (MODE == kModeGateUp && q >= 2) ? &mapW1 : &mapW0;
                         const int wRow = MODE == kModeGateUp ? (int)nt * 128 + (q & 1) * 64
                                                              : (int)nt * 256 + q * 64;
-                        tma_load_3d(pAddr[stage] + (uint32_t)q * (kTilePackedBytes / 4), map,
+                        tma_load_3d(pAddrOf(stage) + (uint32_t)q * (kTilePackedBytes / 4), map,
                                     (int)(g * (kTileK / 2)), wRow, (int)tile.expert, barLoadFull(stage));
                     }
                     if (++stage == kStagesLoad) {
@@ -707,8 +708,8 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t descA = umma_desc_sw128(aAddr[stage]);
-                    const uint64_t descB = umma_desc_sw128(bAddr[bStage]);
+                    const uint64_t descA = umma_desc_sw128(aAddrOf(stage));
+                    const uint64_t descB = umma_desc_sw128(bAddrOf(bStage));
 #pragma unroll
                     for (uint32_t kk = 0; kk < kTileK / 16; ++kk) {
                         // 32 bytes (>> 4 = 2) further along K for every 16-element slice
@@ -785,8 +786,8 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 uint32_t w[4];
                 asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(pAddr[stage] + (uint32_t)r * 32u + (uint32_t)half * 16u));
-                const uint32_t bBase = bAddr[bStage];
+                             : "r"(pAddrOf(stage) + (uint32_t)r * 32u + (uint32_t)half * 16u));
+                const uint32_t bBase = bAddrOf(bStage);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t o[4];
