@@ -10,8 +10,8 @@
 // bulk asynchronous copies into the warp's shared-memory slot, then every group of 64 codes is
 // multiplied as bf16(16+q) and scaled (acc += s * sum((16+q) x) + (b - 16 s) * sum(x)).  All parts
 // of a task accumulate in the same registers, so no partial sums cross warps and results do not
-// depend on scheduling.  Persistent CTAs, eight warps each, deal tasks round robin; the eight
-// slots per SM keep about 100 KB of weights in flight.
+// depend on scheduling.  Persistent CTAs of 16 (gate/up) or 10 (down) warps deal tasks round robin;
+// the slots of an SM keep 100 KB and more of weights in flight.
 //
 // Gate/up jobs read the block's input rows, staged once per CTA as bf16 with every aligned run of
 // eight in the order 0,4,1,5,2,6,3,7 (the order the MMA operands use), with their per-group sums.
@@ -28,8 +28,10 @@
 
 namespace ff {
 
-constexpr int kBlockThreads = 256;
-constexpr int kBlockWarps = kBlockThreads / 32;
+// warps (= slots) per CTA: the gate/up kernel shares its shared memory with the staged input rows
+// and takes short K parts in many slots; the down kernel's slots also hold the input pieces
+constexpr int kGateUpWarps = 16;
+constexpr int kDownWarps = 10;
 constexpr int kMaxBlockJobs = kMaxExperts + 1;
 
 struct BlockArgs {
@@ -104,7 +106,8 @@ __device__ __noinline__ void tile_rows_cols(const uint8_t *lo, const uint8_t *hi
 }
 
 template <bool DUAL>
-__global__ void __launch_bounds__(kBlockThreads, 1) k_block_mma(const BlockArgs a) {
+__global__ void __launch_bounds__((DUAL ? kGateUpWarps : kDownWarps) * 32, 1) k_block_mma(const BlockArgs a) {
+    constexpr int kBlockWarps = DUAL ? kGateUpWarps : kDownWarps;
     extern __shared__ __align__(128) uint8_t smemRaw[];
     __shared__ uint32_t sPrefix[kMaxBlockJobs + 1];
     __shared__ __align__(8) uint64_t sCopyBar[kBlockWarps];
@@ -231,6 +234,7 @@ struct BlockLayout {
 // whose widest matrix has `cols` columns.  Picks the largest K part that fits 227 KB.
 static bool block_layout(bool dual, uint32_t cols, uint32_t rows, BlockLayout *out) {
     const uint32_t groups = cols / 64;
+    const uint32_t kBlockWarps = dual ? kGateUpWarps : kDownWarps;
     for (uint32_t mpg = std::min(groups, 22u); mpg >= 1; --mpg) {
         BlockLayout l{};
         l.maxPartGroups = mpg;
@@ -242,7 +246,7 @@ static bool block_layout(bool dual, uint32_t cols, uint32_t rows, BlockLayout *o
         l.slotBytes = (slot + 127u) & ~127u;
         l.slotsOffset = dual ? ((rows * l.xPitch + rows * groups * 4 + 127u) & ~127u) : 0u;
         l.total = (size_t)l.slotsOffset + (size_t)kBlockWarps * l.slotBytes;
-        if (l.total <= 227 * 1024) {
+        if (l.total + 2048 <= 227 * 1024) {  // 2 KB kept for the static arrays
             *out = l;
             return true;
         }
@@ -281,7 +285,7 @@ static bool launch_block_class(FFContext *ctx, const GemvJob *jobs, const uint32
         configured[DUAL ? 1 : 0][slot] = lay.total;
     }
     LaunchScope scope(ctx, stream, name);
-    k_block_mma<DUAL><<<ctx->smCount, kBlockThreads, lay.total, stream>>>(a);
+    k_block_mma<DUAL><<<ctx->smCount, (DUAL ? kGateUpWarps : kDownWarps) * 32, lay.total, stream>>>(a);
     FF_CUDA_OK(cudaGetLastError(), error);
     return true;
 }

@@ -64,7 +64,7 @@ void ff_destroy(FFContext *ctx) {
     cudaDeviceSynchronize();
     for (auto &L : ctx->layers) free_layer(L);
     void *ptrs[] = {ctx->logits, ctx->ids, ctx->weights, ctx->plan, ctx->jobs[0], ctx->jobs[1],
-                    ctx->items[0], ctx->items[1], ctx->acts, ctx->sharedActs, ctx->h1,
+                    ctx->acts, ctx->sharedActs, ctx->h1,
                     ctx->partials, ctx->xDev, ctx->yDev, ctx->xSorted, ctx->sortedPairs,
                     ctx->expertOffsets, ctx->blockCounts, ctx->units, ctx->unitCount,
                     ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch, ctx->taggedLogits};
@@ -121,10 +121,6 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     const size_t T = c.maxTokens, K = c.topK;
     const size_t smallT = std::min<size_t>(T, kMaxGemvRows);
     const size_t planExperts = std::min<size_t>(c.experts, kMaxGemvRows * K);
-    const size_t rowsPerItem = 32;
-    auto blocks = [&](size_t rows) { return (rows + rowsPerItem - 1) / rowsPerItem; };
-    ctx->maxItems = (uint32_t)std::max(blocks(c.sharedF) + planExperts * blocks(c.f),
-                                       (1 + planExperts) * blocks(c.d));
     bool ok = cudaStreamCreateWithFlags(&ctx->hostStream, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && dev_alloc(ctx, &ctx->logits, smallT * kMaxExperts, error);
     ok = ok && dev_alloc(ctx, &ctx->ids, T * K, error);
@@ -132,8 +128,6 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     ok = ok && dev_alloc(ctx, &ctx->plan, 1, error);
     ok = ok && dev_alloc(ctx, &ctx->jobs[0], 1 + planExperts, error);
     ok = ok && dev_alloc(ctx, &ctx->jobs[1], 1 + planExperts, error);
-    ok = ok && dev_alloc(ctx, &ctx->items[0], ctx->maxItems, error);
-    ok = ok && dev_alloc(ctx, &ctx->items[1], ctx->maxItems, error);
     ok = ok && dev_alloc(ctx, &ctx->acts, (T * K + 256) * c.f, error);  // +256: a GEMM row tile may overhang
     ok = ok && dev_alloc(ctx, &ctx->sharedActs, (T + 256) * c.sharedF, error);
     ok = ok && dev_alloc(ctx, &ctx->h1, T * c.d, error);

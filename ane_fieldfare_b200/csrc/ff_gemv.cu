@@ -234,7 +234,6 @@ struct PlanArgs {
     uint16_t *partials;       // null in decode mode: no routed down jobs
     uint16_t *sharedOut;
     GemvJob *jobs0, *jobs1;
-    uint32_t *items0, *items1;
     RoutePlan *plan;
     int buildPlan;            // 0: top-K only
 };
@@ -246,7 +245,6 @@ struct PlanArgs {
 __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
     __shared__ uint32_t sIds[kMaxGemvRows * 8];
     __shared__ uint32_t sPos[kMaxExperts];
-    __shared__ uint32_t sActive;
     const int warp = threadIdx.x >> 5;
     const int routes = a.T * a.K;
     if (a.logits) {
@@ -262,28 +260,53 @@ __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
     if (!a.buildPlan) return;
     __syncthreads();
     const int e = threadIdx.x;
+    // the routes that chose expert e, as bit masks over the (token, rank) index (at most 128 routes)
+    uint32_t mask[4] = {0u, 0u, 0u, 0u};
+    if (e < a.E) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+#pragma unroll 8
+            for (int b = 0; b < 32; ++b) {
+                const int r = w * 32 + b;
+                if (r < routes && sIds[r] == (uint32_t)e) mask[w] |= 1u << b;
+            }
+        }
+    }
+    // a token's routes are distinct experts, so an expert is chosen by at most T routes; repeats
+    // beyond that are dropped rather than overrunning the row class
     uint32_t list[kMaxGemvRows];
     int n = 0;
-    if (e < a.E) {
-        // a token's routes are distinct experts, so an expert is chosen by at most T routes;
-        // repeats beyond that are dropped rather than overrunning the row class
-        for (int r = 0; r < routes; ++r)
-            if (sIds[r] == (uint32_t)e && n < a.T) list[n++] = (uint32_t)r;
-        sPos[e] = n > 0 ? 1u : 0u;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t run = 0;
-        for (int i = 0; i < a.E; ++i) {
-            const uint32_t flag = sPos[i];
-            sPos[i] = run;
-            run += flag;
+#pragma unroll
+    for (int i = 0; i < kMaxGemvRows; ++i) {
+        uint32_t r = 0;
+        bool found = false;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            if (!found && mask[w]) {
+                const int b = __ffs((int)mask[w]) - 1;
+                mask[w] &= mask[w] - 1u;
+                r = (uint32_t)(w * 32 + b);
+                found = true;
+            }
         }
-        sActive = run;
+        list[i] = r;
+        if (found && i < a.T) n = i + 1;
     }
+    // position of expert e among the active experts: ballots inside a warp, warp totals through
+    // shared memory
+    const bool isActive = e < a.E && n > 0;
+    const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, isActive);
+    const int lane = threadIdx.x & 31;
+    if (lane == 0) sPos[warp] = __popc(ballot);
     __syncthreads();
+    uint32_t before = 0, active = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+        const uint32_t c = sPos[w];
+        if (w < warp) before += c;
+        active += c;
+    }
+    const uint32_t myPos = before + __popc(ballot & ((1u << lane) - 1u));
     const uint32_t sharedJobs = a.shared ? 1u : 0u;
-    const uint32_t active = sActive;
     if (e < a.E && n > 0) {
         const uint8_t *blob = a.experts + (size_t)e * a.stride;
         GemvJob j0{};
@@ -305,7 +328,7 @@ __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
             j0.inRow[i] = i < n ? list[i] / (uint32_t)a.K : 0u;
             j0.outRow[i] = i < n ? list[i] : 0u;
         }
-        a.jobs0[sharedJobs + sPos[e]] = j0;
+        a.jobs0[sharedJobs + myPos] = j0;
         if (a.partials) {
             GemvJob j1{};
             j1.w0 = blob + a.off.downWOff;
@@ -322,7 +345,7 @@ __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
                 j1.inRow[i] = i < n ? list[i] : 0u;
                 j1.outRow[i] = i < n ? list[i] : 0u;
             }
-            a.jobs1[sharedJobs + sPos[e]] = j1;
+            a.jobs1[sharedJobs + myPos] = j1;
         }
     }
     if (threadIdx.x == 0 && a.shared) {
@@ -358,41 +381,12 @@ __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
         a.jobs0[0] = j0;
         a.jobs1[0] = j1;
     }
-    // work items: shared job first, then every routed job, each cut into row blocks
-    const uint32_t sharedBlocks0 = a.shared ? (uint32_t)((a.Fs + kRowsPerItem - 1) / kRowsPerItem) : 0u;
-    const uint32_t routedBlocks0 = (uint32_t)((a.F + kRowsPerItem - 1) / kRowsPerItem);
-    const uint32_t total0 = sharedBlocks0 + active * routedBlocks0;
-    for (uint32_t i = threadIdx.x; i < total0; i += blockDim.x) {
-        uint32_t job, block;
-        if (i < sharedBlocks0) {
-            job = 0;
-            block = i;
-        } else {
-            job = sharedJobs + (i - sharedBlocks0) / routedBlocks0;
-            block = (i - sharedBlocks0) % routedBlocks0;
-        }
-        a.items0[i] = (job << 16) | block;
-    }
-    const uint32_t downBlocks = (uint32_t)((a.D + kRowsPerItem - 1) / kRowsPerItem);
-    const uint32_t sharedBlocks1 = a.shared ? downBlocks : 0u;
     const uint32_t routedJobs1 = a.partials ? active : 0u;
-    const uint32_t total1 = sharedBlocks1 + routedJobs1 * downBlocks;
-    for (uint32_t i = threadIdx.x; i < total1; i += blockDim.x) {
-        uint32_t job, block;
-        if (i < sharedBlocks1) {
-            job = 0;
-            block = i;
-        } else {
-            job = sharedJobs + (i - sharedBlocks1) / downBlocks;
-            block = (i - sharedBlocks1) % downBlocks;
-        }
-        a.items1[i] = (job << 16) | block;
-    }
     if (threadIdx.x == 0) {
         a.plan->jobCount[0] = sharedJobs + active;
         a.plan->jobCount[1] = sharedJobs + routedJobs1;
-        a.plan->itemCount[0] = total0;
-        a.plan->itemCount[1] = total1;
+        a.plan->itemCount[0] = 0;
+        a.plan->itemCount[1] = 0;
         a.plan->activeExperts = active;
     }
 }
@@ -535,13 +529,9 @@ static bool launch_gemv_class(FFContext *ctx, uint32_t rowsClass, const GemvJob 
                               const GemvJob &inlineJob, uint32_t inlineItems, uint32_t maxCols,
                               uint32_t itemBound, cudaStream_t stream, const char **error,
                               const StageAll &all = StageAll()) {
-#define FF_GEMV_DISPATCH(NTV)                                                                        \
-    return all.in ? launch_gemv_kernel<NTV, DUAL, true>(ctx, jobs, items, itemCountPtr, inlineJob,     \
-                                                        inlineItems, maxCols, itemBound, all, stream, \
-                                                        error)                                        \
-                  : launch_gemv_kernel<NTV, DUAL, false>(ctx, jobs, items, itemCountPtr, inlineJob,    \
-                                                         inlineItems, maxCols, itemBound, all, stream, \
-                                                         error)
+#define FF_GEMV_DISPATCH(NTV)                                                                   \
+    return launch_gemv_kernel<NTV, DUAL, false>(ctx, jobs, items, itemCountPtr, inlineJob, inlineItems, \
+                                                maxCols, itemBound, all, stream, error)
     if (rowsClass <= 1) FF_GEMV_DISPATCH(1);
     if (rowsClass <= 2) FF_GEMV_DISPATCH(2);
     if (rowsClass <= 4) FF_GEMV_DISPATCH(4);
@@ -642,8 +632,6 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     a.sharedOut = sharedOut;
     a.jobs0 = ctx->jobs[0];
     a.jobs1 = ctx->jobs[1];
-    a.items0 = ctx->items[0];
-    a.items1 = ctx->items[1];
     a.plan = ctx->plan;
     a.buildPlan = 1;
     {

@@ -94,8 +94,6 @@ struct FFContext {
     uint16_t *weights = nullptr;    // [maxTokens][topK]
     ff::RoutePlan *plan = nullptr;
     ff::GemvJob *jobs[2] = {nullptr, nullptr};
-    uint32_t *items[2] = {nullptr, nullptr};
-    uint32_t maxItems = 0;
     uint16_t *acts = nullptr;       // [maxTokens*topK][f]
     uint16_t *sharedActs = nullptr; // [maxTokens][sharedF]
     uint16_t *h1 = nullptr;         // [maxTokens][d]

@@ -135,13 +135,16 @@ __device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n
                                             uint32_t srcStride = 0) {
     const int runsPerRow = n >> 3, runs = rows * runsPerRow;
     const uint32_t rowRuns = srcStride ? srcStride >> 3 : (uint32_t)runsPerRow;  // 16-byte units between source rows
-    for (int i = threadIdx.x; i < runs; i += blockDim.x) {
+    // two runs per thread and step, both loads issued before either is used
+    auto fetch = [&](int i) {
         const int sr = i / runsPerRow;
         const size_t si = (size_t)sr * rowRuns + (size_t)(i - sr * runsPerRow);
         // plain loads for a source outside global memory (kernel parameters)
-        const uint4 v = (first && i == (int)threadIdx.x) ? *first
-                        : plainLoads              ? reinterpret_cast<const uint4 *>(src)[si]
-                                                  : __ldcg(reinterpret_cast<const uint4 *>(src) + si);
+        return (first && i == (int)threadIdx.x) ? *first
+               : plainLoads                      ? reinterpret_cast<const uint4 *>(src)[si]
+                                                 : __ldcg(reinterpret_cast<const uint4 *>(src) + si);
+    };
+    auto put = [&](int i, const uint4 &v) {
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410);
         o.y = __byte_perm(v.x, v.z, 0x7632);
@@ -149,6 +152,14 @@ __device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n
         o.w = __byte_perm(v.y, v.w, 0x7632);
         const int r = i / runsPerRow;
         *reinterpret_cast<uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16) = o;
+    };
+    for (int i = threadIdx.x; i < runs; i += 2 * blockDim.x) {
+        const int j = i + blockDim.x;
+        const uint4 v0 = fetch(i);
+        uint4 v1 = make_uint4(0, 0, 0, 0);
+        if (j < runs) v1 = fetch(j);
+        put(i, v0);
+        if (j < runs) put(j, v1);
     }
     __syncthreads();
     // eight lanes per group: each sums one run of eight in stored order, then a fixed butterfly;

@@ -753,21 +753,32 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
             const uint32_t nt = u % args.nTiles;
             const uint32_t wRow = MODE == kModeGateUp ? nt * 128 + (uint32_t)(r & 127) : nt * 256 + (uint32_t)r;
             const uint8_t *blob = args.blobBase + (size_t)tile.expert * args.expertStride;
-            // the row's two threads each fetch half of its scale/bias pairs into shared memory
+            // the row's two threads each fetch one contiguous half of its scale/bias pairs into shared
+            // memory, eight pairs (sixteen independent loads) at a time so that the load latency is
+            // paid per batch, not per pair
             __syncwarp();
-            if (wRow < args.N) {
-                const uint16_t *sg = reinterpret_cast<const uint16_t *>(blob + args.scaleOff[matrix]) +
-                                     (size_t)wRow * groupsK;
-                const uint16_t *bg = reinterpret_cast<const uint16_t *>(blob + args.biasOff[matrix]) +
-                                     (size_t)wRow * groupsK;
-                for (uint32_t g = (uint32_t)half; g < groupsK; g += 2) {
-                    rowScales[2 * g] = sg[g];
-                    rowScales[2 * g + 1] = bg[g];
-                }
-            } else {
-                for (uint32_t g = (uint32_t)half; g < groupsK; g += 2) {
-                    rowScales[2 * g] = 0;
-                    rowScales[2 * g + 1] = 0;
+            {
+                const uint32_t perHalf = (groupsK + 1) >> 1;
+                const uint32_t gBegin = (uint32_t)half * perHalf, gEnd = min(groupsK, gBegin + perHalf);
+                uint32_t *dst32 = reinterpret_cast<uint32_t *>(rowScales);
+                if (wRow < args.N) {
+                    const uint16_t *sg = reinterpret_cast<const uint16_t *>(blob + args.scaleOff[matrix]) +
+                                         (size_t)wRow * groupsK;
+                    const uint16_t *bg = reinterpret_cast<const uint16_t *>(blob + args.biasOff[matrix]) +
+                                         (size_t)wRow * groupsK;
+                    for (uint32_t g0 = gBegin; g0 < gEnd; g0 += 8) {
+                        uint32_t v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const uint32_t g = min(g0 + (uint32_t)i, gEnd - 1);
+                            v[i] = (uint32_t)__ldg(sg + g) | ((uint32_t)__ldg(bg + g) << 16);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (g0 + (uint32_t)i < gEnd) dst32[g0 + i] = v[i];
+                    }
+                } else {
+                    for (uint32_t g = gBegin; g < gEnd; ++g) dst32[g] = 0u;
                 }
             }
             __syncwarp();

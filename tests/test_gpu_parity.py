@@ -245,6 +245,15 @@ def test_verify_partials_and_layer(tiny, full, oracle, rows):
         pairs, n = oracle.make_pairs(ref_ids, ref_w, rows, L.topK)
         want_p = oracle.route_partials(ld, x, pairs, n, rows)
         assert_layer_close(hp.bf16_numpy(partials), want_p, oracle, f"partials rows={rows}")
+        if rows == 8:
+            # input rows with a stride wider than the hidden size give the same bits
+            wide = torch.zeros((rows, L.d + 64), dtype=torch.bfloat16, device=ctx.device)
+            wide[:, :L.d] = xd
+            partials2 = torch.full_like(partials, -99.0)
+            hp.PrefillGroupedRoutedMoE(ctx).encodeVerifyBound(None, 0, wide, ids, partials2, rows,
+                                                              hiddenStrideElements=L.d + 64)
+            torch.cuda.synchronize()
+            assert torch.equal(partials2, partials)
         if rows > 1:
             y = ctx.moeLayer(0, xd)
             torch.cuda.synchronize()
