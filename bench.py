@@ -288,7 +288,7 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             "last_layer_rows_received_per_rank": [int(r.item()) for r in rows],
             "output_finite": finite, "device_error_flag": int(err),
             "collective": "NCCL all_to_all_single (dispatch + combine per layer)",
-            "placement": "experts assigned to ranks by greedy balancing of the router prior"}
+            "placement": "experts assigned to ranks by greedy balancing of a load estimated from the router on seeded rows"}
 
 
 def run_ours(args):
