@@ -133,32 +133,84 @@ __device__ void pf_warp_topk(const float *logits, int E, int K, const uint16_t *
 }
 
 // Each warp owns kRouterTokens tokens and walks the experts eight at a time with a register tile
-// of kRouterTokens x 8 running sums, so a router row fetched from L2/L1 feeds 4 tokens and an
+// of kRouterTokens x 8 running sums, so a router row (read from the CTA's slice buffer) feeds 4 tokens and an
 // input chunk read from shared memory feeds 8 experts.  Per (token, expert) the chain is exactly
 // the single-row kernel's: lane l, chunks i ascending, elements ascending, then the butterfly.
 constexpr int kRouterTokens = 4;   // tokens per warp
 constexpr int kRouterExperts = 8;  // experts per register tile
 
+// Router rows of a slice of eight experts come into shared memory by one bulk copy (two buffers,
+// completion on an mbarrier each) and feed every warp of the CTA: the router matrix is read once
+// per 16 tokens instead of once per 4.
+__device__ __forceinline__ void rt_bar_init(uint32_t bar) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void rt_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool rt_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 __global__ void __launch_bounds__(kRouterWarps * 32)
 k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const uint16_t *gain,
               const uint16_t *x, uint32_t xStride, int T, int E, int D, int K, uint32_t *ids,
-              uint16_t *weights, float *logitsOut) {
-    extern __shared__ uint8_t rsmRaw[];
+              uint16_t *weights, float *logitsOut, uint32_t *errorFlag) {
+    extern __shared__ __align__(128) uint8_t rsmRaw[];
+    __shared__ __align__(8) uint64_t sliceBar[2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // per warp: kRouterTokens input rows as bf16, then kRouterTokens x kMaxExperts logits
+    // two slice buffers (kRouterExperts rows each), then per warp: kRouterTokens input rows as bf16
+    // and kRouterTokens x kMaxExperts logits
+    const size_t sliceBytes = (size_t)kRouterExperts * D * 2;
     const size_t perWarp = (size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4;
-    uint16_t *xs = reinterpret_cast<uint16_t *>(rsmRaw + warp * perWarp);
-    float *lg = reinterpret_cast<float *>(rsmRaw + warp * perWarp + (size_t)kRouterTokens * D * 2);
+    uint8_t *warpBase = rsmRaw + 2 * sliceBytes + warp * perWarp;
+    uint16_t *xs = reinterpret_cast<uint16_t *>(warpBase);
+    float *lg = reinterpret_cast<float *>(warpBase + (size_t)kRouterTokens * D * 2);
+    const uint32_t barBase = (uint32_t)__cvta_generic_to_shared(&sliceBar[0]);
+    auto barOf = [&](int slice) { return barBase + 8u * (uint32_t)(slice & 1); };
+    const uint32_t bufAddr = (uint32_t)__cvta_generic_to_shared(rsmRaw);
+    const int nSlices = (E + kRouterExperts - 1) / kRouterExperts;
+    auto request = [&](int slice) {
+        const int rows = min(kRouterExperts, E - slice * kRouterExperts);
+        rt_copy(bufAddr + (uint32_t)((slice & 1) * sliceBytes), W + (size_t)slice * kRouterExperts * D,
+                (uint32_t)((size_t)rows * D * 2), barOf(slice));
+    };
+    if (threadIdx.x == 0) {
+        rt_bar_init(barOf(0));
+        rt_bar_init(barOf(1));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        request(0);
+        if (nSlices > 1) request(1);
+    }
     const int t0 = (blockIdx.x * kRouterWarps + warp) * kRouterTokens;
-    if (t0 >= T) return;
-    const int nTok = min(kRouterTokens, T - t0);
+    const int nTok = max(0, min(kRouterTokens, T - t0));
     for (int tt = 0; tt < kRouterTokens; ++tt) {
-        const uint16_t *xr = x + (size_t)(t0 + min(tt, nTok - 1)) * xStride;
+        const uint16_t *xr = x + (size_t)min(t0 + min(tt, max(nTok, 1) - 1), T - 1) * xStride;
         for (int i = lane * 8; i < D; i += 256)
             *reinterpret_cast<uint4 *>(xs + (size_t)tt * D + i) = *reinterpret_cast<const uint4 *>(xr + i);
     }
-    __syncwarp();
+    __syncthreads();
     for (int e0 = 0; e0 < E; e0 += kRouterExperts) {
+        const int slice = e0 / kRouterExperts;
+        {
+            bool done = false;
+            for (uint32_t spin = 0; spin < (1u << 22) && !done; ++spin) done = rt_try_wait(barOf(slice), (uint32_t)(slice >> 1) & 1u);
+            if (!done && lane == 0) atomicExch(errorFlag, 11u);
+        }
+        const uint16_t *Ws = reinterpret_cast<const uint16_t *>(rsmRaw + (size_t)(slice & 1) * sliceBytes);
         // running sums of two tokens share one packed fp32 pair (fma.rn.f32x2 = two independent fp32
         // FMAs), so every (token, expert) chain is the scalar chain bit for bit at half the issue
         uint64_t acc[kRouterTokens / 2][kRouterExperts];
@@ -194,8 +246,8 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
             }
 #pragma unroll
             for (int ee = 0; ee < kRouterExperts; ++ee) {
-                const int e = min(e0 + ee, E - 1);
-                const uint4 wv = *reinterpret_cast<const uint4 *>(W + (size_t)e * D + base);
+                const int er = min(ee, E - 1 - e0);  // row of the slice (the last slice may be short)
+                const uint4 wv = *reinterpret_cast<const uint4 *>(Ws + (size_t)er * D + base);
                 const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -226,6 +278,10 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
                     lg[(2 * tp + 1) * kMaxExperts + e] = bias ? v1 + bias[e] : v1;
                 }
             }
+        // every warp is done with this buffer: the slice after next may land in it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (threadIdx.x == 0 && slice + 2 < nSlices) request(slice + 2);
     }
     __syncwarp();
     for (int tt = 0; tt < nTok; ++tt) {
@@ -240,8 +296,10 @@ bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *
                            uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
                            cudaStream_t stream, const char **error) {
     const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
-    const size_t smem = (size_t)kRouterWarps * ((size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4);
-    if (smem > 200 * 1024) return fail(error, "model width too large for the router's shared memory");
+    const size_t smem = 2 * (size_t)kRouterExperts * D * 2 +
+                        (size_t)kRouterWarps * ((size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4);
+    if (smem > 225 * 1024) return fail(error, "model width too large for the router's shared memory");
+    if (D % 8) return fail(error, "hidden size must be a multiple of 8");
     static size_t configured[8] = {0};
     if (configured[ctx->device & 7] != smem) {
         FF_CUDA_OK(cudaFuncSetAttribute(k_router_rows, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -254,7 +312,7 @@ bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *
         LaunchScope scope(ctx, stream, "router_rows");
         k_router_rows<<<(tokens + perCta - 1) / perCta, kRouterWarps * 32, smem, stream>>>(
             L.routerW, L.routerScale, L.logitBias, L.gain, x, xStride, (int)tokens, E, D,
-            (int)ctx->cfg.topK, ids, weights, logits);
+            (int)ctx->cfg.topK, ids, weights, logits, ctx->errorFlag);
     }
     FF_CUDA_OK(cudaGetLastError(), error);
     return true;
