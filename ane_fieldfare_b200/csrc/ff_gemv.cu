@@ -161,16 +161,17 @@ k_router_logits(const uint16_t *W, const uint16_t *scale, const float *bias, con
 // Warp-wide top-K over E <= 256 logits held four-plus per lane: K rounds of argmax (higher score,
 // then lower expert id), softmax over the selected scores, times the per-expert gain.  Selection
 // rule and softmax: Metal/MoE/moe.metal:186-237,269-319.
+// sharedIds: optional copy of the ids in shared memory.
 __device__ void warp_topk(const float *logits, int E, int K, const uint16_t *gain, uint32_t *ids,
-                          uint16_t *weights) {
+                          uint16_t *weights, uint32_t *sharedIds = nullptr) {
     const int lane = threadIdx.x & 31;
     float v[8];
-    bool live[8];
+    uint32_t live = 0;  // bit j: candidate j of this lane is still in the race (a register, not an indexed array)
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int e = j * 32 + lane;
         v[j] = e < E ? logits[e] : -INFINITY;
-        live[j] = e < E && v[j] > -INFINITY;
+        if (e < E && v[j] > -INFINITY) live |= 1u << j;
     }
     float topScore[8];
     uint32_t topIdx[8];
@@ -181,7 +182,7 @@ __device__ void warp_topk(const float *logits, int E, int K, const uint16_t *gai
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const uint32_t e = (uint32_t)(j * 32 + lane);
-                if (live[j] && (v[j] > best || (v[j] == best && e < bestE))) {
+                if (((live >> j) & 1u) && (v[j] > best || (v[j] == best && e < bestE))) {
                     best = v[j];
                     bestE = e;
                 }
@@ -196,22 +197,29 @@ __device__ void warp_topk(const float *logits, int E, int K, const uint16_t *gai
                 bestE = oe;
             }
         }
-        if (bestE != 0xFFFFFFFFu && (bestE & 31u) == (uint32_t)lane) live[bestE >> 5] = false;
+        if (bestE != 0xFFFFFFFFu && (bestE & 31u) == (uint32_t)lane) live &= ~(1u << (bestE >> 5));
         topIdx[r] = bestE == 0xFFFFFFFFu ? 0u : bestE;
         topScore[r] = bestE == 0xFFFFFFFFu ? -INFINITY : best;
     }
-    if (lane == 0) {
-        float ex[8], sum = 0.0f;
-        for (int r = 0; r < K; ++r) {
-            ex[r] = expf(topScore[r] - topScore[0]);
-            sum += ex[r];
+    // softmax over the chosen scores: lane r holds route r; exponentials in parallel, the sum in
+    // rank order (the same additions as a serial loop)
+    float myScore = -INFINITY;
+    uint32_t myIdx = 0;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+        if (lane == r) {
+            myScore = topScore[r];
+            myIdx = topIdx[r];
         }
-        for (int r = 0; r < K; ++r) {
-            float w = ex[r] / sum;
-            if (gain) w = w * bf2f(gain[topIdx[r]]);
-            ids[r] = topIdx[r];
-            weights[r] = f2bf(w);
-        }
+    const float ex = lane < K ? expf(myScore - topScore[0]) : 0.0f;
+    float sum = 0.0f;
+    for (int r = 0; r < K; ++r) sum += __shfl_sync(0xFFFFFFFFu, ex, r);
+    if (lane < K) {
+        float w = ex / sum;
+        if (gain) w = w * bf2f(gain[myIdx]);
+        ids[lane] = myIdx;
+        weights[lane] = f2bf(w);
+        if (sharedIds) sharedIds[lane] = myIdx;
     }
 }
 
@@ -245,52 +253,45 @@ struct PlanArgs {
 __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
     __shared__ uint32_t sIds[kMaxGemvRows * 8];
     __shared__ uint32_t sPos[kMaxExperts];
+    __shared__ uint32_t sCount[kMaxExperts];
+    __shared__ __align__(16) uint8_t sList[kMaxExperts * kMaxGemvRows];  // route numbers (< 128)
     const int warp = threadIdx.x >> 5;
     const int routes = a.T * a.K;
     if (a.logits) {
         if (warp < a.T) {
             warp_topk(a.logits + (size_t)warp * a.E, a.E, a.K, a.gain, a.idsOut + warp * a.K,
-                      a.weightsOut + warp * a.K);
+                      a.weightsOut + warp * a.K, sIds + warp * a.K);
         }
-        __syncthreads();
-        for (int i = threadIdx.x; i < routes; i += blockDim.x) sIds[i] = a.idsOut[i];
     } else {
         for (int i = threadIdx.x; i < routes; i += blockDim.x) sIds[i] = a.idsIn[i];
     }
     if (!a.buildPlan) return;
     __syncthreads();
-    const int e = threadIdx.x;
-    // the routes that chose expert e, as bit masks over the (token, rank) index (at most 128 routes)
-    uint32_t mask[4] = {0u, 0u, 0u, 0u};
-    if (e < a.E) {
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-#pragma unroll 8
-            for (int b = 0; b < 32; ++b) {
-                const int r = w * 32 + b;
-                if (r < routes && sIds[r] == (uint32_t)e) mask[w] |= 1u << b;
-            }
+    // Lists of routes per expert, built from the routes' side: route r's place in its expert's list
+    // is the number of earlier routes with the same expert, so every list is in (token, rank) order.
+    // A token's routes are distinct experts, so an expert is chosen by at most T routes; repeats
+    // beyond that are dropped rather than overrunning the row class.
+    for (int i = threadIdx.x; i < kMaxExperts; i += blockDim.x) sCount[i] = 0u;
+    __syncthreads();
+    if ((int)threadIdx.x < routes) {
+        const int r = threadIdx.x;
+        const uint32_t mine = sIds[r];
+        int place = 0;
+        for (int q = 0; q < r; ++q) place += sIds[q] == mine ? 1 : 0;
+        if (mine < (uint32_t)a.E && place < a.T) {
+            sList[mine * kMaxGemvRows + place] = (uint8_t)r;
+            atomicAdd(&sCount[mine], 1u);
         }
     }
-    // a token's routes are distinct experts, so an expert is chosen by at most T routes; repeats
-    // beyond that are dropped rather than overrunning the row class
+    __syncthreads();
+    const int e = threadIdx.x;
     uint32_t list[kMaxGemvRows];
-    int n = 0;
+    const int n = e < a.E ? (int)sCount[e] : 0;
+    {
+        const uint4 packed = e < a.E ? *reinterpret_cast<const uint4 *>(&sList[e * kMaxGemvRows]) : make_uint4(0, 0, 0, 0);
+        const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
-    for (int i = 0; i < kMaxGemvRows; ++i) {
-        uint32_t r = 0;
-        bool found = false;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            if (!found && mask[w]) {
-                const int b = __ffs((int)mask[w]) - 1;
-                mask[w] &= mask[w] - 1u;
-                r = (uint32_t)(w * 32 + b);
-                found = true;
-            }
-        }
-        list[i] = r;
-        if (found && i < a.T) n = i + 1;
+        for (int i = 0; i < kMaxGemvRows; ++i) list[i] = i < n ? (words[i >> 2] >> (8 * (i & 3))) & 0xFFu : 0u;
     }
     // position of expert e among the active experts: ballots inside a warp, warp totals through
     // shared memory
