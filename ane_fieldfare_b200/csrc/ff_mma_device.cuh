@@ -135,7 +135,10 @@ __device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n
                                             uint32_t srcStride = 0) {
     const int runsPerRow = n >> 3, runs = rows * runsPerRow;
     const uint32_t rowRuns = srcStride ? srcStride >> 3 : (uint32_t)runsPerRow;  // 16-byte units between source rows
-    // two runs per thread and step, both loads issued before either is used
+    // Two runs per thread and step, both loads issued before either is used.  A run's eight values
+    // are summed while they are in registers (in stored order), the eight runs of a group sit in
+    // eight adjacent lanes and are added by a fixed butterfly: one pass, one CTA barrier.  The loop
+    // bound is the same for all lanes of a warp.
     auto fetch = [&](int i) {
         const int sr = i / runsPerRow;
         const size_t si = (size_t)sr * rowRuns + (size_t)(i - sr * runsPerRow);
@@ -144,45 +147,38 @@ __device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n
                : plainLoads                      ? reinterpret_cast<const uint4 *>(src)[si]
                                                  : __ldcg(reinterpret_cast<const uint4 *>(src) + si);
     };
-    auto put = [&](int i, const uint4 &v) {
+    auto put = [&](int i, bool valid, const uint4 &v) {
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410);
         o.y = __byte_perm(v.x, v.z, 0x7632);
         o.z = __byte_perm(v.y, v.w, 0x5410);
         o.w = __byte_perm(v.y, v.w, 0x7632);
-        const int r = i / runsPerRow;
-        *reinterpret_cast<uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16) = o;
-    };
-    for (int i = threadIdx.x; i < runs; i += 2 * blockDim.x) {
-        const int j = i + blockDim.x;
-        const uint4 v0 = fetch(i);
-        uint4 v1 = make_uint4(0, 0, 0, 0);
-        if (j < runs) v1 = fetch(j);
-        put(i, v0);
-        if (j < runs) put(j, v1);
-    }
-    __syncthreads();
-    // eight lanes per group: each sums one run of eight in stored order, then a fixed butterfly;
-    // the loop bound is the same for all lanes of a warp
-    for (int base = (threadIdx.x >> 5) << 5; base < runs; base += blockDim.x) {
-        const int i = base + (threadIdx.x & 31);
         float s = 0.0f;
-        if (i < runs) {
+        if (valid) {
             const int r = i / runsPerRow;
-            const uint4 v = *reinterpret_cast<const uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16);
-            s = __uint_as_float(v.x << 16);
-            s += __uint_as_float(v.x & 0xFFFF0000u);
-            s += __uint_as_float(v.y << 16);
-            s += __uint_as_float(v.y & 0xFFFF0000u);
-            s += __uint_as_float(v.z << 16);
-            s += __uint_as_float(v.z & 0xFFFF0000u);
-            s += __uint_as_float(v.w << 16);
-            s += __uint_as_float(v.w & 0xFFFF0000u);
+            *reinterpret_cast<uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16) = o;
+            s = __uint_as_float(o.x << 16);
+            s += __uint_as_float(o.x & 0xFFFF0000u);
+            s += __uint_as_float(o.y << 16);
+            s += __uint_as_float(o.y & 0xFFFF0000u);
+            s += __uint_as_float(o.z << 16);
+            s += __uint_as_float(o.z & 0xFFFF0000u);
+            s += __uint_as_float(o.w << 16);
+            s += __uint_as_float(o.w & 0xFFFF0000u);
         }
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
-        if (i < runs && (i & 7) == 0) sums[i >> 3] = s;
+        if (valid && (i & 7) == 0) sums[i >> 3] = s;
+    };
+    for (int base = (threadIdx.x >> 5) << 5; base < runs; base += 2 * blockDim.x) {
+        const int i = base + (threadIdx.x & 31), j = i + blockDim.x;
+        const bool vi = i < runs, vj = j < runs;
+        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = make_uint4(0, 0, 0, 0);
+        if (vi) v0 = fetch(i);
+        if (vj) v1 = fetch(j);
+        put(i, vi, v0);
+        if (base + (int)blockDim.x < runs) put(j, vj, v1);  // warp-uniform condition
     }
     __syncthreads();
 }
