@@ -245,24 +245,28 @@ static bool moe_layer_host_one_token(FFContext *ctx, uint32_t layer, const uint1
     *handled = true;
     const bool withShared = cfg.sharedF != 0 && L.shared != nullptr;
     ctx->lastTokens = 1;
-    DecodeHostHandoff handoff{hostX, static_cast<uint16_t *>(attr.devicePointer), ctx->mailbox, ++ctx->hostEpoch};
+    DecodeHostHandoff handoff{hostX, static_cast<uint16_t *>(attr.devicePointer),
+                              const_cast<unsigned long long *>(ctx->mailbox), ++ctx->hostEpoch};
     if (handoff.epoch == 0) handoff.epoch = ++ctx->hostEpoch;  // 0 is the mailbox's initial value
     if (!launch_decode_fused(ctx, L, ctx->xDev, nullptr, nullptr, withShared, true, nullptr, ctx->yDev,
                              ctx->hostStream, error, &handoff))
         return false;
     // poll the mailbox; look at the stream now and then so that a failed launch cannot spin forever
+    unsigned long long word = 0;
     for (uint64_t spins = 1;; ++spins) {
-        if (ctx->mailbox[0] == handoff.epoch) break;
+        word = *ctx->mailbox;
+        if ((uint32_t)word == handoff.epoch) break;
         if ((spins & 0xFFFF) == 0) {
             const cudaError_t state = cudaStreamQuery(ctx->hostStream);
             if (state == cudaSuccess) {
-                if (ctx->mailbox[0] == handoff.epoch) break;
+                word = *ctx->mailbox;
+                if ((uint32_t)word == handoff.epoch) break;
                 return fail(error, "the decode kernel ended without reporting");
             }
             if (state != cudaErrorNotReady) return fail(error, std::string("CUDA: ") + cudaGetErrorString(state));
         }
     }
-    const uint32_t flag = ctx->mailbox[1];
+    const uint32_t flag = (uint32_t)(word >> 32);
     if (flag) return fail(error, "a kernel gave up waiting (error flag " + std::to_string(flag) + ")");
     return true;
 }

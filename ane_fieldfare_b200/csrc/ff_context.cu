@@ -70,7 +70,7 @@ void ff_destroy(FFContext *ctx) {
                     ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch, ctx->taggedLogits};
     for (void *p : ptrs) cudaFree(p);
     if (ctx->hostStream) cudaStreamDestroy(ctx->hostStream);
-    if (ctx->mailbox) cudaFreeHost(const_cast<uint32_t *>(ctx->mailbox));
+    if (ctx->mailbox) cudaFreeHost(const_cast<unsigned long long *>(ctx->mailbox));
     delete ctx;
 }
 
@@ -147,7 +147,7 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
         ok = cudaHostAlloc(&box, 64, cudaHostAllocMapped) == cudaSuccess;
         if (ok) {
             memset(box, 0, 64);
-            ctx->mailbox = static_cast<volatile uint32_t *>(box);
+            ctx->mailbox = static_cast<volatile unsigned long long *>(box);
         } else if (error) {
             fail(error, "cudaHostAlloc of the host mailbox failed");
         }

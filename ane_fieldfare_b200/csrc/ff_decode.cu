@@ -70,9 +70,9 @@ struct DecodeArgs {
     int E, D, F, Fs, K;          // K = 0: shared FFN only (y receives its output)
     int prefetch;                // bit 0: L2 prefetch of the chosen experts' down projections
     // host hand-off (null when unused): the last CTA to finish copies y to `hostY` (host memory the
-    // device can write), then the error flag and `epoch` to `mailbox` — the host polls mailbox[0]
+    // device can write), then stores (error flag << 32 | epoch) to `mailbox`, which the host polls
     uint16_t *hostY;
-    volatile uint32_t *mailbox;
+    unsigned long long *mailbox;
     uint32_t epoch;
     // shared-memory carve-up (fused_layout)
     uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
@@ -658,12 +658,13 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
             __threadfence();
             for (int i = threadIdx.x; i < (D >> 3); i += blockDim.x)
                 reinterpret_cast<uint4 *>(a.hostY)[i] = __ldcg(reinterpret_cast<const uint4 *>(a.y) + i);
-            __threadfence_system();
+            // one system-scope release by one thread publishes the row (ordered before it by the CTA
+            // barrier) together with the error flag and the epoch, as one 64-bit word
             __syncthreads();
             if (threadIdx.x == 0) {
-                a.mailbox[1] = __ldcg(a.errorFlag);
-                __threadfence_system();
-                a.mailbox[0] = a.epoch;
+                const unsigned long long word =
+                    ((unsigned long long)__ldcg(a.errorFlag) << 32) | (unsigned long long)a.epoch;
+                asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.mailbox), "l"(word) : "memory");
             }
         }
     }

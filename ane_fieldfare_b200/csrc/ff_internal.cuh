@@ -113,7 +113,7 @@ struct FFContext {
     unsigned long long *phaseStamps = nullptr;  // device: 8 phase + 288 per-warp timestamps of the fused decode kernel
     unsigned long long *taggedLogits = nullptr;  // device: [kMaxExperts] router logits of the fused decode kernel
     uint32_t *gridBarrier = nullptr;        // device: eight 64-bit counters of the fused decode kernel
-    volatile uint32_t *mailbox = nullptr;   // pinned host memory the decode kernel reports to
+    volatile unsigned long long *mailbox = nullptr;  // pinned host word the decode kernel reports to
     uint32_t hostEpoch = 0;
     CUtensorMap *mapScratch = nullptr;
 
@@ -186,11 +186,11 @@ bool launch_block_mma(FFContext *ctx, const uint16_t *x, uint32_t xStride, uint3
 
 // Host hand-off of the one-token kernel: `inlineX` (host memory) travels in the kernel parameters
 // instead of `x`; the last CTA copies the output to `hostY` (host memory mapped for the device) and
-// writes the error flag and `epoch` to mailbox[1], mailbox[0].
+// stores (error flag << 32 | epoch) to the mailbox word.
 struct DecodeHostHandoff {
     const uint16_t *inlineX;
     uint16_t *hostY;
-    volatile uint32_t *mailbox;
+    unsigned long long *mailbox;
     uint32_t epoch;
 };
 bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x, const uint32_t *idsIn,

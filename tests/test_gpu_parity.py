@@ -355,3 +355,41 @@ def test_host_entry_point_and_errors(tiny, oracle):
     with pytest.raises(hp.FieldfareError, match="truncated"):
         ctx.loadLayer(0, L.blobs[:2], L.layout.stride, L.layout.offsets)
     assert ctx.info().kernelLaunches > 0 and ctx.info().smCount > 0
+
+
+def test_decode_kernel_replays_in_a_cuda_graph_and_mixes_with_other_modes(full, oracle):
+    """The one-token kernel keeps its grid-wide counters in device memory with no host-side state:
+    a captured graph of steps replays to the same bits, also when launches of its other modes
+    (shared FFN alone, routed with given routes) run on the same context in between."""
+    hp = _hp()
+    L, ctx = full
+    xs = [dev(workload.make_tokens(300 + i, "graph", 1, L.d), ctx) for i in range(4)]
+    eager = [ctx.moeLayer(0, x).clone() for x in xs]
+    torch.cuda.synchronize()
+    ys = [torch.zeros((1, L.d), dtype=torch.bfloat16, device=ctx.device) for _ in xs]
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        for x, y in zip(xs, ys):
+            ctx.moeLayer(0, x, y)
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for x, y in zip(xs, ys):
+                ctx.moeLayer(0, x, y)
+    h1 = torch.zeros((1, L.d), dtype=torch.bfloat16, device=ctx.device)
+    ids = torch.zeros((1, L.topK), dtype=torch.int32, device=ctx.device)
+    w = torch.zeros((1, L.topK), dtype=torch.bfloat16, device=ctx.device)
+    for replay in range(20):
+        for y in ys:
+            y.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for got, want in zip(ys, eager):
+            assert torch.equal(got, want), replay
+        # other modes of the same kernel in between
+        hp.SharedExpertInt4(ctx).encode(None, 0, xs[replay % 4], h1)
+        hp.MoE(ctx).encodeRouterGemma4(None, 0, xs[replay % 4], ids, w, topK=L.topK)
+        hp.MoE(ctx).encodeRoutedPersistentGPUSlots(None, 0, ids, xs[replay % 4], w, h1, ys[0])
+        torch.cuda.synchronize()
+        assert torch.equal(ys[0], eager[replay % 4]), replay
+    assert ctx.info().deviceErrorFlag == 0
