@@ -302,6 +302,7 @@ bool ff_load_layer(FFContext *ctx, uint32_t layer, const void *hostBytes, uint64
     L.expertCount = expertCount;
     L.off = *offsets;
     L.mapsReady = false;
+    L.decodeMapsReady = false;
     ctx->weightBytes += total;
     return true;
 }
@@ -345,6 +346,7 @@ bool ff_load_shared(FFContext *ctx, uint32_t layer, const FFProjection *gate,
         FF_CUDA_OK(cudaMemcpy(L.shared + o[3 * m + 2], ps[m]->biases, auxSize, cudaMemcpyHostToDevice), error);
     }
     L.mapsReady = false;
+    L.decodeMapsReady = false;
     ctx->weightBytes += payload;
     return true;
 }

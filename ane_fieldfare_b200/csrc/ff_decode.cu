@@ -76,8 +76,15 @@ struct DecodeArgs {
     uint32_t epoch;
     // shared-memory carve-up (fused_layout)
     uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
-    uint32_t strideGU, strideSD, strideRD, actStride, winBytes, winPitch;
+    uint32_t strideGU, strideGUA, strideSD, strideRD, actStride, winBytes, winPitch;
 };
+
+// Row-box tensor maps of the layer (kernel parameters): routed gate, routed up, shared gate, shared
+// up, shared down.  A tile's eight (sixteen) row pieces arrive as one tensor copy per matrix.
+struct alignas(64) DecodeMaps {
+    CUtensorMap m[5];
+};
+enum : int { kMapRoutedGate = 0, kMapRoutedUp = 1, kMapSharedGate = 2, kMapSharedUp = 3, kMapSharedDown = 4 };
 
 // Bulk L2 prefetch of [p, p + bytes); bytes a multiple of 16, p 16-byte aligned.
 __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) {
@@ -191,6 +198,16 @@ __device__ __noinline__ void tile_rows(const uint8_t *lo, const uint8_t *hi, con
     acc1 = v1;
 }
 
+// Box of a row-box map at (64-bit word x, row y, expert z) into shared memory (128-byte aligned).
+// x * 8 bytes must be a multiple of 16.
+__device__ __forceinline__ void box_copy(uint32_t dst, const CUtensorMap *map, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+
 // The input row travelling inside the kernel's parameters (no host-to-device copy before the
 // launch): up to 4096 bf16 values.
 struct InlineRow {
@@ -198,7 +215,7 @@ struct InlineRow {
 };
 
 // xInline: null, or the input row in parameter space (read with plain loads).
-__device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t *xInline) {
+__device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMaps &maps, const uint16_t *xInline) {
     extern __shared__ __align__(128) uint8_t smemRaw[];
     __shared__ float sLogits[kMaxExperts];
     __shared__ uint32_t sIds[8];
@@ -249,44 +266,46 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     const int tilesSGU = sh ? Fs >> 3 : 0;  // 8 gate + 8 up rows per tile, two K halves
     const int tilesSD = sh ? D >> 4 : 0;    // 16 down rows per tile, three K parts
 
-    // Requests of part `part` of `parts` (along K) of a gate/up tile: 16 row pieces, then the eight rows' scales and biases of both
-    // matrices over the full K (contiguous runs).  Lane l issues copy l.
-    auto issue_gate_up = [&](const uint8_t *blob, const FFExpertOffsets &off, int tile, int part, int parts) {
+    // Requests of part `part` of `parts` (along K) of a gate/up tile: one box of eight row pieces per
+    // matrix (`pitch` bytes per row in the slot: the box is as wide as the pitch, what it reads past
+    // the part is not used), then the eight rows' scales and biases of both matrices over the full K
+    // (contiguous runs).
+    auto issue_gate_up = [&](const CUtensorMap *gateMap, const CUtensorMap *upMap, int expert, const uint8_t *blob,
+                             const FFExpertOffsets &off, int tile, int part, int parts, uint32_t pitch) {
         int gb, ge;
         part_range(groupsD, parts, part, gb, ge);
-        const uint32_t piece = (uint32_t)(ge - gb) * 32u, sb = (uint32_t)groupsD * 16u;
-        if (lane == 0) bar_expect(myBar, 16u * piece + 4u * sb);
+        const uint32_t sb = (uint32_t)groupsD * 16u;
+        if (lane == 0) bar_expect(myBar, (ge > gb ? 16u * pitch : 0u) + 4u * sb);
         __syncwarp();
-        if (lane < 16) {
-            const int row = tile * 8 + (lane & 7);
-            const uint8_t *w = blob + (lane < 8 ? off.gateWOff : off.upWOff) + (size_t)row * (D >> 1) + gb * 32;
-            if (piece) bulk_copy(slotAddr + (uint32_t)lane * a.strideGU, w, piece, myBar);
-        } else if (lane < 20) {
+        if (lane < 2) {
+            if (ge > gb) box_copy(slotAddr + (uint32_t)lane * 8u * pitch, lane ? upMap : gateMap, gb * 4, tile * 8, expert, myBar);
+        } else if (lane >= 16 && lane < 20) {
             const uint32_t which = (uint32_t)lane - 16u;
             const uint32_t src = which == 0 ? off.gateSOff : which == 1 ? off.gateBOff : which == 2 ? off.upSOff : off.upBOff;
-            bulk_copy(slotAddr + 16u * a.strideGU + which * sb, blob + src + (size_t)tile * sb, sb, myBar);
+            bulk_copy(slotAddr + 16u * pitch + which * sb, blob + src + (size_t)tile * sb, sb, myBar);
         }
     };
     // Gate/up tile part -> this thread's partial sums of gate row tile*8+g and up row tile*8+g.
-    auto compute_gate_up = [&](int part, int parts, const uint8_t *xp, const float *xs, float &gate, float &up) {
+    auto compute_gate_up = [&](int part, int parts, uint32_t pitch, const uint8_t *xp, const float *xs, float &gate, float &up) {
         int gb, ge;
         part_range(groupsD, parts, part, gb, ge);
-        const uint8_t *lo = mySlot + (size_t)g * a.strideGU + 8 * t;
-        const uint8_t *hi = mySlot + (size_t)(g + 8) * a.strideGU + 8 * t;
-        const uint16_t *sc = reinterpret_cast<const uint16_t *>(mySlot + 16u * a.strideGU);
+        const uint8_t *lo = mySlot + (size_t)g * pitch + 8 * t;
+        const uint8_t *hi = mySlot + (size_t)(g + 8) * pitch + 8 * t;
+        const uint16_t *sc = reinterpret_cast<const uint16_t *>(mySlot + 16u * pitch);
         const uint16_t *gS = sc + g * groupsD, *gB = gS + 8 * groupsD, *uS = gB + 8 * groupsD, *uB = uS + 8 * groupsD;
+        gate = 0.0f;
+        up = 0.0f;
         tile_rows(lo, hi, xp + gb * 128 + t * 32, gS + gb, gB + gb, uS + gb, uB + gb, xs + gb, ge - gb, false, gate, up);
     };
     auto issue_shared_down = [&](int tile, int part) {
         int gb, ge;
         part_range(groupsFs, 3, part, gb, ge);
-        const uint32_t piece = (uint32_t)(ge - gb) * 32u, sb = (uint32_t)groupsFs * 32u;
-        if (lane == 0) bar_expect(myBar, 16u * piece + 2u * sb);
+        const uint32_t sb = (uint32_t)groupsFs * 32u;
+        if (lane == 0) bar_expect(myBar, (ge > gb ? 16u * a.strideSD : 0u) + 2u * sb);
         __syncwarp();
-        if (lane < 16) {
-            const uint8_t *w = sh + a.sharedOff.downWOff + (size_t)(tile * 16 + lane) * (Fs >> 1) + gb * 32;
-            if (piece) bulk_copy(slotAddr + (uint32_t)lane * a.strideSD, w, piece, myBar);
-        } else if (lane < 18) {
+        if (lane == 0) {
+            if (ge > gb) box_copy(slotAddr, &maps.m[kMapSharedDown], gb * 4, tile * 16, 0, myBar);
+        } else if (lane >= 16 && lane < 18) {
             const uint32_t which = (uint32_t)lane - 16u;
             bulk_copy(slotAddr + 16u * a.strideSD + which * sb,
                       sh + (which ? a.sharedOff.downBOff : a.sharedOff.downSOff) + (size_t)tile * sb, sb, myBar);
@@ -309,7 +328,8 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     // shared gate/up tiles: four warps per tile (K quarters), two tiles per CTA and round
     const int partA = warp & 3;
     int tA = warp < kSharedGuWarps ? (warp >> 2) * G + cta : 0x7FFFFFFF;
-    if (tA < tilesSGU) issue_gate_up(sh, a.sharedOff, tA, partA, 4);
+    if (tA < tilesSGU)
+        issue_gate_up(&maps.m[kMapSharedGate], &maps.m[kMapSharedUp], 0, sh, a.sharedOff, tA, partA, 4, a.strideGUA);
     const int triple = warp >= kBigWarps ? (warp - kBigWarps) / 3 : 0;
     const int part3 = warp >= kBigWarps ? (warp - kBigWarps) % 3 : 0;
     int tSD = warp >= kBigWarps ? triple * G + cta : 0x7FFFFFFF;
@@ -321,10 +341,11 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
         float gate, up;
-        compute_gate_up(partA, 4, xPerm, xSum, gate, up);
+        compute_gate_up(partA, 4, a.strideGUA, xPerm, xSum, gate, up);
         slot_release();
         const int next = tA + (kSharedGuWarps / 4) * G;
-        if (next < tilesSGU) issue_gate_up(sh, a.sharedOff, next, partA, 4);
+        if (next < tilesSGU)
+            issue_gate_up(&maps.m[kMapSharedGate], &maps.m[kMapSharedUp], 0, sh, a.sharedOff, next, partA, 4, a.strideGUA);
         float *mine = partial + warp * 16;
         if (partA && t == 0) {
             mine[g] = gate;
@@ -483,7 +504,8 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     int tB = warp < kBigWarps ? (warp >> 1) * G + cta : 0x7FFFFFFF;
     if (tB < tilesRouted) {
         const int slot = tB / tilesF;
-        issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, tB - slot * tilesF, warp & 1, 2);
+        issue_gate_up(&maps.m[kMapRoutedGate], &maps.m[kMapRoutedUp], (int)sIds[slot],
+                      a.experts + (size_t)sIds[slot] * a.stride, a.off, tB - slot * tilesF, warp & 1, 2, a.strideGU);
     }
     warp_stamp(a, 1, 0);
     if ((a.prefetch & 1) && K > 0) {
@@ -505,12 +527,13 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 1, 1);
         float gate, up;
-        compute_gate_up(warp & 1, 2, xPerm, xSum, gate, up);
+        compute_gate_up(warp & 1, 2, a.strideGU, xPerm, xSum, gate, up);
         slot_release();
         const int next = tB + (kBigWarps / 2) * G;
         if (next < tilesRouted) {
             const int slot = next / tilesF;
-            issue_gate_up(a.experts + (size_t)sIds[slot] * a.stride, a.off, next - slot * tilesF, warp & 1, 2);
+            issue_gate_up(&maps.m[kMapRoutedGate], &maps.m[kMapRoutedUp], (int)sIds[slot],
+                          a.experts + (size_t)sIds[slot] * a.stride, a.off, next - slot * tilesF, warp & 1, 2, a.strideGU);
         }
         float *mine = partial + warp * 16;
         if ((warp & 1) && t == 0) {
@@ -670,16 +693,20 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const uint16_t 
     }
 }
 
-__global__ void __launch_bounds__(kFusedThreads, 1) k_decode_fused(const DecodeArgs a) { decode_body(a, nullptr); }
+__global__ void __launch_bounds__(kFusedThreads, 1)
+k_decode_fused(const DecodeArgs a, const __grid_constant__ DecodeMaps maps) {
+    decode_body(a, maps, nullptr);
+}
 
 __global__ void __launch_bounds__(kFusedThreads, 1)
-k_decode_fused_inline_x(const DecodeArgs a, const __grid_constant__ InlineRow row) {
-    decode_body(a, reinterpret_cast<const uint16_t *>(&row));
+k_decode_fused_inline_x(const DecodeArgs a, const __grid_constant__ DecodeMaps maps,
+                        const __grid_constant__ InlineRow row) {
+    decode_body(a, maps, reinterpret_cast<const uint16_t *>(&row));
 }
 
 struct FusedLayout {
     uint32_t regionOffset, partialOffset, slotsOffset, bigBytes, smallBytes;
-    uint32_t strideGU, strideSD, strideRD, actStride, winBytes, winPitch;
+    uint32_t strideGU, strideGUA, strideSD, strideRD, actStride, winBytes, winPitch;
     size_t total;
 };
 
@@ -687,7 +714,8 @@ static FusedLayout fused_layout(const FFConfig &c) {
     const uint32_t D = c.d, F = c.f, Fs = c.sharedF;
     const uint32_t groupsD = D / 64, groupsF = F / 64, groupsFs = Fs / 64;
     FusedLayout l{};
-    l.strideGU = piece_stride(((groupsD + 1) / 2) * 32);
+    l.strideGU = piece_stride(((groupsD + 1) / 2) * 32);   // routed tiles: K halves
+    l.strideGUA = piece_stride(((groupsD + 3) / 4) * 32);  // shared tiles: K quarters
     l.strideSD = Fs ? piece_stride(((groupsFs + 2) / 3) * 32) : 32;
     l.strideRD = piece_stride(groupsF * 32);
     l.winBytes = pad16u(4 * groupsF) + 16;
@@ -774,12 +802,38 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
         if ((routed && (ro[i] % 16 || L.stride % 16)) || (withShared && so[i] % 16))
             return fail(error, "sub-tensor offsets must be multiples of 16 bytes for the decode kernel");
     if (!(host && host->inlineX) && ((uintptr_t)x & 15) != 0) return fail(error, "input row must be 16-byte aligned");
+    // row-box tensor maps of the layer, built once per loaded layer
+    LayerStore &Lm = const_cast<LayerStore &>(L);
+    if (!Lm.decodeMapsReady) {
+        memset(Lm.decodeMap, 0, sizeof(Lm.decodeMap));
+        if (L.experts) {
+            const uint32_t *o = &L.off.gateWOff;
+            for (int m = 0; m < 2; ++m)
+                if (!make_row_box_map(&Lm.decodeMap[kMapRoutedGate + m], L.experts + o[3 * m], c.f, c.d / 2,
+                                      L.expertCount, L.stride, lay.strideGU, 8, error))
+                    return false;
+        }
+        if (L.shared && c.sharedF) {
+            const uint32_t *o = &L.sharedOff.gateWOff;
+            for (int m = 0; m < 2; ++m)
+                if (!make_row_box_map(&Lm.decodeMap[kMapSharedGate + m], L.shared + o[3 * m], c.sharedF, c.d / 2, 1,
+                                      0, lay.strideGUA, 8, error))
+                    return false;
+            if (!make_row_box_map(&Lm.decodeMap[kMapSharedDown], L.shared + o[6], c.d, c.sharedF / 2, 1, 0,
+                                  lay.strideSD, 16, error))
+                return false;
+        }
+        Lm.decodeMapsReady = true;
+    }
+    static thread_local DecodeMaps maps;
+    memcpy(maps.m, L.decodeMap, sizeof(maps.m));
     a.regionOffset = lay.regionOffset;
     a.partialOffset = lay.partialOffset;
     a.slotsOffset = lay.slotsOffset;
     a.bigBytes = lay.bigBytes;
     a.smallBytes = lay.smallBytes;
     a.strideGU = lay.strideGU;
+    a.strideGUA = lay.strideGUA;
     a.strideSD = lay.strideSD;
     a.strideRD = lay.strideRD;
     a.actStride = lay.actStride;
@@ -817,12 +871,12 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
         if (c.d > 4096) return fail(error, "input row too long to travel in the kernel parameters");
         static thread_local InlineRow row;
         memcpy(&row, host->inlineX, (size_t)c.d * 2);
-        void *params[] = {&a, &row};
+        void *params[] = {&a, &maps, &row};
         FF_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(k_decode_fused_inline_x),
                                                dim3(gridFor[slot]), dim3(kFusedThreads), params, smem, stream),
                    error);
     } else {
-        void *params[] = {&a};
+        void *params[] = {&a, &maps};
         FF_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(k_decode_fused), dim3(gridFor[slot]),
                                                dim3(kFusedThreads), params, smem, stream),
                    error);

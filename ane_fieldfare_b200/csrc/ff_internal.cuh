@@ -75,6 +75,9 @@ struct LayerStore {
     bool mapsReady = false;
     CUtensorMap routedMap[3];
     CUtensorMap sharedMap[3];
+    // one-token kernel: row-box maps of routed gate, routed up, shared gate, shared up, shared down
+    bool decodeMapsReady = false;
+    CUtensorMap decodeMap[5];
 };
 
 }  // namespace ff
@@ -180,6 +183,9 @@ bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, c
                           cudaStream_t stream, const char **error);
 
 // ff_decode.cu
+bool make_row_box_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t rowBytes, uint64_t experts,
+                      uint64_t expertStride, uint32_t boxBytes, uint32_t boxRows, const char **error);
+
 // Gate/up + GeGLU jobs, then down jobs, of a planned 2..16-row block on the tensor-core block kernels.
 bool launch_block_mma(FFContext *ctx, const uint16_t *x, uint32_t xStride, uint32_t tokens, bool withShared,
                       bool haveDownJobs, cudaStream_t stream, const char **error);

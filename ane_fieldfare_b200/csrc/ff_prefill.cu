@@ -1029,6 +1029,26 @@ static bool make_activation_map(CUtensorMap *map, const void *base, uint64_t row
 }
 
 // packed codes of one matrix across all experts: bytes [experts][rows][cols/2], box 32 x 64 x 1.
+// Packed codes of one matrix across all experts seen as 64-bit words [experts][rows][rowBytes/8],
+// box `boxBytes` x `boxRows` x 1 without swizzle: a tile of whole row pieces in one copy, rows
+// `boxBytes` apart in shared memory.  Out-of-range parts of a box read as zero.
+bool make_row_box_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t rowBytes, uint64_t experts,
+                      uint64_t expertStride, uint32_t boxBytes, uint32_t boxRows, const char **error) {
+    EncodeTiledFn fn = encode_tiled(error);
+    if (!fn) return false;
+    if (rowBytes % 16 || boxBytes % 16 || boxBytes / 8 > 256 || boxRows > 256 || expertStride % 16)
+        return fail(error, "row box does not fit a tensor map");
+    cuuint64_t dims[3] = {rowBytes / 8, rows, experts};
+    cuuint64_t strides[2] = {rowBytes, expertStride ? expertStride : rows * rowBytes};
+    cuuint32_t box[3] = {boxBytes / 8, boxRows, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(error, "cuTensorMapEncodeTiled(row boxes) failed: " + std::to_string((int)rc));
+    return true;
+}
+
 static bool make_weight_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols,
                             uint64_t experts, uint64_t expertStride, const char **error) {
     EncodeTiledFn fn = encode_tiled(error);
