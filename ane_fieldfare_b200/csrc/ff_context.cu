@@ -67,7 +67,7 @@ void ff_destroy(FFContext *ctx) {
                     ctx->acts, ctx->sharedActs, ctx->h1,
                     ctx->partials, ctx->xDev, ctx->yDev, ctx->xSorted, ctx->sortedPairs,
                     ctx->expertOffsets, ctx->blockCounts, ctx->units, ctx->unitCount,
-                    ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch, ctx->taggedLogits};
+                    ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch, ctx->taggedLogits, ctx->taggedActs};
     for (void *p : ptrs) cudaFree(p);
     if (ctx->hostStream) cudaStreamDestroy(ctx->hostStream);
     if (ctx->mailbox) cudaFreeHost(const_cast<unsigned long long *>(ctx->mailbox));
@@ -140,6 +140,9 @@ FFContext *ff_create(int32_t deviceOrdinal, const FFConfig *config, const char *
     if (ok) ok = cudaMemset(ctx->phaseStamps, 0, kPhaseStampSlots * 8) == cudaSuccess;
     ok = ok && dev_alloc(ctx, &ctx->taggedLogits, kMaxExperts, error);
     if (ok) ok = cudaMemset(ctx->taggedLogits, 0, kMaxExperts * 8) == cudaSuccess;
+    const size_t taggedWords = (size_t)K * c.f / 2 + c.d / 2;
+    ok = ok && dev_alloc(ctx, &ctx->taggedActs, taggedWords, error);
+    if (ok) ok = cudaMemset(ctx->taggedActs, 0, taggedWords * 8) == cudaSuccess;
     ok = ok && dev_alloc(ctx, &ctx->gridBarrier, 16, error);
     if (ok) ok = cudaMemset(ctx->gridBarrier, 0, 64) == cudaSuccess;
     if (ok) {

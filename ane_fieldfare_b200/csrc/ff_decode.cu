@@ -60,7 +60,11 @@ struct DecodeArgs {
     const uint32_t *idsIn;  // non-null: routes are given, the router is skipped
     const uint16_t *weightsIn;
     float *logits;
-    unsigned long long *taggedLogits;  // [E] (1 << 32 | logit bits) while valid, 0 otherwise
+    // Values handed from CTA to CTA travel as 64-bit words (launch tag << 32 | payload) that the
+    // readers poll: a word is valid when its tag is the running launch's, so nothing is cleared.
+    unsigned long long *taggedLogits;  // [E] payload: the logit's bits
+    unsigned long long *taggedActs;    // [K * F / 2] payload: two routed activations (bf16)
+    unsigned long long *taggedH1;      // [D / 2] payload: two rows of the shared FFN's output (bf16)
     uint32_t *ids;
     uint16_t *weights;
     uint16_t *acts, *sharedActs, *h1, *y;
@@ -109,11 +113,13 @@ __device__ __forceinline__ void prefetch_region(const uint8_t *base, uint64_t by
 // Grid-wide synchronisation on 64-bit counters that only grow.  At its start every CTA draws a
 // ticket from counter [3]; ticket / gridDim is the launch's generation g (launches on a context
 // are serialised, so all CTAs of a launch get the same g).  Every launch adds exactly gridDim to
-// each of the counters [0] (shared activations written) and [4] (routed activations written) — also when a mode does not wait on one of them — so "everyone
+// counter [0] (shared activations written) — also when a mode does not wait on it — so "everyone
 // has arrived" is counter >= (g + 1) * gridDim.  An arrival is a release reduction without a
 // return value; a wait polls the counter with acquire loads, bounded.  No reset, no host-side
-// state.  [2] counts finished CTAs for the host hand-off.
-enum : int { kCountShared = 0, kCountDone = 2, kCountTicket = 3, kCountRouted = 4 };
+// state.  [2] counts finished CTAs for the host hand-off.  The low 32 bits of g + 1 are the
+// launch's tag for the values that travel as polled words (logits, routed activations, shared
+// output rows).
+enum : int { kCountShared = 0, kCountDone = 2, kCountTicket = 3 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
     unsigned long long v;
@@ -139,6 +145,15 @@ __device__ __forceinline__ void counter_wait(const unsigned long long *count, un
 // The thread that arrives at and waits for the CTA-wide barriers: lane 0 of the last warp (a warp
 // with no requests to issue between arriving and waiting).
 __device__ __forceinline__ bool is_barrier_thread() { return threadIdx.x == blockDim.x - 32; }
+
+__device__ __forceinline__ void st_tagged(unsigned long long *p, uint32_t tag, uint32_t payload) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(((unsigned long long)tag << 32) | payload) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_tagged(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
 
 __device__ __forceinline__ void stamp(const DecodeArgs &a, int slot) {
     if (a.stamps && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -208,6 +223,35 @@ __device__ __forceinline__ void box_copy(uint32_t dst, const CUtensorMap *map, i
         : "memory");
 }
 
+// stage_input for rows that other CTAs are still writing as tagged words (two bf16 values each):
+// every run of eight values is polled (bounded) until its four words carry `tag`.
+__device__ __forceinline__ void stage_tagged(const unsigned long long *src, uint32_t tag, int rows, int n, uint8_t *dst,
+                                             uint32_t dstStride, float *sums, uint32_t *errorFlag) {
+    const int runsPerRow = n >> 3, runs = rows * runsPerRow;
+    auto fetch = [&](int i, uint4 &v) {
+        unsigned long long w0, w1, w2, w3;
+        asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src + 4 * (size_t)i) : "memory");
+        asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w2), "=l"(w3) : "l"(src + 4 * (size_t)i + 2) : "memory");
+        v = make_uint4((uint32_t)w0, (uint32_t)w1, (uint32_t)w2, (uint32_t)w3);
+        return (uint32_t)(w0 >> 32) == tag && (uint32_t)(w1 >> 32) == tag && (uint32_t)(w2 >> 32) == tag &&
+               (uint32_t)(w3 >> 32) == tag;
+    };
+    for (int base = (threadIdx.x >> 5) << 5; base < runs; base += 2 * blockDim.x) {
+        const int i = base + (threadIdx.x & 31), j = i + blockDim.x;
+        const bool vi = i < runs, vj = j < runs;
+        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = make_uint4(0, 0, 0, 0);
+        bool ok0 = !vi, ok1 = !vj;
+        for (uint32_t spins = 0; spins < kBarrierSpinLimit && !(ok0 && ok1); ++spins) {
+            if (!ok0) ok0 = fetch(i, v0);
+            if (!ok1) ok1 = fetch(j, v1);
+        }
+        if (!(ok0 && ok1)) atomicExch(errorFlag, 9u);
+        stage_put(i, vi, v0, runsPerRow, dst, dstStride, sums);
+        if (base + (int)blockDim.x < runs) stage_put(j, vj, v1, runsPerRow, dst, dstStride, sums);  // warp-uniform
+    }
+    __syncthreads();
+}
+
 // The input row travelling inside the kernel's parameters (no host-to-device copy before the
 // launch): up to 4096 bf16 values.
 struct InlineRow {
@@ -223,6 +267,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
     __shared__ float sScore[8];
     __shared__ __align__(8) uint64_t sCopyBar[kFusedWarps];
     __shared__ unsigned long long sTarget;  // (generation + 1) * gridDim
+    __shared__ uint32_t sTag;               // low 32 bits of generation + 1 (never 0)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = (int)gridDim.x, cta = (int)blockIdx.x;
@@ -335,8 +380,13 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
     int tSD = warp >= kBigWarps ? triple * G + cta : 0x7FFFFFFF;
     if (tSD < tilesSD) issue_shared_down(tSD, part3);
     warp_stamp(a, 0, 0);
-    stage_input(xSrc, 1, D, xPerm, 0, xSum, xPlain, &xMine);
-    if (threadIdx.x == 9 * 32) sTarget = (ticket / gridDim.x + 1ull) * gridDim.x;
+    if (threadIdx.x == 9 * 32) {
+        const unsigned long long gen1 = ticket / gridDim.x + 1ull;
+        sTarget = gen1 * gridDim.x;
+        sTag = (uint32_t)gen1 ? (uint32_t)gen1 : 0xFFFFFFFFu;
+    }
+    stage_input(xSrc, 1, D, xPerm, 0, xSum, xPlain, &xMine);  // ends with a CTA barrier: target and tag are published
+    const uint32_t tag = sTag;
     for (; tA < tilesSGU; tA += (kSharedGuWarps / 4) * G) {
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
@@ -394,9 +444,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
             const float logit = a.logitBias ? acc + a.logitBias[eA] : acc;
             a.logits[eA] = logit;
             // value and validity in one 64-bit store: the readers poll these words
-            asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(a.taggedLogits + eA),
-                         "l"((1ull << 32) | (unsigned long long)__float_as_uint(logit))
-                         : "memory");
+            st_tagged(a.taggedLogits + eA, tag, __float_as_uint(logit));
         }
         slot_release();
         const int next = eA + (kBigWarps - kSharedGuWarps) * G;
@@ -411,8 +459,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
 
     // ---------------- top-8 by warps 8..15 while warps 0..7 finish the shared gate/up rows ----------
     // Each logit travels as one 64-bit word (validity | value) that the readers poll, so ranking
-    // waits neither for a counter round trip nor for the other CTAs' shared rows.  The writer
-    // clears its words again in phase C, when every CTA has read them.
+    // waits neither for a counter round trip nor for the other CTAs' shared rows.
     if (K > 0 && !a.idsIn && warp >= kSharedGuWarps) {
         constexpr int kTopkThreads = (kFusedWarps - kSharedGuWarps) * 32;
         const int tid2 = (int)threadIdx.x - kSharedGuWarps * 32;
@@ -421,7 +468,8 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
         if (warp == kSharedGuWarps) {
             for (int base = 0; base < E; base += 128) {
                 const int e0 = base + 4 * lane;
-                unsigned long long w[4] = {1ull << 32, 1ull << 32, 1ull << 32, 1ull << 32};
+                const unsigned long long filler = (unsigned long long)tag << 32;
+                unsigned long long w[4] = {filler, filler, filler, filler};
                 bool ready = false;
                 for (uint32_t spins = 0; spins < kBarrierSpinLimit && !ready; ++spins) {
                     if (e0 + 3 < E) {
@@ -432,7 +480,8 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
                             if (e0 + i < E)
                                 asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w[i]) : "l"(a.taggedLogits + e0 + i) : "memory");
                     }
-                    const bool mine = (w[0] >> 32) && (w[1] >> 32) && (w[2] >> 32) && (w[3] >> 32);
+                    const bool mine = (uint32_t)(w[0] >> 32) == tag && (uint32_t)(w[1] >> 32) == tag &&
+                                      (uint32_t)(w[2] >> 32) == tag && (uint32_t)(w[3] >> 32) == tag;
                     ready = __all_sync(0xFFFFFFFFu, mine);
                 }
                 if (!ready && lane == 0) atomicExch(a.errorFlag, 9u);
@@ -516,6 +565,30 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
                             (uint64_t)a.off.downBOff - a.off.downWOff + (uint64_t)D * F / kGroup * 2, cursor);
         }
     }
+    // Routed down tile: output rows 2*tile, 2*tile+1 of all eight experts.  Tile row rho*8 + e is
+    // row 2*tile+rho of expert e; lane l copies row piece l (l < 16), or the 16-byte aligned window
+    // around the two rows' scales (l even) or biases (l odd) of expert (l-16)/2.
+    // Tiles go to the warps in the order 10..15, 0..9: the warps of the shared down rows are done
+    // early in phase B and request their routed down tile then, into their own slot, so that it is
+    // in shared memory when the second grid barrier opens; warps 0..9 request theirs at the barrier.
+    const int tilesRD = D >> 1;
+    const int orderC = warp >= kBigWarps ? warp - kBigWarps : warp + (kFusedWarps - kBigWarps);
+    auto issue_routed_down = [&](int tile) {
+        const uint32_t piece = (uint32_t)groupsF * 32u;
+        if (lane == 0) bar_expect(myBar, 16u * piece + 16u * a.winBytes);
+        __syncwarp();
+        const int e = lane < 16 ? (lane & 7) : ((lane - 16) >> 1);
+        const uint8_t *blob = a.experts + (size_t)sIds[e < K ? e : 0] * a.stride;
+        if (lane < 16) {
+            const int row = tile * 2 + (lane >> 3);
+            bulk_copy(slotAddr + (uint32_t)lane * a.strideRD, blob + a.off.downWOff + (size_t)row * (F >> 1), piece, myBar);
+        } else {
+            const uint32_t srcOff = ((lane & 1) ? a.off.downBOff : a.off.downSOff) + (uint32_t)tile * 4u * (uint32_t)groupsF;
+            // windows: scales of expert e at e * winPitch, biases at (8 + e) * winPitch
+            bulk_copy(slotAddr + 16u * a.strideRD + (uint32_t)(((lane & 1) << 3) + e) * a.winPitch, blob + (srcOff & ~15u),
+                      a.winBytes, myBar);
+        }
+    };
     uint8_t *saPerm = region;
     float *saSum = reinterpret_cast<float *>(region + Fs * 2);
     if (sh) {
@@ -541,11 +614,14 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
             mine[8 + g] = up;
         }
         named_barrier(1 + (warp >> 1), 64);
-        if (!(warp & 1) && t == 0) {
+        if (!(warp & 1)) {
+            // the tile's eight activations are one run of the staged row: four tagged words,
+            // written by the lanes t == 0 of even g (the odd neighbour's value comes by shuffle)
             gate += mine[16 + g];
             up += mine[16 + 8 + g];
-            const int slot = tB / tilesF;
-            a.acts[slot * F + (tB - slot * tilesF) * 8 + g] = f2bf(gelu_tanh(gate) * up);
+            const uint32_t act = f2bf(gelu_tanh(gate) * up);
+            const uint32_t two = act | (__shfl_down_sync(0xFFFFFFFFu, act, 4) << 16);
+            if (t == 0 && !(g & 1)) st_tagged(a.taggedActs + ((tB * 8 + g) >> 1), tag, two);
         }
         named_barrier(1 + (warp >> 1), 64);
     }
@@ -570,55 +646,41 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
             mine[8 + g] = v1;
         }
         named_barrier(6 + triple, 96);
-        if (!part3 && t == 0) {
+        if (!part3) {
             v0 = (v0 + mine[16 + g]) + mine[32 + g];
             v1 = (v1 + mine[16 + 8 + g]) + mine[32 + 8 + g];
-            uint16_t *out = K > 0 ? a.h1 : a.y;
-            out[tSD * 16 + g] = f2bf(v0);
-            out[tSD * 16 + 8 + g] = f2bf(v1);
+            const uint32_t r0 = f2bf(v0), r1 = f2bf(v1);
+            if (K > 0) {
+                // read as the residual of the routed rows in phase C: tagged words of two rows
+                const uint32_t two0 = r0 | (__shfl_down_sync(0xFFFFFFFFu, r0, 4) << 16);
+                const uint32_t two1 = r1 | (__shfl_down_sync(0xFFFFFFFFu, r1, 4) << 16);
+                if (t == 0 && !(g & 1)) {
+                    st_tagged(a.taggedH1 + ((tSD * 16 + g) >> 1), tag, two0);
+                    st_tagged(a.taggedH1 + ((tSD * 16 + 8 + g) >> 1), tag, two1);
+                }
+            } else if (t == 0) {
+                a.y[tSD * 16 + g] = (uint16_t)r0;
+                a.y[tSD * 16 + 8 + g] = (uint16_t)r1;
+            }
         }
         named_barrier(6 + triple, 96);
     }
+    int tC = orderC * G + cta;
+    if (K > 0 && warp >= kBigWarps && tC < tilesRD) issue_routed_down(tC);
     warp_stamp(a, 1, 2);
     stamp(a, 4);
     if (K == 0) {
-        if (is_barrier_thread()) counter_arrive(a.barrier + kCountRouted);  // keeps the counters in step
         stamp(a, 5);
         stamp(a, 6);
         return;
     }
 
-    // Routed down tile: output rows 2*tile, 2*tile+1 of all eight experts.  Tile row rho*8 + e is
-    // row 2*tile+rho of expert e; lane l copies row piece l (l < 16), or the 16-byte aligned window
-    // around the two rows' scales (l even) or biases (l odd) of expert (l-16)/2.
-    const int tilesRD = D >> 1;
-    auto issue_routed_down = [&](int tile) {
-        const uint32_t piece = (uint32_t)groupsF * 32u;
-        if (lane == 0) bar_expect(myBar, 16u * piece + 16u * a.winBytes);
-        __syncwarp();
-        const int e = lane < 16 ? (lane & 7) : ((lane - 16) >> 1);
-        const uint8_t *blob = a.experts + (size_t)sIds[e < K ? e : 0] * a.stride;
-        if (lane < 16) {
-            const int row = tile * 2 + (lane >> 3);
-            bulk_copy(slotAddr + (uint32_t)lane * a.strideRD, blob + a.off.downWOff + (size_t)row * (F >> 1), piece, myBar);
-        } else {
-            const uint32_t srcOff = ((lane & 1) ? a.off.downBOff : a.off.downSOff) + (uint32_t)tile * 4u * (uint32_t)groupsF;
-            // windows: scales of expert e at e * winPitch, biases at (8 + e) * winPitch
-            bulk_copy(slotAddr + 16u * a.strideRD + (uint32_t)(((lane & 1) << 3) + e) * a.winPitch, blob + (srcOff & ~15u),
-                      a.winBytes, myBar);
-        }
-    };
-    // the weights do not depend on the activations: request them between arriving and waiting
-    __syncthreads();
-    if (is_barrier_thread()) counter_arrive(a.barrier + kCountRouted);
-    int tC = warp < kBigWarps ? warp * G + cta : 0x7FFFFFFF;
-    if (tC < tilesRD) issue_routed_down(tC);
+    // No grid barrier before phase C: the routed activations and the shared output rows are polled
+    // as tagged words while they are staged.
+    if (warp < kBigWarps && tC < tilesRD) issue_routed_down(tC);
     warp_stamp(a, 2, 0);
-    if (is_barrier_thread()) counter_wait(a.barrier + kCountRouted, sTarget, a.errorFlag);
-    __syncthreads();
+    __syncthreads();  // the region still holds the shared activations that phase B's warps read
     stamp(a, 5);
-    if (!a.idsIn && lane == 0 && warp >= kSharedGuWarps && warp < kBigWarps)
-        for (int e = (warp - kSharedGuWarps) * G + cta; e < E; e += (kBigWarps - kSharedGuWarps) * G) a.taggedLogits[e] = 0ull;
 
     // ---------------- phase C: routed down rows and the combine ----------------
     {
@@ -631,9 +693,8 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
                 for (int i = threadIdx.x; i < groupsF; i += blockDim.x) actSum[e * groupsF + i] = 0.0f;
             }
         }
-        stage_input(a.acts, K, F, region, a.actStride, actSum);
-        const uint16_t *res = a.shared ? a.h1 : a.residual;
-        for (; tC < tilesRD; tC += kBigWarps * G) {
+        stage_tagged(a.taggedActs, tag, K, F, region, a.actStride, actSum, a.errorFlag);
+        for (; tC < tilesRD; tC += kFusedWarps * G) {
             slot_wait(myBar, parity, a.errorFlag);
             warp_stamp(a, 2, 1);
             // this thread: expert g, tile rows g (rho 0) and g+8 (rho 1); column g of the MMA is
@@ -648,11 +709,29 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
             const float *xs = actSum + g * groupsF;
             const bool odd = g & 1;
             const int row = tC * 2 + (lane & 1);
-            float acc = (lane < 2 && res) ? bf2f(__ldcg(res + row)) : 0.0f;
+            // the residual: rows 2*tile and 2*tile+1 of the shared output are one tagged word, asked
+            // for now and checked after the arithmetic; or the caller's residual row
+            unsigned long long resWord = 0;
+            if (a.shared && lane == 0) resWord = ld_tagged(a.taggedH1 + tC);
+            float acc = (!a.shared && a.residual && lane < 2) ? bf2f(__ldcg(a.residual + row)) : 0.0f;
             float v0, v1;
             tile_rows(lo, hi, xe, sS, sB, sS + groupsF, sB + groupsF, xs, groupsF, odd, v0, v1);
             slot_release();
-            const int next = tC + kBigWarps * G;
+            if (a.shared) {
+                if (lane == 0) {
+                    uint32_t spins = 0;
+                    while ((uint32_t)(resWord >> 32) != tag) {
+                        if (++spins > kBarrierSpinLimit) {
+                            atomicExch(a.errorFlag, 9u);
+                            break;
+                        }
+                        resWord = ld_tagged(a.taggedH1 + tC);
+                    }
+                }
+                const uint32_t two = __shfl_sync(0xFFFFFFFFu, (uint32_t)resWord, 0);
+                acc = bf2f((uint16_t)((lane & 1) ? two >> 16 : two & 0xFFFFu));
+            }
+            const int next = tC + kFusedWarps * G;
             if (next < tilesRD) issue_routed_down(next);
             // lane 0 combines row 2*tile, lane 1 row 2*tile+1, experts in rank order
             for (int k = 0; k < K; ++k) {
@@ -737,7 +816,7 @@ static FusedLayout fused_layout(const FFConfig &c) {
     const uint32_t down8 = 16 * l.strideRD + 16 * l.winPitch;
     const uint32_t sharedDown = Fs ? 16 * l.strideSD + 2 * groupsFs * 32 : 0;
     l.bigBytes = (std::max({gateUp, down8, D * 2}) + 127u) & ~127u;
-    l.smallBytes = (std::max(sharedDown, 128u) + 127u) & ~127u;
+    l.smallBytes = (std::max({sharedDown, down8, 128u}) + 127u) & ~127u;
     l.total = (size_t)l.slotsOffset + (size_t)kBigWarps * l.bigBytes + (size_t)(kFusedWarps - kBigWarps) * l.smallBytes;
     return l;
 }
@@ -771,6 +850,8 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.weightsIn = weightsIn;
     a.logits = ctx->logits;
     a.taggedLogits = ctx->taggedLogits;
+    a.taggedActs = ctx->taggedActs;
+    a.taggedH1 = ctx->taggedActs + (size_t)c.topK * c.f / 2;
     a.ids = ctx->ids;
     a.weights = ctx->weights;
     a.acts = ctx->acts;

@@ -115,6 +115,7 @@ struct FFContext {
     uint32_t *errorFlag = nullptr;          // device: set by a kernel that gave up waiting
     unsigned long long *phaseStamps = nullptr;  // device: 8 phase + 288 per-warp timestamps of the fused decode kernel
     unsigned long long *taggedLogits = nullptr;  // device: [kMaxExperts] router logits of the fused decode kernel
+    unsigned long long *taggedActs = nullptr;    // device: [topK * f / 2 + d / 2] routed activations, then shared output rows, as polled words
     uint32_t *gridBarrier = nullptr;        // device: eight 64-bit counters of the fused decode kernel
     volatile unsigned long long *mailbox = nullptr;  // pinned host word the decode kernel reports to
     uint32_t hostEpoch = 0;

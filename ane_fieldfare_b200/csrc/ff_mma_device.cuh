@@ -124,6 +124,35 @@ __device__ __forceinline__ float group_scale(float acc, uint16_t scale, uint16_t
     return fmaf(fmaf(-16.0f, s, bf2f(bias)), xsum, acc);
 }
 
+// Run `i` (eight bf16 values `v`) of a staged input: stored in the order 0,4,1,5,2,6,3,7 at row
+// i / runsPerRow, and its values summed into the group's fp32 sum by a fixed butterfly over the
+// eight adjacent lanes that hold the group's runs.  Called by whole warps.
+__device__ __forceinline__ void stage_put(int i, bool valid, const uint4 &v, int runsPerRow, uint8_t *dst,
+                                          uint32_t dstStride, float *sums) {
+    uint4 o;
+    o.x = __byte_perm(v.x, v.z, 0x5410);
+    o.y = __byte_perm(v.x, v.z, 0x7632);
+    o.z = __byte_perm(v.y, v.w, 0x5410);
+    o.w = __byte_perm(v.y, v.w, 0x7632);
+    float s = 0.0f;
+    if (valid) {
+        const int r = i / runsPerRow;
+        *reinterpret_cast<uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16) = o;
+        s = __uint_as_float(o.x << 16);
+        s += __uint_as_float(o.x & 0xFFFF0000u);
+        s += __uint_as_float(o.y << 16);
+        s += __uint_as_float(o.y & 0xFFFF0000u);
+        s += __uint_as_float(o.z << 16);
+        s += __uint_as_float(o.z & 0xFFFF0000u);
+        s += __uint_as_float(o.w << 16);
+        s += __uint_as_float(o.w & 0xFFFF0000u);
+    }
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+    if (valid && (i & 7) == 0) sums[i >> 3] = s;
+}
+
 // Copies `rows` bf16 rows of `n` values (n a multiple of 64, rows contiguous at the source,
 // `dstStride` bytes apart in shared memory) with every aligned run of eight stored in the order
 // 0,4,1,5,2,6,3,7, then the fp32 sum of each group of 64 (sums[row * n/64 + group]).  All threads
@@ -147,30 +176,7 @@ __device__ __forceinline__ void stage_input(const uint16_t *src, int rows, int n
                : plainLoads                      ? reinterpret_cast<const uint4 *>(src)[si]
                                                  : __ldcg(reinterpret_cast<const uint4 *>(src) + si);
     };
-    auto put = [&](int i, bool valid, const uint4 &v) {
-        uint4 o;
-        o.x = __byte_perm(v.x, v.z, 0x5410);
-        o.y = __byte_perm(v.x, v.z, 0x7632);
-        o.z = __byte_perm(v.y, v.w, 0x5410);
-        o.w = __byte_perm(v.y, v.w, 0x7632);
-        float s = 0.0f;
-        if (valid) {
-            const int r = i / runsPerRow;
-            *reinterpret_cast<uint4 *>(dst + (size_t)r * dstStride + (size_t)(i - r * runsPerRow) * 16) = o;
-            s = __uint_as_float(o.x << 16);
-            s += __uint_as_float(o.x & 0xFFFF0000u);
-            s += __uint_as_float(o.y << 16);
-            s += __uint_as_float(o.y & 0xFFFF0000u);
-            s += __uint_as_float(o.z << 16);
-            s += __uint_as_float(o.z & 0xFFFF0000u);
-            s += __uint_as_float(o.w << 16);
-            s += __uint_as_float(o.w & 0xFFFF0000u);
-        }
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
-        s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
-        if (valid && (i & 7) == 0) sums[i >> 3] = s;
-    };
+    auto put = [&](int i, bool valid, const uint4 &v) { stage_put(i, valid, v, runsPerRow, dst, dstStride, sums); };
     for (int base = (threadIdx.x >> 5) << 5; base < runs; base += 2 * blockDim.x) {
         const int i = base + (threadIdx.x & 31), j = i + blockDim.x;
         const bool vi = i < runs, vj = j < runs;
