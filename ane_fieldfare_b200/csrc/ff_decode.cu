@@ -72,7 +72,7 @@ struct DecodeArgs {
     uint32_t *errorFlag;
     unsigned long long *stamps;  // null, or the phase / per-warp timestamp slots (ns)
     int E, D, F, Fs, K;          // K = 0: shared FFN only (y receives its output)
-    int prefetch;                // bit 0: L2 prefetch of the chosen experts' down projections
+    int prefetch;                // bit 0: L2 prefetch of the chosen experts' down projections (off by default)
     // host hand-off (null when unused): the last CTA to finish copies y to `hostY` (host memory the
     // device can write), then stores (error flag << 32 | epoch) to `mailbox`, which the host polls
     uint16_t *hostY;
@@ -96,13 +96,16 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) 
 }
 
 // The grid prefetches [base, base+bytes) in 8 KiB pieces.  Piece i belongs to CTA (i + cursor) mod
-// gridDim and to one thread of it, so every SM issues the same share: a bulk prefetch is executed
-// by the issuing SM's copy engine, whose throughput is a small fraction of HBM's.
-__device__ __forceinline__ void prefetch_region(const uint8_t *base, uint64_t bytes, uint32_t &cursor) {
+// gridDim and to one of its `nthreads` issuing threads (this one is number `tid`), so every SM
+// issues the same share: a bulk prefetch is executed by the issuing SM's copy engine, whose
+// throughput is a small fraction of HBM's.
+// `issue` false: only the cursor moves on (another warp takes this region).
+__device__ __forceinline__ void prefetch_region(const uint8_t *base, uint64_t bytes, uint32_t &cursor, uint32_t tid,
+                                                uint32_t nthreads, bool issue) {
     constexpr uint32_t kPiece = 8192;
     const uint32_t pieces = (uint32_t)((bytes + kPiece - 1) / kPiece);
     const uint32_t first = (blockIdx.x + gridDim.x - cursor % gridDim.x) % gridDim.x;
-    for (uint32_t i = first + threadIdx.x * gridDim.x; i < pieces; i += gridDim.x * blockDim.x) {
+    for (uint32_t i = first + tid * gridDim.x; issue && i < pieces; i += gridDim.x * nthreads) {
         const uint64_t offset = (uint64_t)i * kPiece;
         const uint32_t len = (uint32_t)min((uint64_t)kPiece, bytes - offset) & ~15u;
         if (len) prefetch_l2_bulk(base + offset, len);
@@ -261,7 +264,7 @@ struct InlineRow {
 // xInline: null, or the input row in parameter space (read with plain loads).
 __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMaps &maps, const uint16_t *xInline) {
     extern __shared__ __align__(128) uint8_t smemRaw[];
-    __shared__ float sLogits[kMaxExperts];
+    __shared__ __align__(16) float sLogits[kMaxExperts + 8];  // padded with -inf up to two spans of the ranking
     __shared__ uint32_t sIds[8];
     __shared__ float sWeights[8];
     __shared__ float sScore[8];
@@ -363,9 +366,11 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
     int eA = (!a.idsIn && K > 0 && warp >= kSharedGuWarps && warp < kBigWarps) ? (warp - kSharedGuWarps) * G + cta
                                                                              : 0x7FFFFFFF;
     if (eA < E) {
+        // the router's per-column scales (the same for every expert) come along behind the row
         if (lane == 0) {
-            bar_expect(myBar, (uint32_t)D * 2u);
+            bar_expect(myBar, (uint32_t)D * (a.routerScale ? 4u : 2u));
             bulk_copy(slotAddr, a.routerW + (size_t)eA * D, (uint32_t)D * 2u, myBar);
+            if (a.routerScale) bulk_copy(slotAddr + (uint32_t)D * 2u, a.routerScale, (uint32_t)D * 2u, myBar);
         }
         __syncwarp();
     }
@@ -409,35 +414,39 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
         }
         named_barrier(1 + (warp >> 2), 128);
     }
+    // eight products of one run: the row's weights and, behind them in the slot, the router's
+    // per-column scales (if any); staged input at `base`
+    auto router_run = [&](const uint16_t *wr, int base, float acc) {
+        const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
+        // the staged run holds elements 0,4,1,5,2,6,3,7: low halves are 0..3, high halves 4..7
+        const uint4 xv = *reinterpret_cast<const uint4 *>(xPerm + base * 2);
+        float xe[8] = {__uint_as_float(xv.x << 16),         __uint_as_float(xv.y << 16),
+                       __uint_as_float(xv.z << 16),         __uint_as_float(xv.w << 16),
+                       __uint_as_float(xv.x & 0xFFFF0000u), __uint_as_float(xv.y & 0xFFFF0000u),
+                       __uint_as_float(xv.z & 0xFFFF0000u), __uint_as_float(xv.w & 0xFFFF0000u)};
+        if (a.routerScale) {
+            const uint4 sv = *reinterpret_cast<const uint4 *>(wr + D + base);
+            const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                xe[2 * k] = xe[2 * k] * __uint_as_float(ss[k] << 16);
+                xe[2 * k + 1] = xe[2 * k + 1] * __uint_as_float(ss[k] & 0xFFFF0000u);
+            }
+        }
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            acc = fmaf(__uint_as_float(ww[k] << 16), xe[2 * k], acc);
+            acc = fmaf(__uint_as_float(ww[k] & 0xFFFF0000u), xe[2 * k + 1], acc);
+        }
+        return acc;
+    };
     for (; eA < E; eA += (kBigWarps - kSharedGuWarps) * G) {
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 0, 1);
         const uint16_t *wr = reinterpret_cast<const uint16_t *>(mySlot);
         float acc = 0.0f;
-        for (int base = 8 * lane; base < D; base += 256) {
-            const uint4 wv = *reinterpret_cast<const uint4 *>(wr + base);
-            // the staged run holds elements 0,4,1,5,2,6,3,7: low halves are 0..3, high halves 4..7
-            const uint4 xv = *reinterpret_cast<const uint4 *>(xPerm + base * 2);
-            float xe[8] = {__uint_as_float(xv.x << 16),         __uint_as_float(xv.y << 16),
-                           __uint_as_float(xv.z << 16),         __uint_as_float(xv.w << 16),
-                           __uint_as_float(xv.x & 0xFFFF0000u), __uint_as_float(xv.y & 0xFFFF0000u),
-                           __uint_as_float(xv.z & 0xFFFF0000u), __uint_as_float(xv.w & 0xFFFF0000u)};
-            if (a.routerScale) {
-                const uint4 sv = *reinterpret_cast<const uint4 *>(a.routerScale + base);
-                const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    xe[2 * k] = xe[2 * k] * __uint_as_float(ss[k] << 16);
-                    xe[2 * k + 1] = xe[2 * k + 1] * __uint_as_float(ss[k] & 0xFFFF0000u);
-                }
-            }
-            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                acc = fmaf(__uint_as_float(ww[k] << 16), xe[2 * k], acc);
-                acc = fmaf(__uint_as_float(ww[k] & 0xFFFF0000u), xe[2 * k + 1], acc);
-            }
-        }
+        for (int base = 8 * lane; base < D; base += 256) acc = router_run(wr, base, acc);
 #pragma unroll
         for (int offset = 16; offset >= 1; offset >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, offset);
         if (lane == 0) {
@@ -449,8 +458,9 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
         slot_release();
         const int next = eA + (kBigWarps - kSharedGuWarps) * G;
         if (next < E && lane == 0) {
-            bar_expect(myBar, (uint32_t)D * 2u);
+            bar_expect(myBar, (uint32_t)D * (a.routerScale ? 4u : 2u));
             bulk_copy(slotAddr, a.routerW + (size_t)next * D, (uint32_t)D * 2u, myBar);
+            if (a.routerScale) bulk_copy(slotAddr + (uint32_t)D * 2u, a.routerScale, (uint32_t)D * 2u, myBar);
         }
         __syncwarp();
     }
@@ -489,27 +499,32 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
                     if (e0 + i < E) sLogits[e0 + i] = __uint_as_float((uint32_t)w[i]);
             }
         }
+        const int rankSpan = (((E + 1) >> 1) + 3) & ~3;
         if (tid2 < 8) {
             sIds[tid2] = 0u;
             sScore[tid2] = -INFINITY;
+        } else if (tid2 >= 32 && tid2 < 40 && E + tid2 - 32 < 2 * rankSpan) {
+            sLogits[E + tid2 - 32] = -INFINITY;
         }
         named_barrier(8, kTopkThreads);
         // rank of every logit under (higher score, then lower expert id); scores of -inf or NaN
         // are never taken — the order of the serial top-8 (moe.metal:269-303).  Two threads per
-        // expert, each counting half of the competitors with the loads unrolled.
+        // expert, each counting the competitors of one span (a multiple of four, read as float4).
         {
-            const int halfSpan = (E + 1) >> 1;
             for (int idx = tid2; idx < 2 * ((E + 127) & ~127); idx += kTopkThreads) {
                 const int e = idx >> 1, half = idx & 1;
                 const float v = e < E ? sLogits[e] : -INFINITY;
-                const int begin = half * halfSpan, end = min(E, begin + halfSpan);
-                // competitors before e win ties, those after e do not
-                const int mid = min(max(e, begin), end);
+                const int begin = half * rankSpan;
                 int rank = 0;
-#pragma unroll 8
-                for (int o = begin; o < mid; ++o) rank += sLogits[o] >= v ? 1 : 0;
-#pragma unroll 8
-                for (int o = max(mid, e + 1); o < end; ++o) rank += sLogits[o] > v ? 1 : 0;
+#pragma unroll 4
+                for (int o = begin; o < begin + rankSpan; o += 4) {
+                    const float4 c = *reinterpret_cast<const float4 *>(sLogits + o);
+                    // a competitor wins with a higher score, or the same score and a lower id
+                    rank += (c.x > v || (c.x == v && o < e)) ? 1 : 0;
+                    rank += (c.y > v || (c.y == v && o + 1 < e)) ? 1 : 0;
+                    rank += (c.z > v || (c.z == v && o + 2 < e)) ? 1 : 0;
+                    rank += (c.w > v || (c.w == v && o + 3 < e)) ? 1 : 0;
+                }
                 rank += __shfl_xor_sync(0xFFFFFFFFu, rank, 1);
                 if (half == 0 && v > -INFINITY && rank < K) {
                     sIds[rank] = (uint32_t)e;
@@ -557,14 +572,6 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
                       a.experts + (size_t)sIds[slot] * a.stride, a.off, tB - slot * tilesF, warp & 1, 2, a.strideGU);
     }
     warp_stamp(a, 1, 0);
-    if ((a.prefetch & 1) && K > 0) {
-        // the down projections of the chosen experts go to L2 now and are read in phase C
-        for (int k = 0; k < K; ++k) {
-            const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
-            prefetch_region(blob + a.off.downWOff,
-                            (uint64_t)a.off.downBOff - a.off.downWOff + (uint64_t)D * F / kGroup * 2, cursor);
-        }
-    }
     // Routed down tile: output rows 2*tile, 2*tile+1 of all eight experts.  Tile row rho*8 + e is
     // row 2*tile+rho of expert e; lane l copies row piece l (l < 16), or the 16-byte aligned window
     // around the two rows' scales (l even) or biases (l odd) of expert (l-16)/2.
@@ -596,9 +603,23 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
         __syncthreads();
         stage_input(a.sharedActs, 1, Fs, saPerm, 0, saSum);
     }
+    bool downAsked = !(a.prefetch & 1) || warp >= K;
     for (; tB < tilesRouted; tB += (kBigWarps / 2) * G) {
         slot_wait(myBar, parity, a.errorFlag);
         warp_stamp(a, 1, 1);
+        if (!downAsked) {
+            // The down projections of the chosen experts go to L2 for phase C: warp k asks for
+            // expert k's once its own rows are there.  Earlier, the prefetch shares HBM with the
+            // gate/up rows that the arithmetic is waiting for; from here on it runs under the
+            // arithmetic.
+            for (int k = 0; k < K; ++k) {
+                const uint8_t *blob = a.experts + (size_t)sIds[k] * a.stride;
+                prefetch_region(blob + a.off.downWOff,
+                                (uint64_t)a.off.downBOff - a.off.downWOff + (uint64_t)D * F / kGroup * 2, cursor, lane, 32,
+                                k == warp);
+            }
+            downAsked = true;
+        }
         float gate, up;
         compute_gate_up(warp & 1, 2, a.strideGU, xPerm, xSum, gate, up);
         slot_release();
@@ -815,7 +836,7 @@ static FusedLayout fused_layout(const FFConfig &c) {
     const uint32_t gateUp = 16 * l.strideGU + 4 * groupsD * 16;
     const uint32_t down8 = 16 * l.strideRD + 16 * l.winPitch;
     const uint32_t sharedDown = Fs ? 16 * l.strideSD + 2 * groupsFs * 32 : 0;
-    l.bigBytes = (std::max({gateUp, down8, D * 2}) + 127u) & ~127u;
+    l.bigBytes = (std::max({gateUp, down8, D * 4}) + 127u) & ~127u;
     l.smallBytes = (std::max({sharedDown, down8, 128u}) + 127u) & ~127u;
     l.total = (size_t)l.slotsOffset + (size_t)kBigWarps * l.bigBytes + (size_t)(kFusedWarps - kBigWarps) * l.smallBytes;
     return l;
@@ -864,7 +885,7 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     static int prefetchMode = -1;
     if (prefetchMode < 0) {
         const char *env = getenv("FF_DECODE_PREFETCH");
-        prefetchMode = env ? atoi(env) : 1;
+        prefetchMode = env ? atoi(env) : 0;  // off: measured slower than the early requests of phase C's tiles
     }
     a.prefetch = prefetchMode;
     a.E = idsIn ? (int)L.expertCount : (int)L.routerExperts;

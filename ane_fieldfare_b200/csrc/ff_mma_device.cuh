@@ -40,11 +40,13 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-// Orders this warp's earlier shared-memory reads of its slot before the next bulk copies into it.
-__device__ __forceinline__ void slot_release() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncwarp();
-}
+// Called by the whole warp when it has used its slot's contents, before the next copies into the
+// slot are requested.  The values read from the slot have been consumed by then (the arithmetic
+// depends on them), so the reads are complete; the warp barrier orders every lane's reads before
+// the requesting lane's next copy — the consumer-release / producer-acquire hand-off of a copy
+// pipeline, with the warp barrier in place of the "empty" mbarrier.  (A proxy fence here would also
+// wait for the warp's outstanding L2 prefetches.)
+__device__ __forceinline__ void slot_release() { __syncwarp(); }
 // Bounded wait for the warp's copies; flips the parity.  On running out the error flag is raised
 // and the warp carries on (its rows are then wrong, the launch still ends).
 __device__ __forceinline__ void slot_wait(uint32_t bar, uint32_t &parity, uint32_t *errorFlag) {
