@@ -114,8 +114,9 @@ uint32_t ff_get_trace(FFContext *ctx, FFTraceEntry *entries, uint32_t capacity);
 
 /* Phase times of the last one-token ff_moe_layer / ff_moe_decode launched while tracing was on,
  * in microseconds, from timestamps the first CTA takes inside the kernel: [0] phase A work
- * (prefetch, router, shared gate/up), [1] first grid barrier, [2] top-k, [3] phase B work (routed
- * gate/up, shared down), [4] second grid barrier, [5] phase C (routed down + combine).  A
+ * (router, shared gate/up), [1] wait for the top-k warps, [2] publishing the routes, [3] phase B
+ * work (routed gate/up, shared down), [4] requests of phase C's tiles and the CTA-wide wait for phase B's
+ * warps, [5] phase C (polling the routed activations, routed down + combine).  A
  * diagnostic with no counterpart in the reference beyond its per-phase GPU nanoseconds
  * (Runtime/Inference/RealForwardRunner.swift:2146-2150). */
 bool ff_decode_phase_times(FFContext *ctx, double *microseconds, const char **error);
