@@ -3,17 +3,21 @@
 //
 // The step streams 37.5 MB of weights once; at B200's HBM rate that is under 6 us, so separate
 // kernels (launch gaps, cold starts) cannot come near the roofline.  Here one CTA per SM runs
-// three phases separated by two grid-wide barriers:
+// three phases:
 //   A  router logits (one warp per expert) and the shared gate/up/GeGLU rows; the shared down
 //      rows are already requested;
 //   B  every CTA ranks the 128 logits itself (top-8, softmax, gain), then routed gate/up/GeGLU
-//      rows and the shared down rows; the routed down rows are requested before the barrier;
+//      rows and the shared down rows; the routed down rows are requested as the warps finish;
 //   C  routed down rows and the fixed-order combine onto the shared output (or the caller's
 //      residual).
+// Values cross from CTA to CTA as tagged 64-bit words that the readers poll (logits, routed
+// activations, shared output rows: value and validity in one L2 round trip), and through one
+// arrival counter (the shared activations between A and B).
 //
-// Weight rows reach the SM as bulk asynchronous copies (cp.async.bulk, one per row piece,
-// completion counted on a per-warp mbarrier) into a per-warp shared-memory slot: a warp has its
-// whole task in flight after one instruction per lane.
+// Weight rows reach the SM as asynchronous copies (completion counted on a per-warp mbarrier)
+// into a per-warp shared-memory slot: cp.async.bulk.tensor over row-box maps of the layer where a
+// tile's rows lie at one stride (one request brings 8 or 16 row pieces), cp.async.bulk for scale
+// runs and for the routed down rows of the eight scattered experts.
 //
 // Row arithmetic runs on the tensor cores without dequantizing: a warp task is a tile of 16 weight
 // rows; per group of 64 codes the packed nibbles are turned into the bf16 values 16+q with two
@@ -119,9 +123,9 @@ __device__ __forceinline__ void prefetch_region(const uint8_t *base, uint64_t by
 // counter [0] (shared activations written) — also when a mode does not wait on it — so "everyone
 // has arrived" is counter >= (g + 1) * gridDim.  An arrival is a release reduction without a
 // return value; a wait polls the counter with acquire loads, bounded.  No reset, no host-side
-// state.  [2] counts finished CTAs for the host hand-off.  The low 32 bits of g + 1 are the
-// launch's tag for the values that travel as polled words (logits, routed activations, shared
-// output rows).
+// state.  [2] counts finished CTAs for the host hand-off.  g also gives the launch's 32-bit tag
+// (never 0, different for consecutive launches) for the values that travel as polled words
+// (logits, routed activations, shared output rows).
 enum : int { kCountShared = 0, kCountDone = 2, kCountTicket = 3 };
 
 __device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long *p) {
@@ -270,7 +274,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
     __shared__ float sScore[8];
     __shared__ __align__(8) uint64_t sCopyBar[kFusedWarps];
     __shared__ unsigned long long sTarget;  // (generation + 1) * gridDim
-    __shared__ uint32_t sTag;               // low 32 bits of generation + 1 (never 0)
+    __shared__ uint32_t sTag;               // the launch's tag for polled words, from the generation
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = (int)gridDim.x, cta = (int)blockIdx.x;
@@ -388,7 +392,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
     if (threadIdx.x == 9 * 32) {
         const unsigned long long gen1 = ticket / gridDim.x + 1ull;
         sTarget = gen1 * gridDim.x;
-        sTag = (uint32_t)gen1 ? (uint32_t)gen1 : 0xFFFFFFFFu;
+        sTag = (uint32_t)(gen1 % 0xFFFFFFFFull) + 1u;  // 1 .. 2^32-1: never 0, consecutive launches differ
     }
     stage_input(xSrc, 1, D, xPerm, 0, xSum, xPlain, &xMine);  // ends with a CTA barrier: target and tag are published
     const uint32_t tag = sTag;
