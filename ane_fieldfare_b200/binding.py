@@ -88,6 +88,8 @@ SIGNATURES = {
                                    c_uint32, _P, _ERR]),
     "ff_rmsnorm": (c_bool, [c_void_p, _P, _P, c_float, c_uint32, _P, _P, _ERR]),
     "ff_moe_layer": (c_bool, [c_void_p, c_uint32, _P, c_uint32, _P, _P, _P, _P, _ERR]),
+    "ff_moe_stack": (c_bool, [c_void_p, c_uint32, c_uint32, _P, c_uint32, c_float, _P, _P, _P, _ERR]),
+    "ff_reset_device_error": (c_bool, [c_void_p, _ERR]),
     "ff_moe_layer_host": (c_bool, [c_void_p, c_uint32, _P, c_uint32, _P, _ERR]),
     "ff_make_token_expert_pairs": (c_uint64, [_P, _P, c_uint32, c_uint32, POINTER(FFTokenExpertPair)]),
     "ff_group_token_expert_pairs": (c_bool, [POINTER(FFTokenExpertPair), c_uint64, c_uint32, c_uint32,

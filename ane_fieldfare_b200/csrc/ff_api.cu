@@ -144,6 +144,11 @@ bool ff_moe_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *wei
     Call c;
     if (!begin(ctx, 0, stream, error, &c)) return false;
     if (!partials || !weights || !y) return fail(error, "null argument");
+    if (tokens > ctx->cfg.maxTokens) return fail(error, "rows exceed the context's maxTokens");
+    // the kernel reads and writes pairs of 16-bit values as 32-bit words
+    if ((reinterpret_cast<uintptr_t>(partials) & 3u) || (reinterpret_cast<uintptr_t>(y) & 3u) ||
+        (reinterpret_cast<uintptr_t>(residual) & 3u) || (reinterpret_cast<uintptr_t>(weights) & 1u) || ctx->cfg.d % 2)
+        return fail(error, "partials, residual and output rows must be 4-byte aligned");
     return launch_reduce(ctx, partials, weights, residual, y, tokens, c.stream, error);
 }
 
@@ -170,7 +175,12 @@ bool ff_int4_gemv_rows(FFContext *ctx, const FFProjection *projection, const uin
     if (!projection || !x || !y) return fail(error, "null argument");
     if (xStride < projection->cols || yStride < projection->rows)
         return fail(error, "row stride is too small");
-    if (xStride % 2) return fail(error, "input stride must be even");
+    if (xStride % 2 || (reinterpret_cast<uintptr_t>(x) & 3u))
+        return fail(error, "input rows must be 4-byte aligned (even stride)");
+    if (reinterpret_cast<uintptr_t>(y) & 1u) return fail(error, "output rows must be 2-byte aligned");
+    if (!projection->weights || !projection->scales || !projection->biases ||
+        (reinterpret_cast<uintptr_t>(projection->scales) & 1u) || (reinterpret_cast<uintptr_t>(projection->biases) & 1u))
+        return fail(error, "projection pointers must be non-null, scales and biases 2-byte aligned");
     return launch_gemv_rows(ctx, *projection, x, xStride, rows, y, yStride, c.stream, error);
 }
 
@@ -179,6 +189,9 @@ bool ff_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float eps,
     Call c;
     if (!begin(ctx, 0, stream, error, &c)) return false;
     if (!x || !y) return fail(error, "null argument");
+    if ((reinterpret_cast<uintptr_t>(x) & 1u) || (reinterpret_cast<uintptr_t>(y) & 1u) ||
+        (reinterpret_cast<uintptr_t>(w) & 1u))
+        return fail(error, "rows must be 2-byte aligned");
     return launch_rmsnorm(ctx, x, w, eps, tokens, y, c.stream, error);
 }
 
@@ -222,6 +235,41 @@ bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t to
         FF_CUDA_OK(cudaMemcpyAsync(weights, ctx->weights, routeCount * sizeof(uint16_t),
                                    cudaMemcpyDeviceToDevice, c.stream),
                    error);
+    return true;
+}
+
+// A stack of MoE blocks with an RMSNorm (no weight) in front of each: x <- block_l(rmsnorm(x)).
+bool ff_moe_stack(FFContext *ctx, uint32_t firstLayer, uint32_t layerCount, const uint16_t *x,
+                  uint32_t tokens, float eps, uint16_t *y, uint32_t *ids, void *stream,
+                  const char **error) {
+    Call c;
+    if (!begin(ctx, firstLayer, stream, error, &c)) return false;
+    const FFConfig &cfg = ctx->cfg;
+    if (layerCount == 0 || firstLayer + layerCount > cfg.layers)
+        return fail(error, "layers " + std::to_string(firstLayer) + "..+" + std::to_string(layerCount) +
+                               " are out of range");
+    if (!check_rows(ctx, x, cfg.d, tokens, error)) return false;
+    if (!y || (reinterpret_cast<uintptr_t>(y) & 15u)) return fail(error, "output rows must be non-null and 16-byte aligned");
+    if (tokens == 0) return true;
+    const uint16_t *cur = x;
+    const size_t routeCount = (size_t)tokens * cfg.topK;
+    for (uint32_t i = 0; i < layerCount; ++i) {
+        if (!launch_rmsnorm(ctx, cur, nullptr, eps, tokens, ctx->xDev, c.stream, error)) return false;
+        uint16_t *out = i + 1 == layerCount ? y : ctx->yDev;
+        if (!ff_moe_layer(ctx, firstLayer + i, ctx->xDev, tokens, out, ids ? ids + i * routeCount : nullptr,
+                          nullptr, stream, error))
+            return false;
+        cur = out;
+    }
+    return true;
+}
+
+bool ff_reset_device_error(FFContext *ctx, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx) return fail(error, "null context");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    FF_CUDA_OK(cudaDeviceSynchronize(), error);
+    FF_CUDA_OK(cudaMemset(ctx->errorFlag, 0, sizeof(uint32_t)), error);
     return true;
 }
 

@@ -276,14 +276,9 @@ static bool launch_block_class(FFContext *ctx, const GemvJob *jobs, const uint32
     a.slotBytes = lay.slotBytes;
     a.slotsOffset = lay.slotsOffset;
     a.errorFlag = ctx->errorFlag;
-    static size_t configured[2][8] = {{0}};
-    const int slot = ctx->device & 7;
-    if (configured[DUAL ? 1 : 0][slot] < lay.total) {
-        FF_CUDA_OK(cudaFuncSetAttribute(k_block_mma<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)lay.total),
-                   error);
-        configured[DUAL ? 1 : 0][slot] = lay.total;
-    }
+    static KernelSmemMemo memo;
+    if (!memo.prepare(k_block_mma<DUAL>, ctx->device, lay.total, (DUAL ? kGateUpWarps : kDownWarps) * 32, nullptr, error))
+        return false;
     LaunchScope scope(ctx, stream, name);
     k_block_mma<DUAL><<<ctx->smCount, (DUAL ? kGateUpWarps : kDownWarps) * 32, lay.total, stream>>>(a);
     FF_CUDA_OK(cudaGetLastError(), error);

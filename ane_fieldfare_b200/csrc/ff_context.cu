@@ -363,7 +363,9 @@ bool ff_load_router(FFContext *ctx, uint32_t layer, const uint16_t *weights,
     if (d != ctx->cfg.d) return fail(error, "router width does not match the context");
     if (experts == 0 || experts > (uint32_t)kMaxExperts)
         return fail(error, "numExperts > 256 is not supported");
-    if (experts < ctx->cfg.topK) return fail(error, "fewer experts than routes per token");
+    if (experts != ctx->cfg.experts)
+        return fail(error, "router has " + std::to_string(experts) + " experts, the context expects " +
+                               std::to_string(ctx->cfg.experts));
     FF_CUDA_OK(cudaSetDevice(ctx->device), error);
     LayerStore &L = ctx->layers[layer];
     cudaFree(L.routerW);

@@ -40,6 +40,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <string>
 
 #include "ff_mma_device.cuh"
 
@@ -76,6 +77,7 @@ struct DecodeArgs {
     uint32_t *errorFlag;
     unsigned long long *stamps;  // null, or the phase / per-warp timestamp slots (ns)
     int E, D, F, Fs, K;          // K = 0: shared FFN only (y receives its output)
+    int expertCount;             // resident experts of the layer: routes at or past it are refused
     int prefetch;                // bit 0: L2 prefetch of the chosen experts' down projections (off by default)
     // host hand-off (null when unused): the last CTA to finish copies y to `hostY` (host memory the
     // device can write), then stores (error flag << 32 | epoch) to `mailbox`, which the host polls
@@ -556,9 +558,19 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
             }
         }
     } else {
+        // Given routes.  A route past the resident experts would address memory outside the layer:
+        // it is replaced by expert 0 with weight 0 and reported through the error flag (the
+        // reference refuses such a route with "route expert N is out of range").
         if (K > 0 && a.idsIn && threadIdx.x < K) {
-            sIds[threadIdx.x] = a.idsIn[threadIdx.x];
-            sWeights[threadIdx.x] = bf2f(a.weightsIn[threadIdx.x]);
+            uint32_t id = a.idsIn[threadIdx.x];
+            float w = bf2f(a.weightsIn[threadIdx.x]);
+            if (id >= (uint32_t)a.expertCount) {
+                atomicExch(a.errorFlag, 12u);
+                id = 0u;
+                w = 0.0f;
+            }
+            sIds[threadIdx.x] = id;
+            sWeights[threadIdx.x] = w;
         }
     }
     // barrier 1 covers the shared activations; the routed rows are requested between arriving
@@ -886,13 +898,16 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.barrier = reinterpret_cast<unsigned long long *>(ctx->gridBarrier);
     a.errorFlag = ctx->errorFlag;
     a.stamps = ctx->tracing ? ctx->phaseStamps : nullptr;
-    static int prefetchMode = -1;
-    if (prefetchMode < 0) {
+    static const int prefetchMode = [] {
         const char *env = getenv("FF_DECODE_PREFETCH");
-        prefetchMode = env ? atoi(env) : 0;  // off: measured slower than the early requests of phase C's tiles
-    }
+        return env ? atoi(env) : 0;  // off: measured slower than the early requests of phase C's tiles
+    }();
     a.prefetch = prefetchMode;
     a.E = idsIn ? (int)L.expertCount : (int)L.routerExperts;
+    a.expertCount = (int)L.expertCount;
+    if (routed && !idsIn && L.routerExperts != L.expertCount)
+        return fail(error, "router has " + std::to_string(L.routerExperts) + " experts, the layer " +
+                               std::to_string(L.expertCount));
     a.D = (int)c.d;
     a.F = (int)c.f;
     a.Fs = withShared ? (int)c.sharedF : 0;
@@ -945,28 +960,13 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     a.actStride = lay.actStride;
     a.winBytes = lay.winBytes;
     a.winPitch = lay.winPitch;
-    static size_t configured[8] = {0};
-    static int gridFor[8] = {0};
-    const int slot = ctx->device & 7;
-    if (configured[slot] != smem) {
-        FF_CUDA_OK(cudaFuncSetAttribute(k_decode_fused, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem),
-                   error);
-        FF_CUDA_OK(cudaFuncSetAttribute(k_decode_fused_inline_x, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem),
-                   error);
-        int perSm = 0;
-        FF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, k_decode_fused, kFusedThreads,
-                                                                 smem),
-                   error);
-        if (perSm < 1) return fail(error, "fused decode kernel does not fit on an SM");
-        FF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, k_decode_fused_inline_x, kFusedThreads,
-                                                                 smem),
-                   error);
-        if (perSm < 1) return fail(error, "fused decode kernel does not fit on an SM");
-        gridFor[slot] = ctx->smCount;
-        configured[slot] = smem;
-    }
+    static KernelSmemMemo memo, memoInline;
+    int perSm = 0;
+    if (!memo.prepare(k_decode_fused, ctx->device, smem, kFusedThreads, &perSm, error)) return false;
+    if (perSm < 1) return fail(error, "fused decode kernel does not fit on an SM");
+    if (!memoInline.prepare(k_decode_fused_inline_x, ctx->device, smem, kFusedThreads, &perSm, error)) return false;
+    if (perSm < 1) return fail(error, "fused decode kernel does not fit on an SM");
+    const int grid = ctx->smCount;
     if (host) {
         a.hostY = host->hostY;
         a.mailbox = host->mailbox;
@@ -979,11 +979,11 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
         memcpy(&row, host->inlineX, (size_t)c.d * 2);
         void *params[] = {&a, &maps, &row};
         FF_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(k_decode_fused_inline_x),
-                                               dim3(gridFor[slot]), dim3(kFusedThreads), params, smem, stream),
+                                               dim3(grid), dim3(kFusedThreads), params, smem, stream),
                    error);
     } else {
         void *params[] = {&a, &maps};
-        FF_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(k_decode_fused), dim3(gridFor[slot]),
+        FF_CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(k_decode_fused), dim3(grid),
                                                dim3(kFusedThreads), params, smem, stream),
                    error);
     }

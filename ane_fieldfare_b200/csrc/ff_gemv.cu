@@ -158,71 +158,6 @@ k_router_logits(const uint16_t *W, const uint16_t *scale, const float *bias, con
     if (lane == 0) logits[(size_t)t * E + e] = bias ? acc + bias[e] : acc;
 }
 
-// Warp-wide top-K over E <= 256 logits held four-plus per lane: K rounds of argmax (higher score,
-// then lower expert id), softmax over the selected scores, times the per-expert gain.  Selection
-// rule and softmax: Metal/MoE/moe.metal:186-237,269-319.
-// sharedIds: optional copy of the ids in shared memory.
-__device__ void warp_topk(const float *logits, int E, int K, const uint16_t *gain, uint32_t *ids,
-                          uint16_t *weights, uint32_t *sharedIds = nullptr) {
-    const int lane = threadIdx.x & 31;
-    float v[8];
-    uint32_t live = 0;  // bit j: candidate j of this lane is still in the race (a register, not an indexed array)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int e = j * 32 + lane;
-        v[j] = e < E ? logits[e] : -INFINITY;
-        if (e < E && v[j] > -INFINITY) live |= 1u << j;
-    }
-    float topScore[8];
-    uint32_t topIdx[8];
-    for (int r = 0; r < 8; ++r) {
-        float best = -INFINITY;
-        uint32_t bestE = 0xFFFFFFFFu;
-        if (r < K) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t e = (uint32_t)(j * 32 + lane);
-                if (((live >> j) & 1u) && (v[j] > best || (v[j] == best && e < bestE))) {
-                    best = v[j];
-                    bestE = e;
-                }
-            }
-        }
-#pragma unroll
-        for (int offset = 16; offset >= 1; offset >>= 1) {
-            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, offset);
-            const uint32_t oe = __shfl_xor_sync(0xFFFFFFFFu, bestE, offset);
-            if (oe != 0xFFFFFFFFu && (bestE == 0xFFFFFFFFu || ob > best || (ob == best && oe < bestE))) {
-                best = ob;
-                bestE = oe;
-            }
-        }
-        if (bestE != 0xFFFFFFFFu && (bestE & 31u) == (uint32_t)lane) live &= ~(1u << (bestE >> 5));
-        topIdx[r] = bestE == 0xFFFFFFFFu ? 0u : bestE;
-        topScore[r] = bestE == 0xFFFFFFFFu ? -INFINITY : best;
-    }
-    // softmax over the chosen scores: lane r holds route r; exponentials in parallel, the sum in
-    // rank order (the same additions as a serial loop)
-    float myScore = -INFINITY;
-    uint32_t myIdx = 0;
-#pragma unroll
-    for (int r = 0; r < 8; ++r)
-        if (lane == r) {
-            myScore = topScore[r];
-            myIdx = topIdx[r];
-        }
-    const float ex = lane < K ? expf(myScore - topScore[0]) : 0.0f;
-    float sum = 0.0f;
-    for (int r = 0; r < K; ++r) sum += __shfl_sync(0xFFFFFFFFu, ex, r);
-    if (lane < K) {
-        float w = ex / sum;
-        if (gain) w = w * bf2f(gain[myIdx]);
-        ids[lane] = myIdx;
-        weights[lane] = f2bf(w);
-        if (sharedIds) sharedIds[lane] = myIdx;
-    }
-}
-
 struct PlanArgs {
     const float *logits;      // [T][E] or null (ids given)
     const uint16_t *gain;
@@ -244,6 +179,7 @@ struct PlanArgs {
     GemvJob *jobs0, *jobs1;
     RoutePlan *plan;
     int buildPlan;            // 0: top-K only
+    uint32_t *errorFlag;      // raised when a route names an expert that is not resident
 };
 
 // One CTA: top-K per token (when logits are given), then the route plan — the role of the
@@ -281,6 +217,10 @@ __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
         if (mine < (uint32_t)a.E && place < a.T) {
             sList[mine * kMaxGemvRows + place] = (uint8_t)r;
             atomicAdd(&sCount[mine], 1u);
+        } else {
+            // the reference refuses such a route ("route expert N is out of range"); here its
+            // partial row stays unwritten and the context's error flag says so
+            atomicExch(a.errorFlag, 12u);
         }
     }
     __syncthreads();
@@ -476,6 +416,16 @@ static size_t gemv_smem_bytes(int rows, uint32_t maxCols) {
     return (size_t)rows * (staged_stride((int)maxCols) + (maxCols >> 5)) * sizeof(float);
 }
 
+constexpr size_t kGemvSmemLimit = 200 * 1024;
+static uint32_t gemv_rows_class(uint32_t n) { return n <= 1 ? 1 : n <= 2 ? 2 : n <= 4 ? 4 : n <= 8 ? 8 : 16; }
+// Input rows one launch can stage for a job of `n` rows and `cols` columns: the job's row class,
+// or the largest smaller class that fits in shared memory; 0 when not even one row fits.
+static uint32_t gemv_pass_rows(uint32_t n, uint32_t cols) {
+    for (uint32_t c = gemv_rows_class(n); c >= 1; c >>= 1)
+        if (gemv_smem_bytes((int)c, cols) <= kGemvSmemLimit) return c;
+    return 0;
+}
+
 // The input block all jobs of a launch read (staged once per CTA), or null.
 struct StageAll {
     const uint16_t *in = nullptr;
@@ -489,28 +439,14 @@ static bool launch_gemv_kernel(FFContext *ctx, const GemvJob *jobs, const uint32
                                const StageAll &all, cudaStream_t stream, const char **error) {
     auto kernel = k_int4_gemv<MAXNT, DUAL, STAGE_ALL>;
     const size_t smem = gemv_smem_bytes(STAGE_ALL ? (int)all.rows : MAXNT, maxCols);
-    if (smem > 200 * 1024)
+    if (smem > kGemvSmemLimit)
         return fail(error, "input rows do not fit in shared memory: " + std::to_string(MAXNT) +
                                " rows x " + std::to_string(maxCols) + " columns");
-    // attribute + occupancy are looked up once per (kernel, shared-memory size): nothing but the
-    // launch itself happens on later calls, which keeps the call legal under stream capture
-    static size_t cachedSmem[8] = {0};
-    static int cachedPerSm[8] = {0};
-    static int cachedDevice[8] = {-1, -1, -1, -1, -1, -1, -1, -1};
+    // attribute + occupancy are looked up once per (kernel, device, shared-memory size): nothing but
+    // the launch itself happens on later calls, which keeps the call legal under stream capture
+    static KernelSmemMemo memo;
     int perSm = 0;
-    const int slot = ctx->device & 7;
-    if (cachedDevice[slot] == ctx->device && cachedSmem[slot] == smem) {
-        perSm = cachedPerSm[slot];
-    } else {
-        FF_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem),
-                   error);
-        FF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, kGemvThreads, smem),
-                   error);
-        cachedDevice[slot] = ctx->device;
-        cachedSmem[slot] = smem;
-        cachedPerSm[slot] = perSm;
-    }
+    if (!memo.prepare(kernel, ctx->device, smem, kGemvThreads, &perSm, error)) return false;
     if (perSm < 1) return fail(error, "GEMV kernel does not fit on an SM");
     uint32_t grid = (uint32_t)(ctx->smCount * perSm);
     if (itemBound < grid) grid = itemBound;
@@ -543,6 +479,29 @@ static bool launch_gemv_class(FFContext *ctx, uint32_t rowsClass, const GemvJob 
 
 static uint32_t blocks_of(uint32_t rows) { return (rows + kRowsPerItem - 1) / kRowsPerItem; }
 
+// One job given by value (a matrix, or a gate/up pair, against job.n <= 16 input rows).  When the
+// rows of the job's class do not fit in shared memory together (wide matrices), the job runs as
+// passes of fewer rows: the arithmetic per (weight row, input row) does not depend on how many
+// rows a launch carries, so the bits are those of a single pass.
+template <bool DUAL>
+static bool launch_inline_job(FFContext *ctx, const GemvJob &job, cudaStream_t stream, const char **error) {
+    const uint32_t pass = gemv_pass_rows(job.n, job.cols);
+    if (pass == 0)
+        return fail(error, "one input row of " + std::to_string(job.cols) + " columns does not fit in shared memory");
+    for (uint32_t first = 0; first < job.n; first += pass) {
+        GemvJob part = job;
+        part.n = std::min(pass, job.n - first);
+        for (uint32_t i = 0; i < (uint32_t)kMaxGemvRows; ++i) {
+            part.inRow[i] = i < part.n ? job.inRow[first + i] : 0u;
+            part.outRow[i] = i < part.n ? job.outRow[first + i] : 0u;
+        }
+        if (!launch_gemv_class<DUAL>(ctx, part.n, nullptr, nullptr, nullptr, part, blocks_of(part.rows), part.cols,
+                                     blocks_of(part.rows), stream, error))
+            return false;
+    }
+    return true;
+}
+
 bool launch_router_topk(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
                         uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
                         cudaStream_t stream, const char **error) {
@@ -567,6 +526,7 @@ bool launch_router_topk(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     a.E = E;
     a.K = (int)ctx->cfg.topK;
     a.buildPlan = 0;
+    a.errorFlag = ctx->errorFlag;
     {
         LaunchScope scope(ctx, stream, "topk_plan");
         k_topk_plan<<<1, 512, 0, stream>>>(a);
@@ -598,6 +558,7 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     uint16_t *weightsDev = ctx->weights;
     if (!ids) {
         if (!L.routerW) return fail(error, "layer has no resident router");
+        if (L.routerExperts != L.expertCount) return fail(error, "router and layer disagree on the expert count");
         dim3 grid((L.routerExperts + 7) / 8, tokens);
         {
             LaunchScope scope(ctx, stream, "router_logits");
@@ -635,6 +596,7 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     a.jobs1 = ctx->jobs[1];
     a.plan = ctx->plan;
     a.buildPlan = 1;
+    a.errorFlag = ctx->errorFlag;
     {
         LaunchScope scope(ctx, stream, "topk_plan");
         k_topk_plan<<<1, 512, 0, stream>>>(a);
@@ -680,8 +642,7 @@ bool launch_gemv_rows(FFContext *ctx, const FFProjection &p, const uint16_t *x, 
     job.outStride = yStride;
     job.n = rows;
     for (uint32_t i = 0; i < kMaxGemvRows; ++i) job.inRow[i] = job.outRow[i] = i < rows ? i : 0u;
-    return launch_gemv_class<false>(ctx, rows, nullptr, nullptr, nullptr, job, blocks_of(p.rows),
-                                    p.cols, blocks_of(p.rows), stream, error);
+    return launch_inline_job<false>(ctx, job, stream, error);
 }
 
 // Shared FFN for up to 16 rows without a route plan: gate/up/GeGLU job, then the down job.
@@ -718,11 +679,8 @@ bool launch_shared_small(FFContext *ctx, const LayerStore &L, const uint16_t *x,
     j1.n = tokens;
     for (uint32_t i = 0; i < kMaxGemvRows; ++i)
         j0.inRow[i] = j0.outRow[i] = j1.inRow[i] = j1.outRow[i] = i < tokens ? i : 0u;
-    if (!launch_gemv_class<true>(ctx, tokens, nullptr, nullptr, nullptr, j0, blocks_of(j0.rows),
-                                 j0.cols, blocks_of(j0.rows), stream, error))
-        return false;
-    return launch_gemv_class<false>(ctx, tokens, nullptr, nullptr, nullptr, j1, blocks_of(j1.rows),
-                                    j1.cols, blocks_of(j1.rows), stream, error);
+    if (!launch_inline_job<true>(ctx, j0, stream, error)) return false;
+    return launch_inline_job<false>(ctx, j1, stream, error);
 }
 
 bool launch_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float eps,
@@ -751,12 +709,6 @@ bool launch_dequant_probe(FFContext *ctx, const uint8_t *w, const uint16_t *s, c
 
 }  // namespace ff
 
-namespace ff {
-struct GemmJobPair {
-    GemvJob first{}, second{};
-};
-}  // namespace ff
-
 // ---- shared FFN without any allocation -----------------------------------------------------
 
 // Scratch for ff_shared_ffn_noalloc: the GeGLU activations between the gate/up kernel and the
@@ -764,6 +716,7 @@ struct GemmJobPair {
 // library image, so every GPU that loads the library holds it until the process exits.
 constexpr uint32_t kNoAllocMaxRows = 16;
 constexpr uint32_t kNoAllocMaxIntermediate = 4096;
+constexpr uint32_t kNoAllocMaxWidth = 16384;
 static __device__ __align__(256) uint16_t g_noAllocActs[kNoAllocMaxRows * kNoAllocMaxIntermediate];
 
 extern "C" bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjection *up,
@@ -782,6 +735,9 @@ extern "C" bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjecti
         return fail(error, "intermediate width " + std::to_string(f) +
                                " exceeds the static scratch's maximum of " +
                                std::to_string(kNoAllocMaxIntermediate));
+    if (d > kNoAllocMaxWidth)
+        return fail(error, "model width " + std::to_string(d) + " exceeds the maximum of " +
+                               std::to_string(kNoAllocMaxWidth) + " (one input row must fit in shared memory)");
     if (up->rows != f || up->cols != d || down->rows != d || down->cols != f)
         return fail(error, "SharedExpert dimension mismatch: gate=(" + std::to_string(gate->rows) + "," +
                                std::to_string(gate->cols) + ") up=(" + std::to_string(up->rows) + "," +
@@ -790,10 +746,18 @@ extern "C" bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjecti
     if (d % kGroup || f % kGroup || d == 0 || f == 0)
         return fail(error, "widths must be non-zero multiples of the group size 64");
     if (xStride < d || yStride < d || xStride % 2) return fail(error, "row stride is too small or odd");
+    if ((reinterpret_cast<uintptr_t>(x) & 3u) || (reinterpret_cast<uintptr_t>(y) & 1u))
+        return fail(error, "input rows must be 4-byte aligned and output rows 2-byte aligned");
     const FFProjection *ps[3] = {gate, up, down};
     for (const FFProjection *p : ps)
-        if (!p->weights || !p->scales || !p->biases || (reinterpret_cast<uintptr_t>(p->weights) & 15u))
-            return fail(error, "projection pointers must be non-null and the weights 16-byte aligned");
+        if (!p->weights || !p->scales || !p->biases || (reinterpret_cast<uintptr_t>(p->weights) & 15u) ||
+            (reinterpret_cast<uintptr_t>(p->scales) & 1u) || (reinterpret_cast<uintptr_t>(p->biases) & 1u))
+            return fail(error, "projection pointers must be non-null, the weights 16-byte aligned, scales and "
+                               "biases 2-byte aligned");
+    // both kernels' staging must fit before anything is enqueued (wide matrices run as passes of
+    // fewer rows; kNoAllocMaxWidth and kNoAllocMaxIntermediate guarantee that one row always fits)
+    if (gemv_pass_rows(rows, d) == 0 || gemv_pass_rows(rows, f) == 0)
+        return fail(error, "one input row does not fit in shared memory");
 
     // Per-device set-up, done by the first call on each device with that device current: the
     // array's name is only a host-side handle, so its device address is looked up here.
@@ -801,19 +765,24 @@ extern "C" bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjecti
         uint16_t *scratch = nullptr;
         int smCount = 0;
     };
-    static DeviceSetup setups[64];
+    static DeviceSetup setups[kMaxDevices];
+    static std::mutex setupLock;
     int device = 0;
     FF_CUDA_OK(cudaGetDevice(&device), error);
-    if (device < 0 || device >= 64) return fail(error, "device ordinal out of range");
-    DeviceSetup &setup = setups[device];
-    if (!setup.scratch) {
-        void *ptr = nullptr;
-        FF_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noAllocActs), error);
-        int sms = 0;
-        FF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), error);
-        if (!ptr || sms <= 0) return fail(error, "could not set up the static scratch on this device");
-        setup.smCount = sms;
-        setup.scratch = static_cast<uint16_t *>(ptr);
+    if (device < 0 || device >= kMaxDevices) return fail(error, "device ordinal out of range");
+    DeviceSetup setup;
+    {
+        std::lock_guard<std::mutex> guard(setupLock);
+        if (!setups[device].scratch) {
+            void *ptr = nullptr;
+            FF_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noAllocActs), error);
+            int sms = 0;
+            FF_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device), error);
+            if (!ptr || sms <= 0) return fail(error, "could not set up the static scratch on this device");
+            setups[device].smCount = sms;
+            setups[device].scratch = static_cast<uint16_t *>(ptr);
+        }
+        setup = setups[device];
     }
 
     FFContext local;  // launch bookkeeping only: owns nothing on the device
@@ -821,8 +790,7 @@ extern "C" bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjecti
     local.smCount = setup.smCount;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    GemmJobPair jobs;
-    GemvJob &j0 = jobs.first, &j1 = jobs.second;
+    GemvJob j0{}, j1{};
     j0.w0 = static_cast<const uint8_t *>(gate->weights);
     j0.s0 = static_cast<const uint16_t *>(gate->scales);
     j0.b0 = static_cast<const uint16_t *>(gate->biases);
@@ -849,10 +817,7 @@ extern "C" bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjecti
     j1.n = rows;
     for (uint32_t i = 0; i < (uint32_t)kMaxGemvRows; ++i)
         j0.inRow[i] = j0.outRow[i] = j1.inRow[i] = j1.outRow[i] = i < rows ? i : 0u;
-    if (!launch_gemv_class<true>(&local, rows, nullptr, nullptr, nullptr, j0, blocks_of(j0.rows),
-                                 j0.cols, blocks_of(j0.rows), s, error))
-        return false;
-    return launch_gemv_class<false>(&local, rows, nullptr, nullptr, nullptr, j1, blocks_of(j1.rows),
-                                    j1.cols, blocks_of(j1.rows), s, error);
+    if (!launch_inline_job<true>(&local, j0, s, error)) return false;
+    return launch_inline_job<false>(&local, j1, s, error);
 }
 

@@ -82,6 +82,9 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
 __device__ __forceinline__ float pair_sum(uint64_t v) {
     float lo, hi;
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
@@ -265,6 +268,71 @@ __device__ __forceinline__ void row_dot(const uint8_t *w0, const uint16_t *s0, c
             a0[t] += __shfl_xor_sync(0xFFFFFFFFu, a0[t], offset);
             if (DUAL) a1[t] += __shfl_xor_sync(0xFFFFFFFFu, a1[t], offset);
         }
+    }
+}
+
+// Warp-wide top-K over E <= 256 logits held four-plus per lane: K rounds of argmax (higher score,
+// then lower expert id), softmax over the selected scores, times the per-expert gain.  Selection
+// rule and softmax: Metal/MoE/moe.metal:186-237,269-319.
+// sharedIds: optional copy of the ids in shared memory.
+__device__ inline void warp_topk(const float *logits, int E, int K, const uint16_t *gain, uint32_t *ids,
+                          uint16_t *weights, uint32_t *sharedIds = nullptr) {
+    const int lane = threadIdx.x & 31;
+    float v[8];
+    uint32_t live = 0;  // bit j: candidate j of this lane is still in the race (a register, not an indexed array)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int e = j * 32 + lane;
+        v[j] = e < E ? logits[e] : -INFINITY;
+        if (e < E && v[j] > -INFINITY) live |= 1u << j;
+    }
+    float topScore[8];
+    uint32_t topIdx[8];
+    for (int r = 0; r < 8; ++r) {
+        float best = -INFINITY;
+        uint32_t bestE = 0xFFFFFFFFu;
+        if (r < K) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t e = (uint32_t)(j * 32 + lane);
+                if (((live >> j) & 1u) && (v[j] > best || (v[j] == best && e < bestE))) {
+                    best = v[j];
+                    bestE = e;
+                }
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset >= 1; offset >>= 1) {
+            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, offset);
+            const uint32_t oe = __shfl_xor_sync(0xFFFFFFFFu, bestE, offset);
+            if (oe != 0xFFFFFFFFu && (bestE == 0xFFFFFFFFu || ob > best || (ob == best && oe < bestE))) {
+                best = ob;
+                bestE = oe;
+            }
+        }
+        if (bestE != 0xFFFFFFFFu && (bestE & 31u) == (uint32_t)lane) live &= ~(1u << (bestE >> 5));
+        topIdx[r] = bestE == 0xFFFFFFFFu ? 0u : bestE;
+        topScore[r] = bestE == 0xFFFFFFFFu ? -INFINITY : best;
+    }
+    // softmax over the chosen scores: lane r holds route r; exponentials in parallel, the sum in
+    // rank order (the same additions as a serial loop)
+    float myScore = -INFINITY;
+    uint32_t myIdx = 0;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+        if (lane == r) {
+            myScore = topScore[r];
+            myIdx = topIdx[r];
+        }
+    const float ex = lane < K ? expf(myScore - topScore[0]) : 0.0f;
+    float sum = 0.0f;
+    for (int r = 0; r < K; ++r) sum += __shfl_sync(0xFFFFFFFFu, ex, r);
+    if (lane < K) {
+        float w = ex / sum;
+        if (gain) w = w * bf2f(gain[myIdx]);
+        ids[lane] = myIdx;
+        weights[lane] = f2bf(w);
+        if (sharedIds) sharedIds[lane] = myIdx;
     }
 }
 

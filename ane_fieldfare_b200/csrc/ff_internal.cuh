@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -27,6 +28,47 @@ bool fail(const char **error, const std::string &message);
         if (ff_status_ != cudaSuccess)                                                       \
             return ff::fail(error, std::string(#call) + ": " + cudaGetErrorString(ff_status_)); \
     } while (0)
+
+// Per-kernel memo of "dynamic shared-memory limit raised on this device" and of the occupancy at
+// the last requested size.  The library's entry points may be called from one host thread per GPU
+// (and context-free entry points from any thread), so the memo is guarded by a mutex.
+constexpr int kMaxDevices = 64;
+class KernelSmemMemo {
+public:
+    // Makes `kernel` launchable with `smem` bytes of dynamic shared memory on `device` and returns
+    // the resident CTAs per SM at (threads, smem) in *perSm (when asked for).
+    template <typename Kernel>
+    bool prepare(Kernel kernel, int device, size_t smem, int threads, int *perSm, const char **error) {
+        if (device < 0 || device >= kMaxDevices) return fail(error, "device ordinal out of range");
+        std::lock_guard<std::mutex> guard(lock_);
+        Entry &e = entries_[device];
+        if (e.limit < smem || !e.touched) {
+            FF_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), error);
+            e.limit = smem;
+            e.touched = true;
+        }
+        if (perSm) {
+            if (e.occSmem != smem || e.occThreads != threads) {
+                int n = 0;
+                FF_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem), error);
+                e.occ = n;
+                e.occSmem = smem;
+                e.occThreads = threads;
+            }
+            *perSm = e.occ;
+        }
+        return true;
+    }
+
+private:
+    struct Entry {
+        size_t limit = 0, occSmem = 0;
+        int occ = 0, occThreads = -1;
+        bool touched = false;
+    };
+    std::mutex lock_;
+    Entry entries_[kMaxDevices];
+};
 
 // ---- work descriptions the kernels read ----------------------------------------------------
 

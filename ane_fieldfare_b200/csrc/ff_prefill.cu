@@ -30,39 +30,12 @@
 #include <algorithm>
 #include <cstring>
 
+#include "ff_gemv_device.cuh"
 #include "ff_internal.cuh"
 
 namespace ff {
 
 // ---- small device helpers --------------------------------------------------------------------
-
-__device__ __forceinline__ float pf_bf2f(uint16_t b) { return __uint_as_float((uint32_t)b << 16); }
-__device__ __forceinline__ uint16_t pf_f2bf(float f) {
-    uint32_t u = __float_as_uint(f);
-    u += 0x7FFFu + ((u >> 16) & 1u);
-    return (uint16_t)(u >> 16);
-}
-__device__ __forceinline__ float pf_gelu_tanh(float x) {
-    const float x3 = x * x * x;
-    float inner = 0.7978845608028654f * (x + 0.044715f * x3);
-    inner = fminf(fmaxf(inner, -20.0f), 20.0f);
-    return 0.5f * x * (1.0f + tanhf(inner));
-}
-
-// Packed fp32 pairs for fma.rn.f32x2 (low half = first value).
-__device__ __forceinline__ uint64_t pf_pack2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ uint64_t pf_fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ void pf_unpack2(uint64_t v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -75,62 +48,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 // [256 i + 8 l, +8), butterfly 16..1, then the logit bias), so logits and indices are bitwise
 // those of the single-row kernel.  Then the warp-wide top-K.
 constexpr int kRouterWarps = 4;
-
-__device__ void pf_warp_topk(const float *logits, int E, int K, const uint16_t *gain, uint32_t *ids,
-                             uint16_t *weights) {
-    const int lane = threadIdx.x & 31;
-    float v[8];
-    bool live[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int e = j * 32 + lane;
-        v[j] = e < E ? logits[e] : -INFINITY;
-        live[j] = e < E && v[j] > -INFINITY;
-    }
-    float topScore[8];
-    uint32_t topIdx[8];
-    for (int r = 0; r < 8; ++r) {
-        float best = -INFINITY;
-        uint32_t bestE = 0xFFFFFFFFu;
-        if (r < K) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t e = (uint32_t)(j * 32 + lane);
-                if (live[j] && (v[j] > best || (v[j] == best && e < bestE))) {
-                    best = v[j];
-                    bestE = e;
-                }
-            }
-        }
-#pragma unroll
-        for (int offset = 16; offset >= 1; offset >>= 1) {
-            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, offset);
-            const uint32_t oe = __shfl_xor_sync(0xFFFFFFFFu, bestE, offset);
-            if (oe != 0xFFFFFFFFu && (bestE == 0xFFFFFFFFu || ob > best || (ob == best && oe < bestE))) {
-                best = ob;
-                bestE = oe;
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (bestE != 0xFFFFFFFFu && bestE == (uint32_t)(j * 32 + lane)) live[j] = false;
-        topIdx[r] = bestE == 0xFFFFFFFFu ? 0u : bestE;
-        topScore[r] = bestE == 0xFFFFFFFFu ? -INFINITY : best;
-    }
-    if (lane == 0) {
-        float ex[8], sum = 0.0f;
-        for (int r = 0; r < K; ++r) {
-            ex[r] = expf(topScore[r] - topScore[0]);
-            sum += ex[r];
-        }
-        for (int r = 0; r < K; ++r) {
-            float w = ex[r] / sum;
-            if (gain) w = w * pf_bf2f(gain[topIdx[r]]);
-            ids[r] = topIdx[r];
-            weights[r] = pf_f2bf(w);
-        }
-    }
-}
 
 // Each warp owns kRouterTokens tokens and walks the experts eight at a time with a register tile
 // of kRouterTokens x 8 running sums, so a router row (read from the CTA's slice buffer) feeds 4 tokens and an
@@ -240,8 +157,8 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
                         b0 = b0 * s0;
                         b1 = b1 * s1;
                     }
-                    xv[tp][2 * k] = pf_pack2(a0, b0);
-                    xv[tp][2 * k + 1] = pf_pack2(a1, b1);
+                    xv[tp][2 * k] = pack2(a0, b0);
+                    xv[tp][2 * k + 1] = pack2(a1, b1);
                 }
             }
 #pragma unroll
@@ -252,11 +169,11 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const float w0 = __uint_as_float(ww[k] << 16), w1 = __uint_as_float(ww[k] & 0xFFFF0000u);
-                    const uint64_t w00 = pf_pack2(w0, w0), w11 = pf_pack2(w1, w1);
+                    const uint64_t w00 = pack2(w0, w0), w11 = pack2(w1, w1);
 #pragma unroll
                     for (int tp = 0; tp < kRouterTokens / 2; ++tp) {
-                        acc[tp][ee] = pf_fma2(w00, xv[tp][2 * k], acc[tp][ee]);
-                        acc[tp][ee] = pf_fma2(w11, xv[tp][2 * k + 1], acc[tp][ee]);
+                        acc[tp][ee] = fma2(w00, xv[tp][2 * k], acc[tp][ee]);
+                        acc[tp][ee] = fma2(w11, xv[tp][2 * k + 1], acc[tp][ee]);
                     }
                 }
             }
@@ -266,7 +183,7 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
 #pragma unroll
             for (int ee = 0; ee < kRouterExperts; ++ee) {
                 float v0, v1;
-                pf_unpack2(acc[tp][ee], v0, v1);
+                unpack2(acc[tp][ee], v0, v1);
 #pragma unroll
                 for (int offset = 16; offset >= 1; offset >>= 1) {
                     v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, offset);
@@ -288,7 +205,7 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
         const int t = t0 + tt;
         if (logitsOut)
             for (int e = lane; e < E; e += 32) logitsOut[(size_t)t * E + e] = lg[tt * kMaxExperts + e];
-        pf_warp_topk(lg + tt * kMaxExperts, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
+        warp_topk(lg + tt * kMaxExperts, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
     }
 }
 
@@ -300,13 +217,8 @@ bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *
                         (size_t)kRouterWarps * ((size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4);
     if (smem > 225 * 1024) return fail(error, "model width too large for the router's shared memory");
     if (D % 8) return fail(error, "hidden size must be a multiple of 8");
-    static size_t configured[8] = {0};
-    if (configured[ctx->device & 7] != smem) {
-        FF_CUDA_OK(cudaFuncSetAttribute(k_router_rows, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem),
-                   error);
-        configured[ctx->device & 7] = smem;
-    }
+    static KernelSmemMemo memo;
+    if (!memo.prepare(k_router_rows, ctx->device, smem, kRouterWarps * 32, nullptr, error)) return false;
     const uint32_t perCta = kRouterWarps * kRouterTokens;
     {
         LaunchScope scope(ctx, stream, "router_rows");
@@ -920,15 +832,15 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                             float g = __uint_as_float(gr[blk * 8 + i]);
                             float uu = __uint_as_float(ur[blk * 8 + i]);
                             if (args.roundGateUp) {
-                                g = pf_bf2f(pf_f2bf(g));
-                                uu = pf_bf2f(pf_f2bf(uu));
+                                g = bf2f(f2bf(g));
+                                uu = bf2f(f2bf(uu));
                             }
-                            a[i] = pf_gelu_tanh(g) * uu;
+                            a[i] = gelu_tanh(g) * uu;
                         }
-                        packed[blk * 4 + 0] = (uint32_t)pf_f2bf(a[0]) | ((uint32_t)pf_f2bf(a[4]) << 16);
-                        packed[blk * 4 + 1] = (uint32_t)pf_f2bf(a[1]) | ((uint32_t)pf_f2bf(a[5]) << 16);
-                        packed[blk * 4 + 2] = (uint32_t)pf_f2bf(a[2]) | ((uint32_t)pf_f2bf(a[6]) << 16);
-                        packed[blk * 4 + 3] = (uint32_t)pf_f2bf(a[3]) | ((uint32_t)pf_f2bf(a[7]) << 16);
+                        packed[blk * 4 + 0] = (uint32_t)f2bf(a[0]) | ((uint32_t)f2bf(a[4]) << 16);
+                        packed[blk * 4 + 1] = (uint32_t)f2bf(a[1]) | ((uint32_t)f2bf(a[5]) << 16);
+                        packed[blk * 4 + 2] = (uint32_t)f2bf(a[2]) | ((uint32_t)f2bf(a[6]) << 16);
+                        packed[blk * 4 + 3] = (uint32_t)f2bf(a[3]) | ((uint32_t)f2bf(a[7]) << 16);
                     }
                     if (rowLive && nt * 128 + (uint32_t)c0 < args.N) {
                         uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
@@ -957,8 +869,8 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
                             uint32_t o[4];
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
-                                o[i] = (uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
-                                       ((uint32_t)pf_f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
+                                o[i] = (uint32_t)f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
+                                       ((uint32_t)f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
                             dst[q] = make_uint4(o[0], o[1], o[2], o[3]);
                         }
                     }
@@ -999,16 +911,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn encode_tiled(const char **error) {
-    static EncodeTiledFn fn = nullptr;
-    if (fn) return fn;
-    void *sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    cudaError_t st = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
-    if (st != cudaSuccess || q != cudaDriverEntryPointSuccess || !sym) {
-        fail(error, "cuTensorMapEncodeTiled is not available from the driver");
-        return nullptr;
-    }
-    fn = reinterpret_cast<EncodeTiledFn>(sym);
+    // looked up once (thread-safe initialisation of a function-local static)
+    static const EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t st = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+        if (st != cudaSuccess || q != cudaDriverEntryPointSuccess) sym = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    if (!fn) fail(error, "cuTensorMapEncodeTiled is not available from the driver");
     return fn;
 }
 
@@ -1103,12 +1014,9 @@ static bool launch_gemm(FFContext *ctx, const CUtensorMap &mapA, const CUtensorM
     auto kernel = k_grouped_int4_gemm<MODE>;
     const size_t smem = gemm_smem_bytes(args.K);
     if (smem > 226 * 1024) return fail(error, "contraction length too large for the GEMM's shared memory");
-    static size_t configured[8] = {0};
-    if (configured[ctx->device & 7] != smem) {
-        FF_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                   error);
-        configured[ctx->device & 7] = smem;
-    }
+    // the routed (K = f) and shared (K = sharedF) GEMMs alternate: the memo keeps the larger limit
+    static KernelSmemMemo memo;
+    if (!memo.prepare(kernel, ctx->device, smem, kGemmThreads, nullptr, error)) return false;
     const uint32_t grid = std::max(1u, std::min<uint32_t>((uint32_t)ctx->smCount, maxUnits));
     {
         LaunchScope scope(ctx, stream, MODE == kModeGateUp ? "int4_gemm_gate_up_act" : "int4_gemm_down");

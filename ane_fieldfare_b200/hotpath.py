@@ -180,6 +180,21 @@ class HotpathContext:
              _stream(stream))
         return y
 
+    def moeStack(self, firstLayer: int, layerCount: int, x: torch.Tensor, eps: float = 1e-6,
+                 y: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None,
+                 stream=None) -> torch.Tensor:
+        """x <- moeLayer(l, rmsnorm(x)) for `layerCount` consecutive layers (benchmark configuration
+        4's stack); `ids` int32 [layerCount, tokens, K] receives every layer's routes."""
+        tokens = x.shape[0]
+        if y is None:
+            y = torch.empty((tokens, self.d), dtype=torch.bfloat16, device=x.device)
+        call("ff_moe_stack", self.handle, firstLayer, layerCount, _ptr(x), tokens, eps, _ptr(y),
+             _ptr(ids), _stream(stream))
+        return y
+
+    def resetDeviceError(self):
+        call("ff_reset_device_error", self.handle)
+
     def moeLayerHost(self, layer: int, hostX: torch.Tensor, hostY: torch.Tensor):
         """Host buffers in, host buffers out (copies inside); blocks until done."""
         if hostX.is_cuda or hostY.is_cuda:

@@ -76,10 +76,15 @@ def balanced_placement(load, world: int) -> Placement:
 
 def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int,
                   placement: Optional[Placement] = None) -> DispatchPlan:
-    """Routes ordered by destination rank, (token, rank) order kept inside a destination."""
+    """Routes ordered by destination rank, (token, rank) order kept inside a destination.  Expert
+    ids past the group's experts raise on the CPU; on a GPU, where looking at them would stall the
+    stream, they are clamped into range instead (the library's own router never produces one)."""
     tokens, k = ids.shape
     flat = ids.reshape(-1).to(torch.int64)
-    if tokens and (int(flat.max()) >= experts_per_rank * world or int(flat.min()) < 0):
+    total = experts_per_rank * world
+    if flat.is_cuda:
+        flat = flat.clamp(0, total - 1)
+    elif tokens and (int(flat.max()) >= total or int(flat.min()) < 0):
         raise ValueError("route expert out of range for this expert-parallel group")
     if placement is None:
         dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
@@ -99,12 +104,54 @@ def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
     return recv
 
 
-def all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group=None) -> torch.Tensor:
-    """Variable-split all-to-all along dim 0; counts are python lists of row counts."""
+def all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group=None, async_op: bool = False):
+    """Variable-split all-to-all along dim 0; counts are python lists of row counts.  Returns the
+    received rows, and with async_op the work handle to wait on before using them."""
     out = torch.empty((int(sum(recv_counts)),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
-    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
-                           input_split_sizes=list(send_counts), group=group)
-    return out
+    work = dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
+                                  input_split_sizes=list(send_counts), group=group, async_op=async_op)
+    return (out, work) if async_op else out
+
+
+class PhaseTimer:
+    """Per-phase device times of ExpertParallelMoE.forward, by CUDA events on the current stream
+    (CPU tensors: no-op).  `totals()` waits for the device and returns {phase: milliseconds}."""
+
+    def __init__(self):
+        self.records = []
+
+    def phase(self, name, tensor):
+        timer = self
+
+        class _Scope:
+            def __enter__(self_inner):
+                self_inner.events = None
+                if tensor.is_cuda:
+                    self_inner.events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                    self_inner.events[0].record()
+
+            def __exit__(self_inner, *exc):
+                if self_inner.events:
+                    self_inner.events[1].record()
+                    timer.records.append((name, *self_inner.events))
+                return False
+
+        return _Scope()
+
+    def totals(self):
+        out = {}
+        if self.records:
+            torch.cuda.synchronize()
+        for name, begin, end in self.records:
+            out[name] = out.get(name, 0.0) + begin.elapsed_time(end)
+        self.records = []
+        return out
+
+
+class _NoTimer:
+    def phase(self, name, tensor):
+        import contextlib
+        return contextlib.nullcontext()
 
 
 class ExpertParallelMoE:
@@ -113,11 +160,15 @@ class ExpertParallelMoE:
     `router_fn(x) -> (ids int32 [T,K], weights [T,K])`, `shared_fn(x) -> [T,D] or None`,
     `experts_fn(rows [R,D], local_ids int32 [R]) -> partial rows [R,D]`,
     `reduce_fn(partials [T*K,D], weights, residual) -> y [T,D]` are supplied by the caller: the CUDA
-    library on GPUs (see `cuda_layer_fns`), plain torch functions in the CPU tests."""
+    library on GPUs (see `cuda_layer_fns`), plain torch functions in the CPU tests.
+
+    `chunks` > 1 cuts the local tokens into that many runs: the dispatch of run i+1 and the combine
+    of run i-1 are in flight (on the collective library's stream) while the experts of run i
+    compute.  The result does not depend on `chunks`."""
 
     def __init__(self, experts: int, top_k: int, router_fn: Callable, shared_fn: Callable,
                  experts_fn: Callable, reduce_fn: Callable, group=None,
-                 placement: Optional[Placement] = None):
+                 placement: Optional[Placement] = None, chunks: int = 1):
         self.group = group
         self.placement = placement
         self.world = dist.get_world_size(group)
@@ -128,23 +179,74 @@ class ExpertParallelMoE:
         self.experts_per_rank = experts // self.world
         self.router_fn, self.shared_fn = router_fn, shared_fn
         self.experts_fn, self.reduce_fn = experts_fn, reduce_fn
+        self.chunks = max(1, int(chunks))
         self.last_recv_rows = 0
+        self.last_expert_counts = None  # routes per (global) expert of the last forward, on request
+        self.count_experts = False
+        self.timer = _NoTimer()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        ids, weights = self.router_fn(x)
-        plan = dispatch_plan(ids, self.experts_per_rank, self.world, self.placement)
-        recv_counts = exchange_counts(plan.send_counts.to(x.device), self.group)
-        send_list = plan.send_counts.tolist()
-        recv_list = recv_counts.tolist()
-        rows = all_to_all_rows(x.index_select(0, plan.token.to(x.device)), send_list, recv_list, self.group)
-        local = all_to_all_rows(plan.local_expert.to(x.device), send_list, recv_list, self.group)
-        self.last_recv_rows = rows.shape[0]
-        residual = self.shared_fn(x)
-        partial_rows = self.experts_fn(rows, local)
-        back = all_to_all_rows(partial_rows, recv_list, send_list, self.group)
-        partials = torch.empty_like(back)
-        partials[plan.order.to(x.device)] = back
-        return self.reduce_fn(partials, weights, residual)
+        T, K, W = x.shape[0], self.top_k, self.world
+        tm = self.timer
+        with tm.phase("router", x):
+            ids, weights = self.router_fn(x)
+        if self.count_experts:
+            self.last_expert_counts = torch.bincount(ids.reshape(-1).to(torch.int64), minlength=self.experts)
+        with tm.phase("plan", x):
+            bounds = [T * c // self.chunks for c in range(self.chunks + 1)]
+            plans = [dispatch_plan(ids[bounds[c]:bounds[c + 1]], self.experts_per_rank, W, self.placement)
+                     for c in range(self.chunks)]
+            send = torch.stack([p.send_counts for p in plans]).to(x.device)        # [chunks, world]
+            # counts of every run to every rank in one exchange: rank r receives column r of every
+            # rank's table; the one host read below is the step's only wait on the device
+            recv = exchange_counts(send.t().contiguous(), self.group).t()            # [chunks, world]
+            both = torch.stack([send, recv]).tolist()
+        send_lists, recv_lists = both
+        self.last_recv_rows = int(sum(sum(r) for r in recv_lists))
+        on_gpu = x.is_cuda
+
+        def dispatch(c):
+            p = plans[c]
+            rows = x[bounds[c]:bounds[c + 1]].index_select(0, p.token.to(x.device))
+            r = all_to_all_rows(rows, send_lists[c], recv_lists[c], self.group, async_op=on_gpu)
+            l = all_to_all_rows(p.local_expert.to(x.device), send_lists[c], recv_lists[c], self.group,
+                                async_op=on_gpu)
+            return r, l
+
+        def ready(pending):
+            if on_gpu:
+                (rows, w0), (local, w1) = pending
+                w0.wait()
+                w1.wait()
+                return rows, local
+            return pending
+
+        partials = torch.empty((T * K,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        with tm.phase("dispatch", x):
+            pending = dispatch(0)
+        residual = None
+        backs = []
+        for c in range(self.chunks):
+            with tm.phase("dispatch", x):
+                rows, local = ready(pending)
+                if c + 1 < self.chunks:
+                    pending = dispatch(c + 1)
+            if c == 0:
+                with tm.phase("shared", x):
+                    residual = self.shared_fn(x)
+            with tm.phase("experts", x):
+                partial_rows = self.experts_fn(rows, local)
+            with tm.phase("combine", x):
+                backs.append(all_to_all_rows(partial_rows, recv_lists[c], send_lists[c], self.group,
+                                             async_op=on_gpu))
+        with tm.phase("combine", x):
+            for c, back in enumerate(backs):
+                if on_gpu:
+                    back, work = back
+                    work.wait()
+                partials[bounds[c] * K + plans[c].order.to(x.device)] = back
+        with tm.phase("reduce", x):
+            return self.reduce_fn(partials, weights, residual)
 
 
 def cuda_layer_fns(home_ctx, expert_ctx, layer: int, expert_layer: Optional[int] = None):

@@ -36,15 +36,28 @@ class SyntheticLayer:
 
 def make_layer(root: int, layer: int, *, experts: int = 128, d: int = 2816, f: int = 704,
                sharedF: int = 2112, topK: int = 8, router_bias: str = "none",
-               router_std: float = 0.02) -> SyntheticLayer:
+               router_std: float = 0.02, down_shift: int = 0) -> SyntheticLayer:
     """router_bias: "none" (decode), "normal" (verify: N(0,1) per expert), "zipf" (prefill:
-    log of a Zipf(1.1) prior in a seeded expert order)."""
+    log of a Zipf(1.1) prior in a seeded expert order).  down_shift = n scales every down
+    projection's scales and biases by 2^-n (exactly: only bf16 exponents change), which scales
+    the layer's outputs by 2^-n; the benchmark configurations use 0."""
     lay = gturbo.expert_layout(d, f)
     blobs = gturbo.synthetic_experts(root, f"layer{layer}.routed", experts, d, f)
     shared_lay = shared_blob = None
     if sharedF:
         shared_lay = gturbo.expert_layout(d, sharedF)
         shared_blob = gturbo.synthetic_experts(root, f"layer{layer}.shared", 1, d, sharedF)[0]
+    if down_shift:
+        def shrink(blob2d, layout):
+            _, s_off, b_off = layout.offsets.as_tuple()[6:9]
+            n = layout.d * layout.f // 64 * 2
+            for off in (s_off, b_off):
+                bits = blob2d[:, off:off + n].view(np.uint16)
+                assert ((bits >> 7) & 0xFF).min() > down_shift  # stays a normal number
+                bits -= np.uint16(down_shift << 7)
+        shrink(blobs, lay)
+        if sharedF:
+            shrink(shared_blob[None, :], shared_lay)
     router = synth.normal_bf16(root, f"layer{layer}.router", (experts, d), router_std)
     if router_bias == "none":
         bias = None

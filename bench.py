@@ -36,11 +36,32 @@ ROUTER_BYTES = E * D * 2                                         # 720 896
 ACT_IO_BYTES = 2 * D * 2                                         # x in, y out
 DECODE_BYTES = K * EXPERT_BYTES + SHARED_BYTES + ROUTER_BYTES + ACT_IO_BYTES  # 37 531 648
 DECODE_FLOPS = 2 * (K * 3 * F * D + 3 * FS * D + E * D)
-KERNELS_PER_DECODE_STEP = 1
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch, from an ncu capture of this
-# kernel on these shapes (bytes)
-NCU_DECODE_TRAFFIC_BYTES = 37_749_760
 ROOT_SEED = 0xF1E1DFA2E
+MIN_TIMED_SECONDS = 0.25  # every leg's timed region runs at least this long
+DECODE_PROFILE = os.path.join("profiles", "decode_fused_config1.md")
+
+
+def profiled_decode_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one decode launch, as recorded in the ncu
+    summary under profiles/ — only when that summary was taken from the kernel sources that are
+    being run (it records their SHA-256); otherwise None: a stale capture is not reported."""
+    import hashlib
+    import re
+    path = os.path.join(ROOT, DECODE_PROFILE)
+    if not os.path.exists(path):
+        return None, "no profile"
+    text = open(path).read()
+    h = hashlib.sha256()
+    for name in ("ff_decode.cu", "ff_mma_device.cuh"):
+        with open(os.path.join(ROOT, "ane_fieldfare_b200", "csrc", name), "rb") as fh:
+            h.update(fh.read())
+    digest = re.search(r"kernel sources sha256: ([0-9a-f]{64})", text)
+    traffic = re.search(r"traffic bytes per launch: (\d+)", text)
+    if not digest or not traffic:
+        return None, "profile records no source hash"
+    if digest.group(1) != h.hexdigest():
+        return None, f"{DECODE_PROFILE} was captured from other kernel sources"
+    return int(traffic.group(1)), DECODE_PROFILE
 
 
 PREFILL_TOKENS = 4096
@@ -79,7 +100,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
             deadline = time.time() + 3.0
@@ -178,18 +199,41 @@ def time_graph(torch, stream, graph, replays):
     return begin.elapsed_time(end)
 
 
+def time_replays(torch, stream, launch, replays):
+    """Milliseconds of each of `replays` back-to-back calls of launch(), from CUDA events recorded
+    between them on the launching stream (no host synchronisation inside the region)."""
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(replays + 1)]
+    with torch.cuda.stream(stream):
+        marks[0].record(stream)
+        for i in range(replays):
+            launch()
+            marks[i + 1].record(stream)
+        stream.synchronize()
+    return [marks[i].elapsed_time(marks[i + 1]) for i in range(replays)]
+
+
+def spread(per_replay_ms, steps_per_replay):
+    a = np.asarray(per_replay_ms, dtype=np.float64) / steps_per_replay
+    return {"replays": int(a.size), "steps_per_replay": int(steps_per_replay), "total_ms": float(a.sum() * steps_per_replay),
+            "median_us_per_step": float(np.median(a) * 1e3), "min_us_per_step": float(a.min() * 1e3),
+            "max_us_per_step": float(a.max() * 1e3)}
+
+
 def capture_steps(torch, ctx, stream, step, group):
     """One CUDA graph holding `group` consecutive steps (a few uncaptured steps run first so that
-    every kernel is configured before the capture)."""
+    every kernel is configured before the capture).  Returns the graph and the number of kernels
+    the library enqueued per step while capturing."""
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
         for i in range(3):
             step(i)
         stream.synchronize()
+        before = ctx.info().kernelLaunches
         with torch.cuda.graph(graph, stream=stream):
             for i in range(group):
                 step(i)
-    return graph
+        launched = ctx.info().kernelLaunches - before
+    return graph, launched / group
 
 
 def traced_kernels(ctx, step, group):
@@ -207,94 +251,215 @@ STACK_LAYERS = 30
 STACK_TOKENS = 32768
 
 
+def stack_flops(layers):
+    return layers * STACK_TOKENS * (2 * (K * 3 * F * D + 3 * FS * D + E * D))
+
+
+def measure_stack_single(torch, hotpath, workload, host_layers, local_rank, device, args):
+    """Configuration 4 on one GPU: all experts of all layers resident in one context, the stack run
+    by the library's own ff_moe_stack (RMSNorm + block per layer) — the time the expert-parallel
+    runs are compared with."""
+    from ane_fieldfare_b200 import synth
+    layers = args.stack_layers
+    ctx = hotpath.HotpathContext(layers=layers, experts=E, d=D, f=F, sharedF=FS, topK=K,
+                                 maxTokens=STACK_TOKENS, device=local_rank)
+    for slot in range(layers):
+        L = host_layers[slot % len(host_layers)]
+        ctx.loadLayer(slot, L.blobs, L.layout.stride, L.layout.offsets)
+        ctx.loadShared(slot, *L.shared_projections())
+        ctx.loadRouter(slot, L.routerW,
+                       logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{slot % len(host_layers)}"))
+    x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED, "stack.x", STACK_TOKENS, D), device)
+    y = torch.empty_like(x0)
+    for _ in range(2):
+        ctx.moeStack(0, layers, x0, 1e-6, y)
+    torch.cuda.synchronize()
+    steps = 3
+    per = time_replays(torch, torch.cuda.current_stream(), lambda: ctx.moeStack(0, layers, x0, 1e-6, y), steps)
+    ms = float(np.median(per))
+    ctx.setTracing(True)
+    ctx.moeStack(0, layers, x0, 1e-6, y)
+    trace = ctx.trace()
+    ctx.setTracing(False)
+    finite = bool(torch.isfinite(y.float()).all().item())
+    err = ctx.info().deviceErrorFlag
+    resident = ctx.info().weightBytesResident
+    ctx.close()
+    peak = measured_bf16_peak()
+    tf = stack_flops(layers) / (ms * 1e-3) / 1e12
+    return {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens", "gpus": 1,
+            "path": "ff_moe_stack on one context (no expert parallelism, no collective)",
+            "tokens_per_s": STACK_TOKENS / (ms * 1e-3), "ms_per_stack": ms, "steps": steps,
+            "timed_region": spread(per, 1), "tflops": tf,
+            "frac_of_measured_bf16_sustained": tf / peak["tflops"], "frac_of_measured_bf16_burst": tf / peak["burst_tflops"],
+            "weight_bytes_resident": int(resident), "output_finite": finite, "device_error_flag": int(err),
+            "kernel_ms_per_stack": {name: round(t, 3) for name, (n, t) in sorted(trace.items())}}
+
+
 def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank, world, device, args):
     """Benchmark configuration 4: a 30-layer stack of MoE blocks (RMSNorm between layers, no
-    attention), 32768 prefill tokens, experts sharded over the ranks with an NCCL all-to-all
-    dispatch and combine per layer.  All 30 layer slots are resident (13.2 GB over the box); their
-    bytes repeat a few distinct seeded layers, which does not change the work."""
+    attention), 32768 prefill tokens.  One GPU: the library's ff_moe_stack.  Several GPUs: experts
+    sharded over the ranks with an NCCL all-to-all dispatch and combine per layer.  All 30 layer
+    slots are resident (13.2 GB over the box); their bytes repeat a few distinct seeded layers,
+    which does not change the work."""
     from ane_fieldfare_b200 import parallel, synth
-    if not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29533")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    if world == 1:
+        return measure_stack_single(torch, hotpath, workload, host_layers, local_rank, device, args)
     layers = args.stack_layers
     tokens_local = STACK_TOKENS // world
     epr = E // world
-    capacity = min(STACK_TOKENS * K, 3 * tokens_local * K)
+    capacity = min(STACK_TOKENS * K, 4 * tokens_local * K)
     home = hotpath.HotpathContext(layers=len(host_layers), experts=E, d=D, f=F, sharedF=FS, topK=K,
                                   maxTokens=tokens_local, device=local_rank)
     local = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=1,
                                    maxTokens=capacity, device=local_rank)
-    placements = []
     for i, L in enumerate(host_layers):
-        prior = synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}")
         home.loadShared(i, *L.shared_projections())
-        home.loadRouter(i, L.routerW, logitBias=prior)
-        # experts go to ranks so that the expected routed load is balanced (the blob layout is
-        # untouched): the load is estimated on the host from the router itself, top-8 over seeded
-        # unit-RMS rows, which is what the inter-layer RMSNorm feeds every block
-        rows = synth.normal(synth.seedtree_key(ROOT_SEED, f"stack.calib.{i}"), 1024 * D).reshape(1024, D)
-        rows /= np.sqrt(np.mean(rows * rows, axis=1, keepdims=True))
-        logits = rows.astype(np.float32) @ synth.bf16_to_float(L.routerW).T + prior[None, :]
-        chosen = np.argpartition(-logits, K - 1, axis=1)[:, :K]
-        load = np.bincount(chosen.reshape(-1), minlength=E).astype(np.float64) + 0.5
-        placements.append(parallel.balanced_placement(load, world))
-    for slot in range(layers):
-        L = host_layers[slot % len(host_layers)]
-        mine = placements[slot % len(host_layers)].experts_of(rank)
-        local.loadLayer(slot, np.ascontiguousarray(L.blobs[mine]), L.layout.stride, L.layout.offsets,
-                        expertCount=epr)
-    blocks = []
-    for slot in range(layers):
-        # the home context is indexed by the distinct layer, the expert context by the stack's slot
-        fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
-        blocks.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot % len(host_layers)]))
+        home.loadRouter(i, L.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}"))
+
+    def load_experts(placements):
+        for slot in range(layers):
+            L = host_layers[slot % len(host_layers)]
+            mine = placements[slot].experts_of(rank)
+            local.loadLayer(slot, np.ascontiguousarray(L.blobs[mine]), L.layout.stride, L.layout.offsets,
+                            expertCount=epr)
+
+    def make_blocks(placements, chunks):
+        out = []
+        for slot in range(layers):
+            # the home context is indexed by the distinct layer, the expert context by the stack's slot
+            fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
+            out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks))
+        return out
+
     x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
 
-    def run_stack():
+    def run_stack(blocks):
         x = x0
         for block in blocks:
             x = block.forward(home.rmsnorm(x, None, 1e-6))
         return x
 
+    # Pass 1, contiguous placement: the stack's outputs do not depend on where an expert lives, so
+    # this pass measures how many routes every expert of every layer receives (summed over the
+    # ranks).  Experts are then placed so that every rank receives about the same number of rows
+    # (the blob layout is untouched: a rank loads the blobs of its experts).
+    contiguous = [parallel.contiguous_placement(E, world)] * layers
+    load_experts(contiguous)
+    blocks = make_blocks(contiguous, 1)
+    for block in blocks:
+        block.count_experts = True
+    run_stack(blocks)
+    counts = torch.stack([block.last_expert_counts for block in blocks]).to(torch.float64)
+    dist.all_reduce(counts)
+    placements = [parallel.balanced_placement((counts[slot] + 0.5).tolist(), world) for slot in range(layers)]
+    load_experts(placements)
+    blocks = make_blocks(placements, args.ep_chunks)
+
+    # the first layer's output for the first rows against ff_moe_layer on one context that holds all
+    # experts of that layer: the same bits
+    check_rows = min(256, tokens_local)
+    full = hotpath.HotpathContext(layers=1, experts=E, d=D, f=F, sharedF=FS, topK=K, maxTokens=tokens_local,
+                                  device=local_rank)
+    L0 = host_layers[0]
+    workload.load_layer(full, 0, L0)
+    full.loadRouter(0, L0.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, "stack.zipf.0"))
+    normed = home.rmsnorm(x0, None, 1e-6)
+    y_ep = blocks[0].forward(normed)
+    y_one = full.moeLayer(0, normed)
+    torch.cuda.synchronize()
+    same = torch.tensor([1.0 if torch.equal(y_ep[:check_rows], y_one[:check_rows]) else 0.0],
+                        dtype=torch.float64, device=device)
+    full.close()
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+
     for _ in range(2):
-        run_stack()
+        run_stack(blocks)
     torch.cuda.synchronize()
     dist.barrier()
     steps = 3
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for _ in range(steps):
-        y = run_stack()
-    end.record()
-    torch.cuda.synchronize()
-    ms = begin.elapsed_time(end) / steps
-    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    per = time_replays(torch, torch.cuda.current_stream(), lambda: run_stack(blocks), steps)
+    t = torch.tensor([float(np.median(per))], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    recv = torch.tensor([float(blocks[-1].last_recv_rows)], dtype=torch.float64, device=device)
+    # one more pass with CUDA events around the phases of every layer
+    timer = parallel.PhaseTimer()
+    for block in blocks:
+        block.timer = timer
+    y = run_stack(blocks)
+    phases = timer.totals()
+    names = sorted(phases)
+    pt = torch.tensor([phases[n] for n in names], dtype=torch.float64, device=device)
+    dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+    recv = torch.tensor([[float(b.last_recv_rows) for b in blocks]], dtype=torch.float64, device=device)
     rows = [torch.zeros_like(recv) for _ in range(world)]
     dist.all_gather(rows, recv)
+    rows = torch.cat(rows).cpu().numpy()  # [world, layers]
     finite = bool(torch.isfinite(y.float()).all().item())
     err = home.info().deviceErrorFlag | local.info().deviceErrorFlag
-    flops = layers * STACK_TOKENS * (2 * (K * 3 * F * D + 3 * FS * D + E * D))
     peak = measured_bf16_peak()
     home.close()
     local.close()
-    tf = flops / (ms * 1e-3) / 1e12
+    tf = stack_flops(layers) / (ms * 1e-3) / 1e12
     return {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens_expert_parallel", "gpus": world,
             "tokens_per_s": STACK_TOKENS / (ms * 1e-3), "ms_per_stack": ms, "steps": steps,
-            "tflops": tf, "frac_of_measured_bf16_per_gpu": tf / (peak["tflops"] * world),
-            "last_layer_rows_received_per_rank": [int(r.item()) for r in rows],
+            "tflops": tf, "frac_of_measured_bf16_sustained_per_gpu": tf / (peak["tflops"] * world),
+            "ep_matches_single_gpu": bool(same.item() == 1.0),
+            "ep_check": f"layer 0, first {check_rows} local rows of every rank, bitwise against ff_moe_layer "
+                        "on one context holding all 128 experts",
+            "phase_ms_per_stack_max_over_ranks": {n: round(float(v), 3) for n, v in zip(names, pt.tolist())},
+            "rows_received_per_rank_by_layer": rows.astype(np.int64).T.tolist(),
+            "rows_received_max_over_mean": float((rows.max(axis=0) / rows.mean(axis=0)).mean()),
+            "chunks_per_layer": args.ep_chunks,
             "output_finite": finite, "device_error_flag": int(err),
-            "collective": "NCCL all_to_all_single (dispatch + combine per layer)",
-            "placement": "experts assigned to ranks by greedy balancing of a load estimated from the router on seeded rows"}
+            "collective": "NCCL all_to_all_single (dispatch + combine per layer and chunk, asynchronous to the GEMMs)",
+            "placement": "experts assigned to ranks by greedy balancing of the routes each expert of each layer "
+                         "received in a first pass of the same stack"}
+
+
+def oracle_layer_data(O, layer_host, logit_bias):
+    return O.LayerData(experts=layer_host.blobs, stride=layer_host.layout.stride,
+                       off=layer_host.layout.offsets.as_tuple(), E=E, D=D, F=F, K=K,
+                       shared=layer_host.sharedBlob, shared_off=layer_host.sharedLayout.offsets.as_tuple(),
+                       Fs=FS, router_w=layer_host.routerW, logit_bias=logit_bias)
+
+
+def cpu_other_configs(layer_host, bias_verify, bias_prefill):
+    """The CPU oracle on bounded samples of configurations 0, 2 and 3 (tokens per second each)."""
+    from ane_fieldfare_b200 import workload
+    from oracle import oracle as O
+    O.set_num_threads(os.cpu_count() or 1)
+    out = {}
+
+    def timed(fn, tokens, budget, what):
+        fn()
+        n, t0 = 0, time.perf_counter()
+        while n == 0 or time.perf_counter() - t0 < budget:
+            fn()
+            n += 1
+        dt = time.perf_counter() - t0
+        return {"value": tokens * n / dt, "unit": "tokens/s", "sample": f"{n} x {what}", "seconds": dt}
+
+    x1 = workload.make_tokens(ROOT_SEED, "cfg0.x", 1, D)
+    off = layer_host.layout.offsets.as_tuple()
+    out["config0_single_expert_1token"] = timed(
+        lambda: O.expert_ffn(layer_host.blobs[0], off, D, F, x1), 1, 2.0, "one expert, one token")
+    x16 = workload.make_tokens(ROOT_SEED, "verify.x", 16, D)
+    ld2 = oracle_layer_data(O, layer_host, bias_verify)
+    out["config2_verify_16token_block"] = timed(
+        lambda: O.moe_layer(ld2, x16, O.MODE_PARTIALS), 16, 4.0, "16-token block, one layer")
+    x256 = workload.make_tokens(ROOT_SEED, "prefill.x", 256, D)
+    ld3 = oracle_layer_data(O, layer_host, bias_prefill)
+    out["config3_prefill_zipf"] = timed(
+        lambda: O.moe_layer(ld3, x256, O.MODE_PARTIALS), 256, 6.0,
+        "the first 256 of the 4096 tokens, one layer (tokens/s extrapolates linearly)")
+    return out
 
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from ane_fieldfare_b200 import hotpath, workload
+    from ane_fieldfare_b200 import hotpath, synth, workload
 
     rank, local_rank, world = dist_env()
     if world > 1:
@@ -315,18 +480,19 @@ def run_ours(args):
     host_layer0 = host_layers[0]
     peaks = measured_peaks()
     stream = torch.cuda.Stream(device=device)
+    min_s = 0.0 if args.quick else MIN_TIMED_SECONDS
+
+    def router_bias(kind, slot):
+        if kind == "none":
+            return None
+        if kind == "normal":
+            return synth.normal(synth.seedtree_key(ROOT_SEED, f"bench.bias.{slot}"), E).astype(np.float32)
+        return synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"bench.zipf.{slot}")
 
     def set_router_bias(kind):
-        from ane_fieldfare_b200 import synth
         for slot in range(n_layers):
             router = host_layers[slot].routerW if slot < STACK_DISTINCT_LAYERS else host_layers[slot][0]
-            if kind == "none":
-                bias = None
-            elif kind == "normal":
-                bias = synth.normal(synth.seedtree_key(ROOT_SEED, f"bench.bias.{slot}"), E).astype(np.float32)
-            else:
-                bias = synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"bench.zipf.{slot}")
-            ctx.loadRouter(slot, router, logitBias=bias)
+            ctx.loadRouter(slot, router, logitBias=router_bias(kind, slot))
 
     def sync_max(ms):
         if world > 1:
@@ -334,6 +500,27 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t.item())
         return ms
+
+    def measure_graph(step, group, warm_steps):
+        """Captures `group` consecutive steps as one CUDA graph, replays it until the timed region
+        has run for MIN_TIMED_SECONDS, and returns (median ms of one replay as the max over ranks,
+        spread record, kernels per step, clock record)."""
+        graph, per_step = capture_steps(torch, ctx, stream, step, group)
+        est = time_graph(torch, stream, graph, max(1, (warm_steps + group - 1) // group))
+        est = max(est / max(1, (warm_steps + group - 1) // group), 1e-3)
+        replays = max(3, int(np.ceil(min_s * 1e3 / est)))
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        per_replay = time_replays(torch, stream, graph.replay, replays)
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if rank == 0 else None
+        if world > 1:
+            dist.barrier()
+        return sync_max(float(np.median(per_replay))), spread(per_replay, group), per_step, clocks
 
     line = {}
     # ================= decode: config 1, the headline =================
@@ -347,36 +534,27 @@ def run_ours(args):
         ctx.moeLayer(i % n_layers, xs[i % n_rows], y1)
 
     set_router_bias("none")
-    for i in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
         decode_step(i)
     torch.cuda.synchronize()
-    group = n_layers * 8
-    graph = capture_steps(torch, ctx, stream, decode_step, group)
-    replays = max(1, (args.steps + group - 1) // group)
-    steps = replays * group
-    time_graph(torch, stream, graph, max(1, (args.warmup + group - 1) // group))
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    ms = time_graph(torch, stream, graph, replays)
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
-    ms = sync_max(ms)
-    if world > 1:
-        dist.barrier()
+    steps = max(1, min(args.steps, 8192))  # one CUDA graph holds exactly these steps
+    ms, timing, kernels_per_step, clocks = measure_graph(decode_step, steps, warmup)
     value = world * steps / (ms * 1e-3)
-    kernels = {} if args.quick else traced_kernels(ctx, decode_step, group)
+    kernels = {"decode_fused": {"launches_per_step": kernels_per_step,
+                                "avg_us_in_graph": round(1e3 * ms / steps / max(kernels_per_step, 1), 3)}}
+    if not args.quick:
+        eager = traced_kernels(ctx, decode_step, n_layers * 8)
+        for name, rec in eager.items():
+            kernels.setdefault(name, {})["avg_us_eager_with_launch_gaps"] = rec["avg_us"]
 
     # end to end through the host-buffer entry point
     hx = [torch.from_numpy(tokens_bits[i:i + 1].view(np.int16).copy()).view(torch.bfloat16).pin_memory()
           for i in range(n_rows)]
     hy = torch.zeros((1, D), dtype=torch.bfloat16).pin_memory()
-    e2e_steps = 8 if args.quick else min(steps, 2000)
     for i in range(5):
         ctx.moeLayerHost(i % n_layers, hx[i % n_rows], hy)
+    e2e_steps = 8 if args.quick else max(steps, 6000)
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
@@ -387,9 +565,10 @@ def run_ours(args):
 
     step_s = ms * 1e-3 / steps
     achieved = DECODE_BYTES / step_s / 1e9
+    traffic, traffic_source = profiled_decode_traffic()
     line.update({
         "metric": "int4_moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
-        "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / steps,
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int4 weights, bf16 activations, fp32 accumulate", "data": "synthetic",
         "config": {"workload": "config1_decode_1token_moe_layer", "hidden": D, "experts": E,
@@ -398,15 +577,18 @@ def run_ours(args):
                    "l2_policy": f"weights of {n_layers} layers rotate: "
                                 f"{n_layers * DECODE_BYTES / 1e6:.0f} MB touched > 126 MB L2",
                    "multi_gpu": "replicas only (decode does not shard)",
-                   "launch": f"CUDA graph of {group} steps"},
+                   "launch": f"one CUDA graph of the {steps} steps, replayed; value = steps / median replay"},
+        "timed_region": timing,
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": D * 2,
-                "d2h_bytes_per_step": D * 2, "steps": e2e_steps},
-        "gpu_launches": steps * KERNELS_PER_DECODE_STEP,
+                "d2h_bytes_per_step": D * 2, "steps": e2e_steps, "seconds": e2e_s,
+                "call": "ff_moe_layer_host, pinned host row in, pinned host row out"},
+        "gpu_launches": int(round(steps * kernels_per_step)),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
-                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC_BYTES,
+                     "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": traffic,
+                     "traffic_source": traffic_source,
                      "peak_source": peaks["source"], "frac_of_nominal_8TBs": achieved / 8000.0,
-                     "kernel": "the whole decode step (all kernels of one token through one layer)",
+                     "kernel": "k_decode_fused: the whole decode step is this one launch",
                      "algorithmic_bytes_per_step": DECODE_BYTES},
         "kernels": kernels,
     })
@@ -429,21 +611,30 @@ def run_ours(args):
             torch.cuda.synchronize()
             active.append(ctx.info().lastActiveExperts)
         vgroup = n_layers * 2
-        vgraph = capture_steps(torch, ctx, stream, verify_step, vgroup)
-        vreplays = max(2, args.steps // (8 * vgroup))
-        time_graph(torch, stream, vgraph, 2)
-        vms = time_graph(torch, stream, vgraph, vreplays)
-        vsteps = vreplays * vgroup
+        vms, vtiming, v_per_step, _ = measure_graph(verify_step, vgroup, vgroup)
         mean_active = float(np.mean(active))
         vbytes = mean_active * EXPERT_BYTES + SHARED_BYTES + ROUTER_BYTES + 16 * ACT_IO_BYTES
-        vach = vbytes / (vms * 1e-3 / vsteps) / 1e9
+        vach = vbytes / (vms * 1e-3 / vgroup) / 1e9
+        hvx = [torch.from_numpy(vbits[16 * i:16 * i + 16].view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+               for i in range(n_blocks)]
+        hvy = torch.zeros((16, D), dtype=torch.bfloat16).pin_memory()
+        for i in range(3):
+            ctx.moeLayerHost(i % n_layers, hvx[i % n_blocks], hvy)
+        ve2e = 8 if args.quick else 1500
+        t0 = time.perf_counter()
+        for i in range(ve2e):
+            ctx.moeLayerHost(i % n_layers, hvx[i % n_blocks], hvy)
+        ve2e_s = time.perf_counter() - t0
         line["verify"] = {
-            "workload": "config2_verify_16token_block", "tokens_per_s": 16 * vsteps / (vms * 1e-3),
-            "ms_per_step": vms / vsteps, "steps": vsteps, "active_experts_mean": mean_active,
+            "workload": "config2_verify_16token_block", "tokens_per_s": 16 * vgroup / (vms * 1e-3),
+            "ms_per_step": vms / vgroup, "steps": vgroup, "timed_region": vtiming,
+            "active_experts_mean": mean_active, "gpu_launches_per_step": v_per_step,
+            "e2e": {"value": 16 * ve2e / ve2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 16 * D * 2,
+                    "d2h_bytes_per_step": 16 * D * 2, "steps": ve2e, "seconds": ve2e_s},
             "roofline": {"bound": "hbm", "achieved": vach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": vach / peaks["hbm_gbs"], "frac_of_nominal_8TBs": vach / 8000.0,
                          "algorithmic_bytes_per_step": vbytes},
-            "kernels": traced_kernels(ctx, verify_step, vgroup)}
+            "kernels": {} if args.quick else traced_kernels(ctx, verify_step, vgroup)}
 
     # ================= prefill: config 3, 4096 tokens, Zipf-skewed routing =================
     if "prefill" in want and rank == 0:
@@ -451,32 +642,40 @@ def run_ours(args):
         pbits = workload.make_tokens(ROOT_SEED, "prefill.x", PREFILL_TOKENS, D)
         px = hotpath.bf16_tensor(pbits, device)
         py = torch.zeros((PREFILL_TOKENS, D), dtype=torch.bfloat16, device=device)
+        counter = [0]
 
-        def prefill_step(i):
-            ctx.moeLayer(i % n_layers, px, py)
+        def prefill_step():
+            ctx.moeLayer(counter[0] % n_layers, px, py)
+            counter[0] += 1
 
-        for i in range(3):
-            prefill_step(i)
+        for _ in range(3):
+            prefill_step()
         torch.cuda.synchronize()
         err = ctx.info().deviceErrorFlag
-        psteps = max(8, min(64, args.steps // 64))
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record()
-        for i in range(psteps):
-            prefill_step(i)
-        end.record()
-        torch.cuda.synchronize()
-        pms = begin.elapsed_time(end)
+        est = float(np.median(time_replays(torch, torch.cuda.current_stream(), prefill_step, 3)))
+        psteps = max(8, int(np.ceil(min_s * 1e3 / max(est, 1e-3))))
+        per_step = time_replays(torch, torch.cuda.current_stream(), prefill_step, psteps)
+        pms = float(np.median(per_step))
         flops = PREFILL_TOKENS * (2 * (K * 3 * F * D + 3 * FS * D + E * D))
-        tf = flops / (pms * 1e-3 / psteps) / 1e12
+        tf = flops / (pms * 1e-3) / 1e12
         bf16_peak = measured_bf16_peak()
+        region_s = float(np.sum(per_step)) * 1e-3
+        # a region of under a second runs at burst clocks: the burst cuBLAS figure is its peak
+        use_burst = region_s < 1.0
+        peak_tf = bf16_peak["burst_tflops"] if use_burst else bf16_peak["tflops"]
+        info = ctx.info()
         line["prefill"] = {
-            "workload": "config3_prefill_4096tokens_zipf", "tokens_per_s": PREFILL_TOKENS * psteps / (pms * 1e-3),
-            "ms_per_step": pms / psteps, "steps": psteps, "device_error_flag": err,
-            "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16_peak["tflops"], "unit": "TFLOP/s",
-                         "frac": tf / bf16_peak["tflops"], "peak_source": bf16_peak["source"],
+            "workload": "config3_prefill_4096tokens_zipf", "tokens_per_s": PREFILL_TOKENS / (pms * 1e-3),
+            "ms_per_step": pms, "steps": psteps, "timed_region": spread(per_step, 1), "device_error_flag": err,
+            "active_experts": info.lastActiveExperts,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": tf / peak_tf,
+                         "peak_source": ("measured burst" if use_burst else "measured sustained")
+                         if bf16_peak["source"].startswith("measured") else "fallback",
+                         "frac_of_measured_burst": tf / bf16_peak["burst_tflops"],
+                         "frac_of_measured_sustained": tf / bf16_peak["tflops"],
                          "frac_of_nominal_2250TF": tf / 2250.0, "algorithmic_flops_per_step": flops},
-            "kernels": traced_kernels(ctx, prefill_step, 4)}
+            "kernels": {} if args.quick else traced_kernels(ctx, lambda i: prefill_step(), 4)}
 
     # ================= stack: config 4, 30 layers x 32768 tokens, experts sharded over the ranks ====
     if "stack" in want:
@@ -491,7 +690,9 @@ def run_ours(args):
         cpu_rate, cpu_steps, cpu_threads = cpu_decode_baseline(host_layer0, tokens_bits)
         line["cpu_baseline"] = {"value": cpu_rate, "unit": "tokens/s", "cores": cpu_threads,
                                 "kind": "port",
-                                "sample": f"{cpu_steps} decode steps of the C oracle (OpenMP), one layer"}
+                                "sample": f"{cpu_steps} decode steps of the C oracle (OpenMP), one layer",
+                                "other_configs": cpu_other_configs(host_layer0, router_bias("normal", 0),
+                                                                   router_bias("zipf", 0))}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if ctx is not None:
@@ -510,6 +711,8 @@ def main():
     ap.add_argument("--layers", type=int, default=8, help="resident layers the steps rotate over")
     ap.add_argument("--only", default="", help="comma list of decode,verify,prefill,stack (default all)")
     ap.add_argument("--stack-layers", type=int, default=STACK_LAYERS, help="layers of the config-4 stack")
+    ap.add_argument("--ep-chunks", type=int, default=2,
+                    help="runs the local tokens are cut into per layer under expert parallelism")
     ap.add_argument("--quick", action="store_true",
                     help="skip the end-to-end loop, per-kernel tracing and the CPU baseline (for profiler runs)")
     args = ap.parse_args()

@@ -8,7 +8,8 @@
  * (Sources/ANEFieldfareANECarrier/include/ANEExpertCarrier.h:14-38): an opaque handle, `bool`
  * results, errors returned as strdup'd C strings the caller frees (ff_string_free or free()),
  * an explicit destroy, a plain info struct.  Calls on one context must be serialized by the
- * caller.
+ * caller; different contexts (one per GPU, each driven by its own host thread) and the
+ * context-free entry points may be called concurrently.
  *
  * Operators take DEVICE pointers and a CUDA stream (passed as void*, a cudaStream_t; NULL is the
  * legacy default stream).  They enqueue work and return without waiting, the way the
@@ -109,6 +110,12 @@ FFInfo ff_get_info(const FFContext *ctx);
  * name), clears the record and returns the number of names.  The counterpart of the reference's
  * per-encoder GPU timestamps (Infrastructure/Metal/GPUTrace.swift:67-90).  Do not trace while a
  * stream is being captured into a CUDA graph. */
+/* Waits for the device and clears the flag ff_get_info reports as deviceErrorFlag (it is sticky:
+ * set by a kernel that gave up a bounded wait, 1..11, or that met a route naming an expert that is
+ * not resident, 12 — the condition the reference traps with "route expert N is out of range",
+ * Runtime/Inference/RealForwardRunner.swift:815). */
+bool ff_reset_device_error(FFContext *ctx, const char **error);
+
 void ff_set_tracing(FFContext *ctx, bool enabled);
 uint32_t ff_get_trace(FFContext *ctx, FFTraceEntry *entries, uint32_t capacity);
 
@@ -224,15 +231,21 @@ bool ff_shared_ffn(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t x
  * counterpart in the reference.  It needs no FFContext: the three projections, x and y are
  * DEVICE pointers supplied by the caller, and the only scratch (the GeGLU activations between the
  * two kernels) is a fixed 128 KiB array inside the library image, which every GPU that loads the
- * library holds until the process exits.  Sizes are therefore limited to rows <= 16 and
- * intermediate width (gate->rows) <= 4096; larger requests fail with a message.  The call
- * performs no cudaMalloc, cudaFree or other allocating routine.  The first call on each device
- * looks up that array's device address (with the device current); make that first call before
- * any stream capture begins.  All calls on a device share the one array and it keeps the last
- * call's contents: nothing in it needs clearing (every element read was written earlier in the
- * same call), but two calls whose kernels overlap on the GPU (issued on different streams without
- * an ordering between them) race on it and must be ordered by the caller.  Results are bitwise
- * those of ff_shared_ffn on the same weights and rows. */
+ * library holds until the process exits.  Sizes are therefore limited to rows <= 16,
+ * intermediate width (gate->rows) <= 4096 and model width (gate->cols) <= 16384; larger requests
+ * fail with a message before anything is enqueued.  (Inside those limits every combination runs:
+ * when the staged input rows of a kernel do not fit in shared memory together, e.g. 16 rows of
+ * width 4096, the kernel is launched in passes of fewer rows.)  x must be 4-byte aligned with an
+ * even xStride.  The call performs no cudaMalloc, cudaFree or other allocating routine.  The
+ * first call on each device looks up that array's device address (with the device current; the
+ * look-up is guarded, so any host thread may make it); make that first call before any stream
+ * capture begins.  All calls on a device share the one array and it keeps the last call's
+ * contents: nothing in it needs clearing (every element read was written earlier in the same
+ * call), but two calls whose kernels overlap on the GPU (issued on different streams without an
+ * ordering between them) race on it and must be ordered by the caller.  For 2..16 rows the
+ * results are bitwise those of ff_shared_ffn on the same weights and rows (the same kernels); one
+ * row differs from ff_shared_ffn, which then runs inside the fused decode kernel with another
+ * summation order, by rounding only. */
 bool ff_shared_ffn_noalloc(const FFProjection *gate, const FFProjection *up,
                            const FFProjection *down, const uint16_t *x, uint32_t xStride,
                            uint32_t rows, uint16_t *y, uint32_t yStride, void *stream,
@@ -254,6 +267,16 @@ bool ff_rmsnorm(FFContext *ctx, const uint16_t *x, const uint16_t *w, float eps,
  * metric times.  ids/weights (optional) receive the routes. */
 bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t tokens,
                   uint16_t *y, uint32_t *ids, uint16_t *weights, void *stream,
+                  const char **error);
+
+/* The layer stack of benchmark configuration 4 (MoE blocks with an RMSNorm between them, no
+ * attention): for l = firstLayer .. firstLayer+layerCount-1:  x <- ff_moe_layer(l, rmsnorm(x)),
+ * rmsnorm without a weight, y receives the last block's output.  ids (optional) receives every
+ * layer's routes, uint32 [layerCount][tokens][K].  The glue stands where the reference has its
+ * fused layer tail (Metal/Prefill/prefill.metal:321-399; CPU statement
+ * Tests/Support/Validation/Reference/Primitives/RmsNorm.swift:8-39). */
+bool ff_moe_stack(FFContext *ctx, uint32_t firstLayer, uint32_t layerCount, const uint16_t *x,
+                  uint32_t tokens, float eps, uint16_t *y, uint32_t *ids, void *stream,
                   const char **error);
 
 /* ff_moe_layer with HOST buffers: copies x in, runs, copies y out, waits.  Host pointers should

@@ -651,6 +651,29 @@ void ffo_moe_layer(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t mod
     free(ids);
 }
 
+/* Benchmark configuration 4: a stack of MoE blocks with an RMSNorm (no weight) in front of each and
+ * no attention:  x <- layer_l(rmsnorm(x)),  l = 0 .. n_layers-1;  y = the last block's output.
+ * The norm is Tests/Support/Validation/Reference/Primitives/RmsNorm.swift:8-39 on the bf16 rows
+ * (fp32 inside, one rounding on store), standing where the reference has its fused layer tail
+ * (Sources/ANEFieldfareHotpath/Metal/Prefill/prefill.metal:321-399).  ids_out (optional) receives
+ * every layer's routes [n_layers][T][K]. */
+void ffo_moe_stack(const ffo_layer *layers, int32_t n_layers, const uint16_t *x, int32_t T, float eps,
+                   int32_t mode, uint16_t *y, uint32_t *ids_out) {
+    if (n_layers <= 0 || T <= 0) return;
+    const int32_t D = layers[0].D;
+    uint16_t *cur = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)T * D);
+    uint16_t *normed = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)T * D);
+    memcpy(cur, x, sizeof(uint16_t) * (size_t)T * D);
+    for (int32_t l = 0; l < n_layers; ++l) {
+        ffo_rmsnorm_bf16(cur, NULL, eps, T, D, normed);
+        ffo_moe_layer(&layers[l], normed, T, mode, cur, NULL,
+                      ids_out ? ids_out + (int64_t)l * T * layers[l].K : NULL, NULL);
+    }
+    memcpy(y, cur, sizeof(uint16_t) * (size_t)T * D);
+    free(normed);
+    free(cur);
+}
+
 void ffo_set_num_threads(int32_t n) {
 #ifdef _OPENMP
     if (n > 0) omp_set_num_threads(n);

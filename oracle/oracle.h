@@ -113,6 +113,8 @@ void ffo_shared_ffn(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_
                     uint16_t *y);
 void ffo_moe_layer(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t mode, uint16_t *y,
                    float *y_f32, uint32_t *ids_out, uint16_t *w_out);
+void ffo_moe_stack(const ffo_layer *layers, int32_t n_layers, const uint16_t *x, int32_t T, float eps,
+                   int32_t mode, uint16_t *y, uint32_t *ids_out);
 int32_t ffo_num_threads(void);
 void ffo_set_num_threads(int32_t n);
 

@@ -231,6 +231,18 @@ def moe_layer(layer: LayerData, x_bits, mode):
     return y, y32, ids, w
 
 
+def moe_stack(layers, x_bits, eps, mode):
+    """x <- layer_l(rmsnorm(x)) over the list of LayerData; returns (y bf16 bits, ids [layers, T, K])."""
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    T = x_bits.shape[0]
+    n = len(layers)
+    arr = (Layer * n)(*[l.c for l in layers])
+    y = np.empty((T, layers[0].D), dtype=np.uint16)
+    ids = np.empty((n, T, layers[0].K), dtype=np.uint32)
+    lib().ffo_moe_stack(arr, c_int32(n), _p(x_bits), c_int32(T), c_float(eps), c_int32(mode), _p(y), _p(ids))
+    return y, ids
+
+
 def set_num_threads(n: int) -> None:
     lib().ffo_set_num_threads(c_int32(int(n)))
 

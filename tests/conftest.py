@@ -44,26 +44,41 @@ def layer_errors(got: np.ndarray, ref: np.ndarray):
     return rel_l2, scaled, literal, peak_rel
 
 
-# Tolerances of bf16 layer outputs against the CPU oracle:
-#   relative L2 <= 1e-2;
-#   max-abs <= 2e-2 in units of the output peak: max|got - ref| <= 2e-2 * max(1, max|ref|).
-# For outputs of unit scale the second bound is the literal max-abs <= 2e-2.  The synthetic
-# layers' outputs are larger (rms ~4, peak ~20: neighbouring bf16 numbers are 0.03..0.125 apart
-# there), so one rounding of an output to the other neighbour already exceeds a fixed 2e-2; the
-# peak-scaled form is the reference's own error measure (RelError.compute,
-# Tests/Support/Validation/Tolerance/RelError.swift:7-17), whose tolerance for chained 16-bit
-# reductions is 1e-2 (Tolerances.swift:13).
+# Tolerances of bf16 layer outputs against the CPU oracle (north_star: "rel-L2 <= 1e-2 and
+# max-abs <= 2e-2 in bf16"):
+#   relative L2 <= 1e-2, always;
+#   literal max-abs <= 2e-2 wherever the outputs are of unit scale (peak <= 1): asserted as
+#     written by the unit-scale variants of the benchmark configurations (down_shift = 5);
+#   at the benchmark configurations' own scale (outputs of rms ~4, peak ~20, where neighbouring
+#     bf16 numbers are 0.03..0.125 apart and one rounding to the other neighbour already exceeds a
+#     fixed 2e-2) the same bound in units of the output peak: max|got - ref| <= 2e-2 * max(1, peak),
+#     the reference's own error measure (RelError.compute,
+#     Tests/Support/Validation/Tolerance/RelError.swift:7-17; tolerance 1e-2 for chained 16-bit
+#     reductions, Tolerances.swift:13);
+#   element by element: |got_i - ref_i| <= elementwise_tol * max(1, |ref_i|) where a caller asks
+#     for it (the GEMV paths, whose weights stay fp32).
+# Every call appends its figures to the file named by FF_PARITY_LOG (when set).
 REL_L2_TOL = 1e-2
 MAX_ABS_TOL = 2e-2
 
 
-def assert_layer_close(got_bits, ref_bits, O, what=""):
+def assert_layer_close(got_bits, ref_bits, O, what="", literal_tol=None, elementwise_tol=None):
     got = O.bf16_to_float(np.asarray(got_bits, dtype=np.uint16))
     ref = O.bf16_to_float(np.asarray(ref_bits, dtype=np.uint16))
     assert np.isfinite(got).all(), f"{what}: non-finite output"
     rel_l2, scaled, literal, peak_rel = layer_errors(got, ref)
-    peak = max(1.0, float(np.abs(ref).max())) if ref.size else 1.0
-    assert rel_l2 <= REL_L2_TOL, f"{what}: rel-L2 {rel_l2:.3e}"
-    assert literal <= MAX_ABS_TOL * peak, \
-        f"{what}: max-abs {literal:.3e} > 2e-2 * peak {peak:.3f} (rel-L2 {rel_l2:.3e})"
+    ref_peak = float(np.abs(ref).max()) if ref.size else 0.0
+    peak = max(1.0, ref_peak)
+    line = (f"{what}: rel-L2 {rel_l2:.3e} max-abs {literal:.3e} element-wise {scaled:.3e} "
+            f"peak {ref_peak:.3f} n {ref.size}")
+    log = os.environ.get("FF_PARITY_LOG")
+    if log:
+        with open(log, "a") as fh:
+            fh.write(line + "\n")
+    assert rel_l2 <= REL_L2_TOL, line
+    assert literal <= MAX_ABS_TOL * peak, line
+    if literal_tol is not None:
+        assert literal <= literal_tol, line
+    if elementwise_tol is not None:
+        assert scaled <= elementwise_tol, line
     return rel_l2, literal, peak_rel

@@ -67,7 +67,7 @@ def _expected(rank):
     return y
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, results, chunks=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -82,8 +82,11 @@ def _worker(rank, world, port, results):
             p = partials.reshape(T_PER_RANK, K, D)
             return residual + (weights[:, :, None] * p).sum(dim=1)
 
-        layer = ExpertParallelMoE(E, K, lambda v: (ids, w), lambda v: 0.5 * v, experts_fn, reduce_fn)
+        layer = ExpertParallelMoE(E, K, lambda v: (ids, w), lambda v: 0.5 * v, experts_fn, reduce_fn,
+                                  chunks=chunks)
+        layer.count_experts = True
         y = layer.forward(x)
+        assert int(layer.last_expert_counts.sum()) == T_PER_RANK * K
         # every route arrives somewhere: received rows over the ranks == routes over the ranks
         total = torch.tensor([layer.last_recv_rows], dtype=torch.int64)
         dist.all_reduce(total)
@@ -93,13 +96,14 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_layer_two_gloo_ranks():
+@pytest.mark.parametrize("chunks", [1, 3])
+def test_expert_parallel_layer_two_gloo_ranks(chunks):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, results, chunks), nprocs=2, join=True)
     assert results[0][0] and results[1][0]
     assert results[0][1] == 2 * T_PER_RANK * K
     assert results[0][2] != results[1][2]  # the skewed routing loads the ranks unevenly

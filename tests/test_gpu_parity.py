@@ -1,8 +1,9 @@
 """Parity of the CUDA library (through the C ABI) with the CPU oracle on the same seeded inputs.
 
 Bit-exact: dequantized weights, router logits, top-K indices, pair grouping.
-Tolerance (bf16 outputs): relative L2 <= 1e-2; max-abs <= 2e-2 with one bf16 ulp of the value
-itself not counted (conftest.assert_layer_close).
+Tolerance (bf16 outputs; conftest.assert_layer_close): relative L2 <= 1e-2; max-abs <= 2e-2 as
+written for the unit-scale variants (outputs of peak <= 1), and in units of the output peak at the
+benchmark configurations' own scale.
 """
 import ctypes
 import os

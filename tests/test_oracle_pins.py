@@ -253,6 +253,89 @@ def test_decode_and_partials_modes_agree_within_rounding(oracle):
     assert np.array_equal(oracle.reduce_token_major(partials, w1, h1, 5, 4, 128), y1)
 
 
+def _bf16_round64(v):
+    """float64 array -> nearest bf16 (ties to even), returned as float64."""
+    f = np.asarray(v, dtype=np.float64).astype(np.float32)
+    return synth.bf16_to_float(synth.bf16_bits(f)).astype(np.float64)
+
+
+def _dense(blob, lay, role):
+    w, s, b = gturbo.sub_tensor(blob, lay, role)
+    rows, cols = lay.matrix_shape(role)
+    q = np.stack([w & 0x0F, w >> 4], axis=-1).reshape(rows, cols).astype(np.float64)
+    return q * np.repeat(synth.bf16_to_float(s).astype(np.float64), 64, axis=1) + \
+        np.repeat(synth.bf16_to_float(b).astype(np.float64), 64, axis=1)
+
+
+def _ffn64(blob, lay, x, round_gate_up):
+    g, u = _dense(blob, lay, "gate") @ x, _dense(blob, lay, "up") @ x
+    if round_gate_up:
+        g, u = _bf16_round64(g), _bf16_round64(u)
+    gelu = 0.5 * g * (1.0 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    return _dense(blob, lay, "down") @ _bf16_round64(gelu * u)
+
+
+def test_whole_layer_against_float64_model(oracle):
+    """ffo_moe_layer end to end against an independent float64 statement of the same layer with the
+    same rounding points (Tests/Support/Validation/Reference/MoE/Moe.swift:26-78 for the routed
+    sum; shared FFN rounding as Metal/MoE/moe.metal:548-570): catches a misplaced rounding, a wrong
+    slot order or weight pairing, which the per-function pins cannot see."""
+    L = workload.make_layer(0x64, 0, experts=16, d=128, f=64, sharedF=192, topK=8, router_bias="normal")
+    ld = oracle_layer(oracle, L)
+    x = workload.make_tokens(0x64, "x", 4, 128)
+    xf = synth.bf16_to_float(x).astype(np.float64)
+    for mode in (oracle.MODE_DECODE, oracle.MODE_PARTIALS):
+        y, y32, ids, w = oracle.moe_layer(ld, x, mode)
+        wf = synth.bf16_to_float(w).astype(np.float64)
+        want = np.zeros((4, 128))
+        for t in range(4):
+            h1 = _bf16_round64(_ffn64(L.sharedBlob, L.sharedLayout, xf[t], True))
+            acc = h1.copy() if mode == oracle.MODE_DECODE else np.zeros(128)
+            for r in range(8):
+                v = _ffn64(L.blobs[ids[t, r]], L.layout, xf[t], False)
+                acc += wf[t, r] * (v if mode == oracle.MODE_DECODE else _bf16_round64(v))
+            want[t] = acc if mode == oracle.MODE_DECODE else acc + h1
+        rel = np.linalg.norm(y32 - want) / np.linalg.norm(want)
+        # fp32 accumulation against float64, plus the rare intermediate that rounds to the other
+        # bf16 neighbour: a misplaced rounding point or a wrong slot pairing gives >= 1e-3
+        assert rel < 3e-4, (mode, rel)
+        assert np.abs(oracle.bf16_to_float(y) - _bf16_round64(want)).max() <= \
+            2.0 ** -7 * np.abs(want).max(), mode
+
+
+def test_stack_is_rmsnorm_then_layer_per_layer(oracle):
+    """ffo_moe_stack == x <- moe_layer_l(rmsnorm(x)) composed from the pinned pieces, bit for bit,
+    with every layer's routes reported."""
+    layers = [workload.make_layer(0x57AC, i, experts=16, d=128, f=64, sharedF=192, topK=8,
+                                  router_bias="normal") for i in range(3)]
+    lds = [oracle_layer(oracle, L) for L in layers]
+    for tokens, mode in ((1, oracle.MODE_DECODE), (5, oracle.MODE_PARTIALS)):
+        x = workload.make_tokens(0x57AC, f"x{tokens}", tokens, 128)
+        y, ids = oracle.moe_stack(lds, x, 1e-6, mode)
+        cur = x
+        for i, ld in enumerate(lds):
+            normed = oracle.rmsnorm_bf16(cur, None, 1e-6, tokens, 128)
+            cur, _, want_ids, _ = oracle.moe_layer(ld, normed, mode)
+            assert np.array_equal(ids[i], want_ids)
+        assert np.array_equal(y, cur)
+        # the norm keeps every block's input at unit RMS
+        assert abs(np.sqrt((oracle.bf16_to_float(normed).astype(np.float64) ** 2).mean()) - 1.0) < 1e-2
+
+
+def test_down_shift_scales_the_layer_output_exactly(oracle):
+    """workload.make_layer(down_shift=n) multiplies the outputs by 2^-n exactly (only exponents of
+    the down projections' scales and biases change): the unit-scale variants of the benchmark
+    configurations are the same arithmetic in other units."""
+    kw = dict(experts=8, d=128, f=64, sharedF=128, topK=4)
+    a = workload.make_layer(31, 0, **kw)
+    b = workload.make_layer(31, 0, down_shift=5, **kw)
+    x = workload.make_tokens(31, "x", 3, 128)
+    ya, _, ida, _ = oracle.moe_layer(oracle_layer(oracle, a), x, oracle.MODE_PARTIALS)
+    yb, _, idb, _ = oracle.moe_layer(oracle_layer(oracle, b), x, oracle.MODE_PARTIALS)
+    assert np.array_equal(ida, idb)
+    assert np.array_equal(oracle.bf16_to_float(ya), oracle.bf16_to_float(yb) * np.float32(32.0))
+
+
 def test_golden_fixture(oracle):
     """Committed oracle outputs for a tiny seeded layer (tests/golden/make_golden.py): guards the
     oracle itself against drift.  The reference holds no golden vectors for this path."""
