@@ -50,6 +50,11 @@ class FFInfo(ctypes.Structure):
                 ("deviceErrorFlag", c_uint32), ("reserved", c_uint32)]
 
 
+class FFGTurboLayoutInfo(ctypes.Structure):
+    _fields_ = [("expertStride", c_uint64), ("numLayers", c_uint32), ("expertsPerLayer", c_uint32),
+                ("offsets", MoEExpertOffsets), ("identityPlacement", c_uint32)]
+
+
 class FFTraceEntry(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char * 40), ("launches", c_uint64), ("milliseconds", ctypes.c_double)]
 
@@ -69,6 +74,8 @@ SIGNATURES = {
     "ff_decode_warp_times": (c_bool, [c_void_p, POINTER(ctypes.c_double), _ERR]),
     "ff_load_layer": (c_bool, [c_void_p, c_uint32, _P, c_uint64, c_uint32, c_uint64,
                                POINTER(MoEExpertOffsets), _ERR]),
+    "ff_gturbo_validate_layout": (c_bool, [c_char_p, c_uint32, c_uint32, POINTER(FFGTurboLayoutInfo), _ERR]),
+    "ff_load_model_dir": (c_bool, [c_void_p, c_char_p, _ERR]),
     "ff_load_shared": (c_bool, [c_void_p, c_uint32, POINTER(FFProjection), POINTER(FFProjection),
                                 POINTER(FFProjection), _ERR]),
     "ff_load_router": (c_bool, [c_void_p, c_uint32, _P, _P, _P, _P, c_uint32, c_uint32, _ERR]),

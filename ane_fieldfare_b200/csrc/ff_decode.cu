@@ -96,6 +96,12 @@ struct alignas(64) DecodeMaps {
 };
 enum : int { kMapRoutedGate = 0, kMapRoutedUp = 1, kMapSharedGate = 2, kMapSharedUp = 3, kMapSharedDown = 4 };
 
+// Fetches a tensor map's descriptor ahead of its first use (the first copy through a map otherwise
+// waits for it).
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 // Bulk L2 prefetch of [p, p + bytes); bytes a multiple of 16, p 16-byte aligned.
 __device__ __forceinline__ void prefetch_l2_bulk(const void *p, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
@@ -301,6 +307,7 @@ __device__ __forceinline__ void decode_body(const DecodeArgs &a, const DecodeMap
         for (int w = 0; w < kFusedWarps; ++w) bar_init(sm_addr(&sCopyBar[w]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (warp >= 11 && lane == 0) prefetch_tensormap(&maps.m[warp - 11]);  // warps 11..15: the five maps
     // the ticket: drawn now by a thread with nothing to request (warp 9), published to the CTA
     // further down so that nobody waits for the atomic's round trip here
     unsigned long long ticket = 0;

@@ -85,9 +85,12 @@ def sub_tensor(blob: np.ndarray, lay: ExpertLayout, role: str):
     return w, s, b
 
 
-def layout_json(num_layers: int, experts: int, lay: ExpertLayout) -> str:
-    """`packed_experts/layout.json` for identity expert placement, with the reference's keys
-    (Sources/ANEFieldfareInstallCore/Format/GTurboJSON.swift:110-172)."""
+def layout_json(num_layers: int, experts: int, lay: ExpertLayout, physical_ranks=None,
+                explicit_ids: bool = True) -> str:
+    """`packed_experts/layout.json` with the reference's keys and conventions
+    (Sources/ANEFieldfareInstallCore/Format/GTurboJSON.swift:110-172): `file` is the layer file's
+    basename, an expert's `size` is the expert stride and its `offset` physicalRank * stride.
+    `physical_ranks[layer][expert]` (default: identity) places expert blobs inside the layer file."""
     off = lay.offsets.as_tuple()
 
     def tensors():
@@ -105,9 +108,34 @@ def layout_json(num_layers: int, experts: int, lay: ExpertLayout) -> str:
 
     layers = []
     for layer in range(num_layers):
-        layers.append({
-            "layer": layer, "file": "packed_experts/layer_%02d.bin" % layer,
-            "experts": [{"expert": e, "physicalRank": e, "offset": e * lay.stride,
-                         "size": lay.payload, "tensors": tensors()} for e in range(experts)]})
+        entries = []
+        for e in range(experts):
+            rank = e if physical_ranks is None else int(physical_ranks[layer][e])
+            entry = {"offset": rank * lay.stride, "size": lay.stride, "tensors": tensors()}
+            if explicit_ids:
+                entry["expert"] = e
+            if rank != e:
+                entry["physicalRank"] = rank
+            entries.append(entry)
+        layers.append({"layer": layer, "file": "layer_%02d.bin" % layer, "experts": entries})
     return json.dumps({"expertStride": lay.stride, "numLayers": num_layers,
                        "expertsPerLayer": experts, "layers": layers})
+
+
+def write_model_dir(path: str, layer_blobs, lay: ExpertLayout, physical_ranks=None) -> None:
+    """Writes `<path>/packed_experts/layout.json` and one `layer_%02d.bin` per entry of
+    `layer_blobs` (uint8 [experts, stride] each, logical expert order); with `physical_ranks` the
+    blob of expert e is stored at rank physical_ranks[layer][e] of its file."""
+    import os
+    out = os.path.join(path, "packed_experts")
+    os.makedirs(out, exist_ok=True)
+    experts = layer_blobs[0].shape[0]
+    for layer, blobs in enumerate(layer_blobs):
+        data = np.ascontiguousarray(blobs, dtype=np.uint8)
+        if physical_ranks is not None:
+            stored = np.empty_like(data)
+            stored[np.asarray(physical_ranks[layer], dtype=np.int64)] = data
+            data = stored
+        data.tofile(os.path.join(out, "layer_%02d.bin" % layer))
+    with open(os.path.join(out, "layout.json"), "w") as fh:
+        fh.write(layout_json(len(layer_blobs), experts, lay, physical_ranks))

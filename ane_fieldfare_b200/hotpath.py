@@ -29,7 +29,7 @@ from .binding import (FFConfig, FFMoEGroup, FFMoETile, FFProjection, FFTokenExpe
                       FieldfareError, call)
 from .gturbo import MoEExpertOffsets
 
-__all__ = ["HotpathContext", "MoE", "SharedExpertInt4", "SharedExpertProjection", "PrefillRouter",
+__all__ = ["HotpathContext", "validateGTurboLayout", "MoE", "SharedExpertInt4", "SharedExpertProjection", "PrefillRouter",
            "PrefillMoEGrouping", "PrefillGroupedRoutedMoE", "PrefillMoE", "PrefillSharedExpert",
            "DequantInt4GEMV", "CudaRoutedPrefillGuest", "PrefillTokenExpertPair", "PrefillMoEGroup",
            "PrefillMoETile", "PrefillMoEGroupedRoutes", "PrefillMoEGroupingError", "FieldfareError",
@@ -47,6 +47,14 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 def _stream(stream: Optional[torch.cuda.Stream]) -> Optional[int]:
     s = stream if stream is not None else torch.cuda.current_stream()
     return s.cuda_stream or None
+
+
+def validateGTurboLayout(path: str, d: int, f: int) -> binding.FFGTurboLayoutInfo:
+    """Checks `<path>/packed_experts/layout.json` (no GPU needed); raises FieldfareError with the
+    reference's message on the first rule that fails."""
+    info = binding.FFGTurboLayoutInfo()
+    call("ff_gturbo_validate_layout", path.encode(), d, f, ctypes.byref(info))
+    return info
 
 
 def bf16_tensor(bits: np.ndarray, device) -> torch.Tensor:
@@ -130,6 +138,12 @@ class HotpathContext:
         count = self.experts if expertCount is None else expertCount
         call("ff_load_layer", self.handle, layer, data.ctypes.data, data.size, count, expertStride,
              ctypes.byref(offsets))
+
+    def loadModelDir(self, path: str):
+        """An installed model's `packed_experts/` (layout.json + layer files) into the layer slots,
+        after the reference's validation (Infrastructure/ModelIO/PackedExpertsLayout.swift:55-90,
+        Runtime/Inference/Model.swift:478-527)."""
+        call("ff_load_model_dir", self.handle, path.encode())
 
     def loadShared(self, layer: int, gate, up, down):
         """Each projection: (packed uint8 [rows, cols/2], scales uint16, biases uint16) on the host."""

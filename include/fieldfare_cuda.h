@@ -148,6 +148,32 @@ bool ff_load_layer(FFContext *ctx, uint32_t layer, const void *hostBytes, uint64
                    uint32_t expertCount, uint64_t expertStride, const FFExpertOffsets *offsets,
                    const char **error);
 
+/* What a validated `packed_experts/layout.json` says. */
+typedef struct {
+    uint64_t expertStride;
+    uint32_t numLayers, expertsPerLayer;
+    FFExpertOffsets offsets;      /* the nine sub-tensor offsets of layer 0's experts */
+    uint32_t identityPlacement;   /* 1: every expert sits at rank == its id in its layer file */
+} FFGTurboLayoutInfo;
+
+/* Reads and checks `<modelDir>/packed_experts/layout.json` without touching a GPU: the decode and
+ * structural validation of Sources/ANEFieldfareImportedFormat/GTurboPackedExpertsLayoutV1.swift:65-162
+ * (dimensions and stride, duplicate layers and file names, expert ids and physical ranks, per-tensor
+ * offset/size/dtype/shape, overlapping ranges) and the runtime's schema check of the routed experts
+ * against the model's widths d and f (Runtime/Inference/Model.swift:478-527: U32 4-bit weights
+ * [rows][cols/8], BF16 scales and biases [rows][cols/64], alignment, identical across a layer's
+ * experts).  Failures carry the reference's messages. */
+bool ff_gturbo_validate_layout(const char *modelDir, uint32_t d, uint32_t f, FFGTurboLayoutInfo *info,
+                               const char **error);
+
+/* Loads an installed model's routed experts into HBM: validates the layout as above, then copies
+ * every `packed_experts/<file>` it names into layer slot `layer` (ff_load_layer), expert e's blob
+ * taken from offset physicalRank * expertStride of its file — the expert lookup of
+ * Sources/ANEFieldfareHotpath/Infrastructure/ModelIO/PackedExpertsLayout.swift:55-90 and
+ * Runtime/Inference/ModelExpertIO.swift:11-35.  A layer file whose size is not expertsPerLayer
+ * strides is refused like the reference's manifest cross-check. */
+bool ff_load_model_dir(FFContext *ctx, const char *modelDir, const char **error);
+
 /* The shared FFN's three projections from HOST pointers (the reference keeps them as resident
  * tensors: Kernels/MoE/SharedExpertInt4.swift:32-38). */
 bool ff_load_shared(FFContext *ctx, uint32_t layer, const FFProjection *gate,

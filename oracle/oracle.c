@@ -201,9 +201,26 @@ float ffo_int4_dot(const uint8_t *w, const uint16_t *s, const uint16_t *b, int32
  * once and the same column-ascending chain runs for all input rows side by side (the layout the
  * reference's Tests/Support/Validation/Reference/Quant/DequantInt4Gemv.swift:9-38 uses:
  * dequantize the row, then dot).  xt is x transposed to [cols][rpad]. */
+/* bf16 nearest to the exact real value q*scale + bias (one rounding, as one bf16 fused multiply-add
+ * gives; see ffo_dequant_int4_bf16). */
+static inline float weight_bf16(uint32_t q, float scale, float bias) {
+    double exact = (double)q * (double)scale + (double)bias;
+    float f = (float)exact;
+    if ((double)f != exact) {
+        uint32_t u;
+        memcpy(&u, &f, 4);
+        if (fabs((double)f) > fabs(exact)) u -= 1;
+        u |= 1u;
+        memcpy(&f, &u, 4);
+    }
+    return bf16_round(f);
+}
+
+/* weights_bf16: multiply the weights rounded once to bf16, the operand of the tensor-core prefill
+ * path (Sources/ANEFieldfareHotpath/Metal/Prefill/prefill.metal:581-590 rounds to half there). */
 static void gemv_rows_t(const uint8_t *w, const uint16_t *s, const uint16_t *b, int32_t rows,
                         int32_t cols, const float *xt, int32_t n, int32_t rpad, float *y,
-                        int32_t y_stride) {
+                        int32_t y_stride, int32_t weights_bf16) {
     const int32_t groups = cols / GROUP;
 #pragma omp parallel if (!omp_in_parallel() && (int64_t)rows * cols * n > 1 << 18)
     {
@@ -217,8 +234,12 @@ static void gemv_rows_t(const uint8_t *w, const uint16_t *s, const uint16_t *b, 
                 float bias = ffo_bf16_to_float(b[(int64_t)o * groups + g]);
                 for (int k = 0; k < GROUP; ++k) {
                     int32_t c = g * GROUP + k;
-                    float prod = (float)nibble_at(wr, c) * scale;
-                    wrow[c] = prod + bias;
+                    if (weights_bf16) {
+                        wrow[c] = weight_bf16(nibble_at(wr, c), scale, bias);
+                    } else {
+                        float prod = (float)nibble_at(wr, c) * scale;
+                        wrow[c] = prod + bias;
+                    }
                 }
             }
             for (int32_t r = 0; r < rpad; ++r) acc[r] = 0.0f;
@@ -252,7 +273,7 @@ void ffo_int4_gemv_rows(const uint8_t *w, const uint16_t *s, const uint16_t *b, 
                         int32_t y_stride) {
     int32_t rpad;
     float *xt = transpose_pad(x, x_rows, x_stride, cols, &rpad);
-    gemv_rows_t(w, s, b, rows, cols, xt, x_rows, rpad, y, y_stride);
+    gemv_rows_t(w, s, b, rows, cols, xt, x_rows, rpad, y, y_stride, 0);
     free(xt);
 }
 
@@ -272,9 +293,9 @@ float ffo_gelu_tanh(float x) {
  * PrefillGroupedRoutedMoETests.swift:139-143 (bf16 here, fp16 there).  round_gate_up rounds the
  * two projections before the activation, as the shared FFN does
  * (Sources/ANEFieldfareHotpath/Metal/MoE/moe.metal:548-570).  out is fp32 [T][out_stride]. */
-void ffo_expert_ffn(const uint8_t *blob, const ffo_offsets *off, int32_t D, int32_t F,
-                    const uint16_t *x, int32_t T, int32_t x_stride, int32_t round_gate_up,
-                    int32_t round_act, float *out, int32_t out_stride) {
+static void expert_ffn_w(const uint8_t *blob, const ffo_offsets *off, int32_t D, int32_t F,
+                         const uint16_t *x, int32_t T, int32_t x_stride, int32_t round_gate_up,
+                         int32_t round_act, int32_t weights_bf16, float *out, int32_t out_stride) {
     if (T <= 0) return;
     float *xf = (float *)malloc(sizeof(float) * (size_t)T * D);
     for (int32_t t = 0; t < T; ++t)
@@ -285,9 +306,9 @@ void ffo_expert_ffn(const uint8_t *blob, const ffo_offsets *off, int32_t D, int3
     float *g = (float *)malloc(sizeof(float) * (size_t)T * F);
     float *u = (float *)malloc(sizeof(float) * (size_t)T * F);
     gemv_rows_t(blob + off->gate_w, (const uint16_t *)(blob + off->gate_s),
-                (const uint16_t *)(blob + off->gate_b), F, D, xt, T, rpad, g, F);
+                (const uint16_t *)(blob + off->gate_b), F, D, xt, T, rpad, g, F, weights_bf16);
     gemv_rows_t(blob + off->up_w, (const uint16_t *)(blob + off->up_s),
-                (const uint16_t *)(blob + off->up_b), F, D, xt, T, rpad, u, F);
+                (const uint16_t *)(blob + off->up_b), F, D, xt, T, rpad, u, F, weights_bf16);
     free(xt);
     for (int64_t i = 0; i < (int64_t)T * F; ++i) {
         float gv = g[i], uv = u[i];
@@ -300,11 +321,17 @@ void ffo_expert_ffn(const uint8_t *blob, const ffo_offsets *off, int32_t D, int3
     }
     float *at = transpose_pad(g, T, F, F, &rpad);
     gemv_rows_t(blob + off->down_w, (const uint16_t *)(blob + off->down_s),
-                (const uint16_t *)(blob + off->down_b), D, F, at, T, rpad, out, out_stride);
+                (const uint16_t *)(blob + off->down_b), D, F, at, T, rpad, out, out_stride, weights_bf16);
     free(at);
     free(g);
     free(u);
     free(xf);
+}
+
+void ffo_expert_ffn(const uint8_t *blob, const ffo_offsets *off, int32_t D, int32_t F,
+                    const uint16_t *x, int32_t T, int32_t x_stride, int32_t round_gate_up,
+                    int32_t round_act, float *out, int32_t out_stride) {
+    expert_ffn_w(blob, off, D, F, x, T, x_stride, round_gate_up, round_act, 0, out, out_stride);
 }
 
 /* ---- router ------------------------------------------------------------------------------ */
@@ -482,8 +509,8 @@ int32_t ffo_group_pairs(const ffo_pair *pairs, int64_t n_pairs, int32_t T, int32
  * PrefillGroupedRoutedMoETests.swift:122-151 (act rounded to 16 bits, then the down row dots).
  * Writes fp32 values to v32[(token*K+rank)*D] and/or bf16 to p16 at the same index. */
 static void routed_values(const ffo_layer *L, const uint16_t *x, int32_t x_stride,
-                          const ffo_pair *pairs, int64_t n_pairs, int32_t round_act, float *v32,
-                          uint16_t *p16) {
+                          const ffo_pair *pairs, int64_t n_pairs, int32_t round_act,
+                          int32_t weights_bf16, float *v32, uint16_t *p16) {
     const int32_t E = L->E, D = L->D, K = L->K;
     int64_t *start = (int64_t *)calloc((size_t)E + 1, sizeof(int64_t));
     for (int64_t i = 0; i < n_pairs; ++i) start[pairs[i].expert + 1]++;
@@ -502,8 +529,8 @@ static void routed_values(const ffo_layer *L, const uint16_t *x, int32_t x_strid
             const ffo_pair *p = &pairs[order[start[e] + j]];
             memcpy(xe + (int64_t)j * D, x + (int64_t)p->token * x_stride, sizeof(uint16_t) * (size_t)D);
         }
-        ffo_expert_ffn(L->experts + (uint64_t)e * L->expert_stride, &L->off, D, L->F, xe, n, D, 0,
-                       round_act, out, D);
+        expert_ffn_w(L->experts + (uint64_t)e * L->expert_stride, &L->off, D, L->F, xe, n, D, 0,
+                     round_act, weights_bf16, out, D);
         for (int32_t j = 0; j < n; ++j) {
             const ffo_pair *p = &pairs[order[start[e] + j]];
             int64_t base = ((int64_t)p->token * K + p->rank) * D;
@@ -526,7 +553,13 @@ static void routed_values(const ffo_layer *L, const uint16_t *x, int32_t x_strid
  * by a pair are left untouched. */
 void ffo_route_partials(const ffo_layer *L, const uint16_t *x, int32_t x_stride,
                         const ffo_pair *pairs, int64_t n_pairs, uint16_t *partials) {
-    routed_values(L, x, x_stride, pairs, n_pairs, 1, NULL, partials);
+    routed_values(L, x, x_stride, pairs, n_pairs, 1, 0, NULL, partials);
+}
+
+/* The same with the weights rounded once to bf16 (the tensor-core prefill path's operand). */
+void ffo_route_partials_bf16w(const ffo_layer *L, const uint16_t *x, int32_t x_stride,
+                              const ffo_pair *pairs, int64_t n_pairs, uint16_t *partials) {
+    routed_values(L, x, x_stride, pairs, n_pairs, 1, 1, NULL, partials);
 }
 
 /* Tests/ANEFieldfareUpstreamTests/Kernels/Prefill/PrefillMoETests.swift:46-64 with the kernel's
@@ -584,12 +617,22 @@ void ffo_rmsnorm_bf16(const uint16_t *x, const uint16_t *w, float eps, int32_t T
 /* Shared INT4 FFN: gate and up rounded to 16 bits before the activation, the activation rounded
  * again, the down projection rounded on store (moe.metal:548-570 + the down GEMV;
  * Tests/ANEFieldfareUpstreamTests/Kernels/MoE/SharedExpertInt4Tests.swift:19-28). */
-void ffo_shared_ffn(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_stride,
-                    uint16_t *y) {
+static void shared_ffn_w(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_stride,
+                         int32_t weights_bf16, uint16_t *y) {
     float *out = (float *)malloc(sizeof(float) * (size_t)T * L->D);
-    ffo_expert_ffn(L->shared, &L->shared_off, L->D, L->Fs, x, T, x_stride, 1, 1, out, L->D);
+    expert_ffn_w(L->shared, &L->shared_off, L->D, L->Fs, x, T, x_stride, 1, 1, weights_bf16, out, L->D);
     ffo_bf16_bits_n(out, y, (int64_t)T * L->D);
     free(out);
+}
+
+void ffo_shared_ffn(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_stride,
+                    uint16_t *y) {
+    shared_ffn_w(L, x, T, x_stride, 0, y);
+}
+
+void ffo_shared_ffn_bf16w(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_stride,
+                          uint16_t *y) {
+    shared_ffn_w(L, x, T, x_stride, 1, y);
 }
 
 /* Router -> top-K -> routed experts (+ shared FFN as the residual) for T rows of x[T][D].
@@ -605,16 +648,18 @@ void ffo_moe_layer(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t mod
     ffo_router_topk(L, x, T, D, ids, w, NULL);
     if (ids_out) memcpy(ids_out, ids, sizeof(uint32_t) * (size_t)T * K);
     if (w_out) memcpy(w_out, w, sizeof(uint16_t) * (size_t)T * K);
+    const int32_t wb = (mode & FFO_MODE_BF16_WEIGHTS) ? 1 : 0;
+    mode &= ~FFO_MODE_BF16_WEIGHTS;
     uint16_t *h1 = NULL;
     if (L->shared) {
         h1 = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)T * D);
-        ffo_shared_ffn(L, x, T, D, h1);
+        shared_ffn_w(L, x, T, D, wb, h1);
     }
     ffo_pair *pairs = (ffo_pair *)malloc(sizeof(ffo_pair) * (size_t)T * K);
     int64_t n_pairs = ffo_make_pairs(ids, w, T, K, pairs);
     if (mode == FFO_MODE_DECODE) {
         float *v = (float *)malloc(sizeof(float) * (size_t)T * K * D);
-        routed_values(L, x, D, pairs, n_pairs, 1, v, NULL);
+        routed_values(L, x, D, pairs, n_pairs, 1, wb, v, NULL);
         for (int32_t t = 0; t < T; ++t)
             for (int32_t d = 0; d < D; ++d) {
                 float acc = h1 ? ffo_bf16_to_float(h1[(int64_t)t * D + d]) : 0.0f;
@@ -629,7 +674,7 @@ void ffo_moe_layer(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t mod
         free(v);
     } else {
         uint16_t *p = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)T * K * D);
-        routed_values(L, x, D, pairs, n_pairs, 1, NULL, p);
+        routed_values(L, x, D, pairs, n_pairs, 1, wb, NULL, p);
         ffo_reduce_token_major(p, w, h1, T, K, D, y);
         if (y_f32) {
 #pragma omp parallel for schedule(static)

@@ -59,7 +59,10 @@ typedef struct {
 
 enum {
     FFO_MODE_DECODE = 0,  /* y = bf16(residual + sum_k w_k * v_k), v_k fp32           */
-    FFO_MODE_PARTIALS = 1 /* P = bf16(v_k); y = bf16(residual + sum_k fma(w_k, P_k))  */
+    FFO_MODE_PARTIALS = 1,/* P = bf16(v_k); y = bf16(residual + sum_k fma(w_k, P_k))  */
+    /* or-ed onto a mode: every weight is rounded once to bf16 before it is multiplied (the operand
+     * of the tensor-core prefill path; ffo_dequant_int4_bf16 gives the same values) */
+    FFO_MODE_BF16_WEIGHTS = 2
 };
 
 uint16_t ffo_bf16_bits(float x);
@@ -102,6 +105,8 @@ int32_t ffo_group_pairs(const ffo_pair *pairs, int64_t n_pairs, int32_t T, int32
                         uint32_t *bad_expert);
 void ffo_route_partials(const ffo_layer *L, const uint16_t *x, int32_t x_stride,
                         const ffo_pair *pairs, int64_t n_pairs, uint16_t *partials);
+void ffo_route_partials_bf16w(const ffo_layer *L, const uint16_t *x, int32_t x_stride,
+                              const ffo_pair *pairs, int64_t n_pairs, uint16_t *partials);
 void ffo_reduce_token_major(const uint16_t *partials, const uint16_t *weights,
                             const uint16_t *residual, int32_t T, int32_t K, int32_t D,
                             uint16_t *out);
@@ -111,6 +116,8 @@ void ffo_rmsnorm_bf16(const uint16_t *x, const uint16_t *w, float eps, int32_t T
 
 void ffo_shared_ffn(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_stride,
                     uint16_t *y);
+void ffo_shared_ffn_bf16w(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_stride,
+                          uint16_t *y);
 void ffo_moe_layer(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t mode, uint16_t *y,
                    float *y_f32, uint32_t *ids_out, uint16_t *w_out);
 void ffo_moe_stack(const ffo_layer *layers, int32_t n_layers, const uint16_t *x, int32_t T, float eps,

@@ -46,6 +46,7 @@ class Layer(ctypes.Structure):
 
 
 MODE_DECODE, MODE_PARTIALS = 0, 1
+MODE_BF16_WEIGHTS = 2  # or-ed onto a mode: weights rounded once to bf16 (the prefill GEMM's operand)
 _lib = None
 
 
@@ -189,11 +190,11 @@ def group_pairs(pairs, n_pairs, T, K, E, tile_experts, sort_keys=None):
     return list(sorted_pairs)[:n_pairs], list(groups)[:ng.value], list(tiles)[:nt.value]
 
 
-def route_partials(layer: LayerData, x_bits, pairs, n_pairs, T):
+def route_partials(layer: LayerData, x_bits, pairs, n_pairs, T, bf16_weights=False):
     x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
     out = np.zeros((T * layer.K, layer.D), dtype=np.uint16)
-    lib().ffo_route_partials(ctypes.byref(layer.c), _p(x_bits), c_int32(x_bits.shape[1]), pairs,
-                             c_int64(n_pairs), _p(out))
+    fn = lib().ffo_route_partials_bf16w if bf16_weights else lib().ffo_route_partials
+    fn(ctypes.byref(layer.c), _p(x_bits), c_int32(x_bits.shape[1]), pairs, c_int64(n_pairs), _p(out))
     return out
 
 
@@ -210,11 +211,12 @@ def rmsnorm_bf16(x_bits, w_bits, eps, T, n):
     return out
 
 
-def shared_ffn(layer: LayerData, x_bits):
+def shared_ffn(layer: LayerData, x_bits, bf16_weights=False):
     x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
     T = x_bits.shape[0]
     y = np.empty((T, layer.D), dtype=np.uint16)
-    lib().ffo_shared_ffn(ctypes.byref(layer.c), _p(x_bits), c_int32(T), c_int32(x_bits.shape[1]), _p(y))
+    fn = lib().ffo_shared_ffn_bf16w if bf16_weights else lib().ffo_shared_ffn
+    fn(ctypes.byref(layer.c), _p(x_bits), c_int32(T), c_int32(x_bits.shape[1]), _p(y))
     return y
 
 

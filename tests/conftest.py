@@ -56,10 +56,14 @@ def layer_errors(got: np.ndarray, ref: np.ndarray):
 #     Tests/Support/Validation/Tolerance/RelError.swift:7-17; tolerance 1e-2 for chained 16-bit
 #     reductions, Tolerances.swift:13);
 #   element by element: |got_i - ref_i| <= elementwise_tol * max(1, |ref_i|) where a caller asks
-#     for it (the GEMV paths, whose weights stay fp32).
+#     for it: ELEMENTWISE_TOL for the outputs of one expert's chain (partial rows, shared FFN rows),
+#     LAYER_ELEMENTWISE_TOL for layer outputs, which add up to nine bf16-rounded rows of either
+#     sign: where they cancel, one ulp of a large term is several percent of a small sum.
 # Every call appends its figures to the file named by FF_PARITY_LOG (when set).
 REL_L2_TOL = 1e-2
 MAX_ABS_TOL = 2e-2
+ELEMENTWISE_TOL = 2e-2
+LAYER_ELEMENTWISE_TOL = 5e-2
 
 
 def assert_layer_close(got_bits, ref_bits, O, what="", literal_tol=None, elementwise_tol=None):

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from ane_fieldfare_b200 import synth, workload
-from conftest import assert_layer_close, oracle_layer
+from conftest import ELEMENTWISE_TOL, LAYER_ELEMENTWISE_TOL, assert_layer_close, oracle_layer
 
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
@@ -99,6 +99,10 @@ def test_prefill_partials_tiny(tiny, oracle, tokens):
     ref_pairs, n = oracle.make_pairs(ref_ids, ref_w, tokens, L.topK)
     want = oracle.route_partials(ld, x, ref_pairs, n, tokens)
     assert_layer_close(hp.bf16_numpy(partials), want, oracle, f"prefill partials T={tokens}")
+    # against the oracle that multiplies the same bf16-rounded weights: element by element
+    want16 = oracle.route_partials(ld, x, ref_pairs, n, tokens, bf16_weights=True)
+    assert_layer_close(hp.bf16_numpy(partials), want16, oracle, f"prefill partials T={tokens} vs bf16 weights",
+                       elementwise_tol=ELEMENTWISE_TOL)
 
 
 @pytest.mark.parametrize("tokens", [20, 300])
@@ -112,6 +116,9 @@ def test_prefill_shared_ffn(tiny, full, oracle, tokens):
         assert ctx.info().deviceErrorFlag == 0
         want = oracle.shared_ffn(oracle_layer(oracle, L), x)
         assert_layer_close(hp.bf16_numpy(y), want, oracle, f"prefill shared T={tokens}")
+        want16 = oracle.shared_ffn(oracle_layer(oracle, L), x, bf16_weights=True)
+        assert_layer_close(hp.bf16_numpy(y), want16, oracle, f"prefill shared T={tokens} vs bf16 weights",
+                           elementwise_tol=ELEMENTWISE_TOL)
 
 
 @pytest.mark.parametrize("tokens", [17, 130, 700])
@@ -126,6 +133,9 @@ def test_prefill_layer_tiny(tiny, oracle, tokens):
     want, _, ref_ids, _ = oracle.moe_layer(oracle_layer(oracle, L), x, oracle.MODE_PARTIALS)
     assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ref_ids)
     assert_layer_close(hp.bf16_numpy(y), want, oracle, f"prefill layer T={tokens}")
+    want16, _, _, _ = oracle.moe_layer(oracle_layer(oracle, L), x, oracle.MODE_PARTIALS | oracle.MODE_BF16_WEIGHTS)
+    assert_layer_close(hp.bf16_numpy(y), want16, oracle, f"prefill layer T={tokens} vs bf16 weights",
+                       elementwise_tol=LAYER_ELEMENTWISE_TOL)
 
 
 def test_prefill_layer_full_shape(full, oracle):
@@ -150,6 +160,9 @@ def test_prefill_layer_full_shape(full, oracle):
     want, _, ref_ids, _ = oracle.moe_layer(ld, x[:512], oracle.MODE_PARTIALS)
     assert np.array_equal(ids[:512].cpu().numpy().astype(np.uint32), ref_ids)
     rel, literal, peak = assert_layer_close(hp.bf16_numpy(y512), want, oracle, "cfg3 rows 0..511")
+    want16, _, _, _ = oracle.moe_layer(ld, x[:512], oracle.MODE_PARTIALS | oracle.MODE_BF16_WEIGHTS)
+    assert_layer_close(hp.bf16_numpy(y512), want16, oracle, "cfg3 rows 0..511 vs bf16 weights",
+                       elementwise_tol=LAYER_ELEMENTWISE_TOL)
     # scattered rows of the full batch against the oracle
     pick = np.arange(0, 4096, 64)
     want_pick, _, _, _ = oracle.moe_layer(ld, x[pick], oracle.MODE_PARTIALS)

@@ -117,8 +117,10 @@ def test_layout_json_has_the_reference_keys():
     doc = json.loads(gturbo.layout_json(2, 4, lay))
     assert doc["expertStride"] == 3_358_720 and doc["numLayers"] == 2 and doc["expertsPerLayer"] == 4
     e1 = doc["layers"][1]["experts"][1]
-    assert doc["layers"][1]["file"] == "packed_experts/layer_01.bin"
-    assert e1["offset"] == 3_358_720 and e1["size"] == 3_345_408
+    # the file is a basename and an expert's size is the stride
+    # (Sources/ANEFieldfareImportedFormat/GTurboPackedExpertsLayoutV1.swift:89,127-131)
+    assert doc["layers"][1]["file"] == "layer_01.bin"
+    assert e1["offset"] == 3_358_720 and e1["size"] == 3_358_720 and e1["expert"] == 1
     assert set(e1["tensors"]) == {"gate", "gate_scales", "gate_biases", "up", "up_scales",
                                   "up_biases", "down", "down_scales", "down_biases"}
     assert e1["tensors"]["down"] == {"offset": 2_230_272, "size": 991_232, "dtype": "U32",

@@ -336,6 +336,35 @@ def test_down_shift_scales_the_layer_output_exactly(oracle):
     assert np.array_equal(oracle.bf16_to_float(ya), oracle.bf16_to_float(yb) * np.float32(32.0))
 
 
+def test_bf16_weight_mode_multiplies_the_rounded_weights(oracle):
+    """FFO_MODE_BF16_WEIGHTS = the same layer with every weight rounded once to bf16 (what
+    ffo_dequant_int4_bf16 returns and the tensor-core prefill path multiplies): checked against a
+    float64 product with those weights, and against the fp32-weight layer, from which it differs by
+    the weights' rounding only (~2^-9 relative per weight)."""
+    L = workload.make_layer(0x16B, 0, experts=8, d=128, f=64, sharedF=128, topK=4)
+    ld = oracle_layer(oracle, L)
+    x = workload.make_tokens(0x16B, "x", 6, 128)
+    xf = synth.bf16_to_float(x).astype(np.float64)
+    got = oracle.bf16_to_float(oracle.shared_ffn(ld, x, bf16_weights=True)).astype(np.float64)
+    mats = {}
+    for role in gturbo.ROLES:
+        w, s, b = gturbo.sub_tensor(L.sharedBlob, L.sharedLayout, role)
+        rows, cols = L.sharedLayout.matrix_shape(role)
+        mats[role] = synth.bf16_to_float(oracle.dequant_int4(
+            np.ascontiguousarray(w), np.ascontiguousarray(s), np.ascontiguousarray(b), rows, cols,
+            bf16=True)).astype(np.float64)
+    g, u = _bf16_round64(xf @ mats["gate"].T), _bf16_round64(xf @ mats["up"].T)
+    act = _bf16_round64(0.5 * g * (1.0 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) * u)
+    want = act @ mats["down"].T
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 3e-3  # bf16 output rounding
+    y32, _, ids32, _ = oracle.moe_layer(ld, x, oracle.MODE_PARTIALS)
+    y16, _, ids16, _ = oracle.moe_layer(ld, x, oracle.MODE_PARTIALS | oracle.MODE_BF16_WEIGHTS)
+    assert np.array_equal(ids32, ids16)
+    a, b = oracle.bf16_to_float(y32).astype(np.float64), oracle.bf16_to_float(y16).astype(np.float64)
+    rel = np.linalg.norm(a - b) / np.linalg.norm(a)
+    assert 1e-4 < rel < 1e-2, rel
+
+
 def test_golden_fixture(oracle):
     """Committed oracle outputs for a tiny seeded layer (tests/golden/make_golden.py): guards the
     oracle itself against drift.  The reference holds no golden vectors for this path."""
