@@ -87,6 +87,7 @@ SIGNATURES = {
     "ff_moe_verify": (c_bool, [c_void_p, c_uint32, _P, c_uint32, c_uint32, _P, _P, _P, _ERR]),
     "ff_moe_prefill": (c_bool, [c_void_p, c_uint32, _P, c_uint32, c_uint32, _P, _P, _P, _ERR]),
     "ff_moe_reduce": (c_bool, [c_void_p, _P, _P, _P, _P, c_uint32, _P, _ERR]),
+    "ff_moe_reduce_indexed": (c_bool, [c_void_p, _P, _P, _P, _P, _P, c_uint32, _P, _ERR]),
     "ff_shared_ffn": (c_bool, [c_void_p, c_uint32, _P, c_uint32, c_uint32, _P, _P, _ERR]),
     "ff_shared_ffn_noalloc": (c_bool, [POINTER(FFProjection), POINTER(FFProjection),
                                        POINTER(FFProjection), _P, c_uint32, c_uint32, _P, c_uint32,

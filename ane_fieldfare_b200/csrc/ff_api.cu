@@ -152,6 +152,20 @@ bool ff_moe_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *wei
     return launch_reduce(ctx, partials, weights, residual, y, tokens, c.stream, error);
 }
 
+bool ff_moe_reduce_indexed(FFContext *ctx, const uint16_t *partials, const uint32_t *rowIndex,
+                           const uint16_t *weights, const uint16_t *residual, uint16_t *y, uint32_t tokens,
+                           void *stream, const char **error) {
+    Call c;
+    if (!begin(ctx, 0, stream, error, &c)) return false;
+    if (!partials || !rowIndex || !weights || !y) return fail(error, "null argument");
+    if (tokens > ctx->cfg.maxTokens) return fail(error, "rows exceed the context's maxTokens");
+    if ((reinterpret_cast<uintptr_t>(partials) & 3u) || (reinterpret_cast<uintptr_t>(y) & 3u) ||
+        (reinterpret_cast<uintptr_t>(residual) & 3u) || (reinterpret_cast<uintptr_t>(rowIndex) & 3u) ||
+        (reinterpret_cast<uintptr_t>(weights) & 1u) || ctx->cfg.d % 2)
+        return fail(error, "partials, residual, output rows and the row index must be 4-byte aligned");
+    return launch_reduce(ctx, partials, weights, residual, y, tokens, c.stream, error, rowIndex);
+}
+
 bool ff_shared_ffn(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t xStride,
                    uint32_t tokens, uint16_t *y, void *stream, const char **error) {
     Call c;

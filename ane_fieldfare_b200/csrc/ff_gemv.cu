@@ -333,17 +333,20 @@ __global__ void __launch_bounds__(512) k_topk_plan(PlanArgs a) {
 }
 
 // Metal/Prefill/prefill.metal:544-565 plus an optional residual row added after the ranks.
+// rowIndex (optional): the partial row of route (t, r) is row rowIndex[t * K + r] of `partials`
+// instead of row t * K + r — rows that came back from other GPUs in another order are reduced
+// where they lie.
 __global__ void __launch_bounds__(256)
-k_reduce_token_major(const uint16_t *partials, const uint16_t *weights, const uint16_t *residual,
-                     uint16_t *y, int T, int K, int D) {
+k_reduce_token_major(const uint16_t *partials, const uint32_t *rowIndex, const uint16_t *weights,
+                     const uint16_t *residual, uint16_t *y, int T, int K, int D) {
     const int t = blockIdx.y;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
     if (t >= T || d >= D) return;
     float acc0 = 0.0f, acc1 = 0.0f;
     for (int r = 0; r < K; ++r) {
         const float w = bf2f(weights[(size_t)t * K + r]);
-        const uint32_t two =
-            *reinterpret_cast<const uint32_t *>(partials + ((size_t)t * K + r) * D + d);
+        const size_t row = rowIndex ? (size_t)rowIndex[(size_t)t * K + r] : (size_t)t * K + r;
+        const uint32_t two = *reinterpret_cast<const uint32_t *>(partials + row * D + d);
         acc0 = fmaf(w, __uint_as_float(two << 16), acc0);
         acc1 = fmaf(w, __uint_as_float(two & 0xFFFF0000u), acc1);
     }
@@ -609,13 +612,13 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
 
 bool launch_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *weights,
                    const uint16_t *residual, uint16_t *y, uint32_t tokens, cudaStream_t stream,
-                   const char **error) {
+                   const char **error, const uint32_t *rowIndex) {
     if (tokens == 0) return true;
     const int D = (int)ctx->cfg.d;
     dim3 grid((D / 2 + 255) / 256, tokens);
     {
         LaunchScope scope(ctx, stream, "reduce_token_major");
-        k_reduce_token_major<<<grid, 256, 0, stream>>>(partials, weights, residual, y, (int)tokens,
+        k_reduce_token_major<<<grid, 256, 0, stream>>>(partials, rowIndex, weights, residual, y, (int)tokens,
                                                        (int)ctx->cfg.topK, D);
     }
     FF_CUDA_OK(cudaGetLastError(), error);

@@ -213,7 +213,7 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
                         cudaStream_t stream, const char **error);
 bool launch_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *weights,
                    const uint16_t *residual, uint16_t *y, uint32_t tokens, cudaStream_t stream,
-                   const char **error);
+                   const char **error, const uint32_t *rowIndex = nullptr);
 bool launch_gemv_rows(FFContext *ctx, const FFProjection &p, const uint16_t *x, uint32_t xStride,
                       uint32_t rows, uint16_t *y, uint32_t yStride, cudaStream_t stream,
                       const char **error);

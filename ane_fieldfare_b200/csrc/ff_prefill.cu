@@ -43,34 +43,27 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 
 // ---- router for many rows ------------------------------------------------------------------
 
-// The reduction order of a logit is part of the contract (top-K indices are compared for equality
-// with the CPU oracle and with the one-row kernels): 32 partial sums, partial l chaining fmaf over
-// elements [256 i + 8 l, +8) for i = 0, 1, ... in increasing index; the partials added by an xor
-// butterfly (16, 8, 4, 2, 1); then the logit bias.  Nothing in that order says which thread holds
-// which partial, so here a THREAD owns an expert and keeps all 32 partials of that expert for four
-// tokens in registers (as two packed fp32 pairs each, advanced by fma.rn.f32x2 = two independent
-// fp32 FMAs): the token's inputs are then the same for all lanes of a warp (one broadcast read from
-// shared memory serves 32 experts) and the expert's weights are read once per four tokens.  The
-// butterfly becomes additions inside the thread, in the butterfly's own order.
-//
-// A CTA is four warps = sixteen tokens.  The router matrix streams through shared memory in blocks
-// of 32 experts x 256 inputs (two buffers, one bulk copy per expert row piece, completion on an
-// mbarrier) that all four warps use; each warp turns its four tokens' 256 inputs of the block into
-// fp32 pairs in its own corner of shared memory (times the router's per-input scale, an exact
-// product of two bf16 values).
+// One warp per token.  The token's (scaled) inputs sit in shared memory as fp32; for every
+// expert the warp forms the logit in the order the decode router uses (lane l chains fmaf over
+// [256 i + 8 l, +8), butterfly 16..1, then the logit bias), so logits and indices are bitwise
+// those of the single-row kernel.  Then the warp-wide top-K.
 constexpr int kRouterWarps = 4;
-constexpr int kRouterTokens = 4;                 // tokens per warp: two packed pairs
-constexpr int kRouterBlock = 256;                // inputs per staged block = one step of every partial
-constexpr int kRouterGroup = 32;                 // experts per block = lanes of a warp
-constexpr uint32_t kRouterRowPitch = kRouterBlock * 2 + 16;  // bytes between expert rows of a block: 16-byte reads of 8 lanes fall into different banks
 
+// Each warp owns kRouterTokens tokens and walks the experts eight at a time with a register tile
+// of kRouterTokens x 8 running sums, so a router row (read from the CTA's slice buffer) feeds 4 tokens and an
+// input chunk read from shared memory feeds 8 experts.  Per (token, expert) the chain is exactly
+// the single-row kernel's: lane l, chunks i ascending, elements ascending, then the butterfly.
+constexpr int kRouterTokens = 4;   // tokens per warp
+constexpr int kRouterExperts = 8;  // experts per register tile
+
+// Router rows of a slice of eight experts come into shared memory by one bulk copy (two buffers,
+// completion on an mbarrier each) and feed every warp of the CTA: the router matrix is read once
+// per 16 tokens instead of once per 4.
 __device__ __forceinline__ void rt_bar_init(uint32_t bar) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void rt_expect(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void rt_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
@@ -88,161 +81,124 @@ __device__ __forceinline__ bool rt_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ uint64_t rt_add2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
 
-struct RouterSmem {
-    static constexpr uint32_t kBlockBytes = kRouterGroup * kRouterRowPitch;         // one buffer of router rows
-    static constexpr uint32_t kPairBytes = 32 * 8 * 2 * 8;                          // a warp's inputs of a block as fp32 pairs
-    static constexpr uint32_t kLogitBytes = kRouterTokens * kMaxExperts * 4;        // a warp's logits
-    static constexpr uint32_t kTotal = 2 * kBlockBytes + kRouterWarps * (kPairBytes + kLogitBytes);
-};
-
-__global__ void __launch_bounds__(kRouterWarps * 32, 3)
+__global__ void __launch_bounds__(kRouterWarps * 32)
 k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const uint16_t *gain,
               const uint16_t *x, uint32_t xStride, int T, int E, int D, int K, uint32_t *ids,
               uint16_t *weights, float *logitsOut, uint32_t *errorFlag) {
     extern __shared__ __align__(128) uint8_t rsmRaw[];
-    __shared__ __align__(8) uint64_t blockBar[2];
+    __shared__ __align__(8) uint64_t sliceBar[2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint8_t *pairsRaw = rsmRaw + 2 * RouterSmem::kBlockBytes + warp * RouterSmem::kPairBytes;
-    float *lg = reinterpret_cast<float *>(rsmRaw + 2 * RouterSmem::kBlockBytes + kRouterWarps * RouterSmem::kPairBytes +
-                                          warp * RouterSmem::kLogitBytes);
-    const uint32_t barBase = (uint32_t)__cvta_generic_to_shared(&blockBar[0]);
-    const uint32_t bufBase = (uint32_t)__cvta_generic_to_shared(rsmRaw);
-    const int steps = (D + kRouterBlock - 1) / kRouterBlock;      // blocks along the inputs
-    const int groups = (E + kRouterGroup - 1) / kRouterGroup;     // blocks along the experts
-    const int nBlocks = steps * groups;
-    // block n = (expert group n / steps, input step n % steps), in buffer n & 1
-    auto request = [&](int n) {  // called by warp 0: lane e copies its expert's piece of the block
-        const int eg = n / steps, i = n - eg * steps;
-        const uint32_t bytes = (uint32_t)min(kRouterBlock, D - i * kRouterBlock) * 2u;
-        const uint32_t bar = barBase + 8u * (uint32_t)(n & 1);
-        if (lane == 0) rt_expect(bar, bytes * kRouterGroup);
-        __syncwarp();
-        const int e = min(eg * kRouterGroup + lane, E - 1);  // lanes past the last expert copy its row again
-        rt_copy(bufBase + (uint32_t)(n & 1) * RouterSmem::kBlockBytes + (uint32_t)lane * kRouterRowPitch,
-                W + (size_t)e * D + (size_t)i * kRouterBlock, bytes, bar);
+    // two slice buffers (kRouterExperts rows each), then per warp: kRouterTokens input rows as bf16
+    // and kRouterTokens x kMaxExperts logits
+    const size_t sliceBytes = (size_t)kRouterExperts * D * 2;
+    const size_t perWarp = (size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4;
+    uint8_t *warpBase = rsmRaw + 2 * sliceBytes + warp * perWarp;
+    uint16_t *xs = reinterpret_cast<uint16_t *>(warpBase);
+    float *lg = reinterpret_cast<float *>(warpBase + (size_t)kRouterTokens * D * 2);
+    const uint32_t barBase = (uint32_t)__cvta_generic_to_shared(&sliceBar[0]);
+    auto barOf = [&](int slice) { return barBase + 8u * (uint32_t)(slice & 1); };
+    const uint32_t bufAddr = (uint32_t)__cvta_generic_to_shared(rsmRaw);
+    const int nSlices = (E + kRouterExperts - 1) / kRouterExperts;
+    auto request = [&](int slice) {
+        const int rows = min(kRouterExperts, E - slice * kRouterExperts);
+        rt_copy(bufAddr + (uint32_t)((slice & 1) * sliceBytes), W + (size_t)slice * kRouterExperts * D,
+                (uint32_t)((size_t)rows * D * 2), barOf(slice));
     };
     if (threadIdx.x == 0) {
-        rt_bar_init(barBase);
-        rt_bar_init(barBase + 8u);
+        rt_bar_init(barOf(0));
+        rt_bar_init(barOf(1));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (warp == 0) {
         request(0);
-        if (nBlocks > 1) request(1);
+        if (nSlices > 1) request(1);
     }
     const int t0 = (blockIdx.x * kRouterWarps + warp) * kRouterTokens;
     const int nTok = max(0, min(kRouterTokens, T - t0));
-    // this lane's run (eight inputs) of the four tokens for input step i: raw bf16 and the scale run
-    const uint16_t *xr[kRouterTokens];
-#pragma unroll
-    for (int tt = 0; tt < kRouterTokens; ++tt) xr[tt] = x + (size_t)min(t0 + tt, T - 1) * xStride;
-    uint4 rawX[kRouterTokens], rawS;
-    auto fetch_inputs = [&](int i) {
-        const int base = i * kRouterBlock + 8 * lane;
-        rawS = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
-#pragma unroll
-        for (int tt = 0; tt < kRouterTokens; ++tt) rawX[tt] = make_uint4(0, 0, 0, 0);
-        if (base < D) {
-#pragma unroll
-            for (int tt = 0; tt < kRouterTokens; ++tt) rawX[tt] = __ldg(reinterpret_cast<const uint4 *>(xr[tt] + base));
-            if (scale) rawS = __ldg(reinterpret_cast<const uint4 *>(scale + base));
-        }
-    };
-    fetch_inputs(0);
-
-    uint64_t acc[32][kRouterTokens / 2];  // [partial][token pair]
-    for (int n = 0; n < nBlocks; ++n) {
-        const int eg = n / steps, i = n - eg * steps;
-        if (i == 0) {
-#pragma unroll
-            for (int l = 0; l < 32; ++l)
-#pragma unroll
-                for (int p = 0; p < kRouterTokens / 2; ++p) acc[l][p] = 0ull;
-        }
-        // ---- the warp's inputs of this step as fp32 pairs: run `lane`, elements 0..7, pairs (t0,t1) (t2,t3)
-        __syncwarp();  // the previous block's reads of the pair area are done
-        {
-            const uint32_t xs[kRouterTokens][4] = {{rawX[0].x, rawX[0].y, rawX[0].z, rawX[0].w},
-                                                   {rawX[1].x, rawX[1].y, rawX[1].z, rawX[1].w},
-                                                   {rawX[2].x, rawX[2].y, rawX[2].z, rawX[2].w},
-                                                   {rawX[3].x, rawX[3].y, rawX[3].z, rawX[3].w}};
-            const uint32_t ss[4] = {rawS.x, rawS.y, rawS.z, rawS.w};
-            uint4 *dst = reinterpret_cast<uint4 *>(pairsRaw + lane * 128);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float lo[kRouterTokens], hi[kRouterTokens];
-#pragma unroll
-                for (int tt = 0; tt < kRouterTokens; ++tt) {
-                    lo[tt] = __uint_as_float(xs[tt][k] << 16);
-                    hi[tt] = __uint_as_float(xs[tt][k] & 0xFFFF0000u);
-                    if (scale) {
-                        lo[tt] = lo[tt] * __uint_as_float(ss[k] << 16);
-                        hi[tt] = hi[tt] * __uint_as_float(ss[k] & 0xFFFF0000u);
-                    }
-                }
-                // element 2k: pairs (t0,t1), (t2,t3); element 2k+1 likewise
-                dst[2 * k] = make_uint4(__float_as_uint(lo[0]), __float_as_uint(lo[1]), __float_as_uint(lo[2]), __float_as_uint(lo[3]));
-                dst[2 * k + 1] = make_uint4(__float_as_uint(hi[0]), __float_as_uint(hi[1]), __float_as_uint(hi[2]), __float_as_uint(hi[3]));
-            }
-        }
-        if (n + 1 < nBlocks) fetch_inputs((n + 1) % steps);  // in flight under this block's arithmetic
-        __syncwarp();
+    for (int tt = 0; tt < kRouterTokens; ++tt) {
+        const uint16_t *xr = x + (size_t)min(t0 + min(tt, max(nTok, 1) - 1), T - 1) * xStride;
+        for (int i = lane * 8; i < D; i += 256)
+            *reinterpret_cast<uint4 *>(xs + (size_t)tt * D + i) = *reinterpret_cast<const uint4 *>(xr + i);
+    }
+    __syncthreads();
+    for (int e0 = 0; e0 < E; e0 += kRouterExperts) {
+        const int slice = e0 / kRouterExperts;
         {
             bool done = false;
-            for (uint32_t spin = 0; spin < (1u << 22) && !done; ++spin) done = rt_try_wait(barBase + 8u * (uint32_t)(n & 1), (uint32_t)(n >> 1) & 1u);
+            for (uint32_t spin = 0; spin < (1u << 22) && !done; ++spin) done = rt_try_wait(barOf(slice), (uint32_t)(slice >> 1) & 1u);
             if (!done && lane == 0) atomicExch(errorFlag, 11u);
         }
-        const uint8_t *wrow = rsmRaw + (size_t)(n & 1) * RouterSmem::kBlockBytes + (size_t)lane * kRouterRowPitch;
-        const int runs = min(32, (D - i * kRouterBlock + 7) >> 3);
+        const uint16_t *Ws = reinterpret_cast<const uint16_t *>(rsmRaw + (size_t)(slice & 1) * sliceBytes);
+        // running sums of two tokens share one packed fp32 pair (fma.rn.f32x2 = two independent fp32
+        // FMAs), so every (token, expert) chain is the scalar chain bit for bit at half the issue
+        uint64_t acc[kRouterTokens / 2][kRouterExperts];
 #pragma unroll
-        for (int l = 0; l < 32; ++l) {
-            if (l < runs) {
-                const uint4 wv = *reinterpret_cast<const uint4 *>(wrow + l * 16);
+        for (int tp = 0; tp < kRouterTokens / 2; ++tp)
+#pragma unroll
+            for (int ee = 0; ee < kRouterExperts; ++ee) acc[tp][ee] = 0ull;
+        for (int base = 8 * lane; base < D; base += 256) {
+            uint64_t xv[kRouterTokens / 2][8];
+            uint4 sv = make_uint4(0, 0, 0, 0);
+            if (scale) sv = *reinterpret_cast<const uint4 *>(scale + base);
+            const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int tp = 0; tp < kRouterTokens / 2; ++tp) {
+                const uint4 rawA = *reinterpret_cast<const uint4 *>(xs + (size_t)(2 * tp) * D + base);
+                const uint4 rawB = *reinterpret_cast<const uint4 *>(xs + (size_t)(2 * tp + 1) * D + base);
+                const uint32_t xa[4] = {rawA.x, rawA.y, rawA.z, rawA.w};
+                const uint32_t xb[4] = {rawB.x, rawB.y, rawB.z, rawB.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float a0 = __uint_as_float(xa[k] << 16), a1 = __uint_as_float(xa[k] & 0xFFFF0000u);
+                    float b0 = __uint_as_float(xb[k] << 16), b1 = __uint_as_float(xb[k] & 0xFFFF0000u);
+                    if (scale) {
+                        const float s0 = __uint_as_float(ss[k] << 16), s1 = __uint_as_float(ss[k] & 0xFFFF0000u);
+                        a0 = a0 * s0;
+                        a1 = a1 * s1;
+                        b0 = b0 * s0;
+                        b1 = b1 * s1;
+                    }
+                    xv[tp][2 * k] = pack2(a0, b0);
+                    xv[tp][2 * k + 1] = pack2(a1, b1);
+                }
+            }
+#pragma unroll
+            for (int ee = 0; ee < kRouterExperts; ++ee) {
+                const int er = min(ee, E - 1 - e0);  // row of the slice (the last slice may be short)
+                const uint4 wv = *reinterpret_cast<const uint4 *>(Ws + (size_t)er * D + base);
                 const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-                const uint4 *xp = reinterpret_cast<const uint4 *>(pairsRaw + l * 128);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const float w0 = __uint_as_float(ww[k] << 16), w1 = __uint_as_float(ww[k] & 0xFFFF0000u);
                     const uint64_t w00 = pack2(w0, w0), w11 = pack2(w1, w1);
-                    const uint4 e0 = xp[2 * k], e1 = xp[2 * k + 1];
-                    acc[l][0] = fma2(w00, pack2(__uint_as_float(e0.x), __uint_as_float(e0.y)), acc[l][0]);
-                    acc[l][1] = fma2(w00, pack2(__uint_as_float(e0.z), __uint_as_float(e0.w)), acc[l][1]);
-                    acc[l][0] = fma2(w11, pack2(__uint_as_float(e1.x), __uint_as_float(e1.y)), acc[l][0]);
-                    acc[l][1] = fma2(w11, pack2(__uint_as_float(e1.z), __uint_as_float(e1.w)), acc[l][1]);
+#pragma unroll
+                    for (int tp = 0; tp < kRouterTokens / 2; ++tp) {
+                        acc[tp][ee] = fma2(w00, xv[tp][2 * k], acc[tp][ee]);
+                        acc[tp][ee] = fma2(w11, xv[tp][2 * k + 1], acc[tp][ee]);
+                    }
                 }
             }
         }
-        if (i == steps - 1) {
-            // the xor butterfly of the 32 partials, as additions inside the thread in the butterfly's order
 #pragma unroll
-            for (int offset = 16; offset >= 1; offset >>= 1)
+        for (int tp = 0; tp < kRouterTokens / 2; ++tp)
 #pragma unroll
-                for (int l = 0; l < offset; ++l)
+            for (int ee = 0; ee < kRouterExperts; ++ee) {
+                float v0, v1;
+                unpack2(acc[tp][ee], v0, v1);
 #pragma unroll
-                    for (int p = 0; p < kRouterTokens / 2; ++p) acc[l][p] = rt_add2(acc[l][p], acc[l + offset][p]);
-            const int e = eg * kRouterGroup + lane;
-            if (e < E) {
-                const float b = bias ? bias[e] : 0.0f;
-#pragma unroll
-                for (int p = 0; p < kRouterTokens / 2; ++p) {
-                    float v0, v1;
-                    unpack2(acc[0][p], v0, v1);
-                    lg[(2 * p) * kMaxExperts + e] = bias ? v0 + b : v0;
-                    lg[(2 * p + 1) * kMaxExperts + e] = bias ? v1 + b : v1;
+                for (int offset = 16; offset >= 1; offset >>= 1) {
+                    v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, offset);
+                    v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, offset);
+                }
+                const int e = e0 + ee;
+                if (lane == 0 && e < E) {
+                    lg[(2 * tp) * kMaxExperts + e] = bias ? v0 + bias[e] : v0;
+                    lg[(2 * tp + 1) * kMaxExperts + e] = bias ? v1 + bias[e] : v1;
                 }
             }
-        }
-        // every warp is done with this buffer: the block after next may land in it
+        // every warp is done with this buffer: the slice after next may land in it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
-        if (warp == 0 && n + 2 < nBlocks) request(n + 2);
+        if (threadIdx.x == 0 && slice + 2 < nSlices) request(slice + 2);
     }
     __syncwarp();
     for (int tt = 0; tt < nTok; ++tt) {
@@ -257,9 +213,10 @@ bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *
                            uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
                            cudaStream_t stream, const char **error) {
     const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
+    const size_t smem = 2 * (size_t)kRouterExperts * D * 2 +
+                        (size_t)kRouterWarps * ((size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4);
+    if (smem > 225 * 1024) return fail(error, "model width too large for the router's shared memory");
     if (D % 8) return fail(error, "hidden size must be a multiple of 8");
-    if (E > kMaxExperts) return fail(error, "numExperts > 256 is not supported");
-    const size_t smem = RouterSmem::kTotal;
     static KernelSmemMemo memo;
     if (!memo.prepare(k_router_rows, ctx->device, smem, kRouterWarps * 32, nullptr, error)) return false;
     const uint32_t perCta = kRouterWarps * kRouterTokens;

@@ -439,9 +439,16 @@ class PrefillMoE:
 
     def encodeReduceTokenMajor(self, stream, routePartials: torch.Tensor, routeWeights: torch.Tensor,
                                h2: torch.Tensor, queryCount: int,
-                               residual: Optional[torch.Tensor] = None):
-        call("ff_moe_reduce", self.context.handle, _ptr(routePartials), _ptr(routeWeights),
-             _ptr(residual), _ptr(h2), queryCount, _stream(stream))
+                               residual: Optional[torch.Tensor] = None,
+                               rowIndex: Optional[torch.Tensor] = None):
+        """rowIndex (int32 [queryCount*K], optional): where each route's partial row lies in
+        `routePartials`, for rows that are not in (token, rank) order."""
+        if rowIndex is None:
+            call("ff_moe_reduce", self.context.handle, _ptr(routePartials), _ptr(routeWeights),
+                 _ptr(residual), _ptr(h2), queryCount, _stream(stream))
+        else:
+            call("ff_moe_reduce_indexed", self.context.handle, _ptr(routePartials), _ptr(rowIndex),
+                 _ptr(routeWeights), _ptr(residual), _ptr(h2), queryCount, _stream(stream))
 
 
 class CudaRoutedPrefillGuest:

@@ -104,13 +104,47 @@ def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
     return recv
 
 
-def all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group=None, async_op: bool = False):
+def all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group=None, async_op: bool = False,
+                    out: Optional[torch.Tensor] = None):
     """Variable-split all-to-all along dim 0; counts are python lists of row counts.  Returns the
-    received rows, and with async_op the work handle to wait on before using them."""
-    out = torch.empty((int(sum(recv_counts)),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    received rows (in `out` when given), and with async_op the work handle to wait on before using
+    them."""
+    if out is None:
+        out = torch.empty((int(sum(recv_counts)),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
     work = dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_counts),
                                   input_split_sizes=list(send_counts), group=group, async_op=async_op)
     return (out, work) if async_op else out
+
+
+class PeerBuffers:
+    """Two buffers in symmetric memory (every rank's copy is mapped into every other rank of the
+    box) through which dispatch and combine move rows with plain peer stores over NVLink instead of
+    a collective: a rank writes the rows for rank p straight into p's buffer at the offset that the
+    exchanged counts give it, and a barrier across the ranks (signals in symmetric memory, on the
+    stream) says when everybody's rows have landed.  One instance serves every layer of a stack.
+    `available()` is false where symmetric memory cannot be set up (CPU tests, gloo)."""
+
+    def __init__(self, capacity_rows: int, row_elems: int, dtype, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only
+        import torch.distributed._symmetric_memory as symm
+        self.capacity = int(capacity_rows)
+        name = (group if group is not None else dist.group.WORLD).group_name
+        self.recv = symm.empty((self.capacity, row_elems), dtype=dtype, device=device)    # rows for my experts
+        self.back = symm.empty((self.capacity, row_elems), dtype=dtype, device=device)    # partial rows of my tokens
+        self.recv_handle = symm.rendezvous(self.recv, name)
+        self.back_handle = symm.rendezvous(self.back, name)
+        self.shape = (self.capacity, row_elems)
+        self.dtype = dtype
+
+    def peer_recv(self, rank: int) -> torch.Tensor:
+        return self.recv_handle.get_buffer(rank, self.shape, self.dtype)
+
+    def peer_back(self, rank: int) -> torch.Tensor:
+        return self.back_handle.get_buffer(rank, self.shape, self.dtype)
+
+    def barrier(self):
+        self.recv_handle.barrier()
 
 
 class PhaseTimer:
@@ -164,11 +198,14 @@ class ExpertParallelMoE:
 
     `chunks` > 1 cuts the local tokens into that many runs: the dispatch of run i+1 and the combine
     of run i-1 are in flight (on the collective library's stream) while the experts of run i
-    compute.  The result does not depend on `chunks`."""
+    compute.  `peer` (a PeerBuffers) moves the rows by peer stores into symmetric memory instead
+    of the collective.  The result depends on neither.  A `reduce_fn` with the attribute
+    `indexed = True` takes a fourth argument, the int32 row index of every route's partial row, and
+    spares the pass that would put the rows back into (token, rank) order."""
 
     def __init__(self, experts: int, top_k: int, router_fn: Callable, shared_fn: Callable,
                  experts_fn: Callable, reduce_fn: Callable, group=None,
-                 placement: Optional[Placement] = None, chunks: int = 1):
+                 placement: Optional[Placement] = None, chunks: int = 1, peer: "Optional[PeerBuffers]" = None):
         self.group = group
         self.placement = placement
         self.world = dist.get_world_size(group)
@@ -180,12 +217,15 @@ class ExpertParallelMoE:
         self.router_fn, self.shared_fn = router_fn, shared_fn
         self.experts_fn, self.reduce_fn = experts_fn, reduce_fn
         self.chunks = max(1, int(chunks))
+        self.peer = peer  # PeerBuffers: exchange rows by peer stores instead of the collective
         self.last_recv_rows = 0
         self.last_expert_counts = None  # routes per (global) expert of the last forward, on request
         self.count_experts = False
         self.timer = _NoTimer()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.peer is not None:
+            return self._forward_peer(x)
         T, K, W = x.shape[0], self.top_k, self.world
         tm = self.timer
         with tm.phase("router", x):
@@ -204,6 +244,7 @@ class ExpertParallelMoE:
         send_lists, recv_lists = both
         self.last_recv_rows = int(sum(sum(r) for r in recv_lists))
         on_gpu = x.is_cuda
+        indexed = bool(getattr(self.reduce_fn, "indexed", False))
 
         def dispatch(c):
             p = plans[c]
@@ -221,6 +262,9 @@ class ExpertParallelMoE:
                 return rows, local
             return pending
 
+        # the partial rows come back grouped by chunk and, inside a chunk, in the order they were sent
+        # (by destination); `partials` receives them as they lie and `row_index` says where the row of
+        # route (t, k) is — or, for a reduce that wants (token, rank) order, they are put back first
         partials = torch.empty((T * K,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         with tm.phase("dispatch", x):
             pending = dispatch(0)
@@ -237,16 +281,81 @@ class ExpertParallelMoE:
             with tm.phase("experts", x):
                 partial_rows = self.experts_fn(rows, local)
             with tm.phase("combine", x):
+                out = partials[bounds[c] * K:bounds[c + 1] * K] if indexed else None
                 backs.append(all_to_all_rows(partial_rows, recv_lists[c], send_lists[c], self.group,
-                                             async_op=on_gpu))
+                                             async_op=on_gpu, out=out))
         with tm.phase("combine", x):
+            row_index = torch.empty(T * K, dtype=torch.int32, device=x.device) if indexed else None
             for c, back in enumerate(backs):
                 if on_gpu:
                     back, work = back
                     work.wait()
-                partials[bounds[c] * K + plans[c].order.to(x.device)] = back
+                order = plans[c].order.to(x.device)
+                if indexed:
+                    n = order.numel()
+                    row_index[bounds[c] * K + order] = torch.arange(bounds[c] * K, bounds[c] * K + n, dtype=torch.int32,
+                                                                    device=x.device)
+                else:
+                    partials[bounds[c] * K + order] = back
         with tm.phase("reduce", x):
+            if indexed:
+                return self.reduce_fn(partials, weights, residual, row_index)
             return self.reduce_fn(partials, weights, residual)
+
+    def _forward_peer(self, x: torch.Tensor) -> torch.Tensor:
+        """Dispatch and combine as peer stores into symmetric memory (see PeerBuffers): the routed
+        rows are gathered straight into the destination ranks' buffers, the partial rows are copied
+        straight into their home ranks' buffers, and the reduce reads them where they lie."""
+        T, K, W = x.shape[0], self.top_k, self.world
+        tm, pb = self.timer, self.peer
+        with tm.phase("router", x):
+            ids, weights = self.router_fn(x)
+        if self.count_experts:
+            self.last_expert_counts = torch.bincount(ids.reshape(-1).to(torch.int64), minlength=self.experts)
+        with tm.phase("plan", x):
+            plan = dispatch_plan(ids, self.experts_per_rank, W, self.placement)
+            table = torch.empty((W, W), dtype=torch.int64, device=x.device)    # [source][destination]
+            dist.all_gather_into_tensor(table, plan.send_counts.to(x.device), group=self.group)
+            counts = table.tolist()                                             # the step's only host read
+            order = plan.order.to(x.device)
+            row_index = torch.empty(T * K, dtype=torch.int32, device=x.device)
+            row_index[order] = torch.arange(T * K, dtype=torch.int32, device=x.device)
+        me = self.rank
+        recv_total = sum(counts[s][me] for s in range(W))
+        if max(recv_total, T * K) > pb.capacity:
+            raise ValueError(f"{recv_total} rows exceed the peer buffers' capacity {pb.capacity}")
+        self.last_recv_rows = recv_total
+        token = plan.token.to(x.device)
+        local_ids = torch.empty(recv_total, dtype=torch.int32, device=x.device)
+        with tm.phase("dispatch", x):
+            pb.barrier()  # every rank is done with the previous contents of the buffers
+            start = 0
+            for p in range(W):
+                n = counts[me][p]
+                offset = sum(counts[s][p] for s in range(me))
+                if n:
+                    torch.index_select(x, 0, token[start:start + n], out=pb.peer_recv(p)[offset:offset + n])
+                start += n
+            # the local expert ids travel with the collective (4 bytes a row)
+            dist.all_to_all_single(local_ids, plan.local_expert.to(x.device),
+                                   output_split_sizes=[counts[s][me] for s in range(W)],
+                                   input_split_sizes=counts[me], group=self.group)
+            pb.barrier()  # everybody's rows have landed
+        with tm.phase("shared", x):
+            residual = self.shared_fn(x)
+        with tm.phase("experts", x):
+            partial_rows = self.experts_fn(pb.recv[:recv_total], local_ids)
+        with tm.phase("combine", x):
+            start = 0
+            for s in range(W):
+                n = counts[s][me]
+                offset = sum(counts[s][p] for p in range(me))  # where my block starts in s's send order
+                if n:
+                    pb.peer_back(s)[offset:offset + n].copy_(partial_rows[start:start + n])
+                start += n
+            pb.barrier()  # my tokens' partial rows have landed
+        with tm.phase("reduce", x):
+            return self.reduce_fn(pb.back[:T * K], weights, residual, row_index)
 
 
 def cuda_layer_fns(home_ctx, expert_ctx, layer: int, expert_layer: Optional[int] = None):
@@ -286,10 +395,12 @@ def cuda_layer_fns(home_ctx, expert_ctx, layer: int, expert_layer: Optional[int]
                                          rows.shape[0])
         return out
 
-    def reduce_fn(partials, weights, residual):
+    def reduce_fn(partials, weights, residual, row_index=None):
         t = weights.shape[0]
         y = torch.empty((t, d), dtype=torch.bfloat16, device=partials.device)
-        reduce.encodeReduceTokenMajor(None, partials, weights, y, t, residual=residual)
+        reduce.encodeReduceTokenMajor(None, partials, weights, y, t, residual=residual, rowIndex=row_index)
         return y
+
+    reduce_fn.indexed = True
 
     return router_fn, shared_fn, experts_fn, reduce_fn

@@ -324,12 +324,149 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             local.loadLayer(slot, np.ascontiguousarray(L.blobs[mine]), L.layout.stride, L.layout.offsets,
                             expertCount=epr)
 
-    def make_blocks(placements, chunks):
+    def make_blocks(placements, chunks, peer=None):
         out = []
         for slot in range(layers):
             # the home context is indexed by the distinct layer, the expert context by the stack's slot
             fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
-            out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks))
+            out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks, peer=peer))
+        return out
+
+    x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
+
+    def run_stack(blocks):
+        x = x0
+        for block in blocks:
+            x = block.forward(home.rmsnorm(x, None, 1e-6))
+        return x
+
+    # Pass 1, contiguous placement: the stack's outputs do not depend on where an expert lives, so
+    # this pass measures how many routes every expert of every layer receives (summed over the
+    # ranks).  Experts are then placed so that every rank receives about the same number of rows
+    # (the blob layout is untouched: a rank loads the blobs of its experts).
+    contiguous = [parallel.contiguous_placement(E, world)] * layers
+    load_experts(contiguous)
+    blocks = make_blocks(contiguous, 1)
+    for block in blocks:
+        block.count_experts = True
+    run_stack(blocks)
+    counts = torch.stack([block.last_expert_counts for block in blocks]).to(torch.float64)
+    dist.all_reduce(counts)
+    placements = [parallel.balanced_placement((counts[slot] + 0.5).tolist(), world) for slot in range(layers)]
+    load_experts(placements)
+    # two ways to move the rows: the collective (tokens in chunks whose exchanges overlap the GEMMs)
+    # and peer stores into symmetric memory; both are checked and timed, the faster one is the line
+    variants = {"nccl_all_to_all": make_blocks(placements, args.ep_chunks)}
+    peer_note = None
+    if args.ep_comm in ("peer", "both"):
+        ok = torch.ones(1, dtype=torch.float64, device=device)
+        try:
+            buffers = parallel.PeerBuffers(capacity, D, torch.bfloat16, device)
+        except Exception as exc:  # symmetric memory not available on this box
+            peer_note = f"{type(exc).__name__}: {exc}"[:200]
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 1.0:
+            variants["peer_stores"] = make_blocks(placements, 1, peer=buffers)
+        if args.ep_comm == "peer" and "peer_stores" in variants:
+            del variants["nccl_all_to_all"]
+
+    # the first layer's output for the first rows against ff_moe_layer on one context that holds all
+    # experts of that layer: the same bits
+    check_rows = min(256, tokens_local)
+    full = hotpath.HotpathContext(layers=1, experts=E, d=D, f=F, sharedF=FS, topK=K, maxTokens=tokens_local,
+                                  device=local_rank)
+    L0 = host_layers[0]
+    workload.load_layer(full, 0, L0)
+    full.loadRouter(0, L0.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, "stack.zipf.0"))
+    normed = home.rmsnorm(x0, None, 1e-6)
+    y_one = full.moeLayer(0, normed)
+    same = torch.ones(1, dtype=torch.float64, device=device)
+    for blocks in variants.values():
+        y_ep = blocks[0].forward(normed)
+        torch.cuda.synchronize()
+        if not torch.equal(y_ep[:check_rows], y_one[:check_rows]):
+            same.zero_()
+    full.close()
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+
+    steps = 3
+    results = {}
+    for name, blocks in variants.items():
+        for _ in range(2):
+            run_stack(blocks)
+        torch.cuda.synchronize()
+        dist.barrier()
+        per = time_replays(torch, torch.cuda.current_stream(), lambda: run_stack(blocks), steps)
+        t = torch.tensor([float(np.median(per))], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        # one more pass with CUDA events around the phases of every layer
+        timer = parallel.PhaseTimer()
+        for block in blocks:
+            block.timer = timer
+        y = run_stack(blocks)
+        phases = timer.totals()
+        names = sorted(phases)
+        pt = torch.tensor([phases[n] for n in names], dtype=torch.float64, device=device)
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        results[name] = {"ms_per_stack": float(t.item()),
+                         "phase_ms_per_stack_max_over_ranks": {n: round(float(v), 3) for n, v in zip(names, pt.tolist())}}
+    best = min(results, key=lambda n: results[n]["ms_per_stack"])
+    ms = results[best]["ms_per_stack"]
+    blocks = variants[best]
+    recv = torch.tensor([[float(b.last_recv_rows) for b in blocks]], dtype=torch.float64, device=device)
+    rows = [torch.zeros_like(recv) for _ in range(world)]
+    dist.all_gather(rows, recv)
+    rows = torch.cat(rows).cpu().numpy()  # [world, layers]
+    finite = bool(torch.isfinite(y.float()).all().item())
+    err = ctx.info().deviceErrorFlag
+    resident = ctx.info().weightBytesResident
+    ctx.close()
+    peak = measured_bf16_peak()
+    tf = stack_flops(layers) / (ms * 1e-3) / 1e12
+    return {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens", "gpus": 1,
+            "path": "ff_moe_stack on one context (no expert parallelism, no collective)",
+            "tokens_per_s": STACK_TOKENS / (ms * 1e-3), "ms_per_stack": ms, "steps": steps,
+            "timed_region": spread(per, 1), "tflops": tf,
+            "frac_of_measured_bf16_sustained": tf / peak["tflops"], "frac_of_measured_bf16_burst": tf / peak["burst_tflops"],
+            "weight_bytes_resident": int(resident), "output_finite": finite, "device_error_flag": int(err),
+            "kernel_ms_per_stack": {name: round(t, 3) for name, (n, t) in sorted(trace.items())}}
+
+
+def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank, world, device, args):
+    """Benchmark configuration 4: a 30-layer stack of MoE blocks (RMSNorm between layers, no
+    attention), 32768 prefill tokens.  One GPU: the library's ff_moe_stack.  Several GPUs: experts
+    sharded over the ranks with an NCCL all-to-all dispatch and combine per layer.  All 30 layer
+    slots are resident (13.2 GB over the box); their bytes repeat a few distinct seeded layers,
+    which does not change the work."""
+    from ane_fieldfare_b200 import parallel, synth
+    if world == 1:
+        return measure_stack_single(torch, hotpath, workload, host_layers, local_rank, device, args)
+    layers = args.stack_layers
+    tokens_local = STACK_TOKENS // world
+    epr = E // world
+    capacity = min(STACK_TOKENS * K, 4 * tokens_local * K)
+    home = hotpath.HotpathContext(layers=len(host_layers), experts=E, d=D, f=F, sharedF=FS, topK=K,
+                                  maxTokens=tokens_local, device=local_rank)
+    local = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=1,
+                                   maxTokens=capacity, device=local_rank)
+    for i, L in enumerate(host_layers):
+        home.loadShared(i, *L.shared_projections())
+        home.loadRouter(i, L.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}"))
+
+    def load_experts(placements):
+        for slot in range(layers):
+            L = host_layers[slot % len(host_layers)]
+            mine = placements[slot].experts_of(rank)
+            local.loadLayer(slot, np.ascontiguousarray(L.blobs[mine]), L.layout.stride, L.layout.offsets,
+                            expertCount=epr)
+
+    def make_blocks(placements, chunks, peer=None):
+        out = []
+        for slot in range(layers):
+            # the home context is indexed by the distinct layer, the expert context by the stack's slot
+            fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
+            out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks, peer=peer))
         return out
 
     x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
@@ -407,12 +544,15 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             "ep_matches_single_gpu": bool(same.item() == 1.0),
             "ep_check": f"layer 0, first {check_rows} local rows of every rank, bitwise against ff_moe_layer "
                         "on one context holding all 128 experts",
-            "phase_ms_per_stack_max_over_ranks": {n: round(float(v), 3) for n, v in zip(names, pt.tolist())},
+            "exchange": best, "exchanges_measured": results, "peer_stores_unavailable": peer_note,
             "rows_received_per_rank_by_layer": rows.astype(np.int64).T.tolist(),
             "rows_received_max_over_mean": float((rows.max(axis=0) / rows.mean(axis=0)).mean()),
             "chunks_per_layer": args.ep_chunks,
             "output_finite": finite, "device_error_flag": int(err),
-            "collective": "NCCL all_to_all_single (dispatch + combine per layer and chunk, asynchronous to the GEMMs)",
+            "exchange_kinds": {"nccl_all_to_all": "all_to_all_single for dispatch and combine of every layer and chunk, "
+                                                  "asynchronous to the GEMMs",
+                               "peer_stores": "rows gathered and copied straight into the destination rank's buffer in "
+                                              "symmetric memory over NVLink, a barrier across the ranks after each"},
             "placement": "experts assigned to ranks by greedy balancing of the routes each expert of each layer "
                          "received in a first pass of the same stack"}
 
@@ -501,15 +641,17 @@ def run_ours(args):
             return float(t.item())
         return ms
 
-    def measure_graph(step, group, warm_steps):
+    def measure_graph(step, group, warm_steps, all_ranks=True):
         """Captures `group` consecutive steps as one CUDA graph, replays it until the timed region
         has run for MIN_TIMED_SECONDS, and returns (median ms of one replay as the max over ranks,
-        spread record, kernels per step, clock record)."""
+        spread record, kernels per step, clock record).  all_ranks: every rank runs this leg (then
+        the ranks meet at barriers and the time is the maximum over them); a leg that rank 0 runs
+        alone must not touch a collective."""
         graph, per_step = capture_steps(torch, ctx, stream, step, group)
         est = time_graph(torch, stream, graph, max(1, (warm_steps + group - 1) // group))
         est = max(est / max(1, (warm_steps + group - 1) // group), 1e-3)
         replays = max(3, int(np.ceil(min_s * 1e3 / est)))
-        if world > 1:
+        if world > 1 and all_ranks:
             dist.barrier()
         torch.cuda.synchronize()
         sampler = ClockSampler(local_rank)
@@ -518,9 +660,10 @@ def run_ours(args):
         per_replay = time_replays(torch, stream, graph.replay, replays)
         torch.cuda.synchronize()
         clocks = sampler.stop() if rank == 0 else None
-        if world > 1:
+        if world > 1 and all_ranks:
             dist.barrier()
-        return sync_max(float(np.median(per_replay))), spread(per_replay, group), per_step, clocks
+        ms_replay = float(np.median(per_replay))
+        return (sync_max(ms_replay) if all_ranks else ms_replay), spread(per_replay, group), per_step, clocks
 
     line = {}
     # ================= decode: config 1, the headline =================
@@ -611,7 +754,7 @@ def run_ours(args):
             torch.cuda.synchronize()
             active.append(ctx.info().lastActiveExperts)
         vgroup = n_layers * 2
-        vms, vtiming, v_per_step, _ = measure_graph(verify_step, vgroup, vgroup)
+        vms, vtiming, v_per_step, _ = measure_graph(verify_step, vgroup, vgroup, all_ranks=False)
         mean_active = float(np.mean(active))
         vbytes = mean_active * EXPERT_BYTES + SHARED_BYTES + ROUTER_BYTES + 16 * ACT_IO_BYTES
         vach = vbytes / (vms * 1e-3 / vgroup) / 1e9
@@ -711,6 +854,8 @@ def main():
     ap.add_argument("--layers", type=int, default=8, help="resident layers the steps rotate over")
     ap.add_argument("--only", default="", help="comma list of decode,verify,prefill,stack (default all)")
     ap.add_argument("--stack-layers", type=int, default=STACK_LAYERS, help="layers of the config-4 stack")
+    ap.add_argument("--ep-comm", choices=("nccl", "peer", "both"), default="both",
+                    help="how the expert-parallel stack moves rows between ranks (both: time each, report the faster)")
     ap.add_argument("--ep-chunks", type=int, default=2,
                     help="runs the local tokens are cut into per layer under expert parallelism")
     ap.add_argument("--quick", action="store_true",

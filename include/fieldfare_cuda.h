@@ -243,6 +243,15 @@ bool ff_moe_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *wei
                    const uint16_t *residual, uint16_t *y, uint32_t tokens, void *stream,
                    const char **error);
 
+/* The same reduce over partial rows that lie in another order: the row of route (t, r) is row
+ * rowIndex[t*K + r] of `partials` (uint32, every entry below the caller's row count).  Used under
+ * expert parallelism, where the rows come back from the other GPUs grouped by source, so that no
+ * pass over memory is spent on putting them back into (token, rank) order.  The arithmetic per
+ * output element is that of ff_moe_reduce.  No counterpart in the reference (one device there). */
+bool ff_moe_reduce_indexed(FFContext *ctx, const uint16_t *partials, const uint32_t *rowIndex,
+                           const uint16_t *weights, const uint16_t *residual, uint16_t *y,
+                           uint32_t tokens, void *stream, const char **error);
+
 /* Shared INT4 FFN for `tokens` rows: y = down(gelu(bf16(gate x)) * bf16(up x)).  GEMV kernels
  * up to 16 rows, tensor-core GEMMs above.  Replaces `SharedExpertInt4.encode`
  * (Kernels/MoE/SharedExpertInt4.swift:32-88) and `PrefillSharedExpert.encodeBlock`

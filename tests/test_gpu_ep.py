@@ -1,5 +1,8 @@
-"""Expert parallelism on real GPUs: two NCCL ranks, experts split in halves, compared with the
-single-GPU layer on the same tokens.  Needs two GPUs; skipped otherwise."""
+"""Expert parallelism on real GPUs: two NCCL ranks, experts split over them (contiguous blocks, and
+a load-balanced placement with the tokens cut into chunks whose exchanges overlap the GEMMs, and
+the same placement with the rows moved by peer stores into symmetric memory),
+compared bit for bit with the single-GPU layer on the same tokens.  Needs two GPUs; skipped
+otherwise."""
 import os
 import socket
 
@@ -27,7 +30,7 @@ def _worker(rank, world, port, results):
         home = hotpath.HotpathContext(layers=1, maxTokens=TOKENS, device=rank, **SHAPE)
         home.loadShared(0, *L.shared_projections())
         home.loadRouter(0, L.routerW, logitBias=L.logitBias)
-        local = hotpath.HotpathContext(layers=1, experts=epr, d=SHAPE["d"], f=SHAPE["f"], sharedF=0, topK=1,
+        local = hotpath.HotpathContext(layers=2, experts=epr, d=SHAPE["d"], f=SHAPE["f"], sharedF=0, topK=1,
                                        maxTokens=TOKENS * SHAPE["topK"] * world, device=rank)
         local.loadLayer(0, L.blobs[rank * epr:(rank + 1) * epr], L.layout.stride, L.layout.offsets,
                         expertCount=epr)
@@ -37,8 +40,32 @@ def _worker(rank, world, port, results):
         y = block.forward(x)
         want = full.moeLayer(0, x)
         torch.cuda.synchronize()
+        same = bool(torch.equal(y, want))
+        rows = int(block.last_recv_rows)
+        # a placement that balances a skewed load (experts interleaved over the ranks), the tokens in
+        # three chunks: the same bits
+        load = [1.0 / (e + 1) ** 1.1 for e in range(SHAPE["experts"])]
+        placement = parallel.balanced_placement(load, world)
+        local.loadLayer(1, np.ascontiguousarray(L.blobs[placement.experts_of(rank)]), L.layout.stride,
+                        L.layout.offsets, expertCount=epr)
+        balanced = parallel.ExpertParallelMoE(SHAPE["experts"], SHAPE["topK"],
+                                              *parallel.cuda_layer_fns(home, local, 0, expert_layer=1),
+                                              placement=placement, chunks=3)
+        y2 = balanced.forward(x)
+        torch.cuda.synchronize()
+        same = same and bool(torch.equal(y2, want))
+        # rows moved by peer stores into symmetric memory instead of the collective: the same bits,
+        # twice over the same buffers (the second pass checks the reuse barriers)
+        buffers = parallel.PeerBuffers(TOKENS * SHAPE["topK"] * world, SHAPE["d"], torch.bfloat16, full.device)
+        peer = parallel.ExpertParallelMoE(SHAPE["experts"], SHAPE["topK"],
+                                          *parallel.cuda_layer_fns(home, local, 0, expert_layer=1),
+                                          placement=placement, peer=buffers)
+        for _ in range(2):
+            y3 = peer.forward(x)
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(y3, want))
         flags = home.info().deviceErrorFlag | local.info().deviceErrorFlag | full.info().deviceErrorFlag
-        results[rank] = (bool(torch.equal(y, want)), int(flags), int(block.last_recv_rows))
+        results[rank] = (same, int(flags), rows)
         for c in (full, home, local):
             c.close()
     finally:

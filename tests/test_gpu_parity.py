@@ -283,6 +283,17 @@ def test_reduce_token_major(tiny, oracle):
         torch.cuda.synchronize()
         want = oracle.reduce_token_major(p, w, residual, T, K, D)
         assert np.array_equal(hp.bf16_numpy(h2), want)
+        # the same rows lying in another order, found through a row index: the same bits
+        perm = np.random.default_rng(5).permutation(T * K)
+        inverse = np.empty(T * K, dtype=np.int32)
+        inverse[perm] = np.arange(T * K, dtype=np.int32)   # row of route i in the shuffled buffer
+        h3 = torch.zeros((T, D), dtype=torch.bfloat16, device=ctx.device)
+        hp.PrefillMoE(ctx).encodeReduceTokenMajor(
+            None, dev(np.ascontiguousarray(p[perm]), ctx), dev(w, ctx), h3, T,
+            residual=None if residual is None else dev(residual, ctx),
+            rowIndex=torch.from_numpy(inverse).to(ctx.device))
+        torch.cuda.synchronize()
+        assert np.array_equal(hp.bf16_numpy(h3), want)
 
 
 def test_rmsnorm(tiny, oracle):

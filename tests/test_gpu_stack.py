@@ -194,6 +194,7 @@ def test_misaligned_and_mismatched_arguments_fail_before_any_launch(oracle):
         wd = torch.from_numpy(np.ascontiguousarray(w)).to(ctx.device)
         sd, bd = dev(np.ascontiguousarray(s), ctx), dev(np.ascontiguousarray(b), ctx)
         proj = binding.FFProjection(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), TOY["sharedF"], d)
+        down = binding.FFProjection(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), d, TOY["sharedF"])
         stream = None
         with pytest.raises(hp.FieldfareError, match="4-byte aligned"):
             binding.call("ff_int4_gemv_rows", ctx.handle, ctypes.byref(proj), odd, d + 8, 2,
@@ -205,7 +206,7 @@ def test_misaligned_and_mismatched_arguments_fail_before_any_launch(oracle):
             binding.call("ff_rmsnorm", ctx.handle, buf.data_ptr() + 1, None, ctypes.c_float(1e-6), 1,
                          out.data_ptr(), stream)
         with pytest.raises(hp.FieldfareError, match="4-byte aligned"):
-            binding.call("ff_shared_ffn_noalloc", ctypes.byref(proj), ctypes.byref(proj), ctypes.byref(proj),
+            binding.call("ff_shared_ffn_noalloc", ctypes.byref(proj), ctypes.byref(proj), ctypes.byref(down),
                          odd, d + 8, 2, out.data_ptr(), d, stream)
         with pytest.raises(hp.FieldfareError, match="16-byte aligned"):
             binding.call("ff_moe_layer", ctx.handle, 0, odd, 1, out.data_ptr(), None, None, stream)
