@@ -218,6 +218,7 @@ class ExpertParallelMoE:
         self.experts_fn, self.reduce_fn = experts_fn, reduce_fn
         self.chunks = max(1, int(chunks))
         self.peer = peer  # PeerBuffers: exchange rows by peer stores instead of the collective
+        self._side = None  # second stream of the peer path (shared FFN beside the dispatch)
         self.last_recv_rows = 0
         self.last_expert_counts = None  # routes per (global) expert of the last forward, on request
         self.count_experts = False
@@ -327,6 +328,17 @@ class ExpertParallelMoE:
         self.last_recv_rows = recv_total
         token = plan.token.to(x.device)
         local_ids = torch.empty(recv_total, dtype=torch.int32, device=x.device)
+        # the shared FFN needs no exchange: it runs on a second stream beside the dispatch
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            with tm.phase("shared", x):
+                residual = self.shared_fn(x)
+        x.record_stream(self._side)
+        if residual is not None:
+            residual.record_stream(main)
         with tm.phase("dispatch", x):
             pb.barrier()  # every rank is done with the previous contents of the buffers
             start = 0
@@ -341,8 +353,6 @@ class ExpertParallelMoE:
                                    output_split_sizes=[counts[s][me] for s in range(W)],
                                    input_split_sizes=counts[me], group=self.group)
             pb.barrier()  # everybody's rows have landed
-        with tm.phase("shared", x):
-            residual = self.shared_fn(x)
         with tm.phase("experts", x):
             partial_rows = self.experts_fn(pb.recv[:recv_total], local_ids)
         with tm.phase("combine", x):
@@ -354,6 +364,7 @@ class ExpertParallelMoE:
                     pb.peer_back(s)[offset:offset + n].copy_(partial_rows[start:start + n])
                 start += n
             pb.barrier()  # my tokens' partial rows have landed
+        main.wait_stream(self._side)
         with tm.phase("reduce", x):
             return self.reduce_fn(pb.back[:T * K], weights, residual, row_index)
 

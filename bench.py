@@ -184,7 +184,7 @@ def run_reference(args):
                          "sample": f"{steps} decode steps of the C oracle (OpenMP), one layer"},
         "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def time_graph(torch, stream, graph, replays):
@@ -414,120 +414,6 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
     best = min(results, key=lambda n: results[n]["ms_per_stack"])
     ms = results[best]["ms_per_stack"]
     blocks = variants[best]
-    recv = torch.tensor([[float(b.last_recv_rows) for b in blocks]], dtype=torch.float64, device=device)
-    rows = [torch.zeros_like(recv) for _ in range(world)]
-    dist.all_gather(rows, recv)
-    rows = torch.cat(rows).cpu().numpy()  # [world, layers]
-    finite = bool(torch.isfinite(y.float()).all().item())
-    err = ctx.info().deviceErrorFlag
-    resident = ctx.info().weightBytesResident
-    ctx.close()
-    peak = measured_bf16_peak()
-    tf = stack_flops(layers) / (ms * 1e-3) / 1e12
-    return {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens", "gpus": 1,
-            "path": "ff_moe_stack on one context (no expert parallelism, no collective)",
-            "tokens_per_s": STACK_TOKENS / (ms * 1e-3), "ms_per_stack": ms, "steps": steps,
-            "timed_region": spread(per, 1), "tflops": tf,
-            "frac_of_measured_bf16_sustained": tf / peak["tflops"], "frac_of_measured_bf16_burst": tf / peak["burst_tflops"],
-            "weight_bytes_resident": int(resident), "output_finite": finite, "device_error_flag": int(err),
-            "kernel_ms_per_stack": {name: round(t, 3) for name, (n, t) in sorted(trace.items())}}
-
-
-def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank, world, device, args):
-    """Benchmark configuration 4: a 30-layer stack of MoE blocks (RMSNorm between layers, no
-    attention), 32768 prefill tokens.  One GPU: the library's ff_moe_stack.  Several GPUs: experts
-    sharded over the ranks with an NCCL all-to-all dispatch and combine per layer.  All 30 layer
-    slots are resident (13.2 GB over the box); their bytes repeat a few distinct seeded layers,
-    which does not change the work."""
-    from ane_fieldfare_b200 import parallel, synth
-    if world == 1:
-        return measure_stack_single(torch, hotpath, workload, host_layers, local_rank, device, args)
-    layers = args.stack_layers
-    tokens_local = STACK_TOKENS // world
-    epr = E // world
-    capacity = min(STACK_TOKENS * K, 4 * tokens_local * K)
-    home = hotpath.HotpathContext(layers=len(host_layers), experts=E, d=D, f=F, sharedF=FS, topK=K,
-                                  maxTokens=tokens_local, device=local_rank)
-    local = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=1,
-                                   maxTokens=capacity, device=local_rank)
-    for i, L in enumerate(host_layers):
-        home.loadShared(i, *L.shared_projections())
-        home.loadRouter(i, L.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}"))
-
-    def load_experts(placements):
-        for slot in range(layers):
-            L = host_layers[slot % len(host_layers)]
-            mine = placements[slot].experts_of(rank)
-            local.loadLayer(slot, np.ascontiguousarray(L.blobs[mine]), L.layout.stride, L.layout.offsets,
-                            expertCount=epr)
-
-    def make_blocks(placements, chunks, peer=None):
-        out = []
-        for slot in range(layers):
-            # the home context is indexed by the distinct layer, the expert context by the stack's slot
-            fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
-            out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks, peer=peer))
-        return out
-
-    x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
-
-    def run_stack(blocks):
-        x = x0
-        for block in blocks:
-            x = block.forward(home.rmsnorm(x, None, 1e-6))
-        return x
-
-    # Pass 1, contiguous placement: the stack's outputs do not depend on where an expert lives, so
-    # this pass measures how many routes every expert of every layer receives (summed over the
-    # ranks).  Experts are then placed so that every rank receives about the same number of rows
-    # (the blob layout is untouched: a rank loads the blobs of its experts).
-    contiguous = [parallel.contiguous_placement(E, world)] * layers
-    load_experts(contiguous)
-    blocks = make_blocks(contiguous, 1)
-    for block in blocks:
-        block.count_experts = True
-    run_stack(blocks)
-    counts = torch.stack([block.last_expert_counts for block in blocks]).to(torch.float64)
-    dist.all_reduce(counts)
-    placements = [parallel.balanced_placement((counts[slot] + 0.5).tolist(), world) for slot in range(layers)]
-    load_experts(placements)
-    blocks = make_blocks(placements, args.ep_chunks)
-
-    # the first layer's output for the first rows against ff_moe_layer on one context that holds all
-    # experts of that layer: the same bits
-    check_rows = min(256, tokens_local)
-    full = hotpath.HotpathContext(layers=1, experts=E, d=D, f=F, sharedF=FS, topK=K, maxTokens=tokens_local,
-                                  device=local_rank)
-    L0 = host_layers[0]
-    workload.load_layer(full, 0, L0)
-    full.loadRouter(0, L0.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, "stack.zipf.0"))
-    normed = home.rmsnorm(x0, None, 1e-6)
-    y_ep = blocks[0].forward(normed)
-    y_one = full.moeLayer(0, normed)
-    torch.cuda.synchronize()
-    same = torch.tensor([1.0 if torch.equal(y_ep[:check_rows], y_one[:check_rows]) else 0.0],
-                        dtype=torch.float64, device=device)
-    full.close()
-    dist.all_reduce(same, op=dist.ReduceOp.MIN)
-
-    for _ in range(2):
-        run_stack(blocks)
-    torch.cuda.synchronize()
-    dist.barrier()
-    steps = 3
-    per = time_replays(torch, torch.cuda.current_stream(), lambda: run_stack(blocks), steps)
-    t = torch.tensor([float(np.median(per))], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    # one more pass with CUDA events around the phases of every layer
-    timer = parallel.PhaseTimer()
-    for block in blocks:
-        block.timer = timer
-    y = run_stack(blocks)
-    phases = timer.totals()
-    names = sorted(phases)
-    pt = torch.tensor([phases[n] for n in names], dtype=torch.float64, device=device)
-    dist.all_reduce(pt, op=dist.ReduceOp.MAX)
     recv = torch.tensor([[float(b.last_recv_rows) for b in blocks]], dtype=torch.float64, device=device)
     rows = [torch.zeros_like(recv) for _ in range(world)]
     dist.all_gather(rows, recv)
@@ -837,12 +723,34 @@ def run_ours(args):
                                 "other_configs": cpu_other_configs(host_layer0, router_bias("normal", 0),
                                                                    router_bias("zipf", 0))}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if ctx is not None:
         ctx.close()
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
+
+
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Everything libraries print while the bench runs (NCCL's version banner, for one) goes to
+    stderr; file descriptor 1 is kept aside for the one JSON line."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict):
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, text)
 
 
 def main():
@@ -861,6 +769,7 @@ def main():
     ap.add_argument("--quick", action="store_true",
                     help="skip the end-to-end loop, per-kernel tracing and the CPU baseline (for profiler runs)")
     args = ap.parse_args()
+    keep_stdout_for_the_result()
     if args.impl == "reference":
         run_reference(args)
     else:
