@@ -29,6 +29,17 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     return 0.5f * x * (1.0f + tanhf(inner));
 }
 
+// The same activation with the hardware's tanh approximation (relative error about 2^-11, below
+// the bf16 rounding that follows it): for the prefill GEMM's epilogue, where the exact tanhf is a
+// measurable share of the step.
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+    const float x3 = x * x * x;
+    float inner = 0.7978845608028654f * (x + 0.044715f * x3);
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(inner));
+    return 0.5f * x * (1.0f + th);
+}
+
 // Position of input element e inside a staged row: chunks are interleaved in blocks of eight so
 // that lanes j = 0..7 (chunks c = 8i + j) read one contiguous 128 bytes per 128-bit load.
 __device__ __forceinline__ int staged_index(int e) {

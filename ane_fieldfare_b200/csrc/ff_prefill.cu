@@ -234,9 +234,11 @@ bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *
 
 constexpr int kSortTokens = 256;  // tokens per permute block
 
+constexpr uint32_t kRowTile = 192;  // rows of one expert per GEMM unit (accumulator columns)
+
 struct RowTile {
     uint32_t rowStart;  // first row in expert-sorted order
-    uint32_t rows;      // 1..128
+    uint32_t rows;      // 1..kRowTile
     uint32_t expert;
     uint32_t pad;
 };
@@ -280,7 +282,7 @@ k_route_count(const uint32_t *ids, int T, int K, int E, uint32_t *blockCounts) {
 }
 
 // Pass 2 (one block): exclusive prefix of every expert's counts over the blocks, expert offsets,
-// and the list of row tiles (up to 128 rows of one expert each), experts ascending.
+// and the list of row tiles (up to kRowTile rows of one expert each), experts ascending.
 // counts[0] = row tiles, counts[1] = pairs, counts[2] = experts with at least one pair.
 __global__ void __launch_bounds__(256)
 k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, RowTile *tiles,
@@ -305,7 +307,7 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
             offset[i] = run;
             tileBase[i] = tilesRun;
             run += total[i];
-            tilesRun += (total[i] + 127u) / 128u;
+            tilesRun += (total[i] + kRowTile - 1u) / kRowTile;
             active += total[i] ? 1u : 0u;
         }
         offset[E] = run;
@@ -320,8 +322,8 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
     if (e == 0) expertOffsets[E] = offset[E];
     if (e < E) {
         const uint32_t n = total[e];
-        for (uint32_t i = 0, tix = tileBase[e]; i < n; i += 128, ++tix)
-            if (tix < maxTiles) tiles[tix] = RowTile{offset[e] + i, min(128u, n - i), (uint32_t)e, 0u};
+        for (uint32_t i = 0, tix = tileBase[e]; i < n; i += kRowTile, ++tix)
+            if (tix < maxTiles) tiles[tix] = RowTile{offset[e] + i, min(kRowTile, n - i), (uint32_t)e, 0u};
     }
 }
 
@@ -376,9 +378,9 @@ k_route_scatter(const uint32_t *ids, const uint16_t *weights, int T, int K, int 
 
 // Row tiles of a dense problem: T rows of one "expert" (the shared FFN).
 __global__ void k_dense_tiles(int T, RowTile *tiles, uint32_t *counts) {
-    const int n = (T + 127) / 128;
+    const int n = (T + (int)kRowTile - 1) / (int)kRowTile;
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        tiles[i] = RowTile{(uint32_t)i * 128u, (uint32_t)min(128, T - i * 128), 0u, 0u};
+        tiles[i] = RowTile{(uint32_t)i * kRowTile, (uint32_t)min((int)kRowTile, T - i * (int)kRowTile), 0u, 0u};
     if (threadIdx.x == 0) {
         counts[0] = (uint32_t)n;
         counts[1] = (uint32_t)T;
@@ -489,17 +491,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmemD, uint64_t descA, uint64_t descB,
-                                            uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(tmemD),
-        "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // 32 consecutive fp32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tc_load_32cols(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -531,22 +522,65 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smemAddr) {
     desc |= (uint64_t)2 << 61;
     return desc;
 }
-// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 128, N = 256.
-constexpr uint32_t kIdescBf16M128N256 =
-    (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 128, N = `n`
+// (a multiple of 16 up to 256).
+__device__ __forceinline__ uint32_t umma_idesc_bf16_m128(uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes x 16 bf16 (eight 32-bit columns per lane).
+__device__ __forceinline__ void tc_mma_bf16_a_tmem(uint32_t tmemD, uint32_t tmemA, uint64_t descB,
+                                                   uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmemD),
+        "r"(tmemA), "l"(descB), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tc_store_32cols(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+        "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+        "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 // ---- grouped INT4 GEMM ---------------------------------------------------------------------
 
-constexpr int kTileM = 128, kTileN = 256, kTileK = 64;
-constexpr int kStagesLoad = 3;   // activations + packed codes (TMA destinations)
-constexpr int kStagesB = 3;      // dequantized bf16 operand tiles
-constexpr int kDequantWarps = 16;  // half an operand row (32 codes per step) per thread
-// warp 0 TMA, warp 1 MMA, warps 2-17 dequant, warps 18-21 epilogue (TMEM lane quarter = warp & 3)
+constexpr int kWeightRows = 128;  // weight rows of a unit = TMEM lanes of its accumulator
+constexpr int kTileK = 64;        // one quantization group per step
+constexpr int kTokStages = 6;     // token tiles (TMA destinations)
+constexpr int kPackStages = 6;    // packed-code tiles (TMA destinations)
+constexpr int kWStages = 4;       // dequantized weight tiles in TMEM, one per dequantizing group
+constexpr int kDequantWarps = 16; // four groups of four warps; a group covers the 128 TMEM lanes
+// warp 0 TMA, warp 1 MMA, warps 2-17 dequantize, warps 18-21 epilogue (TMEM lane quarter = warp & 3)
 constexpr int kGemmThreads = (2 + kDequantWarps + 4) * 32;
-constexpr uint32_t kTileABytes = kTileM * kTileK * 2;       // 16384
-constexpr uint32_t kTilePackedBytes = kTileN * kTileK / 2;  // 8192: four [64 rows x 32 bytes] boxes
-constexpr uint32_t kTileBBytes = kTileN * kTileK * 2;       // 32768
-constexpr uint32_t kTmemCols = 512;  // two accumulator buffers x 256 columns
+constexpr uint32_t kTokTileBytes = kRowTile * kTileK * 2;         // 24576
+constexpr uint32_t kPackTileBytes = kWeightRows * kTileK / 2;     // 4096: two [64 rows x 32 bytes] boxes
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccCols = kRowTile;                           // accumulators at columns 0 and 192
+constexpr uint32_t kWCol0 = 2 * kAccCols;                         // weight stages: 32 columns each from 384
+constexpr int kXchgPitch = 17;                                    // floats per exchanged row (16 + 1 pad)
+constexpr uint32_t kXchgBytes = 2u * 128u * kXchgPitch * 4u;      // two buffers x 128 rows
+constexpr uint32_t kStagePitchGateUp = 64 * 2 + 16;               // bytes per token row of the output tile
+constexpr uint32_t kStagePitchDown = 128 * 2 + 16;
+constexpr uint32_t kStageBytes = 32u * kStagePitchDown;           // one 32-token tile (the larger mode)
+constexpr uint32_t kEpilogueBytes = kXchgBytes + 2u * kStageBytes + 2u * kRowTile * 4u;
+static_assert(kWCol0 + kWStages * 32 <= kTmemCols, "tensor memory layout");
+static_assert(kRowTile % 32 == 0 && kRowTile <= 256, "row tile");
 
 enum GemmMode : int { kModeGateUp = 0, kModeDown = 1 };
 
@@ -557,7 +591,7 @@ struct GemmArgs {
     uint32_t biasOff[2];
     uint32_t K;                // contraction length (multiple of 64)
     uint32_t N;                // outputs per row: F (gate/up) or D (down)
-    uint32_t nTiles;           // column tiles: ceil(N/128) for gate/up, ceil(N/256) for down
+    uint32_t nTiles;           // weight-row tiles: ceil(N/64) for gate/up, ceil(N/128) for down
     const RowTile *tiles;
     const uint32_t *counts;    // counts[0] = row tiles
     uint16_t *out;             // gate/up: activations [row][N]; down: output rows [*][N]
@@ -567,12 +601,17 @@ struct GemmArgs {
     uint32_t *errorFlag;
 };
 
+// position of element i of an aligned run of eight in the order 0,4,1,5,2,6,3,7
+__device__ __forceinline__ uint32_t interleaved_position(uint32_t i) {
+    return (i & ~7u) | (((i & 3u) << 1) | ((i >> 2) & 1u));
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW0,
+k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_constant__ CUtensorMap mapW0,
                     const __grid_constant__ CUtensorMap mapW1, const GemmArgs args) {
     extern __shared__ uint8_t gemmSmemRaw[];
-    __shared__ uint64_t barriers[2 * kStagesLoad + 2 * kStagesB + 4];
+    __shared__ uint64_t barriers[2 * kTokStages + 2 * kPackStages + 2 * kWStages + 4 + 5];
     __shared__ uint32_t tmemBaseSlot;
     __shared__ volatile uint32_t abortFlag;
 
@@ -581,37 +620,52 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const uint32_t base = (rawBase + 1023u) & ~1023u;
     const uint32_t groupsK = args.K / kTileK;
 
-    // carve-up: B stages and A stages (1024-aligned), packed stages, then the unit's scales
+    // carve-up: token stages (1024-aligned), packed stages, the epilogue's exchange buffers
     // (stage addresses are computed, not tabulated: an array indexed by the running stage would
-    // live in local memory and put a load in front of every MMA and every dequantized tile)
-    const uint32_t bBase = base, aBase = bBase + kStagesB * kTileBBytes, pBase = aBase + kStagesLoad * kTileABytes;
-    auto bAddrOf = [&](uint32_t s) { return bBase + s * kTileBBytes; };
-    auto aAddrOf = [&](uint32_t s) { return aBase + s * kTileABytes; };
-    auto pAddrOf = [&](uint32_t s) { return pBase + s * kTilePackedBytes; };
-    uint8_t *scalesPtr = gemmSmemRaw + (pBase + kStagesLoad * kTilePackedBytes - rawBase);  // [256 rows][groupsK][2] bf16
+    // live in local memory)
+    const uint32_t tokBase = base, packBase = tokBase + kTokStages * kTokTileBytes;
+    auto tokAddrOf = [&](uint32_t s) { return tokBase + s * kTokTileBytes; };
+    auto packAddrOf = [&](uint32_t s) { return packBase + s * kPackTileBytes; };
+    uint8_t *epilogueSmem = gemmSmemRaw + (packBase + kPackStages * kPackTileBytes - rawBase);
+    float *xchg = reinterpret_cast<float *>(epilogueSmem);
+    uint8_t *stageBuf = epilogueSmem + kXchgBytes;
+    uint32_t *rowTable = reinterpret_cast<uint32_t *>(stageBuf + 2u * kStageBytes);
 
     const uint32_t barBase = smem_u32(barriers);
-    auto barLoadFull = [&](int s) { return barBase + 8u * (uint32_t)s; };
-    auto barLoadEmpty = [&](int s) { return barBase + 8u * (uint32_t)(kStagesLoad + s); };
-    auto barBFull = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + s); };
-    auto barBEmpty = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + kStagesB + s); };
-    auto barAccFull = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + 2 * kStagesB + s); };
-    auto barAccEmpty = [&](int s) { return barBase + 8u * (uint32_t)(2 * kStagesLoad + 2 * kStagesB + 2 + s); };
+    auto barAt = [&](int i) { return barBase + 8u * (uint32_t)i; };
+    auto barTokFull = [&](int s) { return barAt(s); };
+    auto barTokEmpty = [&](int s) { return barAt(kTokStages + s); };
+    auto barPackFull = [&](int s) { return barAt(2 * kTokStages + s); };
+    auto barPackEmpty = [&](int s) { return barAt(2 * kTokStages + kPackStages + s); };
+    auto barWFull = [&](int s) { return barAt(2 * kTokStages + 2 * kPackStages + s); };
+    auto barWEmpty = [&](int s) { return barAt(2 * kTokStages + 2 * kPackStages + kWStages + s); };
+    auto barAccFull = [&](int s) { return barAt(2 * kTokStages + 2 * kPackStages + 2 * kWStages + s); };
+    auto barAccEmpty = [&](int s) { return barAt(2 * kTokStages + 2 * kPackStages + 2 * kWStages + 2 + s); };
+    auto barXchg = [&](int s) { return barAt(2 * kTokStages + 2 * kPackStages + 2 * kWStages + 4 + s); };
+    auto barStage = [&](int s) { return barAt(2 * kTokStages + 2 * kPackStages + 2 * kWStages + 6 + s); };
+    const uint32_t barRows = barAt(2 * kTokStages + 2 * kPackStages + 2 * kWStages + 8);
 
     if (threadIdx.x == 0) {
         abortFlag = 0;
-        for (int s = 0; s < kStagesLoad; ++s) {
-            mbar_init(barLoadFull(s), 1);
-            mbar_init(barLoadEmpty(s), 1 + kDequantWarps);  // one tcgen05.commit + the dequant warps
+        for (int s = 0; s < kTokStages; ++s) {
+            mbar_init(barTokFull(s), 1);
+            mbar_init(barTokEmpty(s), 1);  // one tcgen05.commit
         }
-        for (int s = 0; s < kStagesB; ++s) {
-            mbar_init(barBFull(s), kDequantWarps);
-            mbar_init(barBEmpty(s), 1);  // one tcgen05.commit
+        for (int s = 0; s < kPackStages; ++s) {
+            mbar_init(barPackFull(s), 1);
+            mbar_init(barPackEmpty(s), 4);  // the four warps of the group that read it
+        }
+        for (int s = 0; s < kWStages; ++s) {
+            mbar_init(barWFull(s), 4);   // the four warps of the group that wrote it
+            mbar_init(barWEmpty(s), 1);  // one tcgen05.commit
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(barAccFull(s), 1);   // one tcgen05.commit
             mbar_init(barAccEmpty(s), 4);  // four epilogue warps
+            mbar_init(barXchg(s), 128);    // every epilogue thread
+            mbar_init(barStage(s), 128);
         }
+        mbar_init(barRows, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -628,36 +682,44 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
 
     const uint32_t rowTiles = args.counts[0];
     const uint32_t units = rowTiles * args.nTiles;
-    // operand rows 0..127 | 128..255 of a unit: gate | up rows [128 nt, +128) for the gate/up GEMM,
-    // matrix rows [256 nt, +256) for the down GEMM; loaded as four boxes of 64 rows
+    // weight rows 0..127 of a unit: gate rows [64 nt, +64) | up rows [64 nt, +64) for the gate/up
+    // GEMM, matrix rows [128 nt, +128) for the down GEMM; loaded as two boxes of 64 rows
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
+            uint32_t ts = 0, tPhase = 0, ps = 0, pPhase = 0;
             bool ok = true;
             for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
                 const RowTile tile = args.tiles[u / args.nTiles];
                 const uint32_t nt = u % args.nTiles;
                 const int row0 = (int)tile.rowStart;
                 for (uint32_t g = 0; g < groupsK; ++g) {
-                    if (!mbar_wait_idle(barLoadEmpty(stage), phase ^ 1u, &abortFlag)) {
+                    if (!mbar_wait_idle(barPackEmpty(ps), pPhase ^ 1u, &abortFlag)) {
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(barLoadFull(stage), kTileABytes + kTilePackedBytes);
-                    tma_load_2d(aAddrOf(stage), &mapA, (int)(g * kTileK), row0, barLoadFull(stage));
+                    mbar_expect_tx(barPackFull(ps), kPackTileBytes);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const CUtensorMap *map = (MODE == kModeGateUp && q >= 2) ? &mapW1 : &mapW0;
-                        const int wRow = MODE == kModeGateUp ? (int)nt * 128 + (q & 1) * 64
-                                                             : (int)nt * 256 + q * 64;
-                        tma_load_3d(pAddrOf(stage) + (uint32_t)q * (kTilePackedBytes / 4), map,
-                                    (int)(g * (kTileK / 2)), wRow, (int)tile.expert, barLoadFull(stage));
+                    for (int q = 0; q < 2; ++q) {
+                        const CUtensorMap *map = (MODE == kModeGateUp && q == 1) ? &mapW1 : &mapW0;
+                        const int wRow = MODE == kModeGateUp ? (int)nt * 64 : (int)nt * 128 + q * 64;
+                        tma_load_3d(packAddrOf(ps) + (uint32_t)q * (kPackTileBytes / 2), map,
+                                    (int)(g * (kTileK / 2)), wRow, (int)tile.expert, barPackFull(ps));
                     }
-                    if (++stage == kStagesLoad) {
-                        stage = 0;
-                        phase ^= 1u;
+                    if (++ps == kPackStages) {
+                        ps = 0;
+                        pPhase ^= 1u;
+                    }
+                    if (!mbar_wait_idle(barTokEmpty(ts), tPhase ^ 1u, &abortFlag)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(barTokFull(ts), kTokTileBytes);
+                    tma_load_2d(tokAddrOf(ts), &mapTok, (int)(g * kTileK), row0, barTokFull(ts));
+                    if (++ts == kTokStages) {
+                        ts = 0;
+                        tPhase ^= 1u;
                     }
                 }
             }
@@ -665,36 +727,40 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0, acc = 0, accPhase = 0;
+            uint32_t ts = 0, tPhase = 0, ws = 0, wPhase = 0, acc = 0, accPhase = 0;
             bool ok = true;
             for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const RowTile tile = args.tiles[u / args.nTiles];
+                // accumulator columns = the tile's rows, to the next multiple of 16
+                const uint32_t idesc = umma_idesc_bf16_m128(max(16u, (tile.rows + 15u) & ~15u));
                 if (!mbar_wait_idle(barAccEmpty(acc), accPhase ^ 1u, &abortFlag)) break;
                 tc_fence_after();
-                const uint32_t tmemD = tmemBase + acc * (uint32_t)kTileN;
+                const uint32_t tmemD = tmemBase + acc * kAccCols;
                 for (uint32_t g = 0; g < groupsK; ++g) {
-                    if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
-                        !mbar_wait(barBFull(bStage), bPhase, &abortFlag)) {
+                    if (!mbar_wait(barTokFull(ts), tPhase, &abortFlag) ||
+                        !mbar_wait(barWFull(ws), wPhase, &abortFlag)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t descA = umma_desc_sw128(aAddrOf(stage));
-                    const uint64_t descB = umma_desc_sw128(bAddrOf(bStage));
+                    const uint64_t descTok = umma_desc_sw128(tokAddrOf(ts));
+                    const uint32_t tmemW = tmemBase + kWCol0 + ws * 32u;
 #pragma unroll
                     for (uint32_t kk = 0; kk < kTileK / 16; ++kk) {
-                        // 32 bytes (>> 4 = 2) further along K for every 16-element slice
-                        tc_mma_bf16(tmemD, descA + 2u * kk, descB + 2u * kk, kIdescBf16M128N256,
-                                    (g | kk) != 0u ? 1u : 0u);
+                        // per 16-element slice: eight columns further in TMEM, 32 bytes (>> 4 = 2)
+                        // further in the token tile
+                        tc_mma_bf16_a_tmem(tmemD, tmemW + 8u * kk, descTok + 2u * kk, idesc,
+                                           (g | kk) != 0u ? 1u : 0u);
                     }
-                    tc_commit(barLoadEmpty(stage));
-                    tc_commit(barBEmpty(bStage));
-                    if (++stage == kStagesLoad) {
-                        stage = 0;
-                        phase ^= 1u;
+                    tc_commit(barTokEmpty(ts));
+                    tc_commit(barWEmpty(ws));
+                    if (++ts == kTokStages) {
+                        ts = 0;
+                        tPhase ^= 1u;
                     }
-                    if (++bStage == kStagesB) {
-                        bStage = 0;
-                        bPhase ^= 1u;
+                    if (++ws == kWStages) {
+                        ws = 0;
+                        wPhase ^= 1u;
                     }
                 }
                 if (!ok) break;
@@ -706,176 +772,212 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapA, const __grid_const
             }
         }
     } else if (warp < 2 + kDequantWarps) {
-        // ---------------- dequantizers: half an operand row (32 codes per step) per thread ----------------
-        const int idx = (warp - 2) * 32 + lane;
-        const int r = idx >> 1;    // operand row 0..255
-        const int half = idx & 1;  // which 16 of the row's 32 packed bytes
-        const int matrix = MODE == kModeGateUp ? (r >> 7) : 0;
-        uint32_t stage = 0, phase = 0, bStage = 0, bPhase = 0;
-        uint16_t *rowScales = reinterpret_cast<uint16_t *>(scalesPtr) + (size_t)r * groupsK * 2;
-        const uint32_t dstRowOff = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
-        uint32_t dstChunk[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) dstChunk[j] = dstRowOff + (((uint32_t)(half * 4 + j) ^ (uint32_t)(r & 7)) << 4);
-        bool ok = true;
-        for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
-            const RowTile tile = args.tiles[u / args.nTiles];
-            const uint32_t nt = u % args.nTiles;
-            const uint32_t wRow = MODE == kModeGateUp ? nt * 128 + (uint32_t)(r & 127) : nt * 256 + (uint32_t)r;
+        // ---------------- dequantizers ----------------
+        // Group `grp` (four warps, one per TMEM lane quarter) takes every fourth step of the CTA's
+        // sequence of steps and owns weight stage `grp`; a thread turns one weight row's 64 codes
+        // of the step into 32 bf16 pairs and stores them to its TMEM lane.  Four steps are in
+        // work at once, which hides a step's latencies behind the other groups' arithmetic.
+        const uint32_t grp = (uint32_t)(warp - 2) >> 2;
+        const uint32_t m = (uint32_t)(warp & 3) * 32u + (uint32_t)lane;  // weight row of the unit = TMEM lane
+        const uint32_t tmemW = tmemBase + kWCol0 + grp * 32u + (((uint32_t)(warp & 3) * 32u) << 16);
+        const uint32_t matrix = MODE == kModeGateUp ? (m >> 6) : 0u;
+
+        struct Cursor {
+            uint32_t u, g;          // unit and step inside the unit
+            const uint16_t *sg, *bg;  // the row's scales and biases (null: row past the matrix)
+        };
+        auto locate = [&](Cursor &c) {
+            c.sg = c.bg = nullptr;
+            if (c.u >= units) return;
+            const RowTile tile = args.tiles[c.u / args.nTiles];
+            const uint32_t nt = c.u % args.nTiles;
+            const uint32_t wRow = MODE == kModeGateUp ? nt * 64u + (m & 63u) : nt * 128u + m;
+            if (wRow >= args.N) return;
             const uint8_t *blob = args.blobBase + (size_t)tile.expert * args.expertStride;
-            // the row's two threads each fetch one contiguous half of its scale/bias pairs into shared
-            // memory, eight pairs (sixteen independent loads) at a time so that the load latency is
-            // paid per batch, not per pair
-            __syncwarp();
-            {
-                const uint32_t perHalf = (groupsK + 1) >> 1;
-                const uint32_t gBegin = (uint32_t)half * perHalf, gEnd = min(groupsK, gBegin + perHalf);
-                uint32_t *dst32 = reinterpret_cast<uint32_t *>(rowScales);
-                if (wRow < args.N) {
-                    const uint16_t *sg = reinterpret_cast<const uint16_t *>(blob + args.scaleOff[matrix]) +
-                                         (size_t)wRow * groupsK;
-                    const uint16_t *bg = reinterpret_cast<const uint16_t *>(blob + args.biasOff[matrix]) +
-                                         (size_t)wRow * groupsK;
-                    for (uint32_t g0 = gBegin; g0 < gEnd; g0 += 8) {
-                        uint32_t v[8];
+            // (selected, not indexed: a run-time index into the parameters would copy them to local memory)
+            const uint32_t scaleOff = matrix ? args.scaleOff[1] : args.scaleOff[0];
+            const uint32_t biasOff = matrix ? args.biasOff[1] : args.biasOff[0];
+            c.sg = reinterpret_cast<const uint16_t *>(blob + scaleOff) + (size_t)wRow * groupsK;
+            c.bg = reinterpret_cast<const uint16_t *>(blob + biasOff) + (size_t)wRow * groupsK;
+        };
+        auto advance = [&](Cursor &c, uint32_t steps) {
+            c.g += steps;
+            bool moved = false;
+            while (c.g >= groupsK && c.u < units) {
+                c.g -= groupsK;
+                c.u += gridDim.x;
+                moved = true;
+            }
+            if (moved) locate(c);
+        };
+        auto fetch = [&](const Cursor &c) -> uint32_t {  // scale | bias << 16 of the cursor's step
+            if (c.u >= units || !c.sg) return 0u;
+            return (uint32_t)__ldg(c.sg + c.g) | ((uint32_t)__ldg(c.bg + c.g) << 16);
+        };
+
+        Cursor cur{blockIdx.x, 0u, nullptr, nullptr};
+        locate(cur);
+        advance(cur, grp);
+        uint32_t sb = fetch(cur);
+        uint32_t ps = grp, pPhase = 0, wPhase = 0;  // kPackStages > group count: the first stage is `grp`
+        while (cur.u < units) {
+            Cursor nxt = cur;
+            advance(nxt, kWStages);
+            const uint32_t sbNext = fetch(nxt);
+            if (!mbar_wait(barPackFull(ps), pPhase, &abortFlag) ||
+                !mbar_wait(barWEmpty(grp), wPhase ^ 1u, &abortFlag))
+                break;
+            tc_fence_after();
+            uint32_t s2, b2;
+            asm("prmt.b32 %0, %1, %1, 0x1010;" : "=r"(s2) : "r"(sb));
+            asm("prmt.b32 %0, %1, %1, 0x3232;" : "=r"(b2) : "r"(sb));
+            uint32_t w[8];
+            const uint32_t src = packAddrOf(ps) + m * 32u;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                         : "r"(src));
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                         : "r"(src + 16u));
+            uint32_t o[32];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const uint32_t g = min(g0 + (uint32_t)i, gEnd - 1);
-                            v[i] = (uint32_t)__ldg(sg + g) | ((uint32_t)__ldg(bg + g) << 16);
-                        }
+            for (int j = 0; j < 8; ++j) {
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            if (g0 + (uint32_t)i < gEnd) dst32[g0 + i] = v[i];
-                    }
-                } else {
-                    for (uint32_t g = gBegin; g < gEnd; ++g) dst32[g] = 0u;
+                for (int i = 0; i < 4; ++i) {
+                    // codes i and i+4 of the word as the bf16 pair (128+q_i, 128+q_{i+4})
+                    uint32_t pair = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+                    uint32_t q2, v2;
+                    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(q2) : "r"(pair), "r"(0x43004300u));
+                    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(v2) : "r"(q2), "r"(s2), "r"(b2));
+                    o[j * 4 + i] = v2;
                 }
             }
+            tc_store_32cols(tmemW, o);
+            tc_wait_st();
+            tc_fence_before();
             __syncwarp();
-            uint32_t sbNext = *reinterpret_cast<const uint32_t *>(rowScales);  // scale | bias << 16
-            for (uint32_t g = 0; g < groupsK; ++g) {
-                const uint32_t sb = sbNext;
-                if (g + 1 < groupsK) sbNext = *reinterpret_cast<const uint32_t *>(rowScales + 2 * (g + 1));
-                if (!mbar_wait(barLoadFull(stage), phase, &abortFlag) ||
-                    !mbar_wait(barBEmpty(bStage), bPhase ^ 1u, &abortFlag)) {
-                    ok = false;
-                    break;
-                }
-                uint32_t s2, b2;
-                asm("prmt.b32 %0, %1, %1, 0x1010;" : "=r"(s2) : "r"(sb));
-                asm("prmt.b32 %0, %1, %1, 0x3232;" : "=r"(b2) : "r"(sb));
-                uint32_t w[4];
-                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
-                             : "r"(pAddrOf(stage) + (uint32_t)r * 32u + (uint32_t)half * 16u));
-                const uint32_t bBase = bAddrOf(bStage);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t o[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        // codes i and i+4 of the word as the bf16 pair (128+q_i, 128+q_{i+4})
-                        uint32_t pair = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
-                        uint32_t q2, v2;
-                        asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(q2) : "r"(pair), "r"(0x43004300u));
-                        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(v2) : "r"(q2), "r"(s2), "r"(b2));
-                        o[i] = v2;
-                    }
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(bBase + dstChunk[j]), "r"(o[0]),
-                                 "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                 : "memory");
-                }
-                fence_generic_to_async();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(barBFull(bStage));
-                    mbar_arrive(barLoadEmpty(stage));
-                }
-                if (++stage == kStagesLoad) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
-                if (++bStage == kStagesB) {
-                    bStage = 0;
-                    bPhase ^= 1u;
-                }
+            if (lane == 0) {
+                mbar_arrive(barWFull(grp));
+                mbar_arrive(barPackEmpty(ps));
             }
+            ps += kWStages;
+            if (ps >= kPackStages) {
+                ps -= kPackStages;
+                pPhase ^= 1u;
+            }
+            wPhase ^= 1u;
+            cur = nxt;
+            sb = sbNext;
         }
     } else {
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
-        const int quarter = warp & 3;  // TMEM lanes this warp may read
-        uint32_t acc = 0, accPhase = 0;
-        for (uint32_t u = blockIdx.x; u < units; u += gridDim.x) {
+        // ---------------- epilogue: TMEM -> registers -> shared -> global ----------------
+        // A thread holds one weight row's results for the unit's tokens (one token per accumulator
+        // column).  Per 32 tokens the four warps put their bf16 results into a [token][output]
+        // tile in shared memory and then write it out a token row at a time, 16 bytes per thread.
+        // All buffers alternate between two copies: a copy is rewritten two chunks (or units)
+        // later, after every thread has passed a barrier in between, hence after it was read.
+        const uint32_t quarter = (uint32_t)(warp & 3);
+        const uint32_t m = quarter * 32u + (uint32_t)lane;
+        const uint32_t t = (uint32_t)threadIdx.x - (2u + kDequantWarps) * 32u;  // 0..127
+        uint32_t acc = 0, accPhase = 0, chunk = 0, unitNo = 0;
+        bool ok = true;
+        for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, ++unitNo) {
             const RowTile tile = args.tiles[u / args.nTiles];
             const uint32_t nt = u % args.nTiles;
+            uint32_t *rowOf = rowTable + (unitNo & 1u) * kRowTile;
+            if (MODE == kModeDown) {
+                // where each of the unit's rows goes
+                for (uint32_t r = t; r < tile.rows; r += 128u) {
+                    uint32_t outRow = tile.rowStart + r;
+                    if (args.pairs) {
+                        const FFTokenExpertPair p = args.pairs[outRow];
+                        outRow = p.token * args.topK + p.rank;
+                    }
+                    rowOf[r] = outRow;
+                }
+                mbar_arrive(barRows);
+            }
             if (!mbar_wait_idle(barAccFull(acc), accPhase, &abortFlag)) break;
+            if (MODE == kModeDown && !mbar_wait(barRows, unitNo & 1u, &abortFlag)) break;
             tc_fence_after();
-            const uint32_t m = (uint32_t)(quarter * 32 + lane);  // row of the unit
-            const uint32_t taddr = tmemBase + acc * (uint32_t)kTileN + ((uint32_t)(quarter * 32) << 16);
-            const bool rowLive = m < tile.rows;
-            if (MODE == kModeGateUp) {
-                // accumulator columns 0..127 = gate rows, 128..255 = up rows of features [128 nt, +128)
-                uint16_t *dstRow = args.out + (size_t)(tile.rowStart + m) * args.N + (size_t)nt * 128;
+            const uint32_t taddr = tmemBase + acc * kAccCols + ((quarter * 32u) << 16);
 #pragma unroll 1
-                for (int c0 = 0; c0 < 128; c0 += 32) {
-                    uint32_t gr[32], ur[32];
-                    tc_load_32cols(taddr + (uint32_t)c0, gr);
-                    tc_load_32cols(taddr + 128u + (uint32_t)c0, ur);
-                    tc_wait_ld();
-                    uint32_t packed[16];
+            for (uint32_t c0 = 0; c0 < tile.rows; c0 += 32, ++chunk) {
+                uint32_t v[32];
+                tc_load_32cols(taddr + c0, v);
+                tc_wait_ld();
+                const uint32_t which = chunk & 1u, parity = (chunk >> 1) & 1u;
+                uint8_t *stage = stageBuf + which * kStageBytes;
+                if (MODE == kModeGateUp) {
+                    // lanes 0..63 hold gate, lanes 64..127 up of features [64 nt, +64).  The gate
+                    // warps hand the second 16 tokens' gates to the up warps and take the first 16
+                    // tokens' ups from them; either side then finishes 16 tokens of its feature.
+                    const bool isUp = m >= 64u;
+                    float *buf = xchg + which * (128u * kXchgPitch);
+                    float *mine = buf + m * kXchgPitch;
 #pragma unroll
-                    for (int blk = 0; blk < 4; ++blk) {
-                        // eight activations, stored as 0,4,1,5,2,6,3,7 for the down GEMM
-                        float a[8];
+                    for (int j = 0; j < 16; ++j) mine[j] = __uint_as_float(isUp ? v[j] : v[16 + j]);
+                    mbar_arrive(barXchg(which));
+                    if (!mbar_wait(barXchg(which), parity, &abortFlag)) {
+                        ok = false;
+                        break;
+                    }
+                    const float *theirs = buf + (m ^ 64u) * kXchgPitch;
+                    // tile [32 tokens][64 features in the interleaved order], 144-byte pitch
+                    uint16_t *col = reinterpret_cast<uint16_t *>(stage) + (isUp ? 16u : 0u) * (kStagePitchGateUp / 2) +
+                                    interleaved_position(m & 63u);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float g = __uint_as_float(gr[blk * 8 + i]);
-                            float uu = __uint_as_float(ur[blk * 8 + i]);
-                            if (args.roundGateUp) {
-                                g = bf2f(f2bf(g));
-                                uu = bf2f(f2bf(uu));
-                            }
-                            a[i] = gelu_tanh(g) * uu;
+                    for (int j = 0; j < 16; ++j) {
+                        const float own = __uint_as_float(isUp ? v[16 + j] : v[j]);
+                        const float other = theirs[j];
+                        float g = isUp ? other : own, uu = isUp ? own : other;
+                        if (args.roundGateUp) {
+                            g = bf2f(f2bf(g));
+                            uu = bf2f(f2bf(uu));
                         }
-                        packed[blk * 4 + 0] = (uint32_t)f2bf(a[0]) | ((uint32_t)f2bf(a[4]) << 16);
-                        packed[blk * 4 + 1] = (uint32_t)f2bf(a[1]) | ((uint32_t)f2bf(a[5]) << 16);
-                        packed[blk * 4 + 2] = (uint32_t)f2bf(a[2]) | ((uint32_t)f2bf(a[6]) << 16);
-                        packed[blk * 4 + 3] = (uint32_t)f2bf(a[3]) | ((uint32_t)f2bf(a[7]) << 16);
+                        col[(uint32_t)j * (kStagePitchGateUp / 2)] = f2bf(gelu_tanh_fast(g) * uu);
                     }
-                    if (rowLive && nt * 128 + (uint32_t)c0 < args.N) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2],
-                                                packed[4 * q + 3]);
+                    mbar_arrive(barStage(which));
+                    if (!mbar_wait(barStage(which), parity, &abortFlag)) {
+                        ok = false;
+                        break;
                     }
-                }
-            } else {
-                size_t outRow = tile.rowStart + m;
-                if (args.pairs && rowLive) {
-                    const FFTokenExpertPair p = args.pairs[tile.rowStart + m];
-                    outRow = (size_t)p.token * args.topK + p.rank;
-                }
-                uint16_t *dstRow = args.out + outRow * args.N + (size_t)nt * 256;
-#pragma unroll 1
-                for (int c0 = 0; c0 < 256; c0 += 32) {
-                    uint32_t vr[32];
-                    tc_load_32cols(taddr + (uint32_t)c0, vr);
-                    tc_wait_ld();
-                    if (rowLive && nt * 256 + (uint32_t)c0 < args.N) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(dstRow + c0);
+                    // a token row of the tile is 128 bytes: eight threads, 16 tokens per pass
+                    const uint32_t piece = t & 7u;
+                    const uint32_t col0 = nt * 64u + piece * 8u;
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t o[4];
+                    for (uint32_t pass = 0; pass < 2; ++pass) {
+                        const uint32_t tok = pass * 16u + (t >> 3);
+                        if (c0 + tok < tile.rows && col0 < args.N) {
+                            const uint4 val = *reinterpret_cast<const uint4 *>(stage + tok * kStagePitchGateUp + piece * 16u);
+                            *reinterpret_cast<uint4 *>(args.out + (size_t)(tile.rowStart + c0 + tok) * args.N + col0) = val;
+                        }
+                    }
+                } else {
+                    // tile [32 tokens][128 outputs], 272-byte pitch
+                    uint16_t *col = reinterpret_cast<uint16_t *>(stage) + m;
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                o[i] = (uint32_t)f2bf(__uint_as_float(vr[q * 8 + 2 * i])) |
-                                       ((uint32_t)f2bf(__uint_as_float(vr[q * 8 + 2 * i + 1])) << 16);
-                            dst[q] = make_uint4(o[0], o[1], o[2], o[3]);
+                    for (int j = 0; j < 32; ++j)
+                        col[(uint32_t)j * (kStagePitchDown / 2)] = f2bf(__uint_as_float(v[j]));
+                    mbar_arrive(barStage(which));
+                    if (!mbar_wait(barStage(which), parity, &abortFlag)) {
+                        ok = false;
+                        break;
+                    }
+                    // a token row of the tile is 256 bytes: sixteen threads, 8 tokens per pass
+                    const uint32_t piece = t & 15u;
+                    const uint32_t col0 = nt * 128u + piece * 8u;
+#pragma unroll
+                    for (uint32_t pass = 0; pass < 4; ++pass) {
+                        const uint32_t tok = pass * 8u + (t >> 4);
+                        if (c0 + tok < tile.rows && col0 < args.N) {
+                            const uint4 val = *reinterpret_cast<const uint4 *>(stage + tok * kStagePitchDown + piece * 16u);
+                            *reinterpret_cast<uint4 *>(args.out + (size_t)rowOf[c0 + tok] * args.N + col0) = val;
                         }
                     }
                 }
             }
+            if (!ok) break;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(barAccEmpty(acc));
@@ -923,14 +1025,14 @@ static EncodeTiledFn encode_tiled(const char **error) {
     return fn;
 }
 
-// bf16 activations [rows][k] (row pitch `strideElems`), box 64 x 128, 128-byte swizzle.
+// bf16 activations [rows][k] (row pitch `strideElems`), box 64 x kRowTile, 128-byte swizzle.
 static bool make_activation_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k,
                                 uint64_t strideElems, const char **error) {
     EncodeTiledFn fn = encode_tiled(error);
     if (!fn) return false;
     cuuint64_t dims[2] = {k, rows};
     cuuint64_t strides[1] = {strideElems * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTileM};
+    cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kRowTile};
     cuuint32_t elem[2] = {1, 1};
     CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
                      box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1002,9 +1104,8 @@ bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error) {
     return true;
 }
 
-static size_t gemm_smem_bytes(uint32_t K) {
-    return 1024 + (size_t)kStagesLoad * (kTileABytes + kTilePackedBytes) + (size_t)kStagesB * kTileBBytes +
-           (size_t)kTileN * (K / kTileK) * 2 * sizeof(uint16_t);
+static size_t gemm_smem_bytes() {
+    return 1024 + (size_t)kTokStages * kTokTileBytes + (size_t)kPackStages * kPackTileBytes + kEpilogueBytes;
 }
 
 template <int MODE>
@@ -1012,9 +1113,7 @@ static bool launch_gemm(FFContext *ctx, const CUtensorMap &mapA, const CUtensorM
                         const CUtensorMap &mapW1, const GemmArgs &args, uint32_t maxUnits,
                         cudaStream_t stream, const char **error) {
     auto kernel = k_grouped_int4_gemm<MODE>;
-    const size_t smem = gemm_smem_bytes(args.K);
-    if (smem > 226 * 1024) return fail(error, "contraction length too large for the GEMM's shared memory");
-    // the routed (K = f) and shared (K = sharedF) GEMMs alternate: the memo keeps the larger limit
+    const size_t smem = gemm_smem_bytes();
     static KernelSmemMemo memo;
     if (!memo.prepare(kernel, ctx->device, smem, kGemmThreads, nullptr, error)) return false;
     const uint32_t grid = std::max(1u, std::min<uint32_t>((uint32_t)ctx->smCount, maxUnits));
@@ -1066,7 +1165,7 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     }
     FF_CUDA_OK(cudaGetLastError(), error);
 
-    const uint32_t tileBound = pairs / 128 + (uint32_t)E;
+    const uint32_t tileBound = pairs / kRowTile + (uint32_t)E;
     CUtensorMap mapX, mapActs;
     if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)pairs + 256, c.d, c.d, error)) return false;
     if (!make_activation_map(&mapActs, ctx->acts, (uint64_t)pairs + 256, c.f, c.f, error)) return false;
@@ -1080,7 +1179,7 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     a.biasOff[1] = L.off.upBOff;
     a.K = c.d;
     a.N = c.f;
-    a.nTiles = (c.f + 127) / 128;
+    a.nTiles = (c.f + 63) / 64;
     a.tiles = tiles;
     a.counts = ctx->unitCount;
     a.out = ctx->acts;
@@ -1097,7 +1196,7 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     b.biasOff[0] = b.biasOff[1] = L.off.downBOff;
     b.K = c.f;
     b.N = c.d;
-    b.nTiles = (c.d + 255) / 256;
+    b.nTiles = (c.d + 127) / 128;
     b.out = partials;
     b.pairs = ctx->sortedPairs;
     return launch_gemm<kModeDown>(ctx, mapActs, L.routedMap[2], L.routedMap[2], b, tileBound * b.nTiles,
@@ -1124,7 +1223,7 @@ bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
                                                             (int)c.d, ctx->xSorted);
     }
     FF_CUDA_OK(cudaGetLastError(), error);
-    const uint32_t rowTiles = (tokens + 127) / 128;
+    const uint32_t rowTiles = (tokens + kRowTile - 1) / kRowTile;
     CUtensorMap mapX, mapActs;
     if (!make_activation_map(&mapX, ctx->xSorted, (uint64_t)tokens + 256, c.d, c.d, error)) return false;
     if (!make_activation_map(&mapActs, ctx->sharedActs, (uint64_t)tokens + 256, c.sharedF, c.sharedF, error))
@@ -1140,7 +1239,7 @@ bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     a.biasOff[1] = L.sharedOff.upBOff;
     a.K = c.d;
     a.N = c.sharedF;
-    a.nTiles = (c.sharedF + 127) / 128;
+    a.nTiles = (c.sharedF + 63) / 64;
     a.tiles = tiles;
     a.counts = counts;
     a.out = ctx->sharedActs;
@@ -1155,7 +1254,7 @@ bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
     b.biasOff[0] = b.biasOff[1] = L.sharedOff.downBOff;
     b.K = c.sharedF;
     b.N = c.d;
-    b.nTiles = (c.d + 255) / 256;
+    b.nTiles = (c.d + 127) / 128;
     b.out = y;
     b.pairs = nullptr;
     return launch_gemm<kModeDown>(ctx, mapActs, L.sharedMap[2], L.sharedMap[2], b, rowTiles * b.nTiles,
