@@ -444,8 +444,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit ran out or another thread of the CTA gave up; the
 // caller leaves its loop.  `abortFlag` lives in shared memory.  kSleep: pause between polls, for
 // the warps whose polling would otherwise take issue slots from the dequantizing warps.
+// The first poll stands alone in front of the loop: measured on the device, a wait that finds its
+// barrier already complete costs 7 cycles this way and about 200 when the poll sits inside the
+// bounded loop.
 template <bool kSleep>
-__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (kSleep) __nanosleep(40);
@@ -453,6 +456,11 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, vo
     }
     *abortFlag = 1u;
     return false;
+}
+template <bool kSleep>
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow<kSleep>(bar, parity, abortFlag);
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
     return mbar_wait_impl<false>(bar, parity, abortFlag);
@@ -487,10 +495,6 @@ __device__ __forceinline__ void tc_fence_after() {
 __device__ __forceinline__ void fence_generic_to_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
-}
 // 32 consecutive fp32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tc_load_32cols(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -522,19 +526,20 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smemAddr) {
     desc |= (uint64_t)2 << 61;
     return desc;
 }
-// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 128, N = `n`
-// (a multiple of 16 up to 256).
-__device__ __forceinline__ uint32_t umma_idesc_bf16_m128(uint32_t n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 256 (128 rows in
+// either CTA of the pair), N = `n` (a multiple of 32 up to 256, half of it in either CTA).
+__device__ __forceinline__ uint32_t umma_idesc_bf16_m256(uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((256u >> 4) << 24);
 }
-// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes x 16 bf16 (eight 32-bit columns per lane).
+// D[tmem] (+)= A[tmem] * B[smem] over the CTA pair: in either CTA, A is 128 lanes x 16 bf16
+// (eight 32-bit columns per lane), B half of the N rows, D 128 lanes x N columns.
 __device__ __forceinline__ void tc_mma_bf16_a_tmem(uint32_t tmemD, uint32_t tmemA, uint64_t descB,
                                                    uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n"
         "}\n" ::"r"(tmemD),
         "r"(tmemA), "l"(descB), "r"(idesc), "r"(accumulate)
         : "memory");
@@ -554,21 +559,88 @@ __device__ __forceinline__ void tc_store_32cols(uint32_t taddr, const uint32_t (
 __device__ __forceinline__ void tc_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+// ---- two CTAs of a cluster working as one tensor-core unit (cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the shared::cluster address of `addr` (a shared-memory address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+// arrive on a barrier that may live in the other CTA of the pair (`clusterAddr` from map_to_cta)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t clusterAddr) {
+    // (default semantics, release at CTA scope: a cluster-scope release holds the warp until everything it
+    // has in flight is acknowledged, over a thousand cycles here; what the other CTA's MMA reads
+    // from this CTA is ordered by the tcgen05 fences and the TMA's own barrier, not by this arrive)
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait on a barrier that the other CTA of the pair arrives on
+template <bool kSleep>
+__device__ __noinline__ bool mbar_wait_cluster_slow(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (kSleep) __nanosleep(40);
+        if ((i & 255u) == 255u && *abortFlag) return false;
+    }
+    *abortFlag = 1u;
+    return false;
+}
+template <bool kSleep>
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t *abortFlag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    return mbar_wait_cluster_slow<kSleep>(bar, parity, abortFlag);
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// This CTA's part of a tile that the pair's MMA reads from both CTAs; completes on the leader's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                                 uint32_t leaderBar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leaderBar)
+        : "memory");
+}
+// arrives once on the barrier at this shared-memory offset in both CTAs when the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"((uint16_t)3)
+        : "memory");
 }
 
 // ---- grouped INT4 GEMM ---------------------------------------------------------------------
 
 constexpr int kWeightRows = 128;  // weight rows of a unit = TMEM lanes of its accumulator
 constexpr int kTileK = 64;        // one quantization group per step
-constexpr int kTokStages = 6;     // token tiles (TMA destinations)
-constexpr int kPackStages = 6;    // packed-code tiles (TMA destinations)
-constexpr int kWStages = 4;       // dequantized weight tiles in TMEM, one per dequantizing group
+constexpr int kTokStages = 8;     // token half tiles (TMA destinations)
+constexpr int kPackStages = 8;    // packed-code tiles (TMA destinations)
+constexpr int kGroups = 4;        // dequantizing groups
+constexpr int kWStages = kGroups; // dequantized weight tiles in TMEM, one per dequantizing group
 constexpr int kDequantWarps = 16; // four groups of four warps; a group covers the 128 TMEM lanes
 // warp 0 TMA, warp 1 MMA, warps 2-17 dequantize, warps 18-21 epilogue (TMEM lane quarter = warp & 3)
 constexpr int kGemmThreads = (2 + kDequantWarps + 4) * 32;
-constexpr uint32_t kTokTileBytes = kRowTile * kTileK * 2;         // 24576
+constexpr uint32_t kTokHalfRows = kRowTile / 2;                   // rows of a token tile held by either CTA of a pair
+constexpr uint32_t kTokTileBytes = kTokHalfRows * kTileK * 2;     // 12288 (a multiple of the 1024-byte swizzle atom)
 constexpr uint32_t kPackTileBytes = kWeightRows * kTileK / 2;     // 4096: two [64 rows x 32 bytes] boxes
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCols = kRowTile;                           // accumulators at columns 0 and 192
@@ -577,8 +649,11 @@ constexpr int kXchgPitch = 17;                                    // floats per 
 constexpr uint32_t kXchgBytes = 2u * 128u * kXchgPitch * 4u;      // two buffers x 128 rows
 constexpr uint32_t kStagePitchGateUp = 64 * 2 + 16;               // bytes per token row of the output tile
 constexpr uint32_t kStagePitchDown = 128 * 2 + 16;
-constexpr uint32_t kStageBytes = 32u * kStagePitchDown;           // one 32-token tile (the larger mode)
-constexpr uint32_t kEpilogueBytes = kXchgBytes + 2u * kStageBytes + 2u * kRowTile * 4u;
+constexpr uint32_t kStageBytesGateUp = 32u * kStagePitchGateUp;   // one 32-token output tile
+constexpr uint32_t kStageBytesDown = 32u * kStagePitchDown;
+// gate/up: exchange buffers + two output tiles; down: two output tiles + two row tables
+constexpr uint32_t kEpilogueBytesGateUp = kXchgBytes + 2u * kStageBytesGateUp;
+constexpr uint32_t kEpilogueBytesDown = 2u * kStageBytesDown + 2u * kRowTile * 4u;
 static_assert(kWCol0 + kWStages * 32 <= kTmemCols, "tensor memory layout");
 static_assert(kRowTile % 32 == 0 && kRowTile <= 256, "row tile");
 
@@ -607,7 +682,7 @@ __device__ __forceinline__ uint32_t interleaved_position(uint32_t i) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_constant__ CUtensorMap mapW0,
                     const __grid_constant__ CUtensorMap mapW1, const GemmArgs args) {
     extern __shared__ uint8_t gemmSmemRaw[];
@@ -627,9 +702,12 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
     auto tokAddrOf = [&](uint32_t s) { return tokBase + s * kTokTileBytes; };
     auto packAddrOf = [&](uint32_t s) { return packBase + s * kPackTileBytes; };
     uint8_t *epilogueSmem = gemmSmemRaw + (packBase + kPackStages * kPackTileBytes - rawBase);
-    float *xchg = reinterpret_cast<float *>(epilogueSmem);
-    uint8_t *stageBuf = epilogueSmem + kXchgBytes;
-    uint32_t *rowTable = reinterpret_cast<uint32_t *>(stageBuf + 2u * kStageBytes);
+    constexpr uint32_t kStageBytes = MODE == kModeGateUp ? kStageBytesGateUp : kStageBytesDown;
+    float *xchg = reinterpret_cast<float *>(epilogueSmem);                                 // gate/up only
+    uint8_t *stageBuf = epilogueSmem + (MODE == kModeGateUp ? kXchgBytes : 0u);
+    uint32_t *rowTable = reinterpret_cast<uint32_t *>(stageBuf + 2u * kStageBytes);        // down only
+    uint32_t *scaleSlots = reinterpret_cast<uint32_t *>(
+        epilogueSmem + (MODE == kModeGateUp ? kEpilogueBytesGateUp : kEpilogueBytesDown));  // [ceil(groupsK/4)][512]
 
     const uint32_t barBase = smem_u32(barriers);
     auto barAt = [&](int i) { return barBase + 8u * (uint32_t)i; };
@@ -645,6 +723,12 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
     auto barStage = [&](int s) { return barAt(2 * kTokStages + 2 * kPackStages + 2 * kWStages + 6 + s); };
     const uint32_t barRows = barAt(2 * kTokStages + 2 * kPackStages + 2 * kWStages + 8);
 
+    // The two CTAs of a cluster work as one unit of the tensor core: the leader (rank 0) issues
+    // the MMAs for both.  Barriers that say "full" to the MMA issuer live in the leader and count
+    // both CTAs' arrivals; barriers that the MMAs' completion frees exist in either CTA and are
+    // signalled in both by one multicast commit.
+    const uint32_t ctaRank = cluster_cta_rank();
+    const bool leader = ctaRank == 0u;
     if (threadIdx.x == 0) {
         abortFlag = 0;
         for (int s = 0; s < kTokStages; ++s) {
@@ -656,12 +740,12 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
             mbar_init(barPackEmpty(s), 4);  // the four warps of the group that read it
         }
         for (int s = 0; s < kWStages; ++s) {
-            mbar_init(barWFull(s), 4);   // the four warps of the group that wrote it
+            mbar_init(barWFull(s), 8);   // (leader's is used) the four warps of the group in either CTA
             mbar_init(barWEmpty(s), 1);  // one tcgen05.commit
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(barAccFull(s), 1);   // one tcgen05.commit
-            mbar_init(barAccEmpty(s), 4);  // four epilogue warps
+            mbar_init(barAccEmpty(s), 8);  // (leader's is used) four epilogue warps in either CTA
             mbar_init(barXchg(s), 128);    // every epilogue thread
             mbar_init(barStage(s), 128);
         }
@@ -669,19 +753,27 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(&tmemBaseSlot)),
                      "r"(kTmemCols)
                      : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();  // the other CTA's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmemBase = tmemBaseSlot;
 
+    // A pair's unit: one row tile, two neighbouring weight-row tiles (this CTA takes 2 np + rank).
     const uint32_t rowTiles = args.counts[0];
-    const uint32_t units = rowTiles * args.nTiles;
+    const uint32_t nPairs = (args.nTiles + 1u) >> 1;
+    const uint32_t units = rowTiles * nPairs;
+    const uint32_t firstUnit = blockIdx.x >> 1, unitStride = gridDim.x >> 1;
+    auto tileOf = [&](uint32_t u) { return args.tiles[u / nPairs]; };
+    auto ntOf = [&](uint32_t u) { return 2u * (u % nPairs) + ctaRank; };
+    // accumulator columns of a tile: its rows to the next multiple of 32, half of them in either CTA
+    auto columnsOf = [&](const RowTile &tile) { return max(32u, (tile.rows + 31u) & ~31u); };
     // weight rows 0..127 of a unit: gate rows [64 nt, +64) | up rows [64 nt, +64) for the gate/up
     // GEMM, matrix rows [128 nt, +128) for the down GEMM; loaded as two boxes of 64 rows
 
@@ -690,10 +782,11 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
         if (lane == 0) {
             uint32_t ts = 0, tPhase = 0, ps = 0, pPhase = 0;
             bool ok = true;
-            for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                const RowTile tile = args.tiles[u / args.nTiles];
-                const uint32_t nt = u % args.nTiles;
-                const int row0 = (int)tile.rowStart;
+            for (uint32_t u = firstUnit; u < units && ok; u += unitStride) {
+                const RowTile tile = tileOf(u);
+                const uint32_t nt = ntOf(u);
+                // this CTA's half of the tile's rows
+                const int row0 = (int)(tile.rowStart + ctaRank * (columnsOf(tile) >> 1));
                 for (uint32_t g = 0; g < groupsK; ++g) {
                     if (!mbar_wait_idle(barPackEmpty(ps), pPhase ^ 1u, &abortFlag)) {
                         ok = false;
@@ -725,20 +818,19 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            uint32_t ts = 0, tPhase = 0, ws = 0, wPhase = 0, acc = 0, accPhase = 0;
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (lane == 0 && leader) {
+            uint32_t ts = 0, ws = 0, wPhase = 0, acc = 0, accPhase = 0;
             bool ok = true;
-            for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
-                const RowTile tile = args.tiles[u / args.nTiles];
-                // accumulator columns = the tile's rows, to the next multiple of 16
-                const uint32_t idesc = umma_idesc_bf16_m128(max(16u, (tile.rows + 15u) & ~15u));
-                if (!mbar_wait_idle(barAccEmpty(acc), accPhase ^ 1u, &abortFlag)) break;
+            for (uint32_t u = firstUnit; u < units && ok; u += unitStride) {
+                const RowTile tile = tileOf(u);
+                const uint32_t idesc = umma_idesc_bf16_m256(columnsOf(tile));
+                if (!mbar_wait_cluster<true>(barAccEmpty(acc), accPhase ^ 1u, &abortFlag)) break;
                 tc_fence_after();
                 const uint32_t tmemD = tmemBase + acc * kAccCols;
                 for (uint32_t g = 0; g < groupsK; ++g) {
-                    if (!mbar_wait(barTokFull(ts), tPhase, &abortFlag) ||
-                        !mbar_wait(barWFull(ws), wPhase, &abortFlag)) {
+                    // (the group that arrives here has also seen both token halves land)
+                    if (!mbar_wait_cluster<false>(barWFull(ws), wPhase, &abortFlag)) {
                         ok = false;
                         break;
                     }
@@ -752,19 +844,16 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
                         tc_mma_bf16_a_tmem(tmemD, tmemW + 8u * kk, descTok + 2u * kk, idesc,
                                            (g | kk) != 0u ? 1u : 0u);
                     }
-                    tc_commit(barTokEmpty(ts));
-                    tc_commit(barWEmpty(ws));
-                    if (++ts == kTokStages) {
-                        ts = 0;
-                        tPhase ^= 1u;
-                    }
+                    tc_commit_pair(barTokEmpty(ts));
+                    tc_commit_pair(barWEmpty(ws));
+                    if (++ts == kTokStages) ts = 0;
                     if (++ws == kWStages) {
                         ws = 0;
                         wPhase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                tc_commit(barAccFull(acc));
+                tc_commit_pair(barAccFull(acc));
                 if (++acc == 2) {
                     acc = 0;
                     accPhase ^= 1u;
@@ -782,52 +871,53 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
         const uint32_t tmemW = tmemBase + kWCol0 + grp * 32u + (((uint32_t)(warp & 3) * 32u) << 16);
         const uint32_t matrix = MODE == kModeGateUp ? (m >> 6) : 0u;
 
-        struct Cursor {
-            uint32_t u, g;          // unit and step inside the unit
-            const uint16_t *sg, *bg;  // the row's scales and biases (null: row past the matrix)
-        };
-        auto locate = [&](Cursor &c) {
-            c.sg = c.bg = nullptr;
-            if (c.u >= units) return;
-            const RowTile tile = args.tiles[c.u / args.nTiles];
-            const uint32_t nt = c.u % args.nTiles;
+        // The thread's scale/bias pairs of a unit (one per step it takes there) are fetched in one
+        // batch when it enters the unit and kept in a private column of shared memory, so that no
+        // global load is in flight in the steady loop (a load in flight would hold up the
+        // releasing arrive below for the load's whole latency).
+        uint32_t *myScales = scaleSlots + (uint32_t)(threadIdx.x - 64);  // [slot][512 threads]
+        uint32_t u = firstUnit, g = grp;   // the thread's current step: unit and step inside it
+        uint32_t gFirst = 0;               // its first step inside the current unit
+        auto enter_unit = [&]() {          // after u or g changed so that g < groupsK again, or at the start
+            while (g >= groupsK && u < units) {
+                g -= groupsK;
+                u += unitStride;
+            }
+            gFirst = g;
+            if (u >= units) return;
+            const RowTile tile = tileOf(u);
+            const uint32_t nt = ntOf(u);
             const uint32_t wRow = MODE == kModeGateUp ? nt * 64u + (m & 63u) : nt * 128u + m;
-            if (wRow >= args.N) return;
+            const bool liveRow = wRow < args.N;
             const uint8_t *blob = args.blobBase + (size_t)tile.expert * args.expertStride;
             // (selected, not indexed: a run-time index into the parameters would copy them to local memory)
             const uint32_t scaleOff = matrix ? args.scaleOff[1] : args.scaleOff[0];
             const uint32_t biasOff = matrix ? args.biasOff[1] : args.biasOff[0];
-            c.sg = reinterpret_cast<const uint16_t *>(blob + scaleOff) + (size_t)wRow * groupsK;
-            c.bg = reinterpret_cast<const uint16_t *>(blob + biasOff) + (size_t)wRow * groupsK;
-        };
-        auto advance = [&](Cursor &c, uint32_t steps) {
-            c.g += steps;
-            bool moved = false;
-            while (c.g >= groupsK && c.u < units) {
-                c.g -= groupsK;
-                c.u += gridDim.x;
-                moved = true;
+            const uint16_t *sg = reinterpret_cast<const uint16_t *>(blob + scaleOff) + (size_t)wRow * groupsK;
+            const uint16_t *bg = reinterpret_cast<const uint16_t *>(blob + biasOff) + (size_t)wRow * groupsK;
+            for (uint32_t i0 = 0; g + 4u * i0 < groupsK; i0 += 4) {
+                uint32_t v[4];
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const uint32_t gi = min(g + 4u * (i0 + i), groupsK - 1u);
+                    v[i] = liveRow ? ((uint32_t)__ldg(sg + gi) | ((uint32_t)__ldg(bg + gi) << 16)) : 0u;
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i)
+                    if (g + 4u * (i0 + i) < groupsK) myScales[(i0 + i) * (uint32_t)(kDequantWarps * 32)] = v[i];
             }
-            if (moved) locate(c);
         };
-        auto fetch = [&](const Cursor &c) -> uint32_t {  // scale | bias << 16 of the cursor's step
-            if (c.u >= units || !c.sg) return 0u;
-            return (uint32_t)__ldg(c.sg + c.g) | ((uint32_t)__ldg(c.bg + c.g) << 16);
-        };
-
-        Cursor cur{blockIdx.x, 0u, nullptr, nullptr};
-        locate(cur);
-        advance(cur, grp);
-        uint32_t sb = fetch(cur);
-        uint32_t ps = grp, pPhase = 0, wPhase = 0;  // kPackStages > group count: the first stage is `grp`
-        while (cur.u < units) {
-            Cursor nxt = cur;
-            advance(nxt, kWStages);
-            const uint32_t sbNext = fetch(nxt);
+        enter_unit();
+        const uint32_t leaderWFull = map_to_cta(barWFull(grp), 0u);
+        static_assert(kTokStages == kPackStages, "the dequantizers use one ring index for both");
+        uint32_t ps = grp % kPackStages, pPhase = 0, wPhase = 0;
+        while (u < units) {
+            const uint32_t sb = myScales[((g - gFirst) >> 2) * (uint32_t)(kDequantWarps * 32)];
             if (!mbar_wait(barPackFull(ps), pPhase, &abortFlag) ||
                 !mbar_wait(barWEmpty(grp), wPhase ^ 1u, &abortFlag))
                 break;
             tc_fence_after();
+
             uint32_t s2, b2;
             asm("prmt.b32 %0, %1, %1, 0x1010;" : "=r"(s2) : "r"(sb));
             asm("prmt.b32 %0, %1, %1, 0x3232;" : "=r"(b2) : "r"(sb));
@@ -853,11 +943,14 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
                 }
             }
             tc_store_32cols(tmemW, o);
+            // this CTA's half of the step's token tile must have landed before the MMA is told to go
+            const bool landed = mbar_wait(barTokFull(ps), pPhase, &abortFlag);
             tc_wait_st();
+            if (!landed) break;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(barWFull(grp));
+                mbar_arrive_cluster(leaderWFull);
                 mbar_arrive(barPackEmpty(ps));
             }
             ps += kWStages;
@@ -866,8 +959,8 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
                 pPhase ^= 1u;
             }
             wPhase ^= 1u;
-            cur = nxt;
-            sb = sbNext;
+            g += kWStages;
+            if (g >= groupsK) enter_unit();
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> shared -> global ----------------
@@ -881,9 +974,9 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
         const uint32_t t = (uint32_t)threadIdx.x - (2u + kDequantWarps) * 32u;  // 0..127
         uint32_t acc = 0, accPhase = 0, chunk = 0, unitNo = 0;
         bool ok = true;
-        for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, ++unitNo) {
-            const RowTile tile = args.tiles[u / args.nTiles];
-            const uint32_t nt = u % args.nTiles;
+        for (uint32_t u = firstUnit; u < units && ok; u += unitStride, ++unitNo) {
+            const RowTile tile = tileOf(u);
+            const uint32_t nt = ntOf(u);
             uint32_t *rowOf = rowTable + (unitNo & 1u) * kRowTile;
             if (MODE == kModeDown) {
                 // where each of the unit's rows goes
@@ -980,7 +1073,7 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
             if (!ok) break;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(barAccEmpty(acc));
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(barAccEmpty(acc), 0u));
             if (++acc == 2) {
                 acc = 0;
                 accPhase ^= 1u;
@@ -997,9 +1090,12 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
+    // neither CTA leaves (or frees its tensor memory) while the other may still arrive on its
+    // barriers or have MMAs reading its shared memory
+    cluster_sync_all();
     tc_fence_after();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase),
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmemBase),
                      "r"(kTmemCols)
                      : "memory");
     }
@@ -1025,14 +1121,15 @@ static EncodeTiledFn encode_tiled(const char **error) {
     return fn;
 }
 
-// bf16 activations [rows][k] (row pitch `strideElems`), box 64 x kRowTile, 128-byte swizzle.
+// bf16 activations [rows][k] (row pitch `strideElems`), box 64 x kTokHalfRows (the half of a row
+// tile that one CTA of a pair holds), 128-byte swizzle.
 static bool make_activation_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t k,
                                 uint64_t strideElems, const char **error) {
     EncodeTiledFn fn = encode_tiled(error);
     if (!fn) return false;
     cuuint64_t dims[2] = {k, rows};
     cuuint64_t strides[1] = {strideElems * 2};
-    cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kRowTile};
+    cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)kTokHalfRows};
     cuuint32_t elem[2] = {1, 1};
     CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
                      box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1104,8 +1201,10 @@ bool prefill_prepare_layer(FFContext *ctx, LayerStore &L, const char **error) {
     return true;
 }
 
-static size_t gemm_smem_bytes() {
-    return 1024 + (size_t)kTokStages * kTokTileBytes + (size_t)kPackStages * kPackTileBytes + kEpilogueBytes;
+static size_t gemm_smem_bytes(int mode, uint32_t K) {
+    const size_t scaleSlots = (size_t)((K / kTileK + kGroups - 1) / kGroups) * kDequantWarps * 32 * sizeof(uint32_t);
+    return 1024 + (size_t)kTokStages * kTokTileBytes + (size_t)kPackStages * kPackTileBytes +
+           (mode == kModeGateUp ? kEpilogueBytesGateUp : kEpilogueBytesDown) + scaleSlots;
 }
 
 template <int MODE>
@@ -1113,10 +1212,13 @@ static bool launch_gemm(FFContext *ctx, const CUtensorMap &mapA, const CUtensorM
                         const CUtensorMap &mapW1, const GemmArgs &args, uint32_t maxUnits,
                         cudaStream_t stream, const char **error) {
     auto kernel = k_grouped_int4_gemm<MODE>;
-    const size_t smem = gemm_smem_bytes();
+    const size_t smem = gemm_smem_bytes(MODE, args.K);
+    if (smem > 226 * 1024) return fail(error, "contraction length too large for the GEMM's shared memory");
     static KernelSmemMemo memo;
     if (!memo.prepare(kernel, ctx->device, smem, kGemmThreads, nullptr, error)) return false;
-    const uint32_t grid = std::max(1u, std::min<uint32_t>((uint32_t)ctx->smCount, maxUnits));
+    // clusters of two CTAs; a cluster takes (row tile, pair of weight-row tiles) units
+    const uint32_t pairUnits = (maxUnits + 1) / 2 + 1;
+    const uint32_t grid = 2u * std::max(1u, std::min<uint32_t>((uint32_t)ctx->smCount / 2u, pairUnits));
     {
         LaunchScope scope(ctx, stream, MODE == kModeGateUp ? "int4_gemm_gate_up_act" : "int4_gemm_down");
         kernel<<<grid, kGemmThreads, smem, stream>>>(mapA, mapW0, mapW1, args);
