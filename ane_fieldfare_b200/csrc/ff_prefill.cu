@@ -741,7 +741,7 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
         }
         for (int s = 0; s < kWStages; ++s) {
             mbar_init(barWFull(s), 8);   // (leader's is used) the four warps of the group in either CTA
-            mbar_init(barWEmpty(s), 1);  // one tcgen05.commit
+            mbar_init(barWEmpty(s), 1);  // (unused: the weight stages are released through the token ring)
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(barAccFull(s), 1);   // one tcgen05.commit
@@ -844,8 +844,9 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
                         tc_mma_bf16_a_tmem(tmemD, tmemW + 8u * kk, descTok + 2u * kk, idesc,
                                            (g | kk) != 0u ? 1u : 0u);
                     }
+                    // one signal per step: the token stage is free, and so is the weight stage that
+                    // the same step used (the dequantizers wait on the token ring's barrier, too)
                     tc_commit_pair(barTokEmpty(ts));
-                    tc_commit_pair(barWEmpty(ws));
                     if (++ts == kTokStages) ts = 0;
                     if (++ws == kWStages) {
                         ws = 0;
@@ -910,11 +911,16 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
         enter_unit();
         const uint32_t leaderWFull = map_to_cta(barWFull(grp), 0u);
         static_assert(kTokStages == kPackStages, "the dequantizers use one ring index for both");
-        uint32_t ps = grp % kPackStages, pPhase = 0, wPhase = 0;
+        uint32_t ps = grp % kPackStages, pPhase = 0, ownSteps = 0;
         while (u < units) {
             const uint32_t sb = myScales[((g - gFirst) >> 2) * (uint32_t)(kDequantWarps * 32)];
+            // The weight stage `grp` was last read by the MMAs of this group's previous step, four
+            // steps back: its completion is that step's signal on the token ring (stage ps - 4,
+            // which in a ring of eight is ps + 4; the group's n-th step, n >= 1, meets that
+            // barrier's completion number (n - 1) / 2).
+            static_assert(kTokStages == 2 * kWStages, "the weight stages are released through the token ring");
             if (!mbar_wait(barPackFull(ps), pPhase, &abortFlag) ||
-                !mbar_wait(barWEmpty(grp), wPhase ^ 1u, &abortFlag))
+                (ownSteps && !mbar_wait(barTokEmpty((ps + kWStages) % kTokStages), ((ownSteps - 1u) >> 1) & 1u, &abortFlag)))
                 break;
             tc_fence_after();
 
@@ -958,7 +964,7 @@ k_grouped_int4_gemm(const __grid_constant__ CUtensorMap mapTok, const __grid_con
                 ps -= kPackStages;
                 pPhase ^= 1u;
             }
-            wPhase ^= 1u;
+            ++ownSteps;
             g += kWStages;
             if (g >= groupsK) enter_unit();
         }
