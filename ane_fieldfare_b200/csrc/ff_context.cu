@@ -43,6 +43,9 @@ static bool dev_alloc(FFContext *ctx, T **ptr, size_t count, const char **error)
 static void free_layer(LayerStore &L) {
     cudaFree(L.experts);
     cudaFree(L.shared);
+    cudaFree(L.routerQ);
+    cudaFree(L.routerQScale);
+    cudaFree(L.routerQBias);
     cudaFree(L.routerW);
     cudaFree(L.routerScale);
     cudaFree(L.gain);
@@ -67,7 +70,8 @@ void ff_destroy(FFContext *ctx) {
                     ctx->acts, ctx->sharedActs, ctx->h1,
                     ctx->partials, ctx->xDev, ctx->yDev, ctx->xSorted, ctx->sortedPairs,
                     ctx->expertOffsets, ctx->blockCounts, ctx->units, ctx->unitCount,
-                    ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch, ctx->taggedLogits, ctx->taggedActs};
+                    ctx->errorFlag, ctx->gridBarrier, ctx->phaseStamps, ctx->mapScratch, ctx->taggedLogits, ctx->taggedActs,
+                    ctx->logitsRows, ctx->routeIds, ctx->routeWeights};
     for (void *p : ptrs) cudaFree(p);
     if (ctx->hostStream) cudaStreamDestroy(ctx->hostStream);
     if (ctx->mailbox) cudaFreeHost(const_cast<unsigned long long *>(ctx->mailbox));
@@ -354,6 +358,65 @@ bool ff_load_shared(FFContext *ctx, uint32_t layer, const FFProjection *gate,
     return true;
 }
 
+static void free_router(ff::LayerStore &L) {
+    cudaFree(L.routerW);
+    cudaFree(L.routerScale);
+    cudaFree(L.gain);
+    cudaFree(L.logitBias);
+    cudaFree(L.routerQ);
+    cudaFree(L.routerQScale);
+    cudaFree(L.routerQBias);
+    L.routerW = L.routerScale = L.gain = L.routerQScale = L.routerQBias = nullptr;
+    L.routerQ = nullptr;
+    L.logitBias = nullptr;
+}
+
+static bool upload(void **dst, const void *src, size_t bytes, const char **error) {
+    FF_CUDA_OK(cudaMalloc(dst, bytes), error);
+    FF_CUDA_OK(cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice), error);
+    return true;
+}
+
+bool ff_load_router_int8(FFContext *ctx, uint32_t layer, const uint8_t *codes, const uint16_t *scales,
+                         const uint16_t *biases, const uint16_t *effectiveScale,
+                         const uint16_t *perExpertScale, const float *logitBias, uint32_t experts,
+                         uint32_t d, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !codes || !scales || !biases) return fail(error, "null argument");
+    if (layer >= ctx->cfg.layers) return fail(error, "layer " + std::to_string(layer) + " out of range");
+    if (d != ctx->cfg.d) return fail(error, "router width does not match the context");
+    if (d % 64) return fail(error, "router width must be a multiple of the group size 64");
+    if (experts == 0 || experts > (uint32_t)kMaxExperts)
+        return fail(error, "numExperts > 256 is not supported");
+    if (experts != ctx->cfg.experts)
+        return fail(error, "router has " + std::to_string(experts) + " experts, the context expects " +
+                               std::to_string(ctx->cfg.experts));
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    LayerStore &L = ctx->layers[layer];
+    free_router(L);
+    const size_t groups = (size_t)experts * (d / 64);
+    if (!upload(reinterpret_cast<void **>(&L.routerQ), codes, (size_t)experts * d, error) ||
+        !upload(reinterpret_cast<void **>(&L.routerQScale), scales, groups * 2, error) ||
+        !upload(reinterpret_cast<void **>(&L.routerQBias), biases, groups * 2, error))
+        return false;
+    if (effectiveScale && !upload(reinterpret_cast<void **>(&L.routerScale), effectiveScale, (size_t)d * 2, error))
+        return false;
+    if (perExpertScale && !upload(reinterpret_cast<void **>(&L.gain), perExpertScale, (size_t)experts * 2, error))
+        return false;
+    if (logitBias && !upload(reinterpret_cast<void **>(&L.logitBias), logitBias, (size_t)experts * 4, error))
+        return false;
+    L.routerExperts = experts;
+    ctx->weightBytes += (size_t)experts * d + groups * 4;
+    // scratch of the INT8 router: logits of every row, and the one-token path's routes
+    if (!ctx->logitsRows) {
+        FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&ctx->logitsRows),
+                              (size_t)ctx->cfg.maxTokens * kMaxExperts * sizeof(float)), error);
+        FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&ctx->routeIds), (size_t)ctx->cfg.topK * sizeof(uint32_t)), error);
+        FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&ctx->routeWeights), (size_t)ctx->cfg.topK * sizeof(uint16_t)), error);
+    }
+    return true;
+}
+
 bool ff_load_router(FFContext *ctx, uint32_t layer, const uint16_t *weights,
                     const uint16_t *effectiveScale, const uint16_t *perExpertScale,
                     const float *logitBias, uint32_t experts, uint32_t d, const char **error) {
@@ -368,12 +431,7 @@ bool ff_load_router(FFContext *ctx, uint32_t layer, const uint16_t *weights,
                                std::to_string(ctx->cfg.experts));
     FF_CUDA_OK(cudaSetDevice(ctx->device), error);
     LayerStore &L = ctx->layers[layer];
-    cudaFree(L.routerW);
-    cudaFree(L.routerScale);
-    cudaFree(L.gain);
-    cudaFree(L.logitBias);
-    L.routerW = L.routerScale = L.gain = nullptr;
-    L.logitBias = nullptr;
+    free_router(L);
     const size_t wBytes = (size_t)experts * d * 2;
     FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(&L.routerW), wBytes), error);
     FF_CUDA_OK(cudaMemcpy(L.routerW, weights, wBytes, cudaMemcpyHostToDevice), error);

@@ -873,7 +873,17 @@ bool launch_decode_fused(FFContext *ctx, const LayerStore &L, const uint16_t *x,
                          uint16_t *y, cudaStream_t stream, const char **error, const DecodeHostHandoff *host) {
     const FFConfig &c = ctx->cfg;
     if (routed && !L.experts) return fail(error, "layer has no resident experts");
-    if (routed && !idsIn && !L.routerW) return fail(error, "layer has no resident router");
+    if (routed && !idsIn && !L.has_router()) return fail(error, "layer has no resident router");
+    if (routed && !idsIn && L.routerQ) {
+        // The kernel's own router reads bf16 rows.  An INT8 router runs as its own launches in
+        // front (logits, top-K), and the kernel takes the routes as given.
+        if (host) return fail(error, "the host hand-off needs a bf16 router");
+        if (L.routerExperts != L.expertCount) return fail(error, "router and layer disagree on the expert count");
+        if (!launch_router_topk(ctx, L, x, ctx->cfg.d, 1, ctx->routeIds, ctx->routeWeights, nullptr, stream, error))
+            return false;
+        idsIn = ctx->routeIds;
+        weightsIn = ctx->routeWeights;
+    }
     if (withShared && !L.shared) return fail(error, "layer has no resident shared FFN");
     if (!routed && !withShared) return fail(error, "nothing to compute");
     if (c.topK > 8) return fail(error, "decode supports at most 8 routes");

@@ -505,17 +505,105 @@ static bool launch_inline_job(FFContext *ctx, const GemvJob &job, cudaStream_t s
     return true;
 }
 
+// INT8 affine router (the shipped checkpoints' form), one warp per expert row and up to four
+// tokens.  The order of the reference's kernel (Metal/MoE/moe.metal:65-103) is kept and made
+// definite: lane l takes elements 64 g + 2 l and 64 g + 2 l + 1 of every group g in increasing g,
+// with x' = float(x) * float(effective scale): acc = fma(s_g, fma(q1, x1', q0 * x0'), acc), then
+// acc = fma(b_g, x0' + x1', acc); the lane sums are added by an xor butterfly (16, 8, 4, 2, 1) and the
+// per-expert logit bias comes last.
+constexpr int kInt8RouterTokens = 4;
+__global__ void __launch_bounds__(256)
+k_router_logits_int8(const uint8_t *W, const uint16_t *scales, const uint16_t *biases, const uint16_t *effScale,
+                     const float *bias, const uint16_t *x, uint32_t xStride, int T, int E, int D, float *logits) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    const int t0 = blockIdx.y * kInt8RouterTokens;
+    if (e >= E) return;
+    const int groups = D / 64;
+    const uint8_t *wr = W + (size_t)e * D;
+    const uint16_t *sr = scales + (size_t)e * groups, *br = biases + (size_t)e * groups;
+    float acc[kInt8RouterTokens];
+#pragma unroll
+    for (int r = 0; r < kInt8RouterTokens; ++r) acc[r] = 0.0f;
+    for (int g = 0; g < groups; ++g) {
+        const int idx = g * 64 + 2 * lane;
+        const uint32_t q = *reinterpret_cast<const uint16_t *>(wr + idx);
+        const float q0 = (float)(q & 0xFFu), q1 = (float)(q >> 8);
+        const float s = bf2f(sr[g]), b = bf2f(br[g]);
+        float e0 = 1.0f, e1 = 1.0f;
+        if (effScale) {
+            const uint32_t ev = *reinterpret_cast<const uint32_t *>(effScale + idx);
+            e0 = __uint_as_float(ev << 16);
+            e1 = __uint_as_float(ev & 0xFFFF0000u);
+        }
+#pragma unroll
+        for (int r = 0; r < kInt8RouterTokens; ++r) {
+            const int t = min(t0 + r, T - 1);
+            const uint32_t xv = *reinterpret_cast<const uint32_t *>(x + (size_t)t * xStride + idx);
+            float x0 = __uint_as_float(xv << 16), x1 = __uint_as_float(xv & 0xFFFF0000u);
+            if (effScale) {
+                x0 = x0 * e0;
+                x1 = x1 * e1;
+            }
+            acc[r] = fmaf(s, fmaf(q1, x1, q0 * x0), acc[r]);
+            acc[r] = fmaf(b, x0 + x1, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kInt8RouterTokens; ++r) {
+        float v = acc[r];
+#pragma unroll
+        for (int offset = 16; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
+        if (lane == 0 && t0 + r < T) logits[(size_t)(t0 + r) * E + e] = bias ? v + bias[e] : v;
+    }
+}
+
+// Top-K of logits rows, one warp per row (the rows' logits are in global memory).
+__global__ void __launch_bounds__(256)
+k_topk_rows(const float *logits, const uint16_t *gain, int T, int E, int K, uint32_t *ids, uint16_t *weights) {
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= T) return;
+    warp_topk(logits + (size_t)t * E, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
+}
+
+bool launch_router_logits_int8(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
+                               uint32_t tokens, float *logits, cudaStream_t stream, const char **error) {
+    const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
+    if (xStride % 2 || ((uintptr_t)x & 3)) return fail(error, "input rows must be 4-byte aligned");
+    dim3 grid((E + 7) / 8, (tokens + kInt8RouterTokens - 1) / kInt8RouterTokens);
+    {
+        LaunchScope scope(ctx, stream, "router_logits_int8");
+        k_router_logits_int8<<<grid, 256, 0, stream>>>(L.routerQ, L.routerQScale, L.routerQBias, L.routerScale,
+                                                       L.logitBias, x, xStride, (int)tokens, E, D, logits);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
 bool launch_router_topk(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
                         uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
                         cudaStream_t stream, const char **error) {
     if (tokens == 0) return true;
-    if (!L.routerW) return fail(error, "layer has no resident router");
+    if (!L.has_router()) return fail(error, "layer has no resident router");
+    const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
+    if (L.routerQ && tokens > kMaxGemvRows) {
+        float *lg = logits ? logits : ctx->logitsRows;
+        if (!launch_router_logits_int8(ctx, L, x, xStride, tokens, lg, stream, error)) return false;
+        {
+            LaunchScope scope(ctx, stream, "topk_rows");
+            k_topk_rows<<<(tokens + 7) / 8, 256, 0, stream>>>(lg, L.gain, (int)tokens, E, (int)ctx->cfg.topK, ids,
+                                                             weights);
+        }
+        FF_CUDA_OK(cudaGetLastError(), error);
+        return true;
+    }
     if (tokens > kMaxGemvRows)
         return launch_router_prefill(ctx, L, x, xStride, tokens, ids, weights, logits, stream, error);
-    const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
     float *lg = logits ? logits : ctx->logits;
-    dim3 grid((E + 7) / 8, tokens);
-    {
+    if (L.routerQ) {
+        if (!launch_router_logits_int8(ctx, L, x, xStride, tokens, lg, stream, error)) return false;
+    } else {
+        dim3 grid((E + 7) / 8, tokens);
         LaunchScope scope(ctx, stream, "router_logits");
         k_router_logits<<<grid, 256, 0, stream>>>(L.routerW, L.routerScale, L.logitBias, x, xStride,
                                                   E, D, lg);
@@ -560,10 +648,12 @@ bool launch_block_small(FFContext *ctx, const LayerStore &L, const uint16_t *x, 
     uint32_t *idsDev = ctx->ids;
     uint16_t *weightsDev = ctx->weights;
     if (!ids) {
-        if (!L.routerW) return fail(error, "layer has no resident router");
+        if (!L.has_router()) return fail(error, "layer has no resident router");
         if (L.routerExperts != L.expertCount) return fail(error, "router and layer disagree on the expert count");
-        dim3 grid((L.routerExperts + 7) / 8, tokens);
-        {
+        if (L.routerQ) {
+            if (!launch_router_logits_int8(ctx, L, x, xStride, tokens, ctx->logits, stream, error)) return false;
+        } else {
+            dim3 grid((L.routerExperts + 7) / 8, tokens);
             LaunchScope scope(ctx, stream, "router_logits");
             k_router_logits<<<grid, 256, 0, stream>>>(L.routerW, L.routerScale, L.logitBias, x,
                                                       xStride, (int)L.routerExperts, (int)c.d,

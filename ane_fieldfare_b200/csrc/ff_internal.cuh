@@ -113,6 +113,11 @@ struct LayerStore {
     uint16_t *gain = nullptr;
     float *logitBias = nullptr;
     uint32_t routerExperts = 0;
+    // INT8 affine router (the shipped checkpoints' form): codes [experts][d], one bf16 scale and
+    // bias per group of 64 inputs; set instead of routerW
+    uint8_t *routerQ = nullptr;
+    uint16_t *routerQScale = nullptr, *routerQBias = nullptr;
+    bool has_router() const { return routerW != nullptr || routerQ != nullptr; }
     // prefill: tensor maps over the packed weights (gate, up, down) of routed and shared blobs
     bool mapsReady = false;
     CUtensorMap routedMap[3];
@@ -135,6 +140,9 @@ struct FFContext {
 
     // decode / verify scratch
     float *logits = nullptr;        // [min(maxTokens,16)][experts]
+    float *logitsRows = nullptr;    // [maxTokens][experts], allocated with the first INT8 router
+    uint32_t *routeIds = nullptr;   // [topK] routes of the one-token path when the router runs as its own launch
+    uint16_t *routeWeights = nullptr;
     uint32_t *ids = nullptr;        // [maxTokens][topK]
     uint16_t *weights = nullptr;    // [maxTokens][topK]
     ff::RoutePlan *plan = nullptr;

@@ -168,6 +168,22 @@ class HotpathContext:
              None if es is None else es.ctypes.data, None if pe is None else pe.ctypes.data,
              None if lb is None else lb.ctypes.data, w.shape[0], w.shape[1])
 
+    def loadRouterInt8(self, layer: int, codes: np.ndarray, scales: np.ndarray, biases: np.ndarray,
+                       effectiveScale=None, perExpertScale=None, logitBias=None):
+        """The INT8 affine router of the shipped checkpoints: codes uint8 [experts][d], scales and
+        biases bf16 bits [experts][d/64] (Runtime/Inference/Model.swift:473-475)."""
+        q = np.ascontiguousarray(codes, dtype=np.uint8)
+        sc = np.ascontiguousarray(scales, dtype=np.uint16)
+        bi = np.ascontiguousarray(biases, dtype=np.uint16)
+        if sc.shape != (q.shape[0], q.shape[1] // 64) or bi.shape != sc.shape:
+            raise FieldfareError("router scales/biases must be [experts][d/64]")
+        es = None if effectiveScale is None else np.ascontiguousarray(effectiveScale, dtype=np.uint16)
+        pe = None if perExpertScale is None else np.ascontiguousarray(perExpertScale, dtype=np.uint16)
+        lb = None if logitBias is None else np.ascontiguousarray(logitBias, dtype=np.float32)
+        call("ff_load_router_int8", self.handle, layer, q.ctypes.data, sc.ctypes.data, bi.ctypes.data,
+             None if es is None else es.ctypes.data, None if pe is None else pe.ctypes.data,
+             None if lb is None else lb.ctypes.data, q.shape[0], q.shape[1])
+
     def expertAddress(self, layer: int, expert: int) -> int:
         return binding.load().ff_expert_address(self.handle, layer, expert)
 

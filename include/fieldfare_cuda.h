@@ -187,6 +187,16 @@ bool ff_load_router(FFContext *ctx, uint32_t layer, const uint16_t *weights,
                     const uint16_t *effectiveScale, const uint16_t *perExpertScale,
                     const float *logitBias, uint32_t experts, uint32_t d, const char **error);
 
+/* The router in the form the shipped checkpoints carry it: INT8 affine codes [experts][d] with one
+ * bf16 scale and bias per group of 64 inputs (Runtime/Inference/Model.swift:473-475; kernel body
+ * Metal/MoE/moe.metal:65-103), from HOST memory; the other arguments as for ff_load_router.
+ * Replaces any router the layer had.  Every operator that runs the router takes either form; the
+ * one-token kernel then runs the INT8 router as launches of its own in front. */
+bool ff_load_router_int8(FFContext *ctx, uint32_t layer, const uint8_t *codes, const uint16_t *scales,
+                         const uint16_t *biases, const uint16_t *effectiveScale,
+                         const uint16_t *perExpertScale, const float *logitBias, uint32_t experts,
+                         uint32_t d, const char **error);
+
 /* Device address of one resident expert blob (the entry the reference's address table holds:
  * Metal/MoE/moe.metal:576-593), 0 when absent. */
 uint64_t ff_expert_address(const FFContext *ctx, uint32_t layer, uint32_t expert);

@@ -374,6 +374,67 @@ void ffo_router_logits(const ffo_layer *L, const uint16_t *x, float *logits) {
     free(xs);
 }
 
+/* The INT8 affine router of the shipped checkpoints, in the order of the reference's kernel
+ * (Sources/ANEFieldfareHotpath/Metal/MoE/moe.metal:65-103), made definite where the kernel leaves
+ * it to the compiler: lane l takes elements 64 g + 2 l and 64 g + 2 l + 1 of every group g in
+ * increasing g, x' = float(x) * float(effective_scale) when a scale is given,
+ *   acc = fma(s_g, fma(q1, x1', q0 * x0'), acc);  acc = fma(b_g, x0' + x1', acc);
+ * the 32 lane sums are added by an xor butterfly (16, 8, 4, 2, 1); logit_bias[e] is added last.
+ * codes uint8 [E][D]; scales, biases bf16 [E][D/64]. */
+void ffo_router_logits_int8(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases,
+                            const uint16_t *effective_scale, const float *logit_bias, int32_t E,
+                            int32_t D, const uint16_t *x, float *logits) {
+    const int32_t groups = D / 64;
+    float *xs = (float *)malloc(sizeof(float) * (size_t)D);
+    for (int32_t d = 0; d < D; ++d) {
+        float v = ffo_bf16_to_float(x[d]);
+        if (effective_scale) v = v * ffo_bf16_to_float(effective_scale[d]);
+        xs[d] = v;
+    }
+    for (int32_t e = 0; e < E; ++e) {
+        const uint8_t *wr = codes + (int64_t)e * D;
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            float acc = 0.0f;
+            for (int32_t g = 0; g < groups; ++g) {
+                const int32_t idx = g * 64 + 2 * l;
+                const float s = ffo_bf16_to_float(scales[(int64_t)e * groups + g]);
+                const float b = ffo_bf16_to_float(biases[(int64_t)e * groups + g]);
+                const float q0 = (float)wr[idx], q1 = (float)wr[idx + 1];
+                const float x0 = xs[idx], x1 = xs[idx + 1];
+                acc = fmaf(s, fmaf(q1, x1, q0 * x0), acc);
+                acc = fmaf(b, x0 + x1, acc);
+            }
+            lane[l] = acc;
+        }
+        for (int offset = 16; offset >= 1; offset >>= 1) {
+            float next[32];
+            for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ offset];
+            memcpy(lane, next, sizeof(lane));
+        }
+        float v = lane[0];
+        if (logit_bias) v = v + logit_bias[e];
+        logits[e] = v;
+    }
+    free(xs);
+}
+
+void ffo_router_topk_int8(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases,
+                          const uint16_t *effective_scale, const float *logit_bias,
+                          const uint16_t *gain, int32_t E, int32_t D, int32_t K, const uint16_t *x,
+                          int32_t T, int32_t x_stride, uint32_t *ids, uint16_t *weights,
+                          float *logits_out) {
+#pragma omp parallel for schedule(static) if (!omp_in_parallel() && T > 8)
+    for (int32_t t = 0; t < T; ++t) {
+        float *logits = (float *)malloc(sizeof(float) * (size_t)E);
+        ffo_router_logits_int8(codes, scales, biases, effective_scale, logit_bias, E, D,
+                               x + (int64_t)t * x_stride, logits);
+        ffo_topk(logits, E, gain, K, ids + (int64_t)t * K, weights + (int64_t)t * K, NULL);
+        if (logits_out) memcpy(logits_out + (int64_t)t * E, logits, sizeof(float) * (size_t)E);
+        free(logits);
+    }
+}
+
 /* Selection rule and softmax of Metal/MoE/moe.metal:269-319 (serial top-8) and its CPU statement
  * Tests/ANEFieldfareUpstreamTests/Kernels/MoE/RouterTopKTests.swift:55-71: highest score first,
  * equal scores -> lower expert id; w_i = exp(l_i - l_0) / sum * gain[e_i], stored in 16 bits

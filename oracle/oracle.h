@@ -92,6 +92,14 @@ void ffo_expert_ffn(const uint8_t *blob, const ffo_offsets *off, int32_t D, int3
                     int32_t round_act, float *out, int32_t out_stride);
 
 void ffo_router_logits(const ffo_layer *L, const uint16_t *x, float *logits);
+void ffo_router_logits_int8(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases,
+                            const uint16_t *effective_scale, const float *logit_bias, int32_t E,
+                            int32_t D, const uint16_t *x, float *logits);
+void ffo_router_topk_int8(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases,
+                          const uint16_t *effective_scale, const float *logit_bias,
+                          const uint16_t *gain, int32_t E, int32_t D, int32_t K, const uint16_t *x,
+                          int32_t T, int32_t x_stride, uint32_t *ids, uint16_t *weights,
+                          float *logits_out);
 void ffo_topk(const float *logits, int32_t E, const uint16_t *gain, int32_t K, uint32_t *ids,
               uint16_t *weights, float *weights_f32);
 void ffo_router_topk(const ffo_layer *L, const uint16_t *x, int32_t T, int32_t x_stride,

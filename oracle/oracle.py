@@ -157,6 +157,27 @@ def expert_ffn(blob, off, D, F, x_bits, round_gate_up=False, round_act=True):
     return out
 
 
+def router_topk_int8(codes, scales, biases, x_bits, K, effective_scale=None, logit_bias=None, gain=None):
+    """INT8 affine router (Metal/MoE/moe.metal:65-103) + top-K: ids, 16-bit weights, logits."""
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint16)
+    biases = np.ascontiguousarray(biases, dtype=np.uint16)
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    E, D = codes.shape
+    T = x_bits.shape[0]
+    es = None if effective_scale is None else np.ascontiguousarray(effective_scale, dtype=np.uint16)
+    lb = None if logit_bias is None else np.ascontiguousarray(logit_bias, dtype=np.float32)
+    gn = None if gain is None else np.ascontiguousarray(gain, dtype=np.uint16)
+    ids = np.empty((T, K), dtype=np.uint32)
+    w = np.empty((T, K), dtype=np.uint16)
+    logits = np.empty((T, E), dtype=np.float32)
+    lib().ffo_router_topk_int8(_p(codes), _p(scales), _p(biases), _p(es) if es is not None else None,
+                               _p(lb) if lb is not None else None, _p(gn) if gn is not None else None,
+                               c_int32(E), c_int32(D), c_int32(K), _p(x_bits), c_int32(T),
+                               c_int32(x_bits.shape[1]), _p(ids), _p(w), _p(logits))
+    return ids, w, logits
+
+
 def router_topk(layer: LayerData, x_bits):
     x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
     T = x_bits.shape[0]

@@ -381,3 +381,31 @@ def test_golden_fixture(oracle):
     assert np.array_equal(y, z["y_partials_mode"])
     y1, _, _, _ = oracle.moe_layer(ld, x[:1], oracle.MODE_DECODE)
     assert np.array_equal(y1, z["y_decode_mode_row0"])
+
+
+def test_int8_router_against_float64(oracle):
+    """ffo_router_logits_int8 (Metal/MoE/moe.metal:65-103) against a float64 evaluation of
+    sum_k (q_k s_g + b_g) x_k e_k: equal within fp32 accumulation error, and the top-K indices
+    agree wherever the float64 scores are separated by more than that error."""
+    rng = np.random.default_rng(31)
+    E, D, K = 32, 256, 8
+    codes = rng.integers(0, 256, size=(E, D), dtype=np.uint8)
+    scales = synth.bf16_bits((rng.uniform(0.5, 1.5, size=(E, D // 64)) * 2e-3).astype(np.float32))
+    biases = synth.bf16_bits((-rng.uniform(0.2, 0.3, size=(E, D // 64))).astype(np.float32))
+    eff = synth.bf16_bits(rng.uniform(0.5, 1.5, size=D).astype(np.float32))
+    bias = rng.uniform(-0.1, 0.1, size=E).astype(np.float32)
+    x = synth.bf16_bits(rng.uniform(-1, 1, size=(5, D)).astype(np.float32))
+    ids, w, logits = oracle.router_topk_int8(codes, scales, biases, x, K, effective_scale=eff, logit_bias=bias)
+    s64 = np.repeat(oracle.bf16_to_float(scales).astype(np.float64), 64, axis=1)
+    b64 = np.repeat(oracle.bf16_to_float(biases).astype(np.float64), 64, axis=1)
+    w64 = codes.astype(np.float64) * s64 + b64
+    xe = oracle.bf16_to_float(x).astype(np.float64) * oracle.bf16_to_float(eff).astype(np.float64)[None, :]
+    want = xe @ w64.T + bias.astype(np.float64)[None, :]
+    scale = np.abs(xe) @ np.abs(w64).T
+    assert np.all(np.abs(logits - want) <= 4e-6 * scale + 1e-6)
+    for t in range(x.shape[0]):
+        order = np.argsort(-want[t], kind="stable")
+        gaps = np.abs(np.diff(want[t][order][:K + 1]))
+        if gaps.min() > 1e-4:
+            assert list(ids[t]) == list(order[:K])
+    assert np.all(np.abs(oracle.bf16_to_float(w).sum(axis=1) - 1.0) < 2e-2)
