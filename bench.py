@@ -693,6 +693,22 @@ def run_ours(args):
         use_burst = region_s < 1.0
         peak_tf = bf16_peak["burst_tflops"] if use_burst else bf16_peak["tflops"]
         info = ctx.info()
+        # flops the GEMM units issue, against the useful ones: a unit is (row tile of up to 192 rows of
+        # one expert, rounded up to 32 accumulator columns) x (128 weight rows, 64 gate + 64 up or 128
+        # down) x the whole contraction; the pair of weight-row tiles a CTA pair takes is padded to
+        # an even count.  From the expert offsets of the last step (read back after the timing).
+        _, offsets = hotpath.PrefillGroupedRoutedMoE(ctx).lastRoutes(PREFILL_TOKENS * K)
+        counts = np.diff(offsets.astype(np.int64))
+        def issued(rows_per_group, f_mid):
+            cols = 0
+            for c in rows_per_group:
+                full, rest = divmod(int(c), 192)
+                cols += full * 192 + (max(32, (rest + 31) // 32 * 32) if rest else 0)
+            gate_up = 2 * ((-(-f_mid // 64) + 1) // 2) * 128 * D     # weight rows issued x contraction
+            down = 2 * ((-(-D // 128) + 1) // 2) * 128 * f_mid
+            return 2 * cols * (gate_up + down)
+        issued_flops = issued(counts, F) + issued([PREFILL_TOKENS], FS)
+        gemm_flops = PREFILL_TOKENS * 2 * (K * 3 * F * D + 3 * FS * D)
         line["prefill"] = {
             "workload": "config3_prefill_4096tokens_zipf", "tokens_per_s": PREFILL_TOKENS / (pms * 1e-3),
             "ms_per_step": pms, "steps": psteps, "timed_region": spread(per_step, 1), "device_error_flag": err,
@@ -704,6 +720,10 @@ def run_ours(args):
                          "frac_of_measured_burst": tf / bf16_peak["burst_tflops"],
                          "frac_of_measured_sustained": tf / bf16_peak["tflops"],
                          "frac_of_nominal_2250TF": tf / 2250.0, "algorithmic_flops_per_step": flops},
+            "gemm_flops": {"useful": gemm_flops, "issued": issued_flops, "useful_over_issued": gemm_flops / issued_flops,
+                           "row_tiles": int(sum(-(-int(c) // 192) for c in counts)),
+                           "note": "issued = accumulator columns (rows of each expert to 32) x weight-row tiles of 128 "
+                                   "(an odd tile count padded for the CTA pair) x contraction"},
             "kernels": {} if args.quick else traced_kernels(ctx, lambda i: prefill_step(), 4)}
 
     # ================= stack: config 4, 30 layers x 32768 tokens, experts sharded over the ranks ====
