@@ -49,9 +49,16 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void *src, uint32_
 __device__ __forceinline__ void slot_release() { __syncwarp(); }
 // Bounded wait for the warp's copies; flips the parity.  On running out the error flag is raised
 // and the warp carries on (its rows are then wrong, the launch still ends).
-__device__ __forceinline__ void slot_wait(uint32_t bar, uint32_t &parity, uint32_t *errorFlag) {
+static __device__ __noinline__ bool slot_wait_slow(uint32_t bar, uint32_t parity) {
     bool done = false;
     for (uint32_t i = 0; i < kCopySpinLimit && !done; ++i) done = bar_try_wait(bar, parity);
+    return done;
+}
+// (The first poll stands alone: a poll inside the bounded loop measured about 200 cycles on a
+// barrier that was already complete, a stand-alone one 7.)
+__device__ __forceinline__ void slot_wait(uint32_t bar, uint32_t &parity, uint32_t *errorFlag) {
+    bool done = bar_try_wait(bar, parity);
+    if (!done) done = slot_wait_slow(bar, parity);
     if (!done && (threadIdx.x & 31) == 0) atomicExch(errorFlag, 10u);
     parity ^= 1u;
     __syncwarp();

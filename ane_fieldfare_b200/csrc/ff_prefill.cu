@@ -123,7 +123,9 @@ k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const
     for (int e0 = 0; e0 < E; e0 += kRouterExperts) {
         const int slice = e0 / kRouterExperts;
         {
-            bool done = false;
+            // (first poll stand-alone: inside the bounded loop it costs about 200 cycles even when the
+            // slice has landed)
+            bool done = rt_try_wait(barOf(slice), (uint32_t)(slice >> 1) & 1u);
             for (uint32_t spin = 0; spin < (1u << 22) && !done; ++spin) done = rt_try_wait(barOf(slice), (uint32_t)(slice >> 1) & 1u);
             if (!done && lane == 0) atomicExch(errorFlag, 11u);
         }

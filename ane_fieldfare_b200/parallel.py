@@ -48,6 +48,15 @@ class Placement:
         mine = torch.nonzero(self.rank_of == rank).reshape(-1)
         return mine[torch.argsort(self.local_of[mine])].tolist()
 
+    def tables_on(self, device):
+        """rank_of and local_of on `device`, copied there once (a copy per layer would make every
+        plan wait for the host)."""
+        cache = self.__dict__.setdefault("_device_tables", {})
+        key = str(device)
+        if key not in cache:
+            cache[key] = (self.rank_of.to(device), self.local_of.to(device))
+        return cache[key]
+
 
 def contiguous_placement(experts: int, world: int) -> Placement:
     """Expert e on rank e // (experts/world): contiguous blocks."""
@@ -90,8 +99,9 @@ def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int,
         dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
         local_all = flat - dest * experts_per_rank
     else:
-        dest = placement.rank_of.to(flat.device)[flat]
-        local_all = placement.local_of.to(flat.device)[flat]
+        rank_of, local_of = placement.tables_on(flat.device)
+        dest = rank_of[flat]
+        local_all = local_of[flat]
     order = torch.argsort(dest, stable=True)
     send_counts = torch.bincount(dest, minlength=world).to(torch.int64)
     local = local_all[order].to(torch.int32)
@@ -132,6 +142,8 @@ class PeerBuffers:
         name = (group if group is not None else dist.group.WORLD).group_name
         self.recv = symm.empty((self.capacity, row_elems), dtype=dtype, device=device)    # rows for my experts
         self.back = symm.empty((self.capacity, row_elems), dtype=dtype, device=device)    # partial rows of my tokens
+        self.ids = symm.empty((self.capacity,), dtype=torch.int32, device=device)          # their local expert ids
+        self.ids_handle = symm.rendezvous(self.ids, name)
         self.recv_handle = symm.rendezvous(self.recv, name)
         self.back_handle = symm.rendezvous(self.back, name)
         self.shape = (self.capacity, row_elems)
@@ -142,6 +154,9 @@ class PeerBuffers:
 
     def peer_back(self, rank: int) -> torch.Tensor:
         return self.back_handle.get_buffer(rank, self.shape, self.dtype)
+
+    def peer_ids(self, rank: int) -> torch.Tensor:
+        return self.ids_handle.get_buffer(rank, (self.capacity,), torch.int32)
 
     def barrier(self):
         self.recv_handle.barrier()
@@ -327,7 +342,7 @@ class ExpertParallelMoE:
             raise ValueError(f"{recv_total} rows exceed the peer buffers' capacity {pb.capacity}")
         self.last_recv_rows = recv_total
         token = plan.token.to(x.device)
-        local_ids = torch.empty(recv_total, dtype=torch.int32, device=x.device)
+        local_expert = plan.local_expert.to(x.device)
         # the shared FFN needs no exchange: it runs on a second stream beside the dispatch
         main = torch.cuda.current_stream()
         if self._side is None:
@@ -347,14 +362,11 @@ class ExpertParallelMoE:
                 offset = sum(counts[s][p] for s in range(me))
                 if n:
                     torch.index_select(x, 0, token[start:start + n], out=pb.peer_recv(p)[offset:offset + n])
+                    pb.peer_ids(p)[offset:offset + n].copy_(local_expert[start:start + n])
                 start += n
-            # the local expert ids travel with the collective (4 bytes a row)
-            dist.all_to_all_single(local_ids, plan.local_expert.to(x.device),
-                                   output_split_sizes=[counts[s][me] for s in range(W)],
-                                   input_split_sizes=counts[me], group=self.group)
-            pb.barrier()  # everybody's rows have landed
+            pb.barrier()  # everybody's rows and their local expert ids have landed
         with tm.phase("experts", x):
-            partial_rows = self.experts_fn(pb.recv[:recv_total], local_ids)
+            partial_rows = self.experts_fn(pb.recv[:recv_total], pb.ids[:recv_total])
         with tm.phase("combine", x):
             start = 0
             for s in range(W):
