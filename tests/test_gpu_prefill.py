@@ -105,6 +105,32 @@ def test_prefill_partials_tiny(tiny, oracle, tokens):
                        elementwise_tol=ELEMENTWISE_TOL)
 
 
+@pytest.mark.parametrize("tokens,experts_used", [(1, 8), (3, 8), (192, 8), (193, 8), (400, 8), (401, 9)])
+def test_prefill_partials_with_chosen_routes(tiny, oracle, tokens, experts_used):
+    """Row tiles at their edges: every token routed to the same eight experts (each expert then has
+    exactly `tokens` rows: one row, a full tile of 192, 192 + 1, two tiles + 16, and the other
+    experts none), and a ninth expert taking one route of the last token (a one-row expert behind
+    full ones).  Routes are handed in, as `PrefillGroupedRoutedMoE.encodeStreamedBatched` takes them
+    (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:275-326)."""
+    hp = _hp()
+    L, ctx = tiny
+    ld = oracle_layer(oracle, L)
+    x = workload.make_tokens(105, f"chosen{tokens}", tokens, L.d)
+    ids_np = np.tile(np.arange(2, 2 + L.topK, dtype=np.uint32), (tokens, 1))
+    if experts_used == 9:
+        ids_np[-1, -1] = 12
+    w_np = np.tile(synth.bf16_bits(np.full(L.topK, 1.0 / L.topK, dtype=np.float32)), (tokens, 1))
+    ids = torch.from_numpy(ids_np.astype(np.int32)).to(ctx.device)
+    partials = torch.full((tokens * L.topK, L.d), -99.0, dtype=torch.bfloat16, device=ctx.device)
+    hp.PrefillGroupedRoutedMoE(ctx).encodeStreamedBatched(None, 0, dev(x, ctx), ids, partials, tokens)
+    torch.cuda.synchronize()
+    assert ctx.info().deviceErrorFlag == 0
+    pairs, n = oracle.make_pairs(ids_np, w_np, tokens, L.topK)
+    want16 = oracle.route_partials(ld, x, pairs, n, tokens, bf16_weights=True)
+    assert_layer_close(hp.bf16_numpy(partials), want16, oracle, f"chosen routes T={tokens}",
+                       elementwise_tol=ELEMENTWISE_TOL)
+
+
 @pytest.mark.parametrize("tokens", [20, 300])
 def test_prefill_shared_ffn(tiny, full, oracle, tokens):
     hp = _hp()
