@@ -359,6 +359,46 @@ k_reduce_token_major(const uint16_t *partials, const uint32_t *rowIndex, const u
         (uint32_t)f2bf(acc0) | ((uint32_t)f2bf(acc1) << 16);
 }
 
+// The same reduce, eight outputs per thread with 128-bit loads (every element's chain is the one
+// above: rank ascending, then the residual); for rows that are 16-byte aligned.
+__global__ void __launch_bounds__(256)
+k_reduce_token_major_x8(const uint16_t *partials, const uint32_t *rowIndex, const uint16_t *weights,
+                        const uint16_t *residual, uint16_t *y, int T, int K, int D) {
+    const int perRow = D >> 3;
+    const size_t item = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (size_t)T * perRow) return;
+    const int t = (int)(item / perRow), d = (int)(item - (size_t)t * perRow) * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (int r = 0; r < K; ++r) {
+        const float w = bf2f(weights[(size_t)t * K + r]);
+        const size_t row = rowIndex ? (size_t)rowIndex[(size_t)t * K + r] : (size_t)t * K + r;
+        const uint4 v = *reinterpret_cast<const uint4 *>(partials + row * D + d);
+        const uint32_t p[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = fmaf(w, __uint_as_float(p[i] << 16), acc[2 * i]);
+            acc[2 * i + 1] = fmaf(w, __uint_as_float(p[i] & 0xFFFF0000u), acc[2 * i + 1]);
+        }
+    }
+    if (residual) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(residual + (size_t)t * D + d);
+        const uint32_t p[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[2 * i] += __uint_as_float(p[i] << 16);
+            acc[2 * i + 1] += __uint_as_float(p[i] & 0xFFFF0000u);
+        }
+    }
+    uint4 o;
+    o.x = (uint32_t)f2bf(acc[0]) | ((uint32_t)f2bf(acc[1]) << 16);
+    o.y = (uint32_t)f2bf(acc[2]) | ((uint32_t)f2bf(acc[3]) << 16);
+    o.z = (uint32_t)f2bf(acc[4]) | ((uint32_t)f2bf(acc[5]) << 16);
+    o.w = (uint32_t)f2bf(acc[6]) | ((uint32_t)f2bf(acc[7]) << 16);
+    *reinterpret_cast<uint4 *>(y + (size_t)t * D + d) = o;
+}
+
 // y = x * w * rsqrt(mean(x^2) + eps) per row; one CTA per row, fp32 throughout.
 __global__ void __launch_bounds__(256)
 k_rmsnorm(const uint16_t *x, const uint16_t *w, float eps, int D, uint16_t *y) {
@@ -705,11 +745,19 @@ bool launch_reduce(FFContext *ctx, const uint16_t *partials, const uint16_t *wei
                    const char **error, const uint32_t *rowIndex) {
     if (tokens == 0) return true;
     const int D = (int)ctx->cfg.d;
-    dim3 grid((D / 2 + 255) / 256, tokens);
+    const bool wide = D % 8 == 0 && !((reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(y) |
+                                        reinterpret_cast<uintptr_t>(residual)) & 15u);
     {
         LaunchScope scope(ctx, stream, "reduce_token_major");
-        k_reduce_token_major<<<grid, 256, 0, stream>>>(partials, rowIndex, weights, residual, y, (int)tokens,
-                                                       (int)ctx->cfg.topK, D);
+        if (wide) {
+            const size_t items = (size_t)tokens * (D / 8);
+            k_reduce_token_major_x8<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(
+                partials, rowIndex, weights, residual, y, (int)tokens, (int)ctx->cfg.topK, D);
+        } else {
+            dim3 grid((D / 2 + 255) / 256, tokens);
+            k_reduce_token_major<<<grid, 256, 0, stream>>>(partials, rowIndex, weights, residual, y, (int)tokens,
+                                                           (int)ctx->cfg.topK, D);
+        }
     }
     FF_CUDA_OK(cudaGetLastError(), error);
     return true;

@@ -294,11 +294,18 @@ k_route_scan(uint32_t *blockCounts, int blocks, int E, uint32_t *expertOffsets, 
     __shared__ uint32_t tileBase[kMaxExperts + 1];
     const int e = threadIdx.x;
     if (e < E) {
+        // eight blocks' counts are fetched together (independent loads), then turned into prefixes
         uint32_t run = 0;
-        for (int b = 0; b < blocks; ++b) {
-            const uint32_t c = blockCounts[(size_t)b * E + e];
-            blockCounts[(size_t)b * E + e] = run;
-            run += c;
+        for (int b0 = 0; b0 < blocks; b0 += 8) {
+            uint32_t c[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c[i] = b0 + i < blocks ? blockCounts[(size_t)(b0 + i) * E + e] : 0u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (b0 + i < blocks) {
+                    blockCounts[(size_t)(b0 + i) * E + e] = run;
+                    run += c[i];
+                }
         }
         total[e] = run;
     }
