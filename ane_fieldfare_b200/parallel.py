@@ -134,7 +134,7 @@ class PeerBuffers:
     stream) says when everybody's rows have landed.  One instance serves every layer of a stack.
     `available()` is false where symmetric memory cannot be set up (CPU tests, gloo)."""
 
-    def __init__(self, capacity_rows: int, row_elems: int, dtype, device, group=None):
+    def __init__(self, capacity_rows: int, row_elems: int, dtype, device, group=None, ids_width: int = 1):
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only
         import torch.distributed._symmetric_memory as symm
@@ -142,7 +142,8 @@ class PeerBuffers:
         name = (group if group is not None else dist.group.WORLD).group_name
         self.recv = symm.empty((self.capacity, row_elems), dtype=dtype, device=device)    # rows for my experts
         self.back = symm.empty((self.capacity, row_elems), dtype=dtype, device=device)    # partial rows of my tokens
-        self.ids = symm.empty((self.capacity,), dtype=torch.int32, device=device)          # their local expert ids
+        self.ids_width = int(ids_width)  # local expert ids per received row (top-K wide for one row per token)
+        self.ids = symm.empty((self.capacity, self.ids_width), dtype=torch.int32, device=device)
         self.ids_handle = symm.rendezvous(self.ids, name)
         self.recv_handle = symm.rendezvous(self.recv, name)
         self.back_handle = symm.rendezvous(self.back, name)
@@ -156,7 +157,7 @@ class PeerBuffers:
         return self.back_handle.get_buffer(rank, self.shape, self.dtype)
 
     def peer_ids(self, rank: int) -> torch.Tensor:
-        return self.ids_handle.get_buffer(rank, (self.capacity,), torch.int32)
+        return self.ids_handle.get_buffer(rank, (self.capacity, self.ids_width), torch.int32)
 
     def barrier(self):
         self.recv_handle.barrier()
@@ -220,7 +221,8 @@ class ExpertParallelMoE:
 
     def __init__(self, experts: int, top_k: int, router_fn: Callable, shared_fn: Callable,
                  experts_fn: Callable, reduce_fn: Callable, group=None,
-                 placement: Optional[Placement] = None, chunks: int = 1, peer: "Optional[PeerBuffers]" = None):
+                 placement: Optional[Placement] = None, chunks: int = 1, peer: "Optional[PeerBuffers]" = None,
+                 one_row_per_token: bool = False):
         self.group = group
         self.placement = placement
         self.world = dist.get_world_size(group)
@@ -234,12 +236,18 @@ class ExpertParallelMoE:
         self.chunks = max(1, int(chunks))
         self.peer = peer  # PeerBuffers: exchange rows by peer stores instead of the collective
         self._side = None  # second stream of the peer path (shared FFN beside the dispatch)
+        # peer path: a token's row crosses to a destination rank once, with all of the token's local
+        # expert ids there (needs an expert context created with topK = K and peer buffers with
+        # ids_width = K); otherwise once per route
+        self.one_row_per_token = bool(one_row_per_token)
         self.last_recv_rows = 0
         self.last_expert_counts = None  # routes per (global) expert of the last forward, on request
         self.count_experts = False
         self.timer = _NoTimer()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.peer is not None and self.one_row_per_token:
+            return self._forward_peer_tokens(x)
         if self.peer is not None:
             return self._forward_peer(x)
         T, K, W = x.shape[0], self.top_k, self.world
@@ -362,11 +370,11 @@ class ExpertParallelMoE:
                 offset = sum(counts[s][p] for s in range(me))
                 if n:
                     torch.index_select(x, 0, token[start:start + n], out=pb.peer_recv(p)[offset:offset + n])
-                    pb.peer_ids(p)[offset:offset + n].copy_(local_expert[start:start + n])
+                    pb.peer_ids(p)[offset:offset + n, 0].copy_(local_expert[start:start + n])
                 start += n
             pb.barrier()  # everybody's rows and their local expert ids have landed
         with tm.phase("experts", x):
-            partial_rows = self.experts_fn(pb.recv[:recv_total], pb.ids[:recv_total])
+            partial_rows = self.experts_fn(pb.recv[:recv_total], pb.ids[:recv_total, 0])
         with tm.phase("combine", x):
             start = 0
             for s in range(W):
@@ -381,13 +389,95 @@ class ExpertParallelMoE:
             return self.reduce_fn(pb.back[:T * K], weights, residual, row_index)
 
 
+    def _forward_peer_tokens(self, x: torch.Tensor) -> torch.Tensor:
+        """The peer-store exchange with one row per (token, destination rank) on dispatch: a token
+        whose routes name several experts of one rank crosses NVLink once, together with the K-wide
+        list of its local expert ids there (ids of other ranks' routes are replaced by an id past
+        the rank's experts, which the receiver's sort drops).  The partial rows come back one per
+        route, in the order the per-route plan gives, so the reduce is the same as everywhere."""
+        T, K, W = x.shape[0], self.top_k, self.world
+        tm, pb = self.timer, self.peer
+        epr = self.experts_per_rank
+        with tm.phase("router", x):
+            ids, weights = self.router_fn(x)
+        if self.count_experts:
+            self.last_expert_counts = torch.bincount(ids.reshape(-1).to(torch.int64), minlength=self.experts)
+        with tm.phase("plan", x):
+            plan = dispatch_plan(ids, epr, W, self.placement)
+            flat = ids.reshape(-1).to(torch.int64).clamp(0, self.experts - 1)
+            if self.placement is None:
+                dest = torch.div(flat, epr, rounding_mode="floor")
+                local = flat - dest * epr
+            else:
+                rank_of, local_of = self.placement.tables_on(x.device)
+                dest, local = rank_of[flat], local_of[flat]
+            dest, local = dest.reshape(T, K), local.reshape(T, K).to(torch.int32)
+            hit = torch.zeros((T, W), dtype=torch.bool, device=x.device)
+            hit.scatter_(1, dest, True)                                   # token t has a route to rank p
+            both = torch.cat([plan.send_counts.to(x.device), hit.sum(0)])  # routes, then tokens, per destination
+            table = torch.empty((W, 2 * W), dtype=torch.int64, device=x.device)
+            dist.all_gather_into_tensor(table, both, group=self.group)
+            counts = table.tolist()                                       # the step's only host read
+            order = plan.order.to(x.device)
+            row_index = torch.empty(T * K, dtype=torch.int32, device=x.device)
+            row_index[order] = torch.arange(T * K, dtype=torch.int32, device=x.device)
+        me = self.rank
+        routes = [[counts[s][p] for p in range(W)] for s in range(W)]        # [source][destination]
+        tokens = [[counts[s][W + p] for p in range(W)] for s in range(W)]
+        recv_tokens = sum(tokens[s][me] for s in range(W))
+        recv_routes = sum(routes[s][me] for s in range(W))
+        if max(recv_tokens, T * K) > pb.capacity or pb.ids_width != K:
+            raise ValueError("peer buffers too small (or not K ids wide) for one row per token")
+        self.last_recv_rows = recv_routes
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            with tm.phase("shared", x):
+                residual = self.shared_fn(x)
+        x.record_stream(self._side)
+        if residual is not None:
+            residual.record_stream(main)
+        with tm.phase("dispatch", x):
+            pb.barrier()  # every rank is done with the previous contents of the buffers
+            for p in range(W):
+                n = tokens[me][p]
+                if not n:
+                    continue
+                offset = sum(tokens[s][p] for s in range(me))
+                # the tokens with a route to p, in token order (no host read: their number is known)
+                mine = torch.argsort(~hit[:, p], stable=True)[:n]
+                torch.index_select(x, 0, mine, out=pb.peer_recv(p)[offset:offset + n])
+                pb.peer_ids(p)[offset:offset + n].copy_(
+                    torch.where(dest[mine] == p, local[mine], torch.full_like(local[mine], epr)))
+            pb.barrier()  # everybody's rows and id lists have landed
+        with tm.phase("experts", x):
+            got_ids = pb.ids[:recv_tokens]
+            partial_rows = self.experts_fn(pb.recv[:recv_tokens], got_ids)       # [recv_tokens * K, D]
+            # rows of the routes that are this rank's, in (source, token, rank) order
+            live = torch.argsort(~(got_ids.reshape(-1) < epr), stable=True)[:recv_routes]
+        with tm.phase("combine", x):
+            start = 0
+            for s in range(W):
+                n = routes[s][me]
+                offset = sum(routes[s][p] for p in range(me))  # where my block starts in s's per-route order
+                if n:
+                    torch.index_select(partial_rows, 0, live[start:start + n], out=pb.peer_back(s)[offset:offset + n])
+                start += n
+            pb.barrier()  # my tokens' partial rows have landed
+        main.wait_stream(self._side)
+        with tm.phase("reduce", x):
+            return self.reduce_fn(pb.back[:T * K], weights, residual, row_index)
+
+
 def cuda_layer_fns(home_ctx, expert_ctx, layer: int, expert_layer: Optional[int] = None):
     """The four callables for `ExpertParallelMoE` backed by libfieldfare_cuda.so.
 
     `home_ctx`: a HotpathContext holding the replicated router and shared FFN of `layer`
-    (topK = K); `expert_ctx`: a HotpathContext created with topK = 1 and experts = E/g holding this
-    rank's experts (in slot `expert_layer`, default `layer`), so a received row with one local
-    expert id is a one-route token."""
+    (topK = K); `expert_ctx`: a HotpathContext with experts = E/g holding this rank's experts (in
+    slot `expert_layer`, default `layer`), created with topK = 1 — a received row with one local
+    expert id is a one-route token — or, for one row per token and destination, with topK = K."""
     from . import hotpath
 
     router = hotpath.PrefillRouter(home_ctx)
@@ -412,9 +502,11 @@ def cuda_layer_fns(home_ctx, expert_ctx, layer: int, expert_layer: Optional[int]
         return y
 
     def experts_fn(rows, local_ids):
-        out = torch.empty_like(rows)
+        # one partial row per (received row, route slot of the expert context)
+        wide = expert_ctx.topK
+        out = torch.empty((rows.shape[0] * wide, rows.shape[1]), dtype=rows.dtype, device=rows.device)
         if rows.shape[0]:
-            routed.encodeStreamedBatched(None, slot, rows, local_ids.reshape(-1, 1).contiguous(), out,
+            routed.encodeStreamedBatched(None, slot, rows, local_ids.reshape(-1, wide).contiguous(), out,
                                          rows.shape[0])
         return out
 

@@ -313,6 +313,12 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
                                   maxTokens=tokens_local, device=local_rank)
     local = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=1,
                                    maxTokens=capacity, device=local_rank)
+    # the same experts behind a context that takes K routes per row: for the exchange that sends a
+    # token's row once per destination rank
+    local_k = None
+    if args.ep_comm in ("peer", "both"):
+        local_k = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=K,
+                                         maxTokens=STACK_TOKENS, device=local_rank)
     for i, L in enumerate(host_layers):
         home.loadShared(i, *L.shared_projections())
         home.loadRouter(i, L.routerW, logitBias=synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}"))
@@ -321,15 +327,19 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
         for slot in range(layers):
             L = host_layers[slot % len(host_layers)]
             mine = placements[slot].experts_of(rank)
-            local.loadLayer(slot, np.ascontiguousarray(L.blobs[mine]), L.layout.stride, L.layout.offsets,
-                            expertCount=epr)
+            blobs = np.ascontiguousarray(L.blobs[mine])
+            local.loadLayer(slot, blobs, L.layout.stride, L.layout.offsets, expertCount=epr)
+            if local_k is not None and placements[slot].rank_of is not contiguous[slot].rank_of:
+                local_k.loadLayer(slot, blobs, L.layout.stride, L.layout.offsets, expertCount=epr)
 
-    def make_blocks(placements, chunks, peer=None):
+    def make_blocks(placements, chunks, peer=None, one_row_per_token=False):
         out = []
         for slot in range(layers):
             # the home context is indexed by the distinct layer, the expert context by the stack's slot
-            fns = parallel.cuda_layer_fns(home, local, slot % len(host_layers), expert_layer=slot)
-            out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks, peer=peer))
+            fns = parallel.cuda_layer_fns(home, local_k if one_row_per_token else local, slot % len(host_layers),
+                                          expert_layer=slot)
+            out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks, peer=peer,
+                                                  one_row_per_token=one_row_per_token))
         return out
 
     x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
@@ -345,7 +355,7 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
     # ranks).  Experts are then placed so that every rank receives about the same number of rows
     # (the blob layout is untouched: a rank loads the blobs of its experts).
     contiguous = [parallel.contiguous_placement(E, world)] * layers
-    load_experts(contiguous)
+    load_experts(contiguous)  # (the K-wide expert context is loaded with the final placement only)
     blocks = make_blocks(contiguous, 1)
     for block in blocks:
         block.count_experts = True
@@ -362,12 +372,15 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
         ok = torch.ones(1, dtype=torch.float64, device=device)
         try:
             buffers = parallel.PeerBuffers(capacity, D, torch.bfloat16, device)
+            buffers_k = parallel.PeerBuffers(capacity, D, torch.bfloat16, device, ids_width=K)
         except Exception as exc:  # symmetric memory not available on this box
             peer_note = f"{type(exc).__name__}: {exc}"[:200]
             ok.zero_()
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if ok.item() == 1.0:
             variants["peer_stores"] = make_blocks(placements, 1, peer=buffers)
+            variants["peer_stores_one_row_per_token_and_rank"] = make_blocks(placements, 1, peer=buffers_k,
+                                                                             one_row_per_token=True)
         if args.ep_comm == "peer" and "peer_stores" in variants:
             del variants["nccl_all_to_all"]
 
@@ -419,10 +432,12 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
     dist.all_gather(rows, recv)
     rows = torch.cat(rows).cpu().numpy()  # [world, layers]
     finite = bool(torch.isfinite(y.float()).all().item())
-    err = home.info().deviceErrorFlag | local.info().deviceErrorFlag
+    err = home.info().deviceErrorFlag | local.info().deviceErrorFlag | (local_k.info().deviceErrorFlag if local_k else 0)
     peak = measured_bf16_peak()
     home.close()
     local.close()
+    if local_k is not None:
+        local_k.close()
     tf = stack_flops(layers) / (ms * 1e-3) / 1e12
     return {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens_expert_parallel", "gpus": world,
             "tokens_per_s": STACK_TOKENS / (ms * 1e-3), "ms_per_stack": ms, "steps": steps,
@@ -438,7 +453,9 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             "exchange_kinds": {"nccl_all_to_all": "all_to_all_single for dispatch and combine of every layer and chunk, "
                                                   "asynchronous to the GEMMs",
                                "peer_stores": "rows gathered and copied straight into the destination rank's buffer in "
-                                              "symmetric memory over NVLink, a barrier across the ranks after each"},
+                                              "symmetric memory over NVLink, a barrier across the ranks after each",
+                               "peer_stores_one_row_per_token_and_rank": "the same, a token's row sent once to every rank "
+                                              "that holds any of its experts, with its K-wide list of local expert ids"},
             "placement": "experts assigned to ranks by greedy balancing of the routes each expert of each layer "
                          "received in a first pass of the same stack"}
 

@@ -1,6 +1,7 @@
 """Expert parallelism on real GPUs: two NCCL ranks, experts split over them (contiguous blocks, and
 a load-balanced placement with the tokens cut into chunks whose exchanges overlap the GEMMs, and
-the same placement with the rows moved by peer stores into symmetric memory),
+the same placement with the rows moved by peer stores into symmetric memory, per route and once
+per token and destination),
 compared bit for bit with the single-GPU layer on the same tokens.  Needs two GPUs; skipped
 otherwise."""
 import os
@@ -64,9 +65,23 @@ def _worker(rank, world, port, results):
             y3 = peer.forward(x)
             torch.cuda.synchronize()
             same = same and bool(torch.equal(y3, want))
-        flags = home.info().deviceErrorFlag | local.info().deviceErrorFlag | full.info().deviceErrorFlag
+        # one row per (token, destination rank): the expert context takes K routes per row
+        wide = hotpath.HotpathContext(layers=1, experts=epr, d=SHAPE["d"], f=SHAPE["f"], sharedF=0,
+                                      topK=SHAPE["topK"], maxTokens=TOKENS * world, device=rank)
+        wide.loadLayer(0, np.ascontiguousarray(L.blobs[placement.experts_of(rank)]), L.layout.stride,
+                       L.layout.offsets, expertCount=epr)
+        buffers_k = parallel.PeerBuffers(TOKENS * SHAPE["topK"] * world, SHAPE["d"], torch.bfloat16, full.device,
+                                         ids_width=SHAPE["topK"])
+        once = parallel.ExpertParallelMoE(SHAPE["experts"], SHAPE["topK"],
+                                          *parallel.cuda_layer_fns(home, wide, 0, expert_layer=0),
+                                          placement=placement, peer=buffers_k, one_row_per_token=True)
+        for _ in range(2):
+            y4 = once.forward(x)
+            torch.cuda.synchronize()
+            same = same and bool(torch.equal(y4, want))
+        flags = wide.info().deviceErrorFlag | home.info().deviceErrorFlag | local.info().deviceErrorFlag | full.info().deviceErrorFlag
         results[rank] = (same, int(flags), rows)
-        for c in (full, home, local):
+        for c in (full, home, local, wide):
             c.close()
     finally:
         dist.destroy_process_group()
