@@ -44,7 +44,7 @@ def layer_errors(got: np.ndarray, ref: np.ndarray):
     return rel_l2, scaled, literal, peak_rel
 
 
-# Tolerances of bf16 layer outputs against the CPU oracle (north_star: "rel-L2 <= 1e-2 and
+# Tolerances of bf16 layer outputs against the CPU oracle (the target stated for this path: "rel-L2 <= 1e-2 and
 # max-abs <= 2e-2 in bf16"):
 #   relative L2 <= 1e-2, always;
 #   literal max-abs <= 2e-2 wherever the outputs are of unit scale (peak <= 1): asserted as

@@ -1,5 +1,5 @@
 """The layer stack of benchmark configuration 4, the unit-scale variants of configurations 1-3
-(where north_star's max-abs <= 2e-2 is asserted as written), and the inputs the library refuses
+(where the stated max-abs <= 2e-2 is asserted as written), and the inputs the library refuses
 before (or instead of) touching memory it does not own."""
 import ctypes
 import dataclasses
@@ -98,7 +98,7 @@ def test_stack_of_three_layers_at_the_benchmark_shape(oracle):
         ctx.close()
 
 
-# ---- unit-scale variants: outputs of peak <= 1, the literal bound of north_star ---------------
+# ---- unit-scale variants: outputs of peak <= 1, the stated bound, literally ---------------
 
 @pytest.fixture(scope="module")
 def unit_full():
