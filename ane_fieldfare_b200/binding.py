@@ -106,6 +106,7 @@ SIGNATURES = {
                                              POINTER(FFMoEGroup), POINTER(c_uint32),
                                              POINTER(FFMoETile), POINTER(c_uint32), _ERR]),
     "ff_last_prefill_routes": (c_bool, [c_void_p, POINTER(FFTokenExpertPair), _P, _ERR]),
+    "ff_sort_routes": (c_bool, [c_void_p, _P, c_uint32, c_uint32, _P, _P, _P, _ERR]),
 }
 
 _lib = None

@@ -333,6 +333,17 @@ static bool moe_layer_host_one_token(FFContext *ctx, uint32_t layer, const uint1
     return true;
 }
 
+bool ff_sort_routes(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, uint32_t groups,
+                    FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !groupIds || !sortedPairs || !offsets) return fail(error, "null argument");
+    if ((reinterpret_cast<uintptr_t>(sortedPairs) & 15u) || (reinterpret_cast<uintptr_t>(groupIds) & 3u) ||
+        (reinterpret_cast<uintptr_t>(offsets) & 3u))
+        return fail(error, "sorted pairs must be 16-byte aligned, ids and offsets 4-byte aligned");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    return launch_route_sort(ctx, groupIds, tokens, groups, sortedPairs, offsets, stream, error);
+}
+
 bool ff_moe_layer_host(FFContext *ctx, uint32_t layer, const uint16_t *hostX, uint32_t tokens,
                        uint16_t *hostY, const char **error) {
     if (error) *error = nullptr;

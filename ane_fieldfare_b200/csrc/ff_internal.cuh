@@ -262,6 +262,8 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
                            cudaStream_t stream, const char **error);
 bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uint32_t xStride,
                            uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error);
+bool launch_route_sort(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, uint32_t groups,
+                       FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream, const char **error);
 bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *x,
                            uint32_t xStride, uint32_t tokens, uint32_t *ids, uint16_t *weights,
                            float *logits, cudaStream_t stream, const char **error);

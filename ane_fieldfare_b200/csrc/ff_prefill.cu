@@ -1320,6 +1320,39 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
                                   stream, error);
 }
 
+// The stable counting sort of routes by a group id, on its own: `groupIds` [tokens][K] on the device
+// (ids >= groups are dropped), `sortedPairs` receives (token, group, rank, 0) in (group, token,
+// rank) order, `offsets` [groups + 1] the first row of every group.  Uses the context's permute
+// scratch.
+bool launch_route_sort(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, uint32_t groups,
+                       FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream, const char **error) {
+    const FFConfig &c = ctx->cfg;
+    if (tokens == 0) return true;
+    if (!ctx->xSorted) return fail(error, "context was created with maxTokens <= 16: no prefill scratch");
+    if (groups == 0 || groups > c.experts) return fail(error, "group count must be 1..experts of the context");
+    if (tokens > c.maxTokens) return fail(error, "rows exceed the context's maxTokens");
+    const int T = (int)tokens, K = (int)c.topK, E = (int)groups;
+    const uint32_t blocks = (tokens + kSortTokens - 1) / kSortTokens;
+    const size_t sortSmem = (size_t)kSortTokens * K * sizeof(uint32_t);
+    RowTile *tiles = reinterpret_cast<RowTile *>(ctx->units);
+    {
+        LaunchScope scope(ctx, stream, "route_count");
+        k_route_count<<<blocks, 256, sortSmem, stream>>>(groupIds, T, K, E, ctx->blockCounts);
+    }
+    {
+        LaunchScope scope(ctx, stream, "route_scan");
+        k_route_scan<<<1, 256, 0, stream>>>(ctx->blockCounts, (int)blocks, E, offsets, tiles, ctx->maxUnits / 2,
+                                            ctx->unitCount);
+    }
+    {
+        LaunchScope scope(ctx, stream, "route_scatter");
+        k_route_scatter<<<blocks, 256, sortSmem, stream>>>(groupIds, nullptr, T, K, E, ctx->blockCounts, offsets,
+                                                           sortedPairs);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
 bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uint32_t xStride,
                            uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error) {
     const FFConfig &c = ctx->cfg;

@@ -439,6 +439,18 @@ class PrefillGroupedRoutedMoE:
         call("ff_moe_prefill", self.context.handle, layer, _ptr(hidden), stride, queryCount,
              _ptr(routeIDs), _ptr(routePartials), _stream(stream))
 
+    def sortRoutesOnDevice(self, stream, groupIds: torch.Tensor, groups: int):
+        """The device permute on its own: routes [tokens][K] (int32 group ids; ids >= groups are
+        dropped) sorted by (group, token, rank).  Returns (pairs int32 [tokens*K][4] with columns
+        token, group, rank, 0 — rows past the kept routes are unwritten —, offsets int32 [groups+1]),
+        both on the device; asynchronous on the stream."""
+        tokens = groupIds.shape[0]
+        pairs = torch.empty((tokens * self.context.topK, 4), dtype=torch.int32, device=groupIds.device)
+        offsets = torch.empty(groups + 1, dtype=torch.int32, device=groupIds.device)
+        call("ff_sort_routes", self.context.handle, _ptr(groupIds), tokens, groups, _ptr(pairs), _ptr(offsets),
+             _stream(stream))
+        return pairs, offsets
+
     def lastRoutes(self, pairCount: int):
         """Sorted pairs and per-expert offsets of the last encodeStreamedBatched (synchronizes)."""
         pairs = (FFTokenExpertPair * max(1, pairCount))()

@@ -84,7 +84,7 @@ def balanced_placement(load, world: int) -> Placement:
 
 
 def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int,
-                  placement: Optional[Placement] = None) -> DispatchPlan:
+                  placement: Optional[Placement] = None, route_sorter: Optional[Callable] = None) -> DispatchPlan:
     """Routes ordered by destination rank, (token, rank) order kept inside a destination.  Expert
     ids past the group's experts raise on the CPU; on a GPU, where looking at them would stall the
     stream, they are clamped into range instead (the library's own router never produces one)."""
@@ -102,6 +102,13 @@ def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int,
         rank_of, local_of = placement.tables_on(flat.device)
         dest = rank_of[flat]
         local_all = local_of[flat]
+    if route_sorter is not None and flat.is_cuda:
+        # the library's counting sort (three launches) in place of a general sort and a histogram
+        pairs, offsets = route_sorter(dest.to(torch.int32).reshape(tokens, k), world)
+        token = pairs[:, 0].to(torch.int64)
+        order = token * k + pairs[:, 2].to(torch.int64)
+        send_counts = (offsets[1:] - offsets[:-1]).to(torch.int64)
+        return DispatchPlan(order, send_counts, local_all[order].to(torch.int32), token)
     order = torch.argsort(dest, stable=True)
     send_counts = torch.bincount(dest, minlength=world).to(torch.int64)
     local = local_all[order].to(torch.int32)
@@ -222,7 +229,7 @@ class ExpertParallelMoE:
     def __init__(self, experts: int, top_k: int, router_fn: Callable, shared_fn: Callable,
                  experts_fn: Callable, reduce_fn: Callable, group=None,
                  placement: Optional[Placement] = None, chunks: int = 1, peer: "Optional[PeerBuffers]" = None,
-                 one_row_per_token: bool = False):
+                 one_row_per_token: bool = False, route_sorter: Optional[Callable] = None):
         self.group = group
         self.placement = placement
         self.world = dist.get_world_size(group)
@@ -240,6 +247,8 @@ class ExpertParallelMoE:
         # expert ids there (needs an expert context created with topK = K and peer buffers with
         # ids_width = K); otherwise once per route
         self.one_row_per_token = bool(one_row_per_token)
+        # (group ids int32 [T][K], groups) -> (pairs int32 [T*K][4], offsets int32 [groups+1]) on the device
+        self.route_sorter = route_sorter
         self.last_recv_rows = 0
         self.last_expert_counts = None  # routes per (global) expert of the last forward, on request
         self.count_experts = False
@@ -258,7 +267,7 @@ class ExpertParallelMoE:
             self.last_expert_counts = torch.bincount(ids.reshape(-1).to(torch.int64), minlength=self.experts)
         with tm.phase("plan", x):
             bounds = [T * c // self.chunks for c in range(self.chunks + 1)]
-            plans = [dispatch_plan(ids[bounds[c]:bounds[c + 1]], self.experts_per_rank, W, self.placement)
+            plans = [dispatch_plan(ids[bounds[c]:bounds[c + 1]], self.experts_per_rank, W, self.placement, self.route_sorter)
                      for c in range(self.chunks)]
             send = torch.stack([p.send_counts for p in plans]).to(x.device)        # [chunks, world]
             # counts of every run to every rank in one exchange: rank r receives column r of every
@@ -337,7 +346,7 @@ class ExpertParallelMoE:
         if self.count_experts:
             self.last_expert_counts = torch.bincount(ids.reshape(-1).to(torch.int64), minlength=self.experts)
         with tm.phase("plan", x):
-            plan = dispatch_plan(ids, self.experts_per_rank, W, self.placement)
+            plan = dispatch_plan(ids, self.experts_per_rank, W, self.placement, self.route_sorter)
             table = torch.empty((W, W), dtype=torch.int64, device=x.device)    # [source][destination]
             dist.all_gather_into_tensor(table, plan.send_counts.to(x.device), group=self.group)
             counts = table.tolist()                                             # the step's only host read
@@ -403,7 +412,7 @@ class ExpertParallelMoE:
         if self.count_experts:
             self.last_expert_counts = torch.bincount(ids.reshape(-1).to(torch.int64), minlength=self.experts)
         with tm.phase("plan", x):
-            plan = dispatch_plan(ids, epr, W, self.placement)
+            plan = dispatch_plan(ids, epr, W, self.placement, self.route_sorter)
             flat = ids.reshape(-1).to(torch.int64).clamp(0, self.experts - 1)
             if self.placement is None:
                 dest = torch.div(flat, epr, rounding_mode="floor")
@@ -469,6 +478,14 @@ class ExpertParallelMoE:
         main.wait_stream(self._side)
         with tm.phase("reduce", x):
             return self.reduce_fn(pb.back[:T * K], weights, residual, row_index)
+
+
+def cuda_route_sorter(home_ctx):
+    """`route_sorter` for ExpertParallelMoE backed by the library's device permute (ff_sort_routes);
+    `home_ctx` needs topK = K, at least as many experts as there are ranks and maxTokens > 16."""
+    from . import hotpath
+    grouping = hotpath.PrefillGroupedRoutedMoE(home_ctx)
+    return lambda group_ids, groups: grouping.sortRoutesOnDevice(None, group_ids.contiguous(), groups)
 
 
 def cuda_layer_fns(home_ctx, expert_ctx, layer: int, expert_layer: Optional[int] = None):

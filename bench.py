@@ -332,6 +332,8 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             if local_k is not None and placements[slot].rank_of is not contiguous[slot].rank_of:
                 local_k.loadLayer(slot, blobs, L.layout.stride, L.layout.offsets, expertCount=epr)
 
+    sorter = parallel.cuda_route_sorter(home)
+
     def make_blocks(placements, chunks, peer=None, one_row_per_token=False):
         out = []
         for slot in range(layers):
@@ -339,7 +341,7 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             fns = parallel.cuda_layer_fns(home, local_k if one_row_per_token else local, slot % len(host_layers),
                                           expert_layer=slot)
             out.append(parallel.ExpertParallelMoE(E, K, *fns, placement=placements[slot], chunks=chunks, peer=peer,
-                                                  one_row_per_token=one_row_per_token))
+                                                  one_row_per_token=one_row_per_token, route_sorter=sorter))
         return out
 
     x0 = hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + rank, "stack.x", tokens_local, D), device)
@@ -367,6 +369,8 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
     # two ways to move the rows: the collective (tokens in chunks whose exchanges overlap the GEMMs)
     # and peer stores into symmetric memory; both are checked and timed, the faster one is the line
     variants = {"nccl_all_to_all": make_blocks(placements, args.ep_chunks)}
+    if args.ep_chunks != 1:
+        variants["nccl_all_to_all_unchunked"] = make_blocks(placements, 1)
     peer_note = None
     if args.ep_comm in ("peer", "both"):
         ok = torch.ones(1, dtype=torch.float64, device=device)
@@ -382,7 +386,8 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             variants["peer_stores_one_row_per_token_and_rank"] = make_blocks(placements, 1, peer=buffers_k,
                                                                              one_row_per_token=True)
         if args.ep_comm == "peer" and "peer_stores" in variants:
-            del variants["nccl_all_to_all"]
+            variants.pop("nccl_all_to_all", None)
+            variants.pop("nccl_all_to_all_unchunked", None)
 
     # the first layer's output for the first rows against ff_moe_layer on one context that holds all
     # experts of that layer: the same bits
@@ -452,6 +457,7 @@ def measure_stack(torch, dist, hotpath, workload, host_layers, rank, local_rank,
             "output_finite": finite, "device_error_flag": int(err),
             "exchange_kinds": {"nccl_all_to_all": "all_to_all_single for dispatch and combine of every layer and chunk, "
                                                   "asynchronous to the GEMMs",
+                               "nccl_all_to_all_unchunked": "the same with the local tokens in one run",
                                "peer_stores": "rows gathered and copied straight into the destination rank's buffer in "
                                               "symmetric memory over NVLink, a barrier across the ranks after each",
                                "peer_stores_one_row_per_token_and_rank": "the same, a token's row sent once to every rank "

@@ -349,6 +349,15 @@ bool ff_group_token_expert_pairs(const FFTokenExpertPair *pairs, uint64_t pairCo
                                  uint32_t *groupCount, FFMoETile *tiles, uint32_t *tileCount,
                                  const char **error);
 
+/* The device-side permute on its own (the sort of PrefillMoEGrouping.groupTokenExpertPairs,
+ * Kernels/Prefill/MoE/PrefillMoEGrouping.swift:49-110, by any group id): `groupIds` [tokens][topK] on
+ * the device, ids >= `groups` are dropped; `sortedPairs` (device) receives (token, group, rank, 0)
+ * in (group, token, rank) order, `offsets` (device, [groups + 1]) every group's first row.  The
+ * expert-parallel dispatch sorts a rank's routes by destination rank with it.  Asynchronous. */
+bool ff_sort_routes(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, uint32_t groups,
+                    FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream,
+                    const char **error);
+
 /* Device-side result of the last ff_moe_prefill permute, copied to the host after a sync:
  * the expert-sorted pairs and per-expert row offsets [experts+1].  For parity tests. */
 bool ff_last_prefill_routes(FFContext *ctx, FFTokenExpertPair *sortedPairs, uint32_t *offsets,

@@ -51,7 +51,8 @@ def _worker(rank, world, port, results):
                         L.layout.offsets, expertCount=epr)
         balanced = parallel.ExpertParallelMoE(SHAPE["experts"], SHAPE["topK"],
                                               *parallel.cuda_layer_fns(home, local, 0, expert_layer=1),
-                                              placement=placement, chunks=3)
+                                              placement=placement, chunks=3,
+                                              route_sorter=parallel.cuda_route_sorter(home))
         y2 = balanced.forward(x)
         torch.cuda.synchronize()
         same = same and bool(torch.equal(y2, want))
@@ -74,7 +75,8 @@ def _worker(rank, world, port, results):
                                          ids_width=SHAPE["topK"])
         once = parallel.ExpertParallelMoE(SHAPE["experts"], SHAPE["topK"],
                                           *parallel.cuda_layer_fns(home, wide, 0, expert_layer=0),
-                                          placement=placement, peer=buffers_k, one_row_per_token=True)
+                                          placement=placement, peer=buffers_k, one_row_per_token=True,
+                                          route_sorter=parallel.cuda_route_sorter(home))
         for _ in range(2):
             y4 = once.forward(x)
             torch.cuda.synchronize()

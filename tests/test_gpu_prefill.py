@@ -131,6 +131,30 @@ def test_prefill_partials_with_chosen_routes(tiny, oracle, tokens, experts_used)
                        elementwise_tol=ELEMENTWISE_TOL)
 
 
+@pytest.mark.parametrize("tokens,groups", [(17, 2), (300, 5), (700, 16)])
+def test_sort_routes_by_any_group_id(tiny, tokens, groups):
+    """ff_sort_routes: the device permute on its own, by an arbitrary group id (the expert-parallel
+    dispatch sorts by destination rank with it).  Against a stable sort on the host: (group, token,
+    rank) order, as PrefillMoEGrouping.groupTokenExpertPairs gives it
+    (Kernels/Prefill/MoE/PrefillMoEGrouping.swift:49-110); ids past `groups` are dropped."""
+    hp = _hp()
+    L, ctx = tiny
+    rng = np.random.default_rng(tokens)
+    ids = rng.integers(0, groups + 1, size=(tokens, L.topK)).astype(np.int32)   # `groups` itself: dropped
+    pairs, offsets = hp.PrefillGroupedRoutedMoE(ctx).sortRoutesOnDevice(
+        None, torch.from_numpy(ids).to(ctx.device), groups)
+    torch.cuda.synchronize()
+    flat = ids.reshape(-1)
+    keep = np.flatnonzero(flat < groups)
+    order = keep[np.argsort(flat[keep], kind="stable")]
+    want_offsets = np.concatenate([[0], np.cumsum(np.bincount(flat[keep], minlength=groups))])
+    assert np.array_equal(offsets.cpu().numpy(), want_offsets.astype(np.int32))
+    got = pairs.cpu().numpy()[:order.size]
+    assert np.array_equal(got[:, 0], order // L.topK)
+    assert np.array_equal(got[:, 1], flat[order])
+    assert np.array_equal(got[:, 2], order % L.topK)
+
+
 @pytest.mark.parametrize("tokens", [20, 300])
 def test_prefill_shared_ffn(tiny, full, oracle, tokens):
     hp = _hp()
