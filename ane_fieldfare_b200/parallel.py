@@ -304,13 +304,14 @@ class ExpertParallelMoE:
         residual = None
         backs = []
         for c in range(self.chunks):
+            if c == 0:
+                # the shared FFN needs no exchange: it is queued while the first dispatch is in flight
+                with tm.phase("shared", x):
+                    residual = self.shared_fn(x)
             with tm.phase("dispatch", x):
                 rows, local = ready(pending)
                 if c + 1 < self.chunks:
                     pending = dispatch(c + 1)
-            if c == 0:
-                with tm.phase("shared", x):
-                    residual = self.shared_fn(x)
             with tm.phase("experts", x):
                 partial_rows = self.experts_fn(rows, local)
             with tm.phase("combine", x):
