@@ -43,31 +43,30 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 
 // ---- router for many rows ------------------------------------------------------------------
 
-// One warp per token.  The token's (scaled) inputs sit in shared memory as fp32; for every
-// expert the warp forms the logit in the order the decode router uses (lane l chains fmaf over
-// [256 i + 8 l, +8), butterfly 16..1, then the logit bias), so logits and indices are bitwise
-// those of the single-row kernel.  Then the warp-wide top-K.
-constexpr int kRouterWarps = 4;
+// For every expert the logit is formed in the order the decode router uses (lane l chains fmaf
+// over [256 i + 8 l, +8) for i ascending, butterfly 16..1, then the logit bias), so logits and
+// indices are bitwise those of the single-row kernel.  Then the warp-wide top-K.
+//
+// A warp owns kTok tokens and walks the experts eight at a time with a register tile of
+// kTok x 8 running sums.  The tokens' inputs sit in shared memory as bf16 for the whole kernel;
+// the router rows stream through a small ring, one [8 experts x 256 inputs] block per copy (a
+// tiled bulk tensor copy issued by a producer warp, completion on an mbarrier), in exactly the
+// order the chains consume them: block i of a slice holds, for lane l, its eight elements of
+// step i.  Per block a lane turns the 8 x 8 router values and its kTok x 8 inputs into fp32 once
+// and issues 8 x kTok x 8 fmaf, element by element over all chains, so consecutive fmaf are
+// independent.  A CTA takes 32 tokens (4096 tokens = 128 CTAs, one wave); shared memory holds
+// their inputs whatever the split into warps, and the split that measured best is sixteen warps of
+// two tokens (four warps per scheduler hide the shared-memory and conversion latencies): 164 us
+// for 4096 tokens, against 182 us with eight warps of four, 214 us with four warps of eight, and
+// 197 us for the previous kernel (whole eight-expert slices in shared memory, four tokens per
+// warp, four warps per SM in two waves, packed FMAs fed by three integer-pipe cycles of conversions
+// each).  In-kernel cycle counts: the chains 135 us of which 10 % waiting for blocks, top-K 15 us.
+constexpr int kRouterTokensPerCta = 32;  // computing warps x tokens per warp (one more warp issues the copies)
+constexpr int kRouterExperts = 8;   // experts per slice = rows of a streamed block
+constexpr int kRouterBlockK = 256;  // inputs per streamed block: one step of every lane's chain
+constexpr int kRouterRing = 8;      // blocks in flight
+constexpr uint32_t kRouterBlockBytes = kRouterExperts * kRouterBlockK * 2;
 
-// Each warp owns kRouterTokens tokens and walks the experts eight at a time with a register tile
-// of kRouterTokens x 8 running sums, so a router row (read from the CTA's slice buffer) feeds 4 tokens and an
-// input chunk read from shared memory feeds 8 experts.  Per (token, expert) the chain is exactly
-// the single-row kernel's: lane l, chunks i ascending, elements ascending, then the butterfly.
-constexpr int kRouterTokens = 4;   // tokens per warp
-constexpr int kRouterExperts = 8;  // experts per register tile
-
-// Router rows of a slice of eight experts come into shared memory by one bulk copy (two buffers,
-// completion on an mbarrier each) and feed every warp of the CTA: the router matrix is read once
-// per 16 tokens instead of once per 4.
-__device__ __forceinline__ void rt_bar_init(uint32_t bar) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void rt_copy(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 __device__ __forceinline__ bool rt_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -81,155 +80,205 @@ __device__ __forceinline__ bool rt_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+static __device__ __noinline__ bool rt_wait_slow(uint32_t bar, uint32_t parity) {
+    bool done = false;
+    for (uint32_t spin = 0; spin < (1u << 22) && !done; ++spin) done = rt_try_wait(bar, parity);
+    return done;
+}
+// bounded; the first poll stands alone (inside the bounded loop it costs about 200 cycles even
+// when the barrier is complete)
+__device__ __forceinline__ bool rt_wait(uint32_t bar, uint32_t parity) {
+    return rt_try_wait(bar, parity) || rt_wait_slow(bar, parity);
+}
 
-__global__ void __launch_bounds__(kRouterWarps * 32)
-k_router_rows(const uint16_t *W, const uint16_t *scale, const float *bias, const uint16_t *gain,
-              const uint16_t *x, uint32_t xStride, int T, int E, int D, int K, uint32_t *ids,
-              uint16_t *weights, float *logitsOut, uint32_t *errorFlag) {
+template <int kTok>
+__global__ void __launch_bounds__((kRouterTokensPerCta / kTok + 1) * 32)
+k_router_rows(const __grid_constant__ CUtensorMap mapW, const uint16_t *scale, const float *bias,
+              const uint16_t *gain, const uint16_t *x, uint32_t xStride, int T, int E, int D, int K,
+              uint32_t *ids, uint16_t *weights, float *logitsOut, uint32_t *errorFlag) {
+    constexpr int kRouterWarps = kRouterTokensPerCta / kTok;
     extern __shared__ __align__(128) uint8_t rsmRaw[];
-    __shared__ __align__(8) uint64_t sliceBar[2];
+    __shared__ __align__(8) uint64_t ringBar[2 * kRouterRing];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // two slice buffers (kRouterExperts rows each), then per warp: kRouterTokens input rows as bf16
-    // and kRouterTokens x kMaxExperts logits
-    const size_t sliceBytes = (size_t)kRouterExperts * D * 2;
-    const size_t perWarp = (size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4;
-    uint8_t *warpBase = rsmRaw + 2 * sliceBytes + warp * perWarp;
-    uint16_t *xs = reinterpret_cast<uint16_t *>(warpBase);
-    float *lg = reinterpret_cast<float *>(warpBase + (size_t)kRouterTokens * D * 2);
-    const uint32_t barBase = (uint32_t)__cvta_generic_to_shared(&sliceBar[0]);
-    auto barOf = [&](int slice) { return barBase + 8u * (uint32_t)(slice & 1); };
-    const uint32_t bufAddr = (uint32_t)__cvta_generic_to_shared(rsmRaw);
+    // ring of router blocks, then per computing warp: kTok input rows as bf16 and kTok x E logits
+    const size_t perWarp = (size_t)kTok * D * 2 + (size_t)kTok * E * 4;
+    const uint32_t ringAddr = (uint32_t)__cvta_generic_to_shared(rsmRaw);
+    const uint32_t barBase = (uint32_t)__cvta_generic_to_shared(&ringBar[0]);
+    auto barFull = [&](int s) { return barBase + 8u * (uint32_t)s; };
+    auto barEmpty = [&](int s) { return barBase + 8u * (uint32_t)(kRouterRing + s); };
     const int nSlices = (E + kRouterExperts - 1) / kRouterExperts;
-    auto request = [&](int slice) {
-        const int rows = min(kRouterExperts, E - slice * kRouterExperts);
-        rt_copy(bufAddr + (uint32_t)((slice & 1) * sliceBytes), W + (size_t)slice * kRouterExperts * D,
-                (uint32_t)((size_t)rows * D * 2), barOf(slice));
-    };
+    const int nBlocks = (D + kRouterBlockK - 1) / kRouterBlockK;
     if (threadIdx.x == 0) {
-        rt_bar_init(barOf(0));
-        rt_bar_init(barOf(1));
+        for (int st = 0; st < kRouterRing; ++st) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barFull(st)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(barEmpty(st)), "r"(kRouterWarps) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        request(0);
-        if (nSlices > 1) request(1);
     }
-    const int t0 = (blockIdx.x * kRouterWarps + warp) * kRouterTokens;
-    const int nTok = max(0, min(kRouterTokens, T - t0));
-    for (int tt = 0; tt < kRouterTokens; ++tt) {
+    __syncthreads();
+
+    if (warp == kRouterWarps) {
+        // ---- producer: every block of every slice, in consumption order ----
+        if (lane == 0) {
+            uint32_t st = 0, phase = 0;
+            bool ok = true;
+            for (int sl = 0; sl < nSlices && ok; ++sl)
+                for (int i = 0; i < nBlocks; ++i) {
+                    if (!rt_wait(barEmpty(st), phase ^ 1u)) {
+                        atomicExch(errorFlag, 11u);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barFull(st)),
+                                 "r"(kRouterBlockBytes)
+                                 : "memory");
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+                        " [%0], [%1, {%2, %3}], [%4];" ::"r"(ringAddr + st * kRouterBlockBytes),
+                        "l"(reinterpret_cast<uint64_t>(&mapW)), "r"(i * kRouterBlockK), "r"(sl * kRouterExperts),
+                        "r"(barFull(st))
+                        : "memory");
+                    if (++st == kRouterRing) {
+                        st = 0;
+                        phase ^= 1u;
+                    }
+                }
+        }
+        return;
+    }
+
+    uint8_t *warpBase = rsmRaw + (size_t)kRouterRing * kRouterBlockBytes + warp * perWarp;
+    uint16_t *xs = reinterpret_cast<uint16_t *>(warpBase);
+    float *lg = reinterpret_cast<float *>(warpBase + (size_t)kTok * D * 2);
+    const int t0 = (blockIdx.x * kRouterWarps + warp) * kTok;
+    const int nTok = max(0, min(kTok, T - t0));
+    for (int tt = 0; tt < kTok; ++tt) {
         const uint16_t *xr = x + (size_t)min(t0 + min(tt, max(nTok, 1) - 1), T - 1) * xStride;
         for (int i = lane * 8; i < D; i += 256)
             *reinterpret_cast<uint4 *>(xs + (size_t)tt * D + i) = *reinterpret_cast<const uint4 *>(xr + i);
     }
-    __syncthreads();
-    for (int e0 = 0; e0 < E; e0 += kRouterExperts) {
-        const int slice = e0 / kRouterExperts;
-        {
-            // (first poll stand-alone: inside the bounded loop it costs about 200 cycles even when the
-            // slice has landed)
-            bool done = rt_try_wait(barOf(slice), (uint32_t)(slice >> 1) & 1u);
-            for (uint32_t spin = 0; spin < (1u << 22) && !done; ++spin) done = rt_try_wait(barOf(slice), (uint32_t)(slice >> 1) & 1u);
-            if (!done && lane == 0) atomicExch(errorFlag, 11u);
-        }
-        const uint16_t *Ws = reinterpret_cast<const uint16_t *>(rsmRaw + (size_t)(slice & 1) * sliceBytes);
-        // running sums of two tokens share one packed fp32 pair (fma.rn.f32x2 = two independent fp32
-        // FMAs), so every (token, expert) chain is the scalar chain bit for bit at half the issue
-        uint64_t acc[kRouterTokens / 2][kRouterExperts];
+    __syncwarp();
+
+    uint32_t st = 0, phase = 0;
+    bool ok = true;
+    for (int sl = 0; sl < nSlices && ok; ++sl) {
+        float acc[kTok][kRouterExperts];
 #pragma unroll
-        for (int tp = 0; tp < kRouterTokens / 2; ++tp)
+        for (int t = 0; t < kTok; ++t)
 #pragma unroll
-            for (int ee = 0; ee < kRouterExperts; ++ee) acc[tp][ee] = 0ull;
-        for (int base = 8 * lane; base < D; base += 256) {
-            uint64_t xv[kRouterTokens / 2][8];
-            uint4 sv = make_uint4(0, 0, 0, 0);
-            if (scale) sv = *reinterpret_cast<const uint4 *>(scale + base);
-            const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
-#pragma unroll
-            for (int tp = 0; tp < kRouterTokens / 2; ++tp) {
-                const uint4 rawA = *reinterpret_cast<const uint4 *>(xs + (size_t)(2 * tp) * D + base);
-                const uint4 rawB = *reinterpret_cast<const uint4 *>(xs + (size_t)(2 * tp + 1) * D + base);
-                const uint32_t xa[4] = {rawA.x, rawA.y, rawA.z, rawA.w};
-                const uint32_t xb[4] = {rawB.x, rawB.y, rawB.z, rawB.w};
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float a0 = __uint_as_float(xa[k] << 16), a1 = __uint_as_float(xa[k] & 0xFFFF0000u);
-                    float b0 = __uint_as_float(xb[k] << 16), b1 = __uint_as_float(xb[k] & 0xFFFF0000u);
-                    if (scale) {
-                        const float s0 = __uint_as_float(ss[k] << 16), s1 = __uint_as_float(ss[k] & 0xFFFF0000u);
-                        a0 = a0 * s0;
-                        a1 = a1 * s1;
-                        b0 = b0 * s0;
-                        b1 = b1 * s1;
-                    }
-                    xv[tp][2 * k] = pack2(a0, b0);
-                    xv[tp][2 * k + 1] = pack2(a1, b1);
-                }
+            for (int e = 0; e < kRouterExperts; ++e) acc[t][e] = 0.0f;
+        for (int i = 0; i < nBlocks; ++i) {
+            if (!rt_wait(barFull(st), phase)) {
+                if (lane == 0) atomicExch(errorFlag, 11u);
+                ok = false;
+                break;
             }
+            const int base = i * kRouterBlockK + 8 * lane;
+            if (base < D) {
+                float xv[kTok][8];
+                uint4 sv = make_uint4(0, 0, 0, 0);
+                if (scale) sv = *reinterpret_cast<const uint4 *>(scale + base);
+                const uint32_t ss[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
-            for (int ee = 0; ee < kRouterExperts; ++ee) {
-                const int er = min(ee, E - 1 - e0);  // row of the slice (the last slice may be short)
-                const uint4 wv = *reinterpret_cast<const uint4 *>(Ws + (size_t)er * D + base);
-                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                for (int t = 0; t < kTok; ++t) {
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(xs + (size_t)t * D + base);
+                    const uint32_t xr[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float w0 = __uint_as_float(ww[k] << 16), w1 = __uint_as_float(ww[k] & 0xFFFF0000u);
-                    const uint64_t w00 = pack2(w0, w0), w11 = pack2(w1, w1);
-#pragma unroll
-                    for (int tp = 0; tp < kRouterTokens / 2; ++tp) {
-                        acc[tp][ee] = fma2(w00, xv[tp][2 * k], acc[tp][ee]);
-                        acc[tp][ee] = fma2(w11, xv[tp][2 * k + 1], acc[tp][ee]);
+                    for (int k = 0; k < 4; ++k) {
+                        float a0 = __uint_as_float(xr[k] << 16), a1 = __uint_as_float(xr[k] & 0xFFFF0000u);
+                        if (scale) {
+                            a0 = a0 * __uint_as_float(ss[k] << 16);
+                            a1 = a1 * __uint_as_float(ss[k] & 0xFFFF0000u);
+                        }
+                        xv[t][2 * k] = a0;
+                        xv[t][2 * k + 1] = a1;
                     }
                 }
+                const uint8_t *blockPtr = rsmRaw + (size_t)st * kRouterBlockBytes;
+                float wv[kRouterExperts][8];
+#pragma unroll
+                for (int e = 0; e < kRouterExperts; ++e) {
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(blockPtr + (size_t)e * (kRouterBlockK * 2) + lane * 16);
+                    const uint32_t ww[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        wv[e][2 * k] = __uint_as_float(ww[k] << 16);
+                        wv[e][2 * k + 1] = __uint_as_float(ww[k] & 0xFFFF0000u);
+                    }
+                }
+                // element by element, all (token, expert) chains side by side: consecutive fmaf are
+                // independent, every chain still takes its eight elements in ascending order
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+#pragma unroll
+                    for (int e = 0; e < kRouterExperts; ++e)
+#pragma unroll
+                        for (int t = 0; t < kTok; ++t) acc[t][e] = fmaf(wv[e][k], xv[t][k], acc[t][e]);
+            }
+            // this warp is done with the block
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(barEmpty(st)) : "memory");
+            if (++st == kRouterRing) {
+                st = 0;
+                phase ^= 1u;
             }
         }
+        if (!ok) break;
 #pragma unroll
-        for (int tp = 0; tp < kRouterTokens / 2; ++tp)
+        for (int t = 0; t < kTok; ++t)
 #pragma unroll
-            for (int ee = 0; ee < kRouterExperts; ++ee) {
-                float v0, v1;
-                unpack2(acc[tp][ee], v0, v1);
+            for (int e = 0; e < kRouterExperts; ++e) {
+                float v = acc[t][e];
 #pragma unroll
-                for (int offset = 16; offset >= 1; offset >>= 1) {
-                    v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, offset);
-                    v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, offset);
-                }
-                const int e = e0 + ee;
-                if (lane == 0 && e < E) {
-                    lg[(2 * tp) * kMaxExperts + e] = bias ? v0 + bias[e] : v0;
-                    lg[(2 * tp + 1) * kMaxExperts + e] = bias ? v1 + bias[e] : v1;
-                }
+                for (int offset = 16; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
+                const int ex = sl * kRouterExperts + e;
+                if (lane == 0 && ex < E) lg[t * E + ex] = bias ? v + bias[ex] : v;
             }
-        // every warp is done with this buffer: the slice after next may land in it
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (threadIdx.x == 0 && slice + 2 < nSlices) request(slice + 2);
     }
     __syncwarp();
     for (int tt = 0; tt < nTok; ++tt) {
         const int t = t0 + tt;
         if (logitsOut)
-            for (int e = lane; e < E; e += 32) logitsOut[(size_t)t * E + e] = lg[tt * kMaxExperts + e];
-        warp_topk(lg + tt * kMaxExperts, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
+            for (int e = lane; e < E; e += 32) logitsOut[(size_t)t * E + e] = lg[tt * E + e];
+        warp_topk(lg + tt * E, E, K, gain, ids + (size_t)t * K, weights + (size_t)t * K);
     }
+}
+
+static bool make_router_map(CUtensorMap *map, const void *base, uint64_t experts, uint64_t d, const char **error);
+
+template <int kTok>
+static bool launch_router_rows(FFContext *ctx, const LayerStore &L, const CUtensorMap &mapW, size_t smem,
+                               const uint16_t *x, uint32_t xStride, uint32_t tokens, uint32_t *ids,
+                               uint16_t *weights, float *logits, cudaStream_t stream, const char **error) {
+    const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
+    constexpr int kThreads = (kRouterTokensPerCta / kTok + 1) * 32;
+    static KernelSmemMemo memo;
+    if (!memo.prepare(k_router_rows<kTok>, ctx->device, smem, kThreads, nullptr, error)) return false;
+    const uint32_t perCta = kRouterTokensPerCta;
+    {
+        LaunchScope scope(ctx, stream, "router_rows");
+        k_router_rows<kTok><<<(tokens + perCta - 1) / perCta, kThreads, smem, stream>>>(
+            mapW, L.routerScale, L.logitBias, L.gain, x, xStride, (int)tokens, E, D, (int)ctx->cfg.topK, ids,
+            weights, logits, ctx->errorFlag);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
 }
 
 bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride,
                            uint32_t tokens, uint32_t *ids, uint16_t *weights, float *logits,
                            cudaStream_t stream, const char **error) {
     const int E = (int)L.routerExperts, D = (int)ctx->cfg.d;
-    const size_t smem = 2 * (size_t)kRouterExperts * D * 2 +
-                        (size_t)kRouterWarps * ((size_t)kRouterTokens * D * 2 + (size_t)kRouterTokens * kMaxExperts * 4);
-    if (smem > 225 * 1024) return fail(error, "model width too large for the router's shared memory");
     if (D % 8) return fail(error, "hidden size must be a multiple of 8");
-    static KernelSmemMemo memo;
-    if (!memo.prepare(k_router_rows, ctx->device, smem, kRouterWarps * 32, nullptr, error)) return false;
-    const uint32_t perCta = kRouterWarps * kRouterTokens;
-    {
-        LaunchScope scope(ctx, stream, "router_rows");
-        k_router_rows<<<(tokens + perCta - 1) / perCta, kRouterWarps * 32, smem, stream>>>(
-            L.routerW, L.routerScale, L.logitBias, L.gain, x, xStride, (int)tokens, E, D,
-            (int)ctx->cfg.topK, ids, weights, logits, ctx->errorFlag);
-    }
-    FF_CUDA_OK(cudaGetLastError(), error);
-    return true;
+    // a tiled copy descriptor over the router matrix, [8 experts x 256 inputs] boxes (built per call:
+    // encoding is host arithmetic only)
+    CUtensorMap mapW;
+    if (!make_router_map(&mapW, L.routerW, (uint64_t)E, (uint64_t)D, error)) return false;
+    // shared memory: the ring, and per CTA 32 tokens' inputs and logits whatever the split into warps
+    const size_t smem = (size_t)kRouterRing * kRouterBlockBytes +
+                        (size_t)kRouterTokensPerCta * ((size_t)D * 2 + (size_t)E * 4);
+    if (smem > 226 * 1024) return fail(error, "model width too large for the router's shared memory");
+    return launch_router_rows<2>(ctx, L, mapW, smem, x, xStride, tokens, ids, weights, logits, stream, error);
 }
 
 // ---- device-side permute -------------------------------------------------------------------
@@ -1150,6 +1199,23 @@ static bool make_activation_map(CUtensorMap *map, const void *base, uint64_t row
                      box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) return fail(error, "cuTensorMapEncodeTiled(activations) failed: " + std::to_string((int)rc));
+    return true;
+}
+
+// router matrix bf16 [experts][d]: boxes of 256 inputs x 8 experts, no swizzle; parts of a box past
+// the matrix read as zero.
+static bool make_router_map(CUtensorMap *map, const void *base, uint64_t experts, uint64_t d, const char **error) {
+    EncodeTiledFn fn = encode_tiled(error);
+    if (!fn) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) || (d * 2) % 16) return fail(error, "router rows must be 16-byte aligned");
+    cuuint64_t dims[2] = {d, experts};
+    cuuint64_t strides[1] = {d * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kRouterBlockK, (cuuint32_t)kRouterExperts};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(error, "cuTensorMapEncodeTiled(router) failed: " + std::to_string((int)rc));
     return true;
 }
 
