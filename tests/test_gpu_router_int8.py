@@ -91,7 +91,20 @@ def test_operators_take_the_int8_router(oracle, rows):
         hp.PrefillRouter(ctx).encodeGemma4Block(None, 0, xd, ids, w, rows)
         torch.cuda.synchronize()
         assert np.array_equal(ids.cpu().numpy().astype(np.uint32), ref_ids)
-        given = ctx.moeLayer(0, xd, ids=ids, weights=w)
+        # the same layer from its parts, the routes handed to the operators that take routes
+        shared = torch.zeros((rows, D), dtype=torch.bfloat16, device=ctx.device)
+        hp.PrefillSharedExpert(ctx).encodeBlock(None, 0, xd, shared, rows)
+        given = torch.zeros((rows, D), dtype=torch.bfloat16, device=ctx.device)
+        if rows == 1:
+            hp.MoE(ctx).encodeRoutedPersistentGPUSlots(None, 0, ids, xd, w, shared, given)
+        else:
+            partials = torch.zeros((rows * K, D), dtype=torch.bfloat16, device=ctx.device)
+            routed = hp.PrefillGroupedRoutedMoE(ctx)
+            if rows <= 16:
+                routed.encodeVerifyBound(None, 0, xd, ids, partials, rows)
+            else:
+                routed.encodeStreamedBatched(None, 0, xd, ids, partials, rows)
+            hp.PrefillMoE(ctx).encodeReduceTokenMajor(None, partials, w, given, rows, residual=shared)
         torch.cuda.synchronize()
         assert torch.equal(y, given)
         assert ctx.info().deviceErrorFlag == 0

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from ane_fieldfare_b200 import binding, gturbo, synth, workload
-from conftest import assert_layer_close, oracle_layer
+from conftest import LAYER_ELEMENTWISE_TOL, assert_layer_close, oracle_layer
 
 pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
@@ -217,5 +217,57 @@ def test_misaligned_and_mismatched_arguments_fail_before_any_launch(oracle):
             ctx.moeStack(0, 2, buf[:1, :d].contiguous())
         assert ctx.info().kernelLaunches == launches
         assert ctx.info().deviceErrorFlag == 0
+    finally:
+        ctx.close()
+
+
+# ---- lossy routing modes: host-side weight edits in front of the K-wide operators ---------------
+
+@pytest.mark.parametrize("tokens", [1, 3, 40])
+def test_lossy_routing_modes_feed_the_operators(oracle, tokens):
+    """`activeRoutedExperts` < 8 and `prefillExpertUnionCap` (RuntimeConfiguration.swift:57-67) edit
+    the route weights on the host (supervisor.apply_active_routed_experts / cap_expert_union); the
+    operators then take the edited weights with the full routes.  Against the oracle's partial rows
+    reduced with the same edited weights."""
+    from ane_fieldfare_b200 import supervisor as sv
+    hp = _hp()
+    L = workload.make_layer(0x4055, 0, **TOY)
+    ld = oracle_layer(oracle, L)
+    ctx = hp.HotpathContext(layers=1, maxTokens=64, **TOY)
+    try:
+        workload.load_layer(ctx, 0, L)
+        x = workload.make_tokens(0x4055, f"lossy{tokens}", tokens, TOY["d"])
+        ids, w, _ = oracle.router_topk(ld, x)
+        ids_dev = torch.from_numpy(ids.astype(np.int32)).to(ctx.device)
+        xd = dev(x, ctx)
+        shared = torch.zeros((tokens, TOY["d"]), dtype=torch.bfloat16, device=ctx.device)
+        hp.PrefillSharedExpert(ctx).encodeBlock(None, 0, xd, shared, tokens)
+        partials = torch.zeros((tokens * TOY["topK"], TOY["d"]), dtype=torch.bfloat16, device=ctx.device)
+        routed = hp.PrefillGroupedRoutedMoE(ctx)
+        if tokens <= 16:
+            routed.encodeVerifyBound(None, 0, xd, ids_dev, partials, tokens)
+        else:
+            routed.encodeStreamedBatched(None, 0, xd, ids_dev, partials, tokens)
+        wide = tokens > 16  # the GEMM path multiplies weights rounded to bf16
+        pairs, n = oracle.make_pairs(ids, w, tokens, TOY["topK"])
+        ref_partials = oracle.route_partials(ld, x, pairs, n, tokens, bf16_weights=wide)
+        ref_shared = oracle.shared_ffn(ld, x, bf16_weights=wide)
+        for what, edited in (("active 5", sv.apply_active_routed_experts(w, 5)),
+                             ("union cap 6", sv.cap_expert_union(ids, w, TOY["experts"], 6))):
+            assert not np.array_equal(edited, w)
+            got = torch.zeros((tokens, TOY["d"]), dtype=torch.bfloat16, device=ctx.device)
+            hp.PrefillMoE(ctx).encodeReduceTokenMajor(None, partials, dev(edited, ctx), got, tokens, residual=shared)
+            torch.cuda.synchronize()
+            want = oracle.reduce_token_major(ref_partials, edited, ref_shared, tokens, TOY["topK"], TOY["d"])
+            assert_layer_close(hp.bf16_numpy(got), want, oracle, f"lossy {what} T={tokens}",
+                               elementwise_tol=LAYER_ELEMENTWISE_TOL)
+            if tokens == 1:
+                # the one-token operator takes the edited weights with the full routes, too
+                y1 = torch.zeros((1, TOY["d"]), dtype=torch.bfloat16, device=ctx.device)
+                hp.MoE(ctx).encodeRoutedPersistentGPUSlots(None, 0, ids_dev, xd, dev(edited, ctx), shared, y1)
+                torch.cuda.synchronize()
+                assert_layer_close(hp.bf16_numpy(y1), want, oracle, f"lossy {what}, one-token operator",
+                                   elementwise_tol=LAYER_ELEMENTWISE_TOL)
+            assert ctx.info().deviceErrorFlag == 0
     finally:
         ctx.close()
