@@ -106,6 +106,8 @@ SIGNATURES = {
                                              POINTER(FFMoEGroup), POINTER(c_uint32),
                                              POINTER(FFMoETile), POINTER(c_uint32), _ERR]),
     "ff_last_prefill_routes": (c_bool, [c_void_p, POINTER(FFTokenExpertPair), _P, _ERR]),
+    "ff_post_attn_setup": (c_bool, [c_void_p, _P, _P, _P, _P, _P, c_uint32, c_float, _P, _P, _P, _P, _ERR]),
+    "ff_layer_tail": (c_bool, [c_void_p, _P, _P, _P, _P, _P, c_uint32, c_float, c_float, _P, _ERR]),
     "ff_sort_routes": (c_bool, [c_void_p, _P, c_uint32, c_uint32, _P, _P, _P, _ERR]),
 }
 

@@ -333,6 +333,37 @@ static bool moe_layer_host_one_token(FFContext *ctx, uint32_t layer, const uint1
     return true;
 }
 
+bool ff_post_attn_setup(FFContext *ctx, uint16_t *hidden, const uint16_t *attn, const uint16_t *wPostAttn,
+                        const uint16_t *wPreFfn, const uint16_t *wPreFfn2, uint32_t tokens, float eps,
+                        uint16_t *denseX, uint16_t *routedX, uint16_t *routerX, void *stream,
+                        const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !hidden || !attn || !wPostAttn || !wPreFfn || !wPreFfn2 || !denseX || !routedX || !routerX)
+        return fail(error, "null argument");
+    const uintptr_t all = reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(attn) |
+                          reinterpret_cast<uintptr_t>(wPostAttn) | reinterpret_cast<uintptr_t>(wPreFfn) |
+                          reinterpret_cast<uintptr_t>(wPreFfn2) | reinterpret_cast<uintptr_t>(denseX) |
+                          reinterpret_cast<uintptr_t>(routedX) | reinterpret_cast<uintptr_t>(routerX);
+    if (all & 1u) return fail(error, "rows must be 2-byte aligned");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    return launch_post_attn_setup(ctx, hidden, attn, wPostAttn, wPreFfn, wPreFfn2, eps, tokens, denseX, routedX,
+                                  routerX, static_cast<cudaStream_t>(stream), error);
+}
+
+bool ff_layer_tail(FFContext *ctx, const uint16_t *h2, const uint16_t *h1, uint16_t *hidden,
+                   const uint16_t *wPostFfn2, const uint16_t *wPostFfn, uint32_t tokens, float eps,
+                   float layerScalar, void *stream, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !h2 || !h1 || !hidden || !wPostFfn2 || !wPostFfn) return fail(error, "null argument");
+    const uintptr_t all = reinterpret_cast<uintptr_t>(h2) | reinterpret_cast<uintptr_t>(h1) |
+                          reinterpret_cast<uintptr_t>(hidden) | reinterpret_cast<uintptr_t>(wPostFfn2) |
+                          reinterpret_cast<uintptr_t>(wPostFfn);
+    if (all & 1u) return fail(error, "rows must be 2-byte aligned");
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    return launch_layer_tail(ctx, h2, h1, hidden, wPostFfn2, wPostFfn, eps, layerScalar, tokens,
+                             static_cast<cudaStream_t>(stream), error);
+}
+
 bool ff_sort_routes(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, uint32_t groups,
                     FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream, const char **error) {
     if (error) *error = nullptr;

@@ -426,6 +426,118 @@ k_rmsnorm(const uint16_t *x, const uint16_t *w, float eps, int D, uint16_t *y) {
     }
 }
 
+// ---- the fused steps either side of the block ----------------------------------------------------
+
+// Sum over the CTA (256 threads) of one float per thread; every thread gets the total.
+__device__ __forceinline__ float cta_sum_256(float v, float *warpSums) {
+#pragma unroll
+    for (int offset = 16; offset >= 1; offset >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, offset);
+    __syncthreads();  // warpSums may still be read from the previous use
+    if ((threadIdx.x & 31) == 0) warpSums[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += warpSums[i];
+    return total;
+}
+
+// prefill_post_attn_setup_block (Metal/Prefill/prefill.metal:244-318), one CTA per row:
+//   a = r16(attn * rms_inv(attn) * w_post_attn);  hidden = r16(hidden + a);
+//   n = hidden * rms_inv(hidden);  dense_x = r16(n * w_pre_ffn);  routed_x = r16(n * w_pre_ffn2);
+//   router_x = r16(n).  The new hidden row is kept in shared memory between the two passes.
+__global__ void __launch_bounds__(256)
+k_post_attn_setup(uint16_t *hidden, const uint16_t *attn, const uint16_t *wPostAttn, const uint16_t *wPreFfn,
+                  const uint16_t *wPreFfn2, float eps, int D, uint16_t *denseX, uint16_t *routedX,
+                  uint16_t *routerX) {
+    extern __shared__ uint16_t glueRow[];
+    __shared__ float warpSums[8];
+    const size_t row = (size_t)blockIdx.x * D;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = bf2f(attn[row + i]);
+        sq = fmaf(v, v, sq);
+    }
+    const float attnInv = 1.0f / sqrtf(cta_sum_256(sq, warpSums) / (float)D + eps);
+    sq = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const uint16_t an = f2bf(bf2f(attn[row + i]) * attnInv * bf2f(wPostAttn[i]));
+        const uint16_t h = f2bf(bf2f(hidden[row + i]) + bf2f(an));
+        glueRow[i] = h;
+        hidden[row + i] = h;
+        const float hf = bf2f(h);
+        sq = fmaf(hf, hf, sq);
+    }
+    const float hiddenInv = 1.0f / sqrtf(cta_sum_256(sq, warpSums) / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float n = bf2f(glueRow[i]) * hiddenInv;
+        denseX[row + i] = f2bf(n * bf2f(wPreFfn[i]));
+        routedX[row + i] = f2bf(n * bf2f(wPreFfn2[i]));
+        routerX[row + i] = f2bf(n);
+    }
+}
+
+// prefill_layer_tail_block (Metal/Prefill/prefill.metal:321-399; one row: Metal/Fusions/fused.metal:470-474):
+//   t = r16(h2 * rms_inv(h2) * w_postffn2);  h12 = r16(h1 + t);
+//   u = r16(h12 * rms_inv(h12) * w_postffn);  hidden = r16(r16(hidden + u) * r16(layer_scalar)).
+__global__ void __launch_bounds__(256)
+k_layer_tail(const uint16_t *h2, const uint16_t *h1, uint16_t *hidden, const uint16_t *wPostFfn2,
+             const uint16_t *wPostFfn, float eps, float layerScalar, int D) {
+    extern __shared__ uint16_t glueRow[];
+    __shared__ float warpSums[8];
+    const size_t row = (size_t)blockIdx.x * D;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = bf2f(h2[row + i]);
+        sq = fmaf(v, v, sq);
+    }
+    const float inv2 = 1.0f / sqrtf(cta_sum_256(sq, warpSums) / (float)D + eps);
+    sq = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const uint16_t tmp = f2bf(bf2f(h2[row + i]) * inv2 * bf2f(wPostFfn2[i]));
+        const uint16_t h12 = f2bf(bf2f(h1[row + i]) + bf2f(tmp));
+        glueRow[i] = h12;
+        const float v = bf2f(h12);
+        sq = fmaf(v, v, sq);
+    }
+    const float inv12 = 1.0f / sqrtf(cta_sum_256(sq, warpSums) / (float)D + eps);
+    const float scale = bf2f(f2bf(layerScalar));
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const uint16_t u = f2bf(bf2f(glueRow[i]) * inv12 * bf2f(wPostFfn[i]));
+        const uint16_t sum = f2bf(bf2f(hidden[row + i]) + bf2f(u));
+        hidden[row + i] = f2bf(bf2f(sum) * scale);
+    }
+}
+
+bool launch_post_attn_setup(FFContext *ctx, uint16_t *hidden, const uint16_t *attn, const uint16_t *wPostAttn,
+                            const uint16_t *wPreFfn, const uint16_t *wPreFfn2, float eps, uint32_t tokens,
+                            uint16_t *denseX, uint16_t *routedX, uint16_t *routerX, cudaStream_t stream,
+                            const char **error) {
+    if (tokens == 0) return true;
+    const int D = (int)ctx->cfg.d;
+    if ((size_t)D * 2 > 96 * 1024) return fail(error, "model width too large for the row buffer");
+    {
+        LaunchScope scope(ctx, stream, "post_attn_setup");
+        k_post_attn_setup<<<tokens, 256, (size_t)D * 2, stream>>>(hidden, attn, wPostAttn, wPreFfn, wPreFfn2, eps, D,
+                                                                  denseX, routedX, routerX);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
+bool launch_layer_tail(FFContext *ctx, const uint16_t *h2, const uint16_t *h1, uint16_t *hidden,
+                       const uint16_t *wPostFfn2, const uint16_t *wPostFfn, float eps, float layerScalar,
+                       uint32_t tokens, cudaStream_t stream, const char **error) {
+    if (tokens == 0) return true;
+    const int D = (int)ctx->cfg.d;
+    if ((size_t)D * 2 > 96 * 1024) return fail(error, "model width too large for the row buffer");
+    {
+        LaunchScope scope(ctx, stream, "layer_tail");
+        k_layer_tail<<<tokens, 256, (size_t)D * 2, stream>>>(h2, h1, hidden, wPostFfn2, wPostFfn, eps, layerScalar, D);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
 // w = q*scale + bias for a whole matrix, fp32 and/or bf16 (one rounding of the exact value:
 // a bf16 fused multiply-add).  One thread per 8 codes.
 __global__ void __launch_bounds__(256)

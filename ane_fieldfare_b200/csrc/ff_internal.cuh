@@ -262,6 +262,13 @@ bool launch_prefill_routed(FFContext *ctx, LayerStore &L, const uint16_t *x, uin
                            cudaStream_t stream, const char **error);
 bool launch_prefill_shared(FFContext *ctx, LayerStore &L, const uint16_t *x, uint32_t xStride,
                            uint32_t tokens, uint16_t *y, cudaStream_t stream, const char **error);
+bool launch_post_attn_setup(FFContext *ctx, uint16_t *hidden, const uint16_t *attn, const uint16_t *wPostAttn,
+                            const uint16_t *wPreFfn, const uint16_t *wPreFfn2, float eps, uint32_t tokens,
+                            uint16_t *denseX, uint16_t *routedX, uint16_t *routerX, cudaStream_t stream,
+                            const char **error);
+bool launch_layer_tail(FFContext *ctx, const uint16_t *h2, const uint16_t *h1, uint16_t *hidden,
+                       const uint16_t *wPostFfn2, const uint16_t *wPostFfn, float eps, float layerScalar,
+                       uint32_t tokens, cudaStream_t stream, const char **error);
 bool launch_route_sort(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, uint32_t groups,
                        FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream, const char **error);
 bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *x,

@@ -459,6 +459,25 @@ class PrefillGroupedRoutedMoE:
         return list(pairs)[:pairCount], offsets
 
 
+class PrefillLayerGlue:
+    """The fused steps either side of the MoE block: `prefill_post_attn_setup_block` and
+    `prefill_layer_tail_block` (Metal/Prefill/prefill.metal:244-399).  Rows [T][d] bf16, contiguous."""
+
+    def __init__(self, context: HotpathContext):
+        self.context = context
+
+    def encodePostAttnSetupBlock(self, stream, hidden: torch.Tensor, attn: torch.Tensor, wPostAttn: torch.Tensor,
+                                 wPreFfn: torch.Tensor, wPreFfn2: torch.Tensor, eps: float, denseX: torch.Tensor,
+                                 routedX: torch.Tensor, routerX: torch.Tensor):
+        call("ff_post_attn_setup", self.context.handle, _ptr(hidden), _ptr(attn), _ptr(wPostAttn), _ptr(wPreFfn),
+             _ptr(wPreFfn2), hidden.shape[0], eps, _ptr(denseX), _ptr(routedX), _ptr(routerX), _stream(stream))
+
+    def encodeLayerTailBlock(self, stream, h2: torch.Tensor, h1: torch.Tensor, hidden: torch.Tensor,
+                             wPostFfn2: torch.Tensor, wPostFfn: torch.Tensor, eps: float, layerScalar: float):
+        call("ff_layer_tail", self.context.handle, _ptr(h2), _ptr(h1), _ptr(hidden), _ptr(wPostFfn2),
+             _ptr(wPostFfn), hidden.shape[0], eps, layerScalar, _stream(stream))
+
+
 class PrefillMoE:
     """Token-major weighted combine (Kernels/Prefill/MoE/PrefillMoE.swift:11-32)."""
 

@@ -349,6 +349,24 @@ bool ff_group_token_expert_pairs(const FFTokenExpertPair *pairs, uint64_t pairCo
                                  uint32_t *groupCount, FFMoETile *tiles, uint32_t *tileCount,
                                  const char **error);
 
+/* The fused step in front of the block, `prefill_post_attn_setup_block`
+ * (Metal/Prefill/prefill.metal:244-318): rows [tokens][d] contiguous, bf16, device pointers; norm
+ * weights bf16 [d].  hidden <- r16(hidden + r16(attn * rms_inv(attn) * wPostAttn)); with
+ * n = hidden * rms_inv(hidden): denseX = r16(n * wPreFfn) (input of the shared FFN), routedX =
+ * r16(n * wPreFfn2) (input of the routed experts), routerX = r16(n) (input of the router). */
+bool ff_post_attn_setup(FFContext *ctx, uint16_t *hidden, const uint16_t *attn, const uint16_t *wPostAttn,
+                        const uint16_t *wPreFfn, const uint16_t *wPreFfn2, uint32_t tokens, float eps,
+                        uint16_t *denseX, uint16_t *routedX, uint16_t *routerX, void *stream,
+                        const char **error);
+
+/* The fused step behind the block, `prefill_layer_tail_block` (Metal/Prefill/prefill.metal:321-399;
+ * one row: Metal/Fusions/fused.metal:470-474): h2 = the routed experts' combined rows, h1 = the
+ * shared FFN's rows; hidden <- r16(r16(hidden + r16(h12 * rms_inv(h12) * wPostFfn)) * r16(layerScalar))
+ * with h12 = r16(h1 + r16(h2 * rms_inv(h2) * wPostFfn2)).  In place on `hidden`. */
+bool ff_layer_tail(FFContext *ctx, const uint16_t *h2, const uint16_t *h1, uint16_t *hidden,
+                   const uint16_t *wPostFfn2, const uint16_t *wPostFfn, uint32_t tokens, float eps,
+                   float layerScalar, void *stream, const char **error);
+
 /* The device-side permute on its own (the sort of PrefillMoEGrouping.groupTokenExpertPairs,
  * Kernels/Prefill/MoE/PrefillMoEGrouping.swift:49-110, by any group id): `groupIds` [tokens][topK] on
  * the device, ids >= `groups` are dropped; `sortedPairs` (device) receives (token, group, rank, 0)

@@ -673,6 +673,72 @@ void ffo_rmsnorm_bf16(const uint16_t *x, const uint16_t *w, float eps, int32_t T
     }
 }
 
+/* ---- the fused steps either side of the block ----------------------------------------------- */
+
+/* 1/sqrt(mean(x^2) + eps) of a 16-bit row, the squares chained by fmaf in index order
+ * (Sources/ANEFieldfareHotpath/Metal/Prefill/prefill.metal:54-85 sums them per thread and then across
+ * the threadgroup; here one chain). */
+static float rms_inv16(const uint16_t *x, int32_t n, float eps) {
+    float acc = 0.0f;
+    for (int32_t i = 0; i < n; ++i) {
+        const float v = ffo_bf16_to_float(x[i]);
+        acc = fmaf(v, v, acc);
+    }
+    return 1.0f / sqrtf(acc / (float)n + eps);
+}
+
+/* prefill_post_attn_setup_block (Metal/Prefill/prefill.metal:244-318): per row
+ *   a = r16(attn * rms_inv(attn) * w_post_attn);  hidden = r16(hidden + a);
+ *   n = hidden * rms_inv(hidden);  dense_x = r16(n * w_pre_ffn);  routed_x = r16(n * w_pre_ffn2);
+ *   router_x = r16(n),  r16 = rounding to the 16-bit activation type (bf16 here, fp16 there). */
+void ffo_post_attn_setup(uint16_t *hidden, const uint16_t *attn, const uint16_t *w_post_attn,
+                         const uint16_t *w_pre_ffn, const uint16_t *w_pre_ffn2, int32_t T, int32_t D,
+                         float eps, uint16_t *dense_x, uint16_t *routed_x, uint16_t *router_x) {
+    for (int32_t t = 0; t < T; ++t) {
+        uint16_t *h = hidden + (int64_t)t * D;
+        const uint16_t *a = attn + (int64_t)t * D;
+        const float attn_inv = rms_inv16(a, D, eps);
+        for (int32_t i = 0; i < D; ++i) {
+            const uint16_t an = ffo_bf16_bits(ffo_bf16_to_float(a[i]) * attn_inv * ffo_bf16_to_float(w_post_attn[i]));
+            h[i] = ffo_bf16_bits(ffo_bf16_to_float(h[i]) + ffo_bf16_to_float(an));
+        }
+        const float hidden_inv = rms_inv16(h, D, eps);
+        for (int32_t i = 0; i < D; ++i) {
+            const float n = ffo_bf16_to_float(h[i]) * hidden_inv;
+            dense_x[(int64_t)t * D + i] = ffo_bf16_bits(n * ffo_bf16_to_float(w_pre_ffn[i]));
+            routed_x[(int64_t)t * D + i] = ffo_bf16_bits(n * ffo_bf16_to_float(w_pre_ffn2[i]));
+            router_x[(int64_t)t * D + i] = ffo_bf16_bits(n);
+        }
+    }
+}
+
+/* prefill_layer_tail_block (Metal/Prefill/prefill.metal:321-399; the one-row form is
+ * Metal/Fusions/fused.metal:470-474): per row
+ *   t = r16(h2 * rms_inv(h2) * w_postffn2);  h12 = r16(h1 + t);
+ *   u = r16(h12 * rms_inv(h12) * w_postffn);  hidden = r16(hidden + u);
+ *   hidden = r16(hidden * r16(layer_scalar)). */
+void ffo_layer_tail(const uint16_t *h2, const uint16_t *h1, uint16_t *hidden, const uint16_t *w_postffn2,
+                    const uint16_t *w_postffn, int32_t T, int32_t D, float eps, float layer_scalar) {
+    uint16_t *h12 = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)D);
+    const float scale = ffo_bf16_to_float(ffo_bf16_bits(layer_scalar));
+    for (int32_t t = 0; t < T; ++t) {
+        const uint16_t *r2 = h2 + (int64_t)t * D, *r1 = h1 + (int64_t)t * D;
+        uint16_t *h = hidden + (int64_t)t * D;
+        const float inv2 = rms_inv16(r2, D, eps);
+        for (int32_t i = 0; i < D; ++i) {
+            const uint16_t tmp = ffo_bf16_bits(ffo_bf16_to_float(r2[i]) * inv2 * ffo_bf16_to_float(w_postffn2[i]));
+            h12[i] = ffo_bf16_bits(ffo_bf16_to_float(r1[i]) + ffo_bf16_to_float(tmp));
+        }
+        const float inv12 = rms_inv16(h12, D, eps);
+        for (int32_t i = 0; i < D; ++i) {
+            const uint16_t u = ffo_bf16_bits(ffo_bf16_to_float(h12[i]) * inv12 * ffo_bf16_to_float(w_postffn[i]));
+            const uint16_t sum = ffo_bf16_bits(ffo_bf16_to_float(h[i]) + ffo_bf16_to_float(u));
+            h[i] = ffo_bf16_bits(ffo_bf16_to_float(sum) * scale);
+        }
+    }
+    free(h12);
+}
+
 /* ---- whole layer ------------------------------------------------------------------------- */
 
 /* Shared INT4 FFN: gate and up rounded to 16 bits before the activation, the activation rounded

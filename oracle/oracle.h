@@ -91,6 +91,11 @@ void ffo_expert_ffn(const uint8_t *blob, const ffo_offsets *off, int32_t D, int3
                     const uint16_t *x, int32_t T, int32_t x_stride, int32_t round_gate_up,
                     int32_t round_act, float *out, int32_t out_stride);
 
+void ffo_post_attn_setup(uint16_t *hidden, const uint16_t *attn, const uint16_t *w_post_attn,
+                         const uint16_t *w_pre_ffn, const uint16_t *w_pre_ffn2, int32_t T, int32_t D,
+                         float eps, uint16_t *dense_x, uint16_t *routed_x, uint16_t *router_x);
+void ffo_layer_tail(const uint16_t *h2, const uint16_t *h1, uint16_t *hidden, const uint16_t *w_postffn2,
+                    const uint16_t *w_postffn, int32_t T, int32_t D, float eps, float layer_scalar);
 void ffo_router_logits(const ffo_layer *L, const uint16_t *x, float *logits);
 void ffo_router_logits_int8(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases,
                             const uint16_t *effective_scale, const float *logit_bias, int32_t E,

@@ -157,6 +157,32 @@ def expert_ffn(blob, off, D, F, x_bits, round_gate_up=False, round_act=True):
     return out
 
 
+def post_attn_setup(hidden, attn, w_post_attn, w_pre_ffn, w_pre_ffn2, eps):
+    """prefill_post_attn_setup_block (Metal/Prefill/prefill.metal:244-318) on bf16 bit patterns
+    [T][D]: returns (hidden', dense_x, routed_x, router_x)."""
+    h = np.array(hidden, dtype=np.uint16, copy=True)
+    attn = np.ascontiguousarray(attn, dtype=np.uint16)
+    T, D = h.shape
+    ws = [np.ascontiguousarray(w, dtype=np.uint16) for w in (w_post_attn, w_pre_ffn, w_pre_ffn2)]
+    outs = [np.empty((T, D), dtype=np.uint16) for _ in range(3)]
+    lib().ffo_post_attn_setup(_p(h), _p(attn), _p(ws[0]), _p(ws[1]), _p(ws[2]), c_int32(T), c_int32(D),
+                              c_float(eps), _p(outs[0]), _p(outs[1]), _p(outs[2]))
+    return h, outs[0], outs[1], outs[2]
+
+
+def layer_tail(h2, h1, hidden, w_postffn2, w_postffn, eps, layer_scalar):
+    """prefill_layer_tail_block (Metal/Prefill/prefill.metal:321-399): returns hidden'."""
+    h = np.array(hidden, dtype=np.uint16, copy=True)
+    h2 = np.ascontiguousarray(h2, dtype=np.uint16)
+    h1 = np.ascontiguousarray(h1, dtype=np.uint16)
+    T, D = h.shape
+    w2 = np.ascontiguousarray(w_postffn2, dtype=np.uint16)
+    w1 = np.ascontiguousarray(w_postffn, dtype=np.uint16)
+    lib().ffo_layer_tail(_p(h2), _p(h1), _p(h), _p(w2), _p(w1), c_int32(T), c_int32(D), c_float(eps),
+                         c_float(layer_scalar))
+    return h
+
+
 def router_topk_int8(codes, scales, biases, x_bits, K, effective_scale=None, logit_bias=None, gain=None):
     """INT8 affine router (Metal/MoE/moe.metal:65-103) + top-K: ids, 16-bit weights, logits."""
     codes = np.ascontiguousarray(codes, dtype=np.uint8)

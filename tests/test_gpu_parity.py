@@ -405,3 +405,39 @@ def test_decode_kernel_replays_in_a_cuda_graph_and_mixes_with_other_modes(full, 
         torch.cuda.synchronize()
         assert torch.equal(ys[0], eager[replay % 4]), replay
     assert ctx.info().deviceErrorFlag == 0
+
+
+@pytest.mark.parametrize("rows", [1, 7, 300])
+def test_fused_steps_either_side_of_the_block(tiny, full, oracle, rows):
+    """`prefill_post_attn_setup_block` and `prefill_layer_tail_block`
+    (Metal/Prefill/prefill.metal:244-399) against the oracle.  Only the order of the RMS sums
+    differs (a CTA-wide reduction here, one chain there), so results agree except where a value sits
+    on a rounding boundary: at most one 16-bit step of the terms involved, in under one element
+    in a hundred."""
+    hp = _hp()
+    for L, ctx in (tiny, full):
+        D, eps = L.d, 1e-6
+        mk = lambda seed, lo, hi, n: synth.bf16_bits(synth.uniform(seed, n, lo, hi))
+        hidden = mk(51, -2, 2, rows * D).reshape(rows, D)
+        attn = mk(52, -4, 4, rows * D).reshape(rows, D)
+        w = [mk(53 + i, 0.5, 1.5, D) for i in range(5)]
+        hd, dense, routed, router = (dev(hidden, ctx), *[torch.zeros((rows, D), dtype=torch.bfloat16, device=ctx.device)
+                                                         for _ in range(3)])
+        glue = hp.PrefillLayerGlue(ctx)
+        glue.encodePostAttnSetupBlock(None, hd, dev(attn, ctx), dev(w[0], ctx), dev(w[1], ctx), dev(w[2], ctx), eps,
+                                      dense, routed, router)
+        h2 = mk(60, -6, 6, rows * D).reshape(rows, D)
+        h1 = mk(61, -2, 2, rows * D).reshape(rows, D)
+        tail = dev(hidden, ctx)
+        glue.encodeLayerTailBlock(None, dev(h2, ctx), dev(h1, ctx), tail, dev(w[3], ctx), dev(w[4], ctx), eps, 0.7071)
+        torch.cuda.synchronize()
+        want = list(oracle.post_attn_setup(hidden, attn, w[0], w[1], w[2], eps))
+        want.append(oracle.layer_tail(h2, h1, hidden, w[3], w[4], eps, 0.7071))
+        for name, got, ref in zip(("hidden", "dense_x", "routed_x", "router_x", "tail"),
+                                  (hd, dense, routed, router, tail), want):
+            g, r = oracle.bf16_to_float(hp.bf16_numpy(got)), oracle.bf16_to_float(ref)
+            # one 16-bit step of the larger of the value and the terms it was summed from (the sums
+            # `hidden + a` and `hidden + u` cancel, their terms are of order one)
+            step = np.maximum(np.abs(r), 4.0) * 2.0 ** -7   # the normalized terms reach about 4 here
+            assert np.all(np.abs(g - r) <= step * 1.01), (name, float(np.abs(g - r).max()))
+            assert np.mean(g != r) < 1e-2, (name, float(np.mean(g != r)))

@@ -409,3 +409,33 @@ def test_int8_router_against_float64(oracle):
         if gaps.min() > 1e-4:
             assert list(ids[t]) == list(order[:K])
     assert np.all(np.abs(oracle.bf16_to_float(w).sum(axis=1) - 1.0) < 2e-2)
+
+
+def test_fused_glue_steps_against_float64(oracle):
+    """ffo_post_attn_setup / ffo_layer_tail (Metal/Prefill/prefill.metal:244-399) against a float64
+    evaluation of the same formulas with the same 16-bit rounding points: the RMS sums are the only
+    place where precision differs, so every output agrees to within one 16-bit step of its value."""
+    rng = np.random.default_rng(41)
+    T, D, eps = 5, 256, 1e-6
+    bits = lambda a: synth.bf16_bits(np.asarray(a, dtype=np.float32))
+    f64 = lambda b: oracle.bf16_to_float(b).astype(np.float64)
+    r16 = lambda a: f64(bits(a))
+    hidden, attn = bits(rng.normal(0, 1, (T, D))), bits(rng.normal(0, 2, (T, D)))
+    w = [bits(rng.uniform(0.5, 1.5, D)) for _ in range(5)]
+    inv = lambda a: 1.0 / np.sqrt((a * a).mean(axis=1, keepdims=True) + eps)
+
+    h, dense, routed, router = oracle.post_attn_setup(hidden, attn, w[0], w[1], w[2], eps)
+    a = r16(f64(attn) * inv(f64(attn)) * f64(w[0]))
+    h64 = r16(f64(hidden) + a)
+    n = h64 * inv(h64)
+    step = lambda ref: np.maximum(np.abs(ref), 1e-30) * 2.0 ** -7   # one bf16 step of the value
+    for got, want in ((h, h64), (dense, n * f64(w[1])), (routed, n * f64(w[2])), (router, n)):
+        assert np.all(np.abs(f64(got) - want) <= step(want))
+
+    h2, h1 = bits(rng.normal(0, 3, (T, D))), bits(rng.normal(0, 1, (T, D)))
+    out = oracle.layer_tail(h2, h1, hidden, w[3], w[4], eps, 0.7071)
+    t = r16(f64(h2) * inv(f64(h2)) * f64(w[3]))
+    h12 = r16(f64(h1) + t)
+    u = r16(h12 * inv(h12) * f64(w[4]))
+    want = r16(f64(hidden) + u) * f64(bits([0.7071]))[0]
+    assert np.all(np.abs(f64(out) - want) <= 2 * step(want))
