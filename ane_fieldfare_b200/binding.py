@@ -78,6 +78,8 @@ SIGNATURES = {
     "ff_load_model_dir": (c_bool, [c_void_p, c_char_p, _ERR]),
     "ff_load_shared": (c_bool, [c_void_p, c_uint32, POINTER(FFProjection), POINTER(FFProjection),
                                 POINTER(FFProjection), _ERR]),
+    "ff_load_shared_int8": (c_bool, [c_void_p, c_uint32, POINTER(FFProjection), POINTER(FFProjection),
+                                     POINTER(FFProjection), _ERR]),
     "ff_load_router": (c_bool, [c_void_p, c_uint32, _P, _P, _P, _P, c_uint32, c_uint32, _ERR]),
     "ff_load_router_int8": (c_bool, [c_void_p, c_uint32, _P, _P, _P, _P, _P, _P, c_uint32, c_uint32, _ERR]),
     "ff_expert_address": (c_uint64, [c_void_p, c_uint32, c_uint32]),

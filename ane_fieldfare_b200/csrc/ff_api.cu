@@ -172,6 +172,7 @@ bool ff_shared_ffn(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t x
     if (!begin(ctx, layer, stream, error, &c)) return false;
     if (!check_rows(ctx, x, xStride, tokens, error)) return false;
     if (!y) return fail(error, "output pointer is null");
+    if (c.L->has_shared8()) return launch_shared_int8(ctx, *c.L, x, xStride, tokens, y, c.stream, error);
     // one row goes through the decode kernel (shared part only), so that the layer call and the
     // operators called one by one give the same bits
     if (tokens == 1 && ((uintptr_t)x & 15) == 0)
@@ -219,17 +220,22 @@ bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t to
     if (!y) return fail(error, "output pointer is null");
     if (tokens == 0) return true;
     LayerStore &L = *c.L;
-    const bool withShared = cfg.sharedF != 0 && L.shared != nullptr;
+    // an INT8 shared FFN runs as launches of its own in front; its rows are then the residual that
+    // the routed part is added to (the INT4 one is part of the fused kernels)
+    const bool shared8 = cfg.sharedF != 0 && L.has_shared8();
+    const bool withShared = cfg.sharedF != 0 && L.shared != nullptr && !shared8;
     ctx->lastTokens = tokens;
     const size_t routeCount = (size_t)tokens * cfg.topK;
-    bool ok;
+    bool ok = true;
+    if (shared8) ok = launch_shared_int8(ctx, L, x, cfg.d, tokens, ctx->h1, c.stream, error);
+    const uint16_t *sharedRows = (withShared || shared8) ? ctx->h1 : nullptr;
+    if (!ok) return false;
     if (tokens <= (uint32_t)kMaxGemvRows) {
         const bool decode = tokens == 1;
         ok = launch_block_small(ctx, L, x, cfg.d, tokens, nullptr, nullptr, withShared, decode,
-                                nullptr, ctx->partials, ctx->h1, y, c.stream, error);
+                                shared8 ? ctx->h1 : nullptr, ctx->partials, ctx->h1, y, c.stream, error);
         if (ok && !decode)
-            ok = launch_reduce(ctx, ctx->partials, ctx->weights, withShared ? ctx->h1 : nullptr, y,
-                               tokens, c.stream, error);
+            ok = launch_reduce(ctx, ctx->partials, ctx->weights, sharedRows, y, tokens, c.stream, error);
     } else {
         ok = launch_router_topk(ctx, L, x, cfg.d, tokens, ctx->ids, ctx->weights, nullptr, c.stream,
                                 error);
@@ -237,8 +243,7 @@ bool ff_moe_layer(FFContext *ctx, uint32_t layer, const uint16_t *x, uint32_t to
             ok = launch_prefill_shared(ctx, L, x, cfg.d, tokens, ctx->h1, c.stream, error);
         ok = ok && launch_prefill_routed(ctx, L, x, cfg.d, tokens, ctx->ids, ctx->partials, c.stream,
                                          error);
-        ok = ok && launch_reduce(ctx, ctx->partials, ctx->weights, withShared ? ctx->h1 : nullptr, y,
-                                 tokens, c.stream, error);
+        ok = ok && launch_reduce(ctx, ctx->partials, ctx->weights, sharedRows, y, tokens, c.stream, error);
     }
     if (!ok) return false;
     if (ids)
@@ -297,7 +302,7 @@ static bool moe_layer_host_one_token(FFContext *ctx, uint32_t layer, const uint1
     const FFConfig &cfg = ctx->cfg;
     if (layer >= cfg.layers || cfg.d > 4096 || !ctx->mailbox) return true;
     LayerStore &L = ctx->layers[layer];
-    if (!L.experts || !L.routerW) return true;
+    if (!L.experts || !L.routerW || L.has_shared8()) return true;
     cudaPointerAttributes attr{};
     if (cudaPointerGetAttributes(&attr, hostY) != cudaSuccess) {
         cudaGetLastError();

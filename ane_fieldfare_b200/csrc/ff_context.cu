@@ -40,9 +40,20 @@ static bool dev_alloc(FFContext *ctx, T **ptr, size_t count, const char **error)
     return true;
 }
 
+static void free_shared8(LayerStore &L) {
+    for (int m = 0; m < 3; ++m) {
+        cudaFree(L.shared8W[m]);
+        cudaFree(L.shared8S[m]);
+        cudaFree(L.shared8B[m]);
+        L.shared8W[m] = nullptr;
+        L.shared8S[m] = L.shared8B[m] = nullptr;
+    }
+}
+
 static void free_layer(LayerStore &L) {
     cudaFree(L.experts);
     cudaFree(L.shared);
+    free_shared8(L);
     cudaFree(L.routerQ);
     cudaFree(L.routerQScale);
     cudaFree(L.routerQBias);
@@ -336,6 +347,7 @@ bool ff_load_shared(FFContext *ctx, uint32_t layer, const FFProjection *gate,
         return false;
     FF_CUDA_OK(cudaSetDevice(ctx->device), error);
     LayerStore &L = ctx->layers[layer];
+    free_shared8(L);
     uint64_t payload = 0;
     L.sharedOff = packed_offsets(d, fs, &payload);
     if (L.shared) {
@@ -374,6 +386,44 @@ static void free_router(ff::LayerStore &L) {
 static bool upload(void **dst, const void *src, size_t bytes, const char **error) {
     FF_CUDA_OK(cudaMalloc(dst, bytes), error);
     FF_CUDA_OK(cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice), error);
+    return true;
+}
+
+bool ff_load_shared_int8(FFContext *ctx, uint32_t layer, const FFProjection *gate, const FFProjection *up,
+                         const FFProjection *down, const char **error) {
+    if (error) *error = nullptr;
+    if (!ctx || !gate || !up || !down) return fail(error, "null argument");
+    if (layer >= ctx->cfg.layers) return fail(error, "layer " + std::to_string(layer) + " out of range");
+    const uint32_t d = ctx->cfg.d, fs = ctx->cfg.sharedF;
+    if (fs == 0) return fail(error, "context was created without a shared FFN");
+    if (d % 64 || fs % 64) return fail(error, "widths must be multiples of the group size 64");
+    const FFProjection *ps[3] = {gate, up, down};
+    const uint32_t wantRows[3] = {fs, fs, d}, wantCols[3] = {d, d, fs};
+    for (int m = 0; m < 3; ++m) {
+        if (!ps[m]->weights || !ps[m]->scales || !ps[m]->biases) return fail(error, "null projection tensor");
+        if (ps[m]->rows != wantRows[m] || ps[m]->cols != wantCols[m])
+            return fail(error, "SharedExpert dimension mismatch: gate=(" + std::to_string(gate->rows) + "," +
+                                   std::to_string(gate->cols) + ") up=(" + std::to_string(up->rows) + "," +
+                                   std::to_string(up->cols) + ") down=(" + std::to_string(down->rows) + "," +
+                                   std::to_string(down->cols) + ")");
+    }
+    FF_CUDA_OK(cudaSetDevice(ctx->device), error);
+    LayerStore &L = ctx->layers[layer];
+    if (L.shared) {
+        cudaFree(L.shared);
+        L.shared = nullptr;
+        L.mapsReady = false;
+        L.decodeMapsReady = false;
+    }
+    free_shared8(L);
+    for (int m = 0; m < 3; ++m) {
+        const size_t codes = (size_t)wantRows[m] * wantCols[m], aux = (size_t)wantRows[m] * (wantCols[m] / 64) * 2;
+        if (!upload(reinterpret_cast<void **>(&L.shared8W[m]), ps[m]->weights, codes, error) ||
+            !upload(reinterpret_cast<void **>(&L.shared8S[m]), ps[m]->scales, aux, error) ||
+            !upload(reinterpret_cast<void **>(&L.shared8B[m]), ps[m]->biases, aux, error))
+            return false;
+        ctx->weightBytes += codes + 2 * aux;
+    }
     return true;
 }
 

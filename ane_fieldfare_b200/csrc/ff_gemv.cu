@@ -710,6 +710,100 @@ k_router_logits_int8(const uint8_t *W, const uint16_t *scales, const uint16_t *b
     }
 }
 
+// INT8 affine shared FFN (Metal/Quant/dequant_int8.metal:41-138; Kernels/MoE/SharedExpertInt8.swift),
+// one warp per output row and up to four input rows, in the reference kernels' order made definite:
+// lane l takes elements 64 g + 2 l and + 1 of every group g in increasing g,
+//   acc = fma(s_g, fma(q1, x1, q0 * x0), acc);  acc = fma(b_g, x0 + x1, acc);
+// lane sums by an xor butterfly (16..1).  DUAL: gate and up rows of the same index, both rounded to
+// 16 bits, then act = r16(gelu_tanh(gate) * up); otherwise one matrix, out = r16(sum).
+template <bool DUAL>
+__global__ void __launch_bounds__(256)
+k_int8_rows(const uint8_t *W0, const uint16_t *S0, const uint16_t *B0, const uint8_t *W1, const uint16_t *S1,
+            const uint16_t *B1, const uint16_t *x, uint32_t xStride, int T, int rows, int cols, uint16_t *out,
+            uint32_t outStride) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + warp;
+    const int t0 = blockIdx.y * kInt8RouterTokens;
+    if (r >= rows) return;
+    const int groups = cols / 64;
+    const uint8_t *w0 = W0 + (size_t)r * cols, *w1 = DUAL ? W1 + (size_t)r * cols : nullptr;
+    const uint16_t *s0 = S0 + (size_t)r * groups, *b0 = B0 + (size_t)r * groups;
+    const uint16_t *s1 = DUAL ? S1 + (size_t)r * groups : nullptr, *b1 = DUAL ? B1 + (size_t)r * groups : nullptr;
+    float acc0[kInt8RouterTokens], acc1[kInt8RouterTokens];
+#pragma unroll
+    for (int i = 0; i < kInt8RouterTokens; ++i) acc0[i] = acc1[i] = 0.0f;
+    for (int g = 0; g < groups; ++g) {
+        const int idx = g * 64 + 2 * lane;
+        const uint32_t q = *reinterpret_cast<const uint16_t *>(w0 + idx);
+        const float q00 = (float)(q & 0xFFu), q01 = (float)(q >> 8);
+        const float sa = bf2f(s0[g]), ba = bf2f(b0[g]);
+        float q10 = 0.0f, q11 = 0.0f, sb = 0.0f, bb = 0.0f;
+        if (DUAL) {
+            const uint32_t p = *reinterpret_cast<const uint16_t *>(w1 + idx);
+            q10 = (float)(p & 0xFFu);
+            q11 = (float)(p >> 8);
+            sb = bf2f(s1[g]);
+            bb = bf2f(b1[g]);
+        }
+#pragma unroll
+        for (int i = 0; i < kInt8RouterTokens; ++i) {
+            const int t = min(t0 + i, T - 1);
+            const uint32_t xv = *reinterpret_cast<const uint32_t *>(x + (size_t)t * xStride + idx);
+            const float x0 = __uint_as_float(xv << 16), x1 = __uint_as_float(xv & 0xFFFF0000u);
+            const float sumX = x0 + x1;
+            acc0[i] = fmaf(sa, fmaf(q01, x1, q00 * x0), acc0[i]);
+            acc0[i] = fmaf(ba, sumX, acc0[i]);
+            if (DUAL) {
+                acc1[i] = fmaf(sb, fmaf(q11, x1, q10 * x0), acc1[i]);
+                acc1[i] = fmaf(bb, sumX, acc1[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kInt8RouterTokens; ++i) {
+        float a = acc0[i], b = acc1[i];
+#pragma unroll
+        for (int offset = 16; offset >= 1; offset >>= 1) {
+            a += __shfl_xor_sync(0xFFFFFFFFu, a, offset);
+            if (DUAL) b += __shfl_xor_sync(0xFFFFFFFFu, b, offset);
+        }
+        if (lane == 0 && t0 + i < T) {
+            uint16_t v;
+            if (DUAL) v = f2bf(gelu_tanh(bf16_round(a)) * bf16_round(b));
+            else v = f2bf(a);
+            out[(size_t)(t0 + i) * outStride + r] = v;
+        }
+    }
+}
+
+// y = down(r16(gelu_tanh(r16(gate x)) * r16(up x))) for any number of rows; the activations go through
+// the context's shared-activation scratch.
+bool launch_shared_int8(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride, uint32_t tokens,
+                        uint16_t *y, cudaStream_t stream, const char **error) {
+    if (tokens == 0) return true;
+    if (!L.has_shared8()) return fail(error, "layer has no resident shared FFN");
+    const int D = (int)ctx->cfg.d, Fs = (int)ctx->cfg.sharedF;
+    if (D % 64 || Fs % 64) return fail(error, "widths must be multiples of 64");
+    if (xStride % 2 || ((uintptr_t)x & 3)) return fail(error, "input rows must be 4-byte aligned");
+    if (tokens > ctx->cfg.maxTokens) return fail(error, "rows exceed the context's maxTokens");
+    uint16_t *acts = ctx->sharedActs;
+    const unsigned tokenBlocks = (tokens + kInt8RouterTokens - 1) / kInt8RouterTokens;
+    {
+        LaunchScope scope(ctx, stream, "shared_int8_gate_up_act");
+        k_int8_rows<true><<<dim3((Fs + 7) / 8, tokenBlocks), 256, 0, stream>>>(
+            L.shared8W[0], L.shared8S[0], L.shared8B[0], L.shared8W[1], L.shared8S[1], L.shared8B[1], x, xStride,
+            (int)tokens, Fs, D, acts, (uint32_t)Fs);
+    }
+    {
+        LaunchScope scope(ctx, stream, "shared_int8_down");
+        k_int8_rows<false><<<dim3((D + 7) / 8, tokenBlocks), 256, 0, stream>>>(
+            L.shared8W[2], L.shared8S[2], L.shared8B[2], nullptr, nullptr, nullptr, acts, (uint32_t)Fs, (int)tokens, D,
+            Fs, y, (uint32_t)D);
+    }
+    FF_CUDA_OK(cudaGetLastError(), error);
+    return true;
+}
+
 // Top-K of logits rows, one warp per row (the rows' logits are in global memory).
 __global__ void __launch_bounds__(256)
 k_topk_rows(const float *logits, const uint16_t *gain, int T, int E, int K, uint32_t *ids, uint16_t *weights) {

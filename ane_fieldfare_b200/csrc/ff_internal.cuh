@@ -118,6 +118,12 @@ struct LayerStore {
     uint8_t *routerQ = nullptr;
     uint16_t *routerQScale = nullptr, *routerQBias = nullptr;
     bool has_router() const { return routerW != nullptr || routerQ != nullptr; }
+    // INT8 affine shared FFN (the shipped checkpoints' form): gate, up [sharedF][d] and down
+    // [d][sharedF] as codes with one bf16 scale and bias per group of 64; set instead of `shared`
+    uint8_t *shared8W[3] = {nullptr, nullptr, nullptr};
+    uint16_t *shared8S[3] = {nullptr, nullptr, nullptr}, *shared8B[3] = {nullptr, nullptr, nullptr};
+    bool has_shared8() const { return shared8W[0] != nullptr; }
+    bool has_shared() const { return shared != nullptr || has_shared8(); }
     // prefill: tensor maps over the packed weights (gate, up, down) of routed and shared blobs
     bool mapsReady = false;
     CUtensorMap routedMap[3];
@@ -269,6 +275,8 @@ bool launch_post_attn_setup(FFContext *ctx, uint16_t *hidden, const uint16_t *at
 bool launch_layer_tail(FFContext *ctx, const uint16_t *h2, const uint16_t *h1, uint16_t *hidden,
                        const uint16_t *wPostFfn2, const uint16_t *wPostFfn, float eps, float layerScalar,
                        uint32_t tokens, cudaStream_t stream, const char **error);
+bool launch_shared_int8(FFContext *ctx, const LayerStore &L, const uint16_t *x, uint32_t xStride, uint32_t tokens,
+                        uint16_t *y, cudaStream_t stream, const char **error);
 bool launch_route_sort(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, uint32_t groups,
                        FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream, const char **error);
 bool launch_router_prefill(FFContext *ctx, const LayerStore &L, const uint16_t *x,

@@ -158,6 +158,19 @@ class HotpathContext:
                                       arrays[2].ctypes.data, rows, half * 2))
         call("ff_load_shared", self.handle, layer, *[ctypes.byref(p) for p in projs])
 
+    def loadSharedInt8(self, layer: int, gate, up, down):
+        """The INT8 affine shared FFN of the shipped checkpoints: every projection a tuple
+        (codes uint8 [rows][cols], scales bf16 bits [rows][cols/64], biases likewise)
+        (Kernels/MoE/SharedExpertInt8.swift:7-29)."""
+        keep, projs = [], []
+        for codes, scales, biases in (gate, up, down):
+            arrays = [np.ascontiguousarray(codes, dtype=np.uint8), np.ascontiguousarray(scales, dtype=np.uint16),
+                      np.ascontiguousarray(biases, dtype=np.uint16)]
+            keep.append(arrays)
+            rows, cols = arrays[0].shape
+            projs.append(FFProjection(arrays[0].ctypes.data, arrays[1].ctypes.data, arrays[2].ctypes.data, rows, cols))
+        call("ff_load_shared_int8", self.handle, layer, *[ctypes.byref(p) for p in projs])
+
     def loadRouter(self, layer: int, weights: np.ndarray, effectiveScale=None, perExpertScale=None,
                    logitBias=None):
         w = np.ascontiguousarray(weights, dtype=np.uint16)

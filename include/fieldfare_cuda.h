@@ -187,6 +187,15 @@ bool ff_load_router(FFContext *ctx, uint32_t layer, const uint16_t *weights,
                     const uint16_t *effectiveScale, const uint16_t *perExpertScale,
                     const float *logitBias, uint32_t experts, uint32_t d, const char **error);
 
+/* The shared FFN in the form the shipped checkpoints carry it: INT8 affine codes (one byte a weight)
+ * with one bf16 scale and bias per group of 64 inputs, three projections from HOST memory —
+ * `weights` uint8 [rows][cols], `scales`/`biases` bf16 [rows][cols/64]
+ * (Kernels/MoE/SharedExpertInt8.swift:7-29; kernels Metal/Quant/dequant_int8.metal:41-138).  Replaces
+ * any shared FFN the layer had; every operator that uses the shared FFN takes either form (the
+ * INT8 one runs as launches of its own, its rows are the residual of the routed part). */
+bool ff_load_shared_int8(FFContext *ctx, uint32_t layer, const FFProjection *gate, const FFProjection *up,
+                         const FFProjection *down, const char **error);
+
 /* The router in the form the shipped checkpoints carry it: INT8 affine codes [experts][d] with one
  * bf16 scale and bias per group of 64 inputs (Runtime/Inference/Model.swift:473-475; kernel body
  * Metal/MoE/moe.metal:65-103), from HOST memory; the other arguments as for ff_load_router.

@@ -739,6 +739,62 @@ void ffo_layer_tail(const uint16_t *h2, const uint16_t *h1, uint16_t *hidden, co
     free(h12);
 }
 
+/* ---- INT8 affine shared FFN -------------------------------------------------------------------- */
+
+/* One output of an INT8 affine matrix row against a 16-bit input row, in the order of the
+ * reference kernels (Sources/ANEFieldfareHotpath/Metal/Quant/dequant_int8.metal:41-83) made
+ * definite: lane l takes elements 64 g + 2 l and + 1 of every group g in increasing g,
+ *   acc = fma(s_g, fma(q1, x1, q0 * x0), acc);  acc = fma(b_g, x0 + x1, acc);
+ * the 32 lane sums are added by an xor butterfly (16, 8, 4, 2, 1). */
+static float int8_row_dot(const uint8_t *w, const uint16_t *s, const uint16_t *b, int32_t cols,
+                          const uint16_t *x) {
+    const int32_t groups = cols / 64;
+    float lane[32];
+    for (int l = 0; l < 32; ++l) {
+        float acc = 0.0f;
+        for (int32_t g = 0; g < groups; ++g) {
+            const int32_t idx = g * 64 + 2 * l;
+            const float x0 = ffo_bf16_to_float(x[idx]), x1 = ffo_bf16_to_float(x[idx + 1]);
+            const float q0 = (float)w[idx], q1 = (float)w[idx + 1];
+            acc = fmaf(ffo_bf16_to_float(s[g]), fmaf(q1, x1, q0 * x0), acc);
+            acc = fmaf(ffo_bf16_to_float(b[g]), x0 + x1, acc);
+        }
+        lane[l] = acc;
+    }
+    for (int offset = 16; offset >= 1; offset >>= 1) {
+        float next[32];
+        for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ offset];
+        memcpy(lane, next, sizeof(lane));
+    }
+    return lane[0];
+}
+
+/* SharedExpertInt8 (Kernels/MoE/SharedExpertInt8.swift; shared_int8_gate_up_act_simd,
+ * dequant_int8.metal:85-138): act = r16(gelu_tanh(r16(gate x)) * r16(up x)), y = r16(down act).
+ * Every projection: codes uint8 [rows][cols], scales and biases bf16 [rows][cols/64]. */
+void ffo_shared_ffn_int8(const uint8_t *gate_w, const uint16_t *gate_s, const uint16_t *gate_b,
+                         const uint8_t *up_w, const uint16_t *up_s, const uint16_t *up_b,
+                         const uint8_t *down_w, const uint16_t *down_s, const uint16_t *down_b,
+                         int32_t D, int32_t Fs, const uint16_t *x, int32_t T, uint16_t *y) {
+#pragma omp parallel for schedule(static) if (!omp_in_parallel() && T > 2)
+    for (int32_t t = 0; t < T; ++t) {
+        uint16_t *act = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)Fs);
+        const uint16_t *xr = x + (int64_t)t * D;
+        const int32_t gd = D / 64, gf = Fs / 64;
+        for (int32_t f = 0; f < Fs; ++f) {
+            const float g = ffo_bf16_to_float(ffo_bf16_bits(
+                int8_row_dot(gate_w + (int64_t)f * D, gate_s + (int64_t)f * gd, gate_b + (int64_t)f * gd, D, xr)));
+            const float u = ffo_bf16_to_float(ffo_bf16_bits(
+                int8_row_dot(up_w + (int64_t)f * D, up_s + (int64_t)f * gd, up_b + (int64_t)f * gd, D, xr)));
+            act[f] = ffo_bf16_bits(ffo_gelu_tanh(g) * u);
+        }
+        for (int32_t d = 0; d < D; ++d)
+            y[(int64_t)t * D + d] = ffo_bf16_bits(
+                int8_row_dot(down_w + (int64_t)d * Fs, down_s + (int64_t)d * gf, down_b + (int64_t)d * gf, Fs, act));
+        free(act);
+    }
+}
+
 /* ---- whole layer ------------------------------------------------------------------------- */
 
 /* Shared INT4 FFN: gate and up rounded to 16 bits before the activation, the activation rounded

@@ -96,6 +96,10 @@ void ffo_post_attn_setup(uint16_t *hidden, const uint16_t *attn, const uint16_t 
                          float eps, uint16_t *dense_x, uint16_t *routed_x, uint16_t *router_x);
 void ffo_layer_tail(const uint16_t *h2, const uint16_t *h1, uint16_t *hidden, const uint16_t *w_postffn2,
                     const uint16_t *w_postffn, int32_t T, int32_t D, float eps, float layer_scalar);
+void ffo_shared_ffn_int8(const uint8_t *gate_w, const uint16_t *gate_s, const uint16_t *gate_b,
+                         const uint8_t *up_w, const uint16_t *up_s, const uint16_t *up_b,
+                         const uint8_t *down_w, const uint16_t *down_s, const uint16_t *down_b,
+                         int32_t D, int32_t Fs, const uint16_t *x, int32_t T, uint16_t *y);
 void ffo_router_logits(const ffo_layer *L, const uint16_t *x, float *logits);
 void ffo_router_logits_int8(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases,
                             const uint16_t *effective_scale, const float *logit_bias, int32_t E,

@@ -183,6 +183,21 @@ def layer_tail(h2, h1, hidden, w_postffn2, w_postffn, eps, layer_scalar):
     return h
 
 
+def shared_ffn_int8(gate, up, down, x_bits):
+    """INT8 affine shared FFN (Kernels/MoE/SharedExpertInt8.swift): gate/up/down = (codes uint8
+    [rows][cols], scales, biases bf16 bits [rows][cols/64]); x bf16 bits [T][D] -> y bf16 bits."""
+    arrs = []
+    for codes, scales, biases in (gate, up, down):
+        arrs += [np.ascontiguousarray(codes, dtype=np.uint8), np.ascontiguousarray(scales, dtype=np.uint16),
+                 np.ascontiguousarray(biases, dtype=np.uint16)]
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    T, D = x_bits.shape
+    Fs = arrs[0].shape[0]
+    y = np.empty((T, D), dtype=np.uint16)
+    lib().ffo_shared_ffn_int8(*[_p(a) for a in arrs], c_int32(D), c_int32(Fs), _p(x_bits), c_int32(T), _p(y))
+    return y
+
+
 def router_topk_int8(codes, scales, biases, x_bits, K, effective_scale=None, logit_bias=None, gain=None):
     """INT8 affine router (Metal/MoE/moe.metal:65-103) + top-K: ids, 16-bit weights, logits."""
     codes = np.ascontiguousarray(codes, dtype=np.uint8)

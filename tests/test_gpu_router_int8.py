@@ -129,3 +129,66 @@ def test_int8_router_refusals():
             ctx.loadRouterInt8(3, codes, scales, biases)
     finally:
         ctx.close()
+
+
+def int8_projection(seed, rows, cols, amp):
+    codes = (synth.uniform(seed, rows * cols, 0.0, 256.0).astype(np.int64).clip(0, 255)).astype(np.uint8)
+    groups = cols // 64
+    scales = synth.uniform(seed + 1, rows * groups, 0.5, 1.5).reshape(rows, groups) * np.float32(2 * amp / 255)
+    biases = -np.float32(amp) * synth.uniform(seed + 2, rows * groups, 0.8, 1.2).reshape(rows, groups)
+    return (codes.reshape(rows, cols), synth.bf16_bits(scales.astype(np.float32)),
+            synth.bf16_bits(biases.astype(np.float32)))
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=["toy", "benchmark"])
+@pytest.mark.parametrize("rows", [1, 5, 40])
+def test_int8_shared_ffn(oracle, shape, rows):
+    """The INT8 affine shared FFN (Kernels/MoE/SharedExpertInt8.swift) against the oracle (same
+    defined order: equal except where the two tanh implementations round an activation apart), and
+    the whole layer with it against the layer put together from its parts, bit for bit."""
+    from conftest import ELEMENTWISE_TOL, assert_layer_close
+    hp = _hp()
+    D, Fs, K = shape["d"], shape["sharedF"], shape["topK"]
+    amp = 0.5 / np.sqrt(D)
+    gate, up = int8_projection(0x80, Fs, D, amp), int8_projection(0x83, Fs, D, amp)
+    down = int8_projection(0x86, D, Fs, 0.5 / np.sqrt(Fs))
+    L = workload.make_layer(0x1A, 0, **shape)
+    ctx = hp.HotpathContext(layers=1, maxTokens=64, **shape)
+    try:
+        ctx.loadLayer(0, L.blobs, L.layout.stride, L.layout.offsets)
+        ctx.loadRouter(0, L.routerW)
+        ctx.loadSharedInt8(0, gate, up, down)
+        x = workload.make_tokens(0x1A, f"int8.shared{rows}", rows, D)
+        xd = dev(x, ctx)
+        shared = torch.zeros((rows, D), dtype=torch.bfloat16, device=ctx.device)
+        hp.PrefillSharedExpert(ctx).encodeBlock(None, 0, xd, shared, rows)
+        torch.cuda.synchronize()
+        want = oracle.shared_ffn_int8(gate, up, down, x)
+        assert_layer_close(hp.bf16_numpy(shared), want, oracle, f"int8 shared rows={rows}",
+                           elementwise_tol=ELEMENTWISE_TOL)
+        assert np.mean(hp.bf16_numpy(shared) != want) < 2e-2
+        # the layer = router + routed experts + this shared FFN, against its parts
+        y = ctx.moeLayer(0, xd)
+        ids = torch.zeros((rows, K), dtype=torch.int32, device=ctx.device)
+        w = torch.zeros((rows, K), dtype=torch.bfloat16, device=ctx.device)
+        hp.PrefillRouter(ctx).encodeGemma4Block(None, 0, xd, ids, w, rows)
+        parts = torch.zeros((rows, D), dtype=torch.bfloat16, device=ctx.device)
+        if rows == 1:
+            hp.MoE(ctx).encodeRoutedPersistentGPUSlots(None, 0, ids, xd, w, shared, parts)
+        else:
+            partials = torch.zeros((rows * K, D), dtype=torch.bfloat16, device=ctx.device)
+            routed = hp.PrefillGroupedRoutedMoE(ctx)
+            if rows <= 16:
+                routed.encodeVerifyBound(None, 0, xd, ids, partials, rows)
+            else:
+                routed.encodeStreamedBatched(None, 0, xd, ids, partials, rows)
+            hp.PrefillMoE(ctx).encodeReduceTokenMajor(None, partials, w, parts, rows, residual=shared)
+        torch.cuda.synchronize()
+        assert torch.equal(y, parts)
+        hx = torch.from_numpy(x.view(np.int16).copy()).view(torch.bfloat16).pin_memory()
+        hy = torch.empty((rows, D), dtype=torch.bfloat16).pin_memory()
+        ctx.moeLayerHost(0, hx, hy)
+        assert torch.equal(hy, y.cpu())
+        assert ctx.info().deviceErrorFlag == 0
+    finally:
+        ctx.close()

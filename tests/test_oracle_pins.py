@@ -439,3 +439,29 @@ def test_fused_glue_steps_against_float64(oracle):
     u = r16(h12 * inv(h12) * f64(w[4]))
     want = r16(f64(hidden) + u) * f64(bits([0.7071]))[0]
     assert np.all(np.abs(f64(out) - want) <= 2 * step(want))
+
+
+def test_int8_shared_ffn_against_float64(oracle):
+    """ffo_shared_ffn_int8 (Kernels/MoE/SharedExpertInt8.swift; Metal/Quant/dequant_int8.metal:41-138)
+    against float64 with the same 16-bit rounding points."""
+    rng = np.random.default_rng(43)
+    D, Fs, T = 128, 192, 4
+
+    def proj(rows, cols, amp):
+        codes = rng.integers(0, 256, size=(rows, cols), dtype=np.uint8)
+        s = synth.bf16_bits((rng.uniform(0.5, 1.5, (rows, cols // 64)) * 2 * amp / 255).astype(np.float32))
+        b = synth.bf16_bits((-amp * rng.uniform(0.8, 1.2, (rows, cols // 64))).astype(np.float32))
+        return codes, s, b
+
+    gate, up, down = proj(Fs, D, 0.2), proj(Fs, D, 0.2), proj(D, Fs, 0.2)
+    x = synth.bf16_bits(rng.uniform(-1, 1, (T, D)).astype(np.float32))
+    y = oracle.shared_ffn_int8(gate, up, down, x)
+    f64 = lambda b: oracle.bf16_to_float(b).astype(np.float64)
+    r16 = lambda a: f64(synth.bf16_bits(np.asarray(a, dtype=np.float32)))
+    w = lambda p: p[0].astype(np.float64) * np.repeat(f64(p[1]), 64, axis=1) + np.repeat(f64(p[2]), 64, axis=1)
+    g, u = r16(f64(x) @ w(gate).T), r16(f64(x) @ w(up).T)
+    act = r16(0.5 * g * (1 + np.tanh(np.clip(0.7978845608028654 * (g + 0.044715 * g ** 3), -20, 20))) * u)
+    want = act @ w(down).T
+    got = f64(y)
+    assert np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()) < 6e-3   # 16-bit outputs, twice-rounded chain
+    assert np.abs(got - want).max() <= 2.0 ** -7 * max(1.0, np.abs(want).max())
