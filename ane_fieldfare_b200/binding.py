@@ -111,6 +111,10 @@ SIGNATURES = {
     "ff_post_attn_setup": (c_bool, [c_void_p, _P, _P, _P, _P, _P, c_uint32, c_float, _P, _P, _P, _P, _ERR]),
     "ff_layer_tail": (c_bool, [c_void_p, _P, _P, _P, _P, _P, c_uint32, c_float, c_float, _P, _ERR]),
     "ff_sort_routes": (c_bool, [c_void_p, _P, c_uint32, c_uint32, _P, _P, _P, _ERR]),
+    "ff_ep_create": (c_void_p, [POINTER(c_void_p), POINTER(c_void_p), c_uint32, c_uint32, _ERR]),
+    "ff_ep_destroy": (None, [c_void_p]),
+    "ff_ep_moe_layer": (c_bool, [c_void_p, c_uint32, POINTER(c_void_p), c_uint32, POINTER(c_void_p), _ERR]),
+    "ff_ep_last_rows_sent": (c_uint64, [c_void_p]),
 }
 
 _lib = None

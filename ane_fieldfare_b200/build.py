@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfieldfare_cuda.so")
-SOURCES = ["ff_context.cu", "ff_gturbo.cu", "ff_gemv.cu", "ff_decode.cu", "ff_block.cu", "ff_prefill.cu", "ff_api.cu"]
+SOURCES = ["ff_context.cu", "ff_gturbo.cu", "ff_gemv.cu", "ff_decode.cu", "ff_block.cu", "ff_prefill.cu", "ff_api.cu", "ff_ep.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

@@ -1,0 +1,311 @@
+// Expert parallelism behind the C ABI, one process driving every GPU of the group: the experts of a
+// layer are split evenly over the ranks (rank p holds experts [p*E/g, (p+1)*E/g)), every rank
+// routes its own rows, the rows travel to the ranks that hold their experts as stores into the
+// destination's memory, the partial rows come back as peer copies, and the home rank combines
+// them.  No collective library: the exchange is this file's own kernel writing over NVLink and
+// cudaMemcpyPeerAsync, ordered by events between the ranks' streams.
+#include <string>
+#include <vector>
+
+#include "ff_internal.cuh"
+
+using namespace ff;
+
+namespace {
+
+// destination rank of every route: the contiguous placement
+__global__ void k_ep_destination(const uint32_t *__restrict__ ids, uint32_t n, uint32_t expertsPerRank,
+                                 uint32_t *__restrict__ dest) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dest[i] = ids[i] / expertsPerRank;
+}
+
+// where each (token, rank-in-row) route sits in the destination-sorted order
+__global__ void k_ep_row_index(const FFTokenExpertPair *__restrict__ pairs, uint32_t n, uint32_t topK,
+                               uint32_t *__restrict__ rowIndex) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) rowIndex[pairs[i].token * topK + pairs[i].rank] = i;
+}
+
+// One warp per route: copies the route's input row (16-byte pieces) and its expert id, local to the
+// destination, into the destination rank's receive buffers — `dstRows` and `dstIds` may be another
+// GPU's memory (plain stores over NVLink).
+__global__ void __launch_bounds__(256)
+k_ep_send_rows(const uint16_t *__restrict__ x, uint32_t xStride, uint32_t d,
+               const FFTokenExpertPair *__restrict__ pairs, uint32_t n, const uint32_t *__restrict__ ids,
+               uint32_t topK, uint32_t expertsPerRank, uint16_t *__restrict__ dstRows,
+               uint32_t *__restrict__ dstIds) {
+    const uint32_t warpsPerCta = blockDim.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t i = blockIdx.x * warpsPerCta + (threadIdx.x >> 5); i < n; i += gridDim.x * warpsPerCta) {
+        const FFTokenExpertPair p = pairs[i];
+        const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)p.token * xStride);
+        uint4 *dst = reinterpret_cast<uint4 *>(dstRows + (size_t)i * d);
+        for (uint32_t c = lane; c < d / 8; c += 32) dst[c] = src[c];
+        if (lane == 0) dstIds[i] = ids[p.token * topK + p.rank] % expertsPerRank;
+    }
+}
+
+struct Rank {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t sent = nullptr, returned = nullptr;
+    uint32_t *ids = nullptr;         // [tokens][K] global expert ids
+    uint16_t *weights = nullptr;     // [tokens][K]
+    uint32_t *dest = nullptr;        // [tokens][K] destination rank of each route
+    FFTokenExpertPair *pairs = nullptr;  // routes sorted by destination
+    uint32_t *offsets = nullptr;     // [world + 1] first route of each destination
+    uint32_t *hostOffsets = nullptr; // pinned copy
+    uint32_t *rowIndex = nullptr;    // [tokens][K] row of `back` holding each route's partial
+    uint16_t *recvRows = nullptr;    // [capacity][d] rows received for this rank's experts
+    uint32_t *recvIds = nullptr;     // [capacity] their local expert ids
+    uint16_t *partials = nullptr;    // [capacity][d] this rank's experts' outputs
+    uint16_t *back = nullptr;        // [tokens*K][d] partial rows of this rank's own routes, returned
+    uint16_t *sharedOut = nullptr;   // [tokens][d]
+};
+
+template <typename T>
+bool device_alloc(T **p, size_t count, const char **error) {
+    FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(p), count * sizeof(T)), error);
+    return true;
+}
+
+}  // namespace
+
+struct FFEPGroup {
+    uint32_t world = 0, experts = 0, expertsPerRank = 0, d = 0, topK = 0, maxTokens = 0, capacity = 0;
+    std::vector<FFContext *> home, expert;
+    std::vector<Rank> ranks;
+    uint64_t lastRowsSent = 0;
+};
+
+namespace {
+
+void release(FFEPGroup *g) {
+    for (Rank &r : g->ranks) {
+        cudaSetDevice(r.device);
+        if (r.stream) cudaStreamSynchronize(r.stream);
+        cudaFree(r.ids); cudaFree(r.weights); cudaFree(r.dest); cudaFree(r.pairs); cudaFree(r.offsets);
+        cudaFree(r.rowIndex); cudaFree(r.recvRows); cudaFree(r.recvIds); cudaFree(r.partials);
+        cudaFree(r.back); cudaFree(r.sharedOut);
+        if (r.hostOffsets) cudaFreeHost(r.hostOffsets);
+        if (r.sent) cudaEventDestroy(r.sent);
+        if (r.returned) cudaEventDestroy(r.returned);
+        if (r.stream) cudaStreamDestroy(r.stream);
+    }
+    delete g;
+}
+
+bool build_group(FFEPGroup *g, const char **error) {
+    const uint32_t world = g->world;
+    for (uint32_t r = 0; r < world; ++r) {
+        Rank &R = g->ranks[r];
+        R.device = g->home[r]->device;
+        FF_CUDA_OK(cudaSetDevice(R.device), error);
+        for (uint32_t p = 0; p < world; ++p) {
+            const int peer = g->home[p]->device;
+            if (peer == R.device) continue;
+            int can = 0;
+            FF_CUDA_OK(cudaDeviceCanAccessPeer(&can, R.device, peer), error);
+            if (!can)
+                return fail(error, "device " + std::to_string(R.device) + " cannot address device " +
+                                       std::to_string(peer) + ": the group needs peer access between all its GPUs");
+            const cudaError_t st = cudaDeviceEnablePeerAccess(peer, 0);
+            if (st == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else FF_CUDA_OK(st, error);
+        }
+        FF_CUDA_OK(cudaStreamCreateWithFlags(&R.stream, cudaStreamNonBlocking), error);
+        FF_CUDA_OK(cudaEventCreateWithFlags(&R.sent, cudaEventDisableTiming), error);
+        FF_CUDA_OK(cudaEventCreateWithFlags(&R.returned, cudaEventDisableTiming), error);
+        const size_t routes = (size_t)g->maxTokens * g->topK;
+        if (!device_alloc(&R.ids, routes, error) || !device_alloc(&R.weights, routes, error) ||
+            !device_alloc(&R.dest, routes, error) || !device_alloc(&R.pairs, routes, error) ||
+            !device_alloc(&R.offsets, world + 1, error) || !device_alloc(&R.rowIndex, routes, error) ||
+            !device_alloc(&R.recvRows, (size_t)g->capacity * g->d, error) ||
+            !device_alloc(&R.recvIds, g->capacity, error) ||
+            !device_alloc(&R.partials, (size_t)g->capacity * g->d, error) ||
+            !device_alloc(&R.back, routes * g->d, error) ||
+            !device_alloc(&R.sharedOut, (size_t)g->maxTokens * g->d, error))
+            return false;
+        FF_CUDA_OK(cudaMallocHost(reinterpret_cast<void **>(&R.hostOffsets), (world + 1) * sizeof(uint32_t)), error);
+    }
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+FFEPGroup *ff_ep_create(FFContext *const *home, FFContext *const *expert, uint32_t world,
+                        uint32_t capacityRows, const char **error) {
+    if (error) *error = nullptr;
+    if (!home || !expert || world == 0 || world > 64) {
+        fail(error, "expert-parallel group needs 1...64 ranks with a home and an expert context each");
+        return nullptr;
+    }
+    FFEPGroup *g = new FFEPGroup;
+    g->world = world;
+    g->home.assign(home, home + world);
+    g->expert.assign(expert, expert + world);
+    g->ranks.resize(world);
+    auto refuse = [&](const std::string &message) -> FFEPGroup * {
+        fail(error, message);
+        release(g);
+        return nullptr;
+    };
+    for (uint32_t r = 0; r < world; ++r)
+        if (!home[r] || !expert[r]) return refuse("null context for rank " + std::to_string(r));
+    for (uint32_t r = 0; r < world; ++r) {
+        if (home[r]->device != expert[r]->device)
+            return refuse("rank " + std::to_string(r) + ": home and expert context sit on different devices");
+        for (uint32_t q = 0; q < r; ++q)
+            if (home[q]->device == home[r]->device) return refuse("two ranks share device " + std::to_string(home[r]->device));
+    }
+    const FFConfig &h = home[0]->cfg, &x = expert[0]->cfg;
+    g->experts = h.experts;
+    g->d = h.d;
+    g->topK = h.topK;
+    g->maxTokens = h.maxTokens;
+    if (h.experts % world) return refuse("the experts do not divide evenly over the ranks");
+    g->expertsPerRank = h.experts / world;
+    if (h.d % 8) return refuse("the hidden width must be a multiple of 8");
+    g->capacity = capacityRows ? capacityRows : world * h.maxTokens * h.topK;
+    for (uint32_t r = 0; r < world; ++r) {
+        const FFConfig &hr = home[r]->cfg, &xr = expert[r]->cfg;
+        if (hr.layers != h.layers || hr.experts != h.experts || hr.d != h.d || hr.topK != h.topK ||
+            hr.maxTokens != h.maxTokens)
+            return refuse("the home contexts of all ranks must share one configuration");
+        if (xr.layers != x.layers || xr.experts != g->expertsPerRank || xr.d != h.d || xr.topK != 1)
+            return refuse("an expert context holds experts/world experts of the same width, with topK = 1 "
+                          "(a received row is a one-route token)");
+        if (xr.maxTokens < g->capacity)
+            return refuse("an expert context's maxTokens must cover the group's capacity of " +
+                          std::to_string(g->capacity) + " received rows");
+    }
+    if (!build_group(g, error)) {
+        release(g);
+        return nullptr;
+    }
+    return g;
+}
+
+void ff_ep_destroy(FFEPGroup *group) {
+    if (group) release(group);
+}
+
+uint64_t ff_ep_last_rows_sent(const FFEPGroup *group) { return group ? group->lastRowsSent : 0; }
+
+bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uint32_t tokens,
+                     uint16_t *const *y, const char **error) {
+    if (error) *error = nullptr;
+    if (!g || !x || !y) return fail(error, "null argument");
+    if (tokens == 0) return true;
+    if (tokens > g->maxTokens)
+        return fail(error, std::to_string(tokens) + " rows per rank exceed the group's " + std::to_string(g->maxTokens));
+    const uint32_t world = g->world, K = g->topK, D = g->d;
+    const uint32_t routes = tokens * K;
+    if (layer >= g->home[0]->cfg.layers || layer >= g->expert[0]->cfg.layers) return fail(error, "layer out of range");
+
+    // 1. every rank: router, shared FFN, destination of every route, routes sorted by destination
+    for (uint32_t r = 0; r < world; ++r) {
+        Rank &R = g->ranks[r];
+        if (!x[r] || !y[r]) return fail(error, "null row pointer for rank " + std::to_string(r));
+        FF_CUDA_OK(cudaSetDevice(R.device), error);
+        if (!ff_router_topk(g->home[r], layer, x[r], D, tokens, R.ids, R.weights, nullptr, R.stream, error)) return false;
+        k_ep_destination<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.ids, routes, g->expertsPerRank, R.dest);
+        FF_CUDA_OK(cudaGetLastError(), error);
+        if (!ff_sort_routes(g->home[r], R.dest, tokens, world, R.pairs, R.offsets, R.stream, error)) return false;
+        FF_CUDA_OK(cudaMemcpyAsync(R.hostOffsets, R.offsets, (world + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                                   R.stream), error);
+        k_ep_row_index<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.pairs, routes, K, R.rowIndex);
+        FF_CUDA_OK(cudaGetLastError(), error);
+    }
+    for (uint32_t r = 0; r < world; ++r) {
+        FF_CUDA_OK(cudaSetDevice(g->ranks[r].device), error);
+        FF_CUDA_OK(cudaStreamSynchronize(g->ranks[r].stream), error);
+        if (g->ranks[r].hostOffsets[world] != routes)
+            return fail(error, "the router of rank " + std::to_string(r) + " wrote an expert id out of range");
+    }
+
+    // 2. where each source's rows land in each destination's receive buffer
+    std::vector<uint32_t> base((size_t)world * world), total(world, 0);  // base[p * world + s]
+    for (uint32_t p = 0; p < world; ++p) {
+        for (uint32_t s = 0; s < world; ++s) {
+            base[(size_t)p * world + s] = total[p];
+            total[p] += g->ranks[s].hostOffsets[p + 1] - g->ranks[s].hostOffsets[p];
+        }
+        if (total[p] > g->capacity)
+            return fail(error, "rank " + std::to_string(p) + " would receive " + std::to_string(total[p]) +
+                                   " rows, more than the group's capacity " + std::to_string(g->capacity));
+    }
+
+    // 3. dispatch: stores into the destinations' buffers; the shared FFN runs behind them
+    const bool withShared = g->home[0]->layers[layer].has_shared();
+    uint64_t sentAway = 0;
+    for (uint32_t s = 0; s < world; ++s) {
+        Rank &S = g->ranks[s];
+        FF_CUDA_OK(cudaSetDevice(S.device), error);
+        for (uint32_t p = 0; p < world; ++p) {
+            const uint32_t first = S.hostOffsets[p], n = S.hostOffsets[p + 1] - first;
+            if (!n) continue;
+            if (p != s) sentAway += n;
+            Rank &P = g->ranks[p];
+            const uint32_t at = base[(size_t)p * world + s];
+            const uint32_t ctas = (n + 7) / 8 < 1184u ? (n + 7) / 8 : 1184u;
+            k_ep_send_rows<<<ctas, 256, 0, S.stream>>>(x[s], D, D, S.pairs + first, n, S.ids, K, g->expertsPerRank,
+                                                       P.recvRows + (size_t)at * D, P.recvIds + at);
+            FF_CUDA_OK(cudaGetLastError(), error);
+        }
+        FF_CUDA_OK(cudaEventRecord(S.sent, S.stream), error);
+        if (withShared && !ff_shared_ffn(g->home[s], layer, x[s], D, tokens, S.sharedOut, S.stream, error)) return false;
+    }
+    g->lastRowsSent = sentAway;
+
+    // 4. every rank's experts on what it received, then the partial rows go home
+    for (uint32_t p = 0; p < world; ++p) {
+        Rank &P = g->ranks[p];
+        FF_CUDA_OK(cudaSetDevice(P.device), error);
+        for (uint32_t s = 0; s < world; ++s)
+            if (s != p) FF_CUDA_OK(cudaStreamWaitEvent(P.stream, g->ranks[s].sent, 0), error);
+        if (total[p] &&
+            !ff_moe_prefill(g->expert[p], layer, P.recvRows, D, total[p], P.recvIds, P.partials, P.stream, error))
+            return false;
+        for (uint32_t s = 0; s < world; ++s) {
+            const uint32_t first = g->ranks[s].hostOffsets[p], n = g->ranks[s].hostOffsets[p + 1] - first;
+            if (!n) continue;
+            const uint16_t *src = P.partials + (size_t)base[(size_t)p * world + s] * D;
+            uint16_t *dst = g->ranks[s].back + (size_t)first * D;
+            const size_t bytes = (size_t)n * D * sizeof(uint16_t);
+            if (s == p) FF_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, P.stream), error);
+            else FF_CUDA_OK(cudaMemcpyPeerAsync(dst, g->ranks[s].device, src, P.device, bytes, P.stream), error);
+        }
+        FF_CUDA_OK(cudaEventRecord(P.returned, P.stream), error);
+    }
+
+    // 5. combine at home: weighted sum of each row's K partials in rank order, plus the shared rows
+    for (uint32_t r = 0; r < world; ++r) {
+        Rank &R = g->ranks[r];
+        FF_CUDA_OK(cudaSetDevice(R.device), error);
+        for (uint32_t p = 0; p < world; ++p)
+            if (p != r) FF_CUDA_OK(cudaStreamWaitEvent(R.stream, g->ranks[p].returned, 0), error);
+        if (!ff_moe_reduce_indexed(g->home[r], R.back, R.rowIndex, R.weights, withShared ? R.sharedOut : nullptr, y[r],
+                                   tokens, R.stream, error))
+            return false;
+    }
+    for (uint32_t r = 0; r < world; ++r) {
+        FF_CUDA_OK(cudaSetDevice(g->ranks[r].device), error);
+        FF_CUDA_OK(cudaStreamSynchronize(g->ranks[r].stream), error);
+    }
+    for (uint32_t r = 0; r < world; ++r) {
+        FFContext *both[2] = {g->home[r], g->expert[r]};
+        for (FFContext *c : both) {
+            uint32_t flag = 0;
+            FF_CUDA_OK(cudaSetDevice(c->device), error);
+            FF_CUDA_OK(cudaMemcpy(&flag, c->errorFlag, sizeof(flag), cudaMemcpyDeviceToHost), error);
+            if (flag) return fail(error, "a kernel of rank " + std::to_string(r) + " gave up waiting (error flag " +
+                                             std::to_string(flag) + ")");
+        }
+    }
+    return true;
+}
+
+}  // extern "C"

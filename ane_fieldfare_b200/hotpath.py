@@ -19,7 +19,7 @@ from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
-from typing import Optional, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -530,3 +530,53 @@ class CudaRoutedPrefillGuest:
             raise
         self.profile["layers"] += 1
         self.profile["pairs"] += queryCount * self.context.topK
+
+
+class ExpertParallelGroup:
+    """`ff_ep_*`: one process driving every GPU of an expert-parallel group.  `home[r]` holds rank
+    r's router and shared FFN (experts = E, topK = K), `expert[r]` its E/world experts (topK = 1,
+    maxTokens >= the capacity).  The reference runs on one device; this stands where its
+    `PrefillMoE` block stands (Kernels/Prefill/MoE/PrefillMoE.swift:60-140) with the grouped experts
+    spread over devices."""
+
+    def __init__(self, home: List[HotpathContext], expert: List[HotpathContext], capacityRows: int = 0):
+        if len(home) != len(expert) or not home:
+            raise ValueError("one home and one expert context per rank")
+        self.home, self.expert = list(home), list(expert)
+        world = len(home)
+        arr = ctypes.c_void_p * world
+        err = ctypes.c_char_p()
+        self._handle = binding.load().ff_ep_create(arr(*[c.handle for c in home]), arr(*[c.handle for c in expert]),
+                                                   world, capacityRows, ctypes.byref(err))
+        if not self._handle:
+            raise FieldfareError(err.value.decode() if err.value else "ff_ep_create failed")
+
+    def close(self):
+        if getattr(self, "_handle", None):
+            binding.load().ff_ep_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def moeLayer(self, layer: int, x: List[torch.Tensor]) -> List[torch.Tensor]:
+        """x[r]: bf16 [tokens][d] on rank r's device, complete (the call runs on the group's own
+        streams); returns every rank's output rows, complete."""
+        world = len(self.home)
+        if len(x) != world or any(t.shape != x[0].shape for t in x):
+            raise ValueError("one tensor of the same shape per rank")
+        for r, t in enumerate(x):
+            if t.device != self.home[r].device:
+                raise ValueError(f"rank {r}'s rows are on {t.device}, its contexts on {self.home[r].device}")
+        y = [torch.empty_like(t) for t in x]
+        arr = ctypes.c_void_p * world
+        call("ff_ep_moe_layer", self._handle, layer, arr(*[_ptr(t) for t in x]), x[0].shape[0],
+             arr(*[_ptr(t) for t in y]))
+        return y
+
+    @property
+    def lastRowsSent(self) -> int:
+        return int(binding.load().ff_ep_last_rows_sent(self._handle))

@@ -385,6 +385,35 @@ bool ff_sort_routes(FFContext *ctx, const uint32_t *groupIds, uint32_t tokens, u
                     FFTokenExpertPair *sortedPairs, uint32_t *offsets, cudaStream_t stream,
                     const char **error);
 
+/* ---- expert parallelism over several GPUs of one process ----------------------------------- */
+
+/* A group of `world` ranks, one GPU each, that splits every layer's experts evenly: rank p holds
+ * experts [p*E/world, (p+1)*E/world).  The reference runs on one device and has no counterpart; the
+ * operator it stands in for is the whole block of `PrefillMoE` (Kernels/Prefill/MoE/PrefillMoE.swift:
+ * 60-140) with the grouped experts spread over devices.  `home[r]` is rank r's context with the
+ * router and the shared FFN of every layer (experts = E, topK = K; it needs no expert blobs),
+ * `expert[r]` its context holding E/world experts per layer in local order, created with topK = 1
+ * (a received row is a one-route token) and maxTokens >= the capacity.  `capacityRows` bounds the
+ * rows one rank may receive in a call (0: world * maxTokens * K, the worst case).  Every pair of
+ * the group's devices must have peer access.  The contexts stay the caller's. */
+typedef struct FFEPGroup FFEPGroup;
+FFEPGroup *ff_ep_create(FFContext *const *home, FFContext *const *expert, uint32_t world,
+                        uint32_t capacityRows, const char **error);
+void ff_ep_destroy(FFEPGroup *group);
+
+/* One MoE block under expert parallelism: x[r] and y[r] are bf16 [tokens][d] on rank r's device,
+ * contiguous and 16-byte aligned.  Per rank: router top-K, routes sorted by destination rank on the
+ * device, rows and local expert ids stored into the destination's receive buffer over NVLink, the
+ * destination's grouped INT4 experts, partial rows copied back, weighted sum in rank order plus the
+ * shared FFN's rows.  Rows travel once per route.  The call runs on the group's own streams and is
+ * synchronous: inputs must be complete when it is made, outputs are complete when it returns.
+ * Results equal ff_moe_layer's on one device holding all experts, bit for bit, for more than 16
+ * rows per rank. */
+bool ff_ep_moe_layer(FFEPGroup *group, uint32_t layer, const uint16_t *const *x, uint32_t tokens,
+                     uint16_t *const *y, const char **error);
+/* Rows the last ff_ep_moe_layer sent to another GPU (each also came back as a partial row). */
+uint64_t ff_ep_last_rows_sent(const FFEPGroup *group);
+
 /* Device-side result of the last ff_moe_prefill permute, copied to the host after a sync:
  * the expert-sorted pairs and per-expert row offsets [experts+1].  For parity tests. */
 bool ff_last_prefill_routes(FFContext *ctx, FFTokenExpertPair *sortedPairs, uint32_t *offsets,
