@@ -13,11 +13,14 @@ using namespace ff;
 
 namespace {
 
-// destination rank of every route: the contiguous placement
+// destination rank of every route: the layer's placement table, or contiguous blocks without one
 __global__ void k_ep_destination(const uint32_t *__restrict__ ids, uint32_t n, uint32_t expertsPerRank,
+                                 uint32_t experts, const uint32_t *__restrict__ rankOf,
                                  uint32_t *__restrict__ dest) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dest[i] = ids[i] / expertsPerRank;
+    if (i >= n) return;
+    const uint32_t e = ids[i];
+    dest[i] = e >= experts ? 0xFFFFFFFFu : rankOf ? rankOf[e] : e / expertsPerRank;
 }
 
 // where each (token, rank-in-row) route sits in the destination-sorted order
@@ -33,15 +36,18 @@ __global__ void k_ep_row_index(const FFTokenExpertPair *__restrict__ pairs, uint
 __global__ void __launch_bounds__(256)
 k_ep_send_rows(const uint16_t *__restrict__ x, uint32_t xStride, uint32_t d,
                const FFTokenExpertPair *__restrict__ pairs, uint32_t n, const uint32_t *__restrict__ ids,
-               uint32_t topK, uint32_t expertsPerRank, uint16_t *__restrict__ dstRows,
-               uint32_t *__restrict__ dstIds) {
+               uint32_t topK, uint32_t expertsPerRank, const uint32_t *__restrict__ localOf,
+               uint16_t *__restrict__ dstRows, uint32_t *__restrict__ dstIds) {
     const uint32_t warpsPerCta = blockDim.x >> 5, lane = threadIdx.x & 31;
     for (uint32_t i = blockIdx.x * warpsPerCta + (threadIdx.x >> 5); i < n; i += gridDim.x * warpsPerCta) {
         const FFTokenExpertPair p = pairs[i];
         const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)p.token * xStride);
         uint4 *dst = reinterpret_cast<uint4 *>(dstRows + (size_t)i * d);
         for (uint32_t c = lane; c < d / 8; c += 32) dst[c] = src[c];
-        if (lane == 0) dstIds[i] = ids[p.token * topK + p.rank] % expertsPerRank;
+        if (lane == 0) {
+            const uint32_t e = ids[p.token * topK + p.rank];
+            dstIds[i] = localOf ? localOf[e] : e % expertsPerRank;
+        }
     }
 }
 
@@ -61,6 +67,9 @@ struct Rank {
     uint16_t *partials = nullptr;    // [capacity][d] this rank's experts' outputs
     uint16_t *back = nullptr;        // [tokens*K][d] partial rows of this rank's own routes, returned
     uint16_t *sharedOut = nullptr;   // [tokens][d]
+    uint16_t *normed = nullptr;      // [tokens][d] stack: the layer's input
+    uint16_t *between = nullptr;     // [tokens][d] stack: a layer's output that is not the last
+    std::vector<uint32_t *> placement;  // per layer: [2][experts] rank of every expert, then its local slot; null = contiguous
 };
 
 template <typename T>
@@ -86,7 +95,8 @@ void release(FFEPGroup *g) {
         if (r.stream) cudaStreamSynchronize(r.stream);
         cudaFree(r.ids); cudaFree(r.weights); cudaFree(r.dest); cudaFree(r.pairs); cudaFree(r.offsets);
         cudaFree(r.rowIndex); cudaFree(r.recvRows); cudaFree(r.recvIds); cudaFree(r.partials);
-        cudaFree(r.back); cudaFree(r.sharedOut);
+        cudaFree(r.back); cudaFree(r.sharedOut); cudaFree(r.normed); cudaFree(r.between);
+        for (uint32_t *t : r.placement) cudaFree(t);
         if (r.hostOffsets) cudaFreeHost(r.hostOffsets);
         if (r.sent) cudaEventDestroy(r.sent);
         if (r.returned) cudaEventDestroy(r.returned);
@@ -124,8 +134,11 @@ bool build_group(FFEPGroup *g, const char **error) {
             !device_alloc(&R.recvIds, g->capacity, error) ||
             !device_alloc(&R.partials, (size_t)g->capacity * g->d, error) ||
             !device_alloc(&R.back, routes * g->d, error) ||
-            !device_alloc(&R.sharedOut, (size_t)g->maxTokens * g->d, error))
+            !device_alloc(&R.sharedOut, (size_t)g->maxTokens * g->d, error) ||
+            !device_alloc(&R.normed, (size_t)g->maxTokens * g->d, error) ||
+            !device_alloc(&R.between, (size_t)g->maxTokens * g->d, error))
             return false;
+        R.placement.assign(g->home[r]->cfg.layers, nullptr);
         FF_CUDA_OK(cudaMallocHost(reinterpret_cast<void **>(&R.hostOffsets), (world + 1) * sizeof(uint32_t)), error);
     }
     return true;
@@ -194,16 +207,13 @@ void ff_ep_destroy(FFEPGroup *group) {
 
 uint64_t ff_ep_last_rows_sent(const FFEPGroup *group) { return group ? group->lastRowsSent : 0; }
 
-bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uint32_t tokens,
-                     uint16_t *const *y, const char **error) {
-    if (error) *error = nullptr;
-    if (!g || !x || !y) return fail(error, "null argument");
-    if (tokens == 0) return true;
-    if (tokens > g->maxTokens)
-        return fail(error, std::to_string(tokens) + " rows per rank exceed the group's " + std::to_string(g->maxTokens));
+// One block, queued on the ranks' streams.  The host waits once, for the counts of rows per
+// destination; the rest is ordered by events, so consecutive layers need no wait between them: a
+// rank sends its next rows only behind its own combine, which waited for every rank's experts.
+static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uint32_t tokens,
+                      uint16_t *const *y, const char **error) {
     const uint32_t world = g->world, K = g->topK, D = g->d;
     const uint32_t routes = tokens * K;
-    if (layer >= g->home[0]->cfg.layers || layer >= g->expert[0]->cfg.layers) return fail(error, "layer out of range");
 
     // 1. every rank: router, shared FFN, destination of every route, routes sorted by destination
     for (uint32_t r = 0; r < world; ++r) {
@@ -211,7 +221,8 @@ bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uin
         if (!x[r] || !y[r]) return fail(error, "null row pointer for rank " + std::to_string(r));
         FF_CUDA_OK(cudaSetDevice(R.device), error);
         if (!ff_router_topk(g->home[r], layer, x[r], D, tokens, R.ids, R.weights, nullptr, R.stream, error)) return false;
-        k_ep_destination<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.ids, routes, g->expertsPerRank, R.dest);
+        k_ep_destination<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.ids, routes, g->expertsPerRank, g->experts,
+                                                                     R.placement[layer], R.dest);
         FF_CUDA_OK(cudaGetLastError(), error);
         if (!ff_sort_routes(g->home[r], R.dest, tokens, world, R.pairs, R.offsets, R.stream, error)) return false;
         FF_CUDA_OK(cudaMemcpyAsync(R.hostOffsets, R.offsets, (world + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost,
@@ -252,6 +263,7 @@ bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uin
             const uint32_t at = base[(size_t)p * world + s];
             const uint32_t ctas = (n + 7) / 8 < 1184u ? (n + 7) / 8 : 1184u;
             k_ep_send_rows<<<ctas, 256, 0, S.stream>>>(x[s], D, D, S.pairs + first, n, S.ids, K, g->expertsPerRank,
+                                                       S.placement[layer] ? S.placement[layer] + g->experts : nullptr,
                                                        P.recvRows + (size_t)at * D, P.recvIds + at);
             FF_CUDA_OK(cudaGetLastError(), error);
         }
@@ -291,6 +303,12 @@ bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uin
                                    tokens, R.stream, error))
             return false;
     }
+    return true;
+}
+
+// Waits for every rank's stream and reads every context's error flag.
+static bool finish(FFEPGroup *g, const char **error) {
+    const uint32_t world = g->world;
     for (uint32_t r = 0; r < world; ++r) {
         FF_CUDA_OK(cudaSetDevice(g->ranks[r].device), error);
         FF_CUDA_OK(cudaStreamSynchronize(g->ranks[r].stream), error);
@@ -304,6 +322,72 @@ bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uin
             if (flag) return fail(error, "a kernel of rank " + std::to_string(r) + " gave up waiting (error flag " +
                                              std::to_string(flag) + ")");
         }
+    }
+    return true;
+}
+
+static bool check_call(FFEPGroup *g, uint32_t firstLayer, uint32_t layerCount, const uint16_t *const *x,
+                       uint32_t tokens, uint16_t *const *y, const char **error) {
+    if (error) *error = nullptr;
+    if (!g || !x || !y) return fail(error, "null argument");
+    if (tokens > g->maxTokens)
+        return fail(error, std::to_string(tokens) + " rows per rank exceed the group's " + std::to_string(g->maxTokens));
+    if (layerCount == 0 || firstLayer + layerCount > g->home[0]->cfg.layers ||
+        firstLayer + layerCount > g->expert[0]->cfg.layers)
+        return fail(error, "layer out of range");
+    for (uint32_t r = 0; r < g->world; ++r)
+        if (!x[r] || !y[r] || ((reinterpret_cast<uintptr_t>(x[r]) | reinterpret_cast<uintptr_t>(y[r])) & 15u))
+            return fail(error, "rank " + std::to_string(r) + ": rows must be non-null and 16-byte aligned");
+    return true;
+}
+
+bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uint32_t tokens,
+                     uint16_t *const *y, const char **error) {
+    if (!check_call(g, layer, 1, x, tokens, y, error)) return false;
+    if (tokens == 0) return true;
+    return run_layer(g, layer, x, tokens, y, error) && finish(g, error);
+}
+
+bool ff_ep_moe_stack(FFEPGroup *g, uint32_t firstLayer, uint32_t layerCount, const uint16_t *const *x,
+                     uint32_t tokens, float eps, uint16_t *const *y, const char **error) {
+    if (!check_call(g, firstLayer, layerCount, x, tokens, y, error)) return false;
+    if (tokens == 0) return true;
+    const uint32_t world = g->world;
+    std::vector<const uint16_t *> cur(x, x + world), in(world);
+    std::vector<uint16_t *> out(world);
+    for (uint32_t i = 0; i < layerCount; ++i) {
+        for (uint32_t r = 0; r < world; ++r) {
+            Rank &R = g->ranks[r];
+            if (!ff_rmsnorm(g->home[r], cur[r], nullptr, eps, tokens, R.normed, R.stream, error)) return false;
+            in[r] = R.normed;
+            out[r] = i + 1 == layerCount ? y[r] : R.between;
+        }
+        if (!run_layer(g, firstLayer + i, in.data(), tokens, out.data(), error)) return false;
+        for (uint32_t r = 0; r < world; ++r) cur[r] = out[r];
+    }
+    return finish(g, error);
+}
+
+bool ff_ep_set_placement(FFEPGroup *g, uint32_t layer, const uint32_t *rankOf, const uint32_t *localOf,
+                         const char **error) {
+    if (error) *error = nullptr;
+    if (!g || !rankOf || !localOf) return fail(error, "null argument");
+    if (layer >= g->home[0]->cfg.layers) return fail(error, "layer out of range");
+    std::vector<uint8_t> taken((size_t)g->world * g->expertsPerRank, 0);
+    for (uint32_t e = 0; e < g->experts; ++e) {
+        if (rankOf[e] >= g->world || localOf[e] >= g->expertsPerRank)
+            return fail(error, "expert " + std::to_string(e) + " is placed outside the group");
+        uint8_t &slot = taken[(size_t)rankOf[e] * g->expertsPerRank + localOf[e]];
+        if (slot) return fail(error, "two experts share slot " + std::to_string(localOf[e]) + " of rank " + std::to_string(rankOf[e]));
+        slot = 1;
+    }
+    for (Rank &R : g->ranks) {
+        FF_CUDA_OK(cudaSetDevice(R.device), error);
+        FF_CUDA_OK(cudaStreamSynchronize(R.stream), error);
+        if (!R.placement[layer] && !device_alloc(&R.placement[layer], 2 * (size_t)g->experts, error)) return false;
+        FF_CUDA_OK(cudaMemcpy(R.placement[layer], rankOf, g->experts * sizeof(uint32_t), cudaMemcpyHostToDevice), error);
+        FF_CUDA_OK(cudaMemcpy(R.placement[layer] + g->experts, localOf, g->experts * sizeof(uint32_t),
+                              cudaMemcpyHostToDevice), error);
     }
     return true;
 }

@@ -577,6 +577,25 @@ class ExpertParallelGroup:
              arr(*[_ptr(t) for t in y]))
         return y
 
+    def moeStack(self, firstLayer: int, layerCount: int, x: List[torch.Tensor], eps: float,
+                 y: Optional[List[torch.Tensor]] = None) -> List[torch.Tensor]:
+        """x <- block(l, rmsnorm(x)) over the layers, per rank; returns the last block's rows."""
+        world = len(self.home)
+        if y is None:
+            y = [torch.empty_like(t) for t in x]
+        arr = ctypes.c_void_p * world
+        call("ff_ep_moe_stack", self._handle, firstLayer, layerCount, arr(*[_ptr(t) for t in x]), x[0].shape[0],
+             eps, arr(*[_ptr(t) for t in y]))
+        return y
+
+    def setPlacement(self, layer: int, rankOf, localOf):
+        """Expert e of `layer` lives on rank rankOf[e], slot localOf[e] of that rank's expert context."""
+        r = np.ascontiguousarray(np.asarray(rankOf, dtype=np.uint32))
+        l = np.ascontiguousarray(np.asarray(localOf, dtype=np.uint32))
+        if r.shape != l.shape or r.ndim != 1 or r.size != self.home[0].experts:
+            raise ValueError("one rank and one slot per expert")
+        call("ff_ep_set_placement", self._handle, layer, r.ctypes.data, l.ctypes.data)
+
     @property
     def lastRowsSent(self) -> int:
         return int(binding.load().ff_ep_last_rows_sent(self._handle))

@@ -796,6 +796,89 @@ def emit(line: dict):
         os.write(_RESULT_FD, text)
 
 
+def run_ep_group(args):
+    """`--ep-group`: configuration 4's stack through ff_ep_moe_stack, ONE process driving
+    `--gpus` GPUs (run with plain `python`, not torchrun).  The experts of each layer are placed to
+    even out the routes a one-device pass over rank 0's rows counted.  Timed by the host clock around
+    the synchronous call; the output of rank 0 is compared with ff_moe_stack on one device holding
+    every expert.  Prints its own JSON line (not the contract's line)."""
+    import time
+
+    import torch
+    from ane_fieldfare_b200 import hotpath, parallel, synth, workload
+    world = args.gpus
+    if torch.cuda.device_count() < world:
+        raise SystemExit(f"--ep-group needs {world} GPUs in this process")
+    layers = args.stack_layers
+    tokens_local = STACK_TOKENS // world
+    epr = E // world
+    capacity = min(STACK_TOKENS * K, 4 * tokens_local * K)
+    host_layers = [workload.make_layer(ROOT_SEED, slot) for slot in range(STACK_DISTINCT_LAYERS)]
+    priors = [synth.zipf_log_prior(E, 1.1, ROOT_SEED, f"stack.zipf.{i}") for i in range(len(host_layers))]
+    xs = [hotpath.bf16_tensor(workload.make_tokens(ROOT_SEED + r, "stack.x", tokens_local, D), torch.device("cuda", r))
+          for r in range(world)]
+
+    # one device, every expert: the expected output of rank 0 and every layer's routes
+    full = hotpath.HotpathContext(layers=layers, experts=E, d=D, f=F, sharedF=FS, topK=K, maxTokens=tokens_local,
+                                  device=0)
+    for slot in range(layers):
+        L = host_layers[slot % len(host_layers)]
+        full.loadLayer(slot, L.blobs, L.layout.stride, L.layout.offsets)
+        full.loadShared(slot, *L.shared_projections())
+        full.loadRouter(slot, L.routerW, logitBias=priors[slot % len(host_layers)])
+    with torch.cuda.device(0):
+        ids = torch.empty((layers, tokens_local, K), dtype=torch.int32, device=xs[0].device)
+        want = torch.empty_like(xs[0])
+        full.moeStack(0, layers, xs[0], 1e-6, want, ids=ids)
+        torch.cuda.synchronize(0)
+        counts = [np.bincount(ids[slot].reshape(-1).cpu().numpy(), minlength=E) for slot in range(layers)]
+        want = want.cpu()
+    full.close()
+    placements = [parallel.balanced_placement((counts[slot] + 0.5).tolist(), world) for slot in range(layers)]
+
+    home, expert = [], []
+    for r in range(world):
+        h = hotpath.HotpathContext(layers=layers, experts=E, d=D, f=F, sharedF=FS, topK=K, maxTokens=tokens_local,
+                                   device=r)
+        e = hotpath.HotpathContext(layers=layers, experts=epr, d=D, f=F, sharedF=0, topK=1, maxTokens=capacity,
+                                   device=r)
+        for slot in range(layers):
+            L = host_layers[slot % len(host_layers)]
+            h.loadShared(slot, *L.shared_projections())
+            h.loadRouter(slot, L.routerW, logitBias=priors[slot % len(host_layers)])
+            e.loadLayer(slot, np.ascontiguousarray(L.blobs[placements[slot].experts_of(r)]), L.layout.stride,
+                        L.layout.offsets, expertCount=epr)
+        home.append(h)
+        expert.append(e)
+    group = hotpath.ExpertParallelGroup(home, expert, capacityRows=capacity)
+    for slot in range(layers):
+        group.setPlacement(slot, placements[slot].rank_of.numpy(), placements[slot].local_of.numpy())
+    ys = [torch.empty_like(x) for x in xs]
+    for _ in range(2):
+        group.moeStack(0, layers, xs, 1e-6, ys)
+    same = bool(torch.equal(ys[0].cpu(), want))
+    per = []
+    for _ in range(max(3, min(args.steps, 5))):
+        t0 = time.perf_counter()
+        group.moeStack(0, layers, xs, 1e-6, ys)
+        per.append(1e3 * (time.perf_counter() - t0))
+    ms = float(np.median(per))
+    flags = [int(c.info().deviceErrorFlag) for c in home + expert]
+    launches = sum(int(c.info().kernelLaunches) for c in home + expert)
+    tf = stack_flops(layers) / (ms * 1e-3) / 1e12
+    emit({"metric": "ep_group_stack_tokens_per_s", "value": STACK_TOKENS / (ms * 1e-3), "unit": "tokens/s",
+          "n_gpus": world, "processes": 1, "ms_per_stack": ms, "per_call_ms": [round(v, 3) for v in per],
+          "timed_by": "host clock around the synchronous ff_ep_moe_stack call", "tflops": tf,
+          "config": {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens", "tokens_per_rank": tokens_local,
+                     "experts_per_rank": epr, "capacity_rows": capacity,
+                     "placement": "balanced on the routes of rank 0's rows"},
+          "rank0_equals_one_device_stack_bit_for_bit": same, "device_error_flags": flags,
+          "kernel_launches_all_contexts": launches, "data": "synthetic"})
+    group.close()
+    for c in home + expert:
+        c.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -811,9 +894,13 @@ def main():
                     help="runs the local tokens are cut into per layer under expert parallelism")
     ap.add_argument("--quick", action="store_true",
                     help="skip the end-to-end loop, per-kernel tracing and the CPU baseline (for profiler runs)")
+    ap.add_argument("--ep-group", action="store_true",
+                    help="time configuration 4's stack through ff_ep_moe_stack: one process driving --gpus GPUs")
     args = ap.parse_args()
     keep_stdout_for_the_result()
-    if args.impl == "reference":
+    if args.ep_group:
+        run_ep_group(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

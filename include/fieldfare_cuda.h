@@ -411,7 +411,19 @@ void ff_ep_destroy(FFEPGroup *group);
  * rows per rank. */
 bool ff_ep_moe_layer(FFEPGroup *group, uint32_t layer, const uint16_t *const *x, uint32_t tokens,
                      uint16_t *const *y, const char **error);
-/* Rows the last ff_ep_moe_layer sent to another GPU (each also came back as a partial row). */
+/* The stack of benchmark configuration 4 under expert parallelism, ff_moe_stack's statement per
+ * rank: for l = firstLayer .. firstLayer+layerCount-1: x <- block(l, rmsnorm(x)).  Between layers
+ * the ranks are ordered by events only; the host waits once per layer, for the row counts.
+ * Synchronous like ff_ep_moe_layer. */
+bool ff_ep_moe_stack(FFEPGroup *group, uint32_t firstLayer, uint32_t layerCount, const uint16_t *const *x,
+                     uint32_t tokens, float eps, uint16_t *const *y, const char **error);
+/* Where the experts of `layer` live: expert e on rank rankOf[e] in slot localOf[e] of that rank's
+ * expert context (host arrays [experts]; every slot of every rank taken once).  Without this call
+ * a layer's experts sit in contiguous blocks.  A placement that evens out a skewed routing load
+ * keeps the ranks' GEMMs the same length; the blob layout of a layer file is untouched. */
+bool ff_ep_set_placement(FFEPGroup *group, uint32_t layer, const uint32_t *rankOf, const uint32_t *localOf,
+                         const char **error);
+/* Rows the last block sent to another GPU (each also came back as a partial row). */
 uint64_t ff_ep_last_rows_sent(const FFEPGroup *group);
 
 /* Device-side result of the last ff_moe_prefill permute, copied to the host after a sync:

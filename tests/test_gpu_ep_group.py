@@ -72,6 +72,49 @@ def test_group_matches_the_one_device_layer(world):
         c.close()
 
 
+@pytest.mark.parametrize("world", [1, 2])
+def test_group_stack_with_a_balanced_placement(world):
+    """Two layers (the second with its experts placed to even out the Zipf load), RMSNorm between:
+    the bits of ff_moe_stack on one device holding everything."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from ane_fieldfare_b200 import hotpath, parallel, workload
+    layers = [workload.make_layer(0xEA, i, router_bias="zipf", **SHAPE) for i in range(2)]
+    epr = SHAPE["experts"] // world
+    load = [1.0 / (e + 1) ** 1.1 for e in range(SHAPE["experts"])]
+    placements = [parallel.contiguous_placement(SHAPE["experts"], world), parallel.balanced_placement(load, world)]
+    home, expert, fulls, xs, wants = [], [], [], [], []
+    for r in range(world):
+        h = hotpath.HotpathContext(layers=2, maxTokens=TOKENS, device=r, **SHAPE)
+        e = hotpath.HotpathContext(layers=2, experts=epr, d=SHAPE["d"], f=SHAPE["f"], sharedF=0, topK=1,
+                                   maxTokens=TOKENS * SHAPE["topK"] * world, device=r)
+        full = hotpath.HotpathContext(layers=2, maxTokens=TOKENS, device=r, **SHAPE)
+        for i, L in enumerate(layers):
+            h.loadShared(i, *L.shared_projections())
+            h.loadRouter(i, L.routerW, logitBias=L.logitBias)
+            e.loadLayer(i, np.ascontiguousarray(L.blobs[placements[i].experts_of(r)]), L.layout.stride,
+                        L.layout.offsets, expertCount=epr)
+            workload.load_layer(full, i, L)
+        x = hotpath.bf16_tensor(workload.make_tokens(0xEA + r, "ep.x", TOKENS, SHAPE["d"]), full.device)
+        with torch.cuda.device(r):
+            want = torch.empty_like(x)
+            full.moeStack(0, 2, x, 1e-6, want)
+            torch.cuda.synchronize(r)
+        home.append(h); expert.append(e); fulls.append(full); xs.append(x); wants.append(want)
+    group = hotpath.ExpertParallelGroup(home, expert)
+    group.setPlacement(1, placements[1].rank_of.numpy(), placements[1].local_of.numpy())
+    with pytest.raises(hotpath.FieldfareError, match="share slot"):
+        group.setPlacement(0, np.zeros(SHAPE["experts"]), np.zeros(SHAPE["experts"]))
+    for _ in range(2):
+        ys = group.moeStack(0, 2, xs, 1e-6)
+        for r in range(world):
+            assert torch.equal(ys[r].cpu(), wants[r].cpu()), f"rank {r} differs from the one-device stack"
+    group.close()
+    for c in home + expert + fulls:
+        assert c.info().deviceErrorFlag == 0
+        c.close()
+
+
 def test_group_refuses_what_it_cannot_run():
     from ane_fieldfare_b200 import hotpath, workload
     from ane_fieldfare_b200.binding import FieldfareError
