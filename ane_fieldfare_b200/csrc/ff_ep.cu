@@ -4,7 +4,11 @@
 // destination's memory, the partial rows come back as peer copies, and the home rank combines
 // them.  No collective library: the exchange is this file's own kernel writing over NVLink and
 // cudaMemcpyPeerAsync, ordered by events between the ranks' streams.
+#include <condition_variable>
+#include <functional>
+#include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "ff_internal.cuh"
@@ -30,24 +34,55 @@ __global__ void k_ep_row_index(const FFTokenExpertPair *__restrict__ pairs, uint
     if (i < n) rowIndex[pairs[i].token * topK + pairs[i].rank] = i;
 }
 
+constexpr uint32_t kMaxRanks = 8;  // the GPUs of one NVSwitch box
+
+// Where a rank's sorted routes go: destination p receives routes [first[p], first[p+1]) as rows
+// rows[p][0...] with their local expert ids in ids[p][0...] (pointers into the destinations' memory).
+struct SendTable {
+    uint16_t *rows[kMaxRanks];
+    uint32_t *ids[kMaxRanks];
+    uint32_t first[kMaxRanks];
+};
+// Where a rank's partial rows go: rows [begin[s], begin[s+1]) belong to source s and land at rows[s][0...].
+struct ReturnTable {
+    uint16_t *rows[kMaxRanks];
+    uint32_t begin[kMaxRanks + 1];
+};
+
 // One warp per route: copies the route's input row (16-byte pieces) and its expert id, local to the
-// destination, into the destination rank's receive buffers — `dstRows` and `dstIds` may be another
-// GPU's memory (plain stores over NVLink).
+// destination, into the destination rank's receive buffers — plain stores, over NVLink when the
+// destination is another GPU.  A sorted pair's `expert` field is its destination rank.
 __global__ void __launch_bounds__(256)
 k_ep_send_rows(const uint16_t *__restrict__ x, uint32_t xStride, uint32_t d,
                const FFTokenExpertPair *__restrict__ pairs, uint32_t n, const uint32_t *__restrict__ ids,
                uint32_t topK, uint32_t expertsPerRank, const uint32_t *__restrict__ localOf,
-               uint16_t *__restrict__ dstRows, uint32_t *__restrict__ dstIds) {
+               const __grid_constant__ SendTable table) {
     const uint32_t warpsPerCta = blockDim.x >> 5, lane = threadIdx.x & 31;
     for (uint32_t i = blockIdx.x * warpsPerCta + (threadIdx.x >> 5); i < n; i += gridDim.x * warpsPerCta) {
         const FFTokenExpertPair p = pairs[i];
+        if (p.expert >= kMaxRanks) continue;
+        const uint32_t j = i - table.first[p.expert];
         const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)p.token * xStride);
-        uint4 *dst = reinterpret_cast<uint4 *>(dstRows + (size_t)i * d);
+        uint4 *dst = reinterpret_cast<uint4 *>(table.rows[p.expert] + (size_t)j * d);
         for (uint32_t c = lane; c < d / 8; c += 32) dst[c] = src[c];
         if (lane == 0) {
             const uint32_t e = ids[p.token * topK + p.rank];
-            dstIds[i] = localOf ? localOf[e] : e % expertsPerRank;
+            table.ids[p.expert][j] = localOf ? localOf[e] : e % expertsPerRank;
         }
+    }
+}
+
+// One warp per partial row: stores it into its home rank's buffer.
+__global__ void __launch_bounds__(256)
+k_ep_return_rows(const uint16_t *__restrict__ partials, uint32_t d, uint32_t n, uint32_t world,
+                 const __grid_constant__ ReturnTable table) {
+    const uint32_t warpsPerCta = blockDim.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t i = blockIdx.x * warpsPerCta + (threadIdx.x >> 5); i < n; i += gridDim.x * warpsPerCta) {
+        uint32_t s = 0;
+        while (s + 1 < world && i >= table.begin[s + 1]) ++s;
+        const uint4 *src = reinterpret_cast<const uint4 *>(partials + (size_t)i * d);
+        uint4 *dst = reinterpret_cast<uint4 *>(table.rows[s] + (size_t)(i - table.begin[s]) * d);
+        for (uint32_t c = lane; c < d / 8; c += 32) dst[c] = src[c];
     }
 }
 
@@ -72,6 +107,86 @@ struct Rank {
     std::vector<uint32_t *> placement;  // per layer: [2][experts] rank of every expert, then its local slot; null = contiguous
 };
 
+// One host thread per rank, so that a phase is queued on all GPUs at once.  run() hands every
+// thread the same job with its rank and returns when all are done; the first failure's message wins.
+class Workers {
+public:
+    using Job = std::function<bool(uint32_t, const char **)>;
+    void start(uint32_t n) {
+        count = n;
+        ok.assign(n, 1);
+        errors.assign(n, nullptr);
+        for (uint32_t r = 1; r < n; ++r) threads.emplace_back([this, r] { loop(r); });
+    }
+    ~Workers() {
+        {
+            std::lock_guard<std::mutex> lock(m);
+            stop = true;
+            ++generation;
+        }
+        wake.notify_all();
+        for (std::thread &t : threads) t.join();
+    }
+    bool run(const Job &fn, const char **error) {
+        {
+            std::lock_guard<std::mutex> lock(m);
+            job = &fn;
+            pending = count - 1;
+            ++generation;
+        }
+        wake.notify_all();
+        errors[0] = nullptr;
+        ok[0] = fn(0, &errors[0]);  // rank 0 on the calling thread
+        {
+            std::unique_lock<std::mutex> lock(m);
+            done.wait(lock, [this] { return pending == 0; });
+        }
+        bool all = true;
+        for (uint32_t r = 0; r < count; ++r) {
+            if (!ok[r] && all) {
+                all = false;
+                if (error) *error = errors[r];
+                else free(const_cast<char *>(errors[r]));
+            } else if (errors[r]) {
+                free(const_cast<char *>(errors[r]));
+            }
+            errors[r] = nullptr;
+        }
+        return all;
+    }
+
+private:
+    void loop(uint32_t r) {
+        uint64_t seen = 0;
+        for (;;) {
+            const Job *mine;
+            {
+                std::unique_lock<std::mutex> lock(m);
+                wake.wait(lock, [&] { return generation != seen; });
+                seen = generation;
+                if (stop) return;
+                mine = job;
+            }
+            errors[r] = nullptr;
+            ok[r] = (*mine)(r, &errors[r]);
+            {
+                std::lock_guard<std::mutex> lock(m);
+                --pending;
+            }
+            done.notify_one();
+        }
+    }
+    uint32_t count = 0, pending = 0;
+    uint64_t generation = 0;
+    bool stop = false;
+    const Job *job = nullptr;
+    std::vector<std::thread> threads;
+    std::vector<char> ok;
+    std::vector<const char *> errors;
+    std::mutex m;
+    std::condition_variable wake, done;
+};
+
 template <typename T>
 bool device_alloc(T **p, size_t count, const char **error) {
     FF_CUDA_OK(cudaMalloc(reinterpret_cast<void **>(p), count * sizeof(T)), error);
@@ -85,6 +200,7 @@ struct FFEPGroup {
     std::vector<FFContext *> home, expert;
     std::vector<Rank> ranks;
     uint64_t lastRowsSent = 0;
+    Workers workers;
 };
 
 namespace {
@@ -151,8 +267,8 @@ extern "C" {
 FFEPGroup *ff_ep_create(FFContext *const *home, FFContext *const *expert, uint32_t world,
                         uint32_t capacityRows, const char **error) {
     if (error) *error = nullptr;
-    if (!home || !expert || world == 0 || world > 64) {
-        fail(error, "expert-parallel group needs 1...64 ranks with a home and an expert context each");
+    if (!home || !expert || world == 0 || world > kMaxRanks) {
+        fail(error, "expert-parallel group needs 1...8 ranks with a home and an expert context each");
         return nullptr;
     }
     FFEPGroup *g = new FFEPGroup;
@@ -198,6 +314,7 @@ FFEPGroup *ff_ep_create(FFContext *const *home, FFContext *const *expert, uint32
         release(g);
         return nullptr;
     }
+    g->workers.start(world);
     return g;
 }
 
@@ -207,103 +324,115 @@ void ff_ep_destroy(FFEPGroup *group) {
 
 uint64_t ff_ep_last_rows_sent(const FFEPGroup *group) { return group ? group->lastRowsSent : 0; }
 
-// One block, queued on the ranks' streams.  The host waits once, for the counts of rows per
-// destination; the rest is ordered by events, so consecutive layers need no wait between them: a
-// rank sends its next rows only behind its own combine, which waited for every rank's experts.
-static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uint32_t tokens,
-                      uint16_t *const *y, const char **error) {
+// One block, queued on the ranks' streams by one host thread per rank.  The host waits once, for
+// the counts of rows per destination; the rest is ordered by events, so consecutive layers need no
+// wait between them: a rank sends its next rows only behind its own combine, which waited for
+// every rank's experts.  An event must be recorded before another thread queues a wait on it,
+// hence the phases: the threads meet between them.  `normFrom` (stack): rows to normalise into the
+// rank's `normed` buffer first, which is then the block's input.
+static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, const uint16_t *const *normFrom,
+                      float eps, uint32_t tokens, uint16_t *const *y, const char **error) {
     const uint32_t world = g->world, K = g->topK, D = g->d;
     const uint32_t routes = tokens * K;
+    const bool withShared = g->home[0]->layers[layer].has_shared();
 
-    // 1. every rank: router, shared FFN, destination of every route, routes sorted by destination
-    for (uint32_t r = 0; r < world; ++r) {
-        Rank &R = g->ranks[r];
-        if (!x[r] || !y[r]) return fail(error, "null row pointer for rank " + std::to_string(r));
-        FF_CUDA_OK(cudaSetDevice(R.device), error);
-        if (!ff_router_topk(g->home[r], layer, x[r], D, tokens, R.ids, R.weights, nullptr, R.stream, error)) return false;
-        k_ep_destination<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.ids, routes, g->expertsPerRank, g->experts,
-                                                                     R.placement[layer], R.dest);
-        FF_CUDA_OK(cudaGetLastError(), error);
-        if (!ff_sort_routes(g->home[r], R.dest, tokens, world, R.pairs, R.offsets, R.stream, error)) return false;
-        FF_CUDA_OK(cudaMemcpyAsync(R.hostOffsets, R.offsets, (world + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost,
-                                   R.stream), error);
-        k_ep_row_index<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.pairs, routes, K, R.rowIndex);
-        FF_CUDA_OK(cudaGetLastError(), error);
-    }
-    for (uint32_t r = 0; r < world; ++r) {
-        FF_CUDA_OK(cudaSetDevice(g->ranks[r].device), error);
-        FF_CUDA_OK(cudaStreamSynchronize(g->ranks[r].stream), error);
-        if (g->ranks[r].hostOffsets[world] != routes)
-            return fail(error, "the router of rank " + std::to_string(r) + " wrote an expert id out of range");
-    }
+    // 1. every rank: router, destination of every route, routes sorted by destination, counts to the host
+    if (!g->workers.run([&](uint32_t r, const char **err) -> bool {
+            Rank &R = g->ranks[r];
+            FF_CUDA_OK(cudaSetDevice(R.device), err);
+            const uint16_t *in = normFrom ? R.normed : x[r];
+            if (normFrom && !ff_rmsnorm(g->home[r], normFrom[r], nullptr, eps, tokens, R.normed, R.stream, err))
+                return false;
+            if (!ff_router_topk(g->home[r], layer, in, D, tokens, R.ids, R.weights, nullptr, R.stream, err)) return false;
+            k_ep_destination<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.ids, routes, g->expertsPerRank, g->experts,
+                                                                         R.placement[layer], R.dest);
+            FF_CUDA_OK(cudaGetLastError(), err);
+            if (!ff_sort_routes(g->home[r], R.dest, tokens, world, R.pairs, R.offsets, R.stream, err)) return false;
+            FF_CUDA_OK(cudaMemcpyAsync(R.hostOffsets, R.offsets, (world + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                                       R.stream), err);
+            k_ep_row_index<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.pairs, routes, K, R.rowIndex);
+            FF_CUDA_OK(cudaGetLastError(), err);
+            FF_CUDA_OK(cudaStreamSynchronize(R.stream), err);
+            if (R.hostOffsets[world] != routes)
+                return fail(err, "the router of rank " + std::to_string(r) + " wrote an expert id out of range");
+            return true;
+        }, error))
+        return false;
 
     // 2. where each source's rows land in each destination's receive buffer
-    std::vector<uint32_t> base((size_t)world * world), total(world, 0);  // base[p * world + s]
-    for (uint32_t p = 0; p < world; ++p) {
-        for (uint32_t s = 0; s < world; ++s) {
-            base[(size_t)p * world + s] = total[p];
-            total[p] += g->ranks[s].hostOffsets[p + 1] - g->ranks[s].hostOffsets[p];
-        }
-        if (total[p] > g->capacity)
-            return fail(error, "rank " + std::to_string(p) + " would receive " + std::to_string(total[p]) +
-                                   " rows, more than the group's capacity " + std::to_string(g->capacity));
-    }
-
-    // 3. dispatch: stores into the destinations' buffers; the shared FFN runs behind them
-    const bool withShared = g->home[0]->layers[layer].has_shared();
+    std::vector<uint32_t> base((size_t)world * (world + 1));  // base[p * (world + 1) + s], the last entry the total
     uint64_t sentAway = 0;
-    for (uint32_t s = 0; s < world; ++s) {
-        Rank &S = g->ranks[s];
-        FF_CUDA_OK(cudaSetDevice(S.device), error);
-        for (uint32_t p = 0; p < world; ++p) {
-            const uint32_t first = S.hostOffsets[p], n = S.hostOffsets[p + 1] - first;
-            if (!n) continue;
-            if (p != s) sentAway += n;
-            Rank &P = g->ranks[p];
-            const uint32_t at = base[(size_t)p * world + s];
-            const uint32_t ctas = (n + 7) / 8 < 1184u ? (n + 7) / 8 : 1184u;
-            k_ep_send_rows<<<ctas, 256, 0, S.stream>>>(x[s], D, D, S.pairs + first, n, S.ids, K, g->expertsPerRank,
-                                                       S.placement[layer] ? S.placement[layer] + g->experts : nullptr,
-                                                       P.recvRows + (size_t)at * D, P.recvIds + at);
-            FF_CUDA_OK(cudaGetLastError(), error);
+    for (uint32_t p = 0; p < world; ++p) {
+        uint32_t total = 0;
+        for (uint32_t s = 0; s < world; ++s) {
+            base[(size_t)p * (world + 1) + s] = total;
+            const uint32_t n = g->ranks[s].hostOffsets[p + 1] - g->ranks[s].hostOffsets[p];
+            total += n;
+            if (s != p) sentAway += n;
         }
-        FF_CUDA_OK(cudaEventRecord(S.sent, S.stream), error);
-        if (withShared && !ff_shared_ffn(g->home[s], layer, x[s], D, tokens, S.sharedOut, S.stream, error)) return false;
+        base[(size_t)p * (world + 1) + world] = total;
+        if (total > g->capacity)
+            return fail(error, "rank " + std::to_string(p) + " would receive " + std::to_string(total) +
+                                   " rows, more than the group's capacity " + std::to_string(g->capacity));
     }
     g->lastRowsSent = sentAway;
 
-    // 4. every rank's experts on what it received, then the partial rows go home
-    for (uint32_t p = 0; p < world; ++p) {
-        Rank &P = g->ranks[p];
-        FF_CUDA_OK(cudaSetDevice(P.device), error);
-        for (uint32_t s = 0; s < world; ++s)
-            if (s != p) FF_CUDA_OK(cudaStreamWaitEvent(P.stream, g->ranks[s].sent, 0), error);
-        if (total[p] &&
-            !ff_moe_prefill(g->expert[p], layer, P.recvRows, D, total[p], P.recvIds, P.partials, P.stream, error))
-            return false;
-        for (uint32_t s = 0; s < world; ++s) {
-            const uint32_t first = g->ranks[s].hostOffsets[p], n = g->ranks[s].hostOffsets[p + 1] - first;
-            if (!n) continue;
-            const uint16_t *src = P.partials + (size_t)base[(size_t)p * world + s] * D;
-            uint16_t *dst = g->ranks[s].back + (size_t)first * D;
-            const size_t bytes = (size_t)n * D * sizeof(uint16_t);
-            if (s == p) FF_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, P.stream), error);
-            else FF_CUDA_OK(cudaMemcpyPeerAsync(dst, g->ranks[s].device, src, P.device, bytes, P.stream), error);
-        }
-        FF_CUDA_OK(cudaEventRecord(P.returned, P.stream), error);
-    }
+    // 3. dispatch: one kernel per rank stores its rows into every destination's buffer; the shared FFN behind it
+    if (!g->workers.run([&](uint32_t s, const char **err) -> bool {
+            Rank &S = g->ranks[s];
+            FF_CUDA_OK(cudaSetDevice(S.device), err);
+            const uint16_t *in = normFrom ? S.normed : x[s];
+            SendTable table{};
+            for (uint32_t p = 0; p < world; ++p) {
+                const uint32_t at = base[(size_t)p * (world + 1) + s];
+                table.rows[p] = g->ranks[p].recvRows + (size_t)at * D;
+                table.ids[p] = g->ranks[p].recvIds + at;
+                table.first[p] = S.hostOffsets[p];
+            }
+            const uint32_t ctas = (routes + 7) / 8 < 1184u ? (routes + 7) / 8 : 1184u;
+            k_ep_send_rows<<<ctas, 256, 0, S.stream>>>(in, D, D, S.pairs, routes, S.ids, K, g->expertsPerRank,
+                                                       S.placement[layer] ? S.placement[layer] + g->experts : nullptr, table);
+            FF_CUDA_OK(cudaGetLastError(), err);
+            FF_CUDA_OK(cudaEventRecord(S.sent, S.stream), err);
+            if (withShared && !ff_shared_ffn(g->home[s], layer, in, D, tokens, S.sharedOut, S.stream, err)) return false;
+            return true;
+        }, error))
+        return false;
+
+    // 4. every rank's experts on what it received; one kernel stores the partial rows into their homes
+    if (!g->workers.run([&](uint32_t p, const char **err) -> bool {
+            Rank &P = g->ranks[p];
+            FF_CUDA_OK(cudaSetDevice(P.device), err);
+            for (uint32_t s = 0; s < world; ++s)
+                if (s != p) FF_CUDA_OK(cudaStreamWaitEvent(P.stream, g->ranks[s].sent, 0), err);
+            const uint32_t total = base[(size_t)p * (world + 1) + world];
+            if (total) {
+                if (!ff_moe_prefill(g->expert[p], layer, P.recvRows, D, total, P.recvIds, P.partials, P.stream, err))
+                    return false;
+                ReturnTable table{};
+                for (uint32_t s = 0; s < world; ++s) {
+                    table.begin[s] = base[(size_t)p * (world + 1) + s];
+                    table.rows[s] = g->ranks[s].back + (size_t)g->ranks[s].hostOffsets[p] * D;
+                }
+                table.begin[world] = total;
+                const uint32_t ctas = (total + 7) / 8 < 1184u ? (total + 7) / 8 : 1184u;
+                k_ep_return_rows<<<ctas, 256, 0, P.stream>>>(P.partials, D, total, world, table);
+                FF_CUDA_OK(cudaGetLastError(), err);
+            }
+            FF_CUDA_OK(cudaEventRecord(P.returned, P.stream), err);
+            return true;
+        }, error))
+        return false;
 
     // 5. combine at home: weighted sum of each row's K partials in rank order, plus the shared rows
-    for (uint32_t r = 0; r < world; ++r) {
+    return g->workers.run([&](uint32_t r, const char **err) -> bool {
         Rank &R = g->ranks[r];
-        FF_CUDA_OK(cudaSetDevice(R.device), error);
+        FF_CUDA_OK(cudaSetDevice(R.device), err);
         for (uint32_t p = 0; p < world; ++p)
-            if (p != r) FF_CUDA_OK(cudaStreamWaitEvent(R.stream, g->ranks[p].returned, 0), error);
-        if (!ff_moe_reduce_indexed(g->home[r], R.back, R.rowIndex, R.weights, withShared ? R.sharedOut : nullptr, y[r],
-                                   tokens, R.stream, error))
-            return false;
-    }
-    return true;
+            if (p != r) FF_CUDA_OK(cudaStreamWaitEvent(R.stream, g->ranks[p].returned, 0), err);
+        return ff_moe_reduce_indexed(g->home[r], R.back, R.rowIndex, R.weights, withShared ? R.sharedOut : nullptr, y[r],
+                                     tokens, R.stream, err);
+    }, error);
 }
 
 // Waits for every rank's stream and reads every context's error flag.
@@ -345,7 +474,7 @@ bool ff_ep_moe_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, uin
                      uint16_t *const *y, const char **error) {
     if (!check_call(g, layer, 1, x, tokens, y, error)) return false;
     if (tokens == 0) return true;
-    return run_layer(g, layer, x, tokens, y, error) && finish(g, error);
+    return run_layer(g, layer, x, nullptr, 0.0f, tokens, y, error) && finish(g, error);
 }
 
 bool ff_ep_moe_stack(FFEPGroup *g, uint32_t firstLayer, uint32_t layerCount, const uint16_t *const *x,
@@ -353,16 +482,11 @@ bool ff_ep_moe_stack(FFEPGroup *g, uint32_t firstLayer, uint32_t layerCount, con
     if (!check_call(g, firstLayer, layerCount, x, tokens, y, error)) return false;
     if (tokens == 0) return true;
     const uint32_t world = g->world;
-    std::vector<const uint16_t *> cur(x, x + world), in(world);
+    std::vector<const uint16_t *> cur(x, x + world);
     std::vector<uint16_t *> out(world);
     for (uint32_t i = 0; i < layerCount; ++i) {
-        for (uint32_t r = 0; r < world; ++r) {
-            Rank &R = g->ranks[r];
-            if (!ff_rmsnorm(g->home[r], cur[r], nullptr, eps, tokens, R.normed, R.stream, error)) return false;
-            in[r] = R.normed;
-            out[r] = i + 1 == layerCount ? y[r] : R.between;
-        }
-        if (!run_layer(g, firstLayer + i, in.data(), tokens, out.data(), error)) return false;
+        for (uint32_t r = 0; r < world; ++r) out[r] = i + 1 == layerCount ? y[r] : g->ranks[r].between;
+        if (!run_layer(g, firstLayer + i, nullptr, cur.data(), eps, tokens, out.data(), error)) return false;
         for (uint32_t r = 0; r < world; ++r) cur[r] = out[r];
     }
     return finish(g, error);
