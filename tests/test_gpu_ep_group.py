@@ -72,10 +72,12 @@ def test_group_matches_the_one_device_layer(world):
         c.close()
 
 
+@pytest.mark.parametrize("rows", [TOKENS, 300])
 @pytest.mark.parametrize("world", [1, 2])
-def test_group_stack_with_a_balanced_placement(world):
+def test_group_stack_with_a_balanced_placement(world, rows):
     """Two layers (the second with its experts placed to even out the Zipf load), RMSNorm between:
-    the bits of ff_moe_stack on one device holding everything."""
+    the bits of ff_moe_stack on one device holding everything.  At 300 rows the shared FFN runs in
+    two parts on its own stream."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     from ane_fieldfare_b200 import hotpath, parallel, workload
@@ -85,17 +87,17 @@ def test_group_stack_with_a_balanced_placement(world):
     placements = [parallel.contiguous_placement(SHAPE["experts"], world), parallel.balanced_placement(load, world)]
     home, expert, fulls, xs, wants = [], [], [], [], []
     for r in range(world):
-        h = hotpath.HotpathContext(layers=2, maxTokens=TOKENS, device=r, **SHAPE)
+        h = hotpath.HotpathContext(layers=2, maxTokens=rows, device=r, **SHAPE)
         e = hotpath.HotpathContext(layers=2, experts=epr, d=SHAPE["d"], f=SHAPE["f"], sharedF=0, topK=1,
-                                   maxTokens=TOKENS * SHAPE["topK"] * world, device=r)
-        full = hotpath.HotpathContext(layers=2, maxTokens=TOKENS, device=r, **SHAPE)
+                                   maxTokens=rows * SHAPE["topK"] * world, device=r)
+        full = hotpath.HotpathContext(layers=2, maxTokens=rows, device=r, **SHAPE)
         for i, L in enumerate(layers):
             h.loadShared(i, *L.shared_projections())
             h.loadRouter(i, L.routerW, logitBias=L.logitBias)
             e.loadLayer(i, np.ascontiguousarray(L.blobs[placements[i].experts_of(r)]), L.layout.stride,
                         L.layout.offsets, expertCount=epr)
             workload.load_layer(full, i, L)
-        x = hotpath.bf16_tensor(workload.make_tokens(0xEA + r, "ep.x", TOKENS, SHAPE["d"]), full.device)
+        x = hotpath.bf16_tensor(workload.make_tokens(0xEA + r, "ep.x", rows, SHAPE["d"]), full.device)
         with torch.cuda.device(r):
             want = torch.empty_like(x)
             full.moeStack(0, 2, x, 1e-6, want)
