@@ -43,12 +43,6 @@ struct SendTable {
     uint32_t *ids[kMaxRanks];
     uint32_t first[kMaxRanks];
 };
-// Where a rank's partial rows go: rows [begin[s], begin[s+1]) belong to source s and land at rows[s][0...].
-struct ReturnTable {
-    uint16_t *rows[kMaxRanks];
-    uint32_t begin[kMaxRanks + 1];
-};
-
 // One warp per route: copies the route's input row (16-byte pieces) and its expert id, local to the
 // destination, into the destination rank's receive buffers — plain stores, over NVLink when the
 // destination is another GPU.  A sorted pair's `expert` field is its destination rank.
@@ -72,24 +66,11 @@ k_ep_send_rows(const uint16_t *__restrict__ x, uint32_t xStride, uint32_t d,
     }
 }
 
-// One warp per partial row: stores it into its home rank's buffer.
-__global__ void __launch_bounds__(256)
-k_ep_return_rows(const uint16_t *__restrict__ partials, uint32_t d, uint32_t n, uint32_t world,
-                 const __grid_constant__ ReturnTable table) {
-    const uint32_t warpsPerCta = blockDim.x >> 5, lane = threadIdx.x & 31;
-    for (uint32_t i = blockIdx.x * warpsPerCta + (threadIdx.x >> 5); i < n; i += gridDim.x * warpsPerCta) {
-        uint32_t s = 0;
-        while (s + 1 < world && i >= table.begin[s + 1]) ++s;
-        const uint4 *src = reinterpret_cast<const uint4 *>(partials + (size_t)i * d);
-        uint4 *dst = reinterpret_cast<uint4 *>(table.rows[s] + (size_t)(i - table.begin[s]) * d);
-        for (uint32_t c = lane; c < d / 8; c += 32) dst[c] = src[c];
-    }
-}
-
 struct Rank {
     int device = 0;
     cudaStream_t stream = nullptr;
-    cudaEvent_t sent = nullptr, returned = nullptr;
+    cudaStream_t side = nullptr;     // the partial rows' way home (copy engines), beside the shared FFN
+    cudaEvent_t sent = nullptr, returned = nullptr, expertsDone = nullptr;
     uint32_t *ids = nullptr;         // [tokens][K] global expert ids
     uint16_t *weights = nullptr;     // [tokens][K]
     uint32_t *dest = nullptr;        // [tokens][K] destination rank of each route
@@ -214,9 +195,12 @@ void release(FFEPGroup *g) {
         cudaFree(r.back); cudaFree(r.sharedOut); cudaFree(r.normed); cudaFree(r.between);
         for (uint32_t *t : r.placement) cudaFree(t);
         if (r.hostOffsets) cudaFreeHost(r.hostOffsets);
+        if (r.side) cudaStreamSynchronize(r.side);
         if (r.sent) cudaEventDestroy(r.sent);
         if (r.returned) cudaEventDestroy(r.returned);
+        if (r.expertsDone) cudaEventDestroy(r.expertsDone);
         if (r.stream) cudaStreamDestroy(r.stream);
+        if (r.side) cudaStreamDestroy(r.side);
     }
     delete g;
 }
@@ -242,6 +226,8 @@ bool build_group(FFEPGroup *g, const char **error) {
         FF_CUDA_OK(cudaStreamCreateWithFlags(&R.stream, cudaStreamNonBlocking), error);
         FF_CUDA_OK(cudaEventCreateWithFlags(&R.sent, cudaEventDisableTiming), error);
         FF_CUDA_OK(cudaEventCreateWithFlags(&R.returned, cudaEventDisableTiming), error);
+        FF_CUDA_OK(cudaStreamCreateWithFlags(&R.side, cudaStreamNonBlocking), error);
+        FF_CUDA_OK(cudaEventCreateWithFlags(&R.expertsDone, cudaEventDisableTiming), error);
         const size_t routes = (size_t)g->maxTokens * g->topK;
         if (!device_alloc(&R.ids, routes, error) || !device_alloc(&R.weights, routes, error) ||
             !device_alloc(&R.dest, routes, error) || !device_alloc(&R.pairs, routes, error) ||
@@ -394,7 +380,6 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
                                                        S.placement[layer] ? S.placement[layer] + g->experts : nullptr, table);
             FF_CUDA_OK(cudaGetLastError(), err);
             FF_CUDA_OK(cudaEventRecord(S.sent, S.stream), err);
-            if (withShared && !ff_shared_ffn(g->home[s], layer, in, D, tokens, S.sharedOut, S.stream, err)) return false;
             return true;
         }, error))
         return false;
@@ -406,20 +391,28 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
             for (uint32_t s = 0; s < world; ++s)
                 if (s != p) FF_CUDA_OK(cudaStreamWaitEvent(P.stream, g->ranks[s].sent, 0), err);
             const uint32_t total = base[(size_t)p * (world + 1) + world];
-            if (total) {
-                if (!ff_moe_prefill(g->expert[p], layer, P.recvRows, D, total, P.recvIds, P.partials, P.stream, err))
-                    return false;
-                ReturnTable table{};
-                for (uint32_t s = 0; s < world; ++s) {
-                    table.begin[s] = base[(size_t)p * (world + 1) + s];
-                    table.rows[s] = g->ranks[s].back + (size_t)g->ranks[s].hostOffsets[p] * D;
-                }
-                table.begin[world] = total;
-                const uint32_t ctas = (total + 7) / 8 < 1184u ? (total + 7) / 8 : 1184u;
-                k_ep_return_rows<<<ctas, 256, 0, P.stream>>>(P.partials, D, total, world, table);
-                FF_CUDA_OK(cudaGetLastError(), err);
+            if (total &&
+                !ff_moe_prefill(g->expert[p], layer, P.recvRows, D, total, P.recvIds, P.partials, P.stream, err))
+                return false;
+            // the partial rows go home by the copy engines on the second stream, while the SMs run the
+            // shared FFN
+            FF_CUDA_OK(cudaEventRecord(P.expertsDone, P.stream), err);
+            FF_CUDA_OK(cudaStreamWaitEvent(P.side, P.expertsDone, 0), err);
+            for (uint32_t i = 1; i <= world; ++i) {
+                const uint32_t s = (p + i) % world;  // the other GPUs first, this one's own rows last
+                const uint32_t first = g->ranks[s].hostOffsets[p], n = g->ranks[s].hostOffsets[p + 1] - first;
+                if (!n) continue;
+                const uint16_t *src = P.partials + (size_t)base[(size_t)p * (world + 1) + s] * D;
+                uint16_t *dst = g->ranks[s].back + (size_t)first * D;
+                const size_t bytes = (size_t)n * D * sizeof(uint16_t);
+                if (s == p) FF_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, P.side), err);
+                else FF_CUDA_OK(cudaMemcpyPeerAsync(dst, g->ranks[s].device, src, P.device, bytes, P.side), err);
             }
-            FF_CUDA_OK(cudaEventRecord(P.returned, P.stream), err);
+            FF_CUDA_OK(cudaEventRecord(P.returned, P.side), err);
+            if (withShared) {
+                const uint16_t *in = normFrom ? P.normed : x[p];
+                if (!ff_shared_ffn(g->home[p], layer, in, D, tokens, P.sharedOut, P.stream, err)) return false;
+            }
             return true;
         }, error))
         return false;
@@ -428,8 +421,7 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
     return g->workers.run([&](uint32_t r, const char **err) -> bool {
         Rank &R = g->ranks[r];
         FF_CUDA_OK(cudaSetDevice(R.device), err);
-        for (uint32_t p = 0; p < world; ++p)
-            if (p != r) FF_CUDA_OK(cudaStreamWaitEvent(R.stream, g->ranks[p].returned, 0), err);
+        for (uint32_t p = 0; p < world; ++p) FF_CUDA_OK(cudaStreamWaitEvent(R.stream, g->ranks[p].returned, 0), err);
         return ff_moe_reduce_indexed(g->home[r], R.back, R.rowIndex, R.weights, withShared ? R.sharedOut : nullptr, y[r],
                                      tokens, R.stream, err);
     }, error);
