@@ -313,7 +313,7 @@ uint64_t ff_ep_last_rows_sent(const FFEPGroup *group) { return group ? group->la
 // One block, queued on the ranks' streams by one host thread per rank.  The host waits once, for
 // the counts of rows per destination; the rest is ordered by events, so consecutive layers need no
 // wait between them: a rank sends its next rows only behind its own combine, which waited for
-// every rank's experts.  An event must be recorded before another thread queues a wait on it,
+// every rank's experts and copies.  An event must be recorded before another thread queues a wait on it,
 // hence the phases: the threads meet between them.  `normFrom` (stack): rows to normalise into the
 // rank's `normed` buffer first, which is then the block's input.
 static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, const uint16_t *const *normFrom,
@@ -363,7 +363,7 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
     }
     g->lastRowsSent = sentAway;
 
-    // 3. dispatch: one kernel per rank stores its rows into every destination's buffer; the shared FFN behind it
+    // 3. dispatch: one kernel per rank stores its rows into every destination's buffer
     if (!g->workers.run([&](uint32_t s, const char **err) -> bool {
             Rank &S = g->ranks[s];
             FF_CUDA_OK(cudaSetDevice(S.device), err);
@@ -384,7 +384,7 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
         }, error))
         return false;
 
-    // 4. every rank's experts on what it received; one kernel stores the partial rows into their homes
+    // 4. every rank's experts on what it received; the partial rows copied into their homes, the shared FFN beside that
     if (!g->workers.run([&](uint32_t p, const char **err) -> bool {
             Rank &P = g->ranks[p];
             FF_CUDA_OK(cudaSetDevice(P.device), err);

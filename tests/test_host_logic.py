@@ -22,6 +22,26 @@ def test_library_loads_and_exports_every_declared_symbol():
         assert getattr(lib, name) is not None
 
 
+def test_expert_parallel_group_refuses_bad_arguments_before_touching_a_device():
+    lib = binding.load()
+    err = ctypes.c_char_p()
+    assert not lib.ff_ep_create(None, None, 2, 0, ctypes.byref(err))
+    assert b"1...8 ranks" in err.value
+    one = (ctypes.c_void_p * 1)(None)
+    err = ctypes.c_char_p()
+    assert not lib.ff_ep_create(one, one, 1, 0, ctypes.byref(err))
+    assert b"null context for rank 0" in err.value
+    nine = (ctypes.c_void_p * 9)()
+    err = ctypes.c_char_p()
+    assert not lib.ff_ep_create(nine, nine, 9, 0, ctypes.byref(err))
+    assert b"1...8 ranks" in err.value
+    err = ctypes.c_char_p()
+    assert not lib.ff_ep_moe_layer(None, 0, None, 1, None, ctypes.byref(err))
+    assert b"null argument" in err.value
+    assert lib.ff_ep_last_rows_sent(None) == 0
+    lib.ff_ep_destroy(None)
+
+
 def test_struct_layouts_match_the_reference_structs():
     # MoEExpertOffsets: 9 x UInt32 (Kernels/MoE/MoE.swift:4-15); PrefillTokenExpertPair: 4 x UInt32
     # (Kernels/Prefill/MoE/PrefillRouter.swift:4-21); groups 3, tiles 4 (PrefillMoEGrouping.swift:4-29)
