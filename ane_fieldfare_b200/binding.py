@@ -117,6 +117,8 @@ SIGNATURES = {
     "ff_ep_last_rows_sent": (c_uint64, [c_void_p]),
     "ff_ep_moe_stack": (c_bool, [c_void_p, c_uint32, c_uint32, POINTER(c_void_p), c_uint32, c_float,
                                  POINTER(c_void_p), _ERR]),
+    "ff_ep_set_tracing": (None, [c_void_p, c_bool]),
+    "ff_ep_get_phase_times": (c_uint32, [c_void_p, POINTER(ctypes.c_double), c_uint32]),
     "ff_ep_set_placement": (c_bool, [c_void_p, c_uint32, _P, _P, _ERR]),
 }
 

@@ -66,6 +66,14 @@ k_ep_send_rows(const uint16_t *__restrict__ x, uint32_t xStride, uint32_t d,
     }
 }
 
+// Points of a layer at which a traced call records an event on the rank's stream (CopiesHome: on
+// its second stream).
+enum Mark : uint32_t {
+    kLayerStart, kRouterDone, kPlanQueued, kSendStart, kSendDone, kRowsArrived, kExpertsDone, kCopiesHome,
+    kSharedDone, kPartialsArrived, kReduceDone, kMarks
+};
+constexpr uint32_t kPhases = 10;
+
 struct Rank {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -85,6 +93,7 @@ struct Rank {
     uint16_t *sharedOut = nullptr;   // [tokens][d]
     uint16_t *normed = nullptr;      // [tokens][d] stack: the layer's input
     uint16_t *between = nullptr;     // [tokens][d] stack: a layer's output that is not the last
+    std::vector<cudaEvent_t> marks;     // tracing: kMarks events per layer, in the order of the Mark enum
     std::vector<uint32_t *> placement;  // per layer: [2][experts] rank of every expert, then its local slot; null = contiguous
 };
 
@@ -181,10 +190,22 @@ struct FFEPGroup {
     std::vector<FFContext *> home, expert;
     std::vector<Rank> ranks;
     uint64_t lastRowsSent = 0;
+    bool tracing = false;
+    std::vector<double> phaseMs;  // [world][kPhases] of the last traced call
     Workers workers;
 };
 
 namespace {
+
+// Records the next mark of a traced layer; a no-op otherwise.
+bool mark(const FFEPGroup *g, Rank &R, cudaStream_t stream, const char **error) {
+    if (!g->tracing) return true;
+    cudaEvent_t e = nullptr;
+    FF_CUDA_OK(cudaEventCreate(&e), error);
+    R.marks.push_back(e);
+    FF_CUDA_OK(cudaEventRecord(e, stream), error);
+    return true;
+}
 
 void release(FFEPGroup *g) {
     for (Rank &r : g->ranks) {
@@ -194,6 +215,7 @@ void release(FFEPGroup *g) {
         cudaFree(r.rowIndex); cudaFree(r.recvRows); cudaFree(r.recvIds); cudaFree(r.partials);
         cudaFree(r.back); cudaFree(r.sharedOut); cudaFree(r.normed); cudaFree(r.between);
         for (uint32_t *t : r.placement) cudaFree(t);
+        for (cudaEvent_t e : r.marks) cudaEventDestroy(e);
         if (r.hostOffsets) cudaFreeHost(r.hostOffsets);
         if (r.side) cudaStreamSynchronize(r.side);
         if (r.sent) cudaEventDestroy(r.sent);
@@ -327,9 +349,11 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
             Rank &R = g->ranks[r];
             FF_CUDA_OK(cudaSetDevice(R.device), err);
             const uint16_t *in = normFrom ? R.normed : x[r];
+            if (!mark(g, R, R.stream, err)) return false;  // kLayerStart
             if (normFrom && !ff_rmsnorm(g->home[r], normFrom[r], nullptr, eps, tokens, R.normed, R.stream, err))
                 return false;
             if (!ff_router_topk(g->home[r], layer, in, D, tokens, R.ids, R.weights, nullptr, R.stream, err)) return false;
+            if (!mark(g, R, R.stream, err)) return false;  // kRouterDone
             k_ep_destination<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.ids, routes, g->expertsPerRank, g->experts,
                                                                          R.placement[layer], R.dest);
             FF_CUDA_OK(cudaGetLastError(), err);
@@ -338,6 +362,7 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
                                        R.stream), err);
             k_ep_row_index<<<(routes + 255) / 256, 256, 0, R.stream>>>(R.pairs, routes, K, R.rowIndex);
             FF_CUDA_OK(cudaGetLastError(), err);
+            if (!mark(g, R, R.stream, err)) return false;  // kPlanQueued
             FF_CUDA_OK(cudaStreamSynchronize(R.stream), err);
             if (R.hostOffsets[world] != routes)
                 return fail(err, "the router of rank " + std::to_string(r) + " wrote an expert id out of range");
@@ -376,11 +401,12 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
                 table.first[p] = S.hostOffsets[p];
             }
             const uint32_t ctas = (routes + 7) / 8 < 1184u ? (routes + 7) / 8 : 1184u;
+            if (!mark(g, S, S.stream, err)) return false;  // kSendStart
             k_ep_send_rows<<<ctas, 256, 0, S.stream>>>(in, D, D, S.pairs, routes, S.ids, K, g->expertsPerRank,
                                                        S.placement[layer] ? S.placement[layer] + g->experts : nullptr, table);
             FF_CUDA_OK(cudaGetLastError(), err);
             FF_CUDA_OK(cudaEventRecord(S.sent, S.stream), err);
-            return true;
+            return mark(g, S, S.stream, err);  // kSendDone
         }, error))
         return false;
 
@@ -391,9 +417,11 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
             for (uint32_t s = 0; s < world; ++s)
                 if (s != p) FF_CUDA_OK(cudaStreamWaitEvent(P.stream, g->ranks[s].sent, 0), err);
             const uint32_t total = base[(size_t)p * (world + 1) + world];
+            if (!mark(g, P, P.stream, err)) return false;  // kRowsArrived
             if (total &&
                 !ff_moe_prefill(g->expert[p], layer, P.recvRows, D, total, P.recvIds, P.partials, P.stream, err))
                 return false;
+            if (!mark(g, P, P.stream, err)) return false;  // kExpertsDone
             // the partial rows go home by the copy engines on the second stream, while the SMs run the
             // shared FFN
             FF_CUDA_OK(cudaEventRecord(P.expertsDone, P.stream), err);
@@ -409,11 +437,12 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
                 else FF_CUDA_OK(cudaMemcpyPeerAsync(dst, g->ranks[s].device, src, P.device, bytes, P.side), err);
             }
             FF_CUDA_OK(cudaEventRecord(P.returned, P.side), err);
+            if (!mark(g, P, P.side, err)) return false;  // kCopiesHome
             if (withShared) {
                 const uint16_t *in = normFrom ? P.normed : x[p];
                 if (!ff_shared_ffn(g->home[p], layer, in, D, tokens, P.sharedOut, P.stream, err)) return false;
             }
-            return true;
+            return mark(g, P, P.stream, err);  // kSharedDone
         }, error))
         return false;
 
@@ -422,9 +451,35 @@ static bool run_layer(FFEPGroup *g, uint32_t layer, const uint16_t *const *x, co
         Rank &R = g->ranks[r];
         FF_CUDA_OK(cudaSetDevice(R.device), err);
         for (uint32_t p = 0; p < world; ++p) FF_CUDA_OK(cudaStreamWaitEvent(R.stream, g->ranks[p].returned, 0), err);
-        return ff_moe_reduce_indexed(g->home[r], R.back, R.rowIndex, R.weights, withShared ? R.sharedOut : nullptr, y[r],
-                                     tokens, R.stream, err);
+        if (!mark(g, R, R.stream, err)) return false;  // kPartialsArrived
+        if (!ff_moe_reduce_indexed(g->home[r], R.back, R.rowIndex, R.weights, withShared ? R.sharedOut : nullptr, y[r],
+                                   tokens, R.stream, err))
+            return false;
+        return mark(g, R, R.stream, err);  // kReduceDone
     }, error);
+}
+
+// Sums a traced call's phases per rank over its layers and drops the events.
+static bool collect_marks(FFEPGroup *g, const char **error) {
+    // phase i runs from mark kFrom[i] to mark kTo[i]
+    static const Mark kFrom[kPhases] = {kLayerStart, kRouterDone, kPlanQueued, kSendStart, kSendDone, kRowsArrived,
+                                        kExpertsDone, kExpertsDone, kSharedDone, kPartialsArrived};
+    static const Mark kTo[kPhases] = {kRouterDone, kPlanQueued, kSendStart, kSendDone, kRowsArrived, kExpertsDone,
+                                      kCopiesHome, kSharedDone, kPartialsArrived, kReduceDone};
+    g->phaseMs.assign((size_t)g->world * kPhases, 0.0);
+    for (uint32_t r = 0; r < g->world; ++r) {
+        Rank &R = g->ranks[r];
+        FF_CUDA_OK(cudaSetDevice(R.device), error);
+        for (size_t at = 0; at + kMarks <= R.marks.size(); at += kMarks)
+            for (uint32_t i = 0; i < kPhases; ++i) {
+                float ms = 0.0f;
+                FF_CUDA_OK(cudaEventElapsedTime(&ms, R.marks[at + kFrom[i]], R.marks[at + kTo[i]]), error);
+                g->phaseMs[(size_t)r * kPhases + i] += ms > 0.0f ? ms : 0.0f;
+            }
+        for (cudaEvent_t e : R.marks) cudaEventDestroy(e);
+        R.marks.clear();
+    }
+    return true;
 }
 
 // Waits for every rank's stream and reads every context's error flag.
@@ -433,7 +488,9 @@ static bool finish(FFEPGroup *g, const char **error) {
     for (uint32_t r = 0; r < world; ++r) {
         FF_CUDA_OK(cudaSetDevice(g->ranks[r].device), error);
         FF_CUDA_OK(cudaStreamSynchronize(g->ranks[r].stream), error);
+        FF_CUDA_OK(cudaStreamSynchronize(g->ranks[r].side), error);
     }
+    if (g->tracing && !collect_marks(g, error)) return false;
     for (uint32_t r = 0; r < world; ++r) {
         FFContext *both[2] = {g->home[r], g->expert[r]};
         for (FFContext *c : both) {
@@ -482,6 +539,17 @@ bool ff_ep_moe_stack(FFEPGroup *g, uint32_t firstLayer, uint32_t layerCount, con
         for (uint32_t r = 0; r < world; ++r) cur[r] = out[r];
     }
     return finish(g, error);
+}
+
+void ff_ep_set_tracing(FFEPGroup *g, bool enabled) {
+    if (g) g->tracing = enabled;
+}
+
+uint32_t ff_ep_get_phase_times(const FFEPGroup *g, double *milliseconds, uint32_t capacity) {
+    if (!g || !milliseconds) return 0;
+    uint32_t n = 0;
+    for (; n < capacity && n < g->phaseMs.size(); ++n) milliseconds[n] = g->phaseMs[n];
+    return n;
 }
 
 bool ff_ep_set_placement(FFEPGroup *g, uint32_t layer, const uint32_t *rankOf, const uint32_t *localOf,

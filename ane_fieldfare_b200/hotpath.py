@@ -596,6 +596,19 @@ class ExpertParallelGroup:
             raise ValueError("one rank and one slot per expert")
         call("ff_ep_set_placement", self._handle, layer, r.ctypes.data, l.ctypes.data)
 
+    PHASES = ("router", "plan", "host", "send", "wait_rows", "experts", "copies_home", "shared_ffn",
+              "wait_partials", "reduce")
+
+    def setTracing(self, enabled: bool):
+        binding.load().ff_ep_set_tracing(self._handle, enabled)
+
+    def phaseTimes(self) -> List[dict]:
+        """Per rank, the last traced call's milliseconds per phase, summed over its layers."""
+        world, n = len(self.home), len(self.PHASES)
+        out = (ctypes.c_double * (world * n))()
+        got = binding.load().ff_ep_get_phase_times(self._handle, out, world * n)
+        return [dict(zip(self.PHASES, out[r * n:(r + 1) * n])) for r in range(got // n)]
+
     @property
     def lastRowsSent(self) -> int:
         return int(binding.load().ff_ep_last_rows_sent(self._handle))

@@ -863,6 +863,11 @@ def run_ep_group(args):
         group.moeStack(0, layers, xs, 1e-6, ys)
         per.append(1e3 * (time.perf_counter() - t0))
     ms = float(np.median(per))
+    group.setTracing(True)
+    group.moeStack(0, layers, xs, 1e-6, ys)
+    group.setTracing(False)
+    phases = group.phaseTimes()
+    phase_max = {name: round(max(p[name] for p in phases), 3) for name in group.PHASES} if phases else {}
     flags = [int(c.info().deviceErrorFlag) for c in home + expert]
     launches = sum(int(c.info().kernelLaunches) for c in home + expert)
     tf = stack_flops(layers) / (ms * 1e-3) / 1e12
@@ -872,6 +877,9 @@ def run_ep_group(args):
           "config": {"workload": f"config4_stack_{layers}layers_{STACK_TOKENS}tokens", "tokens_per_rank": tokens_local,
                      "experts_per_rank": epr, "capacity_rows": capacity,
                      "placement": "balanced on the routes of rank 0's rows"},
+          "phase_ms_per_stack_max_over_ranks": phase_max,
+          "phase_note": "CUDA events of one traced call, summed over the layers; copies_home and shared_ffn both start "
+                        "at the end of the experts and run side by side",
           "rank0_equals_one_device_stack_bit_for_bit": same, "device_error_flags": flags,
           "kernel_launches_all_contexts": launches, "data": "synthetic"})
     group.close()

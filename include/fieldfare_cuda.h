@@ -423,6 +423,14 @@ bool ff_ep_moe_stack(FFEPGroup *group, uint32_t firstLayer, uint32_t layerCount,
  * keeps the ranks' GEMMs the same length; the blob layout of a layer file is untouched. */
 bool ff_ep_set_placement(FFEPGroup *group, uint32_t layer, const uint32_t *rankOf, const uint32_t *localOf,
                          const char **error);
+/* Tracing: while enabled, every layer of a call records CUDA events at its phase boundaries on every
+ * rank; ff_ep_get_phase_times copies the last traced call's sums over its layers, milliseconds
+ * [world][10] in rank order: router (with the stack's RMSNorm), plan (destination, sort, row index),
+ * host (the wait for the counts and the queueing of the send), send, wait for the other ranks'
+ * rows, experts, copies home (second stream, from the end of the experts), shared FFN (from the
+ * end of the experts), wait for the partial rows, reduce.  Returns the number of values written. */
+void ff_ep_set_tracing(FFEPGroup *group, bool enabled);
+uint32_t ff_ep_get_phase_times(const FFEPGroup *group, double *milliseconds, uint32_t capacity);
 /* Rows the last block sent to another GPU (each also came back as a partial row). */
 uint64_t ff_ep_last_rows_sent(const FFEPGroup *group);
 

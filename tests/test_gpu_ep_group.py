@@ -111,6 +111,15 @@ def test_group_stack_with_a_balanced_placement(world, rows):
         ys = group.moeStack(0, 2, xs, 1e-6)
         for r in range(world):
             assert torch.equal(ys[r].cpu(), wants[r].cpu()), f"rank {r} differs from the one-device stack"
+    # a traced call: the same bits, and every rank reports its ten phases
+    group.setTracing(True)
+    ys = group.moeStack(0, 2, xs, 1e-6)
+    group.setTracing(False)
+    phases = group.phaseTimes()
+    assert len(phases) == world and all(set(p) == set(group.PHASES) for p in phases)
+    assert all(v >= 0.0 for p in phases for v in p.values()) and all(p["experts"] > 0.0 for p in phases)
+    for r in range(world):
+        assert torch.equal(ys[r].cpu(), wants[r].cpu())
     group.close()
     for c in home + expert + fulls:
         assert c.info().deviceErrorFlag == 0
