@@ -516,6 +516,11 @@ static bool check_call(FFEPGroup *g, uint32_t firstLayer, uint32_t layerCount, c
     for (uint32_t r = 0; r < g->world; ++r)
         if (!x[r] || !y[r] || ((reinterpret_cast<uintptr_t>(x[r]) | reinterpret_cast<uintptr_t>(y[r])) & 15u))
             return fail(error, "rank " + std::to_string(r) + ": rows must be non-null and 16-byte aligned");
+    // marks a failed traced call left behind
+    for (Rank &R : g->ranks) {
+        for (cudaEvent_t e : R.marks) cudaEventDestroy(e);
+        R.marks.clear();
+    }
     return true;
 }
 
